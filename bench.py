@@ -1,0 +1,471 @@
+"""Benchmark of the ANI-1 AEV hot path: ani_sort -> featurize -> featurize_grad, float32, on
+1024-molecule GDB8-like batches (synthetic, seeded), in atoms per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one 1024-molecule batch.  The run keeps NB distinct
+batches resident in HBM (NB x ~43 MB of inputs and outputs, far more than the 126 MB L2) and
+cycles through them, so consecutive steps never find their data in L2.
+
+Printed keys (one JSON line, rank 0):
+  value        whole-job atoms/s with every input already in HBM, steps replayed as CUDA graphs,
+               timed with CUDA events, max over ranks
+  e2e          the same metric through the C ABI with HOST buffers: every step copies its
+               inputs (coordinates, element ids, molecule table, upstream dL/dAEV) from pinned
+               host memory and copies features and coordinate gradients back
+  roofline     HBM roofline of the dominant kernel (algorithmic bytes per launch / its average
+               duration, timed live with CUDA events; peak = measured copy bandwidth)
+  roofline_fp32  the same kernel's algorithmic flop/s against the FP32 FMA peak
+  kernels      average launch duration of each kernel of the step
+  cpu_baseline the reference's CPU kernels (oracle/_ref) or the CPU port, all host threads, on a
+               bounded sample of the same workload (N=1 only)
+  clocks       SM clock / throttle reasons sampled through NVML while the GPU was under load
+
+With --impl reference the script times only the reference's CPU implementation of the path
+(all host threads) and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "AEV fwd+grad atoms/sec (fp32, 1024-mol batch)"
+UNIT = "atoms/s"
+N_MOLS = 1024
+FEATURE_SIZE = 384
+# algorithmic work per unit: radial pair / angular triplet, forward and gradient
+FLOPS_FWD = (125, 156)
+FLOPS_GRAD = (201, 417)
+FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # SMs x lanes x FMA x max SM clock
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) in a thread."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks_setting",
+    }
+
+    def __init__(self, torch_index: int, period: float = 0.02):
+        self.samples = []
+        self.period = period
+        self._stop = threading.Event()
+        self._thread = None
+        self.sm_max = None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(torch_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:  # NVML missing: clocks are reported as unavailable
+            self.nv = None
+            self.error = repr(exc)
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                power = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                self.samples.append((time.perf_counter(), mhz, reasons, power))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self, t0: float, t1: float):
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable"}
+        window = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples
+        if not window:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        bits = 0
+        for s in window:
+            bits |= s[2]
+        reasons = [name for bit, name in self.REASONS.items() if bits & bit]
+        return {"sm_mhz": int(statistics.median(s[1] for s in window)), "sm_max_mhz": self.sm_max,
+                "reasons": reasons, "samples": len(window),
+                "power_w_max": round(max(s[3] for s in window), 1)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arms
+# ------------------------------------------------------------------------------------------
+def cpu_fwd_grad(oracle, impl, batch, up, threads):
+    """One pass of the reference CPU path on one batch (float32): sort, forward, gradient."""
+    x, y, z = batch.coords(np.float32)
+    si, gi, ac = oracle.ani_sort(batch.atomic_numbers)
+    args = (batch.atomic_numbers, batch.mol_offsets, batch.mol_atom_counts, si, ac)
+    oracle.featurize(x, y, z, *args, impl=impl, threads=threads)
+    oracle.featurize_grad(x, y, z, *args, *up, impl=impl, threads=threads)
+
+
+def cpu_baseline(batch, budget_s: float = 12.0):
+    import oracle
+    from khan_b200.data import synthetic as syn
+    impl = "ref_fast" if oracle.available("ref_fast") else "port"
+    threads = os.cpu_count() or 1
+    ac = np.bincount(batch.atomic_numbers, minlength=4)
+    up = syn.upstream_grads(batch, ac, dtype=np.float32)
+    cpu_fwd_grad(oracle, impl, batch.slice_mols(0, 64), syn.upstream_grads(
+        batch.slice_mols(0, 64), np.bincount(batch.slice_mols(0, 64).atomic_numbers, minlength=4)), threads)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        cpu_fwd_grad(oracle, impl, batch, up, threads)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s or reps >= 64:
+            break
+    return {"value": batch.n_atoms * reps / el, "unit": UNIT, "cores": threads,
+            "kind": "reference" if impl == "ref_fast" else "port",
+            "sample": f"{reps} passes over one {batch.n_mols}-molecule batch ({batch.n_atoms} atoms), "
+                      f"fwd+grad float32, {el:.1f} s",
+            "impl": impl}
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's own CPU kernels, all host threads, same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from khan_b200.data import synthetic as syn
+    impl = "ref_fast" if oracle.available("ref_fast") else "port"
+    threads = os.cpu_count() or 1
+    batch = syn.config1(seed=1, n_mols=N_MOLS)
+    # bound the sample so that warmup + steps stay within ~150 s
+    ac = np.bincount(batch.atomic_numbers, minlength=4)
+    t0 = time.perf_counter()
+    cpu_fwd_grad(oracle, impl, batch, syn.upstream_grads(batch, ac), threads)
+    one = time.perf_counter() - t0
+    total_steps = args.steps + args.warmup
+    n_mols = N_MOLS
+    while n_mols > 32 and one * (n_mols / N_MOLS) * total_steps > 150.0:
+        n_mols //= 2
+    sample = batch.slice_mols(0, n_mols)
+    up = syn.upstream_grads(sample, np.bincount(sample.atomic_numbers, minlength=4))
+    for _ in range(args.warmup):
+        cpu_fwd_grad(oracle, impl, sample, up, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_fwd_grad(oracle, impl, sample, up, threads)
+    el = time.perf_counter() - t0
+    value = sample.n_atoms * args.steps / el
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "gpu_launches": 0,
+        "config": {"workload": "config1: GDB8-like molecules, float32 fwd+grad, seed 1",
+                   "molecules_per_step": sample.n_mols, "atoms_per_step": sample.n_atoms},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads,
+                         "kind": "reference" if impl == "ref_fast" else "port",
+                         "sample": f"each step = first {sample.n_mols} molecules of the config-1 batch "
+                                   f"({sample.n_atoms} atoms), sort+fwd+grad"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2048)
+    ap.add_argument("--warmup", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batches", type=int, default=64, help="distinct batches resident in HBM")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of CUDA graphs")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 256)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from khan_b200 import _lib
+    from khan_b200.data import synthetic as syn
+    from khan_b200.staged import HostBatch, StagedBatch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()  # fail loudly if the CUDA library is missing
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # ---- workload: NB distinct 1024-molecule batches per rank (weak scaling) -------------
+    nb = max(1, min(args.batches, args.steps))
+    batches = syn.batch_pool(nb, n_mols=N_MOLS, seed=1 + 100 * rank)
+    max_atoms = max(b.n_atoms for b in batches)
+    host = []
+    for k, b in enumerate(batches):
+        ac = np.bincount(b.atomic_numbers, minlength=4)
+        host.append(HostBatch(b, syn.upstream_grads(b, ac, seed=12 + k), pin=(k < 16)))
+    staged = []
+    for hb in host:
+        sb = StagedBatch(max_atoms, N_MOLS, device=dev)
+        sb.upload(hb, non_blocking=False)
+        staged.append(sb)
+    torch.cuda.synchronize()
+    atoms_per_step = [sb.n_atoms for sb in staged]
+
+    def stream_ptr():
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # ---- warm-up: W steps, then keep going until ~1 s of device time has passed ----------
+    t_load0 = time.perf_counter()
+    for k in range(args.warmup):
+        staged[k % nb].run_step(stream_ptr())
+    torch.cuda.synchronize()
+
+    graphs = None
+    launch_mode = "eager"
+    if not args.no_graph:
+        try:
+            graphs = []
+            for sb in staged:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    sb.run_step(stream_ptr())
+                graphs.append(g)
+            launch_mode = "cuda_graph"
+        except Exception as exc:
+            print(f"[bench] CUDA graph capture failed ({exc!r}); launching eagerly", file=sys.stderr)
+            graphs = None
+            torch.cuda.synchronize()
+
+    def step(k):
+        if graphs is not None:
+            graphs[k % nb].replay()
+        else:
+            staged[k % nb].run_step(stream_ptr())
+
+    k = 0
+    while time.perf_counter() - t_load0 < 1.0 or k < args.warmup:
+        step(k)
+        k += 1
+        if k % 64 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+
+    # ---- timed region: exactly K steps -----------------------------------------------------
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_timed0 = time.perf_counter()
+    ev0.record()
+    for k in range(args.steps):
+        step(k)
+    ev1.record()
+    torch.cuda.synchronize()
+    t_timed1 = time.perf_counter()
+    if world > 1:
+        dist.barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    my_atoms = sum(atoms_per_step[k % nb] for k in range(args.steps))
+    if world > 1:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+        a = torch.tensor([my_atoms], dtype=torch.float64, device=dev)
+        dist.all_reduce(a, op=dist.ReduceOp.SUM)
+        total_atoms = float(a.item())
+    else:
+        total_atoms = float(my_atoms)
+    value = total_atoms / (elapsed_ms * 1e-3)
+
+    # ---- per-kernel durations (graphs of one kernel kind over all batches) ------------------
+    def time_kernel(fn_name):
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g):
+                for sb in staged:
+                    getattr(sb, fn_name)(stream_ptr())
+            run = g.replay
+        except Exception:
+            torch.cuda.synchronize()
+
+            def run():
+                for sb in staged:
+                    getattr(sb, fn_name)(stream_ptr())
+        reps = max(3, min(50, args.steps // nb))
+        run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / (reps * nb)
+
+    kernel_s = {"ani_sort": time_kernel("run_sort"), "featurize": time_kernel("run_featurize"),
+                "featurize_grad": time_kernel("run_featurize_grad")}
+    t_load1 = time.perf_counter()
+
+    # ---- end to end through the C ABI with host buffers ---------------------------------------
+    e2e_steps = args.e2e_steps or min(args.steps, 256)
+    n_slots = 3
+    n_host = min(len(host), 16)
+    slots = [StagedBatch(max_atoms, N_MOLS, device=dev) for _ in range(n_slots)]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(n_slots)]
+    out_feat = [torch.empty((max_atoms, FEATURE_SIZE), dtype=torch.float32).pin_memory() for _ in range(n_slots)]
+    out_grad = [torch.empty((3, max_atoms), dtype=torch.float32).pin_memory() for _ in range(n_slots)]
+
+    def e2e_pass(n_steps):
+        h2d = d2h = atoms = 0
+        for k in range(n_steps):
+            s = k % n_slots
+            hb = host[k % n_host]
+            with torch.cuda.stream(streams[s]):
+                h2d += slots[s].upload(hb, non_blocking=True)
+                slots[s].run_step(ctypes.c_void_p(streams[s].cuda_stream))
+                n = slots[s].n_atoms
+                out_feat[s][:n].copy_(slots[s].features[:n], non_blocking=True)
+                out_grad[s][:, :n].copy_(slots[s].grads[:, :n], non_blocking=True)
+                d2h += n * (FEATURE_SIZE + 3) * 4
+                atoms += n
+        return h2d, d2h, atoms
+
+    e2e_pass(6)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    main_stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(main_stream)
+    for st in streams:
+        st.wait_event(e0)
+    h2d, d2h, e2e_atoms = e2e_pass(e2e_steps)
+    for st in streams:
+        main_stream.wait_stream(st)
+    e1.record(main_stream)
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+        a = torch.tensor([e2e_atoms], dtype=torch.float64, device=dev)
+        dist.all_reduce(a, op=dist.ReduceOp.SUM)
+        e2e_total = float(a.item())
+    else:
+        e2e_total = float(e2e_atoms)
+    sampler.stop()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel --------------------------------------------------------
+    peaks, peak_kind = measured_peaks()
+    mean_atoms = sum(atoms_per_step) / nb
+    pairs, triplets = syn.count_work(batches[0])
+    p_per_atom, t_per_atom = pairs / batches[0].n_atoms, triplets / batches[0].n_atoms
+    bytes_per_atom = {"ani_sort": 4 + 8, "featurize": 16 + 4 * FEATURE_SIZE,
+                      "featurize_grad": 16 + 4 * FEATURE_SIZE + 12}
+    flops_per_atom = {"ani_sort": 0.0,
+                      "featurize": FLOPS_FWD[0] * p_per_atom + FLOPS_FWD[1] * t_per_atom,
+                      "featurize_grad": FLOPS_GRAD[0] * p_per_atom + FLOPS_GRAD[1] * t_per_atom}
+    dominant = max(kernel_s, key=kernel_s.get)
+    achieved_gbs = bytes_per_atom[dominant] * mean_atoms / kernel_s[dominant] / 1e9
+    achieved_tf = flops_per_atom[dominant] * mean_atoms / kernel_s[dominant] / 1e12
+    roofline = {"kernel": dominant, "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": None,
+                "peak_source": peak_kind,
+                "algorithmic_bytes_per_launch": bytes_per_atom[dominant] * mean_atoms}
+    roofline_fp32 = {"kernel": dominant, "achieved": achieved_tf, "peak": FP32_PEAK_TFLOPS,
+                     "unit": "TFLOP/s", "frac": achieved_tf / FP32_PEAK_TFLOPS,
+                     "peak_source": "148 SM x 128 lanes x 2 x 1.965 GHz (formula)",
+                     "pairs_per_atom": p_per_atom, "triplets_per_atom": t_per_atom}
+    step_flops = (flops_per_atom["featurize"] + flops_per_atom["featurize_grad"])
+    whole_step = {"tflops": step_flops * value / 1e12, "frac_fp32": step_flops * value / 1e12 / FP32_PEAK_TFLOPS,
+                  "gbs": 3116 * value / 1e9, "frac_hbm": 3116 * value / 1e9 / peaks["hbm_gbs"]}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config1: 1024 GDB8-like molecules per step per GPU, float32, "
+                               "ani_sort + featurize + featurize_grad",
+                   "molecules_per_step": N_MOLS, "atoms_per_step": mean_atoms,
+                   "resident_batches": nb, "l2": "inputs larger than L2 (distinct batches cycled)",
+                   "launch": launch_mode, "parallelism": f"molecule shards x{world}, no collective"},
+        "e2e": {"value": e2e_total / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": h2d / e2e_steps, "d2h_bytes_per_step": d2h / e2e_steps,
+                "steps": e2e_steps, "pipeline_slots": n_slots},
+        "gpu_launches": args.steps * StagedBatch.KERNELS_PER_STEP,
+        "kernels": {k: {"avg_us": v * 1e6} for k, v in kernel_s.items()},
+        "roofline": roofline, "roofline_fp32": roofline_fp32, "whole_step": whole_step,
+        "clocks": sampler.summary(t_load0, t_load1),
+        "clocks_timed_region": sampler.summary(t_timed0, t_timed1),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            line["cpu_baseline"] = cpu_baseline(batches[0])
+        except Exception as exc:
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port",
+                                    "sample": f"failed: {exc!r}"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,122 @@
+/*
+ * ani_b200 -- C ABI of the B200 (sm_100a) implementation of khan's ANI-1 featurizer path.
+ *
+ * Every entry point below takes the place of one piece of the reference's `ani.so`
+ * TensorFlow custom-op library (gpu_featurizer/ of proteneer/khan); the comment on each
+ * declaration names the reference interface it replaces.  The argument order follows the
+ * reference functors (gpu_featurizer/functor_op.h:8-69): inputs, then outputs, then the
+ * host-side `acs` array, then the stream.
+ *
+ * Conventions (all entry points):
+ *  - every pointer is a DEVICE pointer unless the name ends in `_host`;
+ *  - outputs are caller-allocated and fully written by the call: no pre-zeroing is needed
+ *    (the reference zero-fills inside its functors, gpu_featurizer/functor_op_cpu.cpp:31-34);
+ *  - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = default stream)
+ *    and the call returns without synchronising;
+ *  - the return value is 0 (ANI_OK) or a negative ANI_ERR_* code; nothing calls exit()
+ *    (the reference does, gpu_featurizer/functor_op_gpu.cu:12-20);
+ *  - problems that only the device can see (an element id outside 0..3, a molecule larger
+ *    than the staging limit) are recorded in a per-device status word that
+ *    ani_device_status() reads back; the offending atom/molecule is skipped or clamped,
+ *    never dereferenced out of bounds;
+ *  - n_atoms == 0 or n_mols == 0 is valid and does nothing (the reference trainer feeds
+ *    empty batches on purpose, khan/training/trainer_multi_tower.py:796-817);
+ *  - calls are re-entrant; concurrent calls on different streams/devices are independent.
+ *
+ * Element ids are the compacted ones of the reference: H 0, C 1, N 2, O 3.  The feature
+ * row of an atom has ani_feature_size() = 384 entries: 64 radial then 320 angular
+ * (gpu_featurizer/parameters.h:61-114).
+ */
+#ifndef ANI_B200_H_
+#define ANI_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ANI_OK 0
+#define ANI_ERR_NULL_POINTER (-1)   /* a required pointer argument is NULL              */
+#define ANI_ERR_BAD_SIZE (-2)       /* negative count, or acs_host inconsistent          */
+#define ANI_ERR_CUDA (-3)           /* a CUDA runtime call failed; see ani_last_cuda_error */
+#define ANI_ERR_BAD_ELEMENT (-4)    /* device saw an element id outside 0..3 (status word) */
+#define ANI_ERR_MOL_TOO_LARGE (-5)  /* device saw a molecule above ani_max_atoms_per_molecule() */
+#define ANI_ERR_BAD_INDEX (-6)      /* device saw an offset/count/scatter index out of range */
+#define ANI_ERR_TOO_MANY_ATOMS (-7) /* size beyond what an entry point supports          */
+
+/* Number of features per atom (384).  Replaces the `feature_size` attr of the Featurize op
+ * (gpu_featurizer/ani_op.cpp:104). */
+int ani_feature_size(void);
+
+/* Largest molecule (atoms) the featurizer kernels stage in shared memory. */
+int ani_max_atoms_per_molecule(void);
+
+/* Text for a status code returned by any entry point. */
+const char* ani_status_string(int status);
+
+/* cudaGetErrorString of the last CUDA failure seen by this library on the calling thread. */
+const char* ani_last_cuda_error(void);
+
+/* Synchronises `stream`, then returns and clears the current device's status word:
+ * ANI_OK or the first ANI_ERR_BAD_ELEMENT / ANI_ERR_MOL_TOO_LARGE / ANI_ERR_BAD_INDEX seen by
+ * a kernel since the last call.  No counterpart in the reference, which does not validate
+ * its inputs (an element id outside 0..3 indexes out of bounds there,
+ * gpu_featurizer/ani_sort.cpp:98-99). */
+int ani_device_status(void* stream);
+
+/*
+ * AniSort -- replaces the CPU-only op of gpu_featurizer/ani_sort.cpp:71-115
+ * (REGISTER_OP at :27-37).  Stable sort of the whole batch by element id:
+ *   scatter_idxs[i] = rank of atom i among the atoms of its element, in batch order;
+ *   gather_idxs[i]  = position of atom i in the element-sorted concatenation;
+ *   atom_counts[4]  = atoms per element (device memory, 4 ints).
+ * The input is read on the device (the reference reads it on the host).
+ */
+int ani_sort(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gather_idxs,
+             int* atom_counts, void* stream);
+
+/*
+ * Featurize -- replaces AniFunctor<Device, T> (gpu_featurizer/functor_op.h:8-25; CPU body
+ * functor_op_cpu.cpp:13-43 -> featurize_cpu, kernel_cpu.cpp:406-537; GPU body
+ * functor_op_gpu.cu:57-92 -> featurize, kernel.cu:72-268) and the op shell
+ * AniCombined::Compute (gpu_featurizer/ani_op.cpp:29-92).
+ *   xs, ys, zs [n_atoms], atomic_numbers [n_atoms], mol_offsets [n_mols],
+ *   mol_atom_counts [n_mols], scatter_idxs [n_atoms] (from ani_sort),
+ *   out_h/c/n/o: acs_host[t] * 384 values each, row-major rows of 384,
+ *   acs_host: HOST array of 4 atom counts (HostMemory input of the op, ani_op.cpp:116).
+ * An output whose acs_host[t] is 0 may be NULL.
+ */
+int ani_featurize_f32(const float* xs, const float* ys, const float* zs,
+                      const int* atomic_numbers, const int* mol_offsets,
+                      const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                      float* out_h, float* out_c, float* out_n, float* out_o,
+                      const int* acs_host, void* stream);
+int ani_featurize_f64(const double* xs, const double* ys, const double* zs,
+                      const int* atomic_numbers, const int* mol_offsets,
+                      const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                      double* out_h, double* out_c, double* out_n, double* out_o,
+                      const int* acs_host, void* stream);
+
+/*
+ * FeaturizeGrad -- replaces AniGrad<Device, T> (gpu_featurizer/functor_op.h:27-47; CPU body
+ * functor_op_cpu.cpp:48-83 -> featurize_grad_cpu, kernel_cpu.cpp:217-366) and
+ * AniCombinedGrad::Compute (gpu_featurizer/ani_op.cpp:129-196).  The reference has no GPU
+ * kernel for this op (ani_op.cpp:339-340).  Vector-Jacobian product: given dL/dfeatures in
+ * the four per-element buffers, writes dL/dx, dL/dy, dL/dz [n_atoms].
+ */
+int ani_featurize_grad_f32(const float* xs, const float* ys, const float* zs,
+                           const int* atomic_numbers, const int* mol_offsets,
+                           const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                           const float* grad_h, const float* grad_c, const float* grad_n,
+                           const float* grad_o, float* x_grads, float* y_grads, float* z_grads,
+                           const int* acs_host, void* stream);
+int ani_featurize_grad_f64(const double* xs, const double* ys, const double* zs,
+                           const int* atomic_numbers, const int* mol_offsets,
+                           const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                           const double* grad_h, const double* grad_c, const double* grad_n,
+                           const double* grad_o, double* x_grads, double* y_grads,
+                           double* z_grads, const int* acs_host, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANI_B200_H_ */

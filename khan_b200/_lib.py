@@ -1,0 +1,113 @@
+"""Loader and builder of ``libani_b200.so``, the C-ABI shared library of CUDA kernels.
+
+The library is built in-tree (``khan_b200/libani_b200.so``) by :func:`build` with nvcc for
+sm_100a only.  :func:`lib` fails loudly when the library is missing or does not load: there
+is no CPU or eager fallback anywhere in this package.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libani_b200.so")
+CSRC = os.path.join(_HERE, "csrc")
+INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
+SOURCES = ["ani_b200.cu"]
+HEADERS = ["ani_params.h", "ani_common.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_grad.cuh"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+_lock = threading.Lock()
+_lib = None
+
+c_int_p = ctypes.POINTER(ctypes.c_int)
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+
+# name -> (restype, argtypes); one entry per declaration in include/ani_b200.h
+SIGNATURES = {
+    "ani_feature_size": (_i, []),
+    "ani_max_atoms_per_molecule": (_i, []),
+    "ani_status_string": (ctypes.c_char_p, [_i]),
+    "ani_last_cuda_error": (ctypes.c_char_p, []),
+    "ani_device_status": (_i, [_vp]),
+    "ani_sort": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
+    "ani_featurize_f32": (_i, [_vp] * 6 + [_i] + [_vp] * 5 + [c_int_p, _vp]),
+    "ani_featurize_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 5 + [c_int_p, _vp]),
+    "ani_featurize_grad_f32": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
+    "ani_featurize_grad_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
+}
+
+
+def nvcc_path() -> str:
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: cannot build libani_b200.so")
+
+
+def _stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    built = os.path.getmtime(LIB_PATH)
+    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS] + [os.path.join(INCLUDE, "ani_b200.h")]
+    return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the CUDA sources for sm_100a into ``khan_b200/libani_b200.so``."""
+    with _lock:
+        if not force and not _stale():
+            return LIB_PATH
+        cmd = [nvcc_path()] + NVCC_FLAGS + ["-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
+        out = subprocess.run(cmd, capture_output=True, text=True, cwd=CSRC)
+        if verbose or out.returncode != 0:
+            print(" ".join(cmd))
+            print(out.stdout, out.stderr)
+        if out.returncode != 0:
+            raise RuntimeError("nvcc failed building libani_b200.so:\n" + out.stderr)
+        return LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library with argument types declared.  Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; "
+                "g.build()'` (needs nvcc).  khan_b200 has no CPU fallback.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the symbol is not exported
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+        return _lib
+
+
+class AniError(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().ani_status_string(status).decode()
+        if status == -3:
+            msg += ": " + lib().ani_last_cuda_error().decode()
+        super().__init__(f"{where}: {msg} (status {status})")
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise AniError(status, where)

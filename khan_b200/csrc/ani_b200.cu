@@ -1,0 +1,287 @@
+// C ABI of libani_b200.so: argument checks, launch configuration and the per-device scratch
+// cache.  All kernels live in the .cuh files included below (one translation unit, so the
+// device status word and the constant tables exist exactly once).
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <mutex>
+
+#include "ani_common.cuh"
+
+#include "ani_featurize.cuh"
+#include "ani_grad.cuh"
+#include "ani_sort.cuh"
+
+namespace {
+
+using namespace ani;
+
+thread_local cudaError_t t_last_error = cudaSuccess;
+
+int cuda_fail(cudaError_t e)
+{
+    t_last_error = e;
+    return ANI_ERR_CUDA;
+}
+
+#define ANI_CUDA(call)                                  \
+    do {                                                \
+        cudaError_t e_ = (call);                        \
+        if (e_ != cudaSuccess) return cuda_fail(e_);    \
+    } while (0)
+
+constexpr int kMaxDevices = 64;
+
+// Per-device scratch for the large-batch sort (per-tile element counts).  Grown on demand,
+// never shrunk, freed with the context.
+struct SortScratch {
+    int* ptr = nullptr;
+    size_t bytes = 0;
+};
+std::mutex g_scratch_mutex;
+SortScratch g_sort_scratch[kMaxDevices];
+
+int sort_scratch(size_t bytes, int** out)
+{
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return ANI_ERR_BAD_SIZE;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    SortScratch& s = g_sort_scratch[dev];
+    if (s.bytes < bytes) {
+        if (s.ptr) ANI_CUDA(cudaFree(s.ptr));
+        s.ptr = nullptr;
+        s.bytes = 0;
+        size_t want = bytes < (1u << 16) ? (1u << 16) : bytes * 2;
+        ANI_CUDA(cudaMalloc(&s.ptr, want));
+        s.bytes = want;
+    }
+    *out = s.ptr;
+    return ANI_OK;
+}
+
+// Featurizer launch shapes.  NW warps per CTA, one CTA per (molecule, split); the list
+// capacities bound the neighbours kept in shared memory per central atom (atoms with more
+// take the streaming path).
+constexpr int kNW = 4;
+constexpr int kACap = 48;
+constexpr int kRCap = 96;
+
+int pick_nsplit(long long n_atoms, int n_mols)
+{
+    // about 16 central atoms per CTA: small molecules get one CTA, large ones several
+    const long long avg = n_mols > 0 ? (n_atoms + n_mols - 1) / n_mols : 1;
+    long long s = (avg + 15) / 16;
+    if (s < 1) s = 1;
+    if (s > 32) s = 32;
+    return (int)s;
+}
+
+template <typename K> int set_smem(K kernel, size_t bytes)
+{
+    ANI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    return ANI_OK;
+}
+
+int check_acs(const int* acs_host, long long* n_atoms)
+{
+    if (!acs_host) return ANI_ERR_NULL_POINTER;
+    long long n = 0;
+    for (int t = 0; t < kTypes; t++) {
+        if (acs_host[t] < 0) return ANI_ERR_BAD_SIZE;
+        n += acs_host[t];
+    }
+    if (n > 0x7fffffffLL) return ANI_ERR_TOO_MANY_ATOMS;
+    *n_atoms = n;
+    return ANI_OK;
+}
+
+template <typename T, int ACAP = kACap, int RCAP = kRCap>
+int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, const int* mos,
+                   const int* macs, int n_mols, const int* sis, T* oh, T* oc, T* on, T* oo,
+                   const int* acs_host, void* stream)
+{
+    long long n_atoms = 0;
+    if (int rc = check_acs(acs_host, &n_atoms)) return rc;
+    if (n_mols < 0) return ANI_ERR_BAD_SIZE;
+    if (n_mols == 0 || n_atoms == 0) return ANI_OK;
+    if (!xs || !ys || !zs || !types || !mos || !macs || !sis) return ANI_ERR_NULL_POINTER;
+    T* outs[kTypes] = {oh, oc, on, oo};
+    for (int t = 0; t < kTypes; t++)
+        if (acs_host[t] > 0 && !outs[t]) return ANI_ERR_NULL_POINTER;
+
+    auto kernel = featurize_kernel<T, kNW, ACAP, RCAP>;
+    const size_t smem = sizeof(FeaturizeShared<T, kNW, ACAP, RCAP>);
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        if (int rc = set_smem(kernel, smem)) return rc;
+        configured_dev = dev;
+    }
+    const int nsplit = pick_nsplit(n_atoms, n_mols);
+    const long long items = (long long)n_mols * nsplit;
+    const int grid = (int)(items < (1 << 20) ? items : (1 << 20));
+    kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
+        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, oh, oc, on, oo, acs_host[0],
+        acs_host[1], acs_host[2], acs_host[3], nsplit);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+template <typename T, int ACAP = kACap, int RCAP = kRCap>
+int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types, const int* mos,
+                        const int* macs, int n_mols, const int* sis, const T* gh, const T* gc,
+                        const T* gn, const T* go, T* gx, T* gy, T* gz, const int* acs_host,
+                        void* stream)
+{
+    long long n_atoms = 0;
+    if (int rc = check_acs(acs_host, &n_atoms)) return rc;
+    if (n_mols < 0) return ANI_ERR_BAD_SIZE;
+    if (n_atoms == 0) return ANI_OK;
+    if (!gx || !gy || !gz) return ANI_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    {
+        const int threads = 256;
+        long long blocks = (n_atoms + threads - 1) / threads;
+        if (blocks > 1184) blocks = 1184;
+        zero3_kernel<T><<<(int)blocks, threads, 0, st>>>(gx, gy, gz, (int)n_atoms);
+        ANI_CUDA(cudaGetLastError());
+    }
+    if (n_mols == 0) return ANI_OK;
+    if (!xs || !ys || !zs || !types || !mos || !macs || !sis) return ANI_ERR_NULL_POINTER;
+    const T* gin[kTypes] = {gh, gc, gn, go};
+    for (int t = 0; t < kTypes; t++)
+        if (acs_host[t] > 0 && !gin[t]) return ANI_ERR_NULL_POINTER;
+
+    auto kernel = featurize_grad_kernel<T, kNW, ACAP, RCAP>;
+    const size_t smem = sizeof(GradShared<T, kNW, ACAP, RCAP>);
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        if (int rc = set_smem(kernel, smem)) return rc;
+        configured_dev = dev;
+    }
+    const int nsplit = pick_nsplit(n_atoms, n_mols);
+    const long long items = (long long)n_mols * nsplit;
+    const int grid = (int)(items < (1 << 20) ? items : (1 << 20));
+    kernel<<<grid, kNW * kWarp, smem, st>>>(xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms,
+                                            sis, gh, gc, gn, go, gx, gy, gz, acs_host[0],
+                                            acs_host[1], acs_host[2], acs_host[3], nsplit);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ani_feature_size(void) { return ani::kTotal; }
+
+int ani_max_atoms_per_molecule(void) { return ani::kMaxAtomsPerMol; }
+
+const char* ani_status_string(int status)
+{
+    switch (status) {
+        case ANI_OK: return "ok";
+        case ANI_ERR_NULL_POINTER: return "a required pointer argument is NULL";
+        case ANI_ERR_BAD_SIZE: return "negative or inconsistent size argument";
+        case ANI_ERR_CUDA: return "CUDA runtime error (see ani_last_cuda_error)";
+        case ANI_ERR_BAD_ELEMENT: return "element id outside 0..3 in atomic_numbers";
+        case ANI_ERR_MOL_TOO_LARGE: return "molecule larger than ani_max_atoms_per_molecule()";
+        case ANI_ERR_BAD_INDEX: return "molecule offset/count or scatter index out of range";
+        case ANI_ERR_TOO_MANY_ATOMS: return "size beyond what this entry point supports";
+        default: return "unknown status";
+    }
+}
+
+const char* ani_last_cuda_error(void) { return cudaGetErrorString(t_last_error); }
+
+int ani_device_status(void* stream)
+{
+    ANI_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    int v = 0;
+    ANI_CUDA(cudaMemcpyFromSymbol(&v, ani::g_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        ANI_CUDA(cudaMemcpyToSymbol(ani::g_status, &zero, sizeof(int)));
+    }
+    return v;
+}
+
+int ani_sort(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gather_idxs,
+             int* atom_counts, void* stream)
+{
+    if (n_atoms < 0) return ANI_ERR_BAD_SIZE;
+    if (!atom_counts) return ANI_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_atoms == 0) {
+        sort_empty_kernel<<<1, 32, 0, st>>>(atom_counts);
+        ANI_CUDA(cudaGetLastError());
+        return ANI_OK;
+    }
+    if (!atomic_numbers || !scatter_idxs || !gather_idxs) return ANI_ERR_NULL_POINTER;
+    const int n_tiles = (n_atoms + kSortTile - 1) / kSortTile;
+    if (n_atoms <= kSortSingleLaunchMax) {
+        sort_single_kernel<<<n_tiles, kSortThreads, 0, st>>>(atomic_numbers, n_atoms, scatter_idxs,
+                                                             gather_idxs, atom_counts);
+        ANI_CUDA(cudaGetLastError());
+        return ANI_OK;
+    }
+    int* scratch = nullptr;
+    if (int rc = sort_scratch((size_t)(n_tiles + 1) * kTypes * sizeof(int), &scratch)) return rc;
+    sort_histogram_kernel<<<n_tiles, kSortThreads, 0, st>>>(atomic_numbers, n_atoms, scratch);
+    ANI_CUDA(cudaGetLastError());
+    sort_scan_kernel<<<1, kSortThreads, 0, st>>>(scratch, n_tiles);
+    ANI_CUDA(cudaGetLastError());
+    sort_rank_kernel<<<n_tiles, kSortThreads, 0, st>>>(atomic_numbers, n_atoms, scratch, n_tiles,
+                                                       scatter_idxs, gather_idxs, atom_counts);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+int ani_featurize_f32(const float* xs, const float* ys, const float* zs, const int* atomic_numbers,
+                      const int* mol_offsets, const int* mol_atom_counts, int n_mols,
+                      const int* scatter_idxs, float* out_h, float* out_c, float* out_n,
+                      float* out_o, const int* acs_host, void* stream)
+{
+    return featurize_impl<float>(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, n_mols,
+                                 scatter_idxs, out_h, out_c, out_n, out_o, acs_host, stream);
+}
+
+int ani_featurize_f64(const double* xs, const double* ys, const double* zs,
+                      const int* atomic_numbers, const int* mol_offsets, const int* mol_atom_counts,
+                      int n_mols, const int* scatter_idxs, double* out_h, double* out_c,
+                      double* out_n, double* out_o, const int* acs_host, void* stream)
+{
+    return featurize_impl<double>(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, n_mols,
+                                  scatter_idxs, out_h, out_c, out_n, out_o, acs_host, stream);
+}
+
+int ani_featurize_grad_f32(const float* xs, const float* ys, const float* zs,
+                           const int* atomic_numbers, const int* mol_offsets,
+                           const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                           const float* grad_h, const float* grad_c, const float* grad_n,
+                           const float* grad_o, float* x_grads, float* y_grads, float* z_grads,
+                           const int* acs_host, void* stream)
+{
+    return featurize_grad_impl<float>(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
+                                      n_mols, scatter_idxs, grad_h, grad_c, grad_n, grad_o,
+                                      x_grads, y_grads, z_grads, acs_host, stream);
+}
+
+int ani_featurize_grad_f64(const double* xs, const double* ys, const double* zs,
+                           const int* atomic_numbers, const int* mol_offsets,
+                           const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                           const double* grad_h, const double* grad_c, const double* grad_n,
+                           const double* grad_o, double* x_grads, double* y_grads,
+                           double* z_grads, const int* acs_host, void* stream)
+{
+    return featurize_grad_impl<double>(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
+                                       n_mols, scatter_idxs, grad_h, grad_c, grad_n, grad_o,
+                                       x_grads, y_grads, z_grads, acs_host, stream);
+}
+
+}  // extern "C"

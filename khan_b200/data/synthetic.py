@@ -175,3 +175,41 @@ def kat_fixture():
     return Batch(atom_matrix[:, 1].copy(), atom_matrix[:, 2].copy(), atom_matrix[:, 3].copy(),
                  atom_matrix[:, 0].astype(np.int32), np.array([0, 8], np.int32),
                  np.array([8, 3], np.int32))
+
+
+def count_work(batch: Batch):
+    """(radial pairs P, angular triplets T) of a batch, float32 distances as the float32 kernels
+    see them: P = unordered pairs with r < 4.6, T = sum over atoms of C(n_ang, 2) with n_ang the
+    neighbours closer than 3.1.  Used to turn a measured time into algorithmic flop/s."""
+    xs, ys, zs = batch.coords(np.float32)
+    pairs = 0
+    triplets = 0
+    for off, cnt in zip(batch.mol_offsets, batch.mol_atom_counts):
+        sl = slice(int(off), int(off + cnt))
+        p = np.stack([xs[sl], ys[sl], zs[sl]], axis=1)
+        d = p[:, None, :] - p[None, :, :]
+        r = np.sqrt((d * d).sum(-1, dtype=np.float32))
+        np.fill_diagonal(r, np.inf)
+        pairs += int((r < np.float32(4.6)).sum()) // 2
+        n_ang = (r < np.float32(3.1)).sum(1)
+        triplets += int((n_ang * (n_ang - 1) // 2).sum())
+    return pairs, triplets
+
+
+def batch_pool(n_batches: int, n_mols: int = 1024, seed: int = 1, pool_factor: int = 4):
+    """``n_batches`` distinct config-1-like batches.  Batch 0 is exactly ``config1(seed)``; the
+    others draw ``n_mols`` molecules from a pool of ``pool_factor * n_mols`` generated ones and
+    apply fresh N(0, 0.05 A) jitter, which is much cheaper than generating every batch anew."""
+    first = config1(seed=seed, n_mols=n_mols)
+    if n_batches <= 1:
+        return [first]
+    pool = gdb_like_batch(pool_factor * n_mols, seed + 1000, heavy_min=1, heavy_max=8)
+    mols = pool.molecules()
+    rng = np.random.default_rng(seed + 2000)
+    out = [first]
+    for _ in range(n_batches - 1):
+        pick = rng.choice(len(mols), size=n_mols, replace=False)
+        chosen = [(mols[i][:, 0].astype(np.int32), mols[i][:, 1:] + rng.normal(0.0, 0.05, mols[i][:, 1:].shape))
+                  for i in pick]
+        out.append(_assemble(chosen))
+    return out

@@ -1,0 +1,65 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/ani_b200.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from khan_b200 import _lib
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ani_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ani_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def handle():
+    _lib.build()
+    return _lib.lib()
+
+
+def test_header_and_signature_table_agree():
+    assert declared_symbols() == sorted(_lib.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol(handle):
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(raw, name), name
+
+
+def test_host_only_entry_points(handle):
+    assert handle.ani_feature_size() == 384
+    assert handle.ani_max_atoms_per_molecule() >= 256
+    assert handle.ani_status_string(0) == b"ok"
+    for code in range(-7, 0):
+        assert handle.ani_status_string(code) != b"unknown status"
+
+
+def test_argument_checks_need_no_gpu(handle):
+    four = (ctypes.c_int * 4)(0, 0, 0, 0)
+    # empty batch: valid, does nothing
+    assert handle.ani_featurize_f32(None, None, None, None, None, None, 0, None, None, None, None,
+                                    None, four, None) == 0
+    assert handle.ani_featurize_grad_f64(None, None, None, None, None, None, 0, None, None, None,
+                                         None, None, None, None, None, four, None) == 0
+    # missing acs / negative sizes are rejected before anything is launched
+    assert handle.ani_featurize_f32(None, None, None, None, None, None, 0, None, None, None, None,
+                                    None, None, None) == -1
+    bad = (ctypes.c_int * 4)(1, -1, 0, 0)
+    assert handle.ani_featurize_f32(None, None, None, None, None, None, 1, None, None, None, None,
+                                    None, bad, None) == -2
+    assert handle.ani_sort(None, -1, None, None, None, None) == -2
+    one = (ctypes.c_int * 4)(1, 0, 0, 0)
+    assert handle.ani_featurize_f32(None, None, None, None, None, None, 1, None, None, None, None,
+                                    None, one, None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(_lib, "_lib", None)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _lib.lib()

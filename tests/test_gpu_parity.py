@@ -1,0 +1,273 @@
+"""GPU parity: the CUDA path, called through the C ABI (ani_mod -> ctypes -> libani_b200.so),
+against the CPU oracle and the committed golden vectors of the reference.
+
+Tolerances (normwise, max|a-b| <= tol * max|b| per output array):
+  features   float32 1e-5 vs the float32 reference;   float64 1e-12
+  gradients  float32 1e-5 vs the float64 reference evaluated on the float32-rounded inputs
+             (the reference's float32 gradient is non-finite on part of realistic inputs);
+             float64 1e-12
+Sort indices are compared bit for bit.
+"""
+import numpy as np
+import pytest
+
+from conftest import normwise
+from khan_b200.data import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+
+ELEMS = "hcno"
+FTOL = {np.float32: 1e-5, np.float64: 1e-12}
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import gpu_util
+    return gpu_util
+
+
+@pytest.fixture(scope="module")
+def ref_impl(oracle_mod):
+    return oracle_mod.best_impl()
+
+
+# --------------------------------------------------------------------------- sort
+def test_sort_known_answer(gpu):
+    b = syn.kat_fixture()
+    si, gi, ac = gpu.gpu_sort(b.atomic_numbers)
+    np.testing.assert_array_equal(ac, [6, 2, 3, 0])
+    np.testing.assert_array_equal(si, [0, 0, 1, 0, 1, 2, 3, 4, 5, 1, 2])
+    np.testing.assert_array_equal(gi, [0, 8, 1, 6, 9, 2, 3, 4, 5, 7, 10])
+
+
+@pytest.mark.parametrize("n", [0, 1, 31, 32, 33, 1023, 1024, 1025, 4097, 13727, 65536, 65537,
+                               200001, 3000017])
+def test_sort_bit_exact(gpu, oracle_mod, n):
+    rng = np.random.default_rng(n)
+    p = rng.dirichlet(np.ones(4)) if n % 2 else np.array([0.67, 0.24, 0.045, 0.045])
+    a = rng.choice(4, size=n, p=p).astype(np.int32)
+    si, gi, ac = gpu.gpu_sort(a)
+    esi, egi, eac = oracle_mod.ani_sort(a)
+    np.testing.assert_array_equal(ac, eac)
+    np.testing.assert_array_equal(si, esi)
+    np.testing.assert_array_equal(gi, egi)
+
+
+def test_sort_single_element_and_sorted_inputs(gpu, oracle_mod):
+    for a in (np.zeros(5000, np.int32), np.full(70000, 3, np.int32),
+              np.sort(np.random.default_rng(0).integers(0, 4, 9000)).astype(np.int32),
+              np.sort(np.random.default_rng(1).integers(0, 4, 9000))[::-1].astype(np.int32)):
+        si, gi, ac = gpu.gpu_sort(a)
+        esi, egi, eac = oracle_mod.ani_sort(a)
+        np.testing.assert_array_equal(ac, eac)
+        np.testing.assert_array_equal(si, esi)
+        np.testing.assert_array_equal(gi, egi)
+
+
+def test_sort_rejects_bad_element(gpu):
+    from khan_b200 import ani_mod
+    a = np.array([0, 1, 7, 2], np.int32)
+    gpu.gpu_sort(a)
+    assert ani_mod.device_status() == -4
+    assert ani_mod.device_status() == 0  # reading clears it
+
+
+# --------------------------------------------------------------------------- forward
+@pytest.mark.parametrize("fixture", ["kat.npz", "c0_head.npz"])
+@pytest.mark.parametrize("tag,dt", [("f32", np.float32), ("f64", np.float64)])
+def test_forward_golden(gpu, golden, fixture, tag, dt):
+    g = golden(fixture)
+    b = syn.Batch(g["xs"], g["ys"], g["zs"], g["atomic_numbers"], g["mol_offsets"],
+                  g["mol_atom_counts"])
+    feats = gpu.gpu_featurize(b, dt)
+    for t, e in enumerate(ELEMS):
+        assert feats[t].shape == g[f"feat_{e}_{tag}"].shape
+        assert normwise(feats[t], g[f"feat_{e}_{tag}"]) < FTOL[dt]
+
+
+def test_forward_config0_checksums(gpu, golden):
+    g = golden("c0_sums.npz")
+    b = syn.Batch(g["xs"], g["ys"], g["zs"], g["atomic_numbers"], g["mol_offsets"],
+                  g["mol_atom_counts"])
+    for tag, dt, tol in (("f32", np.float32, 1e-5), ("f64", np.float64, 1e-12)):
+        feats = gpu.gpu_featurize(b, dt)
+        s = np.array([f.astype(np.float64).sum() for f in feats])
+        s2 = np.array([(f.astype(np.float64) ** 2).sum() for f in feats])
+        np.testing.assert_allclose(s, g["sum_" + tag], rtol=tol * 10)
+        np.testing.assert_allclose(s2, g["sumsq_" + tag], rtol=tol * 10)
+
+
+CASES = {
+    "config0": lambda: syn.config0(),
+    "config1": lambda: syn.config1(),
+    "config4_part": lambda: syn.config4(n_mols=12),
+    "tiny_mols": lambda: syn.gdb_like_batch(40, 7, heavy_min=1, heavy_max=1),
+    "mid_33_to_70_atoms": lambda: syn.config4(seed=9, n_mols=6, n_min=33, n_max=70),
+}
+
+
+@pytest.mark.parametrize("case", list(CASES))
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_forward_vs_oracle(gpu, oracle_mod, ref_impl, case, dt):
+    b = CASES[case]()
+    si, gi, ac = oracle_mod.ani_sort(b.atomic_numbers)
+    x, y, z = b.coords(dt)
+    ref = oracle_mod.featurize(x, y, z, b.atomic_numbers, b.mol_offsets, b.mol_atom_counts, si, ac,
+                               impl=ref_impl, threads=8)
+    feats = gpu.gpu_featurize(b, dt)
+    for t in range(4):
+        assert feats[t].shape == ref[t].shape
+        assert normwise(feats[t], ref[t]) < FTOL[dt], (case, t)
+
+
+def test_forward_is_bit_reproducible(gpu):
+    b = syn.config1(n_mols=256)
+    one = gpu.gpu_featurize(b, np.float32)
+    two = gpu.gpu_featurize(b, np.float32)
+    for a, c in zip(one, two):
+        np.testing.assert_array_equal(a, c)
+
+
+def test_forward_overwrites_stale_output(gpu, oracle_mod):
+    # no pre-zero requirement: rows are fully written even where the features are zero
+    import torch
+    from khan_b200 import ani_mod
+    b = syn.kat_fixture()
+    x, y, z, a, mo, mac = gpu.batch_tensors(b, np.float32)
+    si, gi, ac = ani_mod.ani_sort(a)
+    acs = ac.cpu().numpy()
+    out = torch.full((b.n_atoms, 384), float("nan"), device=x.device)
+    ani_mod.featurize_into(x, y, z, a, mo, mac, si, acs, out)
+    assert torch.isfinite(out).all()
+
+
+# --------------------------------------------------------------------------- gradient
+@pytest.mark.parametrize("fixture", ["kat.npz", "c0_head.npz"])
+@pytest.mark.parametrize("tag,dt", [("f32", np.float32), ("f64", np.float64)])
+def test_gradient_golden(gpu, golden, fixture, tag, dt):
+    g = golden(fixture)
+    b = syn.Batch(g["xs"], g["ys"], g["zs"], g["atomic_numbers"], g["mol_offsets"],
+                  g["mol_atom_counts"])
+    up = [g["up_" + e] for e in ELEMS]
+    out = gpu.gpu_featurize_grad(b, dt, up)
+    for k, c in enumerate("xyz"):
+        assert np.isfinite(out[k]).all()
+        assert normwise(out[k], g[f"grad_{c}_{tag}"]) < FTOL[dt]
+
+
+@pytest.mark.parametrize("case", list(CASES))
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_gradient_vs_oracle(gpu, oracle_mod, case, dt):
+    b = CASES[case]()
+    si, gi, ac = oracle_mod.ani_sort(b.atomic_numbers)
+    up = syn.upstream_grads(b, ac, dtype=dt)
+    x, y, z = b.coords(dt)
+    ref = oracle_mod.featurize_grad(*(v.astype(np.float64) for v in (x, y, z)), b.atomic_numbers,
+                                    b.mol_offsets, b.mol_atom_counts, si, ac,
+                                    *[u.astype(np.float64) for u in up], impl="port", threads=8)
+    out = gpu.gpu_featurize_grad(b, dt, up)
+    for k in range(3):
+        assert np.isfinite(out[k]).all()
+        assert normwise(out[k], ref[k]) < FTOL[dt], (case, k)
+
+
+def test_gradient_sums_to_zero_per_molecule(gpu):
+    # translation invariance, a size-independent property checked at the full config-1 size
+    b = syn.config1()
+    ac = np.bincount(b.atomic_numbers, minlength=4)
+    up = syn.upstream_grads(b, ac, dtype=np.float64)
+    out = gpu.gpu_featurize_grad(b, np.float64, up)
+    for k in range(3):
+        per_mol = np.add.reduceat(out[k], b.mol_offsets)
+        assert np.abs(per_mol).max() < 1e-9 * np.abs(out[k]).max()
+
+
+def test_gradient_finite_differences_on_gpu(gpu):
+    # gpu_featurizer/test_kernel.py:463-535 with the double settings (delta 1e-6, tol 1e-9 there;
+    # central differences here)
+    b = syn.kat_fixture()
+    ac = np.bincount(b.atomic_numbers, minlength=4)
+    rng = np.random.default_rng(2)
+    up = [rng.normal(size=int(c) * 384) for c in ac]
+    grads = gpu.gpu_featurize_grad(b, np.float64, up)
+
+    def loss(xs):
+        bb = syn.Batch(xs, b.ys, b.zs, b.atomic_numbers, b.mol_offsets, b.mol_atom_counts)
+        f = gpu.gpu_featurize(bb, np.float64)
+        return sum(float((a * c).sum()) for a, c in zip(f, up))
+
+    for i in range(b.n_atoms):
+        xp, xm = b.xs.copy(), b.xs.copy()
+        xp[i] += 1e-6
+        xm[i] -= 1e-6
+        assert abs((loss(xp) - loss(xm)) / 2e-6 - grads[0][i]) < 1e-6
+
+
+# --------------------------------------------------------------------------- edge cases
+def test_empty_batch(gpu):
+    import torch
+    from khan_b200 import ani_mod
+    e = torch.zeros(0, device=gpu.DEV)
+    ei = torch.zeros(0, dtype=torch.int32, device=gpu.DEV)
+    si, gi, ac = ani_mod.ani_sort(ei)
+    assert ac.cpu().tolist() == [0, 0, 0, 0]
+    feats = ani_mod.featurize(e, e, e, ei, ei, ei, si, ac)
+    assert all(f.numel() == 0 for f in feats)
+    gx, gy, gz = ani_mod.featurize_grad(e, e, e, ei, ei, ei, si, ac, *feats)
+    assert gx.numel() == 0
+
+
+def test_dense_cluster_takes_the_streaming_path(gpu, oracle_mod):
+    # 120 atoms inside a 3 A sphere: more neighbours than the shared-memory lists hold
+    rng = np.random.default_rng(5)
+    n = 120
+    pos = np.zeros((n, 3))
+    k = 0
+    while k < n:
+        c = rng.uniform(-3.0, 3.0, 3)
+        if c @ c > 9.0 or (k and np.min(np.sum((pos[:k] - c) ** 2, axis=1)) < 0.49):
+            continue
+        pos[k] = c
+        k += 1
+    types = rng.integers(0, 4, n).astype(np.int32)
+    b = syn.Batch(pos[:, 0].copy(), pos[:, 1].copy(), pos[:, 2].copy(), types,
+                  np.array([0], np.int32), np.array([n], np.int32))
+    si, gi, ac = oracle_mod.ani_sort(types)
+    for dt in (np.float32, np.float64):
+        x, y, z = b.coords(dt)
+        ref = oracle_mod.featurize(x, y, z, types, b.mol_offsets, b.mol_atom_counts, si, ac)
+        feats = gpu.gpu_featurize(b, dt)
+        for t in range(4):
+            assert normwise(feats[t], ref[t]) < FTOL[dt]
+        up = syn.upstream_grads(b, ac, dtype=dt)
+        gref = oracle_mod.featurize_grad(*(v.astype(np.float64) for v in (x, y, z)), types,
+                                         b.mol_offsets, b.mol_atom_counts, si, ac,
+                                         *[u.astype(np.float64) for u in up])
+        out = gpu.gpu_featurize_grad(b, dt, up)
+        for k in range(3):
+            assert normwise(out[k], gref[k]) < FTOL[dt]
+
+
+def test_molecule_above_staging_limit_is_reported(gpu):
+    from khan_b200 import _lib, ani_mod
+    n = _lib.lib().ani_max_atoms_per_molecule() + 1
+    rng = np.random.default_rng(0)
+    b = syn.Batch(rng.uniform(0, 30, n), rng.uniform(0, 30, n), rng.uniform(0, 30, n),
+                  np.zeros(n, np.int32), np.array([0], np.int32), np.array([n], np.int32))
+    x, y, z, a, mo, mac = gpu.batch_tensors(b, np.float32)
+    si, gi, ac = ani_mod.ani_sort(a)
+    ani_mod.featurize(x, y, z, a, mo, mac, si, ac)
+    assert ani_mod.device_status() == -5
+
+
+def test_inconsistent_offsets_are_reported_not_dereferenced(gpu):
+    import torch
+    from khan_b200 import ani_mod
+    b = syn.kat_fixture()
+    x, y, z, a, mo, mac = gpu.batch_tensors(b, np.float32)
+    si, gi, ac = ani_mod.ani_sort(a)
+    bad_mo = torch.tensor([0, 9], dtype=torch.int32, device=x.device)  # 9 + 3 > 11 atoms
+    ani_mod.featurize(x, y, z, a, bad_mo, mac, si, ac)
+    assert ani_mod.device_status() == -6
