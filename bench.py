@@ -212,13 +212,17 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2048)
+    ap.add_argument("--steps", type=int, default=4096)
     ap.add_argument("--warmup", type=int, default=64)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batches", type=int, default=64, help="distinct batches resident in HBM")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of CUDA graphs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 256)")
+    ap.add_argument("--streams", type=int, default=4,
+                    help="independent batches in flight: steps are issued round-robin over this many streams")
+    ap.add_argument("--profile", action="store_true",
+                    help="only W warm-up and K timed steps, launched eagerly on one stream (for ncu)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -272,7 +276,21 @@ def main():
         staged[k % nb].run_step(stream_ptr())
     torch.cuda.synchronize()
 
-    graphs = None
+    if args.profile:
+        for k in range(args.steps):
+            staged[k % nb].run_step(stream_ptr())
+        torch.cuda.synchronize()
+        sampler.stop()
+        print(json.dumps({"profile_run": True, "steps": args.steps, "warmup": args.warmup}))
+        return
+
+    # Steps of different batches are independent, so they are issued round-robin over a few
+    # streams: the tail of one batch's kernels overlaps the head of the next batch's.  All
+    # NB steps are captured into ONE graph (fork from the capture stream, one branch per
+    # stream, join), plus one single-step graph per batch for the remainder K mod NB.
+    n_streams = max(1, min(args.streams, nb))
+    side = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
+    graphs = mega = None
     launch_mode = "eager"
     if not args.no_graph:
         try:
@@ -282,25 +300,45 @@ def main():
                 with torch.cuda.graph(g):
                     sb.run_step(stream_ptr())
                 graphs.append(g)
+            mega = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(mega):
+                cap = torch.cuda.current_stream()
+                for st in side:
+                    st.wait_stream(cap)
+                for b, sb in enumerate(staged):
+                    st = side[b % n_streams]
+                    with torch.cuda.stream(st):
+                        sb.run_step(ctypes.c_void_p(st.cuda_stream))
+                for st in side:
+                    cap.wait_stream(st)
             launch_mode = "cuda_graph"
         except Exception as exc:
             print(f"[bench] CUDA graph capture failed ({exc!r}); launching eagerly", file=sys.stderr)
-            graphs = None
+            graphs = mega = None
             torch.cuda.synchronize()
 
-    def step(k):
-        if graphs is not None:
-            graphs[k % nb].replay()
+    def run_steps(n_steps):
+        """Issues exactly n_steps steps (batches 0, 1, 2, ... cyclically)."""
+        done = 0
+        if mega is not None:
+            while n_steps - done >= nb:
+                mega.replay()
+                done += nb
+            for k in range(n_steps - done):
+                graphs[k].replay()
         else:
-            staged[k % nb].run_step(stream_ptr())
+            main = torch.cuda.current_stream()
+            for st in side:
+                st.wait_stream(main)
+            for k in range(n_steps):
+                st = side[k % n_streams]
+                staged[k % nb].run_step(ctypes.c_void_p(st.cuda_stream))
+            for st in side:
+                main.wait_stream(st)
 
-    k = 0
-    while time.perf_counter() - t_load0 < 1.0 or k < args.warmup:
-        step(k)
-        k += 1
-        if k % 64 == 0:
-            torch.cuda.synchronize()
-    torch.cuda.synchronize()
+    while time.perf_counter() - t_load0 < 1.0:
+        run_steps(nb)
+        torch.cuda.synchronize()
 
     # ---- timed region: exactly K steps -----------------------------------------------------
     if world > 1:
@@ -309,8 +347,7 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_timed0 = time.perf_counter()
     ev0.record()
-    for k in range(args.steps):
-        step(k)
+    run_steps(args.steps)
     ev1.record()
     torch.cuda.synchronize()
     t_timed1 = time.perf_counter()
@@ -446,7 +483,8 @@ def main():
                                "ani_sort + featurize + featurize_grad",
                    "molecules_per_step": N_MOLS, "atoms_per_step": mean_atoms,
                    "resident_batches": nb, "l2": "inputs larger than L2 (distinct batches cycled)",
-                   "launch": launch_mode, "parallelism": f"molecule shards x{world}, no collective"},
+                   "launch": launch_mode, "streams": n_streams,
+                   "parallelism": f"molecule shards x{world}, no collective"},
         "e2e": {"value": e2e_total / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": h2d / e2e_steps, "d2h_bytes_per_step": d2h / e2e_steps,
                 "steps": e2e_steps, "pipeline_slots": n_slots},

@@ -15,8 +15,8 @@
  *    and the call returns without synchronising;
  *  - the return value is 0 (ANI_OK) or a negative ANI_ERR_* code; nothing calls exit()
  *    (the reference does, gpu_featurizer/functor_op_gpu.cu:12-20);
- *  - problems that only the device can see (an element id outside 0..3, a molecule larger
- *    than the staging limit) are recorded in a per-device status word that
+ *  - problems that only the device can see (an element id outside 0..3, a molecule range or
+ *    scatter index outside the batch) are recorded in a per-device status word that
  *    ani_device_status() reads back; the offending atom/molecule is skipped or clamped,
  *    never dereferenced out of bounds;
  *  - n_atoms == 0 or n_mols == 0 is valid and does nothing (the reference trainer feeds
@@ -39,16 +39,12 @@ extern "C" {
 #define ANI_ERR_BAD_SIZE (-2)       /* negative count, or acs_host inconsistent          */
 #define ANI_ERR_CUDA (-3)           /* a CUDA runtime call failed; see ani_last_cuda_error */
 #define ANI_ERR_BAD_ELEMENT (-4)    /* device saw an element id outside 0..3 (status word) */
-#define ANI_ERR_MOL_TOO_LARGE (-5)  /* device saw a molecule above ani_max_atoms_per_molecule() */
 #define ANI_ERR_BAD_INDEX (-6)      /* device saw an offset/count/scatter index out of range */
 #define ANI_ERR_TOO_MANY_ATOMS (-7) /* size beyond what an entry point supports          */
 
 /* Number of features per atom (384).  Replaces the `feature_size` attr of the Featurize op
  * (gpu_featurizer/ani_op.cpp:104). */
 int ani_feature_size(void);
-
-/* Largest molecule (atoms) the featurizer kernels stage in shared memory. */
-int ani_max_atoms_per_molecule(void);
 
 /* Text for a status code returned by any entry point. */
 const char* ani_status_string(int status);
@@ -57,7 +53,7 @@ const char* ani_status_string(int status);
 const char* ani_last_cuda_error(void);
 
 /* Synchronises `stream`, then returns and clears the current device's status word:
- * ANI_OK or the first ANI_ERR_BAD_ELEMENT / ANI_ERR_MOL_TOO_LARGE / ANI_ERR_BAD_INDEX seen by
+ * ANI_OK or the first ANI_ERR_BAD_ELEMENT / ANI_ERR_BAD_INDEX seen by
  * a kernel since the last call.  No counterpart in the reference, which does not validate
  * its inputs (an element id outside 0..3 indexes out of bounds there,
  * gpu_featurizer/ani_sort.cpp:98-99). */

@@ -34,7 +34,6 @@ _i = ctypes.c_int
 # name -> (restype, argtypes); one entry per declaration in include/ani_b200.h
 SIGNATURES = {
     "ani_feature_size": (_i, []),
-    "ani_max_atoms_per_molecule": (_i, []),
     "ani_status_string": (ctypes.c_char_p, [_i]),
     "ani_last_cuda_error": (ctypes.c_char_p, []),
     "ani_device_status": (_i, [_vp]),

@@ -61,21 +61,17 @@ int sort_scratch(size_t bytes, int** out)
     return ANI_OK;
 }
 
-// Featurizer launch shapes.  NW warps per CTA, one CTA per (molecule, split); the list
-// capacities bound the neighbours kept in shared memory per central atom (atoms with more
-// take the streaming path).
+// Featurizer launch shapes: NW warps per CTA, kSlotsPerMol / NW CTAs per molecule, one warp
+// per central atom.  The capacities bound the neighbours of one element kept in shared memory
+// per central atom (atoms with more take the streaming path).
 constexpr int kNW = 4;
-constexpr int kACap = 48;
-constexpr int kRCap = 96;
+constexpr int kCapT = 24;  // angular (r < 3.1 A) neighbours per element
+constexpr int kCapR = 48;  // radial (r < 4.6 A) neighbours per element
 
-int pick_nsplit(long long n_atoms, int n_mols)
+int featurizer_grid(int n_mols)
 {
-    // about 16 central atoms per CTA: small molecules get one CTA, large ones several
-    const long long avg = n_mols > 0 ? (n_atoms + n_mols - 1) / n_mols : 1;
-    long long s = (avg + 15) / 16;
-    if (s < 1) s = 1;
-    if (s > 32) s = 32;
-    return (int)s;
+    const long long ctas = (long long)n_mols * (kSlotsPerMol / kNW);
+    return (int)(ctas < (1LL << 30) ? ctas : (1LL << 30));
 }
 
 template <typename K> int set_smem(K kernel, size_t bytes)
@@ -97,7 +93,7 @@ int check_acs(const int* acs_host, long long* n_atoms)
     return ANI_OK;
 }
 
-template <typename T, int ACAP = kACap, int RCAP = kRCap>
+template <typename T, int CAPT = kCapT, int CAPR = kCapR>
 int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, const int* mos,
                    const int* macs, int n_mols, const int* sis, T* oh, T* oc, T* on, T* oo,
                    const int* acs_host, void* stream)
@@ -111,8 +107,8 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
     for (int t = 0; t < kTypes; t++)
         if (acs_host[t] > 0 && !outs[t]) return ANI_ERR_NULL_POINTER;
 
-    auto kernel = featurize_kernel<T, kNW, ACAP, RCAP>;
-    const size_t smem = sizeof(FeaturizeShared<T, kNW, ACAP, RCAP>);
+    auto kernel = featurize_kernel<T, kNW, CAPT, CAPR>;
+    const size_t smem = kNW * sizeof(FeaturizeWarpShared<T, CAPT, CAPR>);
     static thread_local int configured_dev = -1;
     int dev = 0;
     ANI_CUDA(cudaGetDevice(&dev));
@@ -120,17 +116,14 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    const int nsplit = pick_nsplit(n_atoms, n_mols);
-    const long long items = (long long)n_mols * nsplit;
-    const int grid = (int)(items < (1 << 20) ? items : (1 << 20));
-    kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
+    kernel<<<featurizer_grid(n_mols), kNW * kWarp, smem, (cudaStream_t)stream>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, oh, oc, on, oo, acs_host[0],
-        acs_host[1], acs_host[2], acs_host[3], nsplit);
+        acs_host[1], acs_host[2], acs_host[3]);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
 
-template <typename T, int ACAP = kACap, int RCAP = kRCap>
+template <typename T, int CAPT = kCapT>
 int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types, const int* mos,
                         const int* macs, int n_mols, const int* sis, const T* gh, const T* gc,
                         const T* gn, const T* go, T* gx, T* gy, T* gz, const int* acs_host,
@@ -155,8 +148,8 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
     for (int t = 0; t < kTypes; t++)
         if (acs_host[t] > 0 && !gin[t]) return ANI_ERR_NULL_POINTER;
 
-    auto kernel = featurize_grad_kernel<T, kNW, ACAP, RCAP>;
-    const size_t smem = sizeof(GradShared<T, kNW, ACAP, RCAP>);
+    auto kernel = featurize_grad_kernel<T, kNW, CAPT>;
+    const size_t smem = kNW * sizeof(GradWarpShared<T, CAPT>);
     static thread_local int configured_dev = -1;
     int dev = 0;
     ANI_CUDA(cudaGetDevice(&dev));
@@ -164,12 +157,9 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    const int nsplit = pick_nsplit(n_atoms, n_mols);
-    const long long items = (long long)n_mols * nsplit;
-    const int grid = (int)(items < (1 << 20) ? items : (1 << 20));
-    kernel<<<grid, kNW * kWarp, smem, st>>>(xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms,
-                                            sis, gh, gc, gn, go, gx, gy, gz, acs_host[0],
-                                            acs_host[1], acs_host[2], acs_host[3], nsplit);
+    kernel<<<featurizer_grid(n_mols), kNW * kWarp, smem, st>>>(
+        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, gh, gc, gn, go, gx, gy, gz,
+        acs_host[0], acs_host[1], acs_host[2], acs_host[3]);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
@@ -180,8 +170,6 @@ extern "C" {
 
 int ani_feature_size(void) { return ani::kTotal; }
 
-int ani_max_atoms_per_molecule(void) { return ani::kMaxAtomsPerMol; }
-
 const char* ani_status_string(int status)
 {
     switch (status) {
@@ -190,7 +178,6 @@ const char* ani_status_string(int status)
         case ANI_ERR_BAD_SIZE: return "negative or inconsistent size argument";
         case ANI_ERR_CUDA: return "CUDA runtime error (see ani_last_cuda_error)";
         case ANI_ERR_BAD_ELEMENT: return "element id outside 0..3 in atomic_numbers";
-        case ANI_ERR_MOL_TOO_LARGE: return "molecule larger than ani_max_atoms_per_molecule()";
         case ANI_ERR_BAD_INDEX: return "molecule offset/count or scatter index out of range";
         case ANI_ERR_TOO_MANY_ATOMS: return "size beyond what this entry point supports";
         default: return "unknown status";

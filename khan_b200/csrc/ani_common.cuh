@@ -1,6 +1,12 @@
 // Device-side building blocks shared by the featurizer kernels: the per-device status word,
-// warp helpers, staging of one molecule into shared memory in element order, and the
-// per-central-atom neighbour lists.
+// warp helpers, per-central-atom neighbour lists and the enumeration of neighbour pairs.
+//
+// Work decomposition used by every featurizer kernel: ONE WARP PER CENTRAL ATOM, no cooperation
+// between the warps of a CTA (no __syncthreads anywhere).  The grid gives every molecule
+// kSlotsPerMol warps; warp s of molecule m handles atoms s, s + kSlotsPerMol, ... of that
+// molecule and exits at once when the molecule has fewer atoms.  A warp reads its molecule's
+// coordinates straight from global memory (the warps of one CTA belong to the same molecule, so
+// these loads hit L1) and keeps the neighbourhood of its atom in its own slice of shared memory.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -13,10 +19,7 @@ namespace ani {
 
 constexpr int kWarp = 32;
 constexpr unsigned kFull = 0xffffffffu;
-
-// Largest molecule staged in shared memory by the featurizer kernels.
-constexpr int kMaxAtomsPerMol = 512;
-constexpr int kMaxChunks = kMaxAtomsPerMol / kWarp;
+constexpr int kSlotsPerMol = 32;  // warps per molecule in the grid
 
 // First device-side problem seen since the last read (0 = none).  One word per device: the
 // variable is instantiated once per loaded module and context.  (This header is included by
@@ -27,10 +30,6 @@ __device__ __forceinline__ void report(int code) { atomicCAS(&g_status, 0, code)
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & (kWarp - 1); }
 __device__ __forceinline__ int warp_id() { return threadIdx.x >> 5; }
-__device__ __forceinline__ unsigned lanes_below(int k)  // bit l set for l < k, k clamped to 0..32
-{
-    return k <= 0 ? 0u : (k >= 32 ? kFull : ((1u << k) - 1u));
-}
 __device__ __forceinline__ unsigned lanemask_lt()
 {
     unsigned m;
@@ -57,207 +56,88 @@ __constant__ ParamTables c_tab = {
      -8.7422780003724745258e-8, -0.70710673201755099574, -0.9999999999999999289,
      -0.70710688374061164307}};
 
-// ---------------------------------------------------------------------------------------
-// One molecule in shared memory, atoms reordered stably by element so that every neighbour
-// list built from it is grouped by element too.
-// ---------------------------------------------------------------------------------------
-template <typename T> struct MolShared {
-    T x[kMaxAtomsPerMol];
-    T y[kMaxAtomsPerMol];
-    T z[kMaxAtomsPerMol];
-    int orig[kMaxAtomsPerMol];          // slot -> index of the atom inside the molecule
-    int chunk_count[kMaxChunks][kTypes];
-    int group_start[kTypes + 1];        // slot range of each element
-};
-
-// Element of a slot, from the group boundaries.
-__device__ __forceinline__ int slot_type(const int* gs, int slot)
+// Four consecutive values from 16-byte aligned shared memory (float) / two 16-byte reads (double).
+__device__ __forceinline__ void load4(const float* p, float* v)
 {
-    return (slot >= gs[1]) + (slot >= gs[2]) + (slot >= gs[3]);
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+}
+__device__ __forceinline__ void load4(const double* p, double* v)
+{
+    const double2 a = *reinterpret_cast<const double2*>(p);
+    const double2 b = *reinterpret_cast<const double2*>(p + 2);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-// Cooperative (whole CTA) load of molecule [base, base + n) into `ms`, sorted by element.
-// Every thread of the CTA must call it; it ends with a __syncthreads().
-template <typename T, int NW>
-__device__ __forceinline__ void stage_molecule(MolShared<T>& ms, const T* __restrict__ xs,
-                                               const T* __restrict__ ys, const T* __restrict__ zs,
-                                               const int* __restrict__ types, int base, int n)
+// One molecule as the kernels see it, validated.
+struct MolRange {
+    int base;  // index of its first atom in the batch
+    int n;     // atoms
+};
+
+// Reads and checks molecule m.  Returns false (after recording the problem) when the molecule
+// must be skipped.
+__device__ __forceinline__ bool load_molecule(const int* __restrict__ mol_offsets,
+                                              const int* __restrict__ mol_counts, int m,
+                                              int n_atoms, MolRange* out)
 {
-    const int lane = lane_id(), warp = warp_id();
-    const int nchunks = (n + kWarp - 1) / kWarp;
-    for (int c = warp; c < nchunks; c += NW) {
-        const int j = c * kWarp + lane;
-        int t = j < n ? types[base + j] : -1;
-        if (j < n && (t < 0 || t >= kTypes)) {
-            report(ANI_ERR_BAD_ELEMENT);
-            t &= 3;
-        }
-#pragma unroll
-        for (int g = 0; g < kTypes; g++) {
-            const int cnt = __popc(__ballot_sync(kFull, t == g));
-            if (lane == 0) ms.chunk_count[c][g] = cnt;
-        }
+    const int n = mol_counts[m], base = mol_offsets[m];
+    out->base = base;
+    out->n = n;
+    if (n <= 0) return false;
+    if (base < 0 || n > n_atoms || base > n_atoms - n) {
+        report(ANI_ERR_BAD_INDEX);
+        return false;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int tot[kTypes] = {0, 0, 0, 0};
-        for (int c = 0; c < nchunks; c++)
-#pragma unroll
-            for (int g = 0; g < kTypes; g++) tot[g] += ms.chunk_count[c][g];
-        ms.group_start[0] = 0;
-#pragma unroll
-        for (int g = 0; g < kTypes; g++) ms.group_start[g + 1] = ms.group_start[g] + tot[g];
+    return true;
+}
+
+__device__ __forceinline__ int checked_type(int t)
+{
+    if (t < 0 || t >= kTypes) {
+        report(ANI_ERR_BAD_ELEMENT);
+        t &= 3;
     }
-    __syncthreads();
-    for (int c = warp; c < nchunks; c += NW) {
-        const int j = c * kWarp + lane;
-        int t = j < n ? (types[base + j] & 3) : -1;
-        unsigned same = 0;
-#pragma unroll
-        for (int g = 0; g < kTypes; g++) {
-            const unsigned m = __ballot_sync(kFull, t == g);
-            if (t == g) same = m;
-        }
-        if (j < n) {
-            int before = 0;
-            for (int cc = 0; cc < c; cc++) before += ms.chunk_count[cc][t];
-            const int slot = ms.group_start[t] + before + __popc(same & lanemask_lt());
-            ms.x[slot] = xs[base + j];
-            ms.y[slot] = ys[base + j];
-            ms.z[slot] = zs[base + j];
-            ms.orig[slot] = j;
-        }
-    }
-    __syncthreads();
+    return t;
 }
 
 // ---------------------------------------------------------------------------------------
-// Neighbour lists of one central atom, one set per warp.  Both lists are grouped by
-// element (they inherit the order of MolShared) and `count[g]` gives the group sizes.
-//   radial list : every j != i with r_ij < R_Rc
-//   angular list: every j != i with r_ij < A_Rc
+// Angular neighbour list of one central atom: every j != i with r_ij < A_Rc, kept as four
+// per-element sub-lists of capacity CAPT (entry index = type * CAPT + position), each in
+// ascending order of j.
 // ---------------------------------------------------------------------------------------
-template <typename T, int ACAP, int RCAP, bool GRAD> struct NeighborLists {
-    T ang_ux[ACAP], ang_uy[ACAP], ang_uz[ACAP];  // unit vector (x_i - x_j) / r_ij
-    T ang_r[ACAP];
-    T ang_fc[ACAP];                              // f_C(r_ij, A_Rc)
-    T ang_dfc[GRAD ? ACAP : 1];
-    int ang_slot[GRAD ? ACAP : 1];
-    T rad_r[RCAP];
-    T rad_fc[RCAP];                              // f_C(r_ij, R_Rc)
-    T rad_dfc[GRAD ? RCAP : 1];
-    T rad_ux[GRAD ? RCAP : 1], rad_uy[GRAD ? RCAP : 1], rad_uz[GRAD ? RCAP : 1];
-    int rad_slot[GRAD ? RCAP : 1];
+template <typename T, int CAPT, bool GRAD> struct AngularList {
+    T ux[kTypes * CAPT], uy[kTypes * CAPT], uz[kTypes * CAPT];  // (x_i - x_j) / r_ij
+    T r[kTypes * CAPT];
+    T fc[kTypes * CAPT];                        // f_C(r_ij, A_Rc)
+    T dfc[GRAD ? kTypes * CAPT : 1];            // its derivative
+    int atom[GRAD ? kTypes * CAPT : 1];         // batch index of j
 };
 
-struct NeighborCounts {
-    int ang[kTypes];
-    int rad[kTypes];
-    int n_ang, n_rad;
+// ---------------------------------------------------------------------------------------
+// Padded, bucket-major enumeration of the unordered pairs of an angular list.  Bucket
+// bk = pair_bucket(ta, tb), ta <= tb.  The pairs of bucket bk occupy positions
+// [off[bk], off[bk] + cnt) of a range whose length is rounded up to a multiple of 4
+// (off[bk+1] - off[bk]), so that the contraction pass always reads four pairs at a time.
+// ---------------------------------------------------------------------------------------
+struct PairOffsets {
+    int off[kPairBuckets + 1];
 };
 
-// Warp-cooperative build of both lists for the atom in slot `i`.  Returns false when a list
-// would exceed its capacity (the lists are then incomplete and must not be used).
-template <typename T, int ACAP, int RCAP, bool GRAD>
-__device__ __forceinline__ bool build_neighbors(const MolShared<T>& ms, int n, int i,
-                                                NeighborLists<T, ACAP, RCAP, GRAD>& nl,
-                                                NeighborCounts& nc)
-{
-    const int lane = lane_id();
-    const T xi = ms.x[i], yi = ms.y[i], zi = ms.z[i];
-    const int gs0 = ms.group_start[0], gs1 = ms.group_start[1], gs2 = ms.group_start[2],
-              gs3 = ms.group_start[3], gs4 = ms.group_start[4];
-    const int gsv[kTypes + 1] = {gs0, gs1, gs2, gs3, gs4};
-#pragma unroll
-    for (int g = 0; g < kTypes; g++) nc.ang[g] = nc.rad[g] = 0;
-    int n_ang = 0, n_rad = 0;
-    for (int j0 = 0; j0 < n; j0 += kWarp) {
-        const int j = j0 + lane;
-        const bool valid = j < n && j != i;
-        const int jj = j < n ? j : 0;
-        const T dx = xi - ms.x[jj], dy = yi - ms.y[jj], dz = zi - ms.z[jj];
-        const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
-        const bool in_rad = valid && r < (T)kR_Rc;
-        const bool in_ang = valid && r < (T)kA_Rc;
-        const unsigned m_rad = __ballot_sync(kFull, in_rad);
-        const unsigned m_ang = __ballot_sync(kFull, in_ang);
-        if (in_rad) {
-            const int pos = n_rad + __popc(m_rad & lanemask_lt());
-            if (pos < RCAP) {
-                T fc, dfc;
-                cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
-                nl.rad_r[pos] = r;
-                nl.rad_fc[pos] = fc;
-                if (GRAD) {
-                    const T inv = (T)1 / r;
-                    nl.rad_dfc[pos] = dfc;
-                    nl.rad_ux[pos] = dx * inv;
-                    nl.rad_uy[pos] = dy * inv;
-                    nl.rad_uz[pos] = dz * inv;
-                    nl.rad_slot[pos] = j;
-                }
-            }
-        }
-        if (in_ang) {
-            const int pos = n_ang + __popc(m_ang & lanemask_lt());
-            if (pos < ACAP) {
-                T fc, dfc;
-                cutoff<T>(r, (T)kA_Rc, &fc, &dfc);
-                const T inv = (T)1 / r;
-                nl.ang_ux[pos] = dx * inv;
-                nl.ang_uy[pos] = dy * inv;
-                nl.ang_uz[pos] = dz * inv;
-                nl.ang_r[pos] = r;
-                nl.ang_fc[pos] = fc;
-                if (GRAD) {
-                    nl.ang_dfc[pos] = dfc;
-                    nl.ang_slot[pos] = j;
-                }
-            }
-        }
-        // group sizes: lanes of this chunk whose slot lies in [gs[g], gs[g+1])
-#pragma unroll
-        for (int g = 0; g < kTypes; g++) {
-            const unsigned in_group = lanes_below(gsv[g + 1] - j0) & ~lanes_below(gsv[g] - j0);
-            nc.rad[g] += __popc(m_rad & in_group);
-            nc.ang[g] += __popc(m_ang & in_group);
-        }
-        n_rad += __popc(m_rad);
-        n_ang += __popc(m_ang);
-    }
-    nc.n_ang = n_ang;
-    nc.n_rad = n_rad;
-    __syncwarp();
-    return n_ang <= ACAP && n_rad <= RCAP;
-}
-
-// Row q = b(b-1)/2 + a (a < b) of a strictly-lower-triangular enumeration -> b.
-__device__ __forceinline__ int tri_row(int q)
-{
-    int b = (int)((1.0f + sqrtf(8.0f * (float)q + 1.0f)) * 0.5f);
-    if (b * (b - 1) / 2 > q) b--;
-    if ((b + 1) * b / 2 <= q) b++;
-    return b;
-}
-
-// Bucket table of the padded, bucket-major enumeration of neighbour pairs used by the
-// angular passes.  Bucket bk = pair_bucket(ta, tb), ta <= tb.  Pairs of one bucket occupy
-// [off, off + cnt) of a range whose length is rounded up to a multiple of 4, so that the
-// contraction pass can always read four pairs at a time.
-struct PairBucket {
-    int off;       // padded start
-    int cnt;       // real pairs
-    int sa_sb;     // list start of group ta | list start of group tb << 16
-    int nb_same;   // size of group tb | (ta == tb) << 16
+struct PairBucketInfo {
+    int cnt;      // real pairs in the bucket
+    int base_a;   // list index of the first entry of group ta
+    int base_b;   // list index of the first entry of group tb
+    int nb_same;  // size of group tb | (ta == tb) << 16
 };
 
-// Lanes 0..9 fill `tab[0..9]`, lane 10 fills tab[10].off = padded total.  Returns the padded total.
-__device__ __forceinline__ int build_pair_table(PairBucket* tab, const int* ang_count)
+// Every lane computes the offsets (they are warp-uniform); lanes 0..9 also write the per-bucket
+// record used by decode_pair, and the offsets are mirrored to `off_smem[0..10]` for code that
+// indexes them with a runtime (warp-uniform) bucket number.  Ends with __syncwarp().
+template <int CAPT>
+__device__ __forceinline__ void build_pair_table(PairBucketInfo* tab, int* off_smem,
+                                                 const int* ang_count, PairOffsets* po)
 {
-    int start[kTypes + 1];
-    start[0] = 0;
-#pragma unroll
-    for (int g = 0; g < kTypes; g++) start[g + 1] = start[g] + ang_count[g];
     int off = 0;
     const int lane = lane_id();
 #pragma unroll
@@ -267,49 +147,62 @@ __device__ __forceinline__ int build_pair_table(PairBucket* tab, const int* ang_
             const int bk = kTypes * (kTypes - 1) / 2 - (kTypes - ta) * (kTypes - ta - 1) / 2 + tb;
             const int na = ang_count[ta], nb = ang_count[tb];
             const int cnt = ta == tb ? na * (na - 1) / 2 : na * nb;
+            po->off[bk] = off;
             if (lane == bk) {
-                tab[bk].off = off;
-                tab[bk].cnt = cnt;
-                tab[bk].sa_sb = start[ta] | (start[tb] << 16);
-                tab[bk].nb_same = nb | ((ta == tb ? 1 : 0) << 16);
+                PairBucketInfo e;
+                e.cnt = cnt;
+                e.base_a = ta * CAPT;
+                e.base_b = tb * CAPT;
+                e.nb_same = nb | ((ta == tb ? 1 : 0) << 16);
+                tab[bk] = e;
+                off_smem[bk] = off;
             }
             off += (cnt + 3) & ~3;
         }
     }
-    if (lane == kPairBuckets) {
-        tab[kPairBuckets].off = off;
-        tab[kPairBuckets].cnt = 0;
-        tab[kPairBuckets].sa_sb = 0;
-        tab[kPairBuckets].nb_same = 1;
-    }
+    po->off[kPairBuckets] = off;
+    if (lane == kPairBuckets) off_smem[kPairBuckets] = off;
     __syncwarp();
-    return off;
 }
 
-// Padded position p -> (bucket, list index a, list index b, valid).
-__device__ __forceinline__ bool decode_pair(const PairBucket* tab, int p, int* bucket, int* a,
-                                            int* b)
+// Row b of q = b(b-1)/2 + a (a < b), the strictly-lower-triangular enumeration.
+__device__ __forceinline__ int tri_row(int q)
+{
+    int b = (int)((1.0f + sqrtf(8.0f * (float)q + 1.0f)) * 0.5f);
+    if (b * (b - 1) / 2 > q) b--;
+    if ((b + 1) * b / 2 <= q) b++;
+    return b;
+}
+
+// Padded position p -> (bucket, list index a, list index b).  Returns false for a padding slot
+// (a and b then point at entry 0, which is always readable).
+__device__ __forceinline__ bool decode_pair(const PairBucketInfo* tab, const PairOffsets& po, int p,
+                                            int* bucket, int* a, int* b)
 {
     int bk = 0;
 #pragma unroll
-    for (int k = 1; k < kPairBuckets; k++) bk += (p >= tab[k].off) ? 1 : 0;
-    const PairBucket e = tab[bk];
-    const int q = p - e.off;
+    for (int k = 1; k < kPairBuckets; k++) bk += (p >= po.off[k]) ? 1 : 0;
+    int start = po.off[0];
+#pragma unroll
+    for (int k = 1; k < kPairBuckets; k++) start = (p >= po.off[k]) ? po.off[k] : start;
+    const PairBucketInfo e = tab[bk];
+    const int q = p - start;
     const bool valid = q < e.cnt;
-    const int sa = e.sa_sb & 0xffff, sb = e.sa_sb >> 16;
     const int nb = e.nb_same & 0xffff;
-    const bool same = (e.nb_same >> 16) != 0;
     int ia, ib;
-    if (same) {
+    if (e.nb_same >> 16) {
         ib = tri_row(q);
         ia = q - ib * (ib - 1) / 2;
     } else {
-        ia = q / (nb > 0 ? nb : 1);
+        // q / nb for q < 2^22 via a float reciprocal, corrected by one step
+        ia = (int)(((float)q + 0.5f) * (1.0f / (float)(nb > 0 ? nb : 1)));
         ib = q - ia * nb;
+        if (ib < 0) { ia--; ib += nb; }
+        if (ib >= nb && nb > 0) { ia++; ib -= nb; }
     }
     *bucket = bk;
-    *a = valid ? sa + ia : 0;
-    *b = valid ? sb + ib : 0;
+    *a = valid ? e.base_a + ia : 0;
+    *b = valid ? e.base_b + ib : 0;
     return valid;
 }
 

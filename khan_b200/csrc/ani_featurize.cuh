@@ -1,14 +1,16 @@
 // Forward kernel: radial + angular atomic environment vectors.
 //
-// Work decomposition: one CTA stages one molecule (element-sorted) in shared memory; each
-// warp then owns one central atom at a time.  For its atom a warp
-//   A. builds the two neighbour lists (lane = candidate neighbour),
-//   R. accumulates the 64 radial features with lane = (half, radial shift),
+// One warp per central atom (see ani_common.cuh).  For its atom a warp
+//   A. scans the molecule (lane = candidate neighbour j, coordinates from global memory) and
+//      compacts the neighbours into per-element sub-lists in its slice of shared memory:
+//      (r, f_C) for r < R_Rc, and (unit vector, r, f_C) for r < A_Rc;
+//   R. accumulates the 64 radial features with lane = (half, radial shift), walking the
+//      radial sub-lists element by element;
 //   B. evaluates, 32 neighbour pairs at a time (lane = pair), the 8 theta factors and the
-//      4 radial factors of each triplet into shared memory,
+//      4 radial factors of each triplet into shared memory;
 //   C. contracts them with lane = (theta, shift): acc += A[theta][pair] * BF[shift][pair],
-//      walking the pairs bucket by bucket (unordered element pair), so every 32-wide block
-//      of the angular features is finished in registers and written once, coalesced.
+//      walking the pairs bucket by bucket (unordered element pair), so every 32-wide block of
+//      the angular features is finished in registers and written once, coalesced.
 // No feature row is touched twice and nothing is accumulated with atomics, so the output
 // needs no zero fill and is bit-reproducible from run to run.
 //
@@ -23,16 +25,14 @@ namespace ani {
 
 constexpr int kPadStride = 36;  // 32 pairs + 4 words: keeps the 16-byte reads of pass C conflict-free
 
-template <typename T> struct FeaturizeWarpShared {
-    T A[kNumThetas][kPadStride];
-    T BF[kNumARs][kPadStride];
-    PairBucket tab[kPairBuckets + 1];
-};
-
-template <typename T, int NW, int ACAP, int RCAP> struct FeaturizeShared {
-    MolShared<T> mol;
-    NeighborLists<T, ACAP, RCAP, false> nl[NW];
-    FeaturizeWarpShared<T> ws[NW];
+template <typename T, int CAPT, int CAPR> struct FeaturizeWarpShared {
+    AngularList<T, CAPT, false> ang;
+    T rad_r[kTypes * CAPR];
+    T rad_fc[kTypes * CAPR];
+    alignas(16) T A[kNumThetas][kPadStride];
+    alignas(16) T BF[kNumARs][kPadStride];
+    alignas(16) PairBucketInfo tab[kPairBuckets];
+    int off[kPairBuckets + 2];  // copy of the bucket offsets for warp-uniform dynamic indexing
 };
 
 template <typename T> __device__ __forceinline__ T* element_buffer(int t, T* h, T* c, T* n, T* o)
@@ -40,114 +40,155 @@ template <typename T> __device__ __forceinline__ T* element_buffer(int t, T* h, 
     return t == 0 ? h : (t == 1 ? c : (t == 2 ? n : o));
 }
 
-// Slow path for an atom whose neighbourhood does not fit the lists: lane = (theta, shift)
-// for the angular part, lane = (half, radial shift) for the radial part, every pair of
-// molecule atoms tested directly.  Same results, O(n^2) distance tests per atom.
+// Slow path for an atom whose neighbourhood does not fit the sub-lists: every pair of molecule
+// atoms is tested directly, lane = (theta, shift) for the angular part and lane = (half,
+// radial shift) for the radial part.  Same results; O(n^2) distance tests per atom.
 template <typename T>
-__device__ __noinline__ void featurize_atom_streaming(const MolShared<T>& ms, int n, int i, T* row)
+__device__ __noinline__ void featurize_atom_streaming(const T* __restrict__ xs,
+                                                      const T* __restrict__ ys,
+                                                      const T* __restrict__ zs,
+                                                      const int* __restrict__ types, int base,
+                                                      int n, int i, T* row)
 {
     const int lane = lane_id();
-    const T xi = ms.x[i], yi = ms.y[i], zi = ms.z[i];
+    const T xi = xs[base + i], yi = ys[base + i], zi = zs[base + i];
     {
         const int half = lane >> 4;
         const T shift = (T)c_tab.R_Rs[lane & 15];
-        T acc[kTypes];
+        T acc[kTypes] = {(T)0, (T)0, (T)0, (T)0};
+        for (int j = half; j < n; j += 2) {
+            if (j == i) continue;
+            const T dx = xi - xs[base + j], dy = yi - ys[base + j], dz = zi - zs[base + j];
+            const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
+            if (r < (T)kR_Rc) {
+                const T d = r - shift;
+                const T v = Num<T>::exp_neg((T)kR_eta, d * d) * cutoff_value<T>(r, (T)kR_Rc);
+                const int tj = types[base + j] & 3;
 #pragma unroll
-        for (int g = 0; g < kTypes; g++) {
-            acc[g] = (T)0;
-            for (int j = ms.group_start[g] + half; j < ms.group_start[g + 1]; j += 2) {
-                if (j == i) continue;
-                const T dx = xi - ms.x[j], dy = yi - ms.y[j], dz = zi - ms.z[j];
-                const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
-                if (r < (T)kR_Rc) {
-                    const T d = r - shift;
-                    acc[g] += Num<T>::exp_neg((T)kR_eta, d * d) * cutoff_value<T>(r, (T)kR_Rc);
-                }
+                for (int g = 0; g < kTypes; g++) acc[g] += tj == g ? v : (T)0;
             }
-            acc[g] += __shfl_xor_sync(kFull, acc[g], 16);
         }
+#pragma unroll
+        for (int g = 0; g < kTypes; g++) acc[g] += __shfl_xor_sync(kFull, acc[g], 16);
         row[lane] = lane < 16 ? acc[0] : acc[1];
         row[32 + lane] = lane < 16 ? acc[2] : acc[3];
     }
     const T ct = (T)c_tab.cos_t[lane >> 2], st = (T)c_tab.sin_t[lane >> 2];
     const T shift = (T)c_tab.A_Rs[lane & 3];
-#pragma unroll 1
-    for (int ta = 0; ta < kTypes; ta++) {
-#pragma unroll 1
-        for (int tb = ta; tb < kTypes; tb++) {
-            T acc = (T)0;
-            for (int j = ms.group_start[ta]; j < ms.group_start[ta + 1]; j++) {
-                if (j == i) continue;
-                const T dxj = xi - ms.x[j], dyj = yi - ms.y[j], dzj = zi - ms.z[j];
-                const T rj = Num<T>::sqrt_(dxj * dxj + dyj * dyj + dzj * dzj);
-                if (!(rj < (T)kA_Rc)) continue;
-                const T fj = cutoff_value<T>(rj, (T)kA_Rc);
-                const int k0 = ta == tb ? j + 1 : ms.group_start[tb];
-                for (int k = k0; k < ms.group_start[tb + 1]; k++) {
-                    if (k == i) continue;
-                    const T dxk = xi - ms.x[k], dyk = yi - ms.y[k], dzk = zi - ms.z[k];
-                    const T rk = Num<T>::sqrt_(dxk * dxk + dyk * dyk + dzk * dzk);
-                    if (!(rk < (T)kA_Rc)) continue;
-                    const T fk = cutoff_value<T>(rk, (T)kA_Rc);
-                    T c = (dxj * dxk + dyj * dyk + dzj * dzk) / (rj * rk);
-                    c = Num<T>::max_((T)-1, Num<T>::min_((T)1, c));
-                    const T s = Num<T>::sqrt_(Num<T>::max_((T)0, (T)1 - c * c));
-                    const T b = (T)1 + (c * ct + s * st);
-                    const T b2 = b * b, b4 = b2 * b2;
-                    const T d = (T)0.5 * (rj + rk) - shift;
-                    acc += b4 * b4 * Num<T>::exp_neg((T)kA_eta, d * d) * ((T)kA_pref * fj * fk);
-                }
-            }
-            row[kRadial + pair_bucket(ta, tb) * kTS + lane] = acc;
+    T acc[kPairBuckets];
+#pragma unroll
+    for (int b = 0; b < kPairBuckets; b++) acc[b] = (T)0;
+    for (int j = 0; j < n; j++) {
+        if (j == i) continue;
+        const T dxj = xi - xs[base + j], dyj = yi - ys[base + j], dzj = zi - zs[base + j];
+        const T rj = Num<T>::sqrt_(dxj * dxj + dyj * dyj + dzj * dzj);
+        if (!(rj < (T)kA_Rc)) continue;
+        const T fj = cutoff_value<T>(rj, (T)kA_Rc);
+        const int tj = types[base + j] & 3;
+        for (int k = j + 1; k < n; k++) {
+            if (k == i) continue;
+            const T dxk = xi - xs[base + k], dyk = yi - ys[base + k], dzk = zi - zs[base + k];
+            const T rk = Num<T>::sqrt_(dxk * dxk + dyk * dyk + dzk * dzk);
+            if (!(rk < (T)kA_Rc)) continue;
+            const T fk = cutoff_value<T>(rk, (T)kA_Rc);
+            T c = (dxj * dxk + dyj * dyk + dzj * dzk) / (rj * rk);
+            c = Num<T>::max_((T)-1, Num<T>::min_((T)1, c));
+            const T s = Num<T>::sqrt_(Num<T>::max_((T)0, (T)1 - c * c));
+            const T b = (T)1 + (c * ct + s * st);
+            const T b2 = b * b, b4 = b2 * b2;
+            const T d = (T)0.5 * (rj + rk) - shift;
+            const T v = b4 * b4 * Num<T>::exp_neg((T)kA_eta, d * d) * ((T)kA_pref * fj * fk);
+            const int bk = pair_bucket(tj, types[base + k] & 3);
+#pragma unroll
+            for (int q = 0; q < kPairBuckets; q++) acc[q] += bk == q ? v : (T)0;
         }
     }
+#pragma unroll
+    for (int b = 0; b < kPairBuckets; b++) row[kRadial + b * kTS + lane] = acc[b];
 }
 
-template <typename T, int NW, int ACAP, int RCAP>
+template <typename T, int NW, int CAPT, int CAPR>
 __global__ void __launch_bounds__(NW* kWarp)
     featurize_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
                      const int* __restrict__ types, const int* __restrict__ mol_offsets,
                      const int* __restrict__ mol_counts, int n_mols, int n_atoms,
                      const int* __restrict__ scatter, T* out_h, T* out_c, T* out_n, T* out_o,
-                     int acs0, int acs1, int acs2, int acs3, int nsplit)
+                     int acs0, int acs1, int acs2, int acs3)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    auto& sh = *reinterpret_cast<FeaturizeShared<T, NW, ACAP, RCAP>*>(smem_raw);
+    using WarpShared = FeaturizeWarpShared<T, CAPT, CAPR>;
     const int lane = lane_id(), warp = warp_id();
-    auto& nl = sh.nl[warp];
-    auto& ws = sh.ws[warp];
-    const int acs[kTypes] = {acs0, acs1, acs2, acs3};
+    WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
-    for (int item = blockIdx.x; item < n_mols * nsplit; item += gridDim.x) {
-        const int m = item / nsplit, split = item - m * nsplit;
-        const int n = mol_counts[m], base = mol_offsets[m];
-        if (n <= 0) continue;
-        if (n > kMaxAtomsPerMol) {
-            if (threadIdx.x == 0) report(ANI_ERR_MOL_TOO_LARGE);
-            continue;
-        }
-        if (base < 0 || base + n > n_atoms) {
-            if (threadIdx.x == 0) report(ANI_ERR_BAD_INDEX);
-            continue;
-        }
-        __syncthreads();  // previous molecule fully consumed before restaging
-        stage_molecule<T, NW>(sh.mol, xs, ys, zs, types, base, n);
-        const MolShared<T>& ms = sh.mol;
+    constexpr int kCtasPerMol = kSlotsPerMol / NW;
+    for (long long cta = blockIdx.x; cta < (long long)n_mols * kCtasPerMol; cta += gridDim.x) {
+        const int m = (int)(cta / kCtasPerMol);
+        const int slot = (int)(cta - (long long)m * kCtasPerMol) * NW + warp;
+        MolRange mol;
+        if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
+        const int n = mol.n, base = mol.base;
 
-        // heaviest elements (most neighbours) first
-        for (int i = n - 1 - (split * NW + warp); i >= 0; i -= nsplit * NW) {
-            const int ti = slot_type(ms.group_start, i);
-            const int gi = base + ms.orig[i];
+        for (int i = slot; i < n; i += kSlotsPerMol) {
+            const int gi = base + i;
+            const int ti = checked_type(types[gi]);
             const int srow = scatter[gi];
-            if (srow < 0 || srow >= acs[ti]) {
+            const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
+            if (srow < 0 || srow >= cap) {
                 if (lane == 0) report(ANI_ERR_BAD_INDEX);
                 continue;
             }
             T* row = element_buffer<T>(ti, out_h, out_c, out_n, out_o) + (size_t)srow * kTotal;
+            const T xi = xs[gi], yi = ys[gi], zi = zs[gi];
 
-            NeighborCounts nc;
-            if (!build_neighbors<T, ACAP, RCAP, false>(ms, n, i, nl, nc)) {
-                featurize_atom_streaming<T>(ms, n, i, row);
+            // ---- A: neighbour scan, lane = j ----
+            int cA[kTypes] = {0, 0, 0, 0}, cR[kTypes] = {0, 0, 0, 0};
+            for (int j0 = 0; j0 < n; j0 += kWarp) {
+                const int j = j0 + lane;
+                const bool live = j < n;
+                const int gj = base + (live ? j : 0);
+                const T dx = xi - xs[gj], dy = yi - ys[gj], dz = zi - zs[gj];
+                const int tj = live ? checked_type(types[gj]) : -1;
+                const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
+                const bool in_rad = live && j != i && r < (T)kR_Rc;
+                const bool in_ang = in_rad && r < (T)kA_Rc;
+                T fcR = (T)0, fcA = (T)0, inv = (T)0;
+                if (in_rad) fcR = cutoff_value<T>(r, (T)kR_Rc);
+                if (in_ang) {
+                    fcA = cutoff_value<T>(r, (T)kA_Rc);
+                    inv = (T)1 / r;
+                }
+#pragma unroll
+                for (int g = 0; g < kTypes; g++) {
+                    const unsigned mR = __ballot_sync(kFull, in_rad && tj == g);
+                    const unsigned mA = __ballot_sync(kFull, in_ang && tj == g);
+                    if (in_rad && tj == g) {
+                        const int pos = cR[g] + __popc(mR & lanemask_lt());
+                        if (pos < CAPR) {
+                            ws.rad_r[g * CAPR + pos] = r;
+                            ws.rad_fc[g * CAPR + pos] = fcR;
+                        }
+                    }
+                    if (in_ang && tj == g) {
+                        const int pos = cA[g] + __popc(mA & lanemask_lt());
+                        if (pos < CAPT) {
+                            const int e = g * CAPT + pos;
+                            ws.ang.ux[e] = dx * inv;
+                            ws.ang.uy[e] = dy * inv;
+                            ws.ang.uz[e] = dz * inv;
+                            ws.ang.r[e] = r;
+                            ws.ang.fc[e] = fcA;
+                        }
+                    }
+                    cR[g] += __popc(mR);
+                    cA[g] += __popc(mA);
+                }
+            }
+            __syncwarp();
+            bool fits = true;
+#pragma unroll
+            for (int g = 0; g < kTypes; g++) fits = fits && cA[g] <= CAPT && cR[g] <= CAPR;
+            if (!fits) {
+                featurize_atom_streaming<T>(xs, ys, zs, types, base, n, i, row);
                 __syncwarp();
                 continue;
             }
@@ -157,16 +198,13 @@ __global__ void __launch_bounds__(NW* kWarp)
                 const int half = lane >> 4;
                 const T shift = (T)c_tab.R_Rs[lane & 15];
                 T acc[kTypes];
-                int start = 0;
 #pragma unroll
                 for (int g = 0; g < kTypes; g++) {
                     acc[g] = (T)0;
-                    const int end = start + nc.rad[g];
-                    for (int p = start + half; p < end; p += 2) {
-                        const T d = nl.rad_r[p] - shift;
-                        acc[g] += Num<T>::exp_neg((T)kR_eta, d * d) * nl.rad_fc[p];
+                    for (int p = half; p < cR[g]; p += 2) {
+                        const T d = ws.rad_r[g * CAPR + p] - shift;
+                        acc[g] += Num<T>::exp_neg((T)kR_eta, d * d) * ws.rad_fc[g * CAPR + p];
                     }
-                    start = end;
                     acc[g] += __shfl_xor_sync(kFull, acc[g], 16);
                 }
                 row[lane] = lane < 16 ? acc[0] : acc[1];
@@ -174,48 +212,58 @@ __global__ void __launch_bounds__(NW* kWarp)
             }
 
             // ---- B + C: angular features ----
-            const int total = build_pair_table(ws.tab, nc.ang);
+            PairOffsets po;
+            build_pair_table<CAPT>(ws.tab, ws.off, cA, &po);
+            const int total = po.off[kPairBuckets];
             const int my_t = lane >> 2, my_s = lane & 3;
-            int cur = 0;          // bucket being accumulated
-            T acc = (T)0;
+            const T* a_row = &ws.A[my_t][0];
+            const T* b_row = &ws.BF[my_s][0];
+            int cur = 0;  // bucket being accumulated
+            int cur_end = po.off[1];
+            T acc0 = (T)0, acc1 = (T)0;
             for (int c0 = 0; c0 < total; c0 += kWarp) {
                 {   // B: lane = pair
                     int bk, a, b;
-                    const bool valid = decode_pair(ws.tab, c0 + lane, &bk, &a, &b);
-                    const T cosv = nl.ang_ux[a] * nl.ang_ux[b] + nl.ang_uy[a] * nl.ang_uy[b] +
-                                   nl.ang_uz[a] * nl.ang_uz[b];
-                    const T rbar = (T)0.5 * (nl.ang_r[a] + nl.ang_r[b]);
-                    const T fcprod = valid ? nl.ang_fc[a] * nl.ang_fc[b] : (T)0;
+                    const bool valid = decode_pair(ws.tab, po, c0 + lane, &bk, &a, &b);
+                    const T cosv = ws.ang.ux[a] * ws.ang.ux[b] + ws.ang.uy[a] * ws.ang.uy[b] +
+                                   ws.ang.uz[a] * ws.ang.uz[b];
+                    const T rbar = (T)0.5 * (ws.ang.r[a] + ws.ang.r[b]);
+                    const T fcprod = ws.ang.fc[a] * ws.ang.fc[b];
                     T A[kNumThetas], BF[kNumARs];
-                    angular_factors<T>(valid ? cosv : (T)0, rbar, fcprod, A, BF);
+                    angular_factors<T>(cosv, rbar, fcprod, A, BF);
 #pragma unroll
-                    for (int t = 0; t < kNumThetas; t++) ws.A[t][lane] = A[t];
+                    for (int t = 0; t < kNumThetas; t++) ws.A[t][lane] = valid ? A[t] : (T)0;
 #pragma unroll
-                    for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = BF[q];
+                    for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = valid ? BF[q] : (T)0;
                 }
                 __syncwarp();
                 {   // C: lane = (theta, shift)
                     const int chunk_end = min(c0 + kWarp, total);
                     int pp = c0;
                     while (pp < chunk_end) {
-                        while (ws.tab[cur + 1].off <= pp) {
-                            row[kRadial + cur * kTS + lane] = acc;
-                            acc = (T)0;
+                        while (cur_end <= pp) {   // bucket `cur` is complete: write its 32 features
+                            row[kRadial + cur * kTS + lane] = acc0 + acc1;
+                            acc0 = acc1 = (T)0;
                             cur++;
+                            cur_end = ws.off[cur + 1];  // cur + 1 <= 10 here, because pp < total
                         }
-                        const int seg_end = min(chunk_end, ws.tab[cur + 1].off);
+                        const int seg_end = min(chunk_end, cur_end);
                         for (; pp < seg_end; pp += 4) {
-                            const int o = pp - c0;
-#pragma unroll
-                            for (int u = 0; u < 4; u++) acc += ws.A[my_t][o + u] * ws.BF[my_s][o + u];
+                            T av[4], bv[4];
+                            load4(a_row + (pp - c0), av);
+                            load4(b_row + (pp - c0), bv);
+                            acc0 += av[0] * bv[0];
+                            acc1 += av[1] * bv[1];
+                            acc0 += av[2] * bv[2];
+                            acc1 += av[3] * bv[3];
                         }
                     }
                 }
                 __syncwarp();
             }
             for (; cur < kPairBuckets; cur++) {
-                row[kRadial + cur * kTS + lane] = acc;
-                acc = (T)0;
+                row[kRadial + cur * kTS + lane] = acc0 + acc1;
+                acc0 = acc1 = (T)0;
             }
         }
     }

@@ -3,15 +3,20 @@
 // Computes what featurize_grad_cpu of the reference computes
 // (gpu_featurizer/kernel_cpu.cpp:217-366); the reference has no GPU kernel for this op.
 //
-// Same decomposition as the forward kernel: CTA = molecule, warp = central atom i.  The
-// warp copies the 384 upstream values of row(i) into shared memory, then
-//   R. lane = radial neighbour j: contracts the 16 upstream values of block type(j) with the
-//      radial derivatives and pushes +/- D u_ij onto atoms i and j;
-//   B. lane = neighbour pair (j, k): contracts the 32 upstream values of block
-//      (type j, type k) into three scalars (dL/dcos, dL/dr_ij, dL/dr_ik), turns them into
-//      the forces on j and k, and adds those to per-neighbour accumulators of the warp.
-// The force on i is minus the sum over its neighbours (every term depends on coordinate
-// differences only).  Forces are summed per molecule in shared memory and written once.
+// One warp per central atom i (see ani_common.cuh).  The warp copies the 384 upstream values of
+// row(i) into shared memory, then
+//   A. scans the molecule with lane = candidate neighbour j.  A lane whose j is within R_Rc
+//      contracts the 16 upstream values of radial block type(j) with the radial derivatives on
+//      the spot and adds -D u_ij to the gradient of atom j; neighbours within A_Rc are also
+//      compacted into the per-element angular sub-lists;
+//   B. walks the neighbour pairs 32 at a time with lane = pair (j, k): the 32 upstream values of
+//      block (type j, type k) are contracted into three scalars (dL/dcos, dL/dr_ij, dL/dr_ik),
+//      turned into the forces on j and k and added to per-neighbour accumulators of the warp;
+//   C. adds every neighbour's accumulated force to the output and, since all terms depend on
+//      coordinate differences only, minus the total to atom i.
+// Contributions of different central atoms to the same atom meet in the output arrays through
+// floating-point atomic adds, so the outputs must be zero before the kernel starts and the
+// summation order (hence the last bits) may differ between runs.
 #pragma once
 
 #include "ani_common.cuh"
@@ -21,55 +26,39 @@ namespace ani {
 constexpr int kGradBucketStride = 36;  // upstream values of one type pair, padded against bank conflicts
 constexpr int kGradRowWords = kRadial + kPairBuckets * kGradBucketStride;
 
-template <typename T, int ACAP> struct GradWarpShared {
-    T g[kGradRowWords];      // upstream row: radial [0,64), then 10 blocks of 32 at stride 36
-    T facc[ACAP][3];         // force on each angular neighbour, from this central atom
-    PairBucket tab[kPairBuckets + 1];
+template <typename T, int CAPT> struct GradWarpShared {
+    AngularList<T, CAPT, true> ang;
+    alignas(16) T g[kGradRowWords];  // upstream row: radial [0,64), then 10 blocks of 32 at stride 36
+    T facc[kTypes * CAPT][3];        // force on each angular neighbour, from this central atom
+    alignas(16) PairBucketInfo tab[kPairBuckets];
+    int off[kPairBuckets + 2];
 };
 
-template <typename T, int NW, int ACAP, int RCAP> struct GradShared {
-    MolShared<T> mol;
-    T fmol[kMaxAtomsPerMol][3];  // per-slot gradient of the molecule
-    NeighborLists<T, ACAP, RCAP, true> nl[NW];
-    GradWarpShared<T, ACAP> ws[NW];
-};
-
-// Slow path for an atom whose neighbourhood does not fit the lists.  lane = k for the
-// angular part (j is a warp-uniform loop), lane = j for the radial part.
+// Slow path for an atom whose angular neighbourhood does not fit the sub-lists: angular part
+// only (the radial part never needs a list).  lane = k, j is a warp-uniform loop.
 template <typename T>
-__device__ __noinline__ void grad_atom_streaming(const MolShared<T>& ms, int n, int i, const T* g,
-                                                 T (*fmol)[3])
+__device__ __noinline__ void grad_atom_streaming(const T* __restrict__ xs, const T* __restrict__ ys,
+                                                 const T* __restrict__ zs,
+                                                 const int* __restrict__ types, int base, int n,
+                                                 int i, const T* g, T* gx, T* gy, T* gz)
 {
     const int lane = lane_id();
-    const T xi = ms.x[i], yi = ms.y[i], zi = ms.z[i];
+    const T xi = xs[base + i], yi = ys[base + i], zi = zs[base + i];
     T fix = (T)0, fiy = (T)0, fiz = (T)0;
-    for (int j = lane; j < n; j += kWarp) {
-        if (j == i) continue;
-        const T dx = xi - ms.x[j], dy = yi - ms.y[j], dz = zi - ms.z[j];
-        const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
-        if (!(r < (T)kR_Rc)) continue;
-        T fc, dfc;
-        cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
-        const T d = radial_vjp<T, T>(r, fc, dfc, g + slot_type(ms.group_start, j) * kNumRs) / r;
-        fix += d * dx; fiy += d * dy; fiz += d * dz;
-        atomicAdd(&fmol[j][0], -d * dx);
-        atomicAdd(&fmol[j][1], -d * dy);
-        atomicAdd(&fmol[j][2], -d * dz);
-    }
     for (int j = 0; j < n; j++) {
         if (j == i) continue;
-        const T dxj = xi - ms.x[j], dyj = yi - ms.y[j], dzj = zi - ms.z[j];
+        const T dxj = xi - xs[base + j], dyj = yi - ys[base + j], dzj = zi - zs[base + j];
         const T rj = Num<T>::sqrt_(dxj * dxj + dyj * dyj + dzj * dzj);
         if (!(rj < (T)kA_Rc)) continue;
         T fj, dfj;
         cutoff<T>(rj, (T)kA_Rc, &fj, &dfj);
-        const int tj = slot_type(ms.group_start, j);
+        const int tj = types[base + j] & 3;
         const T ujx = dxj / rj, ujy = dyj / rj, ujz = dzj / rj;
         T fjx = (T)0, fjy = (T)0, fjz = (T)0;
         for (int k0 = j + 1; k0 < n; k0 += kWarp) {
             const int k = k0 + lane;
             if (k < n && k != i) {
-                const T dxk = xi - ms.x[k], dyk = yi - ms.y[k], dzk = zi - ms.z[k];
+                const T dxk = xi - xs[base + k], dyk = yi - ys[base + k], dzk = zi - zs[base + k];
                 const T rk = Num<T>::sqrt_(dxk * dxk + dyk * dyk + dzk * dzk);
                 if (rk < (T)kA_Rc) {
                     T fk, dfk;
@@ -77,7 +66,7 @@ __device__ __noinline__ void grad_atom_streaming(const MolShared<T>& ms, int n, 
                     const T ukx = dxk / rk, uky = dyk / rk, ukz = dzk / rk;
                     T c = ujx * ukx + ujy * uky + ujz * ukz;
                     c = Num<T>::max_((T)-1, Num<T>::min_((T)1, c));
-                    const int bk = pair_bucket(tj, slot_type(ms.group_start, k));
+                    const int bk = pair_bucket(tj, types[base + k] & 3);
                     T dc, drj, drk;
                     const T s2 = sin2_from_cross<T>(ujx, ujy, ujz, ukx, uky, ukz);
                     angular_vjp<T, T>(c, s2, rj, rk, fj, dfj, fk, dfk,
@@ -88,9 +77,9 @@ __device__ __noinline__ void grad_atom_streaming(const MolShared<T>& ms, int n, 
                     const T gkx = ak * ujx + bkk * ukx, gky = ak * ujy + bkk * uky, gkz = ak * ujz + bkk * ukz;
                     fjx += gjx; fjy += gjy; fjz += gjz;
                     fix -= gjx + gkx; fiy -= gjy + gky; fiz -= gjz + gkz;
-                    atomicAdd(&fmol[k][0], gkx);
-                    atomicAdd(&fmol[k][1], gky);
-                    atomicAdd(&fmol[k][2], gkz);
+                    atomicAdd(&gx[base + k], gkx);
+                    atomicAdd(&gy[base + k], gky);
+                    atomicAdd(&gz[base + k], gkz);
                 }
             }
         }
@@ -101,9 +90,9 @@ __device__ __noinline__ void grad_atom_streaming(const MolShared<T>& ms, int n, 
             fjz += __shfl_xor_sync(kFull, fjz, o);
         }
         if (lane == 0) {
-            atomicAdd(&fmol[j][0], fjx);
-            atomicAdd(&fmol[j][1], fjy);
-            atomicAdd(&fmol[j][2], fjz);
+            atomicAdd(&gx[base + j], fjx);
+            atomicAdd(&gy[base + j], fjy);
+            atomicAdd(&gz[base + j], fjz);
         }
     }
 #pragma unroll
@@ -113,13 +102,13 @@ __device__ __noinline__ void grad_atom_streaming(const MolShared<T>& ms, int n, 
         fiz += __shfl_xor_sync(kFull, fiz, o);
     }
     if (lane == 0) {
-        atomicAdd(&fmol[i][0], fix);
-        atomicAdd(&fmol[i][1], fiy);
-        atomicAdd(&fmol[i][2], fiz);
+        atomicAdd(&gx[base + i], fix);
+        atomicAdd(&gy[base + i], fiy);
+        atomicAdd(&gz[base + i], fiz);
     }
 }
 
-template <typename T, int NW, int ACAP, int RCAP>
+template <typename T, int NW, int CAPT>
 __global__ void __launch_bounds__(NW* kWarp)
     featurize_grad_kernel(const T* __restrict__ xs, const T* __restrict__ ys,
                           const T* __restrict__ zs, const int* __restrict__ types,
@@ -127,34 +116,24 @@ __global__ void __launch_bounds__(NW* kWarp)
                           int n_mols, int n_atoms, const int* __restrict__ scatter,
                           const T* __restrict__ gh, const T* __restrict__ gc,
                           const T* __restrict__ gn, const T* __restrict__ go, T* gx, T* gy, T* gz,
-                          int acs0, int acs1, int acs2, int acs3, int nsplit)
+                          int acs0, int acs1, int acs2, int acs3)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    auto& sh = *reinterpret_cast<GradShared<T, NW, ACAP, RCAP>*>(smem_raw);
+    using WarpShared = GradWarpShared<T, CAPT>;
     const int lane = lane_id(), warp = warp_id();
-    auto& nl = sh.nl[warp];
-    auto& ws = sh.ws[warp];
+    WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
-    for (int item = blockIdx.x; item < n_mols * nsplit; item += gridDim.x) {
-        const int m = item / nsplit, split = item - m * nsplit;
-        const int n = mol_counts[m], base = mol_offsets[m];
-        if (n <= 0) continue;
-        if (n > kMaxAtomsPerMol) {
-            if (threadIdx.x == 0) report(ANI_ERR_MOL_TOO_LARGE);
-            continue;
-        }
-        if (base < 0 || base + n > n_atoms) {
-            if (threadIdx.x == 0) report(ANI_ERR_BAD_INDEX);
-            continue;
-        }
-        __syncthreads();
-        for (int s = threadIdx.x; s < n * 3; s += NW * kWarp) (&sh.fmol[0][0])[s] = (T)0;
-        stage_molecule<T, NW>(sh.mol, xs, ys, zs, types, base, n);
-        const MolShared<T>& ms = sh.mol;
+    constexpr int kCtasPerMol = kSlotsPerMol / NW;
+    for (long long cta = blockIdx.x; cta < (long long)n_mols * kCtasPerMol; cta += gridDim.x) {
+        const int m = (int)(cta / kCtasPerMol);
+        const int slot = (int)(cta - (long long)m * kCtasPerMol) * NW + warp;
+        MolRange mol;
+        if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
+        const int n = mol.n, base = mol.base;
 
-        for (int i = n - 1 - (split * NW + warp); i >= 0; i -= nsplit * NW) {
-            const int ti = slot_type(ms.group_start, i);
-            const int gi = base + ms.orig[i];
+        for (int i = slot; i < n; i += kSlotsPerMol) {
+            const int gi = base + i;
+            const int ti = checked_type(types[gi]);
             const int srow = scatter[gi];
             const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
             if (srow < 0 || srow >= cap) {
@@ -168,74 +147,112 @@ __global__ void __launch_bounds__(NW* kWarp)
 #pragma unroll
             for (int bk = 0; bk < kPairBuckets; bk++)
                 ws.g[kRadial + bk * kGradBucketStride + lane] = grow[kRadial + bk * kTS + lane];
+            __syncwarp();
+            const T xi = xs[gi], yi = ys[gi], zi = zs[gi];
+            T fix = (T)0, fiy = (T)0, fiz = (T)0;  // this lane's share of the force on atom i
 
-            NeighborCounts nc;
-            const bool fits = build_neighbors<T, ACAP, RCAP, true>(ms, n, i, nl, nc);  // ends with __syncwarp
-            if (!fits) {
-                grad_atom_streaming<T>(ms, n, i, ws.g, sh.fmol);
-                __syncwarp();
-                continue;
-            }
-
-            T fix = (T)0, fiy = (T)0, fiz = (T)0;
-            // ---- R: radial, lane = neighbour ----
-            {
-                const int c1 = nc.rad[0], c2 = c1 + nc.rad[1], c3 = c2 + nc.rad[2];
-                for (int p = lane; p < nc.n_rad; p += kWarp) {
-                    const int tj = (p >= c1) + (p >= c2) + (p >= c3);
-                    const T d = radial_vjp<T, T>(nl.rad_r[p], nl.rad_fc[p], nl.rad_dfc[p],
-                                                 ws.g + tj * kNumRs);
-                    const T fx = d * nl.rad_ux[p], fy = d * nl.rad_uy[p], fz = d * nl.rad_uz[p];
+            // ---- A: neighbour scan + radial part, lane = j ----
+            int cA[kTypes] = {0, 0, 0, 0};
+            for (int j0 = 0; j0 < n; j0 += kWarp) {
+                const int j = j0 + lane;
+                const bool live = j < n;
+                const int gj = base + (live ? j : 0);
+                const T dx = xi - xs[gj], dy = yi - ys[gj], dz = zi - zs[gj];
+                const int tj = live ? checked_type(types[gj]) : -1;
+                const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
+                const bool in_rad = live && j != i && r < (T)kR_Rc;
+                const bool in_ang = in_rad && r < (T)kA_Rc;
+                T ux = (T)0, uy = (T)0, uz = (T)0;
+                if (in_rad) {
+                    const T inv = (T)1 / r;
+                    ux = dx * inv; uy = dy * inv; uz = dz * inv;
+                    T fc, dfc;
+                    cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
+                    const T d = radial_vjp<T, T>(r, fc, dfc, ws.g + tj * kNumRs);
+                    const T fx = d * ux, fy = d * uy, fz = d * uz;
                     fix += fx; fiy += fy; fiz += fz;
-                    const int sj = nl.rad_slot[p];
-                    atomicAdd(&sh.fmol[sj][0], -fx);
-                    atomicAdd(&sh.fmol[sj][1], -fy);
-                    atomicAdd(&sh.fmol[sj][2], -fz);
+                    atomicAdd(&gx[gj], -fx);
+                    atomicAdd(&gy[gj], -fy);
+                    atomicAdd(&gz[gj], -fz);
                 }
-            }
-            // ---- B: angular, lane = pair ----
-            for (int p = lane; p < nc.n_ang; p += kWarp) {
-                ws.facc[p][0] = (T)0;
-                ws.facc[p][1] = (T)0;
-                ws.facc[p][2] = (T)0;
-            }
-            const int total = build_pair_table(ws.tab, nc.ang);  // ends with __syncwarp
-            for (int c0 = 0; c0 < total; c0 += kWarp) {
-                int bk, a, b;
-                const bool valid = decode_pair(ws.tab, c0 + lane, &bk, &a, &b);
-                if (valid) {
-                    const T uax = nl.ang_ux[a], uay = nl.ang_uy[a], uaz = nl.ang_uz[a];
-                    const T ubx = nl.ang_ux[b], uby = nl.ang_uy[b], ubz = nl.ang_uz[b];
-                    const T ra = nl.ang_r[a], rb = nl.ang_r[b];
-                    T c = uax * ubx + uay * uby + uaz * ubz;
-                    c = Num<T>::max_((T)-1, Num<T>::min_((T)1, c));
-                    T gl[kTS];
-                    const T* gsrc = ws.g + kRadial + bk * kGradBucketStride;
+                T fcA = (T)0, dfcA = (T)0;
+                if (in_ang) cutoff<T>(r, (T)kA_Rc, &fcA, &dfcA);
 #pragma unroll
-                    for (int q = 0; q < kTS; q++) gl[q] = gsrc[q];
-                    T dc, dra, drb;
-                    const T s2 = sin2_from_cross<T>(uax, uay, uaz, ubx, uby, ubz);
-                    angular_vjp<T, T>(c, s2, ra, rb, nl.ang_fc[a], nl.ang_dfc[a], nl.ang_fc[b],
-                                      nl.ang_dfc[b], gl, &dc, &dra, &drb);
-                    const T ira = (T)1 / ra, irb = (T)1 / rb;
-                    const T aa = -dc * ira, ba = c * dc * ira - dra;
-                    const T ab = -dc * irb, bb = c * dc * irb - drb;
-                    atomicAdd(&ws.facc[a][0], aa * ubx + ba * uax);
-                    atomicAdd(&ws.facc[a][1], aa * uby + ba * uay);
-                    atomicAdd(&ws.facc[a][2], aa * ubz + ba * uaz);
-                    atomicAdd(&ws.facc[b][0], ab * uax + bb * ubx);
-                    atomicAdd(&ws.facc[b][1], ab * uay + bb * uby);
-                    atomicAdd(&ws.facc[b][2], ab * uaz + bb * ubz);
+                for (int g = 0; g < kTypes; g++) {
+                    const unsigned mA = __ballot_sync(kFull, in_ang && tj == g);
+                    if (in_ang && tj == g) {
+                        const int pos = cA[g] + __popc(mA & lanemask_lt());
+                        if (pos < CAPT) {
+                            const int e = g * CAPT + pos;
+                            ws.ang.ux[e] = ux;
+                            ws.ang.uy[e] = uy;
+                            ws.ang.uz[e] = uz;
+                            ws.ang.r[e] = r;
+                            ws.ang.fc[e] = fcA;
+                            ws.ang.dfc[e] = dfcA;
+                            ws.ang.atom[e] = gj;
+                            ws.facc[e][0] = (T)0;
+                            ws.facc[e][1] = (T)0;
+                            ws.facc[e][2] = (T)0;
+                        }
+                    }
+                    cA[g] += __popc(mA);
                 }
             }
             __syncwarp();
-            for (int p = lane; p < nc.n_ang; p += kWarp) {
-                const T fx = ws.facc[p][0], fy = ws.facc[p][1], fz = ws.facc[p][2];
-                fix -= fx; fiy -= fy; fiz -= fz;
-                const int sj = nl.ang_slot[p];
-                atomicAdd(&sh.fmol[sj][0], fx);
-                atomicAdd(&sh.fmol[sj][1], fy);
-                atomicAdd(&sh.fmol[sj][2], fz);
+            bool fits = true;
+#pragma unroll
+            for (int g = 0; g < kTypes; g++) fits = fits && cA[g] <= CAPT;
+
+            if (!fits) {
+                grad_atom_streaming<T>(xs, ys, zs, types, base, n, i, ws.g, gx, gy, gz);
+            } else {
+                // ---- B: angular part, lane = pair ----
+                PairOffsets po;
+                build_pair_table<CAPT>(ws.tab, ws.off, cA, &po);
+                const int total = po.off[kPairBuckets];
+                for (int c0 = 0; c0 < total; c0 += kWarp) {
+                    int bk, a, b;
+                    const bool valid = decode_pair(ws.tab, po, c0 + lane, &bk, &a, &b);
+                    if (valid) {
+                        const T uax = ws.ang.ux[a], uay = ws.ang.uy[a], uaz = ws.ang.uz[a];
+                        const T ubx = ws.ang.ux[b], uby = ws.ang.uy[b], ubz = ws.ang.uz[b];
+                        const T ra = ws.ang.r[a], rb = ws.ang.r[b];
+                        T c = uax * ubx + uay * uby + uaz * ubz;
+                        c = Num<T>::max_((T)-1, Num<T>::min_((T)1, c));
+                        const T s2 = sin2_from_cross<T>(uax, uay, uaz, ubx, uby, ubz);
+                        T gl[kTS];
+                        const T* gsrc = ws.g + kRadial + bk * kGradBucketStride;
+#pragma unroll
+                        for (int q = 0; q < kTS; q += 4) load4(gsrc + q, gl + q);
+                        T dc, dra, drb;
+                        angular_vjp<T, T>(c, s2, ra, rb, ws.ang.fc[a], ws.ang.dfc[a], ws.ang.fc[b],
+                                          ws.ang.dfc[b], gl, &dc, &dra, &drb);
+                        const T ira = (T)1 / ra, irb = (T)1 / rb;
+                        const T aa = -dc * ira, ba = c * dc * ira - dra;
+                        const T ab = -dc * irb, bb = c * dc * irb - drb;
+                        atomicAdd(&ws.facc[a][0], aa * ubx + ba * uax);
+                        atomicAdd(&ws.facc[a][1], aa * uby + ba * uay);
+                        atomicAdd(&ws.facc[a][2], aa * ubz + ba * uaz);
+                        atomicAdd(&ws.facc[b][0], ab * uax + bb * ubx);
+                        atomicAdd(&ws.facc[b][1], ab * uay + bb * uby);
+                        atomicAdd(&ws.facc[b][2], ab * uaz + bb * ubz);
+                    }
+                }
+                __syncwarp();
+                // ---- C: push the neighbour forces out ----
+#pragma unroll
+                for (int g = 0; g < kTypes; g++) {
+                    for (int p = lane; p < cA[g]; p += kWarp) {
+                        const int e = g * CAPT + p;
+                        const T fx = ws.facc[e][0], fy = ws.facc[e][1], fz = ws.facc[e][2];
+                        fix -= fx; fiy -= fy; fiz -= fz;
+                        const int gj = ws.ang.atom[e];
+                        atomicAdd(&gx[gj], fx);
+                        atomicAdd(&gy[gj], fy);
+                        atomicAdd(&gz[gj], fz);
+                    }
+                }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -244,31 +261,17 @@ __global__ void __launch_bounds__(NW* kWarp)
                 fiz += __shfl_xor_sync(kFull, fiz, o);
             }
             if (lane == 0) {
-                atomicAdd(&sh.fmol[i][0], fix);
-                atomicAdd(&sh.fmol[i][1], fiy);
-                atomicAdd(&sh.fmol[i][2], fiz);
+                atomicAdd(&gx[gi], fix);
+                atomicAdd(&gy[gi], fiy);
+                atomicAdd(&gz[gi], fiz);
             }
             __syncwarp();
-        }
-        __syncthreads();
-        for (int s = threadIdx.x; s < n; s += NW * kWarp) {
-            const int gi = base + ms.orig[s];
-            if (nsplit == 1) {
-                gx[gi] = sh.fmol[s][0];
-                gy[gi] = sh.fmol[s][1];
-                gz[gi] = sh.fmol[s][2];
-            } else {
-                atomicAdd(&gx[gi], sh.fmol[s][0]);
-                atomicAdd(&gy[gi], sh.fmol[s][1]);
-                atomicAdd(&gz[gi], sh.fmol[s][2]);
-            }
         }
     }
 }
 
-// Zero fill of the three gradient arrays in one launch (atoms that belong to no molecule, or
-// to a skipped one, must read as zero, as they do after the reference's memset,
-// gpu_featurizer/functor_op_cpu.cpp:70-72).
+// Zero fill of the three gradient arrays in one launch (the gradient kernel accumulates into
+// them; the reference zero-fills in its functor, gpu_featurizer/functor_op_cpu.cpp:70-72).
 template <typename T> __global__ void zero3_kernel(T* a, T* b, T* c, int n)
 {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {

@@ -3,14 +3,14 @@
 //   scatter[i] = rank of atom i among atoms of its element, gather[i] = element start + rank,
 //   counts[4].
 //
-// The batch is cut into tiles of kSortTile consecutive atoms, one CTA per tile.  Inside a tile
-// the rank is a warp-level split: each warp ranks its 32-atom segments with one ballot per
-// element and a popc of the lanes below, and segment/warp bases come from a small scan in
-// shared memory.  What differs between the two variants is where a tile learns how many atoms
-// of each element precede it:
-//   * single launch (batches up to kSortSingleLaunchMax atoms): every CTA recounts the atoms
-//     in front of its tile straight from the (L2-resident) input, so no scratch memory and
-//     no second launch are needed;
+// The batch is cut into tiles of kSortTile consecutive atoms, one CTA per tile, one thread per
+// atom.  Inside a tile the rank is a warp-level split: each warp ranks its 32-atom segment
+// with one ballot per element and a popc of the lanes below, and the warp bases come from a
+// scan of the 32 per-warp counts by the first warp.  What differs between the two variants is
+// where a tile learns how many atoms of each element precede it:
+//   * single launch (batches up to kSortSingleLaunchMax atoms): every CTA recounts the whole
+//     batch straight from the (L2-resident) input with wide, unrolled loads, so no scratch
+//     memory and no second launch are needed;
 //   * three launches (any size): a histogram kernel writes per-tile counts to a scratch
 //     array of (tiles + 1) x 4 ints, one CTA scans it in place, and the ranking kernel reads
 //     the scanned entry of its tile.
@@ -20,29 +20,20 @@
 
 namespace ani {
 
-constexpr int kSortThreads = 256;
-constexpr int kSortItems = 4;                                  // atoms per thread (one int4)
-constexpr int kSortTile = kSortThreads * kSortItems;           // 1024 atoms per CTA
-constexpr int kSortSingleLaunchMax = 64 * kSortTile;           // 65536 atoms
+constexpr int kSortThreads = 1024;
+constexpr int kSortWarps = kSortThreads / kWarp;
+constexpr int kSortTile = kSortThreads;                 // 1024 atoms per CTA
+constexpr int kSortSingleLaunchMax = 64 * kSortTile;    // 65536 atoms
 
 struct Count4 {
     int c[kTypes];
 };
 
-__device__ __forceinline__ int checked_type(int t)
-{
-    if (t < 0 || t >= kTypes) {
-        report(ANI_ERR_BAD_ELEMENT);
-        t &= 3;
-    }
-    return t;
-}
-
-__device__ __forceinline__ void tally(Count4& v, int t)
+__device__ __forceinline__ void tally(Count4& v, int t, bool on)
 {
     t = checked_type(t);
 #pragma unroll
-    for (int g = 0; g < kTypes; g++) v.c[g] += (t == g) ? 1 : 0;
+    for (int g = 0; g < kTypes; g++) v.c[g] += (on && t == g) ? 1 : 0;
 }
 
 // Sum of per-thread Count4 over the CTA; result valid in every thread.
@@ -59,32 +50,49 @@ __device__ __forceinline__ Count4 block_sum(Count4 v, int (*red)[kTypes])
     Count4 out;
 #pragma unroll
     for (int g = 0; g < kTypes; g++) {
-        int s = 0;
+        int s = lane < kSortWarps ? red[lane][g] : 0;
 #pragma unroll
-        for (int w = 0; w < kSortThreads / kWarp; w++) s += red[w][g];
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
         out.c[g] = s;
     }
     __syncthreads();
     return out;
 }
 
-// Count the elements of types[lo, hi) with the whole CTA (vectorised where aligned).
-__device__ __forceinline__ Count4 count_range(const int* __restrict__ types, int lo, int hi)
+// Counts types[0, n) twice in one sweep: everything (`total`) and the part in front of
+// `split` (`before`).  `split` is a multiple of 4.  Loads are 16 bytes wide and issued four
+// at a time so that their L2 latencies overlap.
+__device__ __forceinline__ void count_two_ranges(const int* __restrict__ types, int n, int split,
+                                                 Count4* before, Count4* total)
 {
-    Count4 v = {{0, 0, 0, 0}};
-    // lo is a multiple of kSortTile, so the vector path only needs an aligned base pointer.
-    const bool aligned = (reinterpret_cast<uintptr_t>(types + lo) & 15u) == 0;
-    const int nvec = aligned ? (hi - lo) / 4 : 0;
-    const int4* p4 = reinterpret_cast<const int4*>(types + lo);
-    for (int k = threadIdx.x; k < nvec; k += kSortThreads) {
-        const int4 q = p4[k];
-        tally(v, q.x);
-        tally(v, q.y);
-        tally(v, q.z);
-        tally(v, q.w);
+    Count4 vb = {{0, 0, 0, 0}}, vt = {{0, 0, 0, 0}};
+    const bool aligned = (reinterpret_cast<uintptr_t>(types) & 15u) == 0;
+    const int nvec = aligned ? n / 4 : 0;
+    const int4* p4 = reinterpret_cast<const int4*>(types);
+    constexpr int kUnroll = 4;
+    for (int k0 = threadIdx.x; k0 < nvec; k0 += kSortThreads * kUnroll) {
+        int4 q[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            const int k = k0 + u * kSortThreads;
+            q[u] = k < nvec ? p4[k] : make_int4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            const int k = k0 + u * kSortThreads;
+            const bool on = k < nvec, front = on && 4 * k < split;
+            tally(vt, q[u].x, on); tally(vt, q[u].y, on); tally(vt, q[u].z, on); tally(vt, q[u].w, on);
+            tally(vb, q[u].x, front); tally(vb, q[u].y, front); tally(vb, q[u].z, front);
+            tally(vb, q[u].w, front);
+        }
     }
-    for (int k = lo + nvec * 4 + threadIdx.x; k < hi; k += kSortThreads) tally(v, types[k]);
-    return v;
+    for (int k = nvec * 4 + threadIdx.x; k < n; k += kSortThreads) {
+        const int t = types[k];
+        tally(vt, t, true);
+        tally(vb, t, k < split);
+    }
+    *before = vb;
+    *total = vt;
 }
 
 // Ranks the atoms of tile `tile` given the per-element counts in front of the tile (`before`)
@@ -95,51 +103,40 @@ __device__ __forceinline__ void rank_tile(const int* __restrict__ types, int n_a
                                           int (*warp_counts)[kTypes])
 {
     const int lane = lane_id(), warp = warp_id();
-    const int tile_base = tile * kSortTile;
-    // warp w ranks segments [w*kSortItems, (w+1)*kSortItems) of 32 consecutive atoms
-    int t[kSortItems];
-    int rank_in_warp[kSortItems];
-    int seen[kTypes] = {0, 0, 0, 0};
+    const int i = tile * kSortTile + threadIdx.x;
+    const int t = i < n_atoms ? checked_type(types[i]) : -1;
+    int rank = 0;
 #pragma unroll
-    for (int s = 0; s < kSortItems; s++) {
-        const int i = tile_base + (warp * kSortItems + s) * kWarp + lane;
-        t[s] = i < n_atoms ? checked_type(types[i]) : -1;
-        rank_in_warp[s] = 0;
-#pragma unroll
-        for (int g = 0; g < kTypes; g++) {
-            const unsigned m = __ballot_sync(kFull, t[s] == g);
-            if (t[s] == g) rank_in_warp[s] = seen[g] + __popc(m & lanemask_lt());
-            seen[g] += __popc(m);
-        }
-    }
-    if (lane == 0) {
-#pragma unroll
-        for (int g = 0; g < kTypes; g++) warp_counts[warp][g] = seen[g];
+    for (int g = 0; g < kTypes; g++) {
+        const unsigned m = __ballot_sync(kFull, t == g);
+        if (t == g) rank = __popc(m & lanemask_lt());
+        if (lane == 0) warp_counts[warp][g] = __popc(m);
     }
     __syncthreads();
-    int start[kTypes];
-    {
-        int acc = 0;
+    if (warp == 0) {  // exclusive scan over the warps, one element per step
 #pragma unroll
         for (int g = 0; g < kTypes; g++) {
-            start[g] = acc;
-            acc += total.c[g];
+            const int v = warp_counts[lane][g];
+            int x = v;
+#pragma unroll
+            for (int o = 1; o < kWarp; o <<= 1) {
+                const int y = __shfl_up_sync(kFull, x, o);
+                if (lane >= o) x += y;
+            }
+            warp_counts[lane][g] = x - v;
         }
     }
+    __syncthreads();
+    if (i < n_atoms) {
+        int start = 0;
 #pragma unroll
-    for (int s = 0; s < kSortItems; s++) {
-        const int i = tile_base + (warp * kSortItems + s) * kWarp + lane;
-        if (i < n_atoms) {
-            int r = rank_in_warp[s];
-#pragma unroll
-            for (int g = 0; g < kTypes; g++) {
-                if (t[s] == g) {
-                    r += before.c[g];
-                    for (int w = 0; w < warp; w++) r += warp_counts[w][g];
-                    scatter[i] = r;
-                    gather[i] = start[g] + r;
-                }
+        for (int g = 0; g < kTypes; g++) {
+            if (t == g) {
+                const int r = before.c[g] + warp_counts[warp][g] + rank;
+                scatter[i] = r;
+                gather[i] = start + r;
             }
+            start += total.c[g];
         }
     }
 }
@@ -149,15 +146,16 @@ __global__ void __launch_bounds__(kSortThreads)
     sort_single_kernel(const int* __restrict__ types, int n_atoms, int* __restrict__ scatter,
                        int* __restrict__ gather, int* __restrict__ counts)
 {
-    __shared__ int red[kSortThreads / kWarp][kTypes];
+    __shared__ int red[kSortWarps][kTypes];
     const int tile = blockIdx.x;
-    const int tile_base = tile * kSortTile;
-    const Count4 before = block_sum(count_range(types, 0, tile_base), red);
-    const Count4 rest = block_sum(count_range(types, tile_base, n_atoms), red);
-    Count4 total;
+    Count4 vb, vt;
+    count_two_ranges(types, n_atoms, tile * kSortTile, &vb, &vt);
+    const Count4 before = block_sum(vb, red);
+    const Count4 total = block_sum(vt, red);
+    if (tile == 0 && threadIdx.x == 0) {
 #pragma unroll
-    for (int g = 0; g < kTypes; g++) total.c[g] = before.c[g] + rest.c[g];
-    if (tile == 0 && threadIdx.x < kTypes) counts[threadIdx.x] = total.c[threadIdx.x];
+        for (int g = 0; g < kTypes; g++) counts[g] = total.c[g];
+    }
     rank_tile(types, n_atoms, tile, before, total, scatter, gather, red);
 }
 
@@ -165,12 +163,16 @@ __global__ void __launch_bounds__(kSortThreads)
 __global__ void __launch_bounds__(kSortThreads)
     sort_histogram_kernel(const int* __restrict__ types, int n_atoms, int* __restrict__ tile_counts)
 {
-    __shared__ int red[kSortThreads / kWarp][kTypes];
+    __shared__ int red[kSortWarps][kTypes];
     const int tile = blockIdx.x;
-    const int lo = tile * kSortTile;
-    const int hi = min(n_atoms, lo + kSortTile);
-    const Count4 c = block_sum(count_range(types, lo, hi), red);
-    if (threadIdx.x < kTypes) tile_counts[tile * kTypes + threadIdx.x] = c.c[threadIdx.x];
+    const int i = tile * kSortTile + threadIdx.x;
+    Count4 v = {{0, 0, 0, 0}};
+    if (i < n_atoms) tally(v, types[i], true);
+    const Count4 c = block_sum(v, red);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int g = 0; g < kTypes; g++) tile_counts[tile * kTypes + g] = c.c[g];
+    }
 }
 
 // Large batches, second: exclusive scan over tiles, in place, by one CTA.  On return
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(kSortThreads)
 __global__ void __launch_bounds__(kSortThreads)
     sort_scan_kernel(int* __restrict__ tile_counts, int n_tiles)
 {
-    __shared__ int warp_tot[kSortThreads / kWarp][kTypes];
+    __shared__ int warp_tot[kSortWarps][kTypes];
     __shared__ int carry[kTypes];
     const int lane = lane_id(), warp = warp_id();
     if (threadIdx.x < kTypes) carry[threadIdx.x] = 0;
@@ -208,7 +210,7 @@ __global__ void __launch_bounds__(kSortThreads)
         __syncthreads();
         if (threadIdx.x < kTypes) {
             int s = carry[threadIdx.x];
-            for (int w = 0; w < kSortThreads / kWarp; w++) s += warp_tot[w][threadIdx.x];
+            for (int w = 0; w < kSortWarps; w++) s += warp_tot[w][threadIdx.x];
             carry[threadIdx.x] = s;
         }
         __syncthreads();
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(kSortThreads)
                      const int* __restrict__ tile_counts, int n_tiles, int* __restrict__ scatter,
                      int* __restrict__ gather, int* __restrict__ counts)
 {
-    __shared__ int red[kSortThreads / kWarp][kTypes];
+    __shared__ int red[kSortWarps][kTypes];
     const int tile = blockIdx.x;
     Count4 before, total;
 #pragma unroll
@@ -230,7 +232,10 @@ __global__ void __launch_bounds__(kSortThreads)
         before.c[g] = tile_counts[tile * kTypes + g];
         total.c[g] = tile_counts[n_tiles * kTypes + g];
     }
-    if (tile == 0 && threadIdx.x < kTypes) counts[threadIdx.x] = total.c[threadIdx.x];
+    if (tile == 0 && threadIdx.x == 0) {
+#pragma unroll
+        for (int g = 0; g < kTypes; g++) counts[g] = total.c[g];
+    }
     rank_tile(types, n_atoms, tile, before, total, scatter, gather, red);
 }
 

@@ -122,6 +122,18 @@ def test_forward_vs_oracle(gpu, oracle_mod, ref_impl, case, dt):
         assert normwise(feats[t], ref[t]) < FTOL[dt], (case, t)
 
 
+def test_sort_no_scratch_and_scratch_paths_agree(gpu, oracle_mod):
+    # 65536 atoms take the single-launch path, 65537 the three-launch path with scratch
+    rng = np.random.default_rng(77)
+    a = rng.integers(0, 4, 65537).astype(np.int32)
+    big = gpu.gpu_sort(a)
+    small = gpu.gpu_sort(a[:65536])
+    e_big, e_small = oracle_mod.ani_sort(a), oracle_mod.ani_sort(a[:65536])
+    for got, exp in ((big, e_big), (small, e_small)):
+        for g, e in zip(got, exp):
+            np.testing.assert_array_equal(g, e)
+
+
 def test_forward_is_bit_reproducible(gpu):
     b = syn.config1(n_mols=256)
     one = gpu.gpu_featurize(b, np.float32)
@@ -250,16 +262,59 @@ def test_dense_cluster_takes_the_streaming_path(gpu, oracle_mod):
             assert normwise(out[k], gref[k]) < FTOL[dt]
 
 
-def test_molecule_above_staging_limit_is_reported(gpu):
-    from khan_b200 import _lib, ani_mod
-    n = _lib.lib().ani_max_atoms_per_molecule() + 1
-    rng = np.random.default_rng(0)
-    b = syn.Batch(rng.uniform(0, 30, n), rng.uniform(0, 30, n), rng.uniform(0, 30, n),
-                  np.zeros(n, np.int32), np.array([0], np.int32), np.array([n], np.int32))
-    x, y, z, a, mo, mac = gpu.batch_tensors(b, np.float32)
-    si, gi, ac = ani_mod.ani_sort(a)
-    ani_mod.featurize(x, y, z, a, mo, mac, si, ac)
-    assert ani_mod.device_status() == -5
+def test_one_large_molecule(gpu, oracle_mod):
+    # a single 700-atom molecule: every warp of the molecule walks 22 atoms, 22 scan chunks each
+    b = syn.config4(seed=11, n_mols=1, n_min=700, n_max=700)
+    si, gi, ac = oracle_mod.ani_sort(b.atomic_numbers)
+    x, y, z = b.coords(np.float64)
+    ref = oracle_mod.featurize(x, y, z, b.atomic_numbers, b.mol_offsets, b.mol_atom_counts, si, ac,
+                               threads=1)
+    feats = gpu.gpu_featurize(b, np.float64)
+    for t in range(4):
+        assert normwise(feats[t], ref[t]) < 1e-12
+    up = syn.upstream_grads(b, ac, dtype=np.float64)
+    gref = oracle_mod.featurize_grad(x, y, z, b.atomic_numbers, b.mol_offsets, b.mol_atom_counts,
+                                     si, ac, *up)
+    out = gpu.gpu_featurize_grad(b, np.float64, up)
+    for k in range(3):
+        assert normwise(out[k], gref[k]) < 1e-12
+
+
+def test_unordered_molecule_table(gpu, oracle_mod):
+    # molecule ranges listed in a shuffled order, with unused atoms between them
+    b = syn.config1(n_mols=40)
+    rng = np.random.default_rng(8)
+    keep = np.sort(rng.choice(40, size=25, replace=False))
+    order = rng.permutation(keep)
+    shuffled = syn.Batch(b.xs, b.ys, b.zs, b.atomic_numbers, b.mol_offsets[order].copy(),
+                         b.mol_atom_counts[order].copy())
+    si, gi, ac = oracle_mod.ani_sort(b.atomic_numbers)
+    x, y, z = b.coords(np.float32)
+    ref = oracle_mod.featurize(x, y, z, b.atomic_numbers, shuffled.mol_offsets,
+                               shuffled.mol_atom_counts, si, ac)
+    import torch
+    from khan_b200 import ani_mod
+    xt, yt, zt, a, mo, mac = gpu.batch_tensors(shuffled, np.float32)
+    out = torch.full((b.n_atoms, 384), 123.0, device=xt.device)
+    ani_mod.featurize_into(xt, yt, zt, a, mo, mac, gpu.to_dev(si), ac.astype(np.int32), out)
+    got = out.cpu().numpy()
+    start = np.concatenate([[0], np.cumsum(ac)])
+    used = np.zeros(b.n_atoms, bool)
+    for off, cnt in zip(shuffled.mol_offsets, shuffled.mol_atom_counts):
+        used[off:off + cnt] = True
+    for t in range(4):
+        rows = got[start[t]:start[t + 1]]
+        mask = used[b.atomic_numbers == t]
+        assert normwise(rows[mask], ref[t].reshape(-1, 384)[mask]) < 1e-5
+        assert (rows[~mask] == 123.0).all()  # rows of atoms outside every molecule are untouched
+    up = syn.upstream_grads(b, ac, dtype=np.float32)
+    gref = oracle_mod.featurize_grad(*(v.astype(np.float64) for v in (x, y, z)), b.atomic_numbers,
+                                     shuffled.mol_offsets, shuffled.mol_atom_counts, si, ac,
+                                     *[u.astype(np.float64) for u in up])
+    outg = gpu.gpu_featurize_grad(shuffled, np.float32, up, si=si, ac=ac)
+    for k in range(3):
+        assert normwise(outg[k], gref[k]) < 1e-5
+        assert (outg[k][~used] == 0).all()
 
 
 def test_inconsistent_offsets_are_reported_not_dereferenced(gpu):
