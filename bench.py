@@ -153,7 +153,7 @@ def cpu_baseline(batch, budget_s: float = 12.0):
         cpu_fwd_grad(oracle, impl, batch, up, threads)
         reps += 1
         el = time.perf_counter() - t0
-        if el >= budget_s or reps >= 64:
+        if el >= budget_s or reps >= 2000:
             break
     return {"value": batch.n_atoms * reps / el, "unit": UNIT, "cores": threads,
             "kind": "reference" if impl == "ref_fast" else "port",
@@ -221,6 +221,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 256)")
     ap.add_argument("--streams", type=int, default=4,
                     help="independent batches in flight: steps are issued round-robin over this many streams")
+    ap.add_argument("--mols", type=int, default=N_MOLS,
+                    help="molecules per batch (1024 is the benchmark workload; other sizes are for profiling)")
     ap.add_argument("--profile", action="store_true",
                     help="only W warm-up and K timed steps, launched eagerly on one stream (for ncu)")
     args = ap.parse_args()
@@ -253,7 +255,7 @@ def main():
 
     # ---- workload: NB distinct 1024-molecule batches per rank (weak scaling) -------------
     nb = max(1, min(args.batches, args.steps))
-    batches = syn.batch_pool(nb, n_mols=N_MOLS, seed=1 + 100 * rank)
+    batches = syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)
     max_atoms = max(b.n_atoms for b in batches)
     host = []
     for k, b in enumerate(batches):
@@ -261,7 +263,7 @@ def main():
         host.append(HostBatch(b, syn.upstream_grads(b, ac, seed=12 + k), pin=(k < 16)))
     staged = []
     for hb in host:
-        sb = StagedBatch(max_atoms, N_MOLS, device=dev)
+        sb = StagedBatch(max_atoms, args.mols, device=dev)
         sb.upload(hb, non_blocking=False)
         staged.append(sb)
     torch.cuda.synchronize()
@@ -399,7 +401,7 @@ def main():
     e2e_steps = args.e2e_steps or min(args.steps, 256)
     n_slots = 3
     n_host = min(len(host), 16)
-    slots = [StagedBatch(max_atoms, N_MOLS, device=dev) for _ in range(n_slots)]
+    slots = [StagedBatch(max_atoms, args.mols, device=dev) for _ in range(n_slots)]
     streams = [torch.cuda.Stream(device=dev) for _ in range(n_slots)]
     out_feat = [torch.empty((max_atoms, FEATURE_SIZE), dtype=torch.float32).pin_memory() for _ in range(n_slots)]
     out_grad = [torch.empty((3, max_atoms), dtype=torch.float32).pin_memory() for _ in range(n_slots)]
@@ -481,7 +483,7 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "config1: 1024 GDB8-like molecules per step per GPU, float32, "
                                "ani_sort + featurize + featurize_grad",
-                   "molecules_per_step": N_MOLS, "atoms_per_step": mean_atoms,
+                   "molecules_per_step": args.mols, "atoms_per_step": mean_atoms,
                    "resident_batches": nb, "l2": "inputs larger than L2 (distinct batches cycled)",
                    "launch": launch_mode, "streams": n_streams,
                    "parallelism": f"molecule shards x{world}, no collective"},

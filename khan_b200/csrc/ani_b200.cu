@@ -123,7 +123,7 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
     return ANI_OK;
 }
 
-template <typename T, int CAPT = kCapT>
+template <typename T>
 int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types, const int* mos,
                         const int* macs, int n_mols, const int* sis, const T* gh, const T* gc,
                         const T* gn, const T* go, T* gx, T* gy, T* gz, const int* acs_host,
@@ -148,8 +148,8 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
     for (int t = 0; t < kTypes; t++)
         if (acs_host[t] > 0 && !gin[t]) return ANI_ERR_NULL_POINTER;
 
-    auto kernel = featurize_grad_kernel<T, kNW, CAPT>;
-    const size_t smem = kNW * sizeof(GradWarpShared<T, CAPT>);
+    auto kernel = featurize_grad_kernel<T, kNW>;
+    const size_t smem = kNW * sizeof(GradWarpShared<T>);
     static thread_local int configured_dev = -1;
     int dev = 0;
     ANI_CUDA(cudaGetDevice(&dev));

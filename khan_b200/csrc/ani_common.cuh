@@ -101,108 +101,143 @@ __device__ __forceinline__ int checked_type(int t)
     return t;
 }
 
-// ---------------------------------------------------------------------------------------
-// Angular neighbour list of one central atom: every j != i with r_ij < A_Rc, kept as four
-// per-element sub-lists of capacity CAPT (entry index = type * CAPT + position), each in
-// ascending order of j.
-// ---------------------------------------------------------------------------------------
-template <typename T, int CAPT, bool GRAD> struct AngularList {
-    T ux[kTypes * CAPT], uy[kTypes * CAPT], uz[kTypes * CAPT];  // (x_i - x_j) / r_ij
-    T r[kTypes * CAPT];
-    T fc[kTypes * CAPT];                        // f_C(r_ij, A_Rc)
-    T dfc[GRAD ? kTypes * CAPT : 1];            // its derivative
-    int atom[GRAD ? kTypes * CAPT : 1];         // batch index of j
+template <typename T> struct alignas(sizeof(T) * 4) Vec4 {
+    T x, y, z, w;
+};
+template <typename T> struct alignas(sizeof(T) * 2) Vec2 {
+    T x, y;
 };
 
-// ---------------------------------------------------------------------------------------
-// Padded, bucket-major enumeration of the unordered pairs of an angular list.  Bucket
-// bk = pair_bucket(ta, tb), ta <= tb.  The pairs of bucket bk occupy positions
-// [off[bk], off[bk] + cnt) of a range whose length is rounded up to a multiple of 4
-// (off[bk+1] - off[bk]), so that the contraction pass always reads four pairs at a time.
-// ---------------------------------------------------------------------------------------
-struct PairOffsets {
-    int off[kPairBuckets + 1];
-};
-
-struct PairBucketInfo {
-    int cnt;      // real pairs in the bucket
-    int base_a;   // list index of the first entry of group ta
-    int base_b;   // list index of the first entry of group tb
-    int nb_same;  // size of group tb | (ta == tb) << 16
-};
-
-// Every lane computes the offsets (they are warp-uniform); lanes 0..9 also write the per-bucket
-// record used by decode_pair, and the offsets are mirrored to `off_smem[0..10]` for code that
-// indexes them with a runtime (warp-uniform) bucket number.  Ends with __syncwarp().
-template <int CAPT>
-__device__ __forceinline__ void build_pair_table(PairBucketInfo* tab, int* off_smem,
-                                                 const int* ang_count, PairOffsets* po)
+// Warp-uniform value picked from four registers by a lane-dependent index 0..3.
+template <typename V> __device__ __forceinline__ V pick4(const V* v, int k)
 {
-    int off = 0;
+    return k == 0 ? v[0] : (k == 1 ? v[1] : (k == 2 ? v[2] : v[3]));
+}
+
+// r = |d| and 1/r from the squared length with one SFU op (float) / full precision (double).
+// A zero length (two atoms at one point) yields r = 0, inv = 0 instead of Inf/NaN, so that a
+// degenerate pair cannot poison the shared-memory lists that later atoms reuse.
+__device__ __forceinline__ void length_and_inverse(float d2, float* r, float* inv)
+{
+    const float rs = d2 > 0.0f ? sfu_rsqrt(d2) : 0.0f;
+    *inv = rs;
+    *r = d2 * rs;
+}
+__device__ __forceinline__ void length_and_inverse(double d2, double* r, double* inv)
+{
+    const double rr = sqrt(d2);
+    *r = rr;
+    *inv = d2 > 0.0 ? 1.0 / rr : 0.0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Padded, bucket-major enumeration of the unordered pairs of an angular neighbour list that is
+// kept as four per-element sub-lists of capacity CAPT (entry index = type * CAPT + position).
+// Bucket bk = pair_bucket(ta, tb), ta <= tb.  The pairs of bucket bk occupy positions
+// [off, off + cnt) of a range whose length is rounded up to a multiple of 4, so that the
+// contraction pass of the forward kernel always reads four pairs at a time.
+// ---------------------------------------------------------------------------------------
+struct alignas(16) PairBucketInfo {
+    int off;      // padded start position
+    int cnt;      // real pairs in the bucket
+    int packed;   // base_a | base_b << 8 | nb << 16 | same << 24
+    float inv_nb; // 1 / size of group tb
+};
+
+constexpr int kQuadTable = 64;  // quads (4 padded positions) whose bucket is looked up from a table
+
+struct PairTables {
+    PairBucketInfo tab[kPairBuckets];
+    int off[kPairBuckets + 2];            // off[bk], off[10] = padded total
+    unsigned char quad_bucket[kQuadTable];
+};
+
+// ta / tb of bucket k, two bits each.
+constexpr unsigned kBucketTa = 0u | (0u << 2) | (0u << 4) | (0u << 6) | (1u << 8) | (1u << 10) |
+                               (1u << 12) | (2u << 14) | (2u << 16) | (3u << 18);
+constexpr unsigned kBucketTb = 0u | (1u << 2) | (2u << 4) | (3u << 6) | (1u << 8) | (2u << 10) |
+                               (3u << 12) | (2u << 14) | (3u << 16) | (3u << 18);
+
+// Lanes 0..9 each build one bucket record; the padded offsets come from a warp scan.  Returns
+// the padded total (warp-uniform).  Ends with __syncwarp().
+template <int CAPT>
+__device__ __forceinline__ int build_pair_tables(PairTables& pt, const int* ang_count)
+{
     const int lane = lane_id();
+    const int ta = (kBucketTa >> (2 * lane)) & 3, tb = (kBucketTb >> (2 * lane)) & 3;
+    const int na = pick4(ang_count, ta), nb = pick4(ang_count, tb);
+    const int cnt = lane < kPairBuckets ? (ta == tb ? na * (na - 1) / 2 : na * nb) : 0;
+    const int pad = (cnt + 3) & ~3;
+    int incl = pad;
 #pragma unroll
-    for (int ta = 0; ta < kTypes; ta++) {
-#pragma unroll
-        for (int tb = ta; tb < kTypes; tb++) {
-            const int bk = kTypes * (kTypes - 1) / 2 - (kTypes - ta) * (kTypes - ta - 1) / 2 + tb;
-            const int na = ang_count[ta], nb = ang_count[tb];
-            const int cnt = ta == tb ? na * (na - 1) / 2 : na * nb;
-            po->off[bk] = off;
-            if (lane == bk) {
-                PairBucketInfo e;
-                e.cnt = cnt;
-                e.base_a = ta * CAPT;
-                e.base_b = tb * CAPT;
-                e.nb_same = nb | ((ta == tb ? 1 : 0) << 16);
-                tab[bk] = e;
-                off_smem[bk] = off;
-            }
-            off += (cnt + 3) & ~3;
-        }
+    for (int o = 1; o < 16; o <<= 1) {
+        const int y = __shfl_up_sync(kFull, incl, o);
+        if (lane >= o) incl += y;
     }
-    po->off[kPairBuckets] = off;
-    if (lane == kPairBuckets) off_smem[kPairBuckets] = off;
+    const int off = incl - pad;
+    if (lane < kPairBuckets) {
+        PairBucketInfo e;
+        e.off = off;
+        e.cnt = cnt;
+        e.packed = (ta * CAPT) | ((tb * CAPT) << 8) | (nb << 16) | ((ta == tb ? 1 : 0) << 24);
+        e.inv_nb = 1.0f / (float)(nb > 0 ? nb : 1);
+        pt.tab[lane] = e;
+    }
+    if (lane <= kPairBuckets) pt.off[lane] = off;
+    const int total = __shfl_sync(kFull, incl, kPairBuckets - 1);
     __syncwarp();
+    // bucket of every quad of padded positions (all bucket starts are multiples of 4)
+    const int n_quads = min(total >> 2, kQuadTable);
+    for (int q = lane; q < n_quads; q += kWarp) {
+        int bk = 0;
+#pragma unroll
+        for (int k = 1; k < kPairBuckets; k++) bk += (4 * q >= pt.off[k]) ? 1 : 0;
+        pt.quad_bucket[q] = (unsigned char)bk;
+    }
+    __syncwarp();
+    return total;
 }
 
 // Row b of q = b(b-1)/2 + a (a < b), the strictly-lower-triangular enumeration.
 __device__ __forceinline__ int tri_row(int q)
 {
-    int b = (int)((1.0f + sqrtf(8.0f * (float)q + 1.0f)) * 0.5f);
+    const float x = 8.0f * (float)q + 1.0f;
+    int b = (int)((1.0f + x * sfu_rsqrt(x)) * 0.5f);
     if (b * (b - 1) / 2 > q) b--;
     if ((b + 1) * b / 2 <= q) b++;
     return b;
 }
 
 // Padded position p -> (bucket, list index a, list index b).  Returns false for a padding slot
-// (a and b then point at entry 0, which is always readable).
-__device__ __forceinline__ bool decode_pair(const PairBucketInfo* tab, const PairOffsets& po, int p,
-                                            int* bucket, int* a, int* b)
+// (a and b then point at entry 0 of the list).
+__device__ __forceinline__ bool decode_pair(const PairTables& pt, int p, int* bucket, int* a, int* b)
 {
-    int bk = 0;
+    int bk;
+    const int quad = p >> 2;
+    if (quad < kQuadTable) {
+        bk = pt.quad_bucket[quad];
+    } else {
+        bk = 0;
 #pragma unroll
-    for (int k = 1; k < kPairBuckets; k++) bk += (p >= po.off[k]) ? 1 : 0;
-    int start = po.off[0];
-#pragma unroll
-    for (int k = 1; k < kPairBuckets; k++) start = (p >= po.off[k]) ? po.off[k] : start;
-    const PairBucketInfo e = tab[bk];
-    const int q = p - start;
+        for (int k = 1; k < kPairBuckets; k++) bk += (p >= pt.off[k]) ? 1 : 0;
+    }
+    const PairBucketInfo e = pt.tab[bk];
+    const int q = p - e.off;
     const bool valid = q < e.cnt;
-    const int nb = e.nb_same & 0xffff;
+    const int nb = (e.packed >> 16) & 0xff;
     int ia, ib;
-    if (e.nb_same >> 16) {
+    if (e.packed >> 24) {
         ib = tri_row(q);
         ia = q - ib * (ib - 1) / 2;
     } else {
-        // q / nb for q < 2^22 via a float reciprocal, corrected by one step
-        ia = (int)(((float)q + 0.5f) * (1.0f / (float)(nb > 0 ? nb : 1)));
+        ia = (int)(((float)q + 0.5f) * e.inv_nb);
         ib = q - ia * nb;
         if (ib < 0) { ia--; ib += nb; }
-        if (ib >= nb && nb > 0) { ia++; ib -= nb; }
+        if (ib >= nb) { ia++; ib -= nb; }
     }
     *bucket = bk;
-    *a = valid ? e.base_a + ia : 0;
-    *b = valid ? e.base_b + ib : 0;
+    *a = valid ? (e.packed & 0xff) + ia : 0;
+    *b = valid ? ((e.packed >> 8) & 0xff) + ib : 0;
     return valid;
 }
 

@@ -26,13 +26,12 @@ namespace ani {
 constexpr int kPadStride = 36;  // 32 pairs + 4 words: keeps the 16-byte reads of pass C conflict-free
 
 template <typename T, int CAPT, int CAPR> struct FeaturizeWarpShared {
-    AngularList<T, CAPT, false> ang;
-    T rad_r[kTypes * CAPR];
-    T rad_fc[kTypes * CAPR];
+    Vec4<T> ang_u[kTypes * CAPT];   // (x_i - x_j) / r_ij and r_ij, per-element sub-lists
+    T ang_fc[kTypes * CAPT];        // f_C(r_ij, A_Rc)
+    Vec2<T> rad[kTypes * CAPR];     // (r_ij, f_C(r_ij, R_Rc)), per-element sub-lists
     alignas(16) T A[kNumThetas][kPadStride];
     alignas(16) T BF[kNumARs][kPadStride];
-    alignas(16) PairBucketInfo tab[kPairBuckets];
-    int off[kPairBuckets + 2];  // copy of the bucket offsets for warp-uniform dynamic indexing
+    PairTables pt;
 };
 
 template <typename T> __device__ __forceinline__ T* element_buffer(int t, T* h, T* c, T* n, T* o)
@@ -120,6 +119,14 @@ __global__ void __launch_bounds__(NW* kWarp)
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
+    // The angular list is read at entry 0 by padding lanes and may be read before this warp
+    // ever wrote it: give every entry a finite value once.
+    for (int e = lane; e < kTypes * CAPT; e += kWarp) {
+        ws.ang_u[e] = Vec4<T>{(T)1, (T)0, (T)0, (T)1};
+        ws.ang_fc[e] = (T)0;
+    }
+    __syncwarp();
+
     constexpr int kCtasPerMol = kSlotsPerMol / NW;
     for (long long cta = blockIdx.x; cta < (long long)n_mols * kCtasPerMol; cta += gridDim.x) {
         const int m = (int)(cta / kCtasPerMol);
@@ -148,39 +155,31 @@ __global__ void __launch_bounds__(NW* kWarp)
                 const int gj = base + (live ? j : 0);
                 const T dx = xi - xs[gj], dy = yi - ys[gj], dz = zi - zs[gj];
                 const int tj = live ? checked_type(types[gj]) : -1;
-                const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
+                T r, inv;
+                length_and_inverse(dx * dx + dy * dy + dz * dz, &r, &inv);
                 const bool in_rad = live && j != i && r < (T)kR_Rc;
                 const bool in_ang = in_rad && r < (T)kA_Rc;
-                T fcR = (T)0, fcA = (T)0, inv = (T)0;
-                if (in_rad) fcR = cutoff_value<T>(r, (T)kR_Rc);
+                unsigned tm[kTypes];
+#pragma unroll
+                for (int g = 0; g < kTypes; g++) tm[g] = __ballot_sync(kFull, tj == g);
+                const unsigned mR = __ballot_sync(kFull, in_rad);
+                const unsigned mA = __ballot_sync(kFull, in_ang);
+                const unsigned mine = pick4(tm, tj) & lanemask_lt();
+                if (in_rad) {
+                    const int pos = pick4(cR, tj) + __popc(mR & mine);
+                    if (pos < CAPR) ws.rad[tj * CAPR + pos] = Vec2<T>{r, cutoff_value<T>(r, (T)kR_Rc)};
+                }
                 if (in_ang) {
-                    fcA = cutoff_value<T>(r, (T)kA_Rc);
-                    inv = (T)1 / r;
+                    const int pos = pick4(cA, tj) + __popc(mA & mine);
+                    if (pos < CAPT) {
+                        ws.ang_u[tj * CAPT + pos] = Vec4<T>{dx * inv, dy * inv, dz * inv, r};
+                        ws.ang_fc[tj * CAPT + pos] = cutoff_value<T>(r, (T)kA_Rc);
+                    }
                 }
 #pragma unroll
                 for (int g = 0; g < kTypes; g++) {
-                    const unsigned mR = __ballot_sync(kFull, in_rad && tj == g);
-                    const unsigned mA = __ballot_sync(kFull, in_ang && tj == g);
-                    if (in_rad && tj == g) {
-                        const int pos = cR[g] + __popc(mR & lanemask_lt());
-                        if (pos < CAPR) {
-                            ws.rad_r[g * CAPR + pos] = r;
-                            ws.rad_fc[g * CAPR + pos] = fcR;
-                        }
-                    }
-                    if (in_ang && tj == g) {
-                        const int pos = cA[g] + __popc(mA & lanemask_lt());
-                        if (pos < CAPT) {
-                            const int e = g * CAPT + pos;
-                            ws.ang.ux[e] = dx * inv;
-                            ws.ang.uy[e] = dy * inv;
-                            ws.ang.uz[e] = dz * inv;
-                            ws.ang.r[e] = r;
-                            ws.ang.fc[e] = fcA;
-                        }
-                    }
-                    cR[g] += __popc(mR);
-                    cA[g] += __popc(mA);
+                    cR[g] += __popc(mR & tm[g]);
+                    cA[g] += __popc(mA & tm[g]);
                 }
             }
             __syncwarp();
@@ -202,8 +201,9 @@ __global__ void __launch_bounds__(NW* kWarp)
                 for (int g = 0; g < kTypes; g++) {
                     acc[g] = (T)0;
                     for (int p = half; p < cR[g]; p += 2) {
-                        const T d = ws.rad_r[g * CAPR + p] - shift;
-                        acc[g] += Num<T>::exp_neg((T)kR_eta, d * d) * ws.rad_fc[g * CAPR + p];
+                        const Vec2<T> e = ws.rad[g * CAPR + p];
+                        const T d = e.x - shift;
+                        acc[g] += Num<T>::exp_neg((T)kR_eta, d * d) * e.y;
                     }
                     acc[g] += __shfl_xor_sync(kFull, acc[g], 16);
                 }
@@ -212,29 +212,26 @@ __global__ void __launch_bounds__(NW* kWarp)
             }
 
             // ---- B + C: angular features ----
-            PairOffsets po;
-            build_pair_table<CAPT>(ws.tab, ws.off, cA, &po);
-            const int total = po.off[kPairBuckets];
-            const int my_t = lane >> 2, my_s = lane & 3;
-            const T* a_row = &ws.A[my_t][0];
-            const T* b_row = &ws.BF[my_s][0];
-            int cur = 0;  // bucket being accumulated
-            int cur_end = po.off[1];
+            const int total = build_pair_tables<CAPT>(ws.pt, cA);
+            const T* a_row = &ws.A[lane >> 2][0];
+            const T* b_row = &ws.BF[lane & 3][0];
+            int cur = 0;                  // bucket being accumulated
+            int cur_end = ws.pt.off[1];   // padded end of bucket `cur`
             T acc0 = (T)0, acc1 = (T)0;
             for (int c0 = 0; c0 < total; c0 += kWarp) {
                 {   // B: lane = pair
                     int bk, a, b;
-                    const bool valid = decode_pair(ws.tab, po, c0 + lane, &bk, &a, &b);
-                    const T cosv = ws.ang.ux[a] * ws.ang.ux[b] + ws.ang.uy[a] * ws.ang.uy[b] +
-                                   ws.ang.uz[a] * ws.ang.uz[b];
-                    const T rbar = (T)0.5 * (ws.ang.r[a] + ws.ang.r[b]);
-                    const T fcprod = ws.ang.fc[a] * ws.ang.fc[b];
+                    const bool valid = decode_pair(ws.pt, c0 + lane, &bk, &a, &b);
+                    const Vec4<T> ua = ws.ang_u[a], ub = ws.ang_u[b];
+                    const T cosv = ua.x * ub.x + ua.y * ub.y + ua.z * ub.z;
+                    const T rbar = (T)0.5 * (ua.w + ub.w);
+                    const T fcprod = valid ? ws.ang_fc[a] * ws.ang_fc[b] : (T)0;
                     T A[kNumThetas], BF[kNumARs];
                     angular_factors<T>(cosv, rbar, fcprod, A, BF);
 #pragma unroll
-                    for (int t = 0; t < kNumThetas; t++) ws.A[t][lane] = valid ? A[t] : (T)0;
+                    for (int t = 0; t < kNumThetas; t++) ws.A[t][lane] = A[t];
 #pragma unroll
-                    for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = valid ? BF[q] : (T)0;
+                    for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = BF[q];
                 }
                 __syncwarp();
                 {   // C: lane = (theta, shift)
@@ -245,7 +242,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                             row[kRadial + cur * kTS + lane] = acc0 + acc1;
                             acc0 = acc1 = (T)0;
                             cur++;
-                            cur_end = ws.off[cur + 1];  // cur + 1 <= 10 here, because pp < total
+                            cur_end = ws.pt.off[cur + 1];  // cur + 1 <= 10 here, because pp < total
                         }
                         const int seg_end = min(chunk_end, cur_end);
                         for (; pp < seg_end; pp += 4) {

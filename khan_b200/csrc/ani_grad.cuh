@@ -8,12 +8,17 @@
 //   A. scans the molecule with lane = candidate neighbour j.  A lane whose j is within R_Rc
 //      contracts the 16 upstream values of radial block type(j) with the radial derivatives on
 //      the spot and adds -D u_ij to the gradient of atom j; neighbours within A_Rc are also
-//      compacted into the per-element angular sub-lists;
-//   B. walks the neighbour pairs 32 at a time with lane = pair (j, k): the 32 upstream values of
-//      block (type j, type k) are contracted into three scalars (dL/dcos, dL/dr_ij, dL/dr_ik),
-//      turned into the forces on j and k and added to per-neighbour accumulators of the warp;
-//   C. adds every neighbour's accumulated force to the output and, since all terms depend on
-//      coordinate differences only, minus the total to atom i.
+//      compacted (in scan order) into the warp's angular list;
+//   B. walks the unordered neighbour pairs in CIRCULANT order.  With n angular neighbours,
+//      lane (g, a) -- g = lane / n, a = lane % n -- owns neighbour a and, in a pass, handles the
+//      pair (a, (a + d) mod n) for offset d = d0 + g.  Within a group every a and every
+//      b = a + d is distinct, so the force on a is accumulated in the lane's own registers and
+//      the force on b is handed to its owner with one shuffle: no atomics, no pair table.
+//      Offsets 1 .. n/2 cover every unordered pair once (for even n, offset n/2 only for
+//      a < n/2).  Per pair the 32 upstream values of block (type a, type b) are contracted
+//      into dL/dcos, dL/dr_a, dL/dr_b, from which the two force vectors follow;
+//   C. sums the per-group partial forces of each neighbour and adds them to the output; the
+//      central atom gets minus the total, since every term depends on coordinate differences.
 // Contributions of different central atoms to the same atom meet in the output arrays through
 // floating-point atomic adds, so the outputs must be zero before the kernel starts and the
 // summation order (hence the last bits) may differ between runs.
@@ -25,13 +30,18 @@ namespace ani {
 
 constexpr int kGradBucketStride = 36;  // upstream values of one type pair, padded against bank conflicts
 constexpr int kGradRowWords = kRadial + kPairBuckets * kGradBucketStride;
+constexpr int kGradMaxNeighbors = 32;  // angular neighbours handled by the circulant passes
 
-template <typename T, int CAPT> struct GradWarpShared {
-    AngularList<T, CAPT, true> ang;
+template <typename T> struct GradNeighbor {   // one angular neighbour
+    Vec4<T> u;   // (x_i - x_j) / r_ij, r_ij
+    T fc, dfc;   // f_C(r_ij, A_Rc) and its derivative
+    int type;
+    int atom;    // batch index of j
+};
+
+template <typename T> struct GradWarpShared {
     alignas(16) T g[kGradRowWords];  // upstream row: radial [0,64), then 10 blocks of 32 at stride 36
-    T facc[kTypes * CAPT][3];        // force on each angular neighbour, from this central atom
-    alignas(16) PairBucketInfo tab[kPairBuckets];
-    int off[kPairBuckets + 2];
+    GradNeighbor<T> nb[kGradMaxNeighbors];
 };
 
 // Slow path for an atom whose angular neighbourhood does not fit the sub-lists: angular part
@@ -108,7 +118,7 @@ __device__ __noinline__ void grad_atom_streaming(const T* __restrict__ xs, const
     }
 }
 
-template <typename T, int NW, int CAPT>
+template <typename T, int NW>
 __global__ void __launch_bounds__(NW* kWarp)
     featurize_grad_kernel(const T* __restrict__ xs, const T* __restrict__ ys,
                           const T* __restrict__ zs, const int* __restrict__ types,
@@ -119,7 +129,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                           int acs0, int acs1, int acs2, int acs3)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    using WarpShared = GradWarpShared<T, CAPT>;
+    using WarpShared = GradWarpShared<T>;
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
@@ -152,20 +162,19 @@ __global__ void __launch_bounds__(NW* kWarp)
             T fix = (T)0, fiy = (T)0, fiz = (T)0;  // this lane's share of the force on atom i
 
             // ---- A: neighbour scan + radial part, lane = j ----
-            int cA[kTypes] = {0, 0, 0, 0};
+            int n_ang = 0;
             for (int j0 = 0; j0 < n; j0 += kWarp) {
                 const int j = j0 + lane;
                 const bool live = j < n;
                 const int gj = base + (live ? j : 0);
                 const T dx = xi - xs[gj], dy = yi - ys[gj], dz = zi - zs[gj];
-                const int tj = live ? checked_type(types[gj]) : -1;
-                const T r = Num<T>::sqrt_(dx * dx + dy * dy + dz * dz);
+                const int tj = live ? checked_type(types[gj]) : 0;
+                T r, inv;
+                length_and_inverse(dx * dx + dy * dy + dz * dz, &r, &inv);
                 const bool in_rad = live && j != i && r < (T)kR_Rc;
                 const bool in_ang = in_rad && r < (T)kA_Rc;
-                T ux = (T)0, uy = (T)0, uz = (T)0;
+                const T ux = dx * inv, uy = dy * inv, uz = dz * inv;
                 if (in_rad) {
-                    const T inv = (T)1 / r;
-                    ux = dx * inv; uy = dy * inv; uz = dz * inv;
                     T fc, dfc;
                     cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
                     const T d = radial_vjp<T, T>(r, fc, dfc, ws.g + tj * kNumRs);
@@ -175,83 +184,87 @@ __global__ void __launch_bounds__(NW* kWarp)
                     atomicAdd(&gy[gj], -fy);
                     atomicAdd(&gz[gj], -fz);
                 }
-                T fcA = (T)0, dfcA = (T)0;
-                if (in_ang) cutoff<T>(r, (T)kA_Rc, &fcA, &dfcA);
-#pragma unroll
-                for (int g = 0; g < kTypes; g++) {
-                    const unsigned mA = __ballot_sync(kFull, in_ang && tj == g);
-                    if (in_ang && tj == g) {
-                        const int pos = cA[g] + __popc(mA & lanemask_lt());
-                        if (pos < CAPT) {
-                            const int e = g * CAPT + pos;
-                            ws.ang.ux[e] = ux;
-                            ws.ang.uy[e] = uy;
-                            ws.ang.uz[e] = uz;
-                            ws.ang.r[e] = r;
-                            ws.ang.fc[e] = fcA;
-                            ws.ang.dfc[e] = dfcA;
-                            ws.ang.atom[e] = gj;
-                            ws.facc[e][0] = (T)0;
-                            ws.facc[e][1] = (T)0;
-                            ws.facc[e][2] = (T)0;
-                        }
+                const unsigned mA = __ballot_sync(kFull, in_ang);
+                if (in_ang) {
+                    const int pos = n_ang + __popc(mA & lanemask_lt());
+                    if (pos < kGradMaxNeighbors) {
+                        GradNeighbor<T> e;
+                        e.u = Vec4<T>{ux, uy, uz, r};
+                        cutoff<T>(r, (T)kA_Rc, &e.fc, &e.dfc);
+                        e.type = tj;
+                        e.atom = gj;
+                        ws.nb[pos] = e;
                     }
-                    cA[g] += __popc(mA);
                 }
+                n_ang += __popc(mA);
             }
             __syncwarp();
-            bool fits = true;
-#pragma unroll
-            for (int g = 0; g < kTypes; g++) fits = fits && cA[g] <= CAPT;
 
-            if (!fits) {
+            if (n_ang > kGradMaxNeighbors) {
                 grad_atom_streaming<T>(xs, ys, zs, types, base, n, i, ws.g, gx, gy, gz);
-            } else {
-                // ---- B: angular part, lane = pair ----
-                PairOffsets po;
-                build_pair_table<CAPT>(ws.tab, ws.off, cA, &po);
-                const int total = po.off[kPairBuckets];
-                for (int c0 = 0; c0 < total; c0 += kWarp) {
-                    int bk, a, b;
-                    const bool valid = decode_pair(ws.tab, po, c0 + lane, &bk, &a, &b);
+            } else if (n_ang >= 2) {
+                // ---- B: angular part, circulant pair order ----
+                const int na = n_ang;
+                const int groups = min(kWarp / na, 4);       // offsets handled per pass
+                const int grp = lane / na;                    // 0 .. (32 / na)
+                const int a = lane - grp * na;
+                const bool owner = grp < groups;
+                const GradNeighbor<T> ea = ws.nb[owner ? a : 0];
+                T fax = (T)0, fay = (T)0, faz = (T)0;         // force on neighbour a (this group's share)
+                const int half = na >> 1;
+                const bool even = (na & 1) == 0;
+                for (int d0 = 1; d0 <= half; d0 += groups) {
+                    const int d = d0 + grp;
+                    const bool valid = owner && d <= half && !(even && d == half && a >= half);
+                    int b = a + d;
+                    if (b >= na) b -= na;
+                    T gbx = (T)0, gby = (T)0, gbz = (T)0;
                     if (valid) {
-                        const T uax = ws.ang.ux[a], uay = ws.ang.uy[a], uaz = ws.ang.uz[a];
-                        const T ubx = ws.ang.ux[b], uby = ws.ang.uy[b], ubz = ws.ang.uz[b];
-                        const T ra = ws.ang.r[a], rb = ws.ang.r[b];
-                        T c = uax * ubx + uay * uby + uaz * ubz;
+                        const GradNeighbor<T> eb = ws.nb[b];
+                        T c = ea.u.x * eb.u.x + ea.u.y * eb.u.y + ea.u.z * eb.u.z;
                         c = Num<T>::max_((T)-1, Num<T>::min_((T)1, c));
-                        const T s2 = sin2_from_cross<T>(uax, uay, uaz, ubx, uby, ubz);
+                        const T s2 = sin2_from_cross<T>(ea.u.x, ea.u.y, ea.u.z, eb.u.x, eb.u.y, eb.u.z);
                         T gl[kTS];
-                        const T* gsrc = ws.g + kRadial + bk * kGradBucketStride;
+                        const T* gsrc = ws.g + kRadial + pair_bucket(ea.type, eb.type) * kGradBucketStride;
 #pragma unroll
                         for (int q = 0; q < kTS; q += 4) load4(gsrc + q, gl + q);
                         T dc, dra, drb;
-                        angular_vjp<T, T>(c, s2, ra, rb, ws.ang.fc[a], ws.ang.dfc[a], ws.ang.fc[b],
-                                          ws.ang.dfc[b], gl, &dc, &dra, &drb);
-                        const T ira = (T)1 / ra, irb = (T)1 / rb;
-                        const T aa = -dc * ira, ba = c * dc * ira - dra;
-                        const T ab = -dc * irb, bb = c * dc * irb - drb;
-                        atomicAdd(&ws.facc[a][0], aa * ubx + ba * uax);
-                        atomicAdd(&ws.facc[a][1], aa * uby + ba * uay);
-                        atomicAdd(&ws.facc[a][2], aa * ubz + ba * uaz);
-                        atomicAdd(&ws.facc[b][0], ab * uax + bb * ubx);
-                        atomicAdd(&ws.facc[b][1], ab * uay + bb * uby);
-                        atomicAdd(&ws.facc[b][2], ab * uaz + bb * ubz);
+                        angular_vjp<T, T>(c, s2, ea.u.w, eb.u.w, ea.fc, ea.dfc, eb.fc, eb.dfc, gl, &dc,
+                                          &dra, &drb);
+                        T ra_inv, rb_inv, unused;
+                        length_and_inverse(ea.u.w * ea.u.w, &unused, &ra_inv);
+                        length_and_inverse(eb.u.w * eb.u.w, &unused, &rb_inv);
+                        const T aa = -dc * ra_inv, ba = c * dc * ra_inv - dra;
+                        const T ab = -dc * rb_inv, bb = c * dc * rb_inv - drb;
+                        fax += aa * eb.u.x + ba * ea.u.x;
+                        fay += aa * eb.u.y + ba * ea.u.y;
+                        faz += aa * eb.u.z + ba * ea.u.z;
+                        gbx = ab * ea.u.x + bb * eb.u.x;
+                        gby = ab * ea.u.y + bb * eb.u.y;
+                        gbz = ab * ea.u.z + bb * eb.u.z;
                     }
+                    // hand the force on b to its owner in the same group: lane (grp, x) takes it
+                    // from lane (grp, (x - d) mod na)
+                    int src = a - d;
+                    if (src < 0) src += na;
+                    if (src < 0) src += na;   // d can exceed na only on lanes that are not valid
+                    src = owner ? grp * na + src : lane;
+                    fax += __shfl_sync(kFull, gbx, src);
+                    fay += __shfl_sync(kFull, gby, src);
+                    faz += __shfl_sync(kFull, gbz, src);
                 }
-                __syncwarp();
-                // ---- C: push the neighbour forces out ----
-#pragma unroll
-                for (int g = 0; g < kTypes; g++) {
-                    for (int p = lane; p < cA[g]; p += kWarp) {
-                        const int e = g * CAPT + p;
-                        const T fx = ws.facc[e][0], fy = ws.facc[e][1], fz = ws.facc[e][2];
-                        fix -= fx; fiy -= fy; fiz -= fz;
-                        const int gj = ws.ang.atom[e];
-                        atomicAdd(&gx[gj], fx);
-                        atomicAdd(&gy[gj], fy);
-                        atomicAdd(&gz[gj], fz);
-                    }
+                // ---- C: sum the groups, push the neighbour forces out ----
+                for (int g = 1; g < groups; g++) {
+                    const int src = lane + g * na < kWarp ? lane + g * na : lane;
+                    const T ox = __shfl_sync(kFull, fax, src), oy = __shfl_sync(kFull, fay, src),
+                            oz = __shfl_sync(kFull, faz, src);
+                    if (lane < na) { fax += ox; fay += oy; faz += oz; }
+                }
+                if (lane < na) {
+                    fix -= fax; fiy -= fay; fiz -= faz;
+                    atomicAdd(&gx[ea.atom], fax);
+                    atomicAdd(&gy[ea.atom], fay);
+                    atomicAdd(&gz[ea.atom], faz);
                 }
             }
 #pragma unroll

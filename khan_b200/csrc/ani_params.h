@@ -95,7 +95,7 @@ template <typename T> ANI_HD T theta_sin(int t)
 // ---------------------------------------------------------------------------------------
 template <typename T> struct Num;
 
-#if defined(__CUDA_ARCH__)
+#if defined(__CUDACC__)
 // Single SFU instructions, written as PTX so that the choice does not depend on compiler flags.
 __device__ __forceinline__ float sfu_ex2(float x)
 {
