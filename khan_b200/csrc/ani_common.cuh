@@ -186,8 +186,10 @@ __device__ __forceinline__ int build_pair_tables(PairTables& pt, const int* ang_
     if (lane <= kPairBuckets) pt.off[lane] = off;
     const int total = __shfl_sync(kFull, incl, kPairBuckets - 1);
     __syncwarp();
-    // bucket of every quad of padded positions (all bucket starts are multiples of 4)
-    const int n_quads = min(total >> 2, kQuadTable);
+    // bucket of every quad of padded positions (all bucket starts are multiples of 4), up to
+    // the end of the last 32-position chunk: positions past `total` resolve to bucket 9, where
+    // they fail the `q < cnt` test of decode_pair.
+    const int n_quads = min(((total + kWarp - 1) & ~(kWarp - 1)) >> 2, kQuadTable);
     for (int q = lane; q < n_quads; q += kWarp) {
         int bk = 0;
 #pragma unroll
@@ -215,7 +217,7 @@ __device__ __forceinline__ bool decode_pair(const PairTables& pt, int p, int* bu
     int bk;
     const int quad = p >> 2;
     if (quad < kQuadTable) {
-        bk = pt.quad_bucket[quad];
+        bk = min((int)pt.quad_bucket[quad], kPairBuckets - 1);
     } else {
         bk = 0;
 #pragma unroll

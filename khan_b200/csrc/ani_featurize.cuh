@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                      const int* __restrict__ scatter, T* out_h, T* out_c, T* out_n, T* out_o,
                      int acs0, int acs1, int acs2, int acs3)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     using WarpShared = FeaturizeWarpShared<T, CAPT, CAPR>;
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];

@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                           const T* __restrict__ gn, const T* __restrict__ go, T* gx, T* gy, T* gz,
                           int acs0, int acs1, int acs2, int acs3)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     using WarpShared = GradWarpShared<T>;
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
