@@ -13,7 +13,7 @@ import subprocess
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libani_b200.so")
+LIB_PATH = os.environ.get("ANI_B200_LIB") or os.path.join(_HERE, "libani_b200.so")
 CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]

@@ -68,10 +68,22 @@ constexpr int kNW = 4;
 constexpr int kCapT = 24;  // angular (r < 3.1 A) neighbours per element
 constexpr int kCapR = 48;  // radial (r < 4.6 A) neighbours per element
 
-int featurizer_grid(int n_mols)
+// Persistent grid: as many CTAs as fit on the device at once (rounded to a multiple of
+// kSlotsPerMol / kNW so that the warp count is a multiple of kSlotsPerMol), or fewer when the
+// batch is small.
+template <typename K> int featurizer_grid(K kernel, size_t smem, int n_mols, int* grid)
 {
-    const long long ctas = (long long)n_mols * (kSlotsPerMol / kNW);
-    return (int)(ctas < (1LL << 30) ? ctas : (1LL << 30));
+    int dev = 0, sms = 0, per_sm = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    ANI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    ANI_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kNW * kWarp, smem));
+    constexpr int kGroup = kSlotsPerMol / kNW;
+    long long resident = (long long)sms * (per_sm > 0 ? per_sm : 1);
+    resident = (resident / kGroup) * kGroup;
+    if (resident < kGroup) resident = kGroup;
+    const long long needed = (long long)n_mols * kGroup;
+    *grid = (int)(needed < resident ? needed : resident);
+    return ANI_OK;
 }
 
 template <typename K> int set_smem(K kernel, size_t bytes)
@@ -116,7 +128,14 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<featurizer_grid(n_mols), kNW * kWarp, smem, (cudaStream_t)stream>>>(
+    static thread_local int cached_grid_dev = -1, cached_resident = 0;
+    if (cached_grid_dev != dev) {
+        if (int rc = featurizer_grid(kernel, smem, 1 << 24, &cached_resident)) return rc;
+        cached_grid_dev = dev;
+    }
+    const long long needed = (long long)n_mols * (kSlotsPerMol / kNW);
+    const int grid = (int)(needed < cached_resident ? needed : cached_resident);
+    kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, oh, oc, on, oo, acs_host[0],
         acs_host[1], acs_host[2], acs_host[3]);
     ANI_CUDA(cudaGetLastError());
@@ -157,7 +176,14 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<featurizer_grid(n_mols), kNW * kWarp, smem, st>>>(
+    static thread_local int cached_grid_dev = -1, cached_resident = 0;
+    if (cached_grid_dev != dev) {
+        if (int rc = featurizer_grid(kernel, smem, 1 << 24, &cached_resident)) return rc;
+        cached_grid_dev = dev;
+    }
+    const long long needed = (long long)n_mols * (kSlotsPerMol / kNW);
+    const int grid = (int)(needed < cached_resident ? needed : cached_resident);
+    kernel<<<grid, kNW * kWarp, smem, st>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, gh, gc, gn, go, gx, gy, gz,
         acs_host[0], acs_host[1], acs_host[2], acs_host[3]);
     ANI_CUDA(cudaGetLastError());
@@ -185,6 +211,18 @@ const char* ani_status_string(int status)
 }
 
 const char* ani_last_cuda_error(void) { return cudaGetErrorString(t_last_error); }
+
+#ifdef ANI_PHASE_TIMING
+// Tuning builds only: copies out and clears the per-phase cycle counters (16 values).
+int ani_debug_phase_cycles(unsigned long long* out_host)
+{
+    ANI_CUDA(cudaDeviceSynchronize());
+    ANI_CUDA(cudaMemcpyFromSymbol(out_host, ani::g_phase_cycles, 16 * sizeof(unsigned long long)));
+    unsigned long long zero[16] = {0};
+    ANI_CUDA(cudaMemcpyToSymbol(ani::g_phase_cycles, zero, sizeof(zero)));
+    return ANI_OK;
+}
+#endif
 
 int ani_device_status(void* stream)
 {

@@ -2,11 +2,13 @@
 // warp helpers, per-central-atom neighbour lists and the enumeration of neighbour pairs.
 //
 // Work decomposition used by every featurizer kernel: ONE WARP PER CENTRAL ATOM, no cooperation
-// between the warps of a CTA (no __syncthreads anywhere).  The grid gives every molecule
-// kSlotsPerMol warps; warp s of molecule m handles atoms s, s + kSlotsPerMol, ... of that
-// molecule and exits at once when the molecule has fewer atoms.  A warp reads its molecule's
-// coordinates straight from global memory (the warps of one CTA belong to the same molecule, so
-// these loads hit L1) and keeps the neighbourhood of its atom in its own slice of shared memory.
+// between the warps of a CTA (no __syncthreads anywhere).  The work list has kSlotsPerMol items
+// per molecule; item (m, s) covers atoms s, s + kSlotsPerMol, ... of molecule m and is empty
+// when the molecule has fewer atoms.  The grid is persistent (a few CTAs per SM): warp w takes
+// items w, w + W, w + 2W, ... (W = warps in the grid, a multiple of kSlotsPerMol), so an empty
+// item costs one cached load instead of a CTA slot, and consecutive warps -- the warps of one
+// CTA -- work on the same molecule, whose coordinates they read straight from global memory
+// (L1 hits).  Each warp keeps the neighbourhood of its atom in its own slice of shared memory.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -27,6 +29,45 @@ constexpr int kSlotsPerMol = 32;  // warps per molecule in the grid
 __device__ int g_status = 0;
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_status, 0, code); }
+
+// Optional per-phase cycle accounting (compiled in only with -DANI_PHASE_TIMING, for tuning):
+// every warp adds the cycles it spent between consecutive marks to g_phase_cycles[phase].
+#ifdef ANI_PHASE_TIMING
+__device__ unsigned long long g_phase_cycles[16];
+__device__ __forceinline__ long long now_cycles()
+{
+    long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+    return t;
+}
+struct PhaseClock {
+    long long last;
+    unsigned long long acc[16];
+    __device__ __forceinline__ PhaseClock() : last(now_cycles())
+    {
+        for (int k = 0; k < 16; k++) acc[k] = 0;
+    }
+    __device__ __forceinline__ void mark(int k)
+    {
+        const long long now = now_cycles();
+        acc[k] += (unsigned long long)(now - last);
+        last = now;
+    }
+    __device__ __forceinline__ void flush()
+    {
+        if ((threadIdx.x & 31) == 0)
+            for (int k = 0; k < 16; k++)
+                if (acc[k]) atomicAdd(&g_phase_cycles[k], acc[k]);
+    }
+};
+#define ANI_PHASE_DECL PhaseClock phase_clock
+#define ANI_PHASE(k) phase_clock.mark(k)
+#define ANI_PHASE_FLUSH phase_clock.flush()
+#else
+#define ANI_PHASE_DECL
+#define ANI_PHASE(k)
+#define ANI_PHASE_FLUSH
+#endif
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & (kWarp - 1); }
 __device__ __forceinline__ int warp_id() { return threadIdx.x >> 5; }
@@ -67,6 +108,16 @@ __device__ __forceinline__ void load4(const double* p, double* v)
     const double2 a = *reinterpret_cast<const double2*>(p);
     const double2 b = *reinterpret_cast<const double2*>(p + 2);
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+// The k-th item of a warp: item index -> (molecule, slot).  The slot is rotated by the round
+// number k so that a warp does not see the same slot -- hence the same chance of an empty item
+// -- in every round.  Requires the number of warps in the grid to be a multiple of
+// kSlotsPerMol, which makes the rotation a permutation of each molecule's slots.
+__device__ __forceinline__ void item_to_work(long long item, int round, int* m, int* slot)
+{
+    *m = (int)(item / kSlotsPerMol);
+    *slot = ((int)(item % kSlotsPerMol) + 11 * round) & (kSlotsPerMol - 1);
 }
 
 // One molecule as the kernels see it, validated.

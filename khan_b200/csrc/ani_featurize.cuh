@@ -106,8 +106,12 @@ __device__ __noinline__ void featurize_atom_streaming(const T* __restrict__ xs,
     for (int b = 0; b < kPairBuckets; b++) row[kRadial + b * kTS + lane] = acc[b];
 }
 
+#ifndef ANI_FWD_MIN_CTAS
+#define ANI_FWD_MIN_CTAS 8
+#endif
+
 template <typename T, int NW, int CAPT, int CAPR>
-__global__ void __launch_bounds__(NW* kWarp)
+__global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS : 1)
     featurize_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
                      const int* __restrict__ types, const int* __restrict__ mol_offsets,
                      const int* __restrict__ mol_counts, int n_mols, int n_atoms,
@@ -119,6 +123,7 @@ __global__ void __launch_bounds__(NW* kWarp)
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
+    ANI_PHASE_DECL;
     // The angular list is read at entry 0 by padding lanes and may be read before this warp
     // ever wrote it: give every entry a finite value once.
     for (int e = lane; e < kTypes * CAPT; e += kWarp) {
@@ -127,16 +132,24 @@ __global__ void __launch_bounds__(NW* kWarp)
     }
     __syncwarp();
 
-    constexpr int kCtasPerMol = kSlotsPerMol / NW;
-    for (long long cta = blockIdx.x; cta < (long long)n_mols * kCtasPerMol; cta += gridDim.x) {
-        const int m = (int)(cta / kCtasPerMol);
-        const int slot = (int)(cta - (long long)m * kCtasPerMol) * NW + warp;
+    const long long n_items = (long long)n_mols * kSlotsPerMol;
+    const int grid_warps = gridDim.x * NW;
+    int round = 0;
+    for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
+        int m, slot;
+        item_to_work(item, round, &m, &slot);
+        if (slot >= mol_counts[m]) continue;   // empty item: one cached load
         MolRange mol;
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
 
         for (int i = slot; i < n; i += kSlotsPerMol) {
             const int gi = base + i;
+            // everything this atom needs from global memory is requested before any of it is used
+            const int j_first = lane < n ? lane : 0;
+            T px = xs[base + j_first], py = ys[base + j_first], pz = zs[base + j_first];
+            int pt = types[base + j_first];
+            const T xi = xs[gi], yi = ys[gi], zi = zs[gi];
             const int ti = checked_type(types[gi]);
             const int srow = scatter[gi];
             const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
@@ -145,16 +158,20 @@ __global__ void __launch_bounds__(NW* kWarp)
                 continue;
             }
             T* row = element_buffer<T>(ti, out_h, out_c, out_n, out_o) + (size_t)srow * kTotal;
-            const T xi = xs[gi], yi = ys[gi], zi = zs[gi];
+            ANI_PHASE(0);
 
             // ---- A: neighbour scan, lane = j ----
             int cA[kTypes] = {0, 0, 0, 0}, cR[kTypes] = {0, 0, 0, 0};
             for (int j0 = 0; j0 < n; j0 += kWarp) {
                 const int j = j0 + lane;
                 const bool live = j < n;
-                const int gj = base + (live ? j : 0);
-                const T dx = xi - xs[gj], dy = yi - ys[gj], dz = zi - zs[gj];
-                const int tj = live ? checked_type(types[gj]) : -1;
+                if (j0 > 0) {   // chunk 0 was requested above
+                    const int gj = base + (live ? j : 0);
+                    px = xs[gj]; py = ys[gj]; pz = zs[gj];
+                    pt = types[gj];
+                }
+                const T dx = xi - px, dy = yi - py, dz = zi - pz;
+                const int tj = live ? checked_type(pt) : -1;
                 T r, inv;
                 length_and_inverse(dx * dx + dy * dy + dz * dz, &r, &inv);
                 const bool in_rad = live && j != i && r < (T)kR_Rc;
@@ -192,6 +209,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                 continue;
             }
 
+            ANI_PHASE(1);
             // ---- R: radial features, lane = (half, shift) ----
             {
                 const int half = lane >> 4;
@@ -211,8 +229,10 @@ __global__ void __launch_bounds__(NW* kWarp)
                 row[32 + lane] = lane < 16 ? acc[2] : acc[3];
             }
 
+            ANI_PHASE(2);
             // ---- B + C: angular features ----
             const int total = build_pair_tables<CAPT>(ws.pt, cA);
+            ANI_PHASE(3);
             const T* a_row = &ws.A[lane >> 2][0];
             const T* b_row = &ws.BF[lane & 3][0];
             int cur = 0;                  // bucket being accumulated
@@ -234,6 +254,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                     for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = BF[q];
                 }
                 __syncwarp();
+                ANI_PHASE(4);
                 {   // C: lane = (theta, shift)
                     const int chunk_end = min(c0 + kWarp, total);
                     int pp = c0;
@@ -257,13 +278,17 @@ __global__ void __launch_bounds__(NW* kWarp)
                     }
                 }
                 __syncwarp();
+                ANI_PHASE(5);
             }
             for (; cur < kPairBuckets; cur++) {
                 row[kRadial + cur * kTS + lane] = acc0 + acc1;
                 acc0 = acc1 = (T)0;
             }
+            ANI_PHASE(6);
         }
     }
+    ANI_PHASE(7);
+    ANI_PHASE_FLUSH;
 }
 
 }  // namespace ani

@@ -118,8 +118,12 @@ __device__ __noinline__ void grad_atom_streaming(const T* __restrict__ xs, const
     }
 }
 
+#ifndef ANI_GRAD_MIN_CTAS
+#define ANI_GRAD_MIN_CTAS 8
+#endif
+
 template <typename T, int NW>
-__global__ void __launch_bounds__(NW* kWarp)
+__global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS : 1)
     featurize_grad_kernel(const T* __restrict__ xs, const T* __restrict__ ys,
                           const T* __restrict__ zs, const int* __restrict__ types,
                           const int* __restrict__ mol_offsets, const int* __restrict__ mol_counts,
@@ -132,17 +136,26 @@ __global__ void __launch_bounds__(NW* kWarp)
     using WarpShared = GradWarpShared<T>;
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
+    ANI_PHASE_DECL;
 
-    constexpr int kCtasPerMol = kSlotsPerMol / NW;
-    for (long long cta = blockIdx.x; cta < (long long)n_mols * kCtasPerMol; cta += gridDim.x) {
-        const int m = (int)(cta / kCtasPerMol);
-        const int slot = (int)(cta - (long long)m * kCtasPerMol) * NW + warp;
+    const long long n_items = (long long)n_mols * kSlotsPerMol;
+    const int grid_warps = gridDim.x * NW;
+    int round = 0;
+    for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
+        int m, slot;
+        item_to_work(item, round, &m, &slot);
+        if (slot >= mol_counts[m]) continue;   // empty item: one cached load
         MolRange mol;
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
 
         for (int i = slot; i < n; i += kSlotsPerMol) {
             const int gi = base + i;
+            // everything this atom needs from global memory is requested before any of it is used
+            const int j_first = lane < n ? lane : 0;
+            T px = xs[base + j_first], py = ys[base + j_first], pz = zs[base + j_first];
+            int pt = types[base + j_first];
+            const T xi = xs[gi], yi = ys[gi], zi = zs[gi];
             const int ti = checked_type(types[gi]);
             const int srow = scatter[gi];
             const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
@@ -150,16 +163,24 @@ __global__ void __launch_bounds__(NW* kWarp)
                 if (lane == 0) report(ANI_ERR_BAD_INDEX);
                 continue;
             }
+            ANI_PHASE(8);
             const T* grow = (ti == 0 ? gh : (ti == 1 ? gc : (ti == 2 ? gn : go))) + (size_t)srow * kTotal;
             // upstream row -> shared memory (12 coalesced loads of 32 values)
-            ws.g[lane] = grow[lane];
-            ws.g[32 + lane] = grow[32 + lane];
+            {
+                T v[2 + kPairBuckets];
+                v[0] = grow[lane];
+                v[1] = grow[32 + lane];
 #pragma unroll
-            for (int bk = 0; bk < kPairBuckets; bk++)
-                ws.g[kRadial + bk * kGradBucketStride + lane] = grow[kRadial + bk * kTS + lane];
+                for (int bk = 0; bk < kPairBuckets; bk++) v[2 + bk] = grow[kRadial + bk * kTS + lane];
+                ws.g[lane] = v[0];
+                ws.g[32 + lane] = v[1];
+#pragma unroll
+                for (int bk = 0; bk < kPairBuckets; bk++)
+                    ws.g[kRadial + bk * kGradBucketStride + lane] = v[2 + bk];
+            }
             __syncwarp();
-            const T xi = xs[gi], yi = ys[gi], zi = zs[gi];
             T fix = (T)0, fiy = (T)0, fiz = (T)0;  // this lane's share of the force on atom i
+            ANI_PHASE(9);
 
             // ---- A: neighbour scan + radial part, lane = j ----
             int n_ang = 0;
@@ -167,8 +188,12 @@ __global__ void __launch_bounds__(NW* kWarp)
                 const int j = j0 + lane;
                 const bool live = j < n;
                 const int gj = base + (live ? j : 0);
-                const T dx = xi - xs[gj], dy = yi - ys[gj], dz = zi - zs[gj];
-                const int tj = live ? checked_type(types[gj]) : 0;
+                if (j0 > 0) {   // chunk 0 was requested above
+                    px = xs[gj]; py = ys[gj]; pz = zs[gj];
+                    pt = types[gj];
+                }
+                const T dx = xi - px, dy = yi - py, dz = zi - pz;
+                const int tj = live ? checked_type(pt) : 0;
                 T r, inv;
                 length_and_inverse(dx * dx + dy * dy + dz * dz, &r, &inv);
                 const bool in_rad = live && j != i && r < (T)kR_Rc;
@@ -199,6 +224,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                 n_ang += __popc(mA);
             }
             __syncwarp();
+            ANI_PHASE(10);
 
             if (n_ang > kGradMaxNeighbors) {
                 grad_atom_streaming<T>(xs, ys, zs, types, base, n, i, ws.g, gx, gy, gz);
@@ -253,6 +279,7 @@ __global__ void __launch_bounds__(NW* kWarp)
                     fay += __shfl_sync(kFull, gby, src);
                     faz += __shfl_sync(kFull, gbz, src);
                 }
+                ANI_PHASE(11);
                 // ---- C: sum the groups, push the neighbour forces out ----
                 for (int g = 1; g < groups; g++) {
                     const int src = lane + g * na < kWarp ? lane + g * na : lane;
@@ -279,8 +306,11 @@ __global__ void __launch_bounds__(NW* kWarp)
                 atomicAdd(&gz[gi], fiz);
             }
             __syncwarp();
+            ANI_PHASE(12);
         }
     }
+    ANI_PHASE(13);
+    ANI_PHASE_FLUSH;
 }
 
 // Zero fill of the three gradient arrays in one launch (the gradient kernel accumulates into
