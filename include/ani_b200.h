@@ -71,6 +71,33 @@ int ani_sort(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gat
              int* atom_counts, void* stream);
 
 /*
+ * AniSort for callers that must not allocate.  It has no counterpart in the reference.
+ *
+ * ani_sort above may call cudaMalloc the first time a batch is too large for its
+ * single-launch path (it caches a scratch buffer per device).  Some hosts cannot live with
+ * that: a plugin whose execute call is forbidden to allocate, a process that has already
+ * handed all device memory to a framework's pool, a latency-critical loop that cannot take
+ * the device-wide synchronisation an allocation implies.  This variant computes exactly the
+ * same three outputs with the same kernels, but its scratch (the per-tile element counts) is
+ * a fixed array inside the library's own device data, so the call never allocates or frees
+ * anything, on the device or through any library.
+ *
+ *  - Limit: n_atoms <= ani_sort_noalloc_max_atoms() (4,194,304); a larger batch is rejected
+ *    with ANI_ERR_TOO_MANY_ATOMS before anything is launched.  The array costs 64 KiB of
+ *    device memory on every GPU that loads the library, for the life of the process.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current) and remembers it; make that first call before any stream capture.
+ *  - All calls on one device share the one array, and it keeps the previous call's contents.
+ *    Every entry a call reads it has written first, so nothing needs clearing, but two calls
+ *    that overlap on the GPU (different streams, or different host threads) race on it:
+ *    keep calls on one device in one stream order.
+ * Inputs and outputs are still the caller's buffers, as for ani_sort.
+ */
+int ani_sort_noalloc(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gather_idxs,
+                     int* atom_counts, void* stream);
+int ani_sort_noalloc_max_atoms(void);
+
+/*
  * Featurize -- replaces AniFunctor<Device, T> (gpu_featurizer/functor_op.h:8-25; CPU body
  * functor_op_cpu.cpp:13-43 -> featurize_cpu, kernel_cpu.cpp:406-537; GPU body
  * functor_op_gpu.cu:57-92 -> featurize, kernel.cu:72-268) and the op shell

@@ -38,6 +38,8 @@ SIGNATURES = {
     "ani_last_cuda_error": (ctypes.c_char_p, []),
     "ani_device_status": (_i, [_vp]),
     "ani_sort": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
+    "ani_sort_noalloc": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
+    "ani_sort_noalloc_max_atoms": (_i, []),
     "ani_featurize_f32": (_i, [_vp] * 6 + [_i] + [_vp] * 5 + [c_int_p, _vp]),
     "ani_featurize_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 5 + [c_int_p, _vp]),
     "ani_featurize_grad_f32": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),

@@ -61,6 +61,34 @@ int sort_scratch(size_t bytes, int** out)
     return ANI_OK;
 }
 
+// Fixed scratch for ani_sort_noalloc: per-tile element counts for batches of up to
+// kSortStaticMaxAtoms atoms ((tiles + 1) x 4 ints = 64 KiB + 16 B).  It lives in the module's
+// static device data, so every GPU that loads this library holds it until the process exits.
+constexpr int kSortStaticMaxAtoms = 1 << 22;  // 4,194,304 atoms
+constexpr int kSortStaticMaxTiles = kSortStaticMaxAtoms / kSortTile;
+static __device__ __align__(256) int g_sort_static_scratch[(kSortStaticMaxTiles + 1) * kTypes];
+
+// Device address of g_sort_static_scratch on each device, resolved on first use.  In host code
+// the array's name is only a handle for the runtime, not a device address, so it is never
+// passed to a kernel; the pointer obtained here is.
+int* g_sort_static_ptr[kMaxDevices] = {};
+std::mutex g_sort_static_mutex;
+
+int sort_static_scratch(int** out)
+{
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return ANI_ERR_BAD_SIZE;
+    std::lock_guard<std::mutex> lock(g_sort_static_mutex);
+    if (!g_sort_static_ptr[dev]) {
+        int* ptr = nullptr;
+        ANI_CUDA(cudaGetSymbolAddress((void**)&ptr, g_sort_static_scratch));  // current device = dev
+        g_sort_static_ptr[dev] = ptr;
+    }
+    *out = g_sort_static_ptr[dev];
+    return ANI_OK;
+}
+
 // Featurizer launch shapes: NW warps per CTA, kSlotsPerMol / NW CTAs per molecule, one warp
 // per central atom.  The capacities bound the neighbours of one element kept in shared memory
 // per central atom (atoms with more take the streaming path).
@@ -266,6 +294,36 @@ int ani_sort(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gat
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
+
+int ani_sort_noalloc(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gather_idxs,
+                     int* atom_counts, void* stream)
+{
+    if (n_atoms < 0) return ANI_ERR_BAD_SIZE;
+    if (n_atoms > kSortStaticMaxAtoms) return ANI_ERR_TOO_MANY_ATOMS;
+    if (!atom_counts) return ANI_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_atoms == 0) {
+        sort_empty_kernel<<<1, 32, 0, st>>>(atom_counts);
+        ANI_CUDA(cudaGetLastError());
+        return ANI_OK;
+    }
+    if (!atomic_numbers || !scatter_idxs || !gather_idxs) return ANI_ERR_NULL_POINTER;
+    int* scratch = nullptr;
+    if (int rc = sort_static_scratch(&scratch)) return rc;
+    // Every scratch entry that is read is written first by the same call (the histogram kernel
+    // fills entries [0, n_tiles), the scan kernel entry n_tiles), so nothing has to be cleared.
+    const int n_tiles = (n_atoms + kSortTile - 1) / kSortTile;
+    sort_histogram_kernel<<<n_tiles, kSortThreads, 0, st>>>(atomic_numbers, n_atoms, scratch);
+    ANI_CUDA(cudaGetLastError());
+    sort_scan_kernel<<<1, kSortThreads, 0, st>>>(scratch, n_tiles);
+    ANI_CUDA(cudaGetLastError());
+    sort_rank_kernel<<<n_tiles, kSortThreads, 0, st>>>(atomic_numbers, n_atoms, scratch, n_tiles,
+                                                       scatter_idxs, gather_idxs, atom_counts);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+int ani_sort_noalloc_max_atoms(void) { return kSortStaticMaxAtoms; }
 
 int ani_featurize_f32(const float* xs, const float* ys, const float* zs, const int* atomic_numbers,
                       const int* mol_offsets, const int* mol_atom_counts, int n_mols,
