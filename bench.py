@@ -49,6 +49,10 @@ FEATURE_SIZE = 384
 FLOPS_FWD = (125, 156)
 FLOPS_GRAD = (201, 417)
 FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # SMs x lanes x FMA x max SM clock
+# DRAM bytes per atom seen by ncu (dram__bytes_read.sum + dram__bytes_write.sum) on an
+# 8192-molecule batch, whose 170 MB of features exceed the L2 (profiles/dram_traffic_8192_molecules.md);
+# traffic grows in proportion to the atoms, so a launch is scaled by its atom count.
+NCU_DRAM_BYTES_PER_ATOM = {"featurize": 1041.1, "featurize_grad": 1575.3, "ani_sort": None}
 
 
 def measured_peaks():
@@ -466,7 +470,9 @@ def main():
     achieved_gbs = bytes_per_atom[dominant] * mean_atoms / kernel_s[dominant] / 1e9
     achieved_tf = flops_per_atom[dominant] * mean_atoms / kernel_s[dominant] / 1e12
     roofline = {"kernel": dominant, "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"],
-                "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": None,
+                "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"],
+                "traffic": (NCU_DRAM_BYTES_PER_ATOM[dominant] * mean_atoms
+                            if NCU_DRAM_BYTES_PER_ATOM.get(dominant) else None),
                 "peak_source": peak_kind,
                 "algorithmic_bytes_per_launch": bytes_per_atom[dominant] * mean_atoms}
     roofline_fp32 = {"kernel": dominant, "achieved": achieved_tf, "peak": FP32_PEAK_TFLOPS,
@@ -474,8 +480,10 @@ def main():
                      "peak_source": "148 SM x 128 lanes x 2 x 1.965 GHz (formula)",
                      "pairs_per_atom": p_per_atom, "triplets_per_atom": t_per_atom}
     step_flops = (flops_per_atom["featurize"] + flops_per_atom["featurize_grad"])
-    whole_step = {"tflops": step_flops * value / 1e12, "frac_fp32": step_flops * value / 1e12 / FP32_PEAK_TFLOPS,
-                  "gbs": 3116 * value / 1e9, "frac_hbm": 3116 * value / 1e9 / peaks["hbm_gbs"]}
+    per_gpu = value / world
+    whole_step = {"per_gpu_tflops": step_flops * per_gpu / 1e12,
+                  "frac_fp32": step_flops * per_gpu / 1e12 / FP32_PEAK_TFLOPS,
+                  "per_gpu_gbs": 3116 * per_gpu / 1e9, "frac_hbm": 3116 * per_gpu / 1e9 / peaks["hbm_gbs"]}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,

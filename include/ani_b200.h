@@ -139,6 +139,32 @@ int ani_featurize_grad_f64(const double* xs, const double* ys, const double* zs,
                            const double* grad_o, double* x_grads, double* y_grads,
                            double* z_grads, const int* acs_host, void* stream);
 
+/*
+ * FeaturizeGradInverse -- replaces AniGradInverse<Device, T> (gpu_featurizer/functor_op.h:49-69;
+ * CPU body functor_op_cpu.cpp:88-121 -> featurize_grad_inverse, kernel_cpu.cpp:37-179) and
+ * AniCombinedGradInverse (gpu_featurizer/ani_op.cpp:224-330), the op TensorFlow calls for the
+ * second derivative through FeaturizeGrad (khan/training/trainer_multi_tower.py:64-91).
+ * Jacobian-vector product: x_grads/y_grads/z_grads [n_atoms] is a displacement of every atom;
+ * the outputs (same layout as Featurize) receive the directional derivative of every feature.
+ * It is the exact transpose of ani_featurize_grad.  The reference kernel indexes the input
+ * vector by the element id of the central atom (kernel_cpu.cpp:111-169), which makes its output
+ * vanish up to rounding; this entry point computes the product that was meant.
+ * Limit: at most 64 atoms within 4.6 A of any atom (else ANI_ERR_TOO_MANY_ATOMS in the status
+ * word and a zero row).
+ */
+int ani_featurize_grad_inverse_f32(const float* xs, const float* ys, const float* zs,
+                                   const int* atomic_numbers, const int* mol_offsets,
+                                   const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                                   const float* x_grads, const float* y_grads, const float* z_grads,
+                                   float* out_h, float* out_c, float* out_n, float* out_o,
+                                   const int* acs_host, void* stream);
+int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const double* zs,
+                                   const int* atomic_numbers, const int* mol_offsets,
+                                   const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                                   const double* x_grads, const double* y_grads,
+                                   const double* z_grads, double* out_h, double* out_c,
+                                   double* out_n, double* out_o, const int* acs_host, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

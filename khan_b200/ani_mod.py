@@ -139,6 +139,79 @@ def featurize_grad(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, sca
     return outs[0], outs[1], outs[2]
 
 
+def featurize_grad_inverse(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, scatter_idxs,
+                           acs, x_grads, y_grads, z_grads):
+    """FeaturizeGradInverse: Jacobian-vector product; returns four flat tensors like
+    :func:`featurize` (the transpose of :func:`featurize_grad`)."""
+    xs, ys, zs, a, mo, mac, si = _common(xs, ys, zs, atomic_numbers, mol_offsets,
+                                         mol_atom_counts, scatter_idxs)
+    suf = _suffix(xs)
+    acs_host = host_counts(acs)
+    n_atoms = int(acs_host.sum())
+    vs = [_dev(v, xs.dtype, "grads").view(-1) for v in (x_grads, y_grads, z_grads)]
+    for v in vs:
+        if v.numel() != n_atoms:
+            raise ValueError(f"coordinate vector has {v.numel()} values, expected {n_atoms}")
+    out = torch.empty((n_atoms, FEATURE_SIZE), dtype=xs.dtype, device=xs.device)
+    flat = out.view(-1)
+    ends = np.cumsum(acs_host) * FEATURE_SIZE
+    starts = ends - acs_host * FEATURE_SIZE
+    ptrs = [ctypes.c_void_p(flat.data_ptr() + int(s) * flat.element_size()) for s in starts]
+    with torch.cuda.device(xs.device):
+        fn = getattr(_lib.lib(), "ani_featurize_grad_inverse_" + suf)
+        _lib.check(fn(_p(xs), _p(ys), _p(zs), _p(a), _p(mo), _p(mac), mo.numel(), _p(si),
+                      *[_p(v) for v in vs], *ptrs, _acs_ptr(acs_host), _stream()),
+                   "ani_featurize_grad_inverse_" + suf)
+    return tuple(flat[int(s):int(e)] for s, e in zip(starts, ends))
+
+
+class _Featurize(torch.autograd.Function):
+    """Featurize with the gradient wiring of the reference trainer: d/d(x, y, z) through
+    FeaturizeGrad (``khan/training/trainer_multi_tower.py:23-52``) and, one level up,
+    through FeaturizeGradInverse (``:64-91``)."""
+
+    @staticmethod
+    def forward(ctx, xs, ys, zs, a, mo, mac, si, acs_t):
+        acs = host_counts(acs_t)
+        ctx.save_for_backward(xs, ys, zs, a, mo, mac, si)
+        ctx.acs = acs
+        h, c, n, o = featurize(xs, ys, zs, a, mo, mac, si, acs)
+        return h, c, n, o
+
+    @staticmethod
+    def backward(ctx, gh, gc, gn, go):
+        xs, ys, zs, a, mo, mac, si = ctx.saved_tensors
+        gx, gy, gz = _FeaturizeGrad.apply(xs, ys, zs, a, mo, mac, si, ctx.acs, gh, gc, gn, go)
+        return gx, gy, gz, None, None, None, None, None
+
+
+class _FeaturizeGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, xs, ys, zs, a, mo, mac, si, acs, gh, gc, gn, go):
+        ctx.save_for_backward(xs, ys, zs, a, mo, mac, si)
+        ctx.acs = acs
+        sizes = [int(c) * FEATURE_SIZE for c in acs]
+        gs = [g if g is not None else torch.zeros(s, dtype=xs.dtype, device=xs.device)
+              for g, s in zip((gh, gc, gn, go), sizes)]
+        return featurize_grad(xs, ys, zs, a, mo, mac, si, acs, *gs)
+
+    @staticmethod
+    def backward(ctx, vx, vy, vz):
+        xs, ys, zs, a, mo, mac, si = ctx.saved_tensors
+        zero = lambda: torch.zeros_like(xs)  # noqa: E731
+        vx, vy, vz = (v if v is not None else zero() for v in (vx, vy, vz))
+        dh, dc, dn, do = featurize_grad_inverse(xs, ys, zs, a, mo, mac, si, ctx.acs, vx, vy, vz)
+        # gradients with respect to the coordinates themselves (third-order terms) are not
+        # provided, as in the reference (it returns None for the first eight inputs)
+        return (None,) * 8 + (dh, dc, dn, do)
+
+
+def featurize_autograd(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, scatter_idxs, acs):
+    """:func:`featurize` that torch.autograd can differentiate with respect to xs, ys, zs."""
+    return _Featurize.apply(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
+                            scatter_idxs, acs)
+
+
 def device_status() -> int:
     """Synchronise the current stream and return (and clear) the device status word."""
     return int(_lib.lib().ani_device_status(_stream()))

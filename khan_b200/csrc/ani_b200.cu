@@ -11,6 +11,7 @@
 
 #include "ani_featurize.cuh"
 #include "ani_grad.cuh"
+#include "ani_grad_inverse.cuh"
 #include "ani_sort.cuh"
 
 namespace {
@@ -218,6 +219,41 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
     return ANI_OK;
 }
 
+template <typename T>
+int featurize_grad_inverse_impl(const T* xs, const T* ys, const T* zs, const int* types,
+                                const int* mos, const int* macs, int n_mols, const int* sis,
+                                const T* vx, const T* vy, const T* vz, T* oh, T* oc, T* on, T* oo,
+                                const int* acs_host, void* stream)
+{
+    long long n_atoms = 0;
+    if (int rc = check_acs(acs_host, &n_atoms)) return rc;
+    if (n_mols < 0) return ANI_ERR_BAD_SIZE;
+    if (n_mols == 0 || n_atoms == 0) return ANI_OK;
+    if (!xs || !ys || !zs || !types || !mos || !macs || !sis || !vx || !vy || !vz)
+        return ANI_ERR_NULL_POINTER;
+    T* outs[kTypes] = {oh, oc, on, oo};
+    for (int t = 0; t < kTypes; t++)
+        if (acs_host[t] > 0 && !outs[t]) return ANI_ERR_NULL_POINTER;
+
+    auto kernel = featurize_grad_inverse_kernel<T, kNW>;
+    const size_t smem = kNW * sizeof(JvpWarpShared<T>);
+    static thread_local int configured_dev = -1, cached_resident = 0;
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        if (int rc = set_smem(kernel, smem)) return rc;
+        if (int rc = featurizer_grid(kernel, smem, 1 << 24, &cached_resident)) return rc;
+        configured_dev = dev;
+    }
+    const long long needed = (long long)n_mols * (kSlotsPerMol / kNW);
+    const int grid = (int)(needed < cached_resident ? needed : cached_resident);
+    kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
+        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, vx, vy, vz, oh, oc, on, oo,
+        acs_host[0], acs_host[1], acs_host[2], acs_host[3]);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -365,6 +401,32 @@ int ani_featurize_grad_f64(const double* xs, const double* ys, const double* zs,
     return featurize_grad_impl<double>(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
                                        n_mols, scatter_idxs, grad_h, grad_c, grad_n, grad_o,
                                        x_grads, y_grads, z_grads, acs_host, stream);
+}
+
+int ani_featurize_grad_inverse_f32(const float* xs, const float* ys, const float* zs,
+                                   const int* atomic_numbers, const int* mol_offsets,
+                                   const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                                   const float* x_grads, const float* y_grads, const float* z_grads,
+                                   float* out_h, float* out_c, float* out_n, float* out_o,
+                                   const int* acs_host, void* stream)
+{
+    return featurize_grad_inverse_impl<float>(xs, ys, zs, atomic_numbers, mol_offsets,
+                                              mol_atom_counts, n_mols, scatter_idxs, x_grads,
+                                              y_grads, z_grads, out_h, out_c, out_n, out_o,
+                                              acs_host, stream);
+}
+
+int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const double* zs,
+                                   const int* atomic_numbers, const int* mol_offsets,
+                                   const int* mol_atom_counts, int n_mols, const int* scatter_idxs,
+                                   const double* x_grads, const double* y_grads,
+                                   const double* z_grads, double* out_h, double* out_c,
+                                   double* out_n, double* out_o, const int* acs_host, void* stream)
+{
+    return featurize_grad_inverse_impl<double>(xs, ys, zs, atomic_numbers, mol_offsets,
+                                               mol_atom_counts, n_mols, scatter_idxs, x_grads,
+                                               y_grads, z_grads, out_h, out_c, out_n, out_o,
+                                               acs_host, stream);
 }
 
 }  // extern "C"

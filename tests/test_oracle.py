@@ -155,3 +155,20 @@ def test_reference_build_agrees_when_present(oracle_mod):
     for a, c in zip(oracle_mod.featurize_grad(x, y, z, *args, *g, impl="port"),
                     oracle_mod.featurize_grad(x, y, z, *args, *g, impl="ref")):
         assert normwise(a, c) < 1e-13
+
+
+def test_reference_indexing_of_grad_inverse_vanishes(oracle_mod):
+    # gpu_featurizer/kernel_cpu.cpp:111,118,155,162,169 read X_grads at the central atom's element
+    # id for every atom of a term; the i/j/k derivatives of a term cancel, so the result is ~0
+    b = syn.kat_fixture()
+    si, gi, ac = oracle_mod.ani_sort(b.atomic_numbers)
+    rng = np.random.default_rng(4)
+    v = [rng.normal(size=b.n_atoms) for _ in range(3)]
+    args = (b.atomic_numbers, b.mol_offsets, b.mol_atom_counts, si, ac)
+    port = oracle_mod.featurize_grad_inverse(b.xs, b.ys, b.zs, *args, *v, reference_indexing=True)
+    assert all(np.abs(o).max() == 0 for o in port if o.size)
+    if oracle_mod.available("ref"):
+        ref = oracle_mod.featurize_grad_inverse(b.xs, b.ys, b.zs, *args, *v, impl="ref")
+        assert all(np.abs(o).max() < 1e-12 for o in ref if o.size)
+    jvp = oracle_mod.featurize_grad_inverse(b.xs, b.ys, b.zs, *args, *v)
+    assert max(np.abs(o).max() for o in jvp if o.size) > 1.0
