@@ -235,6 +235,7 @@ __device__ __forceinline__ int build_pair_tables(PairTables& pt, const int* ang_
         pt.tab[lane] = e;
     }
     if (lane <= kPairBuckets) pt.off[lane] = off;
+    if (lane == kPairBuckets + 1) pt.off[lane] = 0x7fffffff;   // sentinel behind the total
     const int total = __shfl_sync(kFull, incl, kPairBuckets - 1);
     __syncwarp();
     // bucket of every quad of padded positions (all bucket starts are multiples of 4), up to

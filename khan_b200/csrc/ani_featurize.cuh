@@ -106,6 +106,9 @@ __device__ __noinline__ void featurize_atom_streaming(const T* __restrict__ xs,
     for (int b = 0; b < kPairBuckets; b++) row[kRadial + b * kTS + lane] = acc[b];
 }
 
+#ifndef ANI_ABLATE
+#define ANI_ABLATE 0   // tuning builds only: bit mask of phases to leave out (results are wrong)
+#endif
 #ifndef ANI_FWD_MIN_CTAS
 #define ANI_FWD_MIN_CTAS 8
 #endif
@@ -211,6 +214,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
 
             ANI_PHASE(1);
             // ---- R: radial features, lane = (half, shift) ----
+#if !(ANI_ABLATE & 1)
             {
                 const int half = lane >> 4;
                 const T shift = (T)c_tab.R_Rs[lane & 15];
@@ -228,17 +232,30 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
                 row[lane] = lane < 16 ? acc[0] : acc[1];
                 row[32 + lane] = lane < 16 ? acc[2] : acc[3];
             }
+#endif
 
             ANI_PHASE(2);
             // ---- B + C: angular features ----
+#if ANI_ABLATE & 2
+            const int total = (cA[0] + cA[1] + cA[2] + cA[3]) * 0;
+            if (lane < 12) ws.pt.off[lane] = 0;
+            __syncwarp();
+#else
             const int total = build_pair_tables<CAPT>(ws.pt, cA);
+#endif
             ANI_PHASE(3);
             const T* a_row = &ws.A[lane >> 2][0];
             const T* b_row = &ws.BF[lane & 3][0];
             int cur = 0;                  // bucket being accumulated
             int cur_end = ws.pt.off[1];   // padded end of bucket `cur`
-            T acc0 = (T)0, acc1 = (T)0;
+            Pair<T> acc{(T)0, (T)0};
+            while (cur < kPairBuckets && cur_end <= 0) {   // leading empty buckets
+                row[kRadial + cur * kTS + lane] = (T)0;
+                cur++;
+                cur_end = ws.pt.off[cur + 1];
+            }
             for (int c0 = 0; c0 < total; c0 += kWarp) {
+#if !(ANI_ABLATE & 4)
                 {   // B: lane = pair
                     int bk, a, b;
                     const bool valid = decode_pair(ws.pt, c0 + lane, &bk, &a, &b);
@@ -253,36 +270,36 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
 #pragma unroll
                     for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = BF[q];
                 }
+#endif
                 __syncwarp();
                 ANI_PHASE(4);
-                {   // C: lane = (theta, shift)
-                    const int chunk_end = min(c0 + kWarp, total);
-                    int pp = c0;
-                    while (pp < chunk_end) {
-                        while (cur_end <= pp) {   // bucket `cur` is complete: write its 32 features
-                            row[kRadial + cur * kTS + lane] = acc0 + acc1;
-                            acc0 = acc1 = (T)0;
-                            cur++;
-                            cur_end = ws.pt.off[cur + 1];  // cur + 1 <= 10 here, because pp < total
-                        }
-                        const int seg_end = min(chunk_end, cur_end);
-                        for (; pp < seg_end; pp += 4) {
-                            T av[4], bv[4];
-                            load4(a_row + (pp - c0), av);
-                            load4(b_row + (pp - c0), bv);
-                            acc0 += av[0] * bv[0];
-                            acc1 += av[1] * bv[1];
-                            acc0 += av[2] * bv[2];
-                            acc1 += av[3] * bv[3];
+#if !(ANI_ABLATE & 8)
+                {   // C: lane = (theta, shift).  All 8 quads of the chunk, fully unrolled; slots
+                    // past the end of the list hold zeros, so no bound is needed.
+#pragma unroll
+                    for (int q4 = 0; q4 < kWarp; q4 += 4) {
+                        T av[4], bv[4];
+                        load4(a_row + q4, av);
+                        load4(b_row + q4, bv);
+                        acc = pfma(Pair<T>{av[0], av[1]}, Pair<T>{bv[0], bv[1]}, acc);
+                        acc = pfma(Pair<T>{av[2], av[3]}, Pair<T>{bv[2], bv[3]}, acc);
+                        if (c0 + q4 + 4 >= cur_end) {   // bucket `cur` ends with this quad
+                            while (cur < kPairBuckets && c0 + q4 + 4 >= cur_end) {
+                                row[kRadial + cur * kTS + lane] = acc.x + acc.y;
+                                acc = Pair<T>{(T)0, (T)0};
+                                cur++;
+                                cur_end = ws.pt.off[cur + 1];   // off[11] is a large sentinel
+                            }
                         }
                     }
                 }
+#endif
                 __syncwarp();
                 ANI_PHASE(5);
             }
-            for (; cur < kPairBuckets; cur++) {
-                row[kRadial + cur * kTS + lane] = acc0 + acc1;
-                acc0 = acc1 = (T)0;
+            for (; cur < kPairBuckets; cur++) {   // buckets not closed inside the loop (total == 0)
+                row[kRadial + cur * kTS + lane] = acc.x + acc.y;
+                acc = Pair<T>{(T)0, (T)0};
             }
             ANI_PHASE(6);
         }

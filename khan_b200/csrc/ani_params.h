@@ -117,6 +117,66 @@ __device__ __forceinline__ float sfu_sqrt(float x)
 }
 #endif
 
+// Two values processed by one instruction where the hardware can: Blackwell (sm_100) has packed
+// single-precision fma / mul / add (fma.rn.f32x2 ...), which halves the instruction count of the
+// multiply-add heavy loops.  Everywhere else (double, host) a pair is just two scalars.
+template <typename T> struct Pair {
+    T x, y;
+};
+
+template <typename T> ANI_HD Pair<T> pfma(Pair<T> a, Pair<T> b, Pair<T> c)
+{
+    return Pair<T>{a.x * b.x + c.x, a.y * b.y + c.y};
+}
+template <typename T> ANI_HD Pair<T> pmul(Pair<T> a, Pair<T> b) { return Pair<T>{a.x * b.x, a.y * b.y}; }
+template <typename T> ANI_HD Pair<T> padd(Pair<T> a, Pair<T> b) { return Pair<T>{a.x + b.x, a.y + b.y}; }
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ unsigned long long pack2(float x, float y)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ Pair<float> unpack2(unsigned long long r)
+{
+    Pair<float> p;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(p.x), "=f"(p.y) : "l"(r));
+    return p;
+}
+#endif
+
+template <> ANI_HD Pair<float> pfma<float>(Pair<float> a, Pair<float> b, Pair<float> c)
+{
+#if defined(__CUDA_ARCH__)
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack2(a.x, a.y)), "l"(pack2(b.x, b.y)), "l"(pack2(c.x, c.y)));
+    return unpack2(d);
+#else
+    return Pair<float>{a.x * b.x + c.x, a.y * b.y + c.y};
+#endif
+}
+template <> ANI_HD Pair<float> pmul<float>(Pair<float> a, Pair<float> b)
+{
+#if defined(__CUDA_ARCH__)
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack2(a.x, a.y)), "l"(pack2(b.x, b.y)));
+    return unpack2(d);
+#else
+    return Pair<float>{a.x * b.x, a.y * b.y};
+#endif
+}
+template <> ANI_HD Pair<float> padd<float>(Pair<float> a, Pair<float> b)
+{
+#if defined(__CUDA_ARCH__)
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack2(a.x, a.y)), "l"(pack2(b.x, b.y)));
+    return unpack2(d);
+#else
+    return Pair<float>{a.x + b.x, a.y + b.y};
+#endif
+}
+
 template <> struct Num<float> {
     static constexpr float kPi = 3.14159265358979323846f;
     // exp(-eta * x2) for x2 >= 0 (a squared distance offset)
@@ -204,14 +264,18 @@ template <typename T> ANI_HD T radial_term(T rij, T fc, int r)
 // radial part of the coordinate gradient (gpu_featurizer/kernel_cpu.cpp:281-301).
 template <typename T, typename W> ANI_HD T radial_vjp(T rij, T fc, T dfc, const W* w)
 {
-    T acc = (T)0;
+    Pair<T> acc{(T)0, (T)0};
+    const Pair<T> rr{rij, rij}, slope{(T)-2 * (T)kR_eta * fc, (T)-2 * (T)kR_eta * fc}, dd{dfc, dfc};
 #pragma unroll
-    for (int r = 0; r < kNumRs; r++) {
-        const T d = rij - radial_shift<T>(r);
-        const T e = Num<T>::exp_neg((T)kR_eta, d * d);
-        acc += (T)w[r] * e * ((T)-2 * (T)kR_eta * d * fc + dfc);
+    for (int r = 0; r < kNumRs; r += 2) {   // two radial shifts per packed instruction
+        const Pair<T> neg_shift{-radial_shift<T>(r), -radial_shift<T>(r + 1)};
+        const Pair<T> d = padd(rr, neg_shift);
+        const Pair<T> d2 = pmul(d, d);
+        const Pair<T> e{Num<T>::exp_neg((T)kR_eta, d2.x), Num<T>::exp_neg((T)kR_eta, d2.y)};
+        const Pair<T> we = pmul(Pair<T>{(T)w[r], (T)w[r + 1]}, e);
+        acc = pfma(we, pfma(d, slope, dd), acc);
     }
-    return acc;
+    return acc.x + acc.y;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -226,18 +290,28 @@ template <typename T> ANI_HD void angular_factors(T cosv, T rbar, T fcprod, T* A
 {
     const T c = Num<T>::max_((T)-1, Num<T>::min_((T)1, cosv));
     const T s = Num<T>::sqrt_(Num<T>::max_((T)0, (T)1 - c * c));
+    const Pair<T> cc{c, c}, ss{s, s}, one{(T)1, (T)1};
 #pragma unroll
-    for (int t = 0; t < kNumThetas; t++) {
-        const T b = (T)1 + (c * theta_cos<T>(t) + s * theta_sin<T>(t));
-        const T b2 = b * b;
-        const T b4 = b2 * b2;
-        A[t] = b4 * b4;
+    for (int t = 0; t < kNumThetas; t += 2) {   // two theta shifts per (packed) instruction
+        const Pair<T> ct{theta_cos<T>(t), theta_cos<T>(t + 1)}, st{theta_sin<T>(t), theta_sin<T>(t + 1)};
+        const Pair<T> b = pfma(cc, ct, pfma(ss, st, one));
+        const Pair<T> b2 = pmul(b, b);
+        const Pair<T> b4 = pmul(b2, b2);
+        const Pair<T> b8 = pmul(b4, b4);
+        A[t] = b8.x;
+        A[t + 1] = b8.y;
     }
     const T f = (T)kA_pref * fcprod;
+    const Pair<T> ff{f, f}, rr{rbar, rbar};
 #pragma unroll
-    for (int q = 0; q < kNumARs; q++) {
-        const T d = rbar - angular_shift<T>(q);
-        BF[q] = Num<T>::exp_neg((T)kA_eta, d * d) * f;
+    for (int q = 0; q < kNumARs; q += 2) {
+        const Pair<T> neg_shift{-angular_shift<T>(q), -angular_shift<T>(q + 1)};
+        const Pair<T> d = padd(rr, neg_shift);
+        const Pair<T> d2 = pmul(d, d);
+        const Pair<T> e{Num<T>::exp_neg((T)kA_eta, d2.x), Num<T>::exp_neg((T)kA_eta, d2.y)};
+        const Pair<T> bf = pmul(e, ff);
+        BF[q] = bf.x;
+        BF[q + 1] = bf.y;
     }
 }
 
@@ -273,35 +347,46 @@ ANI_HD void angular_vjp(T cosv, T sin2, T rij, T rik, T fcj, T dfcj, T fck, T df
     const T keep = bent ? (T)1 : (T)0;
     const T rbar = (T)0.5 * (rij + rik);
 
-    T e[kNumARs], de[kNumARs];
+    // e[q] = exp(-eta d_q^2), de[q] = d_q e[q], two shifts per packed instruction
+    Pair<T> e[kNumARs / 2], de[kNumARs / 2];
+    const Pair<T> rr{rbar, rbar};
 #pragma unroll
-    for (int q = 0; q < kNumARs; q++) {
-        const T d = rbar - angular_shift<T>(q);
-        e[q] = Num<T>::exp_neg((T)kA_eta, d * d);
-        de[q] = d * e[q];
+    for (int q = 0; q < kNumARs; q += 2) {
+        const Pair<T> neg_shift{-angular_shift<T>(q), -angular_shift<T>(q + 1)};
+        const Pair<T> d = padd(rr, neg_shift);
+        const Pair<T> d2 = pmul(d, d);
+        e[q / 2] = Pair<T>{Num<T>::exp_neg((T)kA_eta, d2.x), Num<T>::exp_neg((T)kA_eta, d2.y)};
+        de[q / 2] = pmul(d, e[q / 2]);
     }
-    T s0 = (T)0, s2sum = (T)0, sc = (T)0, ss = (T)0;
+    // u[t] = sum_q g[t][q] e[q], v[t] = sum_q g[t][q] de[q]
+    T u[kNumThetas], v[kNumThetas];
 #pragma unroll
     for (int t = 0; t < kNumThetas; t++) {
-        T u = (T)0, v = (T)0;
-#pragma unroll
-        for (int q = 0; q < kNumARs; q++) {
-            const T w = (T)g[t * kNumARs + q];
-            u += w * e[q];
-            v += w * de[q];
-        }
-        const T ct = theta_cos<T>(t), st = theta_sin<T>(t);
-        const T b = (T)1 + (c * ct + s * st);
-        const T b2 = b * b;
-        const T b4 = b2 * b2;
-        const T b7 = b4 * b2 * b;
-        const T a = b7 * b;
-        s0 += a * u;
-        s2sum += a * v;
-        const T b7u = b7 * u;
-        sc += b7u * ct;
-        ss += b7u * st;
+        const Pair<T> g01{(T)g[t * kNumARs + 0], (T)g[t * kNumARs + 1]};
+        const Pair<T> g23{(T)g[t * kNumARs + 2], (T)g[t * kNumARs + 3]};
+        const Pair<T> pu = pfma(g23, e[1], pmul(g01, e[0]));
+        const Pair<T> pv = pfma(g23, de[1], pmul(g01, de[0]));
+        u[t] = pu.x + pu.y;
+        v[t] = pv.x + pv.y;
     }
+    Pair<T> s0p{(T)0, (T)0}, s2p{(T)0, (T)0}, scp{(T)0, (T)0}, ssp{(T)0, (T)0};
+    const Pair<T> cc{c, c}, sn{s, s}, one{(T)1, (T)1};
+#pragma unroll
+    for (int t = 0; t < kNumThetas; t += 2) {   // two theta shifts per packed instruction
+        const Pair<T> ct{theta_cos<T>(t), theta_cos<T>(t + 1)}, st{theta_sin<T>(t), theta_sin<T>(t + 1)};
+        const Pair<T> ut{u[t], u[t + 1]}, vt{v[t], v[t + 1]};
+        const Pair<T> b = pfma(cc, ct, pfma(sn, st, one));
+        const Pair<T> b2 = pmul(b, b);
+        const Pair<T> b4 = pmul(b2, b2);
+        const Pair<T> b7 = pmul(pmul(b4, b2), b);
+        const Pair<T> a = pmul(b7, b);
+        s0p = pfma(a, ut, s0p);
+        s2p = pfma(a, vt, s2p);
+        const Pair<T> b7u = pmul(b7, ut);
+        scp = pfma(b7u, ct, scp);
+        ssp = pfma(b7u, st, ssp);
+    }
+    const T s0 = s0p.x + s0p.y, s2sum = s2p.x + s2p.y, sc = scp.x + scp.y, ss = ssp.x + ssp.y;
     const T f = (T)kA_pref * fcj * fck;
     // dA_t/dc = 8 b^7 (cos(theta_t) - sin(theta_t) c / s)
     *dc = (T)8 * f * (keep * sc - cot * ss);
