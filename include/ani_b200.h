@@ -41,6 +41,7 @@ extern "C" {
 #define ANI_ERR_BAD_ELEMENT (-4)    /* device saw an element id outside 0..3 (status word) */
 #define ANI_ERR_BAD_INDEX (-6)      /* device saw an offset/count/scatter index out of range */
 #define ANI_ERR_TOO_MANY_ATOMS (-7) /* size beyond what an entry point supports          */
+#define ANI_ERR_TIMEOUT (-8)        /* a bounded device-side wait ran out (status word)    */
 
 /* Number of features per atom (384).  Replaces the `feature_size` attr of the Featurize op
  * (gpu_featurizer/ani_op.cpp:104). */
@@ -164,6 +165,38 @@ int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const dou
                                    const double* x_grads, const double* y_grads,
                                    const double* z_grads, double* out_h, double* out_c,
                                    double* out_n, double* out_o, const int* acs_host, void* stream);
+
+/*
+ * Atomic networks, forward -- replaces the four AtomNN stacks that MoleculeNN builds
+ * (khan/model/nn.py:39-67, 165-172) for the architecture 384-128-128-64-1 used by the
+ * reference drivers (gdb8.py:91): for every element t,
+ *   energy[t] = act(act(act(F_t W1 + b1) W2 + b2) W3 + b3) w4 + b4,   F_t = features[t] [acs[t]][384].
+ * One launch covers all four elements; the matrix products run on the tensor cores in tf32.
+ * Weights are passed transposed, [out][in] with `in` contiguous.  `activation`: 0 celu(0.1),
+ * 1 gaussian exp(-x^2), 2 normal exp(-x^2/2), 3 softplus - ln 2 (khan/model/activations.py:62-74).
+ * `split_precision` != 0 splits every operand into two tf32 terms (three MMAs per product),
+ * which brings the products to float32 accuracy; 0 uses plain tf32.
+ * act1/act2/act3 receive the hidden activations ([acs[t]][128], [128], [64]) when non-NULL
+ * (the backward pass needs them).  Pointers of an element with acs_host[t] == 0 may be NULL.
+ */
+typedef struct ani_mlp_args {
+    const float* features[4];
+    const float* w1t[4];  /* [128][384] */
+    const float* b1[4];   /* [128] */
+    const float* w2t[4];  /* [128][128] */
+    const float* b2[4];   /* [128] */
+    const float* w3t[4];  /* [64][128] */
+    const float* b3[4];   /* [64] */
+    const float* w4[4];   /* [64] */
+    const float* b4[4];   /* [1] */
+    float* energy[4];     /* [acs[t]] */
+    float* act1[4];
+    float* act2[4];
+    float* act3[4];
+} ani_mlp_args;
+
+int ani_mlp_forward_f32(const ani_mlp_args* args_host, const int* acs_host, int activation,
+                        int split_precision, void* stream);
 
 #ifdef __cplusplus
 }

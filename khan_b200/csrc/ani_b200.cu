@@ -12,6 +12,7 @@
 #include "ani_featurize.cuh"
 #include "ani_grad.cuh"
 #include "ani_grad_inverse.cuh"
+#include "ani_mlp.cuh"
 #include "ani_sort.cuh"
 
 namespace {
@@ -254,6 +255,27 @@ int featurize_grad_inverse_impl(const T* xs, const T* ys, const T* zs, const int
     return ANI_OK;
 }
 
+template <int ACT, bool SPLIT> int mlp_launch(const MlpParams& p, int n_tiles, cudaStream_t st)
+{
+    auto kernel = mlp_forward_kernel<ACT, SPLIT>;
+    const size_t smem = sizeof(MlpShared) + 1024;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        if (int rc = set_smem(kernel, smem)) return rc;
+        configured_dev = dev;
+    }
+    kernel<<<n_tiles, kMlpTile, smem, st>>>(p);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+template <int ACT> int mlp_launch_act(const MlpParams& p, int n_tiles, bool split, cudaStream_t st)
+{
+    return split ? mlp_launch<ACT, true>(p, n_tiles, st) : mlp_launch<ACT, false>(p, n_tiles, st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -270,6 +292,7 @@ const char* ani_status_string(int status)
         case ANI_ERR_BAD_ELEMENT: return "element id outside 0..3 in atomic_numbers";
         case ANI_ERR_BAD_INDEX: return "molecule offset/count or scatter index out of range";
         case ANI_ERR_TOO_MANY_ATOMS: return "size beyond what this entry point supports";
+        case ANI_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         default: return "unknown status";
     }
 }
@@ -427,6 +450,42 @@ int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const dou
                                                mol_atom_counts, n_mols, scatter_idxs, x_grads,
                                                y_grads, z_grads, out_h, out_c, out_n, out_o,
                                                acs_host, stream);
+}
+
+int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activation,
+                        int split_precision, void* stream)
+{
+    long long n_atoms = 0;
+    if (!a) return ANI_ERR_NULL_POINTER;
+    if (int rc = check_acs(acs_host, &n_atoms)) return rc;
+    if (activation < 0 || activation > 3) return ANI_ERR_BAD_SIZE;
+    if (n_atoms == 0) return ANI_OK;
+    MlpParams p;
+    int tiles = 0;
+    for (int t = 0; t < kTypes; t++) {
+        p.tile_start[t] = tiles;
+        p.count[t] = acs_host[t];
+        tiles += (acs_host[t] + kMlpTile - 1) / kMlpTile;
+        if (acs_host[t] > 0 && (!a->features[t] || !a->w1t[t] || !a->b1[t] || !a->w2t[t] || !a->b2[t] ||
+                                !a->w3t[t] || !a->b3[t] || !a->w4[t] || !a->b4[t] || !a->energy[t]))
+            return ANI_ERR_NULL_POINTER;
+        p.feat[t] = a->features[t];
+        p.w1t[t] = a->w1t[t]; p.b1[t] = a->b1[t];
+        p.w2t[t] = a->w2t[t]; p.b2[t] = a->b2[t];
+        p.w3t[t] = a->w3t[t]; p.b3[t] = a->b3[t];
+        p.w4[t] = a->w4[t];   p.b4[t] = a->b4[t];
+        p.energy[t] = a->energy[t];
+        p.act1[t] = a->act1[t]; p.act2[t] = a->act2[t]; p.act3[t] = a->act3[t];
+    }
+    p.tile_start[kTypes] = tiles;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool split = split_precision != 0;
+    switch (activation) {
+        case kActCelu: return mlp_launch_act<kActCelu>(p, tiles, split, st);
+        case kActGaussian: return mlp_launch_act<kActGaussian>(p, tiles, split, st);
+        case kActNormal: return mlp_launch_act<kActNormal>(p, tiles, split, st);
+        default: return mlp_launch_act<kActSoftplus>(p, tiles, split, st);
+    }
 }
 
 }  // extern "C"

@@ -1,0 +1,348 @@
+// Per-element atomic network 384-128-128-64-1, forward pass, fused into one kernel on the
+// Blackwell tensor cores (tcgen05.mma, kind::tf32, accumulators in tensor memory).
+//
+// What it computes is AtomNN of the reference (khan/model/nn.py:39-67): for the atoms of one
+// element, A1 = act(F W1 + b1), A2 = act(A1 W2 + b2), A3 = act(A2 W3 + b3), E = A3 w4 + b4, with
+// F the [n, 384] feature rows of that element.  MoleculeNN (khan/model/nn.py:165-172) runs four
+// of these, one per element; here one launch covers all four (each CTA takes a tile of 128 atoms
+// of one element).
+//
+// Structure of one CTA (128 threads, tile = 128 atoms):
+//   * operands are staged by all threads into shared memory in the K-major, no-swizzle
+//     core-matrix layout that tcgen05.mma reads (8 rows x 16 bytes per core matrix), 64 values
+//     of K at a time; weights are passed pre-transposed ([out][in], K contiguous);
+//   * one thread issues the MMAs (M = 128, N = 128 or 64, K = 8 per instruction) and commits them
+//     to an mbarrier; everybody waits on it (bounded spin: on timeout the kernel records an
+//     error, frees its tensor memory and returns);
+//   * the epilogue reads the accumulator with tcgen05.ld (thread = atom), adds the bias,
+//     applies the activation and writes the row to shared memory, where it becomes the A
+//     operand of the next layer; the last layer (64 -> 1) is a dot product in registers.
+// With SPLIT = true every operand is staged as a high part (the value with its low 13 mantissa
+// bits cleared, exact in tf32) and a low part (the remainder), and hi*hi + hi*lo + lo*hi are
+// accumulated: three MMAs per step give products that are accurate to about 2^-21 instead of
+// the 2^-10 of plain tf32.
+#pragma once
+
+#include "ani_common.cuh"
+
+namespace ani {
+
+constexpr int kMlpIn = 384, kMlpH1 = 128, kMlpH2 = 128, kMlpH3 = 64;
+constexpr int kMlpTile = 128;             // atoms per CTA = MMA M
+constexpr int kMlpKChunk = 64;            // K values staged per step
+constexpr int kMlpLbo = 128;              // bytes between core matrices adjacent in K
+constexpr int kMlpSbo = (kMlpKChunk / 4) * 128;   // bytes between 8-row groups (2048)
+constexpr int kMlpOperandBytes = kMlpTile * kMlpKChunk * 4;   // 32 KiB
+constexpr int kMlpActStride = 129;        // floats per row of the activation buffer (bank-conflict free)
+constexpr int kMlpTmemCols = 128;
+constexpr unsigned kMlpSpinLimit = 1u << 24;
+
+enum MlpActivation { kActCelu = 0, kActGaussian = 1, kActNormal = 2, kActSoftplus = 3 };
+
+struct MlpParams {
+    const float* feat[kTypes];   // [count][384]
+    int count[kTypes];
+    int tile_start[kTypes + 1];  // prefix of ceil(count / 128)
+    const float* w1t[kTypes];    // [128][384]
+    const float* b1[kTypes];
+    const float* w2t[kTypes];    // [128][128]
+    const float* b2[kTypes];
+    const float* w3t[kTypes];    // [64][128]
+    const float* b3[kTypes];
+    const float* w4[kTypes];     // [64]
+    const float* b4[kTypes];     // [1]
+    float* energy[kTypes];       // [count]
+    float* act1[kTypes];         // optional [count][128] (saved for the backward pass)
+    float* act2[kTypes];         // optional [count][128]
+    float* act3[kTypes];         // optional [count][64]
+};
+
+struct MlpShared {
+    alignas(1024) unsigned char a_hi[kMlpOperandBytes];
+    alignas(1024) unsigned char b_hi[kMlpOperandBytes];
+    alignas(1024) unsigned char a_lo[kMlpOperandBytes];
+    alignas(1024) unsigned char b_lo[kMlpOperandBytes];
+    float act[kMlpTile * kMlpActStride];
+    alignas(8) unsigned long long mbar;
+    unsigned tmem_base;
+    int failed;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p)
+{
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// Bounded wait for the phase with the given parity; false on timeout.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity)
+{
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < kMlpSpinLimit; spin++) {
+        unsigned done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tmem_alloc(unsigned* dst_smem, unsigned cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, no swizzle, descriptor version 1.
+__device__ __forceinline__ unsigned long long smem_desc(unsigned byte_addr)
+{
+    unsigned long long d = 0;
+    d |= (unsigned long long)((byte_addr & 0x3ffff) >> 4);
+    d |= (unsigned long long)(kMlpLbo >> 4) << 16;
+    d |= (unsigned long long)(kMlpSbo >> 4) << 32;
+    d |= 1ull << 46;
+    return d;
+}
+// Instruction descriptor for kind::tf32: D = f32, A = B = tf32, both K-major, M x N.
+__device__ __forceinline__ unsigned instr_desc(int m, int n)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_tf32(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                         unsigned idesc, bool accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((unsigned)accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(unsigned long long* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 consecutive accumulator columns of this thread's row (TMEM lane).
+__device__ __forceinline__ void tmem_load32(unsigned taddr, float* v)
+{
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+template <int ACT> __device__ __forceinline__ float mlp_activation(float x)
+{
+    if (ACT == kActCelu) return x >= 0.0f ? x : 0.1f * (expf(x * 10.0f) - 1.0f);   // activations.py:62-65
+    if (ACT == kActGaussian) return expf(-x * x);                                  // activations.py:70-71
+    if (ACT == kActNormal) return expf(-0.5f * x * x);                             // activations.py:67-68
+    return (x > 20.0f ? x : log1pf(expf(x))) - 0.69314718056f;                      // activations.py:73-74
+}
+
+// Position of element (row, k) of a staged chunk in the core-matrix layout, in bytes.
+__device__ __forceinline__ int operand_offset(int row, int k)
+{
+    return (row >> 3) * kMlpSbo + (k >> 2) * kMlpLbo + (row & 7) * 16 + (k & 3) * 4;
+}
+
+// Stores four consecutive K values of one row as the high (tf32-exact) and low parts.
+template <bool SPLIT>
+__device__ __forceinline__ void stage4(unsigned char* hi, unsigned char* lo, int row, int k, float4 v)
+{
+    const int off = operand_offset(row, k);
+    if (SPLIT) {
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+        l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+        *reinterpret_cast<float4*>(hi + off) = h;
+        *reinterpret_cast<float4*>(lo + off) = l;
+    } else {
+        *reinterpret_cast<float4*>(hi + off) = v;
+    }
+}
+
+// (row, group of 4 K values) handled by thread `tid` in staging step `it`: 8 consecutive rows
+// first (one 128-byte core matrix per 8 lanes, conflict-free), then 4 adjacent K groups.
+__device__ __forceinline__ void staging_slot(int it, int tid, int* row, int* kgroup)
+{
+    const int q = it * kMlpTile + tid;
+    const int rest = q >> 5;
+    *row = (rest >> 2) * 8 + (q & 7);
+    *kgroup = (rest & 3) * 4 + ((q >> 3) & 3);
+}
+
+template <int ACT, bool SPLIT>
+__global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p)
+{
+    extern __shared__ unsigned char mlp_smem_raw[];
+    // the launch asks for sizeof(MlpShared) + 1024 bytes so that the struct can be aligned here
+    MlpShared& sh = *reinterpret_cast<MlpShared*>(
+        (reinterpret_cast<uintptr_t>(mlp_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5;
+
+    int e = 0;
+#pragma unroll
+    for (int t = 1; t < kTypes; t++) e += (int)blockIdx.x >= p.tile_start[t] ? 1 : 0;
+    const int row0 = ((int)blockIdx.x - p.tile_start[e]) * kMlpTile;
+    const int n_rows = min(kMlpTile, p.count[e] - row0);
+
+    if (warp == 0) tmem_alloc(&sh.tmem_base, kMlpTmemCols);
+    if (tid == 0) {
+        mbar_init(&sh.mbar, 1);
+        sh.failed = 0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = sh.tmem_base;
+    unsigned parity = 0;
+    bool ok = true;
+
+    const float* layer_w[3] = {p.w1t[e], p.w2t[e], p.w3t[e]};
+    const float* layer_b[3] = {p.b1[e], p.b2[e], p.b3[e]};
+    float* layer_out[3] = {p.act1[e], p.act2[e], p.act3[e]};
+    const int layer_k[3] = {kMlpIn, kMlpH1, kMlpH2};
+    const int layer_n[3] = {kMlpH1, kMlpH2, kMlpH3};
+    float h3[kMlpH3];   // activations of the last hidden layer, this thread's atom
+
+#pragma unroll 1
+    for (int layer = 0; layer < 3; layer++) {
+        const int K = layer_k[layer], N = layer_n[layer];
+        const unsigned idesc = instr_desc(kMlpTile, N);
+#pragma unroll 1
+        for (int kc = 0; kc < K; kc += kMlpKChunk) {
+            // ---- stage the A chunk (128 atoms x 64) and the B chunk (N outputs x 64) ----
+            for (int it = 0; it < kMlpKChunk / 4; it++) {
+                int row, kg;
+                staging_slot(it, tid, &row, &kg);
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (layer == 0) {
+                    if (row < n_rows)
+                        v = *reinterpret_cast<const float4*>(p.feat[e] + (size_t)(row0 + row) * kMlpIn + kc + kg * 4);
+                } else {
+                    const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
+                    v = make_float4(src[0], src[1], src[2], src[3]);
+                }
+                stage4<SPLIT>(sh.a_hi, sh.a_lo, row, kg * 4, v);
+                if (row < N) {
+                    const float4 w = *reinterpret_cast<const float4*>(layer_w[layer] + (size_t)row * K + kc + kg * 4);
+                    stage4<SPLIT>(sh.b_hi, sh.b_lo, row, kg * 4, w);
+                }
+            }
+            fence_async_smem();
+            __syncthreads();
+            if (tid == 0) {
+                tc_fence_after();
+                const unsigned a_hi = smem_u32(sh.a_hi), b_hi = smem_u32(sh.b_hi);
+                const unsigned a_lo = smem_u32(sh.a_lo), b_lo = smem_u32(sh.b_lo);
+#pragma unroll
+                for (int ks = 0; ks < kMlpKChunk / 8; ks++) {
+                    const unsigned step = ks * 2 * kMlpLbo;
+                    const bool first = kc == 0 && ks == 0;
+                    mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_hi + step), idesc, !first);
+                    if (SPLIT) {
+                        mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_lo + step), idesc, true);
+                        mma_tf32(tmem, smem_desc(a_lo + step), smem_desc(b_hi + step), idesc, true);
+                    }
+                }
+                mma_commit(&sh.mbar);
+            }
+            // operands may be overwritten, and the accumulator read, only after the MMAs finish
+            if (ok && !mbar_wait(&sh.mbar, parity)) ok = false;
+            parity ^= 1u;
+            if (!ok) sh.failed = 1;
+            __syncthreads();
+            if (sh.failed) break;
+        }
+        if (sh.failed) break;
+        tc_fence_after();
+        // ---- epilogue: thread = atom (TMEM lane), 32 columns at a time ----
+        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+        if (layer < 2) {
+            for (int c0 = 0; c0 < N; c0 += 32) {
+                float v[32];
+                tmem_load32(lane_addr + c0, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    v[i] = mlp_activation<ACT>(v[i] + layer_b[layer][c0 + i]);
+                    sh.act[tid * kMlpActStride + c0 + i] = v[i];
+                }
+                if (layer_out[layer] && tid < n_rows) {
+                    float* dst = layer_out[layer] + (size_t)(row0 + tid) * N + c0;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int c0 = 0; c0 < kMlpH3; c0 += 32) {
+                float v[32];
+                tmem_load32(lane_addr + c0, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) h3[c0 + i] = mlp_activation<ACT>(v[i] + layer_b[2][c0 + i]);
+                if (layer_out[2] && tid < n_rows) {
+                    float* dst = layer_out[2] + (size_t)(row0 + tid) * kMlpH3 + c0;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + i) =
+                            make_float4(h3[c0 + i], h3[c0 + i + 1], h3[c0 + i + 2], h3[c0 + i + 3]);
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
+    }
+
+    if (!sh.failed) {
+        // ---- output layer 64 -> 1 ----
+        float acc = p.b4[e][0];
+#pragma unroll
+        for (int i = 0; i < kMlpH3; i++) acc += h3[i] * p.w4[e][i];
+        if (tid < n_rows) p.energy[e][row0 + tid] = acc;
+    } else if (tid == 0) {
+        report(ANI_ERR_TIMEOUT);
+    }
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kMlpTmemCols);
+}
+
+}  // namespace ani

@@ -1,0 +1,202 @@
+"""Atomic and molecular networks: the model side of khan (``khan/model/nn.py`` of the reference).
+
+``AtomNN`` is one dense stack per element, ``A = act(A W + b)`` with a linear last layer of width
+one; ``MoleculeNN`` holds one ``AtomNN`` per element, evaluates each on the feature rows of its
+element and brings the atomic energies back to atom order with ``gather_idxs``
+(``khan/model/nn.py:39-67,165-172``).  Parameters keep the reference's shapes and names
+(``W`` is ``(in, out)``, names like ``near_W_H_384x128_l1``) so that its ``.npz`` checkpoints map
+one to one.
+
+For float32 and the architecture 384-128-128-64-1 the forward pass of all four networks is one
+fused tensor-core kernel (``ani_mlp_forward_f32``); its backward pass and every other
+architecture or precision use torch's dense GEMMs on the GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from .. import _lib
+from . import activations
+
+FUSED_LAYERS = (384, 128, 128, 64, 1)
+TYPE_MAP = ["H", "C", "N", "O"]
+
+
+class AtomNN:
+    """Dense stack for the atoms of one element."""
+
+    def __init__(self, layer_sizes, precision=torch.float32, activation_fn=activations.celu,
+                 atom_type: str = "", prefix: str = "", device="cuda", generator=None,
+                 init: str = "reference"):
+        assert precision in (torch.float32, torch.float64)
+        assert layer_sizes[-1] == 1
+        self.layer_sizes = tuple(int(v) for v in layer_sizes)
+        self.precision = precision
+        self.activation_fn = activation_fn
+        self.atom_type = atom_type
+        self.Ws, self.bs, self.names = [], [], []
+        for idx in range(1, len(layer_sizes)):
+            x, y = layer_sizes[idx - 1], layer_sizes[idx]
+            # reference: N(0, sqrt(2 / (x + y))), khan/model/nn.py:45-59; "he": N(0, sqrt(2 / x))
+            std = (2.0 / (x + y)) ** 0.5 if init == "reference" else (2.0 / x) ** 0.5
+            w = torch.randn((x, y), dtype=torch.float64, generator=generator) * std
+            name = "_" + atom_type + "_" + str(x) + "x" + str(y) + "_l" + str(idx)
+            self.Ws.append(w.to(precision).to(device).requires_grad_(True))
+            self.bs.append(torch.zeros(y, dtype=precision, device=device, requires_grad=True))
+            self.names.append((prefix + "W" + name, prefix + "b" + name))
+
+    def get_parameters(self):
+        return self.Ws + self.bs
+
+    def named_parameters(self):
+        out = {}
+        for (wn, bn), w, b in zip(self.names, self.Ws, self.bs):
+            out[wn + ":0"] = w
+            out[bn + ":0"] = b
+        return out
+
+    def atom_energies(self, features: torch.Tensor) -> torch.Tensor:
+        """Energies ``(n,)`` of the feature rows ``(n, layer_sizes[0])`` (dense torch path)."""
+        a = features
+        last = len(self.Ws) - 1
+        for k, (w, b) in enumerate(zip(self.Ws, self.bs)):
+            a = a @ w + b
+            if k != last:
+                a = self.activation_fn(a)
+        return a.reshape(-1)
+
+
+class _FusedMlp(torch.autograd.Function):
+    """Forward of the four atomic networks in one tensor-core kernel; backward in dense torch ops
+    from the hidden activations the kernel saved."""
+
+    @staticmethod
+    def forward(ctx, features, acs, act_id, split, act_fn, *params):
+        # params: for each of the 4 elements W1,b1,W2,b2,W3,b3,W4,b4 (reference shapes, W = (in, out))
+        n = features.shape[0]
+        dev = features.device
+        starts = np.concatenate([[0], np.cumsum(acs)])
+        energy = torch.empty(n, dtype=torch.float32, device=dev)
+        a1 = torch.empty((n, 128), dtype=torch.float32, device=dev)
+        a2 = torch.empty((n, 128), dtype=torch.float32, device=dev)
+        a3 = torch.empty((n, 64), dtype=torch.float32, device=dev)
+        args = _lib.MlpArgs()
+        keep = []
+        for t in range(4):
+            w1, b1, w2, b2, w3, b3, w4, b4 = params[8 * t: 8 * t + 8]
+            tr = [w1.detach().t().contiguous(), w2.detach().t().contiguous(),
+                  w3.detach().t().contiguous(), w4.detach().reshape(-1).contiguous()]
+            keep.extend(tr)
+            s = int(starts[t])
+            cnt = int(acs[t])
+
+            def ptr(tensor, offset=0, live=cnt > 0):
+                return ctypes.c_void_p(tensor.data_ptr() + offset * tensor.element_size()) if live else None
+
+            args.features[t] = ptr(features, s * 384)
+            args.w1t[t], args.w2t[t], args.w3t[t], args.w4[t] = (ptr(x) for x in tr)
+            args.b1[t], args.b2[t], args.b3[t], args.b4[t] = (ptr(b.detach()) for b in (b1, b2, b3, b4))
+            args.energy[t] = ptr(energy, s)
+            args.act1[t], args.act2[t], args.act3[t] = ptr(a1, s * 128), ptr(a2, s * 128), ptr(a3, s * 64)
+        acs_arr = np.ascontiguousarray(np.asarray(acs, dtype=np.int32))
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().ani_mlp_forward_f32(ctypes.byref(args), acs_arr.ctypes.data_as(_lib.c_int_p),
+                                                      int(act_id), int(bool(split)), stream),
+                       "ani_mlp_forward_f32")
+        ctx.save_for_backward(features, a1, a2, a3, *params)
+        ctx.acs, ctx.act_fn = acs_arr, act_fn
+        return energy
+
+    @staticmethod
+    def backward(ctx, grad_energy):
+        features, a1, a2, a3, *params = ctx.saved_tensors
+        acs, act_fn = ctx.acs, ctx.act_fn
+        starts = np.concatenate([[0], np.cumsum(acs)])
+        grad_feat = torch.zeros_like(features) if ctx.needs_input_grad[0] else None
+        grads = [None] * len(params)
+        for t in range(4):
+            s, e = int(starts[t]), int(starts[t + 1])
+            if e == s:
+                continue
+            w1, b1, w2, b2, w3, b3, w4, b4 = params[8 * t: 8 * t + 8]
+            f, h1, h2, h3 = features[s:e], a1[s:e], a2[s:e], a3[s:e]
+            g = grad_energy[s:e].reshape(-1, 1)
+            with torch.enable_grad():
+                # derivative of the activation from its output's pre-image: recompute the
+                # pre-activations with dense products (cheap next to the featurizer)
+                z1 = (f @ w1 + b1).detach().requires_grad_(True)
+                z2 = (h1 @ w2 + b2).detach().requires_grad_(True)
+                z3 = (h2 @ w3 + b3).detach().requires_grad_(True)
+                d1 = torch.autograd.grad(act_fn(z1).sum(), z1)[0]
+                d2 = torch.autograd.grad(act_fn(z2).sum(), z2)[0]
+                d3 = torch.autograd.grad(act_fn(z3).sum(), z3)[0]
+            gw4 = h3.t() @ g
+            gb4 = g.sum(0)
+            gz3 = (g @ w4.t()) * d3
+            gw3, gb3 = h2.t() @ gz3, gz3.sum(0)
+            gz2 = (gz3 @ w3.t()) * d2
+            gw2, gb2 = h1.t() @ gz2, gz2.sum(0)
+            gz1 = (gz2 @ w2.t()) * d1
+            gw1, gb1 = f.t() @ gz1, gz1.sum(0)
+            grads[8 * t: 8 * t + 8] = [gw1, gb1, gw2, gb2, gw3, gb3, gw4, gb4.reshape(b4.shape)]
+            if grad_feat is not None:
+                grad_feat[s:e] = gz1 @ w1.t()
+        return (grad_feat, None, None, None, None, *grads)
+
+
+class MoleculeNN:
+    """One :class:`AtomNN` per element plus the gather back to atom order."""
+
+    def __init__(self, type_map=TYPE_MAP, layer_sizes=FUSED_LAYERS, precision=torch.float32,
+                 activation_fn=activations.celu, prefix: str = "near_", device="cuda", seed=None,
+                 init: str = "reference", split_precision: bool = True):
+        gen = torch.Generator().manual_seed(seed) if seed is not None else None
+        self.type_map = list(type_map)
+        self.layer_sizes = tuple(layer_sizes)
+        self.precision = precision
+        self.activation_fn = activation_fn
+        self.split_precision = split_precision
+        self.anns = [AtomNN(layer_sizes, precision, activation_fn, atom_type=t, prefix=prefix,
+                            device=device, generator=gen, init=init) for t in self.type_map]
+
+    def get_parameters(self):
+        out = []
+        for a in self.anns:
+            out.extend(a.get_parameters())
+        return out
+
+    def named_parameters(self):
+        out = {}
+        for a in self.anns:
+            out.update(a.named_parameters())
+        return out
+
+    @property
+    def fused(self) -> bool:
+        return (self.precision == torch.float32 and self.layer_sizes == FUSED_LAYERS
+                and len(self.anns) == 4 and self.activation_fn in activations.KERNEL_ID)
+
+    def atom_energies_sorted(self, features: torch.Tensor, acs) -> torch.Tensor:
+        """Energies in element-sorted order from the ``[n_atoms, F]`` feature buffer laid out H
+        rows, C rows, N rows, O rows."""
+        acs = np.asarray(acs, dtype=np.int64)
+        if self.fused and features.is_cuda:
+            params = []
+            for a in self.anns:
+                for w, b in zip(a.Ws, a.bs):
+                    params.extend([w, b])
+            return _FusedMlp.apply(features, acs, activations.KERNEL_ID[self.activation_fn],
+                                   self.split_precision, self.activation_fn, *params)
+        starts = np.concatenate([[0], np.cumsum(acs)])
+        parts = [ann.atom_energies(features[int(starts[t]):int(starts[t + 1])])
+                 for t, ann in enumerate(self.anns)]
+        return torch.cat(parts)
+
+    def atom_outputs(self, features: torch.Tensor, acs, gather_idxs: torch.Tensor) -> torch.Tensor:
+        """Atomic energies in atom order (``tf.gather(tf.concat(...), gather_idxs)``,
+        khan/model/nn.py:171-172)."""
+        return self.atom_energies_sorted(features, acs)[gather_idxs.long()]
