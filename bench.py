@@ -211,6 +211,93 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------
+# training step (BASELINE config 3), reported separately from the benchmark metric
+# ------------------------------------------------------------------------------------------
+def run_train_workload(args):
+    """One step = config-1 batch per GPU -> ani_sort -> featurize -> four atomic networks
+    (384-128-128-64-1, gaussian, He-normal init seed 1) -> molecule energies -> MSE against
+    N(0,1) targets -> backward through the networks and through the featurizer into the
+    coordinates -> one NCCL all-reduce of the flat weight-gradient bucket -> Nadam step."""
+    import torch
+    import torch.distributed as dist
+
+    from khan_b200 import ani_mod
+    from khan_b200.data import synthetic as syn
+    from khan_b200.model import activations
+    from khan_b200.model.nn import MoleculeNN
+    from khan_b200.training.trainer_multi_tower import average_gradients
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=1, init="he")
+    params = model.get_parameters()
+    opt = torch.optim.NAdam(params, lr=1e-3)
+    nb = max(1, min(8, args.steps))
+    staged = []
+    for k, b in enumerate(syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)):
+        rng = np.random.default_rng(3000 + 100 * rank + k)
+        xyz = torch.from_numpy(np.stack(b.coords(np.float32))).to(dev)
+        ids = torch.from_numpy(np.repeat(np.arange(b.n_mols), b.mol_atom_counts)).to(dev)
+        staged.append(dict(
+            xyz=xyz, a=torch.from_numpy(b.atomic_numbers).to(dev), mo=torch.from_numpy(b.mol_offsets).to(dev),
+            mac=torch.from_numpy(b.mol_atom_counts).to(dev), ids=ids, n_mols=b.n_mols, n_atoms=b.n_atoms,
+            acs=np.bincount(b.atomic_numbers, minlength=4).astype(np.int32),
+            labels=torch.from_numpy(rng.normal(size=b.n_mols).astype(np.float32)).to(dev)))
+
+    def step(sb):
+        x, y, z = (sb["xyz"][k].clone().requires_grad_(True) for k in range(3))
+        si, gi, _ = ani_mod.ani_sort(sb["a"])
+        feat = ani_mod.featurize_sorted_autograd(x, y, z, sb["a"], sb["mo"], sb["mac"], si, sb["acs"])
+        atom_e = model.atom_outputs(feat, sb["acs"], gi)
+        pred = torch.zeros(sb["n_mols"], dtype=torch.float32, device=dev).index_add_(0, sb["ids"], atom_e)
+        loss = ((pred - sb["labels"]) ** 2).mean()
+        opt.zero_grad(set_to_none=True)
+        loss.backward()                      # weight gradients and d loss / d coordinates
+        average_gradients(params)            # one flat NCCL all-reduce
+        torch.nn.utils.clip_grad_norm_(params, 5.0)
+        opt.step()
+        return loss
+
+    for k in range(max(3, args.warmup)):
+        step(staged[k % nb])
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        loss = step(staged[k % nb])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    atoms = sum(staged[k % nb]["n_atoms"] for k in range(args.steps))
+    if world > 1:
+        t = torch.tensor([ms, float(atoms)], dtype=torch.float64, device=dev)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, atoms = float(tmax[0]), float(t[1])
+    if rank == 0:
+        print(json.dumps({
+            "metric": "training step atoms/sec (fp32, 1024-mol batch per GPU)", "value": atoms / (ms * 1e-3),
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 (tf32x3 tensor-core products in the atomic networks)", "data": "synthetic",
+            "final_loss": float(loss),
+            "config": {"workload": "config3: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian, He init) + MSE "
+                                   "+ backward into weights and coordinates + NCCL all-reduce + Nadam",
+                       "molecules_per_step_per_gpu": args.mols, "launch": "eager (torch autograd drives the step)"},
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
 def main():
@@ -227,6 +314,9 @@ def main():
                     help="independent batches in flight: steps are issued round-robin over this many streams")
     ap.add_argument("--mols", type=int, default=N_MOLS,
                     help="molecules per batch (1024 is the benchmark workload; other sizes are for profiling)")
+    ap.add_argument("--workload", default="aev", choices=["aev", "train"],
+                    help="aev: the benchmark metric (sort + featurize + featurize_grad); train: the full "
+                         "data-parallel training step of BASELINE config 3 (reported separately)")
     ap.add_argument("--profile", action="store_true",
                     help="only W warm-up and K timed steps, launched eagerly on one stream (for ncu)")
     args = ap.parse_args()
@@ -235,6 +325,9 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "train":
+        run_train_workload(args)
         return
 
     import torch

@@ -165,51 +165,74 @@ def featurize_grad_inverse(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_cou
     return tuple(flat[int(s):int(e)] for s, e in zip(starts, ends))
 
 
-class _Featurize(torch.autograd.Function):
+def featurize_sorted(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, scatter_idxs, acs):
+    """Featurize into one ``[n_atoms, 384]`` tensor laid out H rows, C rows, N rows, O rows (the
+    order ``gather_idxs`` indexes; the four outputs of :func:`featurize` are its slices)."""
+    acs_host = host_counts(acs)
+    out = torch.empty((int(acs_host.sum()), FEATURE_SIZE), dtype=xs.dtype, device=xs.device)
+    return featurize_into(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, scatter_idxs,
+                          acs_host, out)
+
+
+def _split(buf, acs_host):
+    flat = buf.reshape(-1)
+    ends = np.cumsum(acs_host) * FEATURE_SIZE
+    starts = ends - acs_host * FEATURE_SIZE
+    return [flat[int(s):int(e)] for s, e in zip(starts, ends)]
+
+
+class _FeaturizeSorted(torch.autograd.Function):
     """Featurize with the gradient wiring of the reference trainer: d/d(x, y, z) through
-    FeaturizeGrad (``khan/training/trainer_multi_tower.py:23-52``) and, one level up,
-    through FeaturizeGradInverse (``:64-91``)."""
+    FeaturizeGrad (``khan/training/trainer_multi_tower.py:23-52``) and, one level up, through
+    FeaturizeGradInverse (``:64-91``)."""
 
     @staticmethod
-    def forward(ctx, xs, ys, zs, a, mo, mac, si, acs_t):
-        acs = host_counts(acs_t)
+    def forward(ctx, xs, ys, zs, a, mo, mac, si, acs):
+        acs = host_counts(acs)
         ctx.save_for_backward(xs, ys, zs, a, mo, mac, si)
         ctx.acs = acs
-        h, c, n, o = featurize(xs, ys, zs, a, mo, mac, si, acs)
-        return h, c, n, o
+        return featurize_sorted(xs, ys, zs, a, mo, mac, si, acs)
 
     @staticmethod
-    def backward(ctx, gh, gc, gn, go):
+    def backward(ctx, grad_buf):
         xs, ys, zs, a, mo, mac, si = ctx.saved_tensors
-        gx, gy, gz = _FeaturizeGrad.apply(xs, ys, zs, a, mo, mac, si, ctx.acs, gh, gc, gn, go)
+        gx, gy, gz = _FeaturizeGradSorted.apply(xs, ys, zs, a, mo, mac, si, ctx.acs, grad_buf)
         return gx, gy, gz, None, None, None, None, None
 
 
-class _FeaturizeGrad(torch.autograd.Function):
+class _FeaturizeGradSorted(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, xs, ys, zs, a, mo, mac, si, acs, gh, gc, gn, go):
+    def forward(ctx, xs, ys, zs, a, mo, mac, si, acs, grad_buf):
         ctx.save_for_backward(xs, ys, zs, a, mo, mac, si)
         ctx.acs = acs
-        sizes = [int(c) * FEATURE_SIZE for c in acs]
-        gs = [g if g is not None else torch.zeros(s, dtype=xs.dtype, device=xs.device)
-              for g, s in zip((gh, gc, gn, go), sizes)]
-        return featurize_grad(xs, ys, zs, a, mo, mac, si, acs, *gs)
+        return featurize_grad(xs, ys, zs, a, mo, mac, si, acs, *_split(grad_buf.contiguous(), acs))
 
     @staticmethod
     def backward(ctx, vx, vy, vz):
         xs, ys, zs, a, mo, mac, si = ctx.saved_tensors
-        zero = lambda: torch.zeros_like(xs)  # noqa: E731
-        vx, vy, vz = (v if v is not None else zero() for v in (vx, vy, vz))
-        dh, dc, dn, do = featurize_grad_inverse(xs, ys, zs, a, mo, mac, si, ctx.acs, vx, vy, vz)
-        # gradients with respect to the coordinates themselves (third-order terms) are not
-        # provided, as in the reference (it returns None for the first eight inputs)
-        return (None,) * 8 + (dh, dc, dn, do)
+        vx, vy, vz = (v if v is not None else torch.zeros_like(xs) for v in (vx, vy, vz))
+        parts = featurize_grad_inverse(xs, ys, zs, a, mo, mac, si, ctx.acs, vx, vy, vz)
+        # the four parts are consecutive slices of one buffer; gradients with respect to the
+        # coordinates themselves (third-order terms) are not provided, as in the reference
+        # (it returns None for the first eight inputs)
+        n = int(ctx.acs.sum())
+        buf = torch.cat(parts).view(n, FEATURE_SIZE) if n else parts[0].view(0, FEATURE_SIZE)
+        return (None,) * 8 + (buf,)
+
+
+def featurize_sorted_autograd(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
+                              scatter_idxs, acs):
+    """:func:`featurize_sorted` that torch.autograd can differentiate with respect to xs, ys, zs."""
+    return _FeaturizeSorted.apply(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
+                                  scatter_idxs, acs)
 
 
 def featurize_autograd(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, scatter_idxs, acs):
-    """:func:`featurize` that torch.autograd can differentiate with respect to xs, ys, zs."""
-    return _Featurize.apply(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
-                            scatter_idxs, acs)
+    """:func:`featurize` (four flat outputs) that torch.autograd can differentiate."""
+    acs_host = host_counts(acs)
+    buf = featurize_sorted_autograd(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
+                                    scatter_idxs, acs_host)
+    return tuple(_split(buf, acs_host))
 
 
 def device_status() -> int:
