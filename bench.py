@@ -236,7 +236,7 @@ def run_train_workload(args):
         dist.init_process_group("nccl", device_id=dev)
     model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=1, init="he")
     params = model.get_parameters()
-    opt = torch.optim.NAdam(params, lr=1e-3)
+    opt = torch.optim.NAdam(params, lr=1e-3, capturable=True)
     nb = max(1, min(8, args.steps))
     staged = []
     for k, b in enumerate(syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)):
@@ -249,29 +249,72 @@ def run_train_workload(args):
             acs=np.bincount(b.atomic_numbers, minlength=4).astype(np.int32),
             labels=torch.from_numpy(rng.normal(size=b.n_mols).astype(np.float32)).to(dev)))
 
-    def step(sb):
+    def forward_backward(sb):
         x, y, z = (sb["xyz"][k].clone().requires_grad_(True) for k in range(3))
         si, gi, _ = ani_mod.ani_sort(sb["a"])
         feat = ani_mod.featurize_sorted_autograd(x, y, z, sb["a"], sb["mo"], sb["mac"], si, sb["acs"])
         atom_e = model.atom_outputs(feat, sb["acs"], gi)
         pred = torch.zeros(sb["n_mols"], dtype=torch.float32, device=dev).index_add_(0, sb["ids"], atom_e)
         loss = ((pred - sb["labels"]) ** 2).mean()
-        opt.zero_grad(set_to_none=True)
+        opt.zero_grad(set_to_none=False)
         loss.backward()                      # weight gradients and d loss / d coordinates
-        average_gradients(params)            # one flat NCCL all-reduce
+        return loss
+
+    def update():
         torch.nn.utils.clip_grad_norm_(params, 5.0)
         opt.step()
+
+    def step(sb):
+        loss = forward_backward(sb)
+        average_gradients(params)            # one flat NCCL all-reduce (no-op on one GPU)
+        update()
         return loss
 
     for k in range(max(3, args.warmup)):
         step(staged[k % nb])
     torch.cuda.synchronize()
+    # Forward + backward of each staged batch and the optimiser update are captured into CUDA
+    # graphs and replayed, so no Python runs between their launches.  The NCCL all-reduce stays
+    # outside the graphs (issued eagerly between the two), which keeps every rank's collective
+    # order independent of graph capture.
+    fb_graphs, up_graph, launch_mode = None, None, "eager (torch autograd drives the step)"
+    if not args.no_graph:
+        try:
+            fb_graphs, losses = [], []
+            pool = None
+            for sb in staged:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=pool):
+                    losses.append(forward_backward(sb))
+                pool = g.pool()
+                fb_graphs.append(g)
+            up_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(up_graph, pool=pool):
+                update()
+            launch_mode = "cuda_graph (forward+backward per staged batch, update; all-reduce eager)"
+        except Exception as exc:
+            print(f"[bench] training-step capture failed ({exc!r}); running eagerly", file=sys.stderr)
+            fb_graphs = up_graph = None
+            torch.cuda.synchronize()
+    use_graphs = torch.tensor([1 if fb_graphs is not None else 0], device=dev)
+    if world > 1:                            # every rank must take the same path
+        dist.all_reduce(use_graphs, op=dist.ReduceOp.MIN)
+    if int(use_graphs.item()) == 0:
+        fb_graphs = up_graph = None
+        launch_mode = "eager (torch autograd drives the step)"
     if world > 1:
         dist.barrier()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for k in range(args.steps):
-        loss = step(staged[k % nb])
+        if fb_graphs is not None:
+            fb_graphs[k % nb].replay()
+            average_gradients(params)
+            up_graph.replay()
+            loss = losses[k % nb]
+        else:
+            loss = step(staged[k % nb])
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
@@ -291,7 +334,7 @@ def run_train_workload(args):
             "final_loss": float(loss),
             "config": {"workload": "config3: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian, He init) + MSE "
                                    "+ backward into weights and coordinates + NCCL all-reduce + Nadam",
-                       "molecules_per_step_per_gpu": args.mols, "launch": "eager (torch autograd drives the step)"},
+                       "molecules_per_step_per_gpu": args.mols, "launch": launch_mode},
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -310,7 +353,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of CUDA graphs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 256)")
-    ap.add_argument("--streams", type=int, default=4,
+    ap.add_argument("--streams", type=int, default=8,
                     help="independent batches in flight: steps are issued round-robin over this many streams")
     ap.add_argument("--mols", type=int, default=N_MOLS,
                     help="molecules per batch (1024 is the benchmark workload; other sizes are for profiling)")
