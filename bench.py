@@ -199,8 +199,10 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "gpu_launches": 0,
-        "config": {"workload": "config1: GDB8-like molecules, float32 fwd+grad, seed 1",
-                   "molecules_per_step": sample.n_mols, "atoms_per_step": sample.n_atoms},
+        "config": {"workload": "config1: 1024 GDB8-like molecules per step per GPU, float32, "
+                               "ani_sort + featurize + featurize_grad",
+                   "molecules_per_step": sample.n_mols, "atoms_per_step": sample.n_atoms,
+                   "host_threads": threads},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads,
                          "kind": "reference" if impl == "ref_fast" else "port",
                          "sample": f"each step = first {sample.n_mols} molecules of the config-1 batch "
