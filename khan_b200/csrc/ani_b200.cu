@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -164,7 +165,10 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
         cached_grid_dev = dev;
     }
     const long long needed = (long long)n_mols * (kSlotsPerMol / kNW);
-    const int grid = (int)(needed < cached_resident ? needed : cached_resident);
+    int grid = (int)(needed < cached_resident ? needed : cached_resident);
+#ifdef ANI_PHASE_TIMING
+    if (getenv("ANI_DEBUG_FULL_GRID")) grid = (int)needed;   // tuning builds: one item per warp
+#endif
     kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, oh, oc, on, oo, acs_host[0],
         acs_host[1], acs_host[2], acs_host[3]);

@@ -195,13 +195,15 @@ struct alignas(16) PairBucketInfo {
     float inv_nb; // 1 / size of group tb
 };
 
-constexpr int kQuadTable = 64;  // quads (4 padded positions) whose bucket is looked up from a table
+constexpr int kQuadTable = 168;  // quads (4 padded positions) in the bucket table: 640 pairs + one chunk
 
 struct PairTables {
     PairBucketInfo tab[kPairBuckets];
     int off[kPairBuckets + 2];            // off[bk], off[10] = padded total
-    unsigned char quad_bucket[kQuadTable];
+    alignas(8) unsigned char quad_bucket[kQuadTable];   // kPairBuckets = "past the end"
 };
+
+constexpr int kMaxPaddedPairs = (kQuadTable - 8) * 4;   // lists with more pairs take the slow path
 
 // ta / tb of bucket k, two bits each.
 constexpr unsigned kBucketTa = 0u | (0u << 2) | (0u << 4) | (0u << 6) | (1u << 8) | (1u << 10) |
@@ -238,15 +240,14 @@ __device__ __forceinline__ int build_pair_tables(PairTables& pt, const int* ang_
     if (lane == kPairBuckets + 1) pt.off[lane] = 0x7fffffff;   // sentinel behind the total
     const int total = __shfl_sync(kFull, incl, kPairBuckets - 1);
     __syncwarp();
-    // bucket of every quad of padded positions (all bucket starts are multiples of 4), up to
-    // the end of the last 32-position chunk: positions past `total` resolve to bucket 9, where
-    // they fail the `q < cnt` test of decode_pair.
-    const int n_quads = min(((total + kWarp - 1) & ~(kWarp - 1)) >> 2, kQuadTable);
-    for (int q = lane; q < n_quads; q += kWarp) {
-        int bk = 0;
-#pragma unroll
-        for (int k = 1; k < kPairBuckets; k++) bk += (4 * q >= pt.off[k]) ? 1 : 0;
-        pt.quad_bucket[q] = (unsigned char)bk;
+    // Bucket of every quad of padded positions (all bucket starts are multiples of 4), through
+    // one chunk past the end of the list; quads past the end get the id kPairBuckets.  Each of
+    // lanes 0..9 fills the quads of its own bucket, lane 10 the tail.
+    if (total <= kMaxPaddedPairs) {
+        int q_lo = off >> 2, q_hi = (off + pad) >> 2;
+        if (lane == kPairBuckets) q_hi = (((total + kWarp - 1) & ~(kWarp - 1)) >> 2) + 8;
+        if (lane <= kPairBuckets)
+            for (int q = q_lo; q < q_hi; q++) pt.quad_bucket[q] = (unsigned char)lane;
     }
     __syncwarp();
     return total;
@@ -266,15 +267,8 @@ __device__ __forceinline__ int tri_row(int q)
 // (a and b then point at entry 0 of the list).
 __device__ __forceinline__ bool decode_pair(const PairTables& pt, int p, int* bucket, int* a, int* b)
 {
-    int bk;
-    const int quad = p >> 2;
-    if (quad < kQuadTable) {
-        bk = min((int)pt.quad_bucket[quad], kPairBuckets - 1);
-    } else {
-        bk = 0;
-#pragma unroll
-        for (int k = 1; k < kPairBuckets; k++) bk += (p >= pt.off[k]) ? 1 : 0;
-    }
+    // the caller guarantees total <= kMaxPaddedPairs, so p >> 2 is inside the table
+    const int bk = min((int)pt.quad_bucket[p >> 2], kPairBuckets - 1);
     const PairBucketInfo e = pt.tab[bk];
     const int q = p - e.off;
     const bool valid = q < e.cnt;

@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
         ws.ang_fc[e] = (T)0;
     }
     __syncwarp();
+    ANI_PHASE(14);
 
     const long long n_items = (long long)n_mols * kSlotsPerMol;
     const int grid_warps = gridDim.x * NW;
@@ -141,7 +142,10 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
     for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
         int m, slot;
         item_to_work(item, round, &m, &slot);
-        if (slot >= mol_counts[m]) continue;   // empty item: one cached load
+        const int n_of_m = mol_counts[m];
+        if (n_of_m < 0) report(ANI_ERR_BAD_INDEX);   // forces the load to complete here in timing builds
+        ANI_PHASE(15);
+        if (slot >= n_of_m) continue;   // empty item: one cached load
         MolRange mol;
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
@@ -244,16 +248,18 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
             const int total = build_pair_tables<CAPT>(ws.pt, cA);
 #endif
             ANI_PHASE(3);
+            if (total > kMaxPaddedPairs) {   // more pairs than the bucket table covers: slow path
+                featurize_atom_streaming<T>(xs, ys, zs, types, base, n, i, row);
+                __syncwarp();
+                continue;
+            }
             const T* a_row = &ws.A[lane >> 2][0];
             const T* b_row = &ws.BF[lane & 3][0];
-            int cur = 0;                  // bucket being accumulated
-            int cur_end = ws.pt.off[1];   // padded end of bucket `cur`
+            // blocks of element pairs that do not occur around this atom are zero
+#pragma unroll
+            for (int bk = 0; bk < kPairBuckets; bk++)
+                if (ws.pt.off[bk + 1] == ws.pt.off[bk]) row[kRadial + bk * kTS + lane] = (T)0;
             Pair<T> acc{(T)0, (T)0};
-            while (cur < kPairBuckets && cur_end <= 0) {   // leading empty buckets
-                row[kRadial + cur * kTS + lane] = (T)0;
-                cur++;
-                cur_end = ws.pt.off[cur + 1];
-            }
             for (int c0 = 0; c0 < total; c0 += kWarp) {
 #if !(ANI_ABLATE & 4)
                 {   // B: lane = pair
@@ -274,32 +280,29 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
                 __syncwarp();
                 ANI_PHASE(4);
 #if !(ANI_ABLATE & 8)
-                {   // C: lane = (theta, shift).  All 8 quads of the chunk, fully unrolled; slots
-                    // past the end of the list hold zeros, so no bound is needed.
+                {   // C: lane = (theta, shift).  All 8 quads of the chunk, fully unrolled (slots past
+                    // the end of the list hold zeros).  A block is written when the next quad belongs
+                    // to another element pair; ids[8] is the first quad of the next chunk.
+                    const unsigned long long ids = *reinterpret_cast<const unsigned long long*>(&ws.pt.quad_bucket[c0 >> 2]);
+                    const unsigned next_id = ws.pt.quad_bucket[(c0 >> 2) + 8];
 #pragma unroll
-                    for (int q4 = 0; q4 < kWarp; q4 += 4) {
+                    for (int q = 0; q < 8; q++) {
                         T av[4], bv[4];
-                        load4(a_row + q4, av);
-                        load4(b_row + q4, bv);
+                        load4(a_row + 4 * q, av);
+                        load4(b_row + 4 * q, bv);
                         acc = pfma(Pair<T>{av[0], av[1]}, Pair<T>{bv[0], bv[1]}, acc);
                         acc = pfma(Pair<T>{av[2], av[3]}, Pair<T>{bv[2], bv[3]}, acc);
-                        if (c0 + q4 + 4 >= cur_end) {   // bucket `cur` ends with this quad
-                            while (cur < kPairBuckets && c0 + q4 + 4 >= cur_end) {
-                                row[kRadial + cur * kTS + lane] = acc.x + acc.y;
-                                acc = Pair<T>{(T)0, (T)0};
-                                cur++;
-                                cur_end = ws.pt.off[cur + 1];   // off[11] is a large sentinel
-                            }
+                        const unsigned id = (unsigned)(ids >> (8 * q)) & 0xffu;
+                        const unsigned id_next = q < 7 ? (unsigned)(ids >> (8 * q + 8)) & 0xffu : next_id;
+                        if (id != id_next && id < kPairBuckets) {
+                            row[kRadial + id * kTS + lane] = acc.x + acc.y;
+                            acc = Pair<T>{(T)0, (T)0};
                         }
                     }
                 }
 #endif
                 __syncwarp();
                 ANI_PHASE(5);
-            }
-            for (; cur < kPairBuckets; cur++) {   // buckets not closed inside the loop (total == 0)
-                row[kRadial + cur * kTS + lane] = acc.x + acc.y;
-                acc = Pair<T>{(T)0, (T)0};
             }
             ANI_PHASE(6);
         }
