@@ -345,6 +345,15 @@ def run_train_workload(args):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
+CASE_WORKLOAD = {
+    "config1": "config1: 1024 GDB8-like molecules per step per GPU, float32, "
+               "ani_sort + featurize + featurize_grad",
+    "config2": "config2: the config1 batches in float64, ani_sort + featurize + featurize_grad",
+    "config4": "config4: 256 molecules of 64-256 atoms per step per GPU, float32, "
+               "ani_sort + featurize + featurize_grad",
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -362,6 +371,9 @@ def main():
     ap.add_argument("--workload", default="aev", choices=["aev", "train"],
                     help="aev: the benchmark metric (sort + featurize + featurize_grad); train: the full "
                          "data-parallel training step of BASELINE config 3 (reported separately)")
+    ap.add_argument("--case", default="config1", choices=["config1", "config2", "config4"],
+                    help="config1 is the benchmark workload; config2 (same batches in float64) and config4 "
+                         "(256 molecules of 64-256 atoms, float32) are extra measurements")
     ap.add_argument("--profile", action="store_true",
                     help="only W warm-up and K timed steps, launched eagerly on one stream (for ncu)")
     args = ap.parse_args()
@@ -397,15 +409,22 @@ def main():
 
     # ---- workload: NB distinct 1024-molecule batches per rank (weak scaling) -------------
     nb = max(1, min(args.batches, args.steps))
-    batches = syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)
+    tdtype = torch.float64 if args.case == "config2" else torch.float32
+    esize = 8 if args.case == "config2" else 4
+    if args.case == "config4":
+        nb = min(nb, 16)
+        args.mols = 256 if args.mols == N_MOLS else args.mols
+        batches = [syn.config4(seed=4 + 10 * k + 1000 * rank, n_mols=args.mols) for k in range(nb)]
+    else:
+        batches = syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)
     max_atoms = max(b.n_atoms for b in batches)
     host = []
     for k, b in enumerate(batches):
         ac = np.bincount(b.atomic_numbers, minlength=4)
-        host.append(HostBatch(b, syn.upstream_grads(b, ac, seed=12 + k), pin=(k < 16)))
+        host.append(HostBatch(b, syn.upstream_grads(b, ac, seed=12 + k), dtype=tdtype, pin=(k < 16)))
     staged = []
     for hb in host:
-        sb = StagedBatch(max_atoms, args.mols, device=dev)
+        sb = StagedBatch(max_atoms, args.mols, dtype=tdtype, device=dev)
         sb.upload(hb, non_blocking=False)
         staged.append(sb)
     torch.cuda.synchronize()
@@ -543,10 +562,10 @@ def main():
     e2e_steps = args.e2e_steps or min(args.steps, 256)
     n_slots = 3
     n_host = min(len(host), 16)
-    slots = [StagedBatch(max_atoms, args.mols, device=dev) for _ in range(n_slots)]
+    slots = [StagedBatch(max_atoms, args.mols, dtype=tdtype, device=dev) for _ in range(n_slots)]
     streams = [torch.cuda.Stream(device=dev) for _ in range(n_slots)]
-    out_feat = [torch.empty((max_atoms, FEATURE_SIZE), dtype=torch.float32).pin_memory() for _ in range(n_slots)]
-    out_grad = [torch.empty((3, max_atoms), dtype=torch.float32).pin_memory() for _ in range(n_slots)]
+    out_feat = [torch.empty((max_atoms, FEATURE_SIZE), dtype=tdtype).pin_memory() for _ in range(n_slots)]
+    out_grad = [torch.empty((3, max_atoms), dtype=tdtype).pin_memory() for _ in range(n_slots)]
 
     def e2e_pass(n_steps):
         h2d = d2h = atoms = 0
@@ -559,7 +578,7 @@ def main():
                 n = slots[s].n_atoms
                 out_feat[s][:n].copy_(slots[s].features[:n], non_blocking=True)
                 out_grad[s][:, :n].copy_(slots[s].grads[:, :n], non_blocking=True)
-                d2h += n * (FEATURE_SIZE + 3) * 4
+                d2h += n * (FEATURE_SIZE + 3) * esize
                 atoms += n
         return h2d, d2h, atoms
 
@@ -599,8 +618,9 @@ def main():
     mean_atoms = sum(atoms_per_step) / nb
     pairs, triplets = syn.count_work(batches[0])
     p_per_atom, t_per_atom = pairs / batches[0].n_atoms, triplets / batches[0].n_atoms
-    bytes_per_atom = {"ani_sort": 4 + 8, "featurize": 16 + 4 * FEATURE_SIZE,
-                      "featurize_grad": 16 + 4 * FEATURE_SIZE + 12}
+    coord = 3 * esize + 4
+    bytes_per_atom = {"ani_sort": 4 + 8, "featurize": coord + esize * FEATURE_SIZE,
+                      "featurize_grad": coord + esize * FEATURE_SIZE + 3 * esize}
     flops_per_atom = {"ani_sort": 0.0,
                       "featurize": FLOPS_FWD[0] * p_per_atom + FLOPS_FWD[1] * t_per_atom,
                       "featurize_grad": FLOPS_GRAD[0] * p_per_atom + FLOPS_GRAD[1] * t_per_atom}
@@ -610,7 +630,7 @@ def main():
     roofline = {"kernel": dominant, "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"],
                 "traffic": (NCU_DRAM_BYTES_PER_ATOM[dominant] * mean_atoms
-                            if NCU_DRAM_BYTES_PER_ATOM.get(dominant) else None),
+                            if args.case == "config1" and NCU_DRAM_BYTES_PER_ATOM.get(dominant) else None),
                 "peak_source": peak_kind,
                 "algorithmic_bytes_per_launch": bytes_per_atom[dominant] * mean_atoms}
     roofline_fp32 = {"kernel": dominant, "achieved": achieved_tf, "peak": FP32_PEAK_TFLOPS,
@@ -626,9 +646,9 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config1: 1024 GDB8-like molecules per step per GPU, float32, "
-                               "ani_sort + featurize + featurize_grad",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f64" if args.case == "config2" else "f32",
+        "data": "synthetic",
+        "config": {"workload": CASE_WORKLOAD[args.case],
                    "molecules_per_step": args.mols, "atoms_per_step": mean_atoms,
                    "resident_batches": nb, "l2": "inputs larger than L2 (distinct batches cycled)",
                    "launch": launch_mode, "streams": n_streams,
@@ -642,7 +662,7 @@ def main():
         "clocks": sampler.summary(t_load0, t_load1),
         "clocks_timed_region": sampler.summary(t_timed0, t_timed1),
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.case == "config1":
         try:
             line["cpu_baseline"] = cpu_baseline(batches[0])
         except Exception as exc:
