@@ -43,6 +43,7 @@ SIGNATURES = {
     "ani_feature_size": (_i, []),
     "ani_status_string": (ctypes.c_char_p, [_i]),
     "ani_last_cuda_error": (ctypes.c_char_p, []),
+    "ani_fma_probe": (_i, [_i, _i, _vp, ctypes.POINTER(ctypes.c_longlong), _vp]),
     "ani_device_status": (_i, [_vp]),
     "ani_sort": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
     "ani_sort_noalloc": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),

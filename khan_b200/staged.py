@@ -61,7 +61,8 @@ class StagedBatch:
         """Copies one pinned host batch in; returns the bytes moved."""
         self.set_shape(host.n_atoms, host.n_mols, host.acs)
         n, m = self.n_atoms, self.n_mols
-        self.xyz[:, :n].copy_(host.xyz[:, :n], non_blocking=non_blocking)
+        for r in range(3):   # row by row: each copy is one contiguous range on both sides
+            self.xyz[r, :n].copy_(host.xyz[r, :n], non_blocking=non_blocking)
         self.types[:n].copy_(host.types[:n], non_blocking=non_blocking)
         self.mol_offsets[:m].copy_(host.mol_offsets[:m], non_blocking=non_blocking)
         self.mol_counts[:m].copy_(host.mol_counts[:m], non_blocking=non_blocking)
@@ -70,6 +71,17 @@ class StagedBatch:
             self.upstream[:n].copy_(host.upstream[:n], non_blocking=non_blocking)
             moved += n * FEATURE_SIZE * self.upstream.element_size()
         return moved
+
+    def download(self, features_host: torch.Tensor, grads_host: torch.Tensor, non_blocking: bool = True) -> int:
+        """Copies the feature rows and the coordinate gradients of the current batch into
+        (pinned) host tensors of shape [>= n_atoms, 384] and [3, >= n_atoms]; returns the
+        bytes moved.  Every copy is one contiguous range on both sides, so none of them falls
+        back to a staged, host-blocking transfer."""
+        n = self.n_atoms
+        features_host[:n].copy_(self.features[:n], non_blocking=non_blocking)
+        for r in range(3):
+            grads_host[r, :n].copy_(self.grads[r, :n], non_blocking=non_blocking)
+        return n * (FEATURE_SIZE + 3) * self.features.element_size()
 
     # -- the hot path ----------------------------------------------------------------------
     def _element_ptrs(self, buf: torch.Tensor):
