@@ -205,6 +205,36 @@ typedef struct ani_mlp_args {
 int ani_mlp_forward_f32(const ani_mlp_args* args_host, const int* acs_host, int activation,
                         int split_precision, void* stream);
 
+/*
+ * AniCharge -- replaces the op of gpu_featurizer/ani_charges.cpp:45-56,58-113 (CPU, float and
+ * double) and gpu_featurizer/ani_charges_gpu.cu:60-128 (GPU, float only).  Damped Coulomb
+ * energy of every molecule,
+ *   charge_energies[m] = k_e * sum_{i<j in m} q_i q_j (1 - f_C(r_ij, R_Rc)) / r_ij ,
+ * k_e = 0.529176917 (gpu_featurizer/parameters.h:10).  `qs` holds one partial charge per atom.
+ * n_atoms is the length of xs/ys/zs/qs and is used only to validate the molecule table
+ * (the reference takes it from the tensor shape and does not check).
+ */
+int ani_charge_f32(const float* xs, const float* ys, const float* zs, const float* qs,
+                   const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                   float* charge_energies, void* stream);
+int ani_charge_f64(const double* xs, const double* ys, const double* zs, const double* qs,
+                   const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                   double* charge_energies, void* stream);
+
+/*
+ * AniChargeGrad -- replaces gpu_featurizer/ani_charges.cpp:123-135,138-214 and
+ * gpu_featurizer/ani_charges_gpu.cu:197-260: q_grads[i] = grads[m(i)] * dE_m/dq_i, the gradient
+ * that the reference registers for AniCharge (khan/training/trainer_multi_tower.py:94-120).
+ * q_grads (n_atoms values) is zero-filled by the call; atoms outside every molecule keep 0.
+ * Molecule ranges must not overlap (the reference would add the contributions up).
+ */
+int ani_charge_grad_f32(const float* xs, const float* ys, const float* zs, const float* qs,
+                        const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                        const float* grads, float* q_grads, void* stream);
+int ani_charge_grad_f64(const double* xs, const double* ys, const double* zs, const double* qs,
+                        const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                        const double* grads, double* q_grads, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

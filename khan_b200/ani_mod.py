@@ -235,6 +235,59 @@ def featurize_autograd(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts,
     return tuple(_split(buf, acs_host))
 
 
+def ani_charge(xs, ys, zs, qs, mol_offsets, mol_atom_counts):
+    """``ani_mod.ani_charge`` (gpu_featurizer/ani_charges.cpp:45-113): damped Coulomb energy of
+    every molecule from per-atom partial charges ``qs``; returns ``[n_mols]``."""
+    xs = _dev(xs, name="xs")
+    suf = _suffix(xs)
+    ys, zs, qs = _dev(ys, xs.dtype, "ys"), _dev(zs, xs.dtype, "zs"), _dev(qs, xs.dtype, "qs")
+    mo, mac = _dev(mol_offsets, torch.int32, "mol_offsets"), _dev(mol_atom_counts, torch.int32, "mol_atom_counts")
+    out = torch.empty(mo.numel(), dtype=xs.dtype, device=xs.device)
+    with torch.cuda.device(xs.device):
+        _lib.check(getattr(_lib.lib(), "ani_charge_" + suf)(
+            _p(xs), _p(ys), _p(zs), _p(qs), _p(mo), _p(mac), mo.numel(), xs.numel(), _p(out), _stream()),
+            "ani_charge_" + suf)
+    return out
+
+
+def ani_charge_grad(xs, ys, zs, qs, mol_offsets, mol_atom_counts, grads):
+    """``ani_mod.ani_charge_grad`` (gpu_featurizer/ani_charges.cpp:123-214): gradient with respect
+    to the charges given ``grads = dL/d(charge_energies)``; returns ``[n_atoms]``."""
+    xs = _dev(xs, name="xs")
+    suf = _suffix(xs)
+    ys, zs, qs = _dev(ys, xs.dtype, "ys"), _dev(zs, xs.dtype, "zs"), _dev(qs, xs.dtype, "qs")
+    grads = _dev(grads, xs.dtype, "grads")
+    mo, mac = _dev(mol_offsets, torch.int32, "mol_offsets"), _dev(mol_atom_counts, torch.int32, "mol_atom_counts")
+    if grads.numel() != mo.numel():
+        raise ValueError("grads must hold one value per molecule")
+    out = torch.empty(xs.numel(), dtype=xs.dtype, device=xs.device)
+    with torch.cuda.device(xs.device):
+        _lib.check(getattr(_lib.lib(), "ani_charge_grad_" + suf)(
+            _p(xs), _p(ys), _p(zs), _p(qs), _p(mo), _p(mac), mo.numel(), xs.numel(), _p(grads), _p(out),
+            _stream()), "ani_charge_grad_" + suf)
+    return out
+
+
+class _AniCharge(torch.autograd.Function):
+    """ani_charge with the gradient the reference registers for it: with respect to the
+    charges only (khan/training/trainer_multi_tower.py:94-120)."""
+
+    @staticmethod
+    def forward(ctx, xs, ys, zs, qs, mo, mac):
+        ctx.save_for_backward(xs, ys, zs, qs, mo, mac)
+        return ani_charge(xs, ys, zs, qs, mo, mac)
+
+    @staticmethod
+    def backward(ctx, grads):
+        xs, ys, zs, qs, mo, mac = ctx.saved_tensors
+        return None, None, None, ani_charge_grad(xs, ys, zs, qs, mo, mac, grads.contiguous()), None, None
+
+
+def ani_charge_autograd(xs, ys, zs, qs, mol_offsets, mol_atom_counts):
+    """ani_charge that torch.autograd can differentiate with respect to ``qs``."""
+    return _AniCharge.apply(xs, ys, zs, qs, mol_offsets, mol_atom_counts)
+
+
 def device_status() -> int:
     """Synchronise the current stream and return (and clear) the device status word."""
     return int(_lib.lib().ani_device_status(_stream()))

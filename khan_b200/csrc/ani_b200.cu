@@ -14,6 +14,7 @@
 #include "ani_grad.cuh"
 #include "ani_grad_inverse.cuh"
 #include "ani_mlp.cuh"
+#include "ani_charge.cuh"
 #include "ani_sort.cuh"
 
 namespace {
@@ -255,6 +256,53 @@ int featurize_grad_inverse_impl(const T* xs, const T* ys, const T* zs, const int
     kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, vx, vy, vz, oh, oc, on, oo,
         acs_host[0], acs_host[1], acs_host[2], acs_host[3]);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+// Grid of the one-warp-per-molecule charge kernels: every molecule gets a warp, up to 16 CTAs per SM.
+int charge_grid(int n_mols, int* grid)
+{
+    int dev = 0, sms = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    ANI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int needed = (n_mols + kNW - 1) / kNW;
+    *grid = needed < sms * 16 ? needed : sms * 16;
+    return ANI_OK;
+}
+
+template <typename T>
+int charge_impl(const T* xs, const T* ys, const T* zs, const T* qs, const int* mos, const int* macs,
+                int n_mols, int n_atoms, T* energies, void* stream)
+{
+    if (n_mols < 0 || n_atoms < 0) return ANI_ERR_BAD_SIZE;
+    if (n_mols == 0) return ANI_OK;
+    if (!mos || !macs || !energies) return ANI_ERR_NULL_POINTER;
+    if (n_atoms > 0 && (!xs || !ys || !zs || !qs)) return ANI_ERR_NULL_POINTER;
+    int grid = 0;
+    if (int rc = charge_grid(n_mols, &grid)) return rc;
+    charge_energy_kernel<T, kNW><<<grid, kNW * kWarp, 0, (cudaStream_t)stream>>>(
+        xs, ys, zs, qs, mos, macs, n_mols, n_atoms, energies);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+template <typename T>
+int charge_grad_impl(const T* xs, const T* ys, const T* zs, const T* qs, const int* mos,
+                     const int* macs, int n_mols, int n_atoms, const T* energy_grads, T* q_grads,
+                     void* stream)
+{
+    if (n_mols < 0 || n_atoms < 0) return ANI_ERR_BAD_SIZE;
+    if (n_atoms == 0) return ANI_OK;
+    if (!xs || !ys || !zs || !qs || !q_grads) return ANI_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    ANI_CUDA(cudaMemsetAsync(q_grads, 0, (size_t)n_atoms * sizeof(T), st));
+    if (n_mols == 0) return ANI_OK;
+    if (!mos || !macs || !energy_grads) return ANI_ERR_NULL_POINTER;
+    int grid = 0;
+    if (int rc = charge_grid(n_mols, &grid)) return rc;
+    charge_grad_kernel<T, kNW><<<grid, kNW * kWarp, 0, st>>>(xs, ys, zs, qs, mos, macs, n_mols, n_atoms,
+                                                             energy_grads, q_grads);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
@@ -524,6 +572,38 @@ int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activati
         case kActNormal: return mlp_launch_act<kActNormal>(p, tiles, split, st);
         default: return mlp_launch_act<kActSoftplus>(p, tiles, split, st);
     }
+}
+
+int ani_charge_f32(const float* xs, const float* ys, const float* zs, const float* qs,
+                   const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                   float* charge_energies, void* stream)
+{
+    return charge_impl<float>(xs, ys, zs, qs, mol_offsets, mol_atom_counts, n_mols, n_atoms,
+                              charge_energies, stream);
+}
+
+int ani_charge_f64(const double* xs, const double* ys, const double* zs, const double* qs,
+                   const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                   double* charge_energies, void* stream)
+{
+    return charge_impl<double>(xs, ys, zs, qs, mol_offsets, mol_atom_counts, n_mols, n_atoms,
+                               charge_energies, stream);
+}
+
+int ani_charge_grad_f32(const float* xs, const float* ys, const float* zs, const float* qs,
+                        const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                        const float* grads, float* q_grads, void* stream)
+{
+    return charge_grad_impl<float>(xs, ys, zs, qs, mol_offsets, mol_atom_counts, n_mols, n_atoms,
+                                   grads, q_grads, stream);
+}
+
+int ani_charge_grad_f64(const double* xs, const double* ys, const double* zs, const double* qs,
+                        const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
+                        const double* grads, double* q_grads, void* stream)
+{
+    return charge_grad_impl<double>(xs, ys, zs, qs, mol_offsets, mol_atom_counts, n_mols, n_atoms,
+                                    grads, q_grads, stream);
 }
 
 }  // extern "C"

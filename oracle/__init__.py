@@ -181,6 +181,28 @@ def featurize_grad_inverse(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_cou
     return outs
 
 
+def ani_charge(xs, ys, zs, qs, mol_offsets, mol_atom_counts):
+    """AniCharge (gpu_featurizer/ani_charges.cpp:58-113): damped Coulomb energy per molecule."""
+    dt = np.asarray(xs).dtype
+    xs, ys, zs, qs = (np.ascontiguousarray(v, dtype=dt) for v in (xs, ys, zs, qs))
+    mo, mac = map(_i32, (mol_offsets, mol_atom_counts))
+    out = np.zeros(mo.shape[0], dt)
+    _sym("port", "charge", dt)(_ptr(xs), _ptr(ys), _ptr(zs), _ptr(qs), _ptr(mo), _ptr(mac),
+                               ctypes.c_int(mo.shape[0]), _ptr(out))
+    return out
+
+
+def ani_charge_grad(xs, ys, zs, qs, mol_offsets, mol_atom_counts, grads):
+    """AniChargeGrad (gpu_featurizer/ani_charges.cpp:138-214): dL/dq from dL/dE per molecule."""
+    dt = np.asarray(xs).dtype
+    xs, ys, zs, qs, grads = (np.ascontiguousarray(v, dtype=dt) for v in (xs, ys, zs, qs, grads))
+    mo, mac = map(_i32, (mol_offsets, mol_atom_counts))
+    out = np.zeros(xs.shape[0], dt)
+    _sym("port", "charge_grad", dt)(_ptr(xs), _ptr(ys), _ptr(zs), _ptr(qs), _ptr(mo), _ptr(mac),
+                                    ctypes.c_int(mo.shape[0]), ctypes.c_int(xs.shape[0]), _ptr(grads), _ptr(out))
+    return out
+
+
 def count_work(xs, ys, zs, mol_offsets, mol_atom_counts):
     """(radial pairs, angular triplets) of a batch, with the forward's float comparisons."""
     xs, ys, zs = (np.ascontiguousarray(v, dtype=np.float32) for v in (xs, ys, zs))

@@ -40,6 +40,7 @@ enum {
 };
 
 /* gpu_featurizer/parameters.h:61-114 -- all single precision, also for the double build */
+static const float kChargeConstant = 0.529176917f;   /* parameters.h:10 */
 static const float kR_eta = 16.0f;
 static const float kR_Rc = 4.6f;
 static const float kA_Rc = 3.1f;

@@ -325,6 +325,67 @@ void FN(oracle_featurize_grad_inverse)(const REAL *X, const REAL *Y, const REAL 
     }
 }
 
+/*
+ * AniCharge, gpu_featurizer/ani_charges.cpp:58-71 (charge_energy) and :100-113 (the loop
+ * over molecules): damped Coulomb energy of every molecule,
+ *   E_m = sum_{i<j} k_e q_i q_j (1 - f_C(r_ij, R_Rc)) / r_ij .
+ * Types follow the C++ expression: k_e is `const float` (parameters.h:10), so
+ * k_e*q_i*q_j is evaluated in NumericType; (1 - f_C) is double, so the product, the
+ * division and the addition to the NumericType accumulator run in double and are rounded
+ * once per pair.  The reference has no golden numbers for this op (its tests check only
+ * the gradient against finite differences, gpu_featurizer/test_kernel.py:412-447).
+ */
+void FN(oracle_charge)(const REAL *X, const REAL *Y, const REAL *Z, const REAL *Q,
+                       const int *mol_offsets, const int *mol_counts, int n_mols, REAL *energies)
+{
+    for (int m = 0; m < n_mols; m++) {
+        const int n = mol_counts[m], base = mol_offsets[m];
+        REAL energy = 0;
+        for (int i = 0; i < n; i++)
+            for (int j = i + 1; j < n; j++) {
+                const REAL dx = X[base + i] - X[base + j];
+                const REAL dy = Y[base + i] - Y[base + j];
+                const REAL dz = Z[base + i] - Z[base + j];
+                const REAL r = (REAL)oracle_dist(dx, dy, dz);
+                const REAL qq = (REAL)(kChargeConstant * Q[base + i]) * Q[base + j];
+                energy = (REAL)((double)energy + (double)qq * (1 - oracle_fc(r, kR_Rc)) / (double)r);
+            }
+        energies[m] = energy;
+    }
+}
+
+/*
+ * AniChargeGrad, gpu_featurizer/ani_charges.cpp:138-160 (charge_grads) and :196-214:
+ * q_grads = dL/dq given dL/dE_m per molecule; q_grads is zero-filled first (:194).
+ * Atom i collects its j > i terms in a local NumericType accumulator that is added to
+ * q_grads[i] afterwards; atom j's share is added to q_grads[j] directly.
+ */
+void FN(oracle_charge_grad)(const REAL *X, const REAL *Y, const REAL *Z, const REAL *Q,
+                            const int *mol_offsets, const int *mol_counts, int n_mols, int n_atoms,
+                            const REAL *energy_grads, REAL *q_grads)
+{
+    memset(q_grads, 0, (size_t)n_atoms * sizeof(REAL));
+    for (int m = 0; m < n_mols; m++) {
+        const int n = mol_counts[m], base = mol_offsets[m];
+        const REAL g = energy_grads[m];
+        for (int i = 0; i < n; i++) {
+            REAL gi = 0;
+            for (int j = i + 1; j < n; j++) {
+                const REAL dx = X[base + i] - X[base + j];
+                const REAL dy = Y[base + i] - Y[base + j];
+                const REAL dz = Z[base + i] - Z[base + j];
+                const REAL r = (REAL)oracle_dist(dx, dy, dz);
+                const double damp = (1 - oracle_fc(r, kR_Rc)) / (double)r;
+                const REAL kj = (REAL)((REAL)(g * kChargeConstant) * Q[base + j]);
+                const REAL ki = (REAL)((REAL)(g * kChargeConstant) * Q[base + i]);
+                gi = (REAL)((double)gi + (double)kj * damp);
+                q_grads[base + j] = (REAL)((double)q_grads[base + j] + (double)ki * damp);
+            }
+            q_grads[base + i] += gi;
+        }
+    }
+}
+
 #undef FN
 #undef CAT
 #undef CAT_
