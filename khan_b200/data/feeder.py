@@ -1,0 +1,302 @@
+"""Packed datasets and a double-buffered, pinned batch feeder.
+
+The reference assembles every batch in Python from per-molecule arrays
+(``khan/data/dataset.py:144-183``) and pushes it through ``feed_dict`` into a TensorFlow queue
+from a submitter thread (``khan/training/trainer_multi_tower.py:749-828``); that path, not the
+featurizer, bounds its throughput.  Here
+
+* :class:`PackedDataset` concatenates the molecules ONCE into CSR form (``ptr`` + flat element
+  ids + ``[3, N]`` coordinates), so a batch is a slice (in order) or one vectorised gather
+  (shuffled) -- no per-molecule Python work per batch;
+* :class:`BatchFeeder` runs a submitter thread that writes each batch into one pinned host
+  arena and moves it to the device with ONE asynchronous copy on a copy stream, ``depth``
+  batches ahead of the consumer, handing over with CUDA events.
+
+The batch contents and their order are exactly those of ``RawDataset.iterate`` (same use of
+``numpy.random`` for the shuffle and the fuzz), which the tests check.  Without CUDA (device
+``None``) the feeder yields the host arrays, which is how the CPU tests run it.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+
+import numpy as np
+import torch
+
+_ALIGN = 256
+
+
+class PackedDataset:
+    """All molecules of a ``RawDataset`` in CSR form."""
+
+    def __init__(self, all_Xs, all_ys=None, all_grads=None, dtype=np.float32):
+        self.dtype = np.dtype(dtype)
+        n_mols = len(all_Xs)
+        self.counts = np.fromiter((len(m) for m in all_Xs), dtype=np.int64, count=n_mols)
+        self.ptr = np.zeros(n_mols + 1, np.int64)
+        np.cumsum(self.counts, out=self.ptr[1:])
+        cat = np.concatenate(all_Xs, axis=0) if n_mols else np.zeros((0, 4))
+        self.types = np.ascontiguousarray(cat[:, 0].astype(np.int32))
+        # coordinates stay in the precision they were given in; the cast to `dtype` happens per
+        # batch, after the fuzz, which is where RawDataset.iterate + the feed would round them
+        self.xyz = np.ascontiguousarray(cat[:, 1:4].T)                          # [3, N]
+        self.ys = None if all_ys is None else np.asarray(all_ys, dtype=self.dtype).reshape(n_mols)
+        if all_grads is None:
+            self.grads = None
+        else:
+            g = np.concatenate(all_grads, axis=0) if n_mols else np.zeros((0, 3))
+            self.grads = np.ascontiguousarray(g.T.astype(self.dtype))           # [3, N]
+
+    @classmethod
+    def from_raw(cls, raw, dtype=np.float32) -> "PackedDataset":
+        """Packs ``raw`` once per precision and keeps the result on the RawDataset object."""
+        cache = raw.__dict__.setdefault("_packed", {})
+        key = np.dtype(dtype).name
+        if key not in cache or cache[key][0] is not raw.all_Xs:
+            cache[key] = (raw.all_Xs, cls(raw.all_Xs, raw.all_ys, raw.all_grads, dtype))
+        return cache[key][1]
+
+    def num_mols(self) -> int:
+        return len(self.counts)
+
+    def num_batches(self, batch_size: int) -> int:
+        return -(-self.num_mols() // batch_size)
+
+    def capacity(self, batch_size: int):
+        """(atoms, molecules) that any batch of ``batch_size`` molecules fits in."""
+        k = min(batch_size, self.num_mols())
+        top = np.sort(self.counts)[-k:] if k else np.zeros(0, np.int64)
+        return int(top.sum()), k
+
+    def gather(self, picks: np.ndarray, slot: "HostSlot", fuzz=None) -> None:
+        """Writes the batch made of molecules ``picks`` (in that order) into ``slot``."""
+        counts = self.counts[picks]
+        m = len(picks)
+        n = int(counts.sum())
+        if n > slot.cap_atoms or m > slot.cap_mols:
+            raise ValueError("batch larger than the slot")
+        offsets = np.cumsum(counts) - counts
+        in_order = m > 0 and np.array_equal(picks, np.arange(picks[0], picks[0] + m))
+        if in_order:
+            src = slice(int(self.ptr[picks[0]]), int(self.ptr[picks[0]]) + n)
+        else:
+            src = np.repeat(self.ptr[picks] - offsets, counts) + np.arange(n)
+        slot.n_atoms, slot.n_mols = n, m
+        if fuzz is None:
+            slot.xyz[:, :n] = self.xyz[:, src]
+        else:   # same draw as RawDataset.iterate: uniform over an (n, 3) array
+            slot.xyz[:, :n] = self.xyz[:, src] + np.random.uniform(-fuzz, fuzz, (n, 3)).T
+        slot.types[:n] = self.types[src]
+        slot.mol_offsets[:m] = offsets
+        slot.mol_counts[:m] = counts
+        slot.mol_ids[:n] = np.repeat(np.arange(m), counts)
+        slot.has_ys = self.ys is not None
+        if slot.has_ys:
+            slot.ys[:m] = self.ys[picks]
+        slot.has_grads = self.grads is not None
+        if slot.has_grads:
+            slot.grads[:, :n] = self.grads[:, src]
+        slot.acs = np.bincount(slot.types[:n], minlength=4).astype(np.int32)
+
+
+def _layout(cap_atoms: int, cap_mols: int, itemsize: int):
+    """Byte offsets of the sections of a slot; every section starts on a 256-byte boundary."""
+    sections = [("xyz", 3 * cap_atoms * itemsize), ("grads", 3 * cap_atoms * itemsize),
+                ("ys", cap_mols * itemsize), ("mol_ids", cap_atoms * 8), ("types", cap_atoms * 4),
+                ("mol_offsets", cap_mols * 4), ("mol_counts", cap_mols * 4)]
+    table, off = {}, 0
+    for name, size in sections:
+        table[name] = (off, size)
+        off += -(-size // _ALIGN) * _ALIGN
+    return table, max(off, _ALIGN)
+
+
+class HostSlot:
+    """One batch in one (pinned, when CUDA is available) host arena, with numpy views."""
+
+    def __init__(self, cap_atoms: int, cap_mols: int, dtype, pin: bool):
+        self.cap_atoms, self.cap_mols = cap_atoms, cap_mols
+        self.np_dtype = np.dtype(dtype)
+        self.table, self.nbytes = _layout(cap_atoms, cap_mols, self.np_dtype.itemsize)
+        self.arena = torch.zeros(self.nbytes, dtype=torch.uint8)
+        if pin:
+            self.arena = self.arena.pin_memory()
+        raw = self.arena.numpy()
+
+        def view(name, dt, shape):
+            off, size = self.table[name]
+            return raw[off:off + size].view(dt).reshape(shape)
+
+        self.xyz = view("xyz", self.np_dtype, (3, cap_atoms))
+        self.grads = view("grads", self.np_dtype, (3, cap_atoms))
+        self.ys = view("ys", self.np_dtype, (cap_mols,))
+        self.mol_ids = view("mol_ids", np.int64, (cap_atoms,))
+        self.types = view("types", np.int32, (cap_atoms,))
+        self.mol_offsets = view("mol_offsets", np.int32, (cap_mols,))
+        self.mol_counts = view("mol_counts", np.int32, (cap_mols,))
+        self.n_atoms = self.n_mols = 0
+        self.has_ys = self.has_grads = False
+        self.acs = np.zeros(4, np.int32)
+
+
+class FedBatch:
+    """What the feeder hands to the consumer: tensors of one batch (device tensors when the
+    feeder has a device, host tensors otherwise) plus the host-side sizes the C ABI needs."""
+
+    def __init__(self, index: int, device, host: HostSlot, arena: torch.Tensor, ready):
+        self.index, self.device, self.ready = index, device, ready
+        n, m = host.n_atoms, host.n_mols
+        self.n_atoms, self.n_mols = n, m
+        self.acs = host.acs.copy()
+        self.offsets_host = host.mol_offsets[:m].copy()
+        self.counts_host = host.mol_counts[:m].copy()
+        tdt = torch.float32 if host.np_dtype == np.float32 else torch.float64
+
+        def view(name, dt, rows, cols, used):
+            off, size = host.table[name]
+            t = arena[off:off + size].view(dt)
+            return t.view(rows, cols)[:, :used] if rows > 1 else t[:used]
+
+        xyz = view("xyz", tdt, 3, host.cap_atoms, n)
+        self.x, self.y, self.z = xyz[0], xyz[1], xyz[2]          # each one contiguous range
+        self.types = view("types", torch.int32, 1, 0, n)
+        self.mol_offsets = view("mol_offsets", torch.int32, 1, 0, m)
+        self.mol_counts = view("mol_counts", torch.int32, 1, 0, m)
+        self.mol_ids = view("mol_ids", torch.int64, 1, 0, n)
+        self.ys = view("ys", tdt, 1, 0, m) if host.has_ys else None
+        self.grads = view("grads", tdt, 3, host.cap_atoms, n) if host.has_grads else None
+
+    def wait(self) -> None:
+        """Makes the current stream of the batch's device wait for the upload."""
+        if self.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.ready)
+
+
+class BatchFeeder:
+    """Iterates a dataset as ``FedBatch`` objects, ``depth`` batches ahead of the consumer.
+
+    ``devices``: list of CUDA devices; batch b goes to ``devices[b % len(devices)]`` (the
+    reference's round-robin over towers, ``trainer_multi_tower.py:753-767``).  ``None`` keeps the
+    batches on the host.  The consumer keeps at most ``hold`` batches alive (one per device by
+    default): advancing the iterator past that releases the oldest one, whose work must have been
+    enqueued on its device's current stream by then; :meth:`release` does it earlier.  Each
+    device has ``depth + 1`` slots, so the submitter runs up to ``depth`` batches ahead.
+    """
+
+    def __init__(self, packed: PackedDataset, batch_size: int, shuffle: bool, fuzz=None, devices=None,
+                 depth: int = 2, hold=None):
+        self.packed, self.batch_size, self.shuffle, self.fuzz = packed, batch_size, shuffle, fuzz
+        self.devices = list(devices) if devices else [None]
+        self.depth = max(1, depth)
+        self.hold = max(1, hold if hold is not None else len(self.devices))
+        cap_atoms, cap_mols = packed.capacity(batch_size)
+        cap_atoms, cap_mols = max(cap_atoms, 1), max(cap_mols, 1)
+        self._slots = []
+        for dev in self.devices:
+            ring = []
+            for _ in range(self.depth + 1):
+                host = HostSlot(cap_atoms, cap_mols, packed.dtype, pin=dev is not None)
+                arena = torch.empty(host.nbytes, dtype=torch.uint8, device=dev) if dev is not None else host.arena
+                ring.append({"host": host, "arena": arena, "consumed": None})
+            self._slots.append(ring)
+        self._copy_streams = [torch.cuda.Stream(device=d) if d is not None else None for d in self.devices]
+        self._ready = queue.Queue(maxsize=self.depth * len(self.devices))
+        self._free = [queue.Queue() for _ in self.devices]
+        for t, ring in enumerate(self._slots):
+            for s in range(len(ring)):
+                self._free[t].put(s)
+        self._error = None
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._submit, name="khan-b200-feeder", daemon=True)
+        self._started = False
+        self._finished = False
+        self._held = []
+
+    # ---- submitter thread ---------------------------------------------------------------
+    def _take_free(self, tower: int):
+        while not self._stop.is_set():
+            try:
+                return self._free[tower].get(timeout=0.1)
+            except queue.Empty:
+                continue
+        return None
+
+    def _submit(self) -> None:
+        try:
+            p = self.packed
+            perm = np.arange(p.num_mols())
+            if self.shuffle:
+                np.random.shuffle(perm)
+            for b in range(p.num_batches(self.batch_size)):
+                tower = b % len(self.devices)
+                s = self._take_free(tower)
+                if s is None:
+                    return
+                slot = self._slots[tower][s]
+                if slot["consumed"] is not None:
+                    slot["consumed"].synchronize()     # the consumer's kernels on this slot are done
+                    slot["consumed"] = None
+                picks = perm[b * self.batch_size: min((b + 1) * self.batch_size, p.num_mols())]
+                p.gather(picks, slot["host"], self.fuzz)
+                dev, ready = self.devices[tower], None
+                if dev is not None:
+                    with torch.cuda.stream(self._copy_streams[tower]):
+                        slot["arena"].copy_(slot["host"].arena, non_blocking=True)
+                        ready = torch.cuda.Event()
+                        ready.record()
+                fed = FedBatch(b, dev, slot["host"], slot["arena"], ready)
+                if dev is not None:
+                    ready.synchronize()   # the pinned arena may be rewritten only after the copy
+                self._put((tower, s, fed))
+            self._put(None)
+        except BaseException as exc:   # handed to the consumer, which re-raises it
+            self._error = exc
+            self._put(None)
+
+    def _put(self, item) -> None:
+        while not self._stop.is_set():
+            try:
+                self._ready.put(item, timeout=0.1)
+                return
+            except queue.Full:
+                continue
+
+    # ---- consumer side ------------------------------------------------------------------
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> FedBatch:
+        if self._finished:
+            raise StopIteration
+        if not self._started:
+            self._started = True
+            self._thread.start()
+        while len(self._held) >= self.hold:
+            self.release(self._held[0][2])
+        item = self._ready.get()
+        if item is None:
+            self._finished = True
+            self.close()
+            if self._error is not None:
+                raise self._error
+            raise StopIteration
+        self._held.append(item)
+        return item[2]
+
+    def release(self, fed: FedBatch) -> None:
+        """Gives the batch's buffers back to the submitter (after the work enqueued so far)."""
+        for k, (tower, s, f) in enumerate(self._held):
+            if f is fed:
+                del self._held[k]
+                if fed.device is not None:
+                    evt = torch.cuda.Event()
+                    evt.record(torch.cuda.current_stream(fed.device))
+                    self._slots[tower][s]["consumed"] = evt
+                self._free[tower].put(s)
+                return
+
+    def close(self) -> None:
+        self._stop.set()
+        if self._started and self._thread.is_alive() and threading.current_thread() is not self._thread:
+            self._thread.join(timeout=5)

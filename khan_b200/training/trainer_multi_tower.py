@@ -9,19 +9,23 @@ variable names, ``initialize``, and the optimiser recipe (Nadam 1e-3, global-nor
 accepted and ignored), a "tower" is a CUDA device of this process, and when
 ``torch.distributed`` is initialised the weight gradients are averaged over all ranks with one
 flat NCCL all-reduce instead of the reference's concat + reduce_mean on the CPU
-(``trainer_multi_tower.py:137-179``).  The learning-rate schedule of ``train()`` is host-side
-policy and is not reproduced.
+(``trainer_multi_tower.py:137-179``).  ``train()`` keeps the reference's schedule: epochs at a
+fixed batch size until the test error has not improved for ``max_local_epoch_count`` epochs, then
+reload the best weights, halve the learning rate and add 128 to the batch size.
 """
 from __future__ import annotations
 
 import os
+import time
 
 import numpy as np
 import torch
 
 from .. import ani_mod
+from ..data.feeder import BatchFeeder, PackedDataset
 from ..model import activations
 from ..model.nn import MoleculeNN
+from ..utils.helpers import ed_harder_rmse
 
 HARTREE_TO_KCAL_PER_MOL = 627.509
 
@@ -181,30 +185,24 @@ class TrainerMultiTower:
             g["lr"] = lr
 
     # ------------------------------------------------------------------ one tower, one batch
-    def _tower_forward(self, device, mol_Xs, mol_ids, need_coord_grad):
+    def _tower_forward(self, device, fed, need_coord_grad):
+        """Sort -> featurize -> atomic networks -> per-molecule sum for one fed batch
+        (``trainer_multi_tower.py:295-350``).  The inputs are already on the device (one
+        asynchronous copy by the feeder); nothing here synchronises with the host."""
         dt = self.precision
-        xyz = torch.from_numpy(np.ascontiguousarray(mol_Xs[:, 1:4].T)).to(device=device, dtype=dt)
-        x, y, z = xyz[0].contiguous(), xyz[1].contiguous(), xyz[2].contiguous()
+        fed.wait()
+        x, y, z = fed.x, fed.y, fed.z
         if need_coord_grad:
-            x.requires_grad_(True); y.requires_grad_(True); z.requires_grad_(True)
-        types_host = mol_Xs[:, 0].astype(np.int32)
-        a = torch.from_numpy(types_host).to(device)
-        ids_host = np.asarray(mol_ids, dtype=np.int64)
-        n_mols = int(ids_host[-1]) + 1 if len(ids_host) else 0
-        counts = np.bincount(ids_host, minlength=n_mols).astype(np.int32)
-        offsets = (np.cumsum(counts) - counts).astype(np.int32)   # tf.cumsum(exclusive=True)
-        mo = torch.from_numpy(offsets).to(device)
-        mac = torch.from_numpy(counts).to(device)
-        acs = np.bincount(types_host, minlength=4).astype(np.int32)   # what ani_sort returns, on the host
+            x, y, z = (c.detach().requires_grad_(True) for c in (x, y, z))
+        acs = fed.acs    # what ani_sort returns, counted on the host while the batch was packed
         with torch.cuda.device(device):
-            si, gi, _ = ani_mod.ani_sort(a)
+            si, gi, _ = ani_mod.ani_sort(fed.types)
             fn = ani_mod.featurize_sorted_autograd if need_coord_grad else ani_mod.featurize_sorted
-            feat_buf = fn(x, y, z, a, mo, mac, si, acs)   # [n_atoms, 384], H rows, C rows, N rows, O rows
-            model = self.model
-            atom_out = model.atom_outputs(feat_buf, acs, gi)
-            ids = torch.from_numpy(ids_host).to(device)
-            pred = torch.zeros(n_mols, dtype=dt, device=device).index_add_(0, ids, atom_out)
-        return dict(x=x, y=y, z=z, pred=pred, feat_buf=feat_buf, gi=gi, offsets=offsets, counts=counts)
+            feat_buf = fn(x, y, z, fed.types, fed.mol_offsets, fed.mol_counts, si, acs)   # [n_atoms, 384], H, C, N, O rows
+            atom_out = self.model.atom_outputs(feat_buf, acs, gi)
+            pred = torch.zeros(fed.n_mols, dtype=dt, device=device).index_add_(0, fed.mol_ids, atom_out)
+        return dict(x=x, y=y, z=z, pred=pred, feat_buf=feat_buf, gi=gi, offsets=fed.offsets_host,
+                    counts=fed.counts_host)
 
     # ------------------------------------------------------------------ feeding
     def feed_dataset(self, dataset, shuffle, target_ops, batch_size, fuzz=None, before_hooks=None):
@@ -216,15 +214,21 @@ class TrainerMultiTower:
         training = [n for n in names if n.startswith("train_op")]
         need_grad = bool(training) or "tower_coord_grads" in names or "tower_force_rmses" in names
         need_coord = "tower_coord_grads" in names or "tower_force_rmses" in names or "train_op_forces" in names
-        it = dataset.iterate(batch_size=batch_size, shuffle=shuffle, fuzz=fuzz)
-        b_idx = 0
+        np_dt = np.float32 if self.precision == torch.float32 else np.float64
+        it = BatchFeeder(PackedDataset.from_raw(dataset, np_dt), batch_size, shuffle, fuzz,
+                         devices=self.towers, depth=2, hold=self.num_towers)
+        try:
+            yield from self._feed_rounds(it, names, training, need_grad, need_coord, before_hooks)
+        finally:
+            it.close()
+
+    def _feed_rounds(self, it, names, training, need_grad, need_coord, before_hooks):
         done = False
         while not done:
             round_batches = []
             for _ in range(self.num_towers):
                 try:
-                    round_batches.append((b_idx, next(it)))
-                    b_idx += 1
+                    round_batches.append(next(it))
                 except StopIteration:
                     done = True
                     break
@@ -236,14 +240,14 @@ class TrainerMultiTower:
             losses = []
             ctx = torch.enable_grad() if need_grad else torch.no_grad()
             with ctx:
-                for tower, (bid, (mol_Xs, mol_ids, mol_yts, mol_grads)) in zip(self.towers, round_batches):
-                    out = self._tower_forward(tower, mol_Xs, mol_ids, need_coord)
-                    res = {"tower_bids": np.array(bid), "tower_mos": out["offsets"]}
+                for tower, fed in zip(self.towers, round_batches):
+                    out = self._tower_forward(tower, fed, need_coord)
+                    mol_yts, mol_grads = fed.ys, fed.grads
+                    res = {"tower_bids": np.array(fed.index), "tower_mos": out["offsets"]}
                     pred = out["pred"]
                     res["tower_preds"] = pred.detach().cpu().numpy()
                     if mol_yts is not None:
-                        labels = torch.as_tensor(np.asarray(mol_yts), dtype=self.precision, device=tower)
-                        l2 = (pred - labels) ** 2
+                        l2 = (pred - mol_yts) ** 2
                         res["tower_l2s"] = l2.detach().cpu().numpy()
                         res["unordered_l2s"] = res["tower_l2s"]
                         rmse = torch.sqrt(l2.mean())
@@ -256,8 +260,7 @@ class TrainerMultiTower:
                                                          retain_graph=True)
                         res["tower_coord_grads"] = [g.detach().cpu().numpy() for g in (gx, gy, gz)]
                         if mol_grads is not None:
-                            f = torch.as_tensor(np.asarray(mol_grads), dtype=self.precision, device=tower)
-                            frmse = sum(torch.sqrt(((-g - f[:, k]) ** 2).mean()) for k, g in enumerate((gx, gy, gz)))
+                            frmse = sum(torch.sqrt(((-g - mol_grads[k]) ** 2).mean()) for k, g in enumerate((gx, gy, gz)))
                             res["tower_force_rmses"] = float(frmse.detach())
                     if training and mol_yts is not None:
                         kind = training[0]
@@ -332,6 +335,68 @@ class TrainerMultiTower:
         res = list(self.feed_dataset(dataset, False, [self.unordered_l2s], batch_size))
         l2s = np.concatenate([np.concatenate(r[0]).reshape(-1) for r in res])
         return float(np.sqrt(np.mean(l2s)) * HARTREE_TO_KCAL_PER_MOL)
+
+
+    def eval_rel_rmse(self, dataset, group_ys, batch_size=1024):
+        """Conformer-group RMSE in kcal/mol; the dataset's own targets are ignored
+        (``trainer_multi_tower.py:680-702``)."""
+        return ed_harder_rmse(group_ys, self.predict(dataset, batch_size)) * HARTREE_TO_KCAL_PER_MOL
+
+    def eval_eh_rmse(self, dataset, group_ys, batch_size=1024):
+        """Old name of :meth:`eval_rel_rmse` (``trainer_multi_tower.py:704-708``)."""
+        return self.eval_rel_rmse(dataset, group_ys, batch_size)
+
+    def train(self, save_dir, rd_train, rd_test, rd_gdb11=None, eval_names=(), eval_datasets=(),
+              eval_groups=(), batch_size=1024, max_local_epoch_count=25, max_batch_size=1e4,
+              min_learning_rate=1e-7, max_global_epoch_count=1000, log=print):
+        """The reference's training schedule (``trainer_multi_tower.py:832-891``): train with the
+        exp-RMSE loss, the max-norm hook and a fuzz that shrinks with the epoch; keep the weights
+        with the best test error in ``save_dir/best.npz``; after ``max_local_epoch_count`` epochs
+        without improvement reload them, halve the learning rate and add 128 to the batch size.
+        Returns the best test error (kcal/mol)."""
+        train_ops = [self.unordered_l2s, self.train_op]
+        best = self.eval_abs_rmse(rd_test)
+        os.makedirs(save_dir, exist_ok=True)
+        best_file = os.path.join(save_dir, "best.npz")
+        self.save_numpy(best_file)
+        start = time.time()
+        while (batch_size < max_batch_size and self.learning_rate > min_learning_rate
+               and self.global_epoch_count <= max_global_epoch_count):
+            while (self.local_epoch_count < max_local_epoch_count
+                   and self.global_epoch_count <= max_global_epoch_count):
+                fuzz = max(1e-3 / (self.global_epoch_count + 1), 1e-5)
+                results = list(self.feed_dataset(rd_train, shuffle=True, target_ops=train_ops,
+                                                 batch_size=batch_size, before_hooks=self.max_norm_ops,
+                                                 fuzz=fuzz))
+                l2s = np.concatenate([np.concatenate(r[0]).reshape(-1) for r in results])
+                train_rmse = float(np.sqrt(np.mean(l2s))) * HARTREE_TO_KCAL_PER_MOL
+                test_rmse = self.eval_abs_rmse(rd_test)
+                line = (f"{save_dir} tpe: {time.time() - start:.2f}s, g-epoch {self.global_epoch_count} "
+                        f"l-epoch {self.local_epoch_count} lr {self.learning_rate:.0e} batch_size {batch_size} "
+                        f"| train/test abs rmse: {train_rmse:.2f} kcal/mol, {test_rmse:.2f} kcal/mol")
+                start = time.time()
+                if test_rmse < best:
+                    self.save_numpy(best_file)
+                    best = test_rmse
+                    self.local_epoch_count = 0
+                else:
+                    self.local_epoch_count += 1
+                self.global_epoch_count += 1
+                if rd_gdb11 is not None:
+                    line += f" | gdb11 abs rmse {self.eval_abs_rmse(rd_gdb11):.2f} kcal/mol"
+                for name, data, groups in zip(eval_names, eval_datasets, eval_groups):
+                    line += (f" | {name} abs/rel rmses {self.eval_abs_rmse(data):.2f} kcal/mol, "
+                             f"{self.eval_rel_rmse(data, groups):.2f} kcal/mol")
+                if log is not None:
+                    log(line)
+            if log is not None:
+                log("========== Decreasing learning rate, increasing batch size ==========")
+            self.load_numpy(best_file)
+            self.set_learning_rate(self.learning_rate * 0.5)
+            self.local_epoch_count = 0
+            self.global_epoch_count += 1
+            batch_size += 128
+        return best
 
 
 class TrainerMultiGPU(TrainerMultiTower):

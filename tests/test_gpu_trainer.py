@@ -101,3 +101,53 @@ def test_training_lowers_the_loss_and_checkpoint_round_trips(small_dataset, tmp_
                               activation_fn=activations.gaussian, seed=9)
     other.load_numpy(path)
     np.testing.assert_allclose(other.predict(ds, 64), tr.predict(ds, 64), rtol=0, atol=1e-6)
+
+
+def test_feeder_uploads_match_the_host_batches():
+    """The pinned arena arrives intact on the device, batch after batch, with slots reused."""
+    import torch
+    from khan_b200 import RawDataset
+    from khan_b200.data.feeder import BatchFeeder, PackedDataset
+    b = syn.config1(n_mols=50)
+    mols = b.molecules()
+    ds = RawDataset(mols, list(np.arange(len(mols), dtype=np.float64)))
+    want = list(ds.iterate(batch_size=6, shuffle=False))
+    feeder = BatchFeeder(PackedDataset.from_raw(ds, np.float32), 6, False, devices=[torch.device("cuda", 0)], depth=2)
+    n = 0
+    for fed, (mol_Xs, mol_ids, mol_yts, _) in zip(feeder, want):
+        fed.wait()
+        assert fed.x.is_cuda and fed.types.dtype == torch.int32
+        assert np.array_equal(fed.y.cpu().numpy(), mol_Xs[:, 2].astype(np.float32))
+        assert np.array_equal(fed.types.cpu().numpy(), mol_Xs[:, 0].astype(np.int32))
+        assert np.array_equal(fed.mol_ids.cpu().numpy(), mol_ids)
+        assert np.array_equal(fed.ys.cpu().numpy(), np.asarray(mol_yts, np.float32))
+        assert np.array_equal(fed.mol_offsets.cpu().numpy(), fed.offsets_host)
+        n += 1
+    assert n == len(want)
+
+
+def test_train_schedule_halves_the_rate_and_keeps_the_best_weights(tmp_path):
+    """The reference's schedule (trainer_multi_tower.py:832-891) on a toy problem: the learning
+    rate is halved and the batch size grows once an epoch budget without improvement is used
+    up, best.npz holds the weights of the best test error, and the error does not get worse."""
+    import torch
+    from khan_b200 import RawDataset, TrainerMultiTower
+    b = syn.config1(n_mols=48)
+    mols = b.molecules()
+    ys = [0.01 * len(m) for m in mols]
+    train, test = RawDataset(mols[:36], ys[:36]), RawDataset(mols[36:], ys[36:])
+    tr = TrainerMultiTower(None, [torch.device("cuda", 0)], layer_sizes=(128, 128, 64, 1), seed=3)
+    before = tr.eval_abs_rmse(test)
+    lines = []
+    best = tr.train(str(tmp_path), train, test, batch_size=16, max_local_epoch_count=2,
+                    max_batch_size=16 + 128 + 1, max_global_epoch_count=6, log=lines.append)
+    assert best <= before
+    assert (tmp_path / "best.npz").exists()
+    assert tr.global_epoch_count >= 2 and any("Decreasing learning rate" in l for l in lines)
+    assert tr.learning_rate < 1e-3
+    # the weights in best.npz reproduce the best score
+    tr2 = TrainerMultiTower(None, [torch.device("cuda", 0)], layer_sizes=(128, 128, 64, 1), seed=9)
+    tr2.load_numpy(str(tmp_path / "best.npz"))
+    assert abs(tr2.eval_abs_rmse(test) - best) < 1e-3 * max(1.0, best)
+    groups = [ys[36:42], ys[42:48]]
+    assert tr2.eval_rel_rmse(test, groups) >= 0

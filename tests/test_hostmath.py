@@ -59,3 +59,14 @@ def test_shared_math_matches_oracle(hostmath, oracle_mod, case, dt, suf, ftol, g
     for k in range(3):
         assert np.isfinite(go[k]).all()
         assert normwise(go[k], gref[k]) < gtol
+
+
+def test_ed_harder_rmse_known_answer():
+    """Two conformer groups worked by hand: group 1 true (2,1,3) / predicted (3,0,2): the lowest
+    true value is the second, so the shift is +1 and the errors are (2,0,0); group 2 true
+    (8,9,2,3) / predicted (7,8,4,1): shift -2, errors (-3,-3,0,-4).  The same example sits in
+    khan/utils/helpers.py:71-80 of the reference."""
+    import math
+    from khan_b200.utils import ed_harder_rmse
+    want = (math.sqrt(4 / 3) + math.sqrt((9 + 9 + 0 + 16) / 4)) / 2
+    assert abs(ed_harder_rmse([[2, 1, 3], [8, 9, 2, 3]], [3, 0, 2, 7, 8, 4, 1]) - want) < 1e-15
