@@ -183,7 +183,8 @@ int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const dou
  * 1 gaussian exp(-x^2), 2 normal exp(-x^2/2), 3 softplus - ln 2 (khan/model/activations.py:62-74).
  * `split_precision` != 0 splits every operand into two tf32 terms (three MMAs per product),
  * which brings the products to float32 accuracy; 0 uses plain tf32.
- * act1/act2/act3 receive the hidden activations ([acs[t]][128], [128], [64]) when non-NULL
+ * act1/act2/act3 receive the hidden activations ([acs[t]][128], [128], [64]) and
+ * dact1/dact2/dact3 the derivatives of the activation function at the same places, when non-NULL
  * (the backward pass needs them).  Pointers of an element with acs_host[t] == 0 may be NULL.
  */
 typedef struct ani_mlp_args {
@@ -200,10 +201,42 @@ typedef struct ani_mlp_args {
     float* act1[4];
     float* act2[4];
     float* act3[4];
+    float* dact1[4];      /* optional: d act / d x at the same places (the backward pass needs them) */
+    float* dact2[4];
+    float* dact3[4];
 } ani_mlp_args;
 
 int ani_mlp_forward_f32(const ani_mlp_args* args_host, const int* acs_host, int activation,
                         int split_precision, void* stream);
+
+/*
+ * Backward pass of the same four networks along the activations (float32), one launch:
+ *   dz3 = (grad_energy w4^T) * dact3,  dz2 = (dz3 W3^T) * dact2,  dz1 = (dz2 W2^T) * dact1,
+ *   grad_features = dz1 W1^T   (optional; this is the upstream of ani_featurize_grad).
+ * It takes the place of the part of tf.gradients through MoleculeNN that reaches the features
+ * (khan/model/nn.py:39-67,165-172 under khan/training/trainer_multi_tower.py:350-419).  The weight
+ * gradients follow from the outputs as plain products over the atoms of an element,
+ * dW_l = A_{l-1}^T dz_l and db_l = column sums of dz_l, and are left to the caller.
+ * Weights are passed in the reference's layout, [in][out] with `out` contiguous; dact1..3 are the
+ * arrays that ani_mlp_forward_f32 filled.  `split_precision` as in the forward call.
+ */
+typedef struct ani_mlp_backward_args {
+    const float* grad_energy[4];  /* [acs[t]] dL/dE per atom, element-sorted order */
+    const float* w1[4];           /* [384][128] */
+    const float* w2[4];           /* [128][128] */
+    const float* w3[4];           /* [128][64] */
+    const float* w4[4];           /* [64] */
+    const float* dact1[4];        /* [acs[t]][128] */
+    const float* dact2[4];        /* [acs[t]][128] */
+    const float* dact3[4];        /* [acs[t]][64] */
+    float* dz1[4];                /* [acs[t]][128] */
+    float* dz2[4];                /* [acs[t]][128] */
+    float* dz3[4];                /* [acs[t]][64] */
+    float* grad_features[4];      /* [acs[t]][384], may be NULL */
+} ani_mlp_backward_args;
+
+int ani_mlp_backward_f32(const ani_mlp_backward_args* args_host, const int* acs_host,
+                         int split_precision, void* stream);
 
 /*
  * AniCharge -- replaces the op of gpu_featurizer/ani_charges.cpp:45-56,58-113 (CPU, float and

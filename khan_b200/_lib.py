@@ -18,7 +18,7 @@ CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
 HEADERS = ["ani_params.h", "ani_common.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_grad.cuh",
-           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_charge.cuh"]
+           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_backward.cuh", "ani_charge.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -33,9 +33,17 @@ _vp = ctypes.c_void_p
 _i = ctypes.c_int
 
 class MlpArgs(ctypes.Structure):
-    """``ani_mlp_args`` of include/ani_b200.h: thirteen arrays of four device pointers."""
+    """``ani_mlp_args`` of include/ani_b200.h: sixteen arrays of four device pointers."""
     _fields_ = [(name, ctypes.c_void_p * 4) for name in (
-        "features", "w1t", "b1", "w2t", "b2", "w3t", "b3", "w4", "b4", "energy", "act1", "act2", "act3")]
+        "features", "w1t", "b1", "w2t", "b2", "w3t", "b3", "w4", "b4", "energy", "act1", "act2", "act3",
+        "dact1", "dact2", "dact3")]
+
+
+class MlpBackwardArgs(ctypes.Structure):
+    """``ani_mlp_backward_args`` of include/ani_b200.h."""
+    _fields_ = [(name, ctypes.c_void_p * 4) for name in (
+        "grad_energy", "w1", "w2", "w3", "w4", "dact1", "dact2", "dact3", "dz1", "dz2", "dz3",
+        "grad_features")]
 
 
 # name -> (restype, argtypes); one entry per declaration in include/ani_b200.h
@@ -54,6 +62,7 @@ SIGNATURES = {
     "ani_featurize_grad_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
     "ani_featurize_grad_inverse_f32": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
     "ani_featurize_grad_inverse_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
+    "ani_mlp_backward_f32": (_i, [ctypes.POINTER(MlpBackwardArgs), c_int_p, _i, _vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_f64": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_grad_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp, _vp]),

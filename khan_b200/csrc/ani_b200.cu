@@ -14,6 +14,7 @@
 #include "ani_grad.cuh"
 #include "ani_grad_inverse.cuh"
 #include "ani_mlp.cuh"
+#include "ani_mlp_backward.cuh"
 #include "ani_charge.cuh"
 #include "ani_sort.cuh"
 
@@ -323,6 +324,22 @@ template <int ACT, bool SPLIT> int mlp_launch(const MlpParams& p, int n_tiles, c
     return ANI_OK;
 }
 
+template <bool SPLIT> int mlp_backward_launch(const MlpBackwardParams& p, int n_tiles, cudaStream_t st)
+{
+    auto kernel = mlp_backward_kernel<SPLIT>;
+    const size_t smem = sizeof(MlpShared) + 1024;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        if (int rc = set_smem(kernel, smem)) return rc;
+        configured_dev = dev;
+    }
+    kernel<<<n_tiles, kMlpTile, smem, st>>>(p);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
 template <int ACT> int mlp_launch_act(const MlpParams& p, int n_tiles, bool split, cudaStream_t st)
 {
     return split ? mlp_launch<ACT, true>(p, n_tiles, st) : mlp_launch<ACT, false>(p, n_tiles, st);
@@ -562,6 +579,7 @@ int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activati
         p.w4[t] = a->w4[t];   p.b4[t] = a->b4[t];
         p.energy[t] = a->energy[t];
         p.act1[t] = a->act1[t]; p.act2[t] = a->act2[t]; p.act3[t] = a->act3[t];
+        p.dact1[t] = a->dact1[t]; p.dact2[t] = a->dact2[t]; p.dact3[t] = a->dact3[t];
     }
     p.tile_start[kTypes] = tiles;
     cudaStream_t st = (cudaStream_t)stream;
@@ -572,6 +590,34 @@ int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activati
         case kActNormal: return mlp_launch_act<kActNormal>(p, tiles, split, st);
         default: return mlp_launch_act<kActSoftplus>(p, tiles, split, st);
     }
+}
+
+int ani_mlp_backward_f32(const ani_mlp_backward_args* a, const int* acs_host, int split_precision,
+                         void* stream)
+{
+    long long n_atoms = 0;
+    if (!a) return ANI_ERR_NULL_POINTER;
+    if (int rc = check_acs(acs_host, &n_atoms)) return rc;
+    if (n_atoms == 0) return ANI_OK;
+    MlpBackwardParams p;
+    int tiles = 0;
+    for (int t = 0; t < kTypes; t++) {
+        p.tile_start[t] = tiles;
+        p.count[t] = acs_host[t];
+        tiles += (acs_host[t] + kMlpTile - 1) / kMlpTile;
+        if (acs_host[t] > 0 && (!a->grad_energy[t] || !a->w1[t] || !a->w2[t] || !a->w3[t] || !a->w4[t] ||
+                                !a->dact1[t] || !a->dact2[t] || !a->dact3[t] || !a->dz1[t] || !a->dz2[t] ||
+                                !a->dz3[t]))
+            return ANI_ERR_NULL_POINTER;
+        p.grad_energy[t] = a->grad_energy[t];
+        p.w1[t] = a->w1[t]; p.w2[t] = a->w2[t]; p.w3[t] = a->w3[t]; p.w4[t] = a->w4[t];
+        p.dact1[t] = a->dact1[t]; p.dact2[t] = a->dact2[t]; p.dact3[t] = a->dact3[t];
+        p.dz1[t] = a->dz1[t]; p.dz2[t] = a->dz2[t]; p.dz3[t] = a->dz3[t];
+        p.grad_feat[t] = a->grad_features[t];
+    }
+    p.tile_start[kTypes] = tiles;
+    cudaStream_t st = (cudaStream_t)stream;
+    return split_precision ? mlp_backward_launch<true>(p, tiles, st) : mlp_backward_launch<false>(p, tiles, st);
 }
 
 int ani_charge_f32(const float* xs, const float* ys, const float* zs, const float* qs,

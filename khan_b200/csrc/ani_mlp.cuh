@@ -55,6 +55,9 @@ struct MlpParams {
     float* act1[kTypes];         // optional [count][128] (saved for the backward pass)
     float* act2[kTypes];         // optional [count][128]
     float* act3[kTypes];         // optional [count][64]
+    float* dact1[kTypes];        // optional [count][128]: derivative of the activation at the same place
+    float* dact2[kTypes];        // optional [count][128]
+    float* dact3[kTypes];        // optional [count][64]
 };
 
 struct MlpShared {
@@ -174,6 +177,15 @@ template <int ACT> __device__ __forceinline__ float mlp_activation(float x)
     return (x > 20.0f ? x : log1pf(expf(x))) - 0.69314718056f;                      // activations.py:73-74
 }
 
+// d act / d x from the pre-activation x and the activation value a = act(x).
+template <int ACT> __device__ __forceinline__ float mlp_activation_grad(float x, float a)
+{
+    if (ACT == kActCelu) return x >= 0.0f ? 1.0f : a * 10.0f + 1.0f;   // exp(x / 0.1)
+    if (ACT == kActGaussian) return -2.0f * x * a;
+    if (ACT == kActNormal) return -x * a;
+    return 1.0f / (1.0f + expf(-x));
+}
+
 // Position of element (row, k) of a staged chunk in the core-matrix layout, in bytes.
 __device__ __forceinline__ int operand_offset(int row, int k)
 {
@@ -209,6 +221,22 @@ __device__ __forceinline__ void staging_slot(int it, int tid, int* row, int* kgr
     *kgroup = (rest & 3) * 4 + ((q >> 3) & 3);
 }
 
+// 32 consecutive floats of one row, as eight 16-byte accesses.
+__device__ __forceinline__ void store_row32(float* dst, const float* v)
+{
+#pragma unroll
+    for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+}
+__device__ __forceinline__ void load_row32(const float* src, float* v)
+{
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(src + i);
+        v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
+    }
+}
+
 template <int ACT, bool SPLIT>
 __global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p)
 {
@@ -239,6 +267,7 @@ __global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p
     const float* layer_w[3] = {p.w1t[e], p.w2t[e], p.w3t[e]};
     const float* layer_b[3] = {p.b1[e], p.b2[e], p.b3[e]};
     float* layer_out[3] = {p.act1[e], p.act2[e], p.act3[e]};
+    float* layer_dout[3] = {p.dact1[e], p.dact2[e], p.dact3[e]};
     const int layer_k[3] = {kMlpIn, kMlpH1, kMlpH2};
     const int layer_n[3] = {kMlpH1, kMlpH2, kMlpH3};
     float h3[kMlpH3];   // activations of the last hidden layer, this thread's atom
@@ -298,34 +327,31 @@ __global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p
         const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
         if (layer < 2) {
             for (int c0 = 0; c0 < N; c0 += 32) {
-                float v[32];
+                float v[32], d[32];
                 tmem_load32(lane_addr + c0, v);
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
-                    v[i] = mlp_activation<ACT>(v[i] + layer_b[layer][c0 + i]);
+                    const float x = v[i] + layer_b[layer][c0 + i];
+                    v[i] = mlp_activation<ACT>(x);
+                    d[i] = mlp_activation_grad<ACT>(x, v[i]);
                     sh.act[tid * kMlpActStride + c0 + i] = v[i];
                 }
-                if (layer_out[layer] && tid < n_rows) {
-                    float* dst = layer_out[layer] + (size_t)(row0 + tid) * N + c0;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                }
+                if (layer_out[layer] && tid < n_rows) store_row32(layer_out[layer] + (size_t)(row0 + tid) * N + c0, v);
+                if (layer_dout[layer] && tid < n_rows) store_row32(layer_dout[layer] + (size_t)(row0 + tid) * N + c0, d);
             }
         } else {
 #pragma unroll
             for (int c0 = 0; c0 < kMlpH3; c0 += 32) {
-                float v[32];
+                float v[32], d[32];
                 tmem_load32(lane_addr + c0, v);
 #pragma unroll
-                for (int i = 0; i < 32; i++) h3[c0 + i] = mlp_activation<ACT>(v[i] + layer_b[2][c0 + i]);
-                if (layer_out[2] && tid < n_rows) {
-                    float* dst = layer_out[2] + (size_t)(row0 + tid) * kMlpH3 + c0;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<float4*>(dst + i) =
-                            make_float4(h3[c0 + i], h3[c0 + i + 1], h3[c0 + i + 2], h3[c0 + i + 3]);
+                for (int i = 0; i < 32; i++) {
+                    const float x = v[i] + layer_b[2][c0 + i];
+                    h3[c0 + i] = mlp_activation<ACT>(x);
+                    d[i] = mlp_activation_grad<ACT>(x, h3[c0 + i]);
                 }
+                if (layer_out[2] && tid < n_rows) store_row32(layer_out[2] + (size_t)(row0 + tid) * kMlpH3 + c0, h3 + c0);
+                if (layer_dout[2] && tid < n_rows) store_row32(layer_dout[2] + (size_t)(row0 + tid) * kMlpH3 + c0, d);
             }
         }
         tc_fence_before();

@@ -1,0 +1,181 @@
+// Per-element atomic network 384-128-128-64-1, backward pass along the activations, fused into
+// one kernel on the Blackwell tensor cores (same machinery as ani_mlp.cuh).
+//
+// Given g = dL/dE per atom and the activation derivatives D1, D2, D3 that the forward kernel
+// saved, a CTA computes for its tile of 128 atoms of one element
+//   dZ3 = (g w4^T) * D3                       (registers, thread = atom)
+//   dZ2 = (dZ3 W3^T) * D2                     (MMA  M=128 N=128 K=64)
+//   dZ1 = (dZ2 W2^T) * D1                     (MMA  M=128 N=128 K=128)
+//   dF  =  dZ1 W1^T                           (MMA  M=128 N=3x128 K=128)
+// and writes dZ1, dZ2, dZ3 (what the weight gradients A_{l-1}^T dZ_l need; those are plain
+// GEMMs over all atoms of the element and are left to the caller) and dF = dL/d(features), the
+// upstream of featurize_grad.  This is the part of the reference's tf.gradients through
+// MoleculeNN (khan/model/nn.py:39-67,165-172; khan/training/trainer_multi_tower.py:350-419)
+// that feeds the coordinate gradients.
+//
+// The weights are read in the reference's own layout W = [in][out]: for dA = dZ W^T the MMA's
+// B operand is [N = in][K = out], which is W as stored.
+#pragma once
+
+#include "ani_mlp.cuh"
+
+namespace ani {
+
+struct MlpBackwardParams {
+    const float* grad_energy[kTypes];   // [count]
+    int count[kTypes];
+    int tile_start[kTypes + 1];
+    const float* w1[kTypes];     // [384][128]
+    const float* w2[kTypes];     // [128][128]
+    const float* w3[kTypes];     // [128][64]
+    const float* w4[kTypes];     // [64]
+    const float* dact1[kTypes];  // [count][128]
+    const float* dact2[kTypes];  // [count][128]
+    const float* dact3[kTypes];  // [count][64]
+    float* dz1[kTypes];          // [count][128]
+    float* dz2[kTypes];          // [count][128]
+    float* dz3[kTypes];          // [count][64]
+    float* grad_feat[kTypes];    // optional [count][384]
+};
+
+// One product  acc[128 x N] = A[128 x K] * B^T  with A in sh.act (row stride kMlpActStride) and
+// B = w[(n0 + n) * ldw + k] in global memory, K a multiple of 64.  Returns false on timeout.
+template <bool SPLIT>
+__device__ __forceinline__ bool mlp_product(MlpShared& sh, unsigned tmem, const float* __restrict__ w, int ldw,
+                                            int n0, int N, int K, unsigned* parity)
+{
+    const int tid = threadIdx.x;
+    const unsigned idesc = instr_desc(kMlpTile, N);
+    bool ok = true;
+#pragma unroll 1
+    for (int kc = 0; kc < K; kc += kMlpKChunk) {
+        for (int it = 0; it < kMlpKChunk / 4; it++) {
+            int row, kg;
+            staging_slot(it, tid, &row, &kg);
+            const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
+            stage4<SPLIT>(sh.a_hi, sh.a_lo, row, kg * 4, make_float4(src[0], src[1], src[2], src[3]));
+            if (row < N) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + (size_t)(n0 + row) * ldw + kc + kg * 4);
+                stage4<SPLIT>(sh.b_hi, sh.b_lo, row, kg * 4, wv);
+            }
+        }
+        fence_async_smem();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const unsigned a_hi = smem_u32(sh.a_hi), b_hi = smem_u32(sh.b_hi);
+            const unsigned a_lo = smem_u32(sh.a_lo), b_lo = smem_u32(sh.b_lo);
+#pragma unroll
+            for (int ks = 0; ks < kMlpKChunk / 8; ks++) {
+                const unsigned step = ks * 2 * kMlpLbo;
+                const bool first = kc == 0 && ks == 0;
+                mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_hi + step), idesc, !first);
+                if (SPLIT) {
+                    mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_lo + step), idesc, true);
+                    mma_tf32(tmem, smem_desc(a_lo + step), smem_desc(b_hi + step), idesc, true);
+                }
+            }
+            mma_commit(&sh.mbar);
+        }
+        if (ok && !mbar_wait(&sh.mbar, *parity)) ok = false;
+        *parity ^= 1u;
+        if (!ok) sh.failed = 1;
+        __syncthreads();
+        if (sh.failed) return false;
+    }
+    tc_fence_after();
+    return true;
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(kMlpTile) mlp_backward_kernel(const MlpBackwardParams p)
+{
+    extern __shared__ unsigned char mlp_smem_raw[];
+    MlpShared& sh = *reinterpret_cast<MlpShared*>(
+        (reinterpret_cast<uintptr_t>(mlp_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5;
+
+    int e = 0;
+#pragma unroll
+    for (int t = 1; t < kTypes; t++) e += (int)blockIdx.x >= p.tile_start[t] ? 1 : 0;
+    const int row0 = ((int)blockIdx.x - p.tile_start[e]) * kMlpTile;
+    const int n_rows = min(kMlpTile, p.count[e] - row0);
+    const bool live = tid < n_rows;
+    const size_t atom = (size_t)(row0 + tid);
+
+    if (warp == 0) tmem_alloc(&sh.tmem_base, kMlpTmemCols);
+    if (tid == 0) {
+        mbar_init(&sh.mbar, 1);
+        sh.failed = 0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = sh.tmem_base;
+    const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+    unsigned parity = 0;
+
+    // ---- dZ3 = g * w4 * D3, thread = atom; rows past the end of the element are zero ----
+    {
+        const float g = live ? p.grad_energy[e][atom] : 0.0f;
+#pragma unroll
+        for (int c0 = 0; c0 < kMlpH3; c0 += 32) {
+            float d[32], v[32];
+            if (live) load_row32(p.dact3[e] + atom * kMlpH3 + c0, d);
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                v[i] = live ? g * p.w4[e][c0 + i] * d[i] : 0.0f;
+                sh.act[tid * kMlpActStride + c0 + i] = v[i];
+            }
+            if (live) store_row32(p.dz3[e] + atom * kMlpH3 + c0, v);
+        }
+    }
+    __syncthreads();
+
+    // ---- dZ2 = (dZ3 W3^T) * D2 and dZ1 = (dZ2 W2^T) * D1 ----
+    const float* step_w[2] = {p.w3[e], p.w2[e]};
+    const float* step_d[2] = {p.dact2[e], p.dact1[e]};
+    float* step_out[2] = {p.dz2[e], p.dz1[e]};
+    const int step_k[2] = {kMlpH3, kMlpH2};
+    bool ok = true;
+#pragma unroll 1
+    for (int s = 0; s < 2 && ok; s++) {
+        ok = mlp_product<SPLIT>(sh, tmem, step_w[s], step_k[s], 0, 128, step_k[s], &parity);
+        if (!ok) break;
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+            float v[32], d[32];
+            tmem_load32(lane_addr + c0, v);
+            if (live) load_row32(step_d[s] + atom * 128 + c0, d);
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                v[i] = live ? v[i] * d[i] : 0.0f;
+                sh.act[tid * kMlpActStride + c0 + i] = v[i];
+            }
+            if (live) store_row32(step_out[s] + atom * 128 + c0, v);
+        }
+        tc_fence_before();
+        __syncthreads();
+    }
+
+    // ---- dF = dZ1 W1^T, 128 feature columns at a time ----
+    if (ok && p.grad_feat[e]) {
+#pragma unroll 1
+        for (int n0 = 0; n0 < kMlpIn && ok; n0 += 128) {
+            ok = mlp_product<SPLIT>(sh, tmem, p.w1[e], kMlpH1, n0, 128, kMlpH1, &parity);
+            if (!ok) break;
+            for (int c0 = 0; c0 < 128; c0 += 32) {
+                float v[32];
+                tmem_load32(lane_addr + c0, v);
+                if (live) store_row32(p.grad_feat[e] + atom * kMlpIn + n0 + c0, v);
+            }
+            tc_fence_before();
+            __syncthreads();   // the accumulator is overwritten by the next product
+        }
+    }
+
+    if (sh.failed && tid == 0) report(ANI_ERR_TIMEOUT);
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kMlpTmemCols);
+}
+
+}  // namespace ani

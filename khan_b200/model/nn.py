@@ -69,9 +69,27 @@ class AtomNN:
         return a.reshape(-1)
 
 
+def _dense_energies(features, acs, act_fn, params):
+    """The four networks in plain differentiable torch ops (element-sorted rows in and out)."""
+    starts = np.concatenate([[0], np.cumsum(acs)])
+    parts = []
+    for t in range(4):
+        a = features[int(starts[t]):int(starts[t + 1])]
+        w1, b1, w2, b2, w3, b3, w4, b4 = params[8 * t: 8 * t + 8]
+        a = act_fn(a @ w1 + b1)
+        a = act_fn(a @ w2 + b2)
+        a = act_fn(a @ w3 + b3)
+        parts.append((a @ w4 + b4).reshape(-1))
+    return torch.cat(parts)
+
+
 class _FusedMlp(torch.autograd.Function):
-    """Forward of the four atomic networks in one tensor-core kernel; backward in dense torch ops
-    from the hidden activations the kernel saved."""
+    """The four atomic networks on the tensor-core kernels: one launch forward
+    (``ani_mlp_forward_f32``), one launch for the backward pass along the activations
+    (``ani_mlp_backward_f32``: dz1, dz2, dz3 and the feature gradient); the weight gradients are
+    the plain products ``A_{l-1}^T dz_l`` over the atoms of each element.  When the backward pass
+    itself has to be differentiated (force training, ``create_graph=True``) it is evaluated in
+    dense differentiable torch ops instead."""
 
     @staticmethod
     def forward(ctx, features, acs, act_id, split, act_fn, *params):
@@ -79,10 +97,10 @@ class _FusedMlp(torch.autograd.Function):
         n = features.shape[0]
         dev = features.device
         starts = np.concatenate([[0], np.cumsum(acs)])
-        energy = torch.empty(n, dtype=torch.float32, device=dev)
-        a1 = torch.empty((n, 128), dtype=torch.float32, device=dev)
-        a2 = torch.empty((n, 128), dtype=torch.float32, device=dev)
-        a3 = torch.empty((n, 64), dtype=torch.float32, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        energy = torch.empty(n, **f32)
+        acts = [torch.empty((n, 128), **f32), torch.empty((n, 128), **f32), torch.empty((n, 64), **f32)]
+        dacts = [torch.empty((n, 128), **f32), torch.empty((n, 128), **f32), torch.empty((n, 64), **f32)]
         args = _lib.MlpArgs()
         keep = []
         for t in range(4):
@@ -100,51 +118,75 @@ class _FusedMlp(torch.autograd.Function):
             args.w1t[t], args.w2t[t], args.w3t[t], args.w4[t] = (ptr(x) for x in tr)
             args.b1[t], args.b2[t], args.b3[t], args.b4[t] = (ptr(b.detach()) for b in (b1, b2, b3, b4))
             args.energy[t] = ptr(energy, s)
-            args.act1[t], args.act2[t], args.act3[t] = ptr(a1, s * 128), ptr(a2, s * 128), ptr(a3, s * 64)
+            args.act1[t], args.act2[t], args.act3[t] = (ptr(a, s * a.shape[1]) for a in acts)
+            args.dact1[t], args.dact2[t], args.dact3[t] = (ptr(d, s * d.shape[1]) for d in dacts)
         acs_arr = np.ascontiguousarray(np.asarray(acs, dtype=np.int32))
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().ani_mlp_forward_f32(ctypes.byref(args), acs_arr.ctypes.data_as(_lib.c_int_p),
                                                       int(act_id), int(bool(split)), stream),
                        "ani_mlp_forward_f32")
-        ctx.save_for_backward(features, a1, a2, a3, *params)
-        ctx.acs, ctx.act_fn = acs_arr, act_fn
+        ctx.save_for_backward(features, *acts, *dacts, *params)
+        ctx.acs, ctx.act_fn, ctx.split = acs_arr, act_fn, bool(split)
         return energy
 
     @staticmethod
     def backward(ctx, grad_energy):
-        features, a1, a2, a3, *params = ctx.saved_tensors
+        features, a1, a2, a3, d1, d2, d3, *params = ctx.saved_tensors
         acs, act_fn = ctx.acs, ctx.act_fn
+        if torch.is_grad_enabled():
+            # double backward: everything from differentiable ops so that the second derivative
+            # through the activation is kept
+            with torch.enable_grad():
+                inputs = [features] + list(params)
+                wanted = [k for k, need in enumerate([ctx.needs_input_grad[0]] + list(ctx.needs_input_grad[5:])) if need]
+                energy = _dense_energies(features, acs, act_fn, params)
+                got = torch.autograd.grad(energy, [inputs[k] for k in wanted], grad_energy, create_graph=True,
+                                          allow_unused=True)
+            out = [None] * len(inputs)
+            for k, g in zip(wanted, got):
+                out[k] = g
+            return (out[0], None, None, None, None, *out[1:])
+        n = features.shape[0]
+        dev = features.device
         starts = np.concatenate([[0], np.cumsum(acs)])
-        grad_feat = torch.zeros_like(features) if ctx.needs_input_grad[0] else None
+        f32 = dict(dtype=torch.float32, device=dev)
+        dz1, dz2, dz3 = torch.empty((n, 128), **f32), torch.empty((n, 128), **f32), torch.empty((n, 64), **f32)
+        grad_feat = torch.empty_like(features) if ctx.needs_input_grad[0] else None
+        g = grad_energy.contiguous()
+        args = _lib.MlpBackwardArgs()
+        keep = []
+        for t in range(4):
+            s, cnt = int(starts[t]), int(acs[t])
+            w1, _, w2, _, w3, _, w4, _ = params[8 * t: 8 * t + 8]
+            ws = [w1.detach().contiguous(), w2.detach().contiguous(), w3.detach().contiguous(),
+                  w4.detach().reshape(-1).contiguous()]
+            keep.extend(ws)
+
+            def ptr(tensor, offset=0, live=cnt > 0):
+                return ctypes.c_void_p(tensor.data_ptr() + offset * tensor.element_size()) if live else None
+
+            args.grad_energy[t] = ptr(g, s)
+            args.w1[t], args.w2[t], args.w3[t], args.w4[t] = (ptr(x) for x in ws)
+            args.dact1[t], args.dact2[t], args.dact3[t] = ptr(d1, s * 128), ptr(d2, s * 128), ptr(d3, s * 64)
+            args.dz1[t], args.dz2[t], args.dz3[t] = ptr(dz1, s * 128), ptr(dz2, s * 128), ptr(dz3, s * 64)
+            args.grad_features[t] = ptr(grad_feat, s * 384) if grad_feat is not None else None
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().ani_mlp_backward_f32(ctypes.byref(args), acs.ctypes.data_as(_lib.c_int_p),
+                                                       int(ctx.split), stream), "ani_mlp_backward_f32")
         grads = [None] * len(params)
         for t in range(4):
             s, e = int(starts[t]), int(starts[t + 1])
             if e == s:
                 continue
-            w1, b1, w2, b2, w3, b3, w4, b4 = params[8 * t: 8 * t + 8]
-            f, h1, h2, h3 = features[s:e], a1[s:e], a2[s:e], a3[s:e]
-            g = grad_energy[s:e].reshape(-1, 1)
-            with torch.enable_grad():
-                # derivative of the activation from its output's pre-image: recompute the
-                # pre-activations with dense products (cheap next to the featurizer)
-                z1 = (f @ w1 + b1).detach().requires_grad_(True)
-                z2 = (h1 @ w2 + b2).detach().requires_grad_(True)
-                z3 = (h2 @ w3 + b3).detach().requires_grad_(True)
-                d1 = torch.autograd.grad(act_fn(z1).sum(), z1)[0]
-                d2 = torch.autograd.grad(act_fn(z2).sum(), z2)[0]
-                d3 = torch.autograd.grad(act_fn(z3).sum(), z3)[0]
-            gw4 = h3.t() @ g
-            gb4 = g.sum(0)
-            gz3 = (g @ w4.t()) * d3
-            gw3, gb3 = h2.t() @ gz3, gz3.sum(0)
-            gz2 = (gz3 @ w3.t()) * d2
-            gw2, gb2 = h1.t() @ gz2, gz2.sum(0)
-            gz1 = (gz2 @ w2.t()) * d1
-            gw1, gb1 = f.t() @ gz1, gz1.sum(0)
-            grads[8 * t: 8 * t + 8] = [gw1, gb1, gw2, gb2, gw3, gb3, gw4, gb4.reshape(b4.shape)]
-            if grad_feat is not None:
-                grad_feat[s:e] = gz1 @ w1.t()
+            b4 = params[8 * t + 7]
+            ge = g[s:e]
+            grads[8 * t: 8 * t + 8] = [
+                features[s:e].t() @ dz1[s:e], dz1[s:e].sum(0),
+                a1[s:e].t() @ dz2[s:e], dz2[s:e].sum(0),
+                a2[s:e].t() @ dz3[s:e], dz3[s:e].sum(0),
+                a3[s:e].t() @ ge.reshape(-1, 1), ge.sum().reshape(b4.shape)]
         return (grad_feat, None, None, None, None, *grads)
 
 
