@@ -259,7 +259,8 @@ def run_train_workload(args):
         dist.init_process_group("nccl", device_id=dev)
     model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=1, init="he")
     params = model.get_parameters()
-    opt = torch.optim.NAdam(params, lr=1e-3, capturable=True)
+    from khan_b200.training.optim import FlatNadam
+    opt = FlatNadam(params, lr=1e-3, clip_norm=5.0)    # flat buffers: clip + Nadam + moving average in one call
     nb = max(1, min(8, args.steps))
     staged = []
     for k, b in enumerate(syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)):
@@ -284,12 +285,11 @@ def run_train_workload(args):
         return loss
 
     def update():
-        torch.nn.utils.clip_grad_norm_(params, 5.0)
         opt.step()
 
     def step(sb):
         loss = forward_backward(sb)
-        average_gradients(params)            # one flat NCCL all-reduce (no-op on one GPU)
+        average_gradients(params, opt.flat_grads)   # one NCCL all-reduce of the gradient buffer (no-op on one GPU)
         update()
         return loss
 
@@ -333,7 +333,7 @@ def run_train_workload(args):
     for k in range(args.steps):
         if fb_graphs is not None:
             fb_graphs[k % nb].replay()
-            average_gradients(params)
+            average_gradients(params, opt.flat_grads)
             up_graph.replay()
             loss = losses[k % nb]
         else:

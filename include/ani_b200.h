@@ -239,6 +239,22 @@ int ani_mlp_backward_f32(const ani_mlp_backward_args* args_host, const int* acs_
                          int split_precision, void* stream);
 
 /*
+ * One optimiser step over a flat float32 weight buffer, two launches: global-norm clipping,
+ * Adam with Nesterov momentum, and the exponential moving average of the weights.  It takes the
+ * place of tf.clip_by_global_norm + NadamOptimizer.apply_gradients +
+ * ExponentialMovingAverage.apply of khan/training/trainer_multi_tower.py:261-266,421-427:
+ *   g <- g * c / max(||g||, c);  m <- b1 m + (1-b1) g;  v <- b2 v + (1-b2) g^2;
+ *   w <- w - lr sqrt(1-b2^t)/(1-b1^t) (b1 m + (1-b1) g) / (sqrt(v) + eps);
+ *   ema <- ema - (1-d)(ema - w),  d = min(ema_decay, (1+t)/(10+t)),   t = steps so far + 1.
+ * `hyper` is DEVICE memory, six floats {lr, beta1, beta2, eps, clip_norm, ema_decay}
+ * (clip_norm <= 0 disables clipping); `state` is 32 bytes of DEVICE memory that the caller
+ * zero-fills once (step counter and scratch; the step counter is its first int).  `ema` may be
+ * NULL.  Nothing is read on the host, so the call can be captured into a CUDA graph.
+ */
+int ani_nadam_step_f32(float* params, const float* grads, float* m, float* v, float* ema,
+                       long long n, const float* hyper, void* state, void* stream);
+
+/*
  * AniCharge -- replaces the op of gpu_featurizer/ani_charges.cpp:45-56,58-113 (CPU, float and
  * double) and gpu_featurizer/ani_charges_gpu.cu:60-128 (GPU, float only).  Damped Coulomb
  * energy of every molecule,

@@ -16,6 +16,7 @@
 #include "ani_mlp.cuh"
 #include "ani_mlp_backward.cuh"
 #include "ani_charge.cuh"
+#include "ani_optim.cuh"
 #include "ani_sort.cuh"
 
 namespace {
@@ -618,6 +619,26 @@ int ani_mlp_backward_f32(const ani_mlp_backward_args* a, const int* acs_host, in
     p.tile_start[kTypes] = tiles;
     cudaStream_t st = (cudaStream_t)stream;
     return split_precision ? mlp_backward_launch<true>(p, tiles, st) : mlp_backward_launch<false>(p, tiles, st);
+}
+
+int ani_nadam_step_f32(float* params, const float* grads, float* m, float* v, float* ema,
+                       long long n, const float* hyper, void* state, void* stream)
+{
+    if (n < 0) return ANI_ERR_BAD_SIZE;
+    if (n == 0) return ANI_OK;
+    if (!params || !grads || !m || !v || !hyper || !state) return ANI_ERR_NULL_POINTER;
+    int dev = 0, sms = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    ANI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long want = (n + 4 * kOptimThreads - 1) / (4 * kOptimThreads);
+    const int grid = (int)(want < (long long)sms * 4 ? want : (long long)sms * 4);
+    cudaStream_t st = (cudaStream_t)stream;
+    grad_sumsq_kernel<<<grid, kOptimThreads, 0, st>>>(grads, n, (OptimState*)state);
+    ANI_CUDA(cudaGetLastError());
+    nadam_update_kernel<<<grid, kOptimThreads, 0, st>>>(params, grads, m, v, ema, n, (const OptimHyper*)hyper,
+                                                        (OptimState*)state);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
 }
 
 int ani_charge_f32(const float* xs, const float* ys, const float* zs, const float* qs,

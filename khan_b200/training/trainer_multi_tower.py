@@ -26,6 +26,7 @@ from ..data.feeder import BatchFeeder, PackedDataset
 from ..model import activations
 from ..model.nn import MoleculeNN
 from ..utils.helpers import ed_harder_rmse
+from .optim import FlatNadam
 
 HARTREE_TO_KCAL_PER_MOL = 627.509
 
@@ -43,13 +44,18 @@ def flatten_results(res, pos=0):
     return np.concatenate(flattened).reshape((-1,))
 
 
-def average_gradients(parameters):
+def average_gradients(parameters, flat_grads=None):
     """Mean of the weight gradients over all ranks: ONE all-reduce of a flat bucket (296,452
     values for four 384-128-128-64-1 networks), the data-parallel replacement of the reference's
     per-variable concat + reduce_mean on the CPU (``trainer_multi_tower.py:137-179``).  A no-op
-    without an initialised process group."""
+    without an initialised process group.  ``flat_grads``: the buffer all ``.grad`` tensors are
+    slices of (``FlatNadam.flat_grads``); it is reduced in place with no packing."""
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return
+    if flat_grads is not None:
+        dist.all_reduce(flat_grads, op=dist.ReduceOp.SUM)
+        flat_grads /= dist.get_world_size()
         return
     params = [p for p in parameters if p.grad is not None]
     if not params:
@@ -106,12 +112,18 @@ class TrainerMultiTower:
         self.all_models = [self.model]
         self.parameters = self.model.get_parameters()
         self.learning_rate = 1e-3
-        self.optimizer = torch.optim.NAdam(self.parameters, lr=self.learning_rate, betas=(0.9, 0.999), eps=1e-8)
+        self.ema_decay = 0.9999
+        if precision == torch.float32 and self.towers[0].type == "cuda":
+            # flat buffers + one fused clip / Nadam / moving-average call per step
+            self.optimizer = FlatNadam(self.parameters, lr=self.learning_rate, clip_norm=5.0,
+                                       ema_decay=self.ema_decay)
+            self.ema = [self.optimizer.ema_of(k) for k in range(len(self.parameters))]
+        else:
+            self.optimizer = torch.optim.NAdam(self.parameters, lr=self.learning_rate, betas=(0.9, 0.999), eps=1e-8)
+            self.ema = [p.detach().clone() for p in self.parameters]
         self.global_step = 0
         self.global_epoch_count = 0
         self.local_epoch_count = 0
-        self.ema_decay = 0.9999
-        self.ema = [p.detach().clone() for p in self.parameters]
         # ops that feed_dataset understands
         self.tower_preds = _Op("tower_preds")
         self.tower_bids = _Op("tower_bids")
@@ -181,6 +193,9 @@ class TrainerMultiTower:
 
     def set_learning_rate(self, lr: float):
         self.learning_rate = lr
+        if isinstance(self.optimizer, FlatNadam):
+            self.optimizer.set_lr(lr)
+            return
         for g in self.optimizer.param_groups:
             g["lr"] = lr
 
@@ -291,16 +306,22 @@ class TrainerMultiTower:
     def _apply_gradients(self, losses):
         """Average of the tower gradients (and of all ranks when torch.distributed is up),
         global-norm clip 5, Nadam step, EMA (``trainer_multi_tower.py:421-427``)."""
-        self.optimizer.zero_grad(set_to_none=True)
+        fused = isinstance(self.optimizer, FlatNadam)
+        self.optimizer.zero_grad(set_to_none=not fused)
         total = sum(l.to(self.towers[0]) if l.device != self.towers[0] else l for l in losses) / len(losses)
         total.backward()
+        self.global_step += 1
+        if fused:      # clip, Nadam and the moving average are inside the fused step
+            average_gradients(self.parameters, self.optimizer.flat_grads)
+            self.optimizer.step()
+            return
         average_gradients(self.parameters)
         torch.nn.utils.clip_grad_norm_(self.parameters, 5.0)
         self.optimizer.step()
-        self.global_step += 1
         with torch.no_grad():
+            decay = min(self.ema_decay, (1.0 + self.global_step) / (10.0 + self.global_step))
             for e, p in zip(self.ema, self.parameters):
-                e.mul_(self.ema_decay).add_(p.detach(), alpha=1.0 - self.ema_decay)
+                e.mul_(decay).add_(p.detach(), alpha=1.0 - decay)
 
     # ------------------------------------------------------------------ user-facing helpers
     def predict(self, dataset, batch_size=2048):
