@@ -239,6 +239,35 @@ int ani_mlp_backward_f32(const ani_mlp_backward_args* args_host, const int* acs_
                          int split_precision, void* stream);
 
 /*
+ * Weight and bias gradients of the same four networks, one launch, ADDED to the outputs (zero
+ * them first, or pass gradient buffers that are being accumulated):
+ *   dw1 += F^T dz1 [384][128],  dw2 += A1^T dz2 [128][128],  dw3 += A2^T dz3 [128][64],
+ *   db1 += column sums of dz1,  db2 += ... dz2,  db3 += ... dz3,
+ * in the reference's weight layout ([in][out]).  features / act1 / act2 are the forward call's
+ * input and saved activations, dz1..3 the outputs of ani_mlp_backward_f32.  The last layer's
+ * gradients (dw4 = A3^T g, db4 = sum g) are a matrix-vector product and a sum, left to the
+ * caller.  Replaces the weight part of optimizer.compute_gradients through AtomNN
+ * (khan/model/nn.py:39-67; khan/training/trainer_multi_tower.py:396-397).
+ */
+typedef struct ani_mlp_weight_grad_args {
+    const float* features[4];  /* [acs[t]][384] */
+    const float* act1[4];      /* [acs[t]][128] */
+    const float* act2[4];      /* [acs[t]][128] */
+    const float* dz1[4];       /* [acs[t]][128] */
+    const float* dz2[4];       /* [acs[t]][128] */
+    const float* dz3[4];       /* [acs[t]][64] */
+    float* dw1[4];             /* [384][128] */
+    float* dw2[4];             /* [128][128] */
+    float* dw3[4];             /* [128][64] */
+    float* db1[4];             /* [128] */
+    float* db2[4];             /* [128] */
+    float* db3[4];             /* [64] */
+} ani_mlp_weight_grad_args;
+
+int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* args_host, const int* acs_host,
+                            int split_precision, void* stream);
+
+/*
  * One optimiser step over a flat float32 weight buffer, two launches: global-norm clipping,
  * Adam with Nesterov momentum, and the exponential moving average of the weights.  It takes the
  * place of tf.clip_by_global_norm + NadamOptimizer.apply_gradients +

@@ -15,6 +15,7 @@
 #include "ani_grad_inverse.cuh"
 #include "ani_mlp.cuh"
 #include "ani_mlp_backward.cuh"
+#include "ani_mlp_wgrad.cuh"
 #include "ani_charge.cuh"
 #include "ani_optim.cuh"
 #include "ani_sort.cuh"
@@ -341,6 +342,22 @@ template <bool SPLIT> int mlp_backward_launch(const MlpBackwardParams& p, int n_
     return ANI_OK;
 }
 
+template <bool SPLIT> int mlp_wgrad_launch(const MlpWgradParams& p, int n_ranges, cudaStream_t st)
+{
+    auto kernel = mlp_wgrad_kernel<SPLIT>;
+    const size_t smem = sizeof(MlpShared) + 1024;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        if (int rc = set_smem(kernel, smem)) return rc;
+        configured_dev = dev;
+    }
+    kernel<<<dim3(n_ranges, kWgradBlocks), kMlpTile, smem, st>>>(p);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
 template <int ACT> int mlp_launch_act(const MlpParams& p, int n_tiles, bool split, cudaStream_t st)
 {
     return split ? mlp_launch<ACT, true>(p, n_tiles, st) : mlp_launch<ACT, false>(p, n_tiles, st);
@@ -619,6 +636,33 @@ int ani_mlp_backward_f32(const ani_mlp_backward_args* a, const int* acs_host, in
     p.tile_start[kTypes] = tiles;
     cudaStream_t st = (cudaStream_t)stream;
     return split_precision ? mlp_backward_launch<true>(p, tiles, st) : mlp_backward_launch<false>(p, tiles, st);
+}
+
+int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* a, const int* acs_host, int split_precision,
+                            void* stream)
+{
+    long long n_atoms = 0;
+    if (!a) return ANI_ERR_NULL_POINTER;
+    if (int rc = check_acs(acs_host, &n_atoms)) return rc;
+    if (n_atoms == 0) return ANI_OK;
+    MlpWgradParams p;
+    int ranges = 0;
+    for (int t = 0; t < kTypes; t++) {
+        p.range_start[t] = ranges;
+        p.count[t] = acs_host[t];
+        ranges += (acs_host[t] + kWgradRange - 1) / kWgradRange;
+        if (acs_host[t] > 0 && (!a->features[t] || !a->act1[t] || !a->act2[t] || !a->dz1[t] || !a->dz2[t] ||
+                                !a->dz3[t] || !a->dw1[t] || !a->dw2[t] || !a->dw3[t] || !a->db1[t] ||
+                                !a->db2[t] || !a->db3[t]))
+            return ANI_ERR_NULL_POINTER;
+        p.feat[t] = a->features[t]; p.act1[t] = a->act1[t]; p.act2[t] = a->act2[t];
+        p.dz1[t] = a->dz1[t]; p.dz2[t] = a->dz2[t]; p.dz3[t] = a->dz3[t];
+        p.dw1[t] = a->dw1[t]; p.dw2[t] = a->dw2[t]; p.dw3[t] = a->dw3[t];
+        p.db1[t] = a->db1[t]; p.db2[t] = a->db2[t]; p.db3[t] = a->db3[t];
+    }
+    p.range_start[kTypes] = ranges;
+    cudaStream_t st = (cudaStream_t)stream;
+    return split_precision ? mlp_wgrad_launch<true>(p, ranges, st) : mlp_wgrad_launch<false>(p, ranges, st);
 }
 
 int ani_nadam_step_f32(float* params, const float* grads, float* m, float* v, float* ema,

@@ -1,0 +1,170 @@
+// Weight and bias gradients of the per-element atomic networks on the Blackwell tensor cores:
+//   dW1 = F^T dZ1 [384 x 128],  dW2 = A1^T dZ2 [128 x 128],  dW3 = A2^T dZ3 [128 x 64],
+//   db_l = column sums of dZ_l,
+// products whose long dimension is the ATOM index.  A CTA takes one range of up to 512 atoms of
+// one element and one 128-row block of one weight matrix (three blocks for W1, one each for W2
+// and W3), accumulates its [128 x N] block in tensor memory over the range, and adds it to the
+// output with 16-byte global reductions; the outputs must be zero before the launch.
+// Both MMA operands are K-major with K = atom, so staging TRANSPOSES the row-major activations:
+// a thread reads four consecutive columns of one atom and scatters them to four operand rows.
+//
+// Same mathematics as the weight part of tf.gradients through AtomNN (khan/model/nn.py:39-67
+// under khan/training/trainer_multi_tower.py:396-397).
+#pragma once
+
+#include "ani_mlp.cuh"
+
+namespace ani {
+
+constexpr int kWgradRange = 512;   // atoms per CTA
+constexpr int kWgradBlocks = 5;    // W1 rows 0-127, 128-255, 256-383; W2; W3
+
+struct MlpWgradParams {
+    int count[kTypes];
+    int range_start[kTypes + 1];   // prefix of ceil(count / kWgradRange)
+    const float* feat[kTypes];     // [count][384]
+    const float* act1[kTypes];     // [count][128]
+    const float* act2[kTypes];     // [count][128]
+    const float* dz1[kTypes];      // [count][128]
+    const float* dz2[kTypes];      // [count][128]
+    const float* dz3[kTypes];      // [count][64]
+    float* dw1[kTypes];            // [384][128]
+    float* dw2[kTypes];            // [128][128]
+    float* dw3[kTypes];            // [128][64]
+    float* db1[kTypes];            // [128]
+    float* db2[kTypes];            // [128]
+    float* db3[kTypes];            // [64]
+};
+
+// Stages the transpose of src[atom0 .. atom0+63][col0 .. col0+rows-1] (row stride ld) as an
+// operand chunk: operand row = column of src, operand k = atom.  Atoms past `n_valid` are zero.
+// Returns this thread's partial column sums over the atoms it touched (four columns).
+template <bool SPLIT>
+__device__ __forceinline__ float4 stage_transposed(unsigned char* hi, unsigned char* lo,
+                                                   const float* __restrict__ src, int ld, int col0,
+                                                   int rows, long long atom0, int n_valid)
+{
+    const int tid = threadIdx.x;
+    const int quads = rows >> 2;                 // float4 groups per atom: 32 or 16
+    const int atoms_per_it = kMlpTile / quads;   // 4 or 8
+    const int q = tid % quads, a_in = tid / quads;
+    float4 colsum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < kMlpKChunk; k0 += atoms_per_it) {
+        const int k = k0 + a_in;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < n_valid) v = *reinterpret_cast<const float4*>(src + (size_t)(atom0 + k) * ld + col0 + 4 * q);
+        colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int off = operand_offset(4 * q + j, k);
+            if (SPLIT) {
+                const float h = __uint_as_float(__float_as_uint(e[j]) & 0xffffe000u);
+                *reinterpret_cast<float*>(hi + off) = h;
+                *reinterpret_cast<float*>(lo + off) = e[j] - h;
+            } else {
+                *reinterpret_cast<float*>(hi + off) = e[j];
+            }
+        }
+    }
+    return colsum;
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(kMlpTile) mlp_wgrad_kernel(const MlpWgradParams p)
+{
+    extern __shared__ unsigned char mlp_smem_raw[];
+    MlpShared& sh = *reinterpret_cast<MlpShared*>(
+        (reinterpret_cast<uintptr_t>(mlp_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5;
+
+    int e = 0;
+#pragma unroll
+    for (int t = 1; t < kTypes; t++) e += (int)blockIdx.x >= p.range_start[t] ? 1 : 0;
+    const long long first = (long long)((int)blockIdx.x - p.range_start[e]) * kWgradRange;
+    const int n_here = (int)min((long long)kWgradRange, (long long)p.count[e] - first);
+    const int blk = blockIdx.y;
+
+    // which product this CTA computes
+    const float* a_src = blk < 3 ? p.feat[e] : (blk == 3 ? p.act1[e] : p.act2[e]);
+    const int a_ld = blk < 3 ? kMlpIn : 128;
+    const int a_col0 = blk < 3 ? blk * 128 : 0;
+    const float* b_src = blk < 3 ? p.dz1[e] : (blk == 3 ? p.dz2[e] : p.dz3[e]);
+    const int N = blk == 4 ? kMlpH3 : 128;
+    float* out = blk < 3 ? p.dw1[e] + (size_t)blk * 128 * 128 : (blk == 3 ? p.dw2[e] : p.dw3[e]);
+    float* bias_out = blk == 0 ? p.db1[e] : (blk == 3 ? p.db2[e] : (blk == 4 ? p.db3[e] : nullptr));
+
+    if (warp == 0) tmem_alloc(&sh.tmem_base, kMlpTmemCols);
+    if (tid == 0) {
+        mbar_init(&sh.mbar, 1);
+        sh.failed = 0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = sh.tmem_base;
+    const unsigned idesc = instr_desc(kMlpTile, N);
+    unsigned parity = 0;
+    bool ok = true;
+    float4 bias_acc = make_float4(0.f, 0.f, 0.f, 0.f);
+
+#pragma unroll 1
+    for (int k0 = 0; k0 < n_here; k0 += kMlpKChunk) {
+        const int n_valid = min(kMlpKChunk, n_here - k0);
+        stage_transposed<SPLIT>(sh.a_hi, sh.a_lo, a_src, a_ld, a_col0, 128, first + k0, n_valid);
+        const float4 cs = stage_transposed<SPLIT>(sh.b_hi, sh.b_lo, b_src, N, 0, N, first + k0, n_valid);
+        bias_acc.x += cs.x; bias_acc.y += cs.y; bias_acc.z += cs.z; bias_acc.w += cs.w;
+        fence_async_smem();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const unsigned a_hi = smem_u32(sh.a_hi), b_hi = smem_u32(sh.b_hi);
+            const unsigned a_lo = smem_u32(sh.a_lo), b_lo = smem_u32(sh.b_lo);
+#pragma unroll
+            for (int ks = 0; ks < kMlpKChunk / 8; ks++) {
+                const unsigned step = ks * 2 * kMlpLbo;
+                const bool first_mma = k0 == 0 && ks == 0;
+                mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_hi + step), idesc, !first_mma);
+                if (SPLIT) {
+                    mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_lo + step), idesc, true);
+                    mma_tf32(tmem, smem_desc(a_lo + step), smem_desc(b_hi + step), idesc, true);
+                }
+            }
+            mma_commit(&sh.mbar);
+        }
+        if (ok && !mbar_wait(&sh.mbar, parity)) ok = false;
+        parity ^= 1u;
+        if (!ok) sh.failed = 1;
+        __syncthreads();
+        if (sh.failed) break;
+    }
+
+    if (!sh.failed && n_here > 0) {
+        tc_fence_after();
+        // thread = row of the weight block (TMEM lane); its N values are contiguous in the output
+        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+        for (int c0 = 0; c0 < N; c0 += 32) {
+            float v[32];
+            tmem_load32(lane_addr + c0, v);
+            float* dst = out + (size_t)tid * N + c0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+                atomicAdd(reinterpret_cast<float4*>(dst + i), make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));
+        }
+        if (bias_out) {
+            // this thread summed columns 4q .. 4q+3 of dZ over the atoms it staged
+            const int quads = N >> 2, q = tid % quads;
+            atomicAdd(bias_out + 4 * q + 0, bias_acc.x);
+            atomicAdd(bias_out + 4 * q + 1, bias_acc.y);
+            atomicAdd(bias_out + 4 * q + 2, bias_acc.z);
+            atomicAdd(bias_out + 4 * q + 3, bias_acc.w);
+        }
+    } else if (sh.failed && tid == 0) {
+        report(ANI_ERR_TIMEOUT);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kMlpTmemCols);
+}
+
+}  // namespace ani

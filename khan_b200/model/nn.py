@@ -175,18 +175,37 @@ class _FusedMlp(torch.autograd.Function):
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().ani_mlp_backward_f32(ctypes.byref(args), acs.ctypes.data_as(_lib.c_int_p),
                                                        int(ctx.split), stream), "ani_mlp_backward_f32")
+        # weight and bias gradients of the three hidden layers: one more launch, accumulated
+        # into one zero-filled buffer that the returned gradients are slices of
+        sizes = [384 * 128, 128, 128 * 128, 128, 128 * 64, 64]
+        per_elem = sum(sizes)
+        wbuf = torch.zeros(4 * per_elem, **f32)
+        wargs = _lib.MlpWeightGradArgs()
         grads = [None] * len(params)
         for t in range(4):
             s, e = int(starts[t]), int(starts[t + 1])
-            if e == s:
+            cnt = e - s
+
+            def ptr(tensor, offset=0, live=cnt > 0):
+                return ctypes.c_void_p(tensor.data_ptr() + offset * tensor.element_size()) if live else None
+
+            wargs.features[t], wargs.act1[t], wargs.act2[t] = ptr(features, s * 384), ptr(a1, s * 128), ptr(a2, s * 128)
+            wargs.dz1[t], wargs.dz2[t], wargs.dz3[t] = ptr(dz1, s * 128), ptr(dz2, s * 128), ptr(dz3, s * 64)
+            offs = np.concatenate([[0], np.cumsum(sizes)]) + t * per_elem
+            wargs.dw1[t], wargs.db1[t], wargs.dw2[t], wargs.db2[t], wargs.dw3[t], wargs.db3[t] = (
+                ptr(wbuf, int(o)) for o in offs[:6])
+            if cnt == 0:
                 continue
             b4 = params[8 * t + 7]
             ge = g[s:e]
+            views = [wbuf[int(offs[k]):int(offs[k + 1])] for k in range(6)]
             grads[8 * t: 8 * t + 8] = [
-                features[s:e].t() @ dz1[s:e], dz1[s:e].sum(0),
-                a1[s:e].t() @ dz2[s:e], dz2[s:e].sum(0),
-                a2[s:e].t() @ dz3[s:e], dz3[s:e].sum(0),
+                views[0].view(384, 128), views[1], views[2].view(128, 128), views[3],
+                views[4].view(128, 64), views[5],
                 a3[s:e].t() @ ge.reshape(-1, 1), ge.sum().reshape(b4.shape)]
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().ani_mlp_weight_grad_f32(ctypes.byref(wargs), acs.ctypes.data_as(_lib.c_int_p),
+                                                          int(ctx.split), stream), "ani_mlp_weight_grad_f32")
         return (grad_feat, None, None, None, None, *grads)
 
 
