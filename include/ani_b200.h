@@ -42,6 +42,7 @@ extern "C" {
 #define ANI_ERR_BAD_INDEX (-6)      /* device saw an offset/count/scatter index out of range */
 #define ANI_ERR_TOO_MANY_ATOMS (-7) /* size beyond what an entry point supports          */
 #define ANI_ERR_TIMEOUT (-8)        /* a bounded device-side wait ran out (status word)    */
+#define ANI_ERR_MISALIGNED (-9)     /* a pointer that must be 16-byte aligned is not       */
 
 /* Number of features per atom (384).  Replaces the `feature_size` attr of the Featurize op
  * (gpu_featurizer/ani_op.cpp:104). */
@@ -243,10 +244,10 @@ int ani_mlp_backward_f32(const ani_mlp_backward_args* args_host, const int* acs_
  * them first, or pass gradient buffers that are being accumulated):
  *   dw1 += F^T dz1 [384][128],  dw2 += A1^T dz2 [128][128],  dw3 += A2^T dz3 [128][64],
  *   db1 += column sums of dz1,  db2 += ... dz2,  db3 += ... dz3,
- * in the reference's weight layout ([in][out]).  features / act1 / act2 are the forward call's
- * input and saved activations, dz1..3 the outputs of ani_mlp_backward_f32.  The last layer's
- * gradients (dw4 = A3^T g, db4 = sum g) are a matrix-vector product and a sum, left to the
- * caller.  Replaces the weight part of optimizer.compute_gradients through AtomNN
+ *   dw4 += A3^T g [64],  db4 += sum g   (g = grad_energy),
+ * in the reference's weight layout ([in][out]); dw1, dw2, dw3 and every input matrix must be
+ * 16-byte aligned (ANI_ERR_MISALIGNED otherwise).  features / act1..3 are the forward call's
+ * input and saved activations, dz1..3 the outputs of ani_mlp_backward_f32.  Replaces the weight part of optimizer.compute_gradients through AtomNN
  * (khan/model/nn.py:39-67; khan/training/trainer_multi_tower.py:396-397).
  */
 typedef struct ani_mlp_weight_grad_args {
@@ -262,6 +263,10 @@ typedef struct ani_mlp_weight_grad_args {
     float* db1[4];             /* [128] */
     float* db2[4];             /* [128] */
     float* db3[4];             /* [64] */
+    const float* act3[4];      /* [acs[t]][64] */
+    const float* grad_energy[4];   /* [acs[t]] */
+    float* dw4[4];             /* [64] */
+    float* db4[4];             /* [1] */
 } ani_mlp_weight_grad_args;
 
 int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* args_host, const int* acs_host,

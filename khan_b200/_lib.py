@@ -49,7 +49,8 @@ class MlpBackwardArgs(ctypes.Structure):
 class MlpWeightGradArgs(ctypes.Structure):
     """``ani_mlp_weight_grad_args`` of include/ani_b200.h."""
     _fields_ = [(name, ctypes.c_void_p * 4) for name in (
-        "features", "act1", "act2", "dz1", "dz2", "dz3", "dw1", "dw2", "dw3", "db1", "db2", "db3")]
+        "features", "act1", "act2", "dz1", "dz2", "dz3", "dw1", "dw2", "dw3", "db1", "db2", "db3",
+        "act3", "grad_energy", "dw4", "db4")]
 
 
 # name -> (restype, argtypes); one entry per declaration in include/ani_b200.h

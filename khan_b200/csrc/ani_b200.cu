@@ -397,6 +397,7 @@ const char* ani_status_string(int status)
         case ANI_ERR_BAD_INDEX: return "molecule offset/count or scatter index out of range";
         case ANI_ERR_TOO_MANY_ATOMS: return "size beyond what this entry point supports";
         case ANI_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+        case ANI_ERR_MISALIGNED: return "a pointer that must be 16-byte aligned is not";
         default: return "unknown status";
     }
 }
@@ -653,12 +654,21 @@ int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* a, const int* acs_ho
         ranges += (acs_host[t] + kWgradRange - 1) / kWgradRange;
         if (acs_host[t] > 0 && (!a->features[t] || !a->act1[t] || !a->act2[t] || !a->dz1[t] || !a->dz2[t] ||
                                 !a->dz3[t] || !a->dw1[t] || !a->dw2[t] || !a->dw3[t] || !a->db1[t] ||
-                                !a->db2[t] || !a->db3[t]))
+                                !a->db2[t] || !a->db3[t] || !a->act3[t] || !a->grad_energy[t] ||
+                                !a->dw4[t] || !a->db4[t]))
             return ANI_ERR_NULL_POINTER;
+        if (acs_host[t] > 0) {
+            const void* vec[] = {a->features[t], a->act1[t], a->act2[t], a->act3[t], a->dz1[t], a->dz2[t],
+                                 a->dz3[t], a->dw1[t], a->dw2[t], a->dw3[t]};
+            for (const void* ptr : vec)
+                if (reinterpret_cast<uintptr_t>(ptr) & 15) return ANI_ERR_MISALIGNED;
+        }
         p.feat[t] = a->features[t]; p.act1[t] = a->act1[t]; p.act2[t] = a->act2[t];
         p.dz1[t] = a->dz1[t]; p.dz2[t] = a->dz2[t]; p.dz3[t] = a->dz3[t];
         p.dw1[t] = a->dw1[t]; p.dw2[t] = a->dw2[t]; p.dw3[t] = a->dw3[t];
         p.db1[t] = a->db1[t]; p.db2[t] = a->db2[t]; p.db3[t] = a->db3[t];
+        p.act3[t] = a->act3[t]; p.grad_energy[t] = a->grad_energy[t];
+        p.dw4[t] = a->dw4[t]; p.db4[t] = a->db4[t];
     }
     p.range_start[kTypes] = ranges;
     cudaStream_t st = (cudaStream_t)stream;

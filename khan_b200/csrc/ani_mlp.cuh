@@ -35,6 +35,7 @@ constexpr int kMlpSbo = (kMlpKChunk / 4) * 128;   // bytes between 8-row groups 
 constexpr int kMlpOperandBytes = kMlpTile * kMlpKChunk * 4;   // 32 KiB
 constexpr int kMlpActStride = 129;        // floats per row of the activation buffer (bank-conflict free)
 constexpr int kMlpTmemCols = 128;
+constexpr int kMlpStageBatch = 8;        // staging steps whose loads are in flight together
 constexpr unsigned kMlpSpinLimit = 1u << 24;
 
 enum MlpActivation { kActCelu = 0, kActGaussian = 1, kActNormal = 2, kActSoftplus = 3 };
@@ -279,21 +280,30 @@ __global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p
 #pragma unroll 1
         for (int kc = 0; kc < K; kc += kMlpKChunk) {
             // ---- stage the A chunk (128 atoms x 64) and the B chunk (N outputs x 64) ----
-            for (int it = 0; it < kMlpKChunk / 4; it++) {
-                int row, kg;
-                staging_slot(it, tid, &row, &kg);
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (layer == 0) {
-                    if (row < n_rows)
-                        v = *reinterpret_cast<const float4*>(p.feat[e] + (size_t)(row0 + row) * kMlpIn + kc + kg * 4);
-                } else {
-                    const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
-                    v = make_float4(src[0], src[1], src[2], src[3]);
+            // all global loads of a batch are issued before any of them is used: with one CTA
+            // per SM there is nothing else to hide their latency
+            for (int it0 = 0; it0 < kMlpKChunk / 4; it0 += kMlpStageBatch) {
+                float4 av[kMlpStageBatch], wv[kMlpStageBatch];
+                int rows[kMlpStageBatch], kgs[kMlpStageBatch];
+#pragma unroll
+                for (int j = 0; j < kMlpStageBatch; j++) {
+                    staging_slot(it0 + j, tid, &rows[j], &kgs[j]);
+                    const int row = rows[j], kg = kgs[j];
+                    av[j] = wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (layer == 0) {
+                        if (row < n_rows)
+                            av[j] = *reinterpret_cast<const float4*>(p.feat[e] + (size_t)(row0 + row) * kMlpIn + kc + kg * 4);
+                    } else {
+                        const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
+                        av[j] = make_float4(src[0], src[1], src[2], src[3]);
+                    }
+                    if (row < N)
+                        wv[j] = *reinterpret_cast<const float4*>(layer_w[layer] + (size_t)row * K + kc + kg * 4);
                 }
-                stage4<SPLIT>(sh.a_hi, sh.a_lo, row, kg * 4, v);
-                if (row < N) {
-                    const float4 w = *reinterpret_cast<const float4*>(layer_w[layer] + (size_t)row * K + kc + kg * 4);
-                    stage4<SPLIT>(sh.b_hi, sh.b_lo, row, kg * 4, w);
+#pragma unroll
+                for (int j = 0; j < kMlpStageBatch; j++) {
+                    stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, av[j]);
+                    if (rows[j] < N) stage4<SPLIT>(sh.b_hi, sh.b_lo, rows[j], kgs[j] * 4, wv[j]);
                 }
             }
             fence_async_smem();

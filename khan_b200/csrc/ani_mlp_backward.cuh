@@ -49,14 +49,21 @@ __device__ __forceinline__ bool mlp_product(MlpShared& sh, unsigned tmem, const 
     bool ok = true;
 #pragma unroll 1
     for (int kc = 0; kc < K; kc += kMlpKChunk) {
-        for (int it = 0; it < kMlpKChunk / 4; it++) {
-            int row, kg;
-            staging_slot(it, tid, &row, &kg);
-            const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
-            stage4<SPLIT>(sh.a_hi, sh.a_lo, row, kg * 4, make_float4(src[0], src[1], src[2], src[3]));
-            if (row < N) {
-                const float4 wv = *reinterpret_cast<const float4*>(w + (size_t)(n0 + row) * ldw + kc + kg * 4);
-                stage4<SPLIT>(sh.b_hi, sh.b_lo, row, kg * 4, wv);
+        for (int it0 = 0; it0 < kMlpKChunk / 4; it0 += kMlpStageBatch) {
+            float4 wv[kMlpStageBatch];
+            int rows[kMlpStageBatch], kgs[kMlpStageBatch];
+#pragma unroll
+            for (int j = 0; j < kMlpStageBatch; j++) {   // weight loads of the batch in flight together
+                staging_slot(it0 + j, tid, &rows[j], &kgs[j]);
+                wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (rows[j] < N)
+                    wv[j] = *reinterpret_cast<const float4*>(w + (size_t)(n0 + rows[j]) * ldw + kc + kgs[j] * 4);
+            }
+#pragma unroll
+            for (int j = 0; j < kMlpStageBatch; j++) {
+                const float* src = sh.act + rows[j] * kMlpActStride + kc + kgs[j] * 4;
+                stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, make_float4(src[0], src[1], src[2], src[3]));
+                if (rows[j] < N) stage4<SPLIT>(sh.b_hi, sh.b_lo, rows[j], kgs[j] * 4, wv[j]);
             }
         }
         fence_async_smem();

@@ -4,7 +4,8 @@
 // products whose long dimension is the ATOM index.  A CTA takes one range of up to 512 atoms of
 // one element and one 128-row block of one weight matrix (three blocks for W1, one each for W2
 // and W3), accumulates its [128 x N] block in tensor memory over the range, and adds it to the
-// output with 16-byte global reductions; the outputs must be zero before the launch.
+// output with 16-byte global reductions (the call ADDS to its outputs).  A sixth kind of CTA does
+// the output layer (dw4 = A3^T g, db4 = sum g) with plain loads.
 // Both MMA operands are K-major with K = atom, so staging TRANSPOSES the row-major activations:
 // a thread reads four consecutive columns of one atom and scatters them to four operand rows.
 //
@@ -17,7 +18,7 @@
 namespace ani {
 
 constexpr int kWgradRange = 512;   // atoms per CTA
-constexpr int kWgradBlocks = 5;    // W1 rows 0-127, 128-255, 256-383; W2; W3
+constexpr int kWgradBlocks = 6;    // W1 rows 0-127, 128-255, 256-383; W2; W3; the output layer (w4, b4)
 
 struct MlpWgradParams {
     int count[kTypes];
@@ -34,6 +35,10 @@ struct MlpWgradParams {
     float* db1[kTypes];            // [128]
     float* db2[kTypes];            // [128]
     float* db3[kTypes];            // [64]
+    const float* act3[kTypes];     // [count][64]
+    const float* grad_energy[kTypes];   // [count]
+    float* dw4[kTypes];            // [64]
+    float* db4[kTypes];            // [1]
 };
 
 // Stages the transpose of src[atom0 .. atom0+63][col0 .. col0+rows-1] (row stride ld) as an
@@ -49,21 +54,31 @@ __device__ __forceinline__ float4 stage_transposed(unsigned char* hi, unsigned c
     const int atoms_per_it = kMlpTile / quads;   // 4 or 8
     const int q = tid % quads, a_in = tid / quads;
     float4 colsum = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int k0 = 0; k0 < kMlpKChunk; k0 += atoms_per_it) {
-        const int k = k0 + a_in;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k < n_valid) v = *reinterpret_cast<const float4*>(src + (size_t)(atom0 + k) * ld + col0 + 4 * q);
-        colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
-        const float e[4] = {v.x, v.y, v.z, v.w};
+    constexpr int kBatch = 4;
+    for (int k0 = 0; k0 < kMlpKChunk; k0 += kBatch * atoms_per_it) {
+        float4 vs[kBatch];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int off = operand_offset(4 * q + j, k);
-            if (SPLIT) {
-                const float h = __uint_as_float(__float_as_uint(e[j]) & 0xffffe000u);
-                *reinterpret_cast<float*>(hi + off) = h;
-                *reinterpret_cast<float*>(lo + off) = e[j] - h;
-            } else {
-                *reinterpret_cast<float*>(hi + off) = e[j];
+        for (int b = 0; b < kBatch; b++) {   // the loads of a batch are in flight together
+            const int k = k0 + b * atoms_per_it + a_in;
+            vs[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < n_valid) vs[b] = *reinterpret_cast<const float4*>(src + (size_t)(atom0 + k) * ld + col0 + 4 * q);
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; b++) {
+            const int k = k0 + b * atoms_per_it + a_in;
+            const float4 v = vs[b];
+            colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int off = operand_offset(4 * q + j, k);
+                if (SPLIT) {
+                    const float h = __uint_as_float(__float_as_uint(e[j]) & 0xffffe000u);
+                    *reinterpret_cast<float*>(hi + off) = h;
+                    *reinterpret_cast<float*>(lo + off) = e[j] - h;
+                } else {
+                    *reinterpret_cast<float*>(hi + off) = e[j];
+                }
             }
         }
     }
@@ -84,6 +99,25 @@ __global__ void __launch_bounds__(kMlpTile) mlp_wgrad_kernel(const MlpWgradParam
     const long long first = (long long)((int)blockIdx.x - p.range_start[e]) * kWgradRange;
     const int n_here = (int)min((long long)kWgradRange, (long long)p.count[e] - first);
     const int blk = blockIdx.y;
+
+    if (blk == 5) {
+        // output layer: dw4 = A3^T g and db4 = sum g over this range; no tensor cores involved
+        const int q = tid & 15, a_in = tid >> 4;      // 16 column quads x 8 atoms per pass
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float gsum = 0.0f;
+        for (int k = a_in; k < n_here; k += 8) {
+            const float g = p.grad_energy[e][first + k];
+            const float4 v = *reinterpret_cast<const float4*>(p.act3[e] + (size_t)(first + k) * kMlpH3 + 4 * q);
+            acc.x += v.x * g; acc.y += v.y * g; acc.z += v.z * g; acc.w += v.w * g;
+            gsum += q == 0 ? g : 0.0f;
+        }
+        atomicAdd(p.dw4[e] + 4 * q + 0, acc.x);
+        atomicAdd(p.dw4[e] + 4 * q + 1, acc.y);
+        atomicAdd(p.dw4[e] + 4 * q + 2, acc.z);
+        atomicAdd(p.dw4[e] + 4 * q + 3, acc.w);
+        if (q == 0) atomicAdd(p.db4[e], gsum);
+        return;
+    }
 
     // which product this CTA computes
     const float* a_src = blk < 3 ? p.feat[e] : (blk == 3 ? p.act1[e] : p.act2[e]);

@@ -175,11 +175,15 @@ class _FusedMlp(torch.autograd.Function):
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().ani_mlp_backward_f32(ctypes.byref(args), acs.ctypes.data_as(_lib.c_int_p),
                                                        int(ctx.split), stream), "ani_mlp_backward_f32")
-        # weight and bias gradients of the three hidden layers: one more launch, accumulated
-        # into one zero-filled buffer that the returned gradients are slices of
-        sizes = [384 * 128, 128, 128 * 128, 128, 128 * 64, 64]
+        # weight and bias gradients: one more launch.  Where a parameter already has a gradient
+        # buffer (the flat optimiser gives every parameter one) the kernel adds into it directly
+        # and None is returned for it, which is what autograd's own accumulation would do with
+        # 32 separate additions; otherwise the gradients are slices of one zero-filled buffer.
+        sizes = [384 * 128, 128, 128 * 128, 128, 128 * 64, 64, 64, 4]   # the last slot holds b4 (1 value): keeps every slice 16-byte aligned
         per_elem = sum(sizes)
-        wbuf = torch.zeros(4 * per_elem, **f32)
+        direct = all(p.grad is not None and p.grad.is_contiguous() and p.grad.dtype == torch.float32
+                     and p.grad.data_ptr() % 16 == 0 for p in params)
+        wbuf = None if direct else torch.zeros(4 * per_elem, **f32)
         wargs = _lib.MlpWeightGradArgs()
         grads = [None] * len(params)
         for t in range(4):
@@ -190,19 +194,19 @@ class _FusedMlp(torch.autograd.Function):
                 return ctypes.c_void_p(tensor.data_ptr() + offset * tensor.element_size()) if live else None
 
             wargs.features[t], wargs.act1[t], wargs.act2[t] = ptr(features, s * 384), ptr(a1, s * 128), ptr(a2, s * 128)
+            wargs.act3[t], wargs.grad_energy[t] = ptr(a3, s * 64), ptr(g, s)
             wargs.dz1[t], wargs.dz2[t], wargs.dz3[t] = ptr(dz1, s * 128), ptr(dz2, s * 128), ptr(dz3, s * 64)
-            offs = np.concatenate([[0], np.cumsum(sizes)]) + t * per_elem
-            wargs.dw1[t], wargs.db1[t], wargs.dw2[t], wargs.db2[t], wargs.dw3[t], wargs.db3[t] = (
-                ptr(wbuf, int(o)) for o in offs[:6])
-            if cnt == 0:
-                continue
-            b4 = params[8 * t + 7]
-            ge = g[s:e]
-            views = [wbuf[int(offs[k]):int(offs[k + 1])] for k in range(6)]
-            grads[8 * t: 8 * t + 8] = [
-                views[0].view(384, 128), views[1], views[2].view(128, 128), views[3],
-                views[4].view(128, 64), views[5],
-                a3[s:e].t() @ ge.reshape(-1, 1), ge.sum().reshape(b4.shape)]
+            if direct:
+                outs = [ptr(p.grad) for p in params[8 * t: 8 * t + 8]]
+            else:
+                offs = np.concatenate([[0], np.cumsum(sizes)]) + t * per_elem
+                outs = [ptr(wbuf, int(o)) for o in offs[:8]]
+                if cnt > 0:
+                    grads[8 * t: 8 * t + 8] = [
+                        wbuf[int(offs[k]):int(offs[k]) + params[8 * t + k].numel()].view(params[8 * t + k].shape)
+                        for k in range(8)]
+            (wargs.dw1[t], wargs.db1[t], wargs.dw2[t], wargs.db2[t], wargs.dw3[t], wargs.db3[t],
+             wargs.dw4[t], wargs.db4[t]) = outs
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().ani_mlp_weight_grad_f32(ctypes.byref(wargs), acs.ctypes.data_as(_lib.c_int_p),
                                                           int(ctx.split), stream), "ani_mlp_weight_grad_f32")

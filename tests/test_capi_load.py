@@ -34,7 +34,7 @@ def test_library_exports_every_declared_symbol(handle):
 def test_host_only_entry_points(handle):
     assert handle.ani_feature_size() == 384
     assert handle.ani_status_string(0) == b"ok"
-    for code in (-1, -2, -3, -4, -6, -7):
+    for code in (-1, -2, -3, -4, -6, -7, -8, -9):
         assert handle.ani_status_string(code) != b"unknown status"
 
 
@@ -55,6 +55,21 @@ def test_argument_checks_need_no_gpu(handle):
     one = (ctypes.c_int * 4)(1, 0, 0, 0)
     assert handle.ani_featurize_f32(None, None, None, None, None, None, 1, None, None, None, None,
                                     None, one, None) == -1
+
+
+def test_weight_grad_rejects_misaligned_matrices_before_launching(handle):
+    """The tensor-core weight-gradient kernel uses 16-byte accesses: a matrix pointer that is
+    only 4-byte aligned is refused on the host (nothing is dereferenced, no GPU needed)."""
+    args = _lib.MlpWeightGradArgs()
+    for name, _ in args._fields_:
+        getattr(args, name)[0] = 0x10000
+    one = (ctypes.c_int * 4)(5, 0, 0, 0)
+    args.dw2[0] = 0x10004
+    assert handle.ani_mlp_weight_grad_f32(ctypes.byref(args), one, 1, None) == -9
+    args.dw2[0] = None
+    assert handle.ani_mlp_weight_grad_f32(ctypes.byref(args), one, 1, None) == -1
+    assert handle.ani_nadam_step_f32(None, None, None, None, None, 10, None, None, None) == -1
+    assert handle.ani_nadam_step_f32(None, None, None, None, None, 0, None, None, None) == 0
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

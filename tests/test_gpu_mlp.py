@@ -118,3 +118,24 @@ def test_double_backward_keeps_the_second_derivative():
             assert a is None or a.abs().max().item() == 0.0
             continue
         assert (a.double() - b).abs().max().item() < 1e-3 * b.abs().max().item()
+
+
+def test_weight_gradients_accumulate_into_existing_buffers():
+    """Second backward pass: the parameters already have gradient buffers, so the kernel adds
+    into them directly; the result must be exactly twice the first pass up to rounding."""
+    import torch
+    from khan_b200.model import activations, nn
+    acs = np.array([140, 0, 33, 600])
+    n = int(acs.sum())
+    model = nn.MoleculeNN(activation_fn=activations.celu, seed=8, init="he")
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    feats = torch.rand((n, 384), device="cuda", generator=gen)
+    w = torch.randn(n, device="cuda", generator=gen)
+    (model.atom_energies_sorted(feats, acs) * w).sum().backward()
+    params = [p for p in _interleaved(model) if p.grad is not None]
+    first = [p.grad.clone() for p in params]
+    ptrs = [p.grad.data_ptr() for p in params]
+    (model.atom_energies_sorted(feats, acs) * w).sum().backward()
+    for p, f, ptr in zip(params, first, ptrs):
+        assert p.grad.data_ptr() == ptr
+        assert (p.grad - 2 * f).abs().max().item() <= 1e-5 * f.abs().max().item()
