@@ -180,7 +180,8 @@ int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const dou
  * reference drivers (gdb8.py:91): for every element t,
  *   energy[t] = act(act(act(F_t W1 + b1) W2 + b2) W3 + b3) w4 + b4,   F_t = features[t] [acs[t]][384].
  * One launch covers all four elements; the matrix products run on the tensor cores in tf32.
- * Weights are passed transposed, [out][in] with `in` contiguous.  `activation`: 0 celu(0.1),
+ * Weights are passed as the reference stores them, [in][out] with `out` contiguous
+ * (khan/model/nn.py:42-47), 16-byte aligned.  `activation`: 0 celu(0.1),
  * 1 gaussian exp(-x^2), 2 normal exp(-x^2/2), 3 softplus - ln 2 (khan/model/activations.py:62-74).
  * `split_precision` != 0 splits every operand into two tf32 terms (three MMAs per product),
  * which brings the products to float32 accuracy; 0 uses plain tf32.
@@ -190,11 +191,11 @@ int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const dou
  */
 typedef struct ani_mlp_args {
     const float* features[4];
-    const float* w1t[4];  /* [128][384] */
+    const float* w1[4];   /* [384][128] */
     const float* b1[4];   /* [128] */
-    const float* w2t[4];  /* [128][128] */
+    const float* w2[4];   /* [128][128] */
     const float* b2[4];   /* [128] */
-    const float* w3t[4];  /* [64][128] */
+    const float* w3[4];   /* [128][64] */
     const float* b3[4];   /* [64] */
     const float* w4[4];   /* [64] */
     const float* b4[4];   /* [1] */

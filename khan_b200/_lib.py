@@ -35,7 +35,7 @@ _i = ctypes.c_int
 class MlpArgs(ctypes.Structure):
     """``ani_mlp_args`` of include/ani_b200.h: sixteen arrays of four device pointers."""
     _fields_ = [(name, ctypes.c_void_p * 4) for name in (
-        "features", "w1t", "b1", "w2t", "b2", "w3t", "b3", "w4", "b4", "energy", "act1", "act2", "act3",
+        "features", "w1", "b1", "w2", "b2", "w3", "b3", "w4", "b4", "energy", "act1", "act2", "act3",
         "dact1", "dact2", "dact3")]
 
 

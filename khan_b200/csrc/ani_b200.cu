@@ -321,7 +321,7 @@ template <int ACT, bool SPLIT> int mlp_launch(const MlpParams& p, int n_tiles, c
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<n_tiles, kMlpTile, smem, st>>>(p);
+    kernel<<<n_tiles, kMlpThreads, smem, st>>>(p);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
@@ -337,7 +337,7 @@ template <bool SPLIT> int mlp_backward_launch(const MlpBackwardParams& p, int n_
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<n_tiles, kMlpTile, smem, st>>>(p);
+    kernel<<<n_tiles, kMlpThreads, smem, st>>>(p);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
@@ -353,7 +353,7 @@ template <bool SPLIT> int mlp_wgrad_launch(const MlpWgradParams& p, int n_ranges
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<dim3(n_ranges, kWgradBlocks), kMlpTile, smem, st>>>(p);
+    kernel<<<dim3(n_ranges, kWgradBlocks), kMlpThreads, smem, st>>>(p);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
@@ -588,13 +588,13 @@ int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activati
         p.tile_start[t] = tiles;
         p.count[t] = acs_host[t];
         tiles += (acs_host[t] + kMlpTile - 1) / kMlpTile;
-        if (acs_host[t] > 0 && (!a->features[t] || !a->w1t[t] || !a->b1[t] || !a->w2t[t] || !a->b2[t] ||
-                                !a->w3t[t] || !a->b3[t] || !a->w4[t] || !a->b4[t] || !a->energy[t]))
+        if (acs_host[t] > 0 && (!a->features[t] || !a->w1[t] || !a->b1[t] || !a->w2[t] || !a->b2[t] ||
+                                !a->w3[t] || !a->b3[t] || !a->w4[t] || !a->b4[t] || !a->energy[t]))
             return ANI_ERR_NULL_POINTER;
         p.feat[t] = a->features[t];
-        p.w1t[t] = a->w1t[t]; p.b1[t] = a->b1[t];
-        p.w2t[t] = a->w2t[t]; p.b2[t] = a->b2[t];
-        p.w3t[t] = a->w3t[t]; p.b3[t] = a->b3[t];
+        p.w1[t] = a->w1[t]; p.b1[t] = a->b1[t];
+        p.w2[t] = a->w2[t]; p.b2[t] = a->b2[t];
+        p.w3[t] = a->w3[t]; p.b3[t] = a->b3[t];
         p.w4[t] = a->w4[t];   p.b4[t] = a->b4[t];
         p.energy[t] = a->energy[t];
         p.act1[t] = a->act1[t]; p.act2[t] = a->act2[t]; p.act3[t] = a->act3[t];
@@ -647,11 +647,8 @@ int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* a, const int* acs_ho
     if (int rc = check_acs(acs_host, &n_atoms)) return rc;
     if (n_atoms == 0) return ANI_OK;
     MlpWgradParams p;
-    int ranges = 0;
     for (int t = 0; t < kTypes; t++) {
-        p.range_start[t] = ranges;
         p.count[t] = acs_host[t];
-        ranges += (acs_host[t] + kWgradRange - 1) / kWgradRange;
         if (acs_host[t] > 0 && (!a->features[t] || !a->act1[t] || !a->act2[t] || !a->dz1[t] || !a->dz2[t] ||
                                 !a->dz3[t] || !a->dw1[t] || !a->dw2[t] || !a->dw3[t] || !a->db1[t] ||
                                 !a->db2[t] || !a->db3[t] || !a->act3[t] || !a->grad_energy[t] ||
@@ -669,6 +666,23 @@ int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* a, const int* acs_ho
         p.db1[t] = a->db1[t]; p.db2[t] = a->db2[t]; p.db3[t] = a->db3[t];
         p.act3[t] = a->act3[t]; p.grad_energy[t] = a->grad_energy[t];
         p.dw4[t] = a->dw4[t]; p.db4[t] = a->db4[t];
+    }
+    // atoms per CTA: the smallest multiple of 64 for which the grid fits the SMs once (the
+    // kernels run one CTA per SM, so a second partial wave would double the time)
+    int dev = 0, sms = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    ANI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int range = 256;
+    for (;; range += 64) {
+        long long ctas = 0;
+        for (int t = 0; t < kTypes; t++) ctas += (acs_host[t] + range - 1) / range;
+        if (ctas * kWgradBlocks <= sms || range >= (1 << 20)) break;
+    }
+    p.range = range;
+    int ranges = 0;
+    for (int t = 0; t < kTypes; t++) {
+        p.range_start[t] = ranges;
+        ranges += (acs_host[t] + range - 1) / range;
     }
     p.range_start[kTypes] = ranges;
     cudaStream_t st = (cudaStream_t)stream;

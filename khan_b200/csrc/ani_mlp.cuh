@@ -7,16 +7,18 @@
 // of these, one per element; here one launch covers all four (each CTA takes a tile of 128 atoms
 // of one element).
 //
-// Structure of one CTA (128 threads, tile = 128 atoms):
+// Structure of one CTA (512 threads, tile = 128 atoms):
 //   * operands are staged by all threads into shared memory in the K-major, no-swizzle
 //     core-matrix layout that tcgen05.mma reads (8 rows x 16 bytes per core matrix), 64 values
-//     of K at a time; weights are passed pre-transposed ([out][in], K contiguous);
+//     of K at a time; weights are read in the reference's layout ([in][out]) and transposed
+//     while they are staged;
 //   * one thread issues the MMAs (M = 128, N = 128 or 64, K = 8 per instruction) and commits them
 //     to an mbarrier; everybody waits on it (bounded spin: on timeout the kernel records an
 //     error, frees its tensor memory and returns);
-//   * the epilogue reads the accumulator with tcgen05.ld (thread = atom), adds the bias,
-//     applies the activation and writes the row to shared memory, where it becomes the A
-//     operand of the next layer; the last layer (64 -> 1) is a dot product in registers.
+//   * the epilogue reads the accumulator with tcgen05.ld (warp w: rows 32 (w % 4) .., columns
+//     32 (w / 4) ..), adds the bias, applies the activation and writes the values to shared
+//     memory, where they become the A operand of the next layer; the last layer (64 -> 1) is a
+//     dot product per atom from shared memory.
 // With SPLIT = true every operand is staged as a high part (the value with its low 13 mantissa
 // bits cleared, exact in tf32) and a low part (the remainder), and hi*hi + hi*lo + lo*hi are
 // accumulated: three MMAs per step give products that are accurate to about 2^-21 instead of
@@ -29,13 +31,14 @@ namespace ani {
 
 constexpr int kMlpIn = 384, kMlpH1 = 128, kMlpH2 = 128, kMlpH3 = 64;
 constexpr int kMlpTile = 128;             // atoms per CTA = MMA M
+constexpr int kMlpThreads = 512;          // 16 warps: warp w reads TMEM lanes 32 (w % 4) .., columns 32 (w / 4) ..
 constexpr int kMlpKChunk = 64;            // K values staged per step
 constexpr int kMlpLbo = 128;              // bytes between core matrices adjacent in K
 constexpr int kMlpSbo = (kMlpKChunk / 4) * 128;   // bytes between 8-row groups (2048)
 constexpr int kMlpOperandBytes = kMlpTile * kMlpKChunk * 4;   // 32 KiB
 constexpr int kMlpActStride = 129;        // floats per row of the activation buffer (bank-conflict free)
 constexpr int kMlpTmemCols = 128;
-constexpr int kMlpStageBatch = 8;        // staging steps whose loads are in flight together
+constexpr int kMlpStageSteps = kMlpTile * (kMlpKChunk / 4) / kMlpThreads;   // staging slots per thread and chunk (4)
 constexpr unsigned kMlpSpinLimit = 1u << 24;
 
 enum MlpActivation { kActCelu = 0, kActGaussian = 1, kActNormal = 2, kActSoftplus = 3 };
@@ -44,11 +47,11 @@ struct MlpParams {
     const float* feat[kTypes];   // [count][384]
     int count[kTypes];
     int tile_start[kTypes + 1];  // prefix of ceil(count / 128)
-    const float* w1t[kTypes];    // [128][384]
+    const float* w1[kTypes];     // [384][128]  (the reference's layout, [in][out])
     const float* b1[kTypes];
-    const float* w2t[kTypes];    // [128][128]
+    const float* w2[kTypes];     // [128][128]
     const float* b2[kTypes];
-    const float* w3t[kTypes];    // [64][128]
+    const float* w3[kTypes];     // [128][64]
     const float* b3[kTypes];
     const float* w4[kTypes];     // [64]
     const float* b4[kTypes];     // [1]
@@ -216,7 +219,7 @@ __device__ __forceinline__ void stage4(unsigned char* hi, unsigned char* lo, int
 // first (one 128-byte core matrix per 8 lanes, conflict-free), then 4 adjacent K groups.
 __device__ __forceinline__ void staging_slot(int it, int tid, int* row, int* kgroup)
 {
-    const int q = it * kMlpTile + tid;
+    const int q = it * kMlpThreads + tid;
     const int rest = q >> 5;
     *row = (rest >> 2) * 8 + (q & 7);
     *kgroup = (rest & 3) * 4 + ((q >> 3) & 3);
@@ -238,14 +241,64 @@ __device__ __forceinline__ void load_row32(const float* src, float* v)
     }
 }
 
+// Stages the TRANSPOSE of src[r0 .. r0+63][col0 .. col0+rows-1] (row stride ld) as an operand
+// chunk: operand row = column of src, operand k = row of src (an atom for the weight gradients,
+// an input index for weights stored [in][out]).  Source rows past `n_valid` are zero.  A thread
+// reads four consecutive columns of one source row and scatters them to four operand rows.
+// Returns this thread's partial column sums over the source rows it touched (four columns).
+template <bool SPLIT>
+__device__ __forceinline__ float4 stage_transposed(unsigned char* hi, unsigned char* lo,
+                                                   const float* __restrict__ src, int ld, int col0,
+                                                   int rows, long long atom0, int n_valid)
+{
+    const int tid = threadIdx.x;
+    const int quads = rows >> 2;                 // float4 groups per atom: 32 or 16
+    const int atoms_per_it = kMlpThreads / quads;   // 16 or 32
+    const int q = tid % quads, a_in = tid / quads;
+    float4 colsum = make_float4(0.f, 0.f, 0.f, 0.f);
+    // 64 atoms per chunk: 4 passes with 32 quads per atom, 2 with 16; all loads issued first
+    constexpr int kMaxPasses = 4;
+    const int passes = kMlpKChunk / atoms_per_it;
+    float4 vs[kMaxPasses];
+#pragma unroll
+    for (int b = 0; b < kMaxPasses; b++) {
+        const int k = b * atoms_per_it + a_in;
+        vs[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < passes && k < n_valid)
+            vs[b] = *reinterpret_cast<const float4*>(src + (size_t)(atom0 + k) * ld + col0 + 4 * q);
+    }
+#pragma unroll
+    for (int b = 0; b < kMaxPasses; b++) {
+        if (b >= passes) break;
+        const int k = b * atoms_per_it + a_in;
+        const float4 v = vs[b];
+        colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int off = operand_offset(4 * q + j, k);
+            if (SPLIT) {
+                const float h = __uint_as_float(__float_as_uint(e[j]) & 0xffffe000u);
+                *reinterpret_cast<float*>(hi + off) = h;
+                *reinterpret_cast<float*>(lo + off) = e[j] - h;
+            } else {
+                *reinterpret_cast<float*>(hi + off) = e[j];
+            }
+        }
+    }
+    return colsum;
+}
+
 template <int ACT, bool SPLIT>
-__global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p)
+__global__ void __launch_bounds__(kMlpThreads, 1) mlp_forward_kernel(const MlpParams p)
 {
     extern __shared__ unsigned char mlp_smem_raw[];
     // the launch asks for sizeof(MlpShared) + 1024 bytes so that the struct can be aligned here
     MlpShared& sh = *reinterpret_cast<MlpShared*>(
         (reinterpret_cast<uintptr_t>(mlp_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5;
+    // epilogue role of this thread: one accumulator row (TMEM lane), one group of 32 columns
+    const int erow = (warp & 3) * 32 + (tid & 31), ecg = warp >> 2;
 
     int e = 0;
 #pragma unroll
@@ -264,14 +317,14 @@ __global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p
     const unsigned tmem = sh.tmem_base;
     unsigned parity = 0;
     bool ok = true;
+    ANI_PHASE_DECL;
 
-    const float* layer_w[3] = {p.w1t[e], p.w2t[e], p.w3t[e]};
+    const float* layer_w[3] = {p.w1[e], p.w2[e], p.w3[e]};
     const float* layer_b[3] = {p.b1[e], p.b2[e], p.b3[e]};
     float* layer_out[3] = {p.act1[e], p.act2[e], p.act3[e]};
     float* layer_dout[3] = {p.dact1[e], p.dact2[e], p.dact3[e]};
     const int layer_k[3] = {kMlpIn, kMlpH1, kMlpH2};
     const int layer_n[3] = {kMlpH1, kMlpH2, kMlpH3};
-    float h3[kMlpH3];   // activations of the last hidden layer, this thread's atom
 
 #pragma unroll 1
     for (int layer = 0; layer < 3; layer++) {
@@ -279,35 +332,31 @@ __global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p
         const unsigned idesc = instr_desc(kMlpTile, N);
 #pragma unroll 1
         for (int kc = 0; kc < K; kc += kMlpKChunk) {
-            // ---- stage the A chunk (128 atoms x 64) and the B chunk (N outputs x 64) ----
-            // all global loads of a batch are issued before any of them is used: with one CTA
-            // per SM there is nothing else to hide their latency
-            for (int it0 = 0; it0 < kMlpKChunk / 4; it0 += kMlpStageBatch) {
-                float4 av[kMlpStageBatch], wv[kMlpStageBatch];
-                int rows[kMlpStageBatch], kgs[kMlpStageBatch];
+            // ---- stage the A chunk (128 atoms x 64) and the B chunk (N outputs x 64); all global
+            // loads of the chunk are issued before any of them is used ----
+            float4 av[kMlpStageSteps];
+            int rows[kMlpStageSteps], kgs[kMlpStageSteps];
 #pragma unroll
-                for (int j = 0; j < kMlpStageBatch; j++) {
-                    staging_slot(it0 + j, tid, &rows[j], &kgs[j]);
-                    const int row = rows[j], kg = kgs[j];
-                    av[j] = wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (layer == 0) {
-                        if (row < n_rows)
-                            av[j] = *reinterpret_cast<const float4*>(p.feat[e] + (size_t)(row0 + row) * kMlpIn + kc + kg * 4);
-                    } else {
-                        const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
-                        av[j] = make_float4(src[0], src[1], src[2], src[3]);
-                    }
-                    if (row < N)
-                        wv[j] = *reinterpret_cast<const float4*>(layer_w[layer] + (size_t)row * K + kc + kg * 4);
-                }
-#pragma unroll
-                for (int j = 0; j < kMlpStageBatch; j++) {
-                    stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, av[j]);
-                    if (rows[j] < N) stage4<SPLIT>(sh.b_hi, sh.b_lo, rows[j], kgs[j] * 4, wv[j]);
+            for (int j = 0; j < kMlpStageSteps; j++) {
+                staging_slot(j, tid, &rows[j], &kgs[j]);
+                const int row = rows[j], kg = kgs[j];
+                av[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (layer == 0) {
+                    if (row < n_rows)
+                        av[j] = *reinterpret_cast<const float4*>(p.feat[e] + (size_t)(row0 + row) * kMlpIn + kc + kg * 4);
+                } else {
+                    const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
+                    av[j] = make_float4(src[0], src[1], src[2], src[3]);
                 }
             }
+            // B[n = out][k = in] = W[k][n]: the weights are read as stored ([in][out]) and transposed
+            stage_transposed<SPLIT>(sh.b_hi, sh.b_lo, layer_w[layer], N, 0, N, kc, kMlpKChunk);
+#pragma unroll
+            for (int j = 0; j < kMlpStageSteps; j++) stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, av[j]);
+            ANI_PHASE(0);
             fence_async_smem();
             __syncthreads();
+            ANI_PHASE(1);
             if (tid == 0) {
                 tc_fence_after();
                 const unsigned a_hi = smem_u32(sh.a_hi), b_hi = smem_u32(sh.b_hi);
@@ -328,52 +377,45 @@ __global__ void __launch_bounds__(kMlpTile) mlp_forward_kernel(const MlpParams p
             if (ok && !mbar_wait(&sh.mbar, parity)) ok = false;
             parity ^= 1u;
             if (!ok) sh.failed = 1;
+            ANI_PHASE(2);
             __syncthreads();
+            ANI_PHASE(3);
             if (sh.failed) break;
         }
         if (sh.failed) break;
         tc_fence_after();
-        // ---- epilogue: thread = atom (TMEM lane), 32 columns at a time ----
-        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
-        if (layer < 2) {
-            for (int c0 = 0; c0 < N; c0 += 32) {
-                float v[32], d[32];
-                tmem_load32(lane_addr + c0, v);
+        // ---- epilogue: bias, activation and its derivative; the row goes back to shared memory
+        // as the next layer's A operand (the last hidden layer included: the output layer reads
+        // it from there) ----
+        const int c0 = ecg * 32;
+        if (c0 < N) {
+            float v[32], d[32];
+            tmem_load32(tmem + ((unsigned)((warp & 3) * 32) << 16) + c0, v);
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float x = v[i] + layer_b[layer][c0 + i];
-                    v[i] = mlp_activation<ACT>(x);
-                    d[i] = mlp_activation_grad<ACT>(x, v[i]);
-                    sh.act[tid * kMlpActStride + c0 + i] = v[i];
-                }
-                if (layer_out[layer] && tid < n_rows) store_row32(layer_out[layer] + (size_t)(row0 + tid) * N + c0, v);
-                if (layer_dout[layer] && tid < n_rows) store_row32(layer_dout[layer] + (size_t)(row0 + tid) * N + c0, d);
+            for (int i = 0; i < 32; i++) {
+                const float x = v[i] + layer_b[layer][c0 + i];
+                v[i] = mlp_activation<ACT>(x);
+                d[i] = mlp_activation_grad<ACT>(x, v[i]);
+                sh.act[erow * kMlpActStride + c0 + i] = v[i];
             }
-        } else {
-#pragma unroll
-            for (int c0 = 0; c0 < kMlpH3; c0 += 32) {
-                float v[32], d[32];
-                tmem_load32(lane_addr + c0, v);
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float x = v[i] + layer_b[2][c0 + i];
-                    h3[c0 + i] = mlp_activation<ACT>(x);
-                    d[i] = mlp_activation_grad<ACT>(x, h3[c0 + i]);
-                }
-                if (layer_out[2] && tid < n_rows) store_row32(layer_out[2] + (size_t)(row0 + tid) * kMlpH3 + c0, h3 + c0);
-                if (layer_dout[2] && tid < n_rows) store_row32(layer_dout[2] + (size_t)(row0 + tid) * kMlpH3 + c0, d);
-            }
+            if (layer_out[layer] && erow < n_rows) store_row32(layer_out[layer] + (size_t)(row0 + erow) * N + c0, v);
+            if (layer_dout[layer] && erow < n_rows) store_row32(layer_dout[layer] + (size_t)(row0 + erow) * N + c0, d);
         }
+        ANI_PHASE(4);
         tc_fence_before();
         __syncthreads();
+        ANI_PHASE(5);
     }
+    ANI_PHASE_FLUSH;
 
     if (!sh.failed) {
-        // ---- output layer 64 -> 1 ----
-        float acc = p.b4[e][0];
-#pragma unroll
-        for (int i = 0; i < kMlpH3; i++) acc += h3[i] * p.w4[e][i];
-        if (tid < n_rows) p.energy[e][row0 + tid] = acc;
+        // ---- output layer 64 -> 1: one thread per atom, its last hidden row from shared memory ----
+        if (tid < n_rows) {
+            float acc = p.b4[e][0];
+#pragma unroll 8
+            for (int i = 0; i < kMlpH3; i++) acc += sh.act[tid * kMlpActStride + i] * p.w4[e][i];
+            p.energy[e][row0 + tid] = acc;
+        }
     } else if (tid == 0) {
         report(ANI_ERR_TIMEOUT);
     }

@@ -49,22 +49,20 @@ __device__ __forceinline__ bool mlp_product(MlpShared& sh, unsigned tmem, const 
     bool ok = true;
 #pragma unroll 1
     for (int kc = 0; kc < K; kc += kMlpKChunk) {
-        for (int it0 = 0; it0 < kMlpKChunk / 4; it0 += kMlpStageBatch) {
-            float4 wv[kMlpStageBatch];
-            int rows[kMlpStageBatch], kgs[kMlpStageBatch];
+        float4 wv[kMlpStageSteps];
+        int rows[kMlpStageSteps], kgs[kMlpStageSteps];
 #pragma unroll
-            for (int j = 0; j < kMlpStageBatch; j++) {   // weight loads of the batch in flight together
-                staging_slot(it0 + j, tid, &rows[j], &kgs[j]);
-                wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (rows[j] < N)
-                    wv[j] = *reinterpret_cast<const float4*>(w + (size_t)(n0 + rows[j]) * ldw + kc + kgs[j] * 4);
-            }
+        for (int j = 0; j < kMlpStageSteps; j++) {   // the weight loads of the chunk are in flight together
+            staging_slot(j, tid, &rows[j], &kgs[j]);
+            wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (rows[j] < N)
+                wv[j] = *reinterpret_cast<const float4*>(w + (size_t)(n0 + rows[j]) * ldw + kc + kgs[j] * 4);
+        }
 #pragma unroll
-            for (int j = 0; j < kMlpStageBatch; j++) {
-                const float* src = sh.act + rows[j] * kMlpActStride + kc + kgs[j] * 4;
-                stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, make_float4(src[0], src[1], src[2], src[3]));
-                if (rows[j] < N) stage4<SPLIT>(sh.b_hi, sh.b_lo, rows[j], kgs[j] * 4, wv[j]);
-            }
+        for (int j = 0; j < kMlpStageSteps; j++) {
+            const float* src = sh.act + rows[j] * kMlpActStride + kc + kgs[j] * 4;
+            stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, make_float4(src[0], src[1], src[2], src[3]));
+            if (rows[j] < N) stage4<SPLIT>(sh.b_hi, sh.b_lo, rows[j], kgs[j] * 4, wv[j]);
         }
         fence_async_smem();
         __syncthreads();
@@ -95,20 +93,22 @@ __device__ __forceinline__ bool mlp_product(MlpShared& sh, unsigned tmem, const 
 }
 
 template <bool SPLIT>
-__global__ void __launch_bounds__(kMlpTile) mlp_backward_kernel(const MlpBackwardParams p)
+__global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpBackwardParams p)
 {
     extern __shared__ unsigned char mlp_smem_raw[];
     MlpShared& sh = *reinterpret_cast<MlpShared*>(
         (reinterpret_cast<uintptr_t>(mlp_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5;
+    // this thread's accumulator row (TMEM lane = atom of the tile) and group of 32 columns
+    const int erow = (warp & 3) * 32 + (tid & 31), ecg = warp >> 2;
 
     int e = 0;
 #pragma unroll
     for (int t = 1; t < kTypes; t++) e += (int)blockIdx.x >= p.tile_start[t] ? 1 : 0;
     const int row0 = ((int)blockIdx.x - p.tile_start[e]) * kMlpTile;
     const int n_rows = min(kMlpTile, p.count[e] - row0);
-    const bool live = tid < n_rows;
-    const size_t atom = (size_t)(row0 + tid);
+    const bool live = erow < n_rows;
+    const size_t atom = (size_t)(row0 + erow);
 
     if (warp == 0) tmem_alloc(&sh.tmem_base, kMlpTmemCols);
     if (tid == 0) {
@@ -119,22 +119,31 @@ __global__ void __launch_bounds__(kMlpTile) mlp_backward_kernel(const MlpBackwar
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sh.tmem_base;
-    const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+    const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
     unsigned parity = 0;
 
-    // ---- dZ3 = g * w4 * D3, thread = atom; rows past the end of the element are zero ----
+    // ---- dZ3 = g * w4 * D3: 16 of the 64 columns per thread; rows past the end are zero ----
     {
         const float g = live ? p.grad_energy[e][atom] : 0.0f;
+        const int c0 = ecg * 16;
+        float d[16], v[16];
+        if (live) {
 #pragma unroll
-        for (int c0 = 0; c0 < kMlpH3; c0 += 32) {
-            float d[32], v[32];
-            if (live) load_row32(p.dact3[e] + atom * kMlpH3 + c0, d);
-#pragma unroll
-            for (int i = 0; i < 32; i++) {
-                v[i] = live ? g * p.w4[e][c0 + i] * d[i] : 0.0f;
-                sh.act[tid * kMlpActStride + c0 + i] = v[i];
+            for (int i = 0; i < 16; i += 4) {
+                const float4 q = *reinterpret_cast<const float4*>(p.dact3[e] + atom * kMlpH3 + c0 + i);
+                d[i] = q.x; d[i + 1] = q.y; d[i + 2] = q.z; d[i + 3] = q.w;
             }
-            if (live) store_row32(p.dz3[e] + atom * kMlpH3 + c0, v);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            v[i] = live ? g * p.w4[e][c0 + i] * d[i] : 0.0f;
+            sh.act[erow * kMlpActStride + c0 + i] = v[i];
+        }
+        if (live) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(p.dz3[e] + atom * kMlpH3 + c0 + i) =
+                    make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
         }
     }
     __syncthreads();
@@ -144,19 +153,20 @@ __global__ void __launch_bounds__(kMlpTile) mlp_backward_kernel(const MlpBackwar
     const float* step_d[2] = {p.dact2[e], p.dact1[e]};
     float* step_out[2] = {p.dz2[e], p.dz1[e]};
     const int step_k[2] = {kMlpH3, kMlpH2};
+    const int c0 = ecg * 32;
     bool ok = true;
 #pragma unroll 1
     for (int s = 0; s < 2 && ok; s++) {
         ok = mlp_product<SPLIT>(sh, tmem, step_w[s], step_k[s], 0, 128, step_k[s], &parity);
         if (!ok) break;
-        for (int c0 = 0; c0 < 128; c0 += 32) {
+        {
             float v[32], d[32];
             tmem_load32(lane_addr + c0, v);
             if (live) load_row32(step_d[s] + atom * 128 + c0, d);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
                 v[i] = live ? v[i] * d[i] : 0.0f;
-                sh.act[tid * kMlpActStride + c0 + i] = v[i];
+                sh.act[erow * kMlpActStride + c0 + i] = v[i];
             }
             if (live) store_row32(step_out[s] + atom * 128 + c0, v);
         }
@@ -170,11 +180,9 @@ __global__ void __launch_bounds__(kMlpTile) mlp_backward_kernel(const MlpBackwar
         for (int n0 = 0; n0 < kMlpIn && ok; n0 += 128) {
             ok = mlp_product<SPLIT>(sh, tmem, p.w1[e], kMlpH1, n0, 128, kMlpH1, &parity);
             if (!ok) break;
-            for (int c0 = 0; c0 < 128; c0 += 32) {
-                float v[32];
-                tmem_load32(lane_addr + c0, v);
-                if (live) store_row32(p.grad_feat[e] + atom * kMlpIn + n0 + c0, v);
-            }
+            float v[32];
+            tmem_load32(lane_addr + c0, v);
+            if (live) store_row32(p.grad_feat[e] + atom * kMlpIn + n0 + c0, v);
             tc_fence_before();
             __syncthreads();   // the accumulator is overwritten by the next product
         }

@@ -1,11 +1,12 @@
 // Weight and bias gradients of the per-element atomic networks on the Blackwell tensor cores:
 //   dW1 = F^T dZ1 [384 x 128],  dW2 = A1^T dZ2 [128 x 128],  dW3 = A2^T dZ3 [128 x 64],
 //   db_l = column sums of dZ_l,
-// products whose long dimension is the ATOM index.  A CTA takes one range of up to 512 atoms of
+// products whose long dimension is the ATOM index.  A CTA takes one range of atoms (sized on the
+// host so that the whole grid is one wave) of
 // one element and one 128-row block of one weight matrix (three blocks for W1, one each for W2
 // and W3), accumulates its [128 x N] block in tensor memory over the range, and adds it to the
-// output with 16-byte global reductions (the call ADDS to its outputs).  A sixth kind of CTA does
-// the output layer (dw4 = A3^T g, db4 = sum g) with plain loads.
+// output with 16-byte global reductions (the call ADDS to its outputs).  The CTA of the W3 block
+// also does the output layer (dw4 = A3^T g, db4 = sum g) with plain loads.
 // Both MMA operands are K-major with K = atom, so staging TRANSPOSES the row-major activations:
 // a thread reads four consecutive columns of one atom and scatters them to four operand rows.
 //
@@ -17,12 +18,12 @@
 
 namespace ani {
 
-constexpr int kWgradRange = 512;   // atoms per CTA
-constexpr int kWgradBlocks = 6;    // W1 rows 0-127, 128-255, 256-383; W2; W3; the output layer (w4, b4)
+constexpr int kWgradBlocks = 5;    // W1 rows 0-127, 128-255, 256-383; W2; W3 (+ the output layer w4, b4)
 
 struct MlpWgradParams {
     int count[kTypes];
-    int range_start[kTypes + 1];   // prefix of ceil(count / kWgradRange)
+    int range;                     // atoms per CTA, a multiple of 64 chosen so that the grid is one wave
+    int range_start[kTypes + 1];   // prefix of ceil(count / range)
     const float* feat[kTypes];     // [count][384]
     const float* act1[kTypes];     // [count][128]
     const float* act2[kTypes];     // [count][128]
@@ -41,52 +42,8 @@ struct MlpWgradParams {
     float* db4[kTypes];            // [1]
 };
 
-// Stages the transpose of src[atom0 .. atom0+63][col0 .. col0+rows-1] (row stride ld) as an
-// operand chunk: operand row = column of src, operand k = atom.  Atoms past `n_valid` are zero.
-// Returns this thread's partial column sums over the atoms it touched (four columns).
 template <bool SPLIT>
-__device__ __forceinline__ float4 stage_transposed(unsigned char* hi, unsigned char* lo,
-                                                   const float* __restrict__ src, int ld, int col0,
-                                                   int rows, long long atom0, int n_valid)
-{
-    const int tid = threadIdx.x;
-    const int quads = rows >> 2;                 // float4 groups per atom: 32 or 16
-    const int atoms_per_it = kMlpTile / quads;   // 4 or 8
-    const int q = tid % quads, a_in = tid / quads;
-    float4 colsum = make_float4(0.f, 0.f, 0.f, 0.f);
-    constexpr int kBatch = 4;
-    for (int k0 = 0; k0 < kMlpKChunk; k0 += kBatch * atoms_per_it) {
-        float4 vs[kBatch];
-#pragma unroll
-        for (int b = 0; b < kBatch; b++) {   // the loads of a batch are in flight together
-            const int k = k0 + b * atoms_per_it + a_in;
-            vs[b] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (k < n_valid) vs[b] = *reinterpret_cast<const float4*>(src + (size_t)(atom0 + k) * ld + col0 + 4 * q);
-        }
-#pragma unroll
-        for (int b = 0; b < kBatch; b++) {
-            const int k = k0 + b * atoms_per_it + a_in;
-            const float4 v = vs[b];
-            colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
-            const float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int off = operand_offset(4 * q + j, k);
-                if (SPLIT) {
-                    const float h = __uint_as_float(__float_as_uint(e[j]) & 0xffffe000u);
-                    *reinterpret_cast<float*>(hi + off) = h;
-                    *reinterpret_cast<float*>(lo + off) = e[j] - h;
-                } else {
-                    *reinterpret_cast<float*>(hi + off) = e[j];
-                }
-            }
-        }
-    }
-    return colsum;
-}
-
-template <bool SPLIT>
-__global__ void __launch_bounds__(kMlpTile) mlp_wgrad_kernel(const MlpWgradParams p)
+__global__ void __launch_bounds__(kMlpThreads, 1) mlp_wgrad_kernel(const MlpWgradParams p)
 {
     extern __shared__ unsigned char mlp_smem_raw[];
     MlpShared& sh = *reinterpret_cast<MlpShared*>(
@@ -96,28 +53,9 @@ __global__ void __launch_bounds__(kMlpTile) mlp_wgrad_kernel(const MlpWgradParam
     int e = 0;
 #pragma unroll
     for (int t = 1; t < kTypes; t++) e += (int)blockIdx.x >= p.range_start[t] ? 1 : 0;
-    const long long first = (long long)((int)blockIdx.x - p.range_start[e]) * kWgradRange;
-    const int n_here = (int)min((long long)kWgradRange, (long long)p.count[e] - first);
+    const long long first = (long long)((int)blockIdx.x - p.range_start[e]) * p.range;
+    const int n_here = (int)min((long long)p.range, (long long)p.count[e] - first);
     const int blk = blockIdx.y;
-
-    if (blk == 5) {
-        // output layer: dw4 = A3^T g and db4 = sum g over this range; no tensor cores involved
-        const int q = tid & 15, a_in = tid >> 4;      // 16 column quads x 8 atoms per pass
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float gsum = 0.0f;
-        for (int k = a_in; k < n_here; k += 8) {
-            const float g = p.grad_energy[e][first + k];
-            const float4 v = *reinterpret_cast<const float4*>(p.act3[e] + (size_t)(first + k) * kMlpH3 + 4 * q);
-            acc.x += v.x * g; acc.y += v.y * g; acc.z += v.z * g; acc.w += v.w * g;
-            gsum += q == 0 ? g : 0.0f;
-        }
-        atomicAdd(p.dw4[e] + 4 * q + 0, acc.x);
-        atomicAdd(p.dw4[e] + 4 * q + 1, acc.y);
-        atomicAdd(p.dw4[e] + 4 * q + 2, acc.z);
-        atomicAdd(p.dw4[e] + 4 * q + 3, acc.w);
-        if (q == 0) atomicAdd(p.db4[e], gsum);
-        return;
-    }
 
     // which product this CTA computes
     const float* a_src = blk < 3 ? p.feat[e] : (blk == 3 ? p.act1[e] : p.act2[e]);
@@ -175,12 +113,12 @@ __global__ void __launch_bounds__(kMlpTile) mlp_wgrad_kernel(const MlpWgradParam
 
     if (!sh.failed && n_here > 0) {
         tc_fence_after();
-        // thread = row of the weight block (TMEM lane); its N values are contiguous in the output
-        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
-        for (int c0 = 0; c0 < N; c0 += 32) {
+        // warp w: rows 32 (w % 4) .. of the weight block (TMEM lanes), columns 32 (w / 4) ..
+        const int erow = (warp & 3) * 32 + (tid & 31), c0 = (warp >> 2) * 32;
+        if (c0 < N) {
             float v[32];
-            tmem_load32(lane_addr + c0, v);
-            float* dst = out + (size_t)tid * N + c0;
+            tmem_load32(tmem + ((unsigned)((warp & 3) * 32) << 16) + c0, v);
+            float* dst = out + (size_t)erow * N + c0;
 #pragma unroll
             for (int i = 0; i < 32; i += 4)
                 atomicAdd(reinterpret_cast<float4*>(dst + i), make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));
@@ -195,6 +133,24 @@ __global__ void __launch_bounds__(kMlpTile) mlp_wgrad_kernel(const MlpWgradParam
         }
     } else if (sh.failed && tid == 0) {
         report(ANI_ERR_TIMEOUT);
+    }
+    if (blk == 4) {
+        // output layer, done by the CTA with the lightest product: dw4 = A3^T g and db4 = sum g
+        // over this range; no tensor cores involved
+        const int q = tid & 15, a_in = tid >> 4;      // 16 column quads x 32 atoms per pass
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float gsum = 0.0f;
+        for (int k = a_in; k < n_here; k += kMlpThreads / 16) {
+            const float g = p.grad_energy[e][first + k];
+            const float4 v = *reinterpret_cast<const float4*>(p.act3[e] + (size_t)(first + k) * kMlpH3 + 4 * q);
+            acc.x += v.x * g; acc.y += v.y * g; acc.z += v.z * g; acc.w += v.w * g;
+            gsum += q == 0 ? g : 0.0f;
+        }
+        atomicAdd(p.dw4[e] + 4 * q + 0, acc.x);
+        atomicAdd(p.dw4[e] + 4 * q + 1, acc.y);
+        atomicAdd(p.dw4[e] + 4 * q + 2, acc.z);
+        atomicAdd(p.dw4[e] + 4 * q + 3, acc.w);
+        if (q == 0) atomicAdd(p.db4[e], gsum);
     }
     tc_fence_before();
     __syncthreads();

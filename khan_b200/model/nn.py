@@ -105,8 +105,8 @@ class _FusedMlp(torch.autograd.Function):
         keep = []
         for t in range(4):
             w1, b1, w2, b2, w3, b3, w4, b4 = params[8 * t: 8 * t + 8]
-            tr = [w1.detach().t().contiguous(), w2.detach().t().contiguous(),
-                  w3.detach().t().contiguous(), w4.detach().reshape(-1).contiguous()]
+            tr = [w1.detach().contiguous(), w2.detach().contiguous(), w3.detach().contiguous(),
+                  w4.detach().reshape(-1).contiguous()]      # no copies: the kernel reads [in][out]
             keep.extend(tr)
             s = int(starts[t])
             cnt = int(acs[t])
@@ -115,7 +115,7 @@ class _FusedMlp(torch.autograd.Function):
                 return ctypes.c_void_p(tensor.data_ptr() + offset * tensor.element_size()) if live else None
 
             args.features[t] = ptr(features, s * 384)
-            args.w1t[t], args.w2t[t], args.w3t[t], args.w4[t] = (ptr(x) for x in tr)
+            args.w1[t], args.w2[t], args.w3[t], args.w4[t] = (ptr(x) for x in tr)
             args.b1[t], args.b2[t], args.b3[t], args.b4[t] = (ptr(b.detach()) for b in (b1, b2, b3, b4))
             args.energy[t] = ptr(energy, s)
             args.act1[t], args.act2[t], args.act3[t] = (ptr(a, s * a.shape[1]) for a in acts)
@@ -213,6 +213,23 @@ class _FusedMlp(torch.autograd.Function):
         return (grad_feat, None, None, None, None, *grads)
 
 
+class _GatherRows(torch.autograd.Function):
+    """``x[idx]`` whose backward is one scatter-add (torch's own index backward sorts the
+    indices first: five launches instead of two)."""
+
+    @staticmethod
+    def forward(ctx, x, idx):
+        ctx.save_for_backward(idx)
+        ctx.n = x.shape[0]
+        return x[idx]
+
+    @staticmethod
+    def backward(ctx, grad):
+        (idx,) = ctx.saved_tensors
+        out = torch.zeros((ctx.n,) + tuple(grad.shape[1:]), dtype=grad.dtype, device=grad.device)
+        return out.index_add_(0, idx, grad), None
+
+
 class MoleculeNN:
     """One :class:`AtomNN` per element plus the gather back to atom order."""
 
@@ -264,4 +281,4 @@ class MoleculeNN:
     def atom_outputs(self, features: torch.Tensor, acs, gather_idxs: torch.Tensor) -> torch.Tensor:
         """Atomic energies in atom order (``tf.gather(tf.concat(...), gather_idxs)``,
         khan/model/nn.py:171-172)."""
-        return self.atom_energies_sorted(features, acs)[gather_idxs.long()]
+        return _GatherRows.apply(self.atom_energies_sorted(features, acs), gather_idxs.long())
