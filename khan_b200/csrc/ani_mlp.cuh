@@ -70,6 +70,7 @@ struct MlpShared {
     alignas(1024) unsigned char a_lo[kMlpOperandBytes];
     alignas(1024) unsigned char b_lo[kMlpOperandBytes];
     float act[kMlpTile * kMlpActStride];
+    float vec[128];      // the layer's bias (forward) or the output weights w4 (backward)
     alignas(8) unsigned long long mbar;
     unsigned tmem_base;
     int failed;
@@ -225,6 +226,62 @@ __device__ __forceinline__ void staging_slot(int it, int tid, int* row, int* kgr
     *kgroup = (rest & 3) * 4 + ((q >> 3) & 3);
 }
 
+// Per-warp transposition scratch for the epilogues: 32 x 33 floats per warp, carved out of the
+// operand buffers, which are idle while an epilogue runs (the MMAs that read them have finished
+// and the next staging pass rewrites them).  a_hi, b_hi and a_lo are contiguous (96 KiB).
+constexpr int kMlpScratchStride = 33;
+__device__ __forceinline__ float* warp_scratch(MlpShared& sh)
+{
+    return reinterpret_cast<float*>(sh.a_hi) + (threadIdx.x >> 5) * (32 * kMlpScratchStride);
+}
+
+// A 32 x 32 tile that the warp holds as "lane = row, v[32] = columns" goes to global memory
+// (row stride ld) with every 16-byte store instruction covering whole 128-byte row segments
+// (4 rows x 8 lanes), instead of 32 different rows per instruction.  ADD = true adds with
+// 16-byte reductions.  Rows >= rows_valid are skipped.
+template <bool ADD>
+__device__ __forceinline__ void warp_tile_to_global(float* scratch, const float* v, float* gbase, size_t ld,
+                                                    int rows_valid)
+{
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 32; i++) scratch[lane * kMlpScratchStride + i] = v[i];
+    __syncwarp();
+    const int sub = lane >> 3, c = 4 * (lane & 7);
+#pragma unroll
+    for (int r = 0; r < 32; r += 4) {
+        const int rr = r + sub;
+        const float* s = scratch + rr * kMlpScratchStride + c;
+        const float4 q = make_float4(s[0], s[1], s[2], s[3]);
+        if (rr < rows_valid) {
+            float4* dst = reinterpret_cast<float4*>(gbase + (size_t)rr * ld + c);
+            if (ADD) atomicAdd(dst, q); else *dst = q;
+        }
+    }
+    __syncwarp();
+}
+
+// The inverse: a 32 x 32 tile of global memory into "lane = row, v[32] = columns"; rows past
+// rows_valid read as zero.
+__device__ __forceinline__ void warp_tile_from_global(float* scratch, float* v, const float* gbase, size_t ld,
+                                                      int rows_valid)
+{
+    const int lane = threadIdx.x & 31;
+    const int sub = lane >> 3, c = 4 * (lane & 7);
+#pragma unroll
+    for (int r = 0; r < 32; r += 4) {
+        const int rr = r + sub;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rr < rows_valid) q = *reinterpret_cast<const float4*>(gbase + (size_t)rr * ld + c);
+        float* s = scratch + rr * kMlpScratchStride + c;
+        s[0] = q.x; s[1] = q.y; s[2] = q.z; s[3] = q.w;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = scratch[lane * kMlpScratchStride + i];
+    __syncwarp();
+}
+
 // 32 consecutive floats of one row, as eight 16-byte accesses.
 __device__ __forceinline__ void store_row32(float* dst, const float* v)
 {
@@ -330,6 +387,7 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_forward_kernel(const MlpPa
     for (int layer = 0; layer < 3; layer++) {
         const int K = layer_k[layer], N = layer_n[layer];
         const unsigned idesc = instr_desc(kMlpTile, N);
+        if (tid < N) sh.vec[tid] = layer_b[layer][tid];   // read in the epilogue, after several barriers
 #pragma unroll 1
         for (int kc = 0; kc < K; kc += kMlpKChunk) {
             // ---- stage the A chunk (128 atoms x 64) and the B chunk (N outputs x 64); all global
@@ -393,13 +451,16 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_forward_kernel(const MlpPa
             tmem_load32(tmem + ((unsigned)((warp & 3) * 32) << 16) + c0, v);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
-                const float x = v[i] + layer_b[layer][c0 + i];
+                const float x = v[i] + sh.vec[c0 + i];
                 v[i] = mlp_activation<ACT>(x);
                 d[i] = mlp_activation_grad<ACT>(x, v[i]);
                 sh.act[erow * kMlpActStride + c0 + i] = v[i];
             }
-            if (layer_out[layer] && erow < n_rows) store_row32(layer_out[layer] + (size_t)(row0 + erow) * N + c0, v);
-            if (layer_dout[layer] && erow < n_rows) store_row32(layer_dout[layer] + (size_t)(row0 + erow) * N + c0, d);
+            const int tile_row0 = (warp & 3) * 32;
+            const size_t g0 = (size_t)(row0 + tile_row0) * N + c0;
+            float* scratch = warp_scratch(sh);
+            if (layer_out[layer]) warp_tile_to_global<false>(scratch, v, layer_out[layer] + g0, N, n_rows - tile_row0);
+            if (layer_dout[layer]) warp_tile_to_global<false>(scratch, d, layer_dout[layer] + g0, N, n_rows - tile_row0);
         }
         ANI_PHASE(4);
         tc_fence_before();
@@ -410,10 +471,12 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_forward_kernel(const MlpPa
 
     if (!sh.failed) {
         // ---- output layer 64 -> 1: one thread per atom, its last hidden row from shared memory ----
+        if (tid < kMlpH3) sh.vec[tid] = p.w4[e][tid];
+        __syncthreads();
         if (tid < n_rows) {
             float acc = p.b4[e][0];
 #pragma unroll 8
-            for (int i = 0; i < kMlpH3; i++) acc += sh.act[tid * kMlpActStride + i] * p.w4[e][i];
+            for (int i = 0; i < kMlpH3; i++) acc += sh.act[tid * kMlpActStride + i] * sh.vec[i];
             p.energy[e][row0 + tid] = acc;
         }
     } else if (tid == 0) {

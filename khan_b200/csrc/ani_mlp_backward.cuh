@@ -122,29 +122,26 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
     const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
     unsigned parity = 0;
 
-    // ---- dZ3 = g * w4 * D3: 16 of the 64 columns per thread; rows past the end are zero ----
-    {
+    const int tile_row0 = (warp & 3) * 32;          // first row of this warp's 32 x 32 tiles
+    const int tile_rows = n_rows - tile_row0;        // how many of them exist (may be <= 0)
+    const size_t tile_atom0 = (size_t)(row0 + tile_row0);
+    const int c0 = ecg * 32;
+    float* scratch = warp_scratch(sh);
+
+    // ---- dZ3 = g * w4 * D3 (64 columns: the warps of column groups 0 and 1); rows past the end
+    // of the element are zero ----
+    if (tid < kMlpH3) sh.vec[tid] = p.w4[e][tid];
+    __syncthreads();
+    if (c0 < kMlpH3) {
         const float g = live ? p.grad_energy[e][atom] : 0.0f;
-        const int c0 = ecg * 16;
-        float d[16], v[16];
-        if (live) {
+        float d[32], v[32];
+        warp_tile_from_global(scratch, d, p.dact3[e] + tile_atom0 * kMlpH3 + c0, kMlpH3, tile_rows);
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-                const float4 q = *reinterpret_cast<const float4*>(p.dact3[e] + atom * kMlpH3 + c0 + i);
-                d[i] = q.x; d[i + 1] = q.y; d[i + 2] = q.z; d[i + 3] = q.w;
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            v[i] = live ? g * p.w4[e][c0 + i] * d[i] : 0.0f;
+        for (int i = 0; i < 32; i++) {
+            v[i] = g * sh.vec[c0 + i] * d[i];
             sh.act[erow * kMlpActStride + c0 + i] = v[i];
         }
-        if (live) {
-#pragma unroll
-            for (int i = 0; i < 16; i += 4)
-                *reinterpret_cast<float4*>(p.dz3[e] + atom * kMlpH3 + c0 + i) =
-                    make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-        }
+        warp_tile_to_global<false>(scratch, v, p.dz3[e] + tile_atom0 * kMlpH3 + c0, kMlpH3, tile_rows);
     }
     __syncthreads();
 
@@ -153,7 +150,6 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
     const float* step_d[2] = {p.dact2[e], p.dact1[e]};
     float* step_out[2] = {p.dz2[e], p.dz1[e]};
     const int step_k[2] = {kMlpH3, kMlpH2};
-    const int c0 = ecg * 32;
     bool ok = true;
 #pragma unroll 1
     for (int s = 0; s < 2 && ok; s++) {
@@ -162,13 +158,13 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
         {
             float v[32], d[32];
             tmem_load32(lane_addr + c0, v);
-            if (live) load_row32(step_d[s] + atom * 128 + c0, d);
+            warp_tile_from_global(scratch, d, step_d[s] + tile_atom0 * 128 + c0, 128, tile_rows);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
-                v[i] = live ? v[i] * d[i] : 0.0f;
+                v[i] *= d[i];                      // d is zero on rows past the end
                 sh.act[erow * kMlpActStride + c0 + i] = v[i];
             }
-            if (live) store_row32(step_out[s] + atom * 128 + c0, v);
+            warp_tile_to_global<false>(scratch, v, step_out[s] + tile_atom0 * 128 + c0, 128, tile_rows);
         }
         tc_fence_before();
         __syncthreads();
@@ -182,9 +178,9 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
             if (!ok) break;
             float v[32];
             tmem_load32(lane_addr + c0, v);
-            if (live) store_row32(p.grad_feat[e] + atom * kMlpIn + n0 + c0, v);
+            warp_tile_to_global<false>(scratch, v, p.grad_feat[e] + tile_atom0 * kMlpIn + n0 + c0, kMlpIn, tile_rows);
             tc_fence_before();
-            __syncthreads();   // the accumulator is overwritten by the next product
+            __syncthreads();   // the accumulator and the scratch are overwritten by the next product
         }
     }
 

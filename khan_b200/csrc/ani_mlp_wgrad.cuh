@@ -114,14 +114,11 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_wgrad_kernel(const MlpWgra
     if (!sh.failed && n_here > 0) {
         tc_fence_after();
         // warp w: rows 32 (w % 4) .. of the weight block (TMEM lanes), columns 32 (w / 4) ..
-        const int erow = (warp & 3) * 32 + (tid & 31), c0 = (warp >> 2) * 32;
+        const int tile_row0 = (warp & 3) * 32, c0 = (warp >> 2) * 32;
         if (c0 < N) {
             float v[32];
-            tmem_load32(tmem + ((unsigned)((warp & 3) * 32) << 16) + c0, v);
-            float* dst = out + (size_t)erow * N + c0;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-                atomicAdd(reinterpret_cast<float4*>(dst + i), make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));
+            tmem_load32(tmem + ((unsigned)tile_row0 << 16) + c0, v);
+            warp_tile_to_global<true>(warp_scratch(sh), v, out + (size_t)tile_row0 * N + c0, N, 32);
         }
         if (bias_out) {
             // this thread summed columns 4q .. 4q+3 of dZ over the atoms it staged
