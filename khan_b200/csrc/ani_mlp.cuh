@@ -303,43 +303,56 @@ __device__ __forceinline__ void load_row32(const float* src, float* v)
 // an input index for weights stored [in][out]).  Source rows past `n_valid` are zero.  A thread
 // reads four consecutive columns of one source row and scatters them to four operand rows.
 // Returns this thread's partial column sums over the source rows it touched (four columns).
+// Column quad (four consecutive source columns) that this thread handles in stage_transposed
+// for an operand of `rows` rows; the same in every pass.
+__device__ __forceinline__ int transposed_quad(int rows)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    return (warp % (rows >> 5)) * 8 + (lane >> 2);
+}
+
+// Lane mapping: a warp takes 8 column quads x 4 source rows, lane = (quad, source row).  Its
+// loads are four 128-byte row segments; its stores are conflict-free because the bank of an
+// operand element is 4 (row mod 8) + (k mod 4) and each store instruction writes 8 different
+// (row mod 8) -- lanes rotate which of their four values they store -- times 4 different k.
 template <bool SPLIT>
 __device__ __forceinline__ float4 stage_transposed(unsigned char* hi, unsigned char* lo,
                                                    const float* __restrict__ src, int ld, int col0,
-                                                   int rows, long long atom0, int n_valid)
+                                                   int rows, long long r0, int n_valid)
 {
-    const int tid = threadIdx.x;
-    const int quads = rows >> 2;                 // float4 groups per atom: 32 or 16
-    const int atoms_per_it = kMlpThreads / quads;   // 16 or 32
-    const int q = tid % quads, a_in = tid / quads;
-    float4 colsum = make_float4(0.f, 0.f, 0.f, 0.f);
-    // 64 atoms per chunk: 4 passes with 32 quads per atom, 2 with 16; all loads issued first
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ksub = lane & 3, qsub = lane >> 2, rot = qsub >> 1;
+    const int qblocks = rows >> 5;                        // 4 (128 rows) or 2 (64 rows)
+    const int q = (warp % qblocks) * 8 + qsub;
+    constexpr int kWarps = kMlpThreads / 32;
     constexpr int kMaxPasses = 4;
-    const int passes = kMlpKChunk / atoms_per_it;
+    const int passes = qblocks * (kMlpKChunk / 4) / kWarps;   // 4 or 2
+    float4 colsum = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 vs[kMaxPasses];
 #pragma unroll
-    for (int b = 0; b < kMaxPasses; b++) {
-        const int k = b * atoms_per_it + a_in;
+    for (int b = 0; b < kMaxPasses; b++) {                // all loads of the chunk in flight together
+        const int k = ((b * kWarps + warp) / qblocks) * 4 + ksub;
         vs[b] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (b < passes && k < n_valid)
-            vs[b] = *reinterpret_cast<const float4*>(src + (size_t)(atom0 + k) * ld + col0 + 4 * q);
+            vs[b] = *reinterpret_cast<const float4*>(src + (size_t)(r0 + k) * ld + col0 + 4 * q);
     }
 #pragma unroll
     for (int b = 0; b < kMaxPasses; b++) {
         if (b >= passes) break;
-        const int k = b * atoms_per_it + a_in;
+        const int k = ((b * kWarps + warp) / qblocks) * 4 + ksub;
         const float4 v = vs[b];
         colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
-        const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const int off = operand_offset(4 * q + j, k);
+            const int jj = (j + rot) & 3;
+            const float val = jj == 0 ? v.x : (jj == 1 ? v.y : (jj == 2 ? v.z : v.w));
+            const int off = operand_offset(4 * q + jj, k);
             if (SPLIT) {
-                const float h = __uint_as_float(__float_as_uint(e[j]) & 0xffffe000u);
+                const float h = __uint_as_float(__float_as_uint(val) & 0xffffe000u);
                 *reinterpret_cast<float*>(hi + off) = h;
-                *reinterpret_cast<float*>(lo + off) = e[j] - h;
+                *reinterpret_cast<float*>(lo + off) = val - h;
             } else {
-                *reinterpret_cast<float*>(hi + off) = e[j];
+                *reinterpret_cast<float*>(hi + off) = val;
             }
         }
     }

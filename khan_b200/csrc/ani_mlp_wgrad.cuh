@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_wgrad_kernel(const MlpWgra
         }
         if (bias_out) {
             // this thread summed columns 4q .. 4q+3 of dZ over the atoms it staged
-            const int quads = N >> 2, q = tid % quads;
+            const int q = transposed_quad(N);
             atomicAdd(bias_out + 4 * q + 0, bias_acc.x);
             atomicAdd(bias_out + 4 * q + 1, bias_acc.y);
             atomicAdd(bias_out + 4 * q + 2, bias_acc.z);
