@@ -96,7 +96,7 @@ int sort_static_scratch(int** out)
     return ANI_OK;
 }
 
-// Featurizer launch shapes: NW warps per CTA, kSlotsPerMol / NW CTAs per molecule, one warp
+// Featurizer launch shapes: NW warps per CTA, (slots per molecule) / NW CTAs per molecule, one warp
 // per central atom.  The capacities bound the neighbours of one element kept in shared memory
 // per central atom (atoms with more take the streaming path).
 constexpr int kNW = 4;
@@ -119,6 +119,18 @@ template <typename K> int featurizer_grid(K kernel, size_t smem, int n_mols, int
     const long long needed = (long long)n_mols * kGroup;
     *grid = (int)(needed < resident ? needed : resident);
     return ANI_OK;
+}
+
+// Work-list slots per molecule for a launch, as a shift: the smallest power of two that is not
+// below the mean atoms per molecule, between kNW and kSlotsPerMol.  With one slot per atom of a
+// typical molecule few items are empty (every empty item costs its warp a dependent load) and
+// larger molecules simply give some slots a second atom.
+int pick_slot_shift(long long n_atoms, int n_mols)
+{
+    const long long mean = n_mols > 0 ? (n_atoms + n_mols - 1) / n_mols : 1;
+    int shift = 2;   // kNW = 4 slots
+    while ((1 << shift) < mean && (1 << shift) < kSlotsPerMol) shift++;
+    return shift;
 }
 
 template <typename K> int set_smem(K kernel, size_t bytes)
@@ -168,13 +180,14 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
         if (int rc = featurizer_grid(kernel, smem, 1 << 24, &cached_resident)) return rc;
         cached_grid_dev = dev;
     }
-    const long long needed = (long long)n_mols * (kSlotsPerMol / kNW);
+    const int slot_shift = pick_slot_shift(n_atoms, n_mols);
+    const long long needed = (long long)n_mols * ((1 << slot_shift) / kNW);
     int grid = (int)(needed < cached_resident ? needed : cached_resident);
 #ifdef ANI_PHASE_TIMING
     if (getenv("ANI_DEBUG_FULL_GRID")) grid = (int)needed;   // tuning builds: one item per warp
 #endif
     kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
-        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, oh, oc, on, oo, acs_host[0],
+        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, slot_shift, sis, oh, oc, on, oo, acs_host[0],
         acs_host[1], acs_host[2], acs_host[3]);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
@@ -219,10 +232,11 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
         if (int rc = featurizer_grid(kernel, smem, 1 << 24, &cached_resident)) return rc;
         cached_grid_dev = dev;
     }
-    const long long needed = (long long)n_mols * (kSlotsPerMol / kNW);
+    const int slot_shift = pick_slot_shift(n_atoms, n_mols);
+    const long long needed = (long long)n_mols * ((1 << slot_shift) / kNW);
     const int grid = (int)(needed < cached_resident ? needed : cached_resident);
     kernel<<<grid, kNW * kWarp, smem, st>>>(
-        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, gh, gc, gn, go, gx, gy, gz,
+        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, slot_shift, sis, gh, gc, gn, go, gx, gy, gz,
         acs_host[0], acs_host[1], acs_host[2], acs_host[3]);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
@@ -254,10 +268,11 @@ int featurize_grad_inverse_impl(const T* xs, const T* ys, const T* zs, const int
         if (int rc = featurizer_grid(kernel, smem, 1 << 24, &cached_resident)) return rc;
         configured_dev = dev;
     }
-    const long long needed = (long long)n_mols * (kSlotsPerMol / kNW);
+    const int slot_shift = pick_slot_shift(n_atoms, n_mols);
+    const long long needed = (long long)n_mols * ((1 << slot_shift) / kNW);
     const int grid = (int)(needed < cached_resident ? needed : cached_resident);
     kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
-        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, vx, vy, vz, oh, oc, on, oo,
+        xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, slot_shift, sis, vx, vy, vz, oh, oc, on, oo,
         acs_host[0], acs_host[1], acs_host[2], acs_host[3]);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;

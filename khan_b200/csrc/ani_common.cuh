@@ -2,10 +2,11 @@
 // warp helpers, per-central-atom neighbour lists and the enumeration of neighbour pairs.
 //
 // Work decomposition used by every featurizer kernel: ONE WARP PER CENTRAL ATOM, no cooperation
-// between the warps of a CTA (no __syncthreads anywhere).  The work list has kSlotsPerMol items
-// per molecule; item (m, s) covers atoms s, s + kSlotsPerMol, ... of molecule m and is empty
-// when the molecule has fewer atoms.  The grid is persistent (a few CTAs per SM): warp w takes
-// items w, w + W, w + 2W, ... (W = warps in the grid, a multiple of kSlotsPerMol), so an empty
+// between the warps of a CTA (no __syncthreads anywhere).  The work list has S = 2^slot_shift
+// items per molecule (S is chosen per launch: the power of two next above the mean molecule
+// size, 4 <= S <= 32); item (m, s) covers atoms s, s + S, ... of molecule m and is empty when
+// the molecule has fewer atoms.  The grid is persistent (a few CTAs per SM): warp w takes
+// items w, w + W, w + 2W, ... (W = warps in the grid, a multiple of 32), so an empty
 // item costs one cached load instead of a CTA slot, and consecutive warps -- the warps of one
 // CTA -- work on the same molecule, whose coordinates they read straight from global memory
 // (L1 hits).  Each warp keeps the neighbourhood of its atom in its own slice of shared memory.
@@ -21,7 +22,7 @@ namespace ani {
 
 constexpr int kWarp = 32;
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kSlotsPerMol = 32;  // warps per molecule in the grid
+constexpr int kSlotsPerMol = 32;  // most work-list slots per molecule; a launch uses 2^slot_shift <= 32 of them
 
 // First device-side problem seen since the last read (0 = none).  One word per device: the
 // variable is instantiated once per loaded module and context.  (This header is included by
@@ -113,11 +114,13 @@ __device__ __forceinline__ void load4(const double* p, double* v)
 // The k-th item of a warp: item index -> (molecule, slot).  The slot is rotated by the round
 // number k so that a warp does not see the same slot -- hence the same chance of an empty item
 // -- in every round.  Requires the number of warps in the grid to be a multiple of
-// kSlotsPerMol, which makes the rotation a permutation of each molecule's slots.
-__device__ __forceinline__ void item_to_work(long long item, int round, int* m, int* slot)
+// the slots per molecule (2^slot_shift), which makes the rotation a permutation of each
+// molecule's slots.
+__device__ __forceinline__ void item_to_work(long long item, int round, int slot_shift, int* m, int* slot)
 {
-    *m = (int)(item / kSlotsPerMol);
-    *slot = ((int)(item % kSlotsPerMol) + 11 * round) & (kSlotsPerMol - 1);
+    const int mask = (1 << slot_shift) - 1;
+    *m = (int)(item >> slot_shift);
+    *slot = (((int)item & mask) + 11 * round) & mask;
 }
 
 // One molecule as the kernels see it, validated.

@@ -117,7 +117,7 @@ template <typename T, int NW, int CAPT, int CAPR>
 __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS : 1)
     featurize_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
                      const int* __restrict__ types, const int* __restrict__ mol_offsets,
-                     const int* __restrict__ mol_counts, int n_mols, int n_atoms,
+                     const int* __restrict__ mol_counts, int n_mols, int n_atoms, int slot_shift,
                      const int* __restrict__ scatter, T* out_h, T* out_c, T* out_n, T* out_o,
                      int acs0, int acs1, int acs2, int acs3)
 {
@@ -136,12 +136,12 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
     __syncwarp();
     ANI_PHASE(14);
 
-    const long long n_items = (long long)n_mols * kSlotsPerMol;
+    const long long n_items = (long long)n_mols << slot_shift;
     const int grid_warps = gridDim.x * NW;
     int round = 0;
     for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
         int m, slot;
-        item_to_work(item, round, &m, &slot);
+        item_to_work(item, round, slot_shift, &m, &slot);
         const int n_of_m = mol_counts[m];
         if (n_of_m < 0) report(ANI_ERR_BAD_INDEX);   // forces the load to complete here in timing builds
         ANI_PHASE(15);
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS :
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
 
-        for (int i = slot; i < n; i += kSlotsPerMol) {
+        for (int i = slot; i < n; i += 1 << slot_shift) {
             const int gi = base + i;
             // everything this atom needs from global memory is requested before any of it is used
             const int j_first = lane < n ? lane : 0;

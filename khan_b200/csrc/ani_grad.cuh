@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
     featurize_grad_kernel(const T* __restrict__ xs, const T* __restrict__ ys,
                           const T* __restrict__ zs, const int* __restrict__ types,
                           const int* __restrict__ mol_offsets, const int* __restrict__ mol_counts,
-                          int n_mols, int n_atoms, const int* __restrict__ scatter,
+                          int n_mols, int n_atoms, int slot_shift, const int* __restrict__ scatter,
                           const T* __restrict__ gh, const T* __restrict__ gc,
                           const T* __restrict__ gn, const T* __restrict__ go, T* gx, T* gy, T* gz,
                           int acs0, int acs1, int acs2, int acs3)
@@ -138,18 +138,18 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
     ANI_PHASE_DECL;
 
-    const long long n_items = (long long)n_mols * kSlotsPerMol;
+    const long long n_items = (long long)n_mols << slot_shift;
     const int grid_warps = gridDim.x * NW;
     int round = 0;
     for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
         int m, slot;
-        item_to_work(item, round, &m, &slot);
+        item_to_work(item, round, slot_shift, &m, &slot);
         if (slot >= mol_counts[m]) continue;   // empty item: one cached load
         MolRange mol;
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
 
-        for (int i = slot; i < n; i += kSlotsPerMol) {
+        for (int i = slot; i < n; i += 1 << slot_shift) {
             const int gi = base + i;
             // everything this atom needs from global memory is requested before any of it is used
             const int j_first = lane < n ? lane : 0;

@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(NW* kWarp)
     featurize_grad_inverse_kernel(const T* __restrict__ xs, const T* __restrict__ ys,
                                   const T* __restrict__ zs, const int* __restrict__ types,
                                   const int* __restrict__ mol_offsets,
-                                  const int* __restrict__ mol_counts, int n_mols, int n_atoms,
+                                  const int* __restrict__ mol_counts, int n_mols, int n_atoms, int slot_shift,
                                   const int* __restrict__ scatter, const T* __restrict__ vx,
                                   const T* __restrict__ vy, const T* __restrict__ vz, T* out_h,
                                   T* out_c, T* out_n, T* out_o, int acs0, int acs1, int acs2,
@@ -79,18 +79,18 @@ __global__ void __launch_bounds__(NW* kWarp)
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
-    const long long n_items = (long long)n_mols * kSlotsPerMol;
+    const long long n_items = (long long)n_mols << slot_shift;
     const int grid_warps = gridDim.x * NW;
     int round = 0;
     for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
         int m, slot;
-        item_to_work(item, round, &m, &slot);
+        item_to_work(item, round, slot_shift, &m, &slot);
         if (slot >= mol_counts[m]) continue;
         MolRange mol;
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
 
-        for (int i = slot; i < n; i += kSlotsPerMol) {
+        for (int i = slot; i < n; i += 1 << slot_shift) {
             const int gi = base + i;
             const int ti = checked_type(types[gi]);
             const int srow = scatter[gi];
