@@ -18,7 +18,7 @@ CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
 HEADERS = ["ani_params.h", "ani_common.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_grad.cuh",
-           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh"]
+           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -13,7 +13,7 @@
 #include "ani_featurize.cuh"
 #include "ani_grad.cuh"
 #include "ani_grad_inverse.cuh"
-#include "ani_mlp.cuh"
+#include "ani_mlp_forward.cuh"
 #include "ani_mlp_backward.cuh"
 #include "ani_mlp_wgrad.cuh"
 #include "ani_charge.cuh"

@@ -1,24 +1,19 @@
-// Per-element atomic network 384-128-128-64-1, forward pass, fused into one kernel on the
-// Blackwell tensor cores (tcgen05.mma, kind::tf32, accumulators in tensor memory).
+// Shared pieces of the atomic-network kernels (per-element stacks 384-128-128-64-1 on the
+// Blackwell tensor cores: tcgen05.mma kind::tf32, accumulators in tensor memory): parameter
+// blocks, the shared-memory layout, PTX wrappers, activations and the epilogue helpers.
+// The kernels are in ani_mlp_forward.cuh, ani_mlp_backward.cuh and ani_mlp_wgrad.cuh; the operand
+// pipeline they share is in ani_mlp_pipe.cuh.
 //
-// What it computes is AtomNN of the reference (khan/model/nn.py:39-67): for the atoms of one
-// element, A1 = act(F W1 + b1), A2 = act(A1 W2 + b2), A3 = act(A2 W3 + b3), E = A3 w4 + b4, with
-// F the [n, 384] feature rows of that element.  MoleculeNN (khan/model/nn.py:165-172) runs four
-// of these, one per element; here one launch covers all four (each CTA takes a tile of 128 atoms
-// of one element).
-//
-// Structure of one CTA (512 threads, tile = 128 atoms):
+// Common structure of a CTA (512 threads, tile = 128 rows of the accumulator):
 //   * operands are staged by all threads into shared memory in the K-major, no-swizzle
-//     core-matrix layout that tcgen05.mma reads (8 rows x 16 bytes per core matrix), 64 values
-//     of K at a time; weights are read in the reference's layout ([in][out]) and transposed
-//     while they are staged;
+//     core-matrix layout that tcgen05.mma reads (8 rows x 16 bytes per core matrix), 32 values
+//     of K per pipeline stage; weights are read in the reference's layout ([in][out]);
 //   * one thread issues the MMAs (M = 128, N = 128 or 64, K = 8 per instruction) and commits them
-//     to an mbarrier; everybody waits on it (bounded spin: on timeout the kernel records an
-//     error, frees its tensor memory and returns);
-//   * the epilogue reads the accumulator with tcgen05.ld (warp w: rows 32 (w % 4) .., columns
-//     32 (w / 4) ..), adds the bias, applies the activation and writes the values to shared
-//     memory, where they become the A operand of the next layer; the last layer (64 -> 1) is a
-//     dot product per atom from shared memory.
+//     to the stage's mbarrier; waits are bounded (on timeout the kernel records an error, frees
+//     its tensor memory and returns);
+//   * epilogues read the accumulator with tcgen05.ld (warp w: rows 32 (w % 4) .., columns
+//     32 (w / 4) ..) and move 32 x 32 tiles to and from global memory through a per-warp
+//     transposition scratch, so that every 16-byte access covers whole 128-byte row segments.
 // With SPLIT = true every operand is staged as a high part (the value with its low 13 mantissa
 // bits cleared, exact in tf32) and a low part (the remainder), and hi*hi + hi*lo + lo*hi are
 // accumulated: three MMAs per step give products that are accurate to about 2^-21 instead of
@@ -32,13 +27,10 @@ namespace ani {
 constexpr int kMlpIn = 384, kMlpH1 = 128, kMlpH2 = 128, kMlpH3 = 64;
 constexpr int kMlpTile = 128;             // atoms per CTA = MMA M
 constexpr int kMlpThreads = 512;          // 16 warps: warp w reads TMEM lanes 32 (w % 4) .., columns 32 (w / 4) ..
-constexpr int kMlpKChunk = 64;            // K values staged per step
 constexpr int kMlpLbo = 128;              // bytes between core matrices adjacent in K
-constexpr int kMlpSbo = (kMlpKChunk / 4) * 128;   // bytes between 8-row groups (2048)
-constexpr int kMlpOperandBytes = kMlpTile * kMlpKChunk * 4;   // 32 KiB
+constexpr int kMlpOperandBytes = 32 * 1024;   // four of these make the 128 KiB operand area
 constexpr int kMlpActStride = 129;        // floats per row of the activation buffer (bank-conflict free)
 constexpr int kMlpTmemCols = 128;
-constexpr int kMlpStageSteps = kMlpTile * (kMlpKChunk / 4) / kMlpThreads;   // staging slots per thread and chunk (4)
 constexpr unsigned kMlpSpinLimit = 1u << 24;
 
 enum MlpActivation { kActCelu = 0, kActGaussian = 1, kActNormal = 2, kActSoftplus = 3 };
@@ -71,7 +63,7 @@ struct MlpShared {
     alignas(1024) unsigned char b_lo[kMlpOperandBytes];
     float act[kMlpTile * kMlpActStride];
     float vec[128];      // the layer's bias (forward) or the output weights w4 (backward)
-    alignas(8) unsigned long long mbar;
+    alignas(8) unsigned long long stage_bar[2];   // one mbarrier per operand stage of the pipeline
     unsigned tmem_base;
     int failed;
 };
@@ -123,16 +115,6 @@ __device__ __forceinline__ void fence_async_smem()
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// Shared-memory matrix descriptor: K-major, no swizzle, descriptor version 1.
-__device__ __forceinline__ unsigned long long smem_desc(unsigned byte_addr)
-{
-    unsigned long long d = 0;
-    d |= (unsigned long long)((byte_addr & 0x3ffff) >> 4);
-    d |= (unsigned long long)(kMlpLbo >> 4) << 16;
-    d |= (unsigned long long)(kMlpSbo >> 4) << 32;
-    d |= 1ull << 46;
-    return d;
-}
 // Instruction descriptor for kind::tf32: D = f32, A = B = tf32, both K-major, M x N.
 __device__ __forceinline__ unsigned instr_desc(int m, int n)
 {
@@ -189,41 +171,6 @@ template <int ACT> __device__ __forceinline__ float mlp_activation_grad(float x,
     if (ACT == kActGaussian) return -2.0f * x * a;
     if (ACT == kActNormal) return -x * a;
     return 1.0f / (1.0f + expf(-x));
-}
-
-// Position of element (row, k) of a staged chunk in the core-matrix layout, in bytes.
-__device__ __forceinline__ int operand_offset(int row, int k)
-{
-    return (row >> 3) * kMlpSbo + (k >> 2) * kMlpLbo + (row & 7) * 16 + (k & 3) * 4;
-}
-
-// Stores four consecutive K values of one row as the high (tf32-exact) and low parts.
-template <bool SPLIT>
-__device__ __forceinline__ void stage4(unsigned char* hi, unsigned char* lo, int row, int k, float4 v)
-{
-    const int off = operand_offset(row, k);
-    if (SPLIT) {
-        float4 h, l;
-        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-        l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-        *reinterpret_cast<float4*>(hi + off) = h;
-        *reinterpret_cast<float4*>(lo + off) = l;
-    } else {
-        *reinterpret_cast<float4*>(hi + off) = v;
-    }
-}
-
-// (row, group of 4 K values) handled by thread `tid` in staging step `it`: 8 consecutive rows
-// first (one 128-byte core matrix per 8 lanes, conflict-free), then 4 adjacent K groups.
-__device__ __forceinline__ void staging_slot(int it, int tid, int* row, int* kgroup)
-{
-    const int q = it * kMlpThreads + tid;
-    const int rest = q >> 5;
-    *row = (rest >> 2) * 8 + (q & 7);
-    *kgroup = (rest & 3) * 4 + ((q >> 3) & 3);
 }
 
 // Per-warp transposition scratch for the epilogues: 32 x 33 floats per warp, carved out of the
@@ -296,207 +243,6 @@ __device__ __forceinline__ void load_row32(const float* src, float* v)
         const float4 q = *reinterpret_cast<const float4*>(src + i);
         v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
     }
-}
-
-// Stages the TRANSPOSE of src[r0 .. r0+63][col0 .. col0+rows-1] (row stride ld) as an operand
-// chunk: operand row = column of src, operand k = row of src (an atom for the weight gradients,
-// an input index for weights stored [in][out]).  Source rows past `n_valid` are zero.  A thread
-// reads four consecutive columns of one source row and scatters them to four operand rows.
-// Returns this thread's partial column sums over the source rows it touched (four columns).
-// Column quad (four consecutive source columns) that this thread handles in stage_transposed
-// for an operand of `rows` rows; the same in every pass.
-__device__ __forceinline__ int transposed_quad(int rows)
-{
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    return (warp % (rows >> 5)) * 8 + (lane >> 2);
-}
-
-// Lane mapping: a warp takes 8 column quads x 4 source rows, lane = (quad, source row).  Its
-// loads are four 128-byte row segments; its stores are conflict-free because the bank of an
-// operand element is 4 (row mod 8) + (k mod 4) and each store instruction writes 8 different
-// (row mod 8) -- lanes rotate which of their four values they store -- times 4 different k.
-template <bool SPLIT>
-__device__ __forceinline__ float4 stage_transposed(unsigned char* hi, unsigned char* lo,
-                                                   const float* __restrict__ src, int ld, int col0,
-                                                   int rows, long long r0, int n_valid)
-{
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ksub = lane & 3, qsub = lane >> 2, rot = qsub >> 1;
-    const int qblocks = rows >> 5;                        // 4 (128 rows) or 2 (64 rows)
-    const int q = (warp % qblocks) * 8 + qsub;
-    constexpr int kWarps = kMlpThreads / 32;
-    constexpr int kMaxPasses = 4;
-    const int passes = qblocks * (kMlpKChunk / 4) / kWarps;   // 4 or 2
-    float4 colsum = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 vs[kMaxPasses];
-#pragma unroll
-    for (int b = 0; b < kMaxPasses; b++) {                // all loads of the chunk in flight together
-        const int k = ((b * kWarps + warp) / qblocks) * 4 + ksub;
-        vs[b] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (b < passes && k < n_valid)
-            vs[b] = *reinterpret_cast<const float4*>(src + (size_t)(r0 + k) * ld + col0 + 4 * q);
-    }
-#pragma unroll
-    for (int b = 0; b < kMaxPasses; b++) {
-        if (b >= passes) break;
-        const int k = ((b * kWarps + warp) / qblocks) * 4 + ksub;
-        const float4 v = vs[b];
-        colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int jj = (j + rot) & 3;
-            const float val = jj == 0 ? v.x : (jj == 1 ? v.y : (jj == 2 ? v.z : v.w));
-            const int off = operand_offset(4 * q + jj, k);
-            if (SPLIT) {
-                const float h = __uint_as_float(__float_as_uint(val) & 0xffffe000u);
-                *reinterpret_cast<float*>(hi + off) = h;
-                *reinterpret_cast<float*>(lo + off) = val - h;
-            } else {
-                *reinterpret_cast<float*>(hi + off) = val;
-            }
-        }
-    }
-    return colsum;
-}
-
-template <int ACT, bool SPLIT>
-__global__ void __launch_bounds__(kMlpThreads, 1) mlp_forward_kernel(const MlpParams p)
-{
-    extern __shared__ unsigned char mlp_smem_raw[];
-    // the launch asks for sizeof(MlpShared) + 1024 bytes so that the struct can be aligned here
-    MlpShared& sh = *reinterpret_cast<MlpShared*>(
-        (reinterpret_cast<uintptr_t>(mlp_smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int tid = threadIdx.x, warp = tid >> 5;
-    // epilogue role of this thread: one accumulator row (TMEM lane), one group of 32 columns
-    const int erow = (warp & 3) * 32 + (tid & 31), ecg = warp >> 2;
-
-    int e = 0;
-#pragma unroll
-    for (int t = 1; t < kTypes; t++) e += (int)blockIdx.x >= p.tile_start[t] ? 1 : 0;
-    const int row0 = ((int)blockIdx.x - p.tile_start[e]) * kMlpTile;
-    const int n_rows = min(kMlpTile, p.count[e] - row0);
-
-    if (warp == 0) tmem_alloc(&sh.tmem_base, kMlpTmemCols);
-    if (tid == 0) {
-        mbar_init(&sh.mbar, 1);
-        sh.failed = 0;
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const unsigned tmem = sh.tmem_base;
-    unsigned parity = 0;
-    bool ok = true;
-    ANI_PHASE_DECL;
-
-    const float* layer_w[3] = {p.w1[e], p.w2[e], p.w3[e]};
-    const float* layer_b[3] = {p.b1[e], p.b2[e], p.b3[e]};
-    float* layer_out[3] = {p.act1[e], p.act2[e], p.act3[e]};
-    float* layer_dout[3] = {p.dact1[e], p.dact2[e], p.dact3[e]};
-    const int layer_k[3] = {kMlpIn, kMlpH1, kMlpH2};
-    const int layer_n[3] = {kMlpH1, kMlpH2, kMlpH3};
-
-#pragma unroll 1
-    for (int layer = 0; layer < 3; layer++) {
-        const int K = layer_k[layer], N = layer_n[layer];
-        const unsigned idesc = instr_desc(kMlpTile, N);
-        if (tid < N) sh.vec[tid] = layer_b[layer][tid];   // read in the epilogue, after several barriers
-#pragma unroll 1
-        for (int kc = 0; kc < K; kc += kMlpKChunk) {
-            // ---- stage the A chunk (128 atoms x 64) and the B chunk (N outputs x 64); all global
-            // loads of the chunk are issued before any of them is used ----
-            float4 av[kMlpStageSteps];
-            int rows[kMlpStageSteps], kgs[kMlpStageSteps];
-#pragma unroll
-            for (int j = 0; j < kMlpStageSteps; j++) {
-                staging_slot(j, tid, &rows[j], &kgs[j]);
-                const int row = rows[j], kg = kgs[j];
-                av[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (layer == 0) {
-                    if (row < n_rows)
-                        av[j] = *reinterpret_cast<const float4*>(p.feat[e] + (size_t)(row0 + row) * kMlpIn + kc + kg * 4);
-                } else {
-                    const float* src = sh.act + row * kMlpActStride + kc + kg * 4;
-                    av[j] = make_float4(src[0], src[1], src[2], src[3]);
-                }
-            }
-            // B[n = out][k = in] = W[k][n]: the weights are read as stored ([in][out]) and transposed
-            stage_transposed<SPLIT>(sh.b_hi, sh.b_lo, layer_w[layer], N, 0, N, kc, kMlpKChunk);
-#pragma unroll
-            for (int j = 0; j < kMlpStageSteps; j++) stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, av[j]);
-            ANI_PHASE(0);
-            fence_async_smem();
-            __syncthreads();
-            ANI_PHASE(1);
-            if (tid == 0) {
-                tc_fence_after();
-                const unsigned a_hi = smem_u32(sh.a_hi), b_hi = smem_u32(sh.b_hi);
-                const unsigned a_lo = smem_u32(sh.a_lo), b_lo = smem_u32(sh.b_lo);
-#pragma unroll
-                for (int ks = 0; ks < kMlpKChunk / 8; ks++) {
-                    const unsigned step = ks * 2 * kMlpLbo;
-                    const bool first = kc == 0 && ks == 0;
-                    mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_hi + step), idesc, !first);
-                    if (SPLIT) {
-                        mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_lo + step), idesc, true);
-                        mma_tf32(tmem, smem_desc(a_lo + step), smem_desc(b_hi + step), idesc, true);
-                    }
-                }
-                mma_commit(&sh.mbar);
-            }
-            // operands may be overwritten, and the accumulator read, only after the MMAs finish
-            if (ok && !mbar_wait(&sh.mbar, parity)) ok = false;
-            parity ^= 1u;
-            if (!ok) sh.failed = 1;
-            ANI_PHASE(2);
-            __syncthreads();
-            ANI_PHASE(3);
-            if (sh.failed) break;
-        }
-        if (sh.failed) break;
-        tc_fence_after();
-        // ---- epilogue: bias, activation and its derivative; the row goes back to shared memory
-        // as the next layer's A operand (the last hidden layer included: the output layer reads
-        // it from there) ----
-        const int c0 = ecg * 32;
-        if (c0 < N) {
-            float v[32], d[32];
-            tmem_load32(tmem + ((unsigned)((warp & 3) * 32) << 16) + c0, v);
-#pragma unroll
-            for (int i = 0; i < 32; i++) {
-                const float x = v[i] + sh.vec[c0 + i];
-                v[i] = mlp_activation<ACT>(x);
-                d[i] = mlp_activation_grad<ACT>(x, v[i]);
-                sh.act[erow * kMlpActStride + c0 + i] = v[i];
-            }
-            const int tile_row0 = (warp & 3) * 32;
-            const size_t g0 = (size_t)(row0 + tile_row0) * N + c0;
-            float* scratch = warp_scratch(sh);
-            if (layer_out[layer]) warp_tile_to_global<false>(scratch, v, layer_out[layer] + g0, N, n_rows - tile_row0);
-            if (layer_dout[layer]) warp_tile_to_global<false>(scratch, d, layer_dout[layer] + g0, N, n_rows - tile_row0);
-        }
-        ANI_PHASE(4);
-        tc_fence_before();
-        __syncthreads();
-        ANI_PHASE(5);
-    }
-    ANI_PHASE_FLUSH;
-
-    if (!sh.failed) {
-        // ---- output layer 64 -> 1: one thread per atom, its last hidden row from shared memory ----
-        if (tid < kMlpH3) sh.vec[tid] = p.w4[e][tid];
-        __syncthreads();
-        if (tid < n_rows) {
-            float acc = p.b4[e][0];
-#pragma unroll 8
-            for (int i = 0; i < kMlpH3; i++) acc += sh.act[tid * kMlpActStride + i] * sh.vec[i];
-            p.energy[e][row0 + tid] = acc;
-        }
-    } else if (tid == 0) {
-        report(ANI_ERR_TIMEOUT);
-    }
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, kMlpTmemCols);
 }
 
 }  // namespace ani

@@ -17,7 +17,7 @@
 // B operand is [N = in][K = out], which is W as stored.
 #pragma once
 
-#include "ani_mlp.cuh"
+#include "ani_mlp_pipe.cuh"
 
 namespace ani {
 
@@ -37,60 +37,6 @@ struct MlpBackwardParams {
     float* dz3[kTypes];          // [count][64]
     float* grad_feat[kTypes];    // optional [count][384]
 };
-
-// One product  acc[128 x N] = A[128 x K] * B^T  with A in sh.act (row stride kMlpActStride) and
-// B = w[(n0 + n) * ldw + k] in global memory, K a multiple of 64.  Returns false on timeout.
-template <bool SPLIT>
-__device__ __forceinline__ bool mlp_product(MlpShared& sh, unsigned tmem, const float* __restrict__ w, int ldw,
-                                            int n0, int N, int K, unsigned* parity)
-{
-    const int tid = threadIdx.x;
-    const unsigned idesc = instr_desc(kMlpTile, N);
-    bool ok = true;
-#pragma unroll 1
-    for (int kc = 0; kc < K; kc += kMlpKChunk) {
-        float4 wv[kMlpStageSteps];
-        int rows[kMlpStageSteps], kgs[kMlpStageSteps];
-#pragma unroll
-        for (int j = 0; j < kMlpStageSteps; j++) {   // the weight loads of the chunk are in flight together
-            staging_slot(j, tid, &rows[j], &kgs[j]);
-            wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (rows[j] < N)
-                wv[j] = *reinterpret_cast<const float4*>(w + (size_t)(n0 + rows[j]) * ldw + kc + kgs[j] * 4);
-        }
-#pragma unroll
-        for (int j = 0; j < kMlpStageSteps; j++) {
-            const float* src = sh.act + rows[j] * kMlpActStride + kc + kgs[j] * 4;
-            stage4<SPLIT>(sh.a_hi, sh.a_lo, rows[j], kgs[j] * 4, make_float4(src[0], src[1], src[2], src[3]));
-            if (rows[j] < N) stage4<SPLIT>(sh.b_hi, sh.b_lo, rows[j], kgs[j] * 4, wv[j]);
-        }
-        fence_async_smem();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            const unsigned a_hi = smem_u32(sh.a_hi), b_hi = smem_u32(sh.b_hi);
-            const unsigned a_lo = smem_u32(sh.a_lo), b_lo = smem_u32(sh.b_lo);
-#pragma unroll
-            for (int ks = 0; ks < kMlpKChunk / 8; ks++) {
-                const unsigned step = ks * 2 * kMlpLbo;
-                const bool first = kc == 0 && ks == 0;
-                mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_hi + step), idesc, !first);
-                if (SPLIT) {
-                    mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_lo + step), idesc, true);
-                    mma_tf32(tmem, smem_desc(a_lo + step), smem_desc(b_hi + step), idesc, true);
-                }
-            }
-            mma_commit(&sh.mbar);
-        }
-        if (ok && !mbar_wait(&sh.mbar, *parity)) ok = false;
-        *parity ^= 1u;
-        if (!ok) sh.failed = 1;
-        __syncthreads();
-        if (sh.failed) return false;
-    }
-    tc_fence_after();
-    return true;
-}
 
 template <bool SPLIT>
 __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpBackwardParams p)
@@ -112,7 +58,8 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
 
     if (warp == 0) tmem_alloc(&sh.tmem_base, kMlpTmemCols);
     if (tid == 0) {
-        mbar_init(&sh.mbar, 1);
+        mbar_init(&sh.stage_bar[0], 1);
+        mbar_init(&sh.stage_bar[1], 1);
         sh.failed = 0;
     }
     tc_fence_before();
@@ -120,7 +67,8 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
     tc_fence_after();
     const unsigned tmem = sh.tmem_base;
     const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
-    unsigned parity = 0;
+    PipeState ps;
+    const DirectShared<SPLIT> a_sh{sh.act};
 
     const int tile_row0 = (warp & 3) * 32;          // first row of this warp's 32 x 32 tiles
     const int tile_rows = n_rows - tile_row0;        // how many of them exist (may be <= 0)
@@ -153,7 +101,9 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
     bool ok = true;
 #pragma unroll 1
     for (int s = 0; s < 2 && ok; s++) {
-        ok = mlp_product<SPLIT>(sh, tmem, step_w[s], step_k[s], 0, 128, step_k[s], &parity);
+        // B[n = in][k = out] = W[n][k]: the weights as stored
+        DirectGlobal<SPLIT> b_w{step_w[s], (size_t)step_k[s], 128, 128, 0};
+        ok = pipe_product<SPLIT, true>(sh, tmem, 128, step_k[s] / kPipeK, true, ps, b_w, a_sh, b_w) && pipe_drain(sh, ps);
         if (!ok) break;
         {
             float v[32], d[32];
@@ -174,7 +124,8 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
     if (ok && p.grad_feat[e]) {
 #pragma unroll 1
         for (int n0 = 0; n0 < kMlpIn && ok; n0 += 128) {
-            ok = mlp_product<SPLIT>(sh, tmem, p.w1[e], kMlpH1, n0, 128, kMlpH1, &parity);
+            DirectGlobal<SPLIT> b_w{p.w1[e] + (size_t)n0 * kMlpH1, (size_t)kMlpH1, 128, 128, 0};
+            ok = pipe_product<SPLIT, true>(sh, tmem, 128, kMlpH1 / kPipeK, true, ps, b_w, a_sh, b_w) && pipe_drain(sh, ps);
             if (!ok) break;
             float v[32];
             tmem_load32(lane_addr + c0, v);

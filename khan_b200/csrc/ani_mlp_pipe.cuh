@@ -1,0 +1,265 @@
+// Two-stage operand pipeline shared by the three atomic-network kernels.
+//
+// A product  acc[128 x N] (+)= A[128 x K] * B[N x K]^T  is cut into chunks of 32 values of K.  The
+// 128 KiB operand area of MlpShared holds two stages (each: A hi, A lo, B hi, B lo, 16 KiB
+// apiece); while the tensor core works on one stage the 512 threads fill the other, and the global
+// loads of chunk c+1 are issued before the barrier of chunk c, so that neither the MMAs nor the
+// load latency sit on the critical path.  Each stage has its own mbarrier; a stage is refilled
+// only after the commit of the MMAs that read it has been seen (bounded wait).
+//
+// Operand sources (where a chunk comes from and how it is laid out):
+//   DirectGlobal   rows of a row-major global matrix, K along the row (16-byte loads and stores);
+//   DirectShared   rows of the activation buffer in shared memory;
+//   Transposed     the transpose of a row-major global matrix: operand row = source column,
+//                  K = source row (weights stored [in][out]; activations with K = atom).
+#pragma once
+
+#include "ani_mlp.cuh"
+
+namespace ani {
+
+constexpr int kPipeK = 32;                                  // K values per stage
+constexpr int kPipeSbo = (kPipeK / 4) * 128;                // 1024 bytes between 8-row groups
+constexpr int kPipeOperandBytes = kMlpTile * kPipeK * 4;    // 16 KiB
+constexpr int kPipeStageBytes = 4 * kPipeOperandBytes;      // A hi, A lo, B hi, B lo
+static_assert(2 * kPipeStageBytes == 4 * kMlpOperandBytes, "two stages fill the operand area");
+
+__device__ __forceinline__ int pipe_offset(int row, int k)
+{
+    return (row >> 3) * kPipeSbo + (k >> 2) * kMlpLbo + (row & 7) * 16 + (k & 3) * 4;
+}
+__device__ __forceinline__ unsigned long long pipe_desc(unsigned byte_addr)
+{
+    unsigned long long d = 0;
+    d |= (unsigned long long)((byte_addr & 0x3ffff) >> 4);
+    d |= (unsigned long long)(kMlpLbo >> 4) << 16;
+    d |= (unsigned long long)(kPipeSbo >> 4) << 32;
+    d |= 1ull << 46;
+    return d;
+}
+
+template <bool SPLIT> __device__ __forceinline__ void pipe_store4(unsigned char* hi, unsigned char* lo, int off, float4 v)
+{
+    if (SPLIT) {
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+        l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+        *reinterpret_cast<float4*>(hi + off) = h;
+        *reinterpret_cast<float4*>(lo + off) = l;
+    } else {
+        *reinterpret_cast<float4*>(hi + off) = v;
+    }
+}
+template <bool SPLIT> __device__ __forceinline__ void pipe_store1(unsigned char* hi, unsigned char* lo, int off, float v)
+{
+    if (SPLIT) {
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        *reinterpret_cast<float*>(hi + off) = h;
+        *reinterpret_cast<float*>(lo + off) = v - h;
+    } else {
+        *reinterpret_cast<float*>(hi + off) = v;
+    }
+}
+
+// (row, group of 4 K values) of direct-staging slot j of this thread: 8 consecutive rows first
+// (one 128-byte core matrix per 8 lanes, conflict-free stores), then 4 adjacent K groups.
+// 128 rows x 8 groups = 1024 slots, two per thread.
+__device__ __forceinline__ void pipe_slot(int j, int* row, int* kgroup)
+{
+    const int q = j * kMlpThreads + (int)threadIdx.x;
+    const int rest = q >> 5;
+    *row = (rest >> 1) * 8 + (q & 7);
+    *kgroup = (rest & 1) * 4 + ((q >> 3) & 3);
+}
+
+struct PipeRegs {
+    float4 v[2];
+};
+
+// Rows [0, rows) of a row-major global matrix (row stride ld); rows >= rows_valid read as zero;
+// chunk c covers columns k0 + 32 c .. + 31.
+template <bool SPLIT> struct DirectGlobal {
+    const float* base;
+    size_t ld;
+    int rows, rows_valid, k0;
+    __device__ __forceinline__ void load(int c, PipeRegs& r) const
+    {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            int row, kg;
+            pipe_slot(j, &row, &kg);
+            r.v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < rows_valid) r.v[j] = *reinterpret_cast<const float4*>(base + (size_t)row * ld + k0 + c * kPipeK + kg * 4);
+        }
+    }
+    __device__ __forceinline__ void store(const PipeRegs& r, unsigned char* hi, unsigned char* lo)
+    {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            int row, kg;
+            pipe_slot(j, &row, &kg);
+            if (row < rows) pipe_store4<SPLIT>(hi, lo, pipe_offset(row, kg * 4), r.v[j]);
+        }
+    }
+};
+
+// All 128 rows of the activation buffer in shared memory (row stride kMlpActStride).
+template <bool SPLIT> struct DirectShared {
+    const float* act;
+    __device__ __forceinline__ void load(int, PipeRegs&) const {}
+    __device__ __forceinline__ void store_chunk(int c, unsigned char* hi, unsigned char* lo) const
+    {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            int row, kg;
+            pipe_slot(j, &row, &kg);
+            const float* src = act + row * kMlpActStride + c * kPipeK + kg * 4;
+            pipe_store4<SPLIT>(hi, lo, pipe_offset(row, kg * 4), make_float4(src[0], src[1], src[2], src[3]));
+        }
+    }
+};
+
+// Column quad (four consecutive source columns) of this thread in a Transposed source with
+// `rows` operand rows; the same for every chunk.
+__device__ __forceinline__ int transposed_quad(int rows)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    return (warp % (rows >> 5)) * 8 + (lane >> 2);
+}
+
+// The transpose of src[r0 + 32 c + k][col0 + row] (row stride ld): operand row = source column
+// (rows = 128 or 64 of them), K = source row; source rows >= n_valid (counted from r0) are zero.
+// Lane mapping: a warp takes 8 column quads x 4 source rows, lane = (quad, source row): loads are
+// four 128-byte row segments; stores are conflict-free because the bank of an operand element
+// is 4 (row mod 8) + (k mod 4) and each store instruction writes 8 different (row mod 8) -- lanes
+// rotate which of their four values they store -- times 4 different k.
+// colsum accumulates this thread's column sums (four columns) over everything it staged.
+template <bool SPLIT> struct Transposed {
+    const float* base;
+    size_t ld;
+    int col0, rows;
+    long long r0;
+    int n_valid;
+    float4 colsum;
+    __device__ __forceinline__ int passes() const { return (rows >> 5) * (kPipeK / 4) / (kMlpThreads / 32); }   // 2 or 1
+    __device__ __forceinline__ int k_of(int b) const
+    {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        return ((b * (kMlpThreads / 32) + warp) / (rows >> 5)) * 4 + (lane & 3);
+    }
+    __device__ __forceinline__ void load(int c, PipeRegs& r) const
+    {
+        const int q = transposed_quad(rows);
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const int k = c * kPipeK + k_of(b);
+            r.v[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b < passes() && k < n_valid)
+                r.v[b] = *reinterpret_cast<const float4*>(base + (size_t)(r0 + k) * ld + col0 + 4 * q);
+        }
+    }
+    __device__ __forceinline__ void store(const PipeRegs& r, unsigned char* hi, unsigned char* lo)
+    {
+        const int lane = threadIdx.x & 31;
+        const int q = transposed_quad(rows), rot = lane >> 3;
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            if (b >= passes()) break;
+            const int k = k_of(b);
+            const float4 v = r.v[b];
+            colsum.x += v.x; colsum.y += v.y; colsum.z += v.z; colsum.w += v.w;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int jj = (j + rot) & 3;
+                const float val = jj == 0 ? v.x : (jj == 1 ? v.y : (jj == 2 ? v.z : v.w));
+                pipe_store1<SPLIT>(hi, lo, pipe_offset(4 * q + jj, k), val);
+            }
+        }
+    }
+};
+
+struct PipeState {
+    unsigned chunks = 0;          // chunks issued so far in this kernel (stage = chunks & 1)
+    unsigned parity0 = 0, parity1 = 0;
+    bool pending0 = false, pending1 = false;
+    bool ok = true;
+};
+
+// Waits (bounded) for the MMAs that last read stage s, if any are outstanding.
+__device__ __forceinline__ void pipe_wait_stage(MlpShared& sh, PipeState& ps, int s)
+{
+    bool& pending = s ? ps.pending1 : ps.pending0;
+    unsigned& parity = s ? ps.parity1 : ps.parity0;
+    if (!pending) return;
+    if (ps.ok && !mbar_wait(&sh.stage_bar[s], parity)) {
+        ps.ok = false;
+        sh.failed = 1;
+    }
+    parity ^= 1u;
+    pending = false;
+}
+
+// acc (+)= A * B^T over `nchunks` chunks.  `fresh` = overwrite the accumulator with the first
+// chunk.  ASHARED selects the activation buffer as the A source (a_sh) instead of a_src.
+// Returns false after a timeout (uniform across the CTA).
+template <bool SPLIT, bool ASHARED, class ASrc, class BSrc>
+__device__ __forceinline__ bool pipe_product(MlpShared& sh, unsigned tmem, int N, int nchunks, bool fresh, PipeState& ps,
+                                             ASrc& a_src, const DirectShared<SPLIT>& a_sh, BSrc& b_src)
+{
+    const unsigned idesc = instr_desc(kMlpTile, N);
+    PipeRegs ra, rb;
+    if (!ASHARED) a_src.load(0, ra);
+    b_src.load(0, rb);
+#pragma unroll 1
+    for (int c = 0; c < nchunks; c++) {
+        const int s = (int)(ps.chunks & 1u);
+        unsigned char* stage = sh.a_hi + s * kPipeStageBytes;
+        pipe_wait_stage(sh, ps, s);
+        if (ASHARED) a_sh.store_chunk(c, stage, stage + kPipeOperandBytes);
+        else a_src.store(ra, stage, stage + kPipeOperandBytes);
+        b_src.store(rb, stage + 2 * kPipeOperandBytes, stage + 3 * kPipeOperandBytes);
+        if (c + 1 < nchunks) {           // next chunk's loads fly during the barrier and the wait
+            if (!ASHARED) a_src.load(c + 1, ra);
+            b_src.load(c + 1, rb);
+        }
+        fence_async_smem();
+        __syncthreads();
+        if (sh.failed) return false;
+        if (threadIdx.x == 0) {
+            tc_fence_after();
+            const unsigned a_hi = smem_u32(stage), a_lo = a_hi + kPipeOperandBytes;
+            const unsigned b_hi = a_hi + 2 * kPipeOperandBytes, b_lo = a_hi + 3 * kPipeOperandBytes;
+#pragma unroll
+            for (int ks = 0; ks < kPipeK / 8; ks++) {
+                const unsigned step = ks * 2 * kMlpLbo;
+                const bool first = fresh && c == 0 && ks == 0;
+                mma_tf32(tmem, pipe_desc(a_hi + step), pipe_desc(b_hi + step), idesc, !first);
+                if (SPLIT) {
+                    mma_tf32(tmem, pipe_desc(a_hi + step), pipe_desc(b_lo + step), idesc, true);
+                    mma_tf32(tmem, pipe_desc(a_lo + step), pipe_desc(b_hi + step), idesc, true);
+                }
+            }
+            mma_commit(&sh.stage_bar[s]);
+        }
+        if (s) ps.pending1 = true; else ps.pending0 = true;
+        ps.chunks++;
+    }
+    return true;
+}
+
+// Waits for every outstanding MMA (before an epilogue reads the accumulator or reuses the operand
+// area as scratch).  Returns false after a timeout (uniform across the CTA).
+__device__ __forceinline__ bool pipe_drain(MlpShared& sh, PipeState& ps)
+{
+    pipe_wait_stage(sh, ps, 0);
+    pipe_wait_stage(sh, ps, 1);
+    __syncthreads();
+    if (sh.failed) return false;
+    tc_fence_after();
+    return true;
+}
+
+}  // namespace ani

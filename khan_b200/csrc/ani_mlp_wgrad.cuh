@@ -14,7 +14,7 @@
 // under khan/training/trainer_multi_tower.py:396-397).
 #pragma once
 
-#include "ani_mlp.cuh"
+#include "ani_mlp_pipe.cuh"
 
 namespace ani {
 
@@ -68,51 +68,24 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_wgrad_kernel(const MlpWgra
 
     if (warp == 0) tmem_alloc(&sh.tmem_base, kMlpTmemCols);
     if (tid == 0) {
-        mbar_init(&sh.mbar, 1);
+        mbar_init(&sh.stage_bar[0], 1);
+        mbar_init(&sh.stage_bar[1], 1);
         sh.failed = 0;
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sh.tmem_base;
-    const unsigned idesc = instr_desc(kMlpTile, N);
-    unsigned parity = 0;
-    bool ok = true;
-    float4 bias_acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    PipeState ps;
+    const DirectShared<SPLIT> unused_sh{sh.act};
+    // both operands are transposes with K = atom: A[m = in][k] = X[atom k][in m], B[n = out][k] = dZ[atom k][out n]
+    Transposed<SPLIT> a_x{a_src, (size_t)a_ld, a_col0, 128, first, n_here, make_float4(0.f, 0.f, 0.f, 0.f)};
+    Transposed<SPLIT> b_dz{b_src, (size_t)N, 0, N, first, n_here, make_float4(0.f, 0.f, 0.f, 0.f)};
+    const int nchunks = (n_here + kPipeK - 1) / kPipeK;
+    const bool ok = pipe_product<SPLIT, false>(sh, tmem, N, nchunks, true, ps, a_x, unused_sh, b_dz) && pipe_drain(sh, ps);
+    const float4 bias_acc = b_dz.colsum;
 
-#pragma unroll 1
-    for (int k0 = 0; k0 < n_here; k0 += kMlpKChunk) {
-        const int n_valid = min(kMlpKChunk, n_here - k0);
-        stage_transposed<SPLIT>(sh.a_hi, sh.a_lo, a_src, a_ld, a_col0, 128, first + k0, n_valid);
-        const float4 cs = stage_transposed<SPLIT>(sh.b_hi, sh.b_lo, b_src, N, 0, N, first + k0, n_valid);
-        bias_acc.x += cs.x; bias_acc.y += cs.y; bias_acc.z += cs.z; bias_acc.w += cs.w;
-        fence_async_smem();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            const unsigned a_hi = smem_u32(sh.a_hi), b_hi = smem_u32(sh.b_hi);
-            const unsigned a_lo = smem_u32(sh.a_lo), b_lo = smem_u32(sh.b_lo);
-#pragma unroll
-            for (int ks = 0; ks < kMlpKChunk / 8; ks++) {
-                const unsigned step = ks * 2 * kMlpLbo;
-                const bool first_mma = k0 == 0 && ks == 0;
-                mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_hi + step), idesc, !first_mma);
-                if (SPLIT) {
-                    mma_tf32(tmem, smem_desc(a_hi + step), smem_desc(b_lo + step), idesc, true);
-                    mma_tf32(tmem, smem_desc(a_lo + step), smem_desc(b_hi + step), idesc, true);
-                }
-            }
-            mma_commit(&sh.mbar);
-        }
-        if (ok && !mbar_wait(&sh.mbar, parity)) ok = false;
-        parity ^= 1u;
-        if (!ok) sh.failed = 1;
-        __syncthreads();
-        if (sh.failed) break;
-    }
-
-    if (!sh.failed && n_here > 0) {
-        tc_fence_after();
+    if (ok && n_here > 0) {
         // warp w: rows 32 (w % 4) .. of the weight block (TMEM lanes), columns 32 (w / 4) ..
         const int tile_row0 = (warp & 3) * 32, c0 = (warp >> 2) * 32;
         if (c0 < N) {
@@ -128,7 +101,7 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_wgrad_kernel(const MlpWgra
             atomicAdd(bias_out + 4 * q + 2, bias_acc.z);
             atomicAdd(bias_out + 4 * q + 3, bias_acc.w);
         }
-    } else if (sh.failed && tid == 0) {
+    } else if (!ok && tid == 0) {
         report(ANI_ERR_TIMEOUT);
     }
     if (blk == 4) {
