@@ -336,7 +336,7 @@ template <int ACT, bool SPLIT> int mlp_launch(const MlpParams& p, int n_tiles, c
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<n_tiles, kMlpThreads, smem, st>>>(p);
+    kernel<<<n_tiles, kMlpAllThreads, smem, st>>>(p);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
@@ -352,7 +352,7 @@ template <bool SPLIT> int mlp_backward_launch(const MlpBackwardParams& p, int n_
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<n_tiles, kMlpThreads, smem, st>>>(p);
+    kernel<<<n_tiles, kMlpAllThreads, smem, st>>>(p);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }
@@ -368,7 +368,7 @@ template <bool SPLIT> int mlp_wgrad_launch(const MlpWgradParams& p, int n_ranges
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
     }
-    kernel<<<dim3(n_ranges, kWgradBlocks), kMlpThreads, smem, st>>>(p);
+    kernel<<<dim3(n_ranges, kWgradBlocks), kMlpAllThreads, smem, st>>>(p);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;
 }

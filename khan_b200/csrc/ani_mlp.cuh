@@ -4,13 +4,14 @@
 // The kernels are in ani_mlp_forward.cuh, ani_mlp_backward.cuh and ani_mlp_wgrad.cuh; the operand
 // pipeline they share is in ani_mlp_pipe.cuh.
 //
-// Common structure of a CTA (512 threads, tile = 128 rows of the accumulator):
+// Common structure of a CTA (512 + 32 threads, tile = 128 rows of the accumulator):
 //   * operands are staged by all threads into shared memory in the K-major, no-swizzle
 //     core-matrix layout that tcgen05.mma reads (8 rows x 16 bytes per core matrix), 32 values
 //     of K per pipeline stage; weights are read in the reference's layout ([in][out]);
-//   * one thread issues the MMAs (M = 128, N = 128 or 64, K = 8 per instruction) and commits them
-//     to the stage's mbarrier; waits are bounded (on timeout the kernel records an error, frees
-//     its tensor memory and returns);
+//   * a seventeenth warp does nothing but wait for a filled stage, issue its MMAs (M = 128,
+//     N = 128 or 64, K = 8 per instruction) and commit them to the stage's mbarrier, so that the
+//     producers never stall behind the tensor-core queue; every wait is bounded (on timeout the
+//     kernel records an error, frees its tensor memory and returns);
 //   * epilogues read the accumulator with tcgen05.ld (warp w: rows 32 (w % 4) .., columns
 //     32 (w / 4) ..) and move 32 x 32 tiles to and from global memory through a per-warp
 //     transposition scratch, so that every 16-byte access covers whole 128-byte row segments.
@@ -26,7 +27,8 @@ namespace ani {
 
 constexpr int kMlpIn = 384, kMlpH1 = 128, kMlpH2 = 128, kMlpH3 = 64;
 constexpr int kMlpTile = 128;             // atoms per CTA = MMA M
-constexpr int kMlpThreads = 512;          // 16 warps: warp w reads TMEM lanes 32 (w % 4) .., columns 32 (w / 4) ..
+constexpr int kMlpThreads = 512;          // 16 producer / epilogue warps: warp w reads TMEM lanes 32 (w % 4) .., columns 32 (w / 4) ..
+constexpr int kMlpAllThreads = kMlpThreads + 32;   // plus one warp that only issues the MMAs
 constexpr int kMlpLbo = 128;              // bytes between core matrices adjacent in K
 constexpr int kMlpOperandBytes = 32 * 1024;   // four of these make the 128 KiB operand area
 constexpr int kMlpActStride = 129;        // floats per row of the activation buffer (bank-conflict free)
@@ -63,7 +65,8 @@ struct MlpShared {
     alignas(1024) unsigned char b_lo[kMlpOperandBytes];
     float act[kMlpTile * kMlpActStride];
     float vec[128];      // the layer's bias (forward) or the output weights w4 (backward)
-    alignas(8) unsigned long long stage_bar[2];   // one mbarrier per operand stage of the pipeline
+    alignas(8) unsigned long long stage_bar[2];   // per operand stage: the MMAs that read it have finished
+    alignas(8) unsigned long long full_bar[2];    // per operand stage: all 512 producers have filled it
     unsigned tmem_base;
     int failed;
 };
@@ -97,6 +100,12 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     }
     return false;
 }
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Barrier among the 512 producer / epilogue threads only (the MMA warp does not take part).
+__device__ __forceinline__ void producer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(unsigned* dst_smem, unsigned cols)
 {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),

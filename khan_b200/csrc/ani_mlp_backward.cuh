@@ -39,7 +39,7 @@ struct MlpBackwardParams {
 };
 
 template <bool SPLIT>
-__global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpBackwardParams p)
+__global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_backward_kernel(const MlpBackwardParams p)
 {
     extern __shared__ unsigned char mlp_smem_raw[];
     MlpShared& sh = *reinterpret_cast<MlpShared*>(
@@ -60,82 +60,96 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_backward_kernel(const MlpB
     if (tid == 0) {
         mbar_init(&sh.stage_bar[0], 1);
         mbar_init(&sh.stage_bar[1], 1);
+        mbar_init(&sh.full_bar[0], kMlpThreads);
+        mbar_init(&sh.full_bar[1], kMlpThreads);
         sh.failed = 0;
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sh.tmem_base;
-    const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
-    PipeState ps;
-    const DirectShared<SPLIT> a_sh{sh.act};
-
-    const int tile_row0 = (warp & 3) * 32;          // first row of this warp's 32 x 32 tiles
-    const int tile_rows = n_rows - tile_row0;        // how many of them exist (may be <= 0)
-    const size_t tile_atom0 = (size_t)(row0 + tile_row0);
-    const int c0 = ecg * 32;
-    float* scratch = warp_scratch(sh);
-
-    // ---- dZ3 = g * w4 * D3 (64 columns: the warps of column groups 0 and 1); rows past the end
-    // of the element are zero ----
-    if (tid < kMlpH3) sh.vec[tid] = p.w4[e][tid];
-    __syncthreads();
-    if (c0 < kMlpH3) {
-        const float g = live ? p.grad_energy[e][atom] : 0.0f;
-        float d[32], v[32];
-        warp_tile_from_global(scratch, d, p.dact3[e] + tile_atom0 * kMlpH3 + c0, kMlpH3, tile_rows);
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-            v[i] = g * sh.vec[c0 + i] * d[i];
-            sh.act[erow * kMlpActStride + c0 + i] = v[i];
-        }
-        warp_tile_to_global<false>(scratch, v, p.dz3[e] + tile_atom0 * kMlpH3 + c0, kMlpH3, tile_rows);
-    }
-    __syncthreads();
-
-    // ---- dZ2 = (dZ3 W3^T) * D2 and dZ1 = (dZ2 W2^T) * D1 ----
-    const float* step_w[2] = {p.w3[e], p.w2[e]};
-    const float* step_d[2] = {p.dact2[e], p.dact1[e]};
-    float* step_out[2] = {p.dz2[e], p.dz1[e]};
     const int step_k[2] = {kMlpH3, kMlpH2};
-    bool ok = true;
-#pragma unroll 1
-    for (int s = 0; s < 2 && ok; s++) {
-        // B[n = in][k = out] = W[n][k]: the weights as stored
-        DirectGlobal<SPLIT> b_w{step_w[s], (size_t)step_k[s], 128, 128, 0};
-        ok = pipe_product<SPLIT, true>(sh, tmem, 128, step_k[s] / kPipeK, true, ps, b_w, a_sh, b_w) && pipe_drain(sh, ps);
-        if (!ok) break;
-        {
-            float v[32], d[32];
-            tmem_load32(lane_addr + c0, v);
-            warp_tile_from_global(scratch, d, step_d[s] + tile_atom0 * 128 + c0, 128, tile_rows);
+    const bool want_feat = p.grad_feat[e] != nullptr;
+
+    if (warp == kMlpThreads / 32) {
+        // ---- the MMA warp: the two products of the chain, then three for the feature gradient ----
+        IssueState is;
+        pipe_issue<SPLIT>(sh, tmem, 128, step_k[0] / kPipeK, true, is);
+        pipe_issue<SPLIT>(sh, tmem, 128, step_k[1] / kPipeK, true, is);
+        if (want_feat)
+            for (int n0 = 0; n0 < kMlpIn; n0 += 128) pipe_issue<SPLIT>(sh, tmem, 128, kMlpH1 / kPipeK, true, is);
+    } else {
+        // ---- producers / epilogue warps ----
+        const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
+        PipeState ps;
+        const DirectShared<SPLIT> a_sh{sh.act};
+        const int tile_row0 = (warp & 3) * 32;          // first row of this warp's 32 x 32 tiles
+        const int tile_rows = n_rows - tile_row0;        // how many of them exist (may be <= 0)
+        const size_t tile_atom0 = (size_t)(row0 + tile_row0);
+        const int c0 = ecg * 32;
+        float* scratch = warp_scratch(sh);
+
+        // ---- dZ3 = g * w4 * D3 (64 columns: the warps of column groups 0 and 1); rows past the
+        // end of the element are zero ----
+        if (tid < kMlpH3) sh.vec[tid] = p.w4[e][tid];
+        producer_sync();
+        if (c0 < kMlpH3) {
+            const float g = live ? p.grad_energy[e][atom] : 0.0f;
+            float d[32], v[32];
+            warp_tile_from_global(scratch, d, p.dact3[e] + tile_atom0 * kMlpH3 + c0, kMlpH3, tile_rows);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
-                v[i] *= d[i];                      // d is zero on rows past the end
+                v[i] = g * sh.vec[c0 + i] * d[i];
                 sh.act[erow * kMlpActStride + c0 + i] = v[i];
             }
-            warp_tile_to_global<false>(scratch, v, step_out[s] + tile_atom0 * 128 + c0, 128, tile_rows);
+            warp_tile_to_global<false>(scratch, v, p.dz3[e] + tile_atom0 * kMlpH3 + c0, kMlpH3, tile_rows);
         }
-        tc_fence_before();
-        __syncthreads();
-    }
+        producer_sync();
 
-    // ---- dF = dZ1 W1^T, 128 feature columns at a time ----
-    if (ok && p.grad_feat[e]) {
+        // ---- dZ2 = (dZ3 W3^T) * D2 and dZ1 = (dZ2 W2^T) * D1 ----
+        const float* step_w[2] = {p.w3[e], p.w2[e]};
+        const float* step_d[2] = {p.dact2[e], p.dact1[e]};
+        float* step_out[2] = {p.dz2[e], p.dz1[e]};
+        bool ok = true;
 #pragma unroll 1
-        for (int n0 = 0; n0 < kMlpIn && ok; n0 += 128) {
-            DirectGlobal<SPLIT> b_w{p.w1[e] + (size_t)n0 * kMlpH1, (size_t)kMlpH1, 128, 128, 0};
-            ok = pipe_product<SPLIT, true>(sh, tmem, 128, kMlpH1 / kPipeK, true, ps, b_w, a_sh, b_w) && pipe_drain(sh, ps);
+        for (int s = 0; s < 2 && ok; s++) {
+            // B[n = in][k = out] = W[n][k]: the weights as stored
+            DirectGlobal<SPLIT> b_w{step_w[s], (size_t)step_k[s], 128, 128, 0};
+            pipe_produce<SPLIT, true>(sh, step_k[s] / kPipeK, ps, b_w, a_sh, b_w);
+            ok = pipe_drain(sh, ps);
             if (!ok) break;
-            float v[32];
-            tmem_load32(lane_addr + c0, v);
-            warp_tile_to_global<false>(scratch, v, p.grad_feat[e] + tile_atom0 * kMlpIn + n0 + c0, kMlpIn, tile_rows);
+            {
+                float v[32], d[32];
+                tmem_load32(lane_addr + c0, v);
+                warp_tile_from_global(scratch, d, step_d[s] + tile_atom0 * 128 + c0, 128, tile_rows);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    v[i] *= d[i];                      // d is zero on rows past the end
+                    sh.act[erow * kMlpActStride + c0 + i] = v[i];
+                }
+                warp_tile_to_global<false>(scratch, v, step_out[s] + tile_atom0 * 128 + c0, 128, tile_rows);
+            }
             tc_fence_before();
-            __syncthreads();   // the accumulator and the scratch are overwritten by the next product
+            producer_sync();
         }
-    }
 
-    if (sh.failed && tid == 0) report(ANI_ERR_TIMEOUT);
+        // ---- dF = dZ1 W1^T, 128 feature columns at a time ----
+        if (ok && want_feat) {
+#pragma unroll 1
+            for (int n0 = 0; n0 < kMlpIn && ok; n0 += 128) {
+                DirectGlobal<SPLIT> b_w{p.w1[e] + (size_t)n0 * kMlpH1, (size_t)kMlpH1, 128, 128, 0};
+                pipe_produce<SPLIT, true>(sh, kMlpH1 / kPipeK, ps, b_w, a_sh, b_w);
+                ok = pipe_drain(sh, ps);
+                if (!ok) break;
+                float v[32];
+                tmem_load32(lane_addr + c0, v);
+                warp_tile_to_global<false>(scratch, v, p.grad_feat[e] + tile_atom0 * kMlpIn + n0 + c0, kMlpIn, tile_rows);
+                tc_fence_before();
+                producer_sync();   // the accumulator and the scratch are overwritten by the next product
+            }
+        }
+        if (!ok && tid == 0) report(ANI_ERR_TIMEOUT);
+    }
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, kMlpTmemCols);
 }

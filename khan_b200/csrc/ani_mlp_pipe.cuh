@@ -2,10 +2,11 @@
 //
 // A product  acc[128 x N] (+)= A[128 x K] * B[N x K]^T  is cut into chunks of 32 values of K.  The
 // 128 KiB operand area of MlpShared holds two stages (each: A hi, A lo, B hi, B lo, 16 KiB
-// apiece); while the tensor core works on one stage the 512 threads fill the other, and the global
-// loads of chunk c+1 are issued before the barrier of chunk c, so that neither the MMAs nor the
-// load latency sit on the critical path.  Each stage has its own mbarrier; a stage is refilled
-// only after the commit of the MMAs that read it has been seen (bounded wait).
+// apiece); while the tensor core works on one stage the 512 producer threads fill the other, and
+// the global loads of chunk c+1 are issued before chunk c is handed over, so that neither the MMAs
+// nor the load latency sit on the critical path.  Hand-over is by mbarriers only: producers
+// arrive on the stage's "full" barrier; the MMA warp waits for it, issues, and commits to the
+// stage's "done" barrier, which the producers wait for before refilling.  All waits are bounded.
 //
 // Operand sources (where a chunk comes from and how it is laid out):
 //   DirectGlobal   rows of a row-major global matrix, K along the row (16-byte loads and stores);
@@ -202,14 +203,13 @@ __device__ __forceinline__ void pipe_wait_stage(MlpShared& sh, PipeState& ps, in
     pending = false;
 }
 
-// acc (+)= A * B^T over `nchunks` chunks.  `fresh` = overwrite the accumulator with the first
-// chunk.  ASHARED selects the activation buffer as the A source (a_sh) instead of a_src.
-// Returns false after a timeout (uniform across the CTA).
+// Producer side of  acc (+)= A * B^T  over `nchunks` chunks: fills stage after stage and
+// signals each one.  ASHARED selects the activation buffer as the A source (a_sh) instead of
+// a_src.  Never blocks without a bound; a timeout is reported by pipe_drain.
 template <bool SPLIT, bool ASHARED, class ASrc, class BSrc>
-__device__ __forceinline__ bool pipe_product(MlpShared& sh, unsigned tmem, int N, int nchunks, bool fresh, PipeState& ps,
-                                             ASrc& a_src, const DirectShared<SPLIT>& a_sh, BSrc& b_src)
+__device__ __forceinline__ void pipe_produce(MlpShared& sh, int nchunks, PipeState& ps, ASrc& a_src,
+                                             const DirectShared<SPLIT>& a_sh, BSrc& b_src)
 {
-    const unsigned idesc = instr_desc(kMlpTile, N);
     PipeRegs ra, rb;
     if (!ASHARED) a_src.load(0, ra);
     b_src.load(0, rb);
@@ -221,16 +221,41 @@ __device__ __forceinline__ bool pipe_product(MlpShared& sh, unsigned tmem, int N
         if (ASHARED) a_sh.store_chunk(c, stage, stage + kPipeOperandBytes);
         else a_src.store(ra, stage, stage + kPipeOperandBytes);
         b_src.store(rb, stage + 2 * kPipeOperandBytes, stage + 3 * kPipeOperandBytes);
-        if (c + 1 < nchunks) {           // next chunk's loads fly during the barrier and the wait
+        if (c + 1 < nchunks) {           // the next chunk's loads fly while this one is consumed
             if (!ASHARED) a_src.load(c + 1, ra);
             b_src.load(c + 1, rb);
         }
         fence_async_smem();
-        __syncthreads();
-        if (sh.failed) return false;
-        if (threadIdx.x == 0) {
+        mbar_arrive(&sh.full_bar[s]);
+        if (s) ps.pending1 = true; else ps.pending0 = true;
+        ps.chunks++;
+    }
+}
+
+// MMA-warp side of the same product: waits (bounded) for each filled stage, issues its MMAs and
+// commits them to the stage's barrier.  `fresh` = overwrite the accumulator with the first chunk.
+struct IssueState {
+    unsigned chunks = 0;
+    unsigned parity0 = 0, parity1 = 0;
+    bool ok = true;
+};
+template <bool SPLIT>
+__device__ __forceinline__ void pipe_issue(MlpShared& sh, unsigned tmem, int N, int nchunks, bool fresh, IssueState& is)
+{
+    const unsigned idesc = instr_desc(kMlpTile, N);
+    const int lane = threadIdx.x & 31;
+#pragma unroll 1
+    for (int c = 0; c < nchunks; c++) {
+        const int s = (int)(is.chunks & 1u);
+        unsigned& parity = s ? is.parity1 : is.parity0;
+        if (is.ok && !mbar_wait(&sh.full_bar[s], parity)) {
+            is.ok = false;
+            sh.failed = 1;
+        }
+        parity ^= 1u;
+        if (is.ok && lane == 0) {
             tc_fence_after();
-            const unsigned a_hi = smem_u32(stage), a_lo = a_hi + kPipeOperandBytes;
+            const unsigned a_hi = smem_u32(sh.a_hi + s * kPipeStageBytes), a_lo = a_hi + kPipeOperandBytes;
             const unsigned b_hi = a_hi + 2 * kPipeOperandBytes, b_lo = a_hi + 3 * kPipeOperandBytes;
 #pragma unroll
             for (int ks = 0; ks < kPipeK / 8; ks++) {
@@ -244,19 +269,18 @@ __device__ __forceinline__ bool pipe_product(MlpShared& sh, unsigned tmem, int N
             }
             mma_commit(&sh.stage_bar[s]);
         }
-        if (s) ps.pending1 = true; else ps.pending0 = true;
-        ps.chunks++;
+        __syncwarp();
+        is.chunks++;
     }
-    return true;
 }
 
-// Waits for every outstanding MMA (before an epilogue reads the accumulator or reuses the operand
-// area as scratch).  Returns false after a timeout (uniform across the CTA).
+// Producers: waits for every outstanding MMA (before an epilogue reads the accumulator or reuses
+// the operand area as scratch).  Returns false after a timeout (uniform across the producers).
 __device__ __forceinline__ bool pipe_drain(MlpShared& sh, PipeState& ps)
 {
     pipe_wait_stage(sh, ps, 0);
     pipe_wait_stage(sh, ps, 1);
-    __syncthreads();
+    producer_sync();
     if (sh.failed) return false;
     tc_fence_after();
     return true;

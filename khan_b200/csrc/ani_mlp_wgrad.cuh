@@ -43,7 +43,7 @@ struct MlpWgradParams {
 };
 
 template <bool SPLIT>
-__global__ void __launch_bounds__(kMlpThreads, 1) mlp_wgrad_kernel(const MlpWgradParams p)
+__global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_wgrad_kernel(const MlpWgradParams p)
 {
     extern __shared__ unsigned char mlp_smem_raw[];
     MlpShared& sh = *reinterpret_cast<MlpShared*>(
@@ -70,57 +70,65 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_wgrad_kernel(const MlpWgra
     if (tid == 0) {
         mbar_init(&sh.stage_bar[0], 1);
         mbar_init(&sh.stage_bar[1], 1);
+        mbar_init(&sh.full_bar[0], kMlpThreads);
+        mbar_init(&sh.full_bar[1], kMlpThreads);
         sh.failed = 0;
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sh.tmem_base;
-    PipeState ps;
-    const DirectShared<SPLIT> unused_sh{sh.act};
-    // both operands are transposes with K = atom: A[m = in][k] = X[atom k][in m], B[n = out][k] = dZ[atom k][out n]
-    Transposed<SPLIT> a_x{a_src, (size_t)a_ld, a_col0, 128, first, n_here, make_float4(0.f, 0.f, 0.f, 0.f)};
-    Transposed<SPLIT> b_dz{b_src, (size_t)N, 0, N, first, n_here, make_float4(0.f, 0.f, 0.f, 0.f)};
     const int nchunks = (n_here + kPipeK - 1) / kPipeK;
-    const bool ok = pipe_product<SPLIT, false>(sh, tmem, N, nchunks, true, ps, a_x, unused_sh, b_dz) && pipe_drain(sh, ps);
-    const float4 bias_acc = b_dz.colsum;
+    if (warp == kMlpThreads / 32) {
+        IssueState is;
+        pipe_issue<SPLIT>(sh, tmem, N, nchunks, true, is);
+    } else {
+        PipeState ps;
+        const DirectShared<SPLIT> unused_sh{sh.act};
+        // both operands are transposes with K = atom: A[m = in][k] = X[atom k][in m], B[n = out][k] = dZ[atom k][out n]
+        Transposed<SPLIT> a_x{a_src, (size_t)a_ld, a_col0, 128, first, n_here, make_float4(0.f, 0.f, 0.f, 0.f)};
+        Transposed<SPLIT> b_dz{b_src, (size_t)N, 0, N, first, n_here, make_float4(0.f, 0.f, 0.f, 0.f)};
+        pipe_produce<SPLIT, false>(sh, nchunks, ps, a_x, unused_sh, b_dz);
+        const bool ok = pipe_drain(sh, ps);
+        const float4 bias_acc = b_dz.colsum;
 
-    if (ok && n_here > 0) {
-        // warp w: rows 32 (w % 4) .. of the weight block (TMEM lanes), columns 32 (w / 4) ..
-        const int tile_row0 = (warp & 3) * 32, c0 = (warp >> 2) * 32;
-        if (c0 < N) {
-            float v[32];
-            tmem_load32(tmem + ((unsigned)tile_row0 << 16) + c0, v);
-            warp_tile_to_global<true>(warp_scratch(sh), v, out + (size_t)tile_row0 * N + c0, N, 32);
+        if (ok && n_here > 0) {
+            // warp w: rows 32 (w % 4) .. of the weight block (TMEM lanes), columns 32 (w / 4) ..
+            const int tile_row0 = (warp & 3) * 32, c0 = (warp >> 2) * 32;
+            if (c0 < N) {
+                float v[32];
+                tmem_load32(tmem + ((unsigned)tile_row0 << 16) + c0, v);
+                warp_tile_to_global<true>(warp_scratch(sh), v, out + (size_t)tile_row0 * N + c0, N, 32);
+            }
+            if (bias_out) {
+                // this thread summed columns 4q .. 4q+3 of dZ over the atoms it staged
+                const int q = transposed_quad(N);
+                atomicAdd(bias_out + 4 * q + 0, bias_acc.x);
+                atomicAdd(bias_out + 4 * q + 1, bias_acc.y);
+                atomicAdd(bias_out + 4 * q + 2, bias_acc.z);
+                atomicAdd(bias_out + 4 * q + 3, bias_acc.w);
+            }
+        } else if (!ok && tid == 0) {
+            report(ANI_ERR_TIMEOUT);
         }
-        if (bias_out) {
-            // this thread summed columns 4q .. 4q+3 of dZ over the atoms it staged
-            const int q = transposed_quad(N);
-            atomicAdd(bias_out + 4 * q + 0, bias_acc.x);
-            atomicAdd(bias_out + 4 * q + 1, bias_acc.y);
-            atomicAdd(bias_out + 4 * q + 2, bias_acc.z);
-            atomicAdd(bias_out + 4 * q + 3, bias_acc.w);
+        if (blk == 4) {
+            // output layer, done by the CTA with the lightest product: dw4 = A3^T g and db4 = sum g
+            // over this range; no tensor cores involved
+            const int q = tid & 15, a_in = tid >> 4;      // 16 column quads x 32 atoms per pass
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float gsum = 0.0f;
+            for (int k = a_in; k < n_here; k += kMlpThreads / 16) {
+                const float g = p.grad_energy[e][first + k];
+                const float4 v = *reinterpret_cast<const float4*>(p.act3[e] + (size_t)(first + k) * kMlpH3 + 4 * q);
+                acc.x += v.x * g; acc.y += v.y * g; acc.z += v.z * g; acc.w += v.w * g;
+                gsum += q == 0 ? g : 0.0f;
+            }
+            atomicAdd(p.dw4[e] + 4 * q + 0, acc.x);
+            atomicAdd(p.dw4[e] + 4 * q + 1, acc.y);
+            atomicAdd(p.dw4[e] + 4 * q + 2, acc.z);
+            atomicAdd(p.dw4[e] + 4 * q + 3, acc.w);
+            if (q == 0) atomicAdd(p.db4[e], gsum);
         }
-    } else if (!ok && tid == 0) {
-        report(ANI_ERR_TIMEOUT);
-    }
-    if (blk == 4) {
-        // output layer, done by the CTA with the lightest product: dw4 = A3^T g and db4 = sum g
-        // over this range; no tensor cores involved
-        const int q = tid & 15, a_in = tid >> 4;      // 16 column quads x 32 atoms per pass
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float gsum = 0.0f;
-        for (int k = a_in; k < n_here; k += kMlpThreads / 16) {
-            const float g = p.grad_energy[e][first + k];
-            const float4 v = *reinterpret_cast<const float4*>(p.act3[e] + (size_t)(first + k) * kMlpH3 + 4 * q);
-            acc.x += v.x * g; acc.y += v.y * g; acc.z += v.z * g; acc.w += v.w * g;
-            gsum += q == 0 ? g : 0.0f;
-        }
-        atomicAdd(p.dw4[e] + 4 * q + 0, acc.x);
-        atomicAdd(p.dw4[e] + 4 * q + 1, acc.y);
-        atomicAdd(p.dw4[e] + 4 * q + 2, acc.z);
-        atomicAdd(p.dw4[e] + 4 * q + 3, acc.w);
-        if (q == 0) atomicAdd(p.db4[e], gsum);
     }
     tc_fence_before();
     __syncthreads();
