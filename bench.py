@@ -236,6 +236,81 @@ def run_reference_arm(args):
 # ------------------------------------------------------------------------------------------
 # training step (BASELINE config 3), reported separately from the benchmark metric
 # ------------------------------------------------------------------------------------------
+def run_forces_workload(args):
+    """One step = config-1 batch -> ani_sort -> featurize -> four atomic networks -> molecule
+    energies -> network backward to the features -> featurize_grad: energies and forces as
+    `predict` + `coordinate_gradients` deliver them, C-ABI calls on pre-allocated buffers, one CUDA
+    graph per staged batch."""
+    import torch
+    import torch.distributed as dist
+
+    from khan_b200.data import synthetic as syn
+    from khan_b200.inference import EnergyForces
+    from khan_b200.model import activations
+    from khan_b200.model.nn import MoleculeNN
+    from khan_b200.staged import HostBatch, StagedBatch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=1, init="he")
+    nb = max(1, min(16, args.steps))
+    batches = syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)
+    cap = max(b.n_atoms for b in batches)
+    staged, ids = [], []
+    for b in batches:
+        sb = StagedBatch(cap, args.mols, device=dev)
+        sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
+        staged.append(sb)
+        ids.append(torch.from_numpy(np.repeat(np.arange(b.n_mols), b.mol_atom_counts)).to(dev))
+    ev = EnergyForces(model, cap, args.mols, device=dev)
+    side = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(side):
+        for k in range(max(3, args.warmup)):
+            ev.run(staged[k % nb], ids[k % nb])
+    torch.cuda.synchronize()
+    graphs = []
+    for sb, mi in zip(staged, ids):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            ev.run(sb, mi)
+        graphs.append(g)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        graphs[k % nb].replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    atoms = float(sum(batches[k % nb].n_atoms for k in range(args.steps)))
+    if world > 1:
+        t = torch.tensor([ms, atoms], dtype=torch.float64, device=dev)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, atoms = float(tmax[0]), float(t[1])
+    if rank == 0:
+        print(json.dumps({
+            "metric": "energies + forces atoms/sec (fp32, 1024-mol batch per GPU)", "value": atoms / (ms * 1e-3),
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 (tf32x3 tensor-core products in the atomic networks)", "data": "synthetic",
+            "gpu_launches": args.steps * EnergyForces.KERNELS_PER_PASS,
+            "config": {"workload": "config1 batches: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian) forward + "
+                                   "molecule sums + MLP backward to the features + featurize_grad",
+                       "molecules_per_step_per_gpu": args.mols, "launch": "cuda_graph per staged batch",
+                       "resident_batches": nb}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_train_workload(args):
     """One step = config-1 batch per GPU -> ani_sort -> featurize -> four atomic networks
     (384-128-128-64-1, gaussian, He-normal init seed 1) -> molecule energies -> MSE against
@@ -389,9 +464,10 @@ def main():
                     help="independent batches in flight: steps are issued round-robin over this many streams")
     ap.add_argument("--mols", type=int, default=N_MOLS,
                     help="molecules per batch (1024 is the benchmark workload; other sizes are for profiling)")
-    ap.add_argument("--workload", default="aev", choices=["aev", "train"],
+    ap.add_argument("--workload", default="aev", choices=["aev", "train", "forces"],
                     help="aev: the benchmark metric (sort + featurize + featurize_grad); train: the full "
-                         "data-parallel training step of BASELINE config 3 (reported separately)")
+                         "data-parallel training step of BASELINE config 3; forces: energies + forces of "
+                         "config-1 batches through the C ABI only (both reported separately)")
     ap.add_argument("--e2e-slots", type=int, default=4,
                     help="batches in flight (one stream each) in the end-to-end measurement")
     ap.add_argument("--case", default="config1", choices=["config1", "config2", "config4"],
@@ -408,6 +484,9 @@ def main():
         return
     if args.workload == "train":
         run_train_workload(args)
+        return
+    if args.workload == "forces":
+        run_forces_workload(args)
         return
 
     import torch

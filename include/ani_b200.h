@@ -181,7 +181,8 @@ int ani_featurize_grad_inverse_f64(const double* xs, const double* ys, const dou
  *   energy[t] = act(act(act(F_t W1 + b1) W2 + b2) W3 + b3) w4 + b4,   F_t = features[t] [acs[t]][384].
  * One launch covers all four elements; the matrix products run on the tensor cores in tf32.
  * Weights are passed as the reference stores them, [in][out] with `out` contiguous
- * (khan/model/nn.py:42-47), 16-byte aligned.  `activation`: 0 celu(0.1),
+ * (khan/model/nn.py:42-47).  Every matrix pointer (features, weights, act*, dact*) must be
+ * 16-byte aligned (ANI_ERR_MISALIGNED otherwise).  `activation`: 0 celu(0.1),
  * 1 gaussian exp(-x^2), 2 normal exp(-x^2/2), 3 softplus - ln 2 (khan/model/activations.py:62-74).
  * `split_precision` != 0 splits every operand into two tf32 terms (three MMAs per product),
  * which brings the products to float32 accuracy; 0 uses plain tf32.
@@ -220,7 +221,8 @@ int ani_mlp_forward_f32(const ani_mlp_args* args_host, const int* acs_host, int 
  * gradients follow from the outputs as plain products over the atoms of an element,
  * dW_l = A_{l-1}^T dz_l and db_l = column sums of dz_l, and are left to the caller.
  * Weights are passed in the reference's layout, [in][out] with `out` contiguous; dact1..3 are the
- * arrays that ani_mlp_forward_f32 filled.  `split_precision` as in the forward call.
+ * arrays that ani_mlp_forward_f32 filled.  `split_precision` as in the forward call.  Every
+ * matrix pointer must be 16-byte aligned (ANI_ERR_MISALIGNED otherwise).
  */
 typedef struct ani_mlp_backward_args {
     const float* grad_energy[4];  /* [acs[t]] dL/dE per atom, element-sorted order */

@@ -6,6 +6,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <initializer_list>
 #include <mutex>
 
 #include "ani_common.cuh"
@@ -373,6 +374,15 @@ template <bool SPLIT> int mlp_wgrad_launch(const MlpWgradParams& p, int n_ranges
     return ANI_OK;
 }
 
+// True when every non-null pointer of the list is 16-byte aligned (the atomic-network kernels use
+// 16-byte accesses on all of their matrices).
+bool all_aligned16(std::initializer_list<const void*> ptrs)
+{
+    for (const void* q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) & 15) return false;
+    return true;
+}
+
 template <int ACT> int mlp_launch_act(const MlpParams& p, int n_tiles, bool split, cudaStream_t st)
 {
     return split ? mlp_launch<ACT, true>(p, n_tiles, st) : mlp_launch<ACT, false>(p, n_tiles, st);
@@ -606,6 +616,9 @@ int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activati
         if (acs_host[t] > 0 && (!a->features[t] || !a->w1[t] || !a->b1[t] || !a->w2[t] || !a->b2[t] ||
                                 !a->w3[t] || !a->b3[t] || !a->w4[t] || !a->b4[t] || !a->energy[t]))
             return ANI_ERR_NULL_POINTER;
+        if (acs_host[t] > 0 && !all_aligned16({a->features[t], a->w1[t], a->w2[t], a->w3[t], a->act1[t], a->act2[t],
+                                               a->act3[t], a->dact1[t], a->dact2[t], a->dact3[t]}))
+            return ANI_ERR_MISALIGNED;
         p.feat[t] = a->features[t];
         p.w1[t] = a->w1[t]; p.b1[t] = a->b1[t];
         p.w2[t] = a->w2[t]; p.b2[t] = a->b2[t];
@@ -643,6 +656,9 @@ int ani_mlp_backward_f32(const ani_mlp_backward_args* a, const int* acs_host, in
                                 !a->dact1[t] || !a->dact2[t] || !a->dact3[t] || !a->dz1[t] || !a->dz2[t] ||
                                 !a->dz3[t]))
             return ANI_ERR_NULL_POINTER;
+        if (acs_host[t] > 0 && !all_aligned16({a->w1[t], a->w2[t], a->w3[t], a->dact1[t], a->dact2[t], a->dact3[t],
+                                               a->dz1[t], a->dz2[t], a->dz3[t], a->grad_features[t]}))
+            return ANI_ERR_MISALIGNED;
         p.grad_energy[t] = a->grad_energy[t];
         p.w1[t] = a->w1[t]; p.w2[t] = a->w2[t]; p.w3[t] = a->w3[t]; p.w4[t] = a->w4[t];
         p.dact1[t] = a->dact1[t]; p.dact2[t] = a->dact2[t]; p.dact3[t] = a->dact3[t];

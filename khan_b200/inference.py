@@ -1,0 +1,88 @@
+"""Energies and forces of staged batches through the C ABI only (no autograd):
+
+    ani_sort -> featurize -> atomic networks (forward) -> molecule sums
+             -> atomic networks (backward to the features, dE_mol/dE_atom = 1) -> featurize_grad
+
+which is what the reference evaluates for ``predict`` + ``coordinate_gradients``
+(``khan/training/trainer_multi_tower.py:580-614,655-678``: ``tf.gradients(tower_pred, [x, y, z])``),
+with every buffer pre-allocated so that a pass can be captured into a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+from .model import activations
+from .staged import FEATURE_SIZE, StagedBatch
+
+
+def _ptr(t: torch.Tensor, offset_elems: int = 0):
+    return ctypes.c_void_p(t.data_ptr() + offset_elems * t.element_size())
+
+
+class EnergyForces:
+    """Pre-allocated evaluator for one model (float32, the fused 384-128-128-64-1 networks)."""
+
+    def __init__(self, model, n_atoms: int, n_mols: int, device="cuda:0"):
+        if not model.fused:
+            raise ValueError("EnergyForces needs the fused float32 384-128-128-64-1 networks")
+        self.model = model
+        self.device = torch.device(device)
+        self.act_id = activations.KERNEL_ID[model.activation_fn]
+        self.split = bool(model.split_precision)
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.energy_sorted = torch.empty(n_atoms, **f32)
+        self.ones = torch.ones(n_atoms, **f32)
+        self.acts = [torch.empty((n_atoms, w), **f32) for w in (128, 128, 64)]
+        self.dacts = [torch.empty((n_atoms, w), **f32) for w in (128, 128, 64)]
+        self.dzs = [torch.empty((n_atoms, w), **f32) for w in (128, 128, 64)]
+        self.mol_energy = torch.zeros(n_mols, **f32)
+        self.n_atoms_cap, self.n_mols_cap = n_atoms, n_mols
+
+    def _weights(self, t: int):
+        ann = self.model.anns[t]
+        return [w.detach() for w in ann.Ws], [b.detach() for b in ann.bs]
+
+    def run(self, sb: StagedBatch, mol_ids: torch.Tensor, stream: ctypes.c_void_p | None = None) -> None:
+        """One pass over the batch staged in ``sb``.  Afterwards ``self.mol_energy[:sb.n_mols]``
+        holds the molecule energies and ``sb.grads[:, :sb.n_atoms]`` dE/dx, dE/dy, dE/dz (forces are
+        their negatives).  ``mol_ids``: int64 molecule index of every atom (device)."""
+        if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
+            raise ValueError("batch does not fit this evaluator")
+        if stream is None:
+            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        lib = _lib.lib()
+        n, acs = sb.n_atoms, sb.acs_host
+        starts = np.concatenate([[0], np.cumsum(acs)])
+        sb.run_sort(stream)
+        sb.run_featurize(stream)
+        fwd, bwd = _lib.MlpArgs(), _lib.MlpBackwardArgs()
+        for t in range(4):
+            if acs[t] == 0:
+                continue
+            s = int(starts[t])
+            (w1, w2, w3, w4), (b1, b2, b3, b4) = self._weights(t)
+            fwd.features[t] = _ptr(sb.features, s * FEATURE_SIZE)
+            fwd.w1[t], fwd.w2[t], fwd.w3[t], fwd.w4[t] = _ptr(w1), _ptr(w2), _ptr(w3), _ptr(w4)
+            fwd.b1[t], fwd.b2[t], fwd.b3[t], fwd.b4[t] = _ptr(b1), _ptr(b2), _ptr(b3), _ptr(b4)
+            fwd.energy[t] = _ptr(self.energy_sorted, s)
+            fwd.act1[t], fwd.act2[t], fwd.act3[t] = (_ptr(a, s * a.shape[1]) for a in self.acts)
+            fwd.dact1[t], fwd.dact2[t], fwd.dact3[t] = (_ptr(d, s * d.shape[1]) for d in self.dacts)
+            bwd.grad_energy[t] = _ptr(self.ones, s)
+            bwd.w1[t], bwd.w2[t], bwd.w3[t], bwd.w4[t] = _ptr(w1), _ptr(w2), _ptr(w3), _ptr(w4)
+            bwd.dact1[t], bwd.dact2[t], bwd.dact3[t] = (_ptr(d, s * d.shape[1]) for d in self.dacts)
+            bwd.dz1[t], bwd.dz2[t], bwd.dz3[t] = (_ptr(z, s * z.shape[1]) for z in self.dzs)
+            bwd.grad_features[t] = _ptr(sb.upstream, s * FEATURE_SIZE)   # the upstream of featurize_grad
+        _lib.check(lib.ani_mlp_forward_f32(ctypes.byref(fwd), sb._acs_ptr, self.act_id, int(self.split), stream),
+                   "ani_mlp_forward_f32")
+        # molecule energies: atom order = sorted order gathered, then one scatter-add per molecule
+        atom_e = self.energy_sorted[:n][sb.gather[:n].long()]
+        self.mol_energy[:sb.n_mols].zero_().index_add_(0, mol_ids[:n], atom_e)
+        _lib.check(lib.ani_mlp_backward_f32(ctypes.byref(bwd), sb._acs_ptr, int(self.split), stream),
+                   "ani_mlp_backward_f32")
+        sb.run_featurize_grad(stream)
+
+    KERNELS_PER_PASS = 6   # sort, featurize, mlp forward, mlp backward, zero fill, featurize_grad (+ 4 small torch kernels)

@@ -68,6 +68,16 @@ def test_weight_grad_rejects_misaligned_matrices_before_launching(handle):
     assert handle.ani_mlp_weight_grad_f32(ctypes.byref(args), one, 1, None) == -9
     args.dw2[0] = None
     assert handle.ani_mlp_weight_grad_f32(ctypes.byref(args), one, 1, None) == -1
+    fwd = _lib.MlpArgs()
+    for name, _ in fwd._fields_:
+        getattr(fwd, name)[0] = 0x20000
+    fwd.features[0] = 0x20008
+    assert handle.ani_mlp_forward_f32(ctypes.byref(fwd), one, 0, 1, None) == -9
+    bwd = _lib.MlpBackwardArgs()
+    for name, _ in bwd._fields_:
+        getattr(bwd, name)[0] = 0x30000
+    bwd.dz2[0] = 0x30004
+    assert handle.ani_mlp_backward_f32(ctypes.byref(bwd), one, 1, None) == -9
     assert handle.ani_nadam_step_f32(None, None, None, None, None, 10, None, None, None) == -1
     assert handle.ani_nadam_step_f32(None, None, None, None, None, 0, None, None, None) == 0
 

@@ -151,3 +151,30 @@ def test_train_schedule_halves_the_rate_and_keeps_the_best_weights(tmp_path):
     assert abs(tr2.eval_abs_rmse(test) - best) < 1e-3 * max(1.0, best)
     groups = [ys[36:42], ys[42:48]]
     assert tr2.eval_rel_rmse(test, groups) >= 0
+
+
+def test_energy_forces_evaluator_matches_the_trainer():
+    """The allocation-free evaluator (C ABI only) against predict + coordinate_gradients of the
+    trainer (autograd path) on the same weights."""
+    import ctypes
+    import torch
+    from khan_b200 import RawDataset, TrainerMultiTower
+    from khan_b200.inference import EnergyForces
+    from khan_b200.staged import HostBatch, StagedBatch
+    b = syn.config1(n_mols=40)
+    mols = b.molecules()
+    ds = RawDataset(mols)
+    tr = TrainerMultiTower(None, [torch.device("cuda", 0)], layer_sizes=(128, 128, 64, 1), seed=5)
+    want_e = np.array(tr.predict(ds, batch_size=64))
+    want_g = np.concatenate(list(tr.coordinate_gradients(ds, batch_size=64)), axis=0)      # (n_atoms, 3)
+    sb = StagedBatch(b.n_atoms, b.n_mols)
+    sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
+    mol_ids = torch.from_numpy(np.repeat(np.arange(b.n_mols), b.mol_atom_counts)).cuda()
+    ev = EnergyForces(tr.model, b.n_atoms, b.n_mols)
+    for _ in range(2):                      # twice: the buffers are reused
+        ev.run(sb, mol_ids)
+    torch.cuda.synchronize()
+    got_e = ev.mol_energy[:b.n_mols].cpu().numpy()
+    got_g = sb.grads[:, :b.n_atoms].cpu().numpy().T
+    assert np.abs(got_e - want_e).max() < 1e-5 * np.abs(want_e).max()
+    assert np.abs(got_g - want_g).max() < 1e-4 * np.abs(want_g).max()

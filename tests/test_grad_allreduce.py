@@ -35,6 +35,10 @@ def _worker(rank, world, port, out_dir):
     local = torch.cat([p.grad.reshape(-1) for p in model.get_parameters()]).clone()
     average_gradients(model.get_parameters())
     avg = torch.cat([p.grad.reshape(-1) for p in model.get_parameters()])
+    # the flat-buffer form (what FlatNadam hands over): the buffer itself is reduced in place
+    flat = local.clone()
+    average_gradients([], flat_grads=flat)
+    np.save(os.path.join(out_dir, f"flat{rank}.npy"), flat.numpy())
     np.save(os.path.join(out_dir, f"local{rank}.npy"), local.numpy())
     np.save(os.path.join(out_dir, f"avg{rank}.npy"), avg.numpy())
     dist.destroy_process_group()
@@ -49,3 +53,6 @@ def test_two_ranks_end_up_with_the_mean_gradient(tmp_path):
     assert np.abs(local[0] - local[1]).max() > 0
     np.testing.assert_allclose(avg[0], (local[0] + local[1]) / 2, rtol=1e-12, atol=1e-15)
     np.testing.assert_array_equal(avg[0], avg[1])
+    flat = [np.load(tmp_path / f"flat{r}.npy") for r in range(world)]
+    np.testing.assert_array_equal(flat[0], avg[0])
+    np.testing.assert_array_equal(flat[1], avg[0])
