@@ -2,7 +2,7 @@
 // warp helpers, per-central-atom neighbour lists and the enumeration of neighbour pairs.
 //
 // Work decomposition used by every featurizer kernel: ONE WARP PER CENTRAL ATOM, no cooperation
-// between the warps of a CTA (no __syncthreads anywhere).  The work list has S = 2^slot_shift
+// between the warps of a CTA beyond a shared work counter (one __syncthreads, at the start).  The work list has S = 2^slot_shift
 // items per molecule (S is chosen per launch: the power of two next above the mean molecule
 // size, 4 <= S <= 32); item (m, s) covers atoms s, s + S, ... of molecule m and is empty when
 // the molecule has fewer atoms.  The grid is persistent (a few CTAs per SM): warp w takes
@@ -121,6 +121,22 @@ __device__ __forceinline__ void item_to_work(long long item, int round, int slot
     const int mask = (1 << slot_shift) - 1;
     *m = (int)(item >> slot_shift);
     *slot = (((int)item & mask) + 11 * round) & mask;
+}
+
+// The items of a CTA (those that its NW warps would take statically: items w, w + W, ... for
+// each of its warps w) are handed out from a counter in shared memory, so that a warp that
+// drew cheap atoms takes more of them: the spread in cost per item is large (a hydrogen at the
+// edge of a small molecule against a carbon inside a large one) and a warp only sees a few
+// items.  Returns the next item of this CTA and its round, or -1 when the CTA's list is done.
+template <int NW>
+__device__ __forceinline__ long long next_cta_item(int* counter, int grid_warps, long long n_items, int* round)
+{
+    int t = 0;
+    if (lane_id() == 0) t = atomicAdd(counter, 1);
+    t = __shfl_sync(kFull, t, 0);
+    *round = t / NW;
+    const long long item = (long long)blockIdx.x * NW + (t % NW) + (long long)(t / NW) * grid_warps;
+    return item < n_items ? item : -1;
 }
 
 // One molecule as the kernels see it, validated.

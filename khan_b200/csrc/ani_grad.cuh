@@ -140,8 +140,13 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
 
     const long long n_items = (long long)n_mols << slot_shift;
     const int grid_warps = gridDim.x * NW;
-    int round = 0;
-    for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
+    __shared__ int cta_next_item;
+    if (threadIdx.x == 0) cta_next_item = 0;
+    __syncthreads();
+    for (;;) {
+        int round;
+        const long long item = next_cta_item<NW>(&cta_next_item, grid_warps, n_items, &round);
+        if (item < 0) break;
         int m, slot;
         item_to_work(item, round, slot_shift, &m, &slot);
         if (slot >= mol_counts[m]) continue;   // empty item: one cached load
