@@ -100,7 +100,10 @@ int sort_static_scratch(int** out)
 // Featurizer launch shapes: NW warps per CTA, (slots per molecule) / NW CTAs per molecule, one warp
 // per central atom.  The capacities bound the neighbours of one element kept in shared memory
 // per central atom (atoms with more take the streaming path).
-constexpr int kNW = 4;
+#ifndef ANI_NW
+#define ANI_NW 4
+#endif
+constexpr int kNW = ANI_NW;   // warps per CTA of the featurizer kernels (a power of two <= 32)
 constexpr int kCapT = 24;  // angular (r < 3.1 A) neighbours per element
 constexpr int kCapR = 48;  // radial (r < 4.6 A) neighbours per element
 
@@ -129,7 +132,8 @@ template <typename K> int featurizer_grid(K kernel, size_t smem, int n_mols, int
 int pick_slot_shift(long long n_atoms, int n_mols)
 {
     const long long mean = n_mols > 0 ? (n_atoms + n_mols - 1) / n_mols : 1;
-    int shift = 2;   // kNW = 4 slots
+    int shift = 0;
+    while ((1 << shift) < kNW) shift++;   // at least one slot per warp of a CTA
     while ((1 << shift) < mean && (1 << shift) < kSlotsPerMol) shift++;
     return shift;
 }

@@ -123,7 +123,7 @@ __device__ __noinline__ void grad_atom_streaming(const T* __restrict__ xs, const
 #endif
 
 template <typename T, int NW>
-__global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS : 1)
+__global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS * 4 / NW : 1)
     featurize_grad_kernel(const T* __restrict__ xs, const T* __restrict__ ys,
                           const T* __restrict__ zs, const int* __restrict__ types,
                           const int* __restrict__ mol_offsets, const int* __restrict__ mol_counts,
