@@ -234,7 +234,7 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------
-# training step (BASELINE config 3), reported separately from the benchmark metric
+# training step (benchmark configuration 3), reported separately from the benchmark metric
 # ------------------------------------------------------------------------------------------
 def run_forces_workload(args):
     """One step = config-1 batch -> ani_sort -> featurize -> four atomic networks -> molecule
@@ -466,7 +466,7 @@ def main():
                     help="molecules per batch (1024 is the benchmark workload; other sizes are for profiling)")
     ap.add_argument("--workload", default="aev", choices=["aev", "train", "forces"],
                     help="aev: the benchmark metric (sort + featurize + featurize_grad); train: the full "
-                         "data-parallel training step of BASELINE config 3; forces: energies + forces of "
+                         "data-parallel training step of benchmark configuration 3; forces: energies + forces of "
                          "config-1 batches through the C ABI only (both reported separately)")
     ap.add_argument("--e2e-slots", type=int, default=4,
                     help="batches in flight (one stream each) in the end-to-end measurement")

@@ -125,17 +125,22 @@ template <typename K> int featurizer_grid(K kernel, size_t smem, int n_mols, int
     return ANI_OK;
 }
 
-// Work-list slots per molecule for a launch, as a shift: the smallest power of two that is not
-// below the mean atoms per molecule, between kNW and kSlotsPerMol.  With one slot per atom of a
-// typical molecule few items are empty (every empty item costs its warp a dependent load) and
-// larger molecules simply give some slots a second atom.
+// Work list of a launch, packed into one kernel argument: bits 0-4 = log2 of the slots per
+// molecule (the smallest power of two that is not below the mean atoms per molecule, between kNW
+// and kSlotsPerMol: few empty items, and larger molecules simply give some slots a second atom);
+// bit 5 = slot-major order, used when molecules are small (see next_work).
+constexpr int kSlotMajorFlag = 32;
 int pick_slot_shift(long long n_atoms, int n_mols)
 {
     const long long mean = n_mols > 0 ? (n_atoms + n_mols - 1) / n_mols : 1;
     int shift = 0;
     while ((1 << shift) < kNW) shift++;   // at least one slot per warp of a CTA
     while ((1 << shift) < mean && (1 << shift) < kSlotsPerMol) shift++;
-    return shift;
+#ifdef ANI_TUNING
+    if (const char* e = getenv("ANI_SLOT_SHIFT")) shift = atoi(e);
+    if (const char* e = getenv("ANI_SLOT_MAJOR")) return shift | (atoi(e) ? kSlotMajorFlag : 0);
+#endif
+    return shift | (mean <= kSlotsPerMol ? kSlotMajorFlag : 0);
 }
 
 template <typename K> int set_smem(K kernel, size_t bytes)
@@ -186,7 +191,7 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
         cached_grid_dev = dev;
     }
     const int slot_shift = pick_slot_shift(n_atoms, n_mols);
-    const long long needed = (long long)n_mols * ((1 << slot_shift) / kNW);
+    const long long needed = (long long)n_mols * ((1 << (slot_shift & 31)) / kNW);
     int grid = (int)(needed < cached_resident ? needed : cached_resident);
 #ifdef ANI_PHASE_TIMING
     if (getenv("ANI_DEBUG_FULL_GRID")) grid = (int)needed;   // tuning builds: one item per warp
@@ -238,7 +243,7 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
         cached_grid_dev = dev;
     }
     const int slot_shift = pick_slot_shift(n_atoms, n_mols);
-    const long long needed = (long long)n_mols * ((1 << slot_shift) / kNW);
+    const long long needed = (long long)n_mols * ((1 << (slot_shift & 31)) / kNW);
     const int grid = (int)(needed < cached_resident ? needed : cached_resident);
     kernel<<<grid, kNW * kWarp, smem, st>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, slot_shift, sis, gh, gc, gn, go, gx, gy, gz,
@@ -274,7 +279,7 @@ int featurize_grad_inverse_impl(const T* xs, const T* ys, const T* zs, const int
         configured_dev = dev;
     }
     const int slot_shift = pick_slot_shift(n_atoms, n_mols);
-    const long long needed = (long long)n_mols * ((1 << slot_shift) / kNW);
+    const long long needed = (long long)n_mols * ((1 << (slot_shift & 31)) / kNW);
     const int grid = (int)(needed < cached_resident ? needed : cached_resident);
     kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, slot_shift, sis, vx, vy, vz, oh, oc, on, oo,

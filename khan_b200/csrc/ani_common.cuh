@@ -111,32 +111,38 @@ __device__ __forceinline__ void load4(const double* p, double* v)
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-// The k-th item of a warp: item index -> (molecule, slot).  The slot is rotated by the round
-// number k so that a warp does not see the same slot -- hence the same chance of an empty item
-// -- in every round.  Requires the number of warps in the grid to be a multiple of
-// the slots per molecule (2^slot_shift), which makes the rotation a permutation of each
-// molecule's slots.
-__device__ __forceinline__ void item_to_work(long long item, int round, int slot_shift, int* m, int* slot)
-{
-    const int mask = (1 << slot_shift) - 1;
-    *m = (int)(item >> slot_shift);
-    *slot = (((int)item & mask) + 11 * round) & mask;
-}
-
-// The items of a CTA (those that its NW warps would take statically: items w, w + W, ... for
-// each of its warps w) are handed out from a counter in shared memory, so that a warp that
-// drew cheap atoms takes more of them: the spread in cost per item is large (a hydrogen at the
-// edge of a small molecule against a carbon inside a large one) and a warp only sees a few
-// items.  Returns the next item of this CTA and its round, or -1 when the CTA's list is done.
+// Work list.  A molecule has S = 2^slot_shift slots (slot s covers atoms s, s + S, ...), so there
+// are n_mols * S items.  Warp w of the grid statically owns items w, w + W, ... (W = warps in the
+// grid); inside a CTA those items are handed out from a counter in shared memory instead, so
+// that a warp that drew cheap atoms takes more of them (the spread in cost per item is large --
+// a hydrogen at the edge of a small molecule against a carbon inside a large one -- and a warp
+// only sees a few items).  Two orders of the list:
+//   molecule-major  item = m * S + slot (slot rotated per round): the warps of a CTA work on the
+//                   same molecule and share its coordinates in L1 -- best for large molecules;
+//   slot-major      item = slot * n_mols + m: the warps of a CTA, and the rounds of a warp, see a
+//                   mix of molecules, and the first atoms of all molecules (the heavy atoms, in
+//                   the usual ordering of data sets) come before the last ones, most of which are
+//                   hydrogens or empty slots -- best balance for small molecules.
+// Returns false when the CTA's list is exhausted.
 template <int NW>
-__device__ __forceinline__ long long next_cta_item(int* counter, int grid_warps, long long n_items, int* round)
+__device__ __forceinline__ bool next_work(int* counter, int n_mols, int slot_shift, bool slot_major, int* m, int* slot)
 {
     int t = 0;
     if (lane_id() == 0) t = atomicAdd(counter, 1);
     t = __shfl_sync(kFull, t, 0);
-    *round = t / NW;
-    const long long item = (long long)blockIdx.x * NW + (t % NW) + (long long)(t / NW) * grid_warps;
-    return item < n_items ? item : -1;
+    const int round = t / NW;
+    const long long item = (long long)blockIdx.x * NW + (t % NW) + (long long)round * gridDim.x * NW;
+    if (item >= ((long long)n_mols << slot_shift)) return false;
+    if (slot_major) {
+        const int s = (int)(item / n_mols);
+        *slot = s;
+        *m = (int)(item - (long long)s * n_mols);
+    } else {
+        const int mask = (1 << slot_shift) - 1;
+        *m = (int)(item >> slot_shift);
+        *slot = (((int)item & mask) + 11 * round) & mask;   // a permutation of the slots: W is a multiple of 32
+    }
+    return true;
 }
 
 // One molecule as the kernels see it, validated.

@@ -136,17 +136,12 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
     __syncwarp();
     ANI_PHASE(14);
 
-    const long long n_items = (long long)n_mols << slot_shift;
-    const int grid_warps = gridDim.x * NW;
     __shared__ int cta_next_item;
     if (threadIdx.x == 0) cta_next_item = 0;
     __syncthreads();
     for (;;) {
-        int round;
-        const long long item = next_cta_item<NW>(&cta_next_item, grid_warps, n_items, &round);
-        if (item < 0) break;
         int m, slot;
-        item_to_work(item, round, slot_shift, &m, &slot);
+        if (!next_work<NW>(&cta_next_item, n_mols, slot_shift & 31, (slot_shift & 32) != 0, &m, &slot)) break;
         const int n_of_m = mol_counts[m];
         if (n_of_m < 0) report(ANI_ERR_BAD_INDEX);   // forces the load to complete here in timing builds
         ANI_PHASE(15);
@@ -155,7 +150,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
 
-        for (int i = slot; i < n; i += 1 << slot_shift) {
+        for (int i = slot; i < n; i += 1 << (slot_shift & 31)) {
             const int gi = base + i;
             // everything this atom needs from global memory is requested before any of it is used
             const int j_first = lane < n ? lane : 0;

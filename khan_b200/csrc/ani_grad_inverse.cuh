@@ -79,18 +79,18 @@ __global__ void __launch_bounds__(NW* kWarp)
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
-    const long long n_items = (long long)n_mols << slot_shift;
-    const int grid_warps = gridDim.x * NW;
-    int round = 0;
-    for (long long item = (long long)blockIdx.x * NW + warp; item < n_items; item += grid_warps, round++) {
+    __shared__ int cta_next_item;
+    if (threadIdx.x == 0) cta_next_item = 0;
+    __syncthreads();
+    for (;;) {
         int m, slot;
-        item_to_work(item, round, slot_shift, &m, &slot);
+        if (!next_work<NW>(&cta_next_item, n_mols, slot_shift & 31, (slot_shift & 32) != 0, &m, &slot)) break;
         if (slot >= mol_counts[m]) continue;
         MolRange mol;
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
 
-        for (int i = slot; i < n; i += 1 << slot_shift) {
+        for (int i = slot; i < n; i += 1 << (slot_shift & 31)) {
             const int gi = base + i;
             const int ti = checked_type(types[gi]);
             const int srow = scatter[gi];
