@@ -52,7 +52,7 @@ FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # SMs x lanes x FMA x max SM 
 # DRAM bytes per atom seen by ncu (dram__bytes_read.sum + dram__bytes_write.sum) on an
 # 8192-molecule batch, whose 170 MB of features exceed the L2 (profiles/dram_traffic_8192_molecules.md);
 # traffic grows in proportion to the atoms, so a launch is scaled by its atom count.
-NCU_DRAM_BYTES_PER_ATOM = {"featurize": 1060.4, "featurize_grad": 1577.6, "ani_sort": None}
+NCU_DRAM_BYTES_PER_ATOM = {"featurize": 1035.2, "featurize_grad": 1571.7, "ani_sort": None}
 
 
 def measured_peaks():
