@@ -261,23 +261,22 @@ def run_forces_workload(args):
     nb = max(1, min(16, args.steps))
     batches = syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)
     cap = max(b.n_atoms for b in batches)
-    staged, ids = [], []
+    staged = []
     for b in batches:
         sb = StagedBatch(cap, args.mols, device=dev)
         sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
         staged.append(sb)
-        ids.append(torch.from_numpy(np.repeat(np.arange(b.n_mols), b.mol_atom_counts)).to(dev))
     ev = EnergyForces(model, cap, args.mols, device=dev)
     side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(side):
         for k in range(max(3, args.warmup)):
-            ev.run(staged[k % nb], ids[k % nb])
+            ev.run(staged[k % nb])
     torch.cuda.synchronize()
     graphs = []
-    for sb, mi in zip(staged, ids):
+    for sb in staged:
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            ev.run(sb, mi)
+            ev.run(sb)
         graphs.append(g)
     if world > 1:
         dist.barrier()
@@ -307,6 +306,104 @@ def run_forces_workload(args):
                                    "molecule sums + MLP backward to the features + featurize_grad",
                        "molecules_per_step_per_gpu": args.mols, "launch": "cuda_graph per staged batch",
                        "resident_batches": nb}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_fused_train_workload(args):
+    """The training step of `run_train_workload` on the C ABI only (khan_b200.training.fused_step):
+    no autograd, 11 launches, the gradient all-reduce issued right after the weight gradients so
+    that it overlaps the coordinate-gradient kernel, which runs on a second stream."""
+    import torch
+    import torch.distributed as dist
+
+    from khan_b200.data import synthetic as syn
+    from khan_b200.model import activations
+    from khan_b200.model.nn import MoleculeNN
+    from khan_b200.staged import HostBatch, StagedBatch
+    from khan_b200.training.fused_step import FusedTrainStep
+    from khan_b200.training.optim import FlatNadam
+    from khan_b200.training.trainer_multi_tower import average_gradients
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=1, init="he")
+    params = model.get_parameters()
+    opt = FlatNadam(params, lr=1e-3, clip_norm=5.0)
+    nb = max(1, min(8, args.steps))
+    batches = syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)
+    cap = max(b.n_atoms for b in batches)
+    staged, labels = [], []
+    for k, b in enumerate(batches):
+        sb = StagedBatch(cap, args.mols, device=dev)
+        sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
+        staged.append(sb)
+        rng = np.random.default_rng(3000 + 100 * rank + k)
+        labels.append(torch.from_numpy(rng.normal(size=b.n_mols).astype(np.float32)).to(dev))
+    step = FusedTrainStep(model, opt, cap, args.mols, device=dev)
+    side = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(side):
+        for k in range(max(3, args.warmup)):
+            step.step(staged[k % nb], labels[k % nb])
+    torch.cuda.synchronize()
+    fb_graphs, cg_graphs = [], []
+    for sb, y in zip(staged, labels):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step.forward_backward(sb, y)
+        fb_graphs.append(g)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step.coordinate_gradient(sb)
+        cg_graphs.append(g)
+    up_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(up_graph):
+        opt.step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    main = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        fb_graphs[k % nb].replay()
+        if world > 1:      # coordinate gradients on the second stream, under the all-reduce
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                cg_graphs[k % nb].replay()
+            average_gradients(params, opt.flat_grads)
+            main.wait_stream(side)
+        else:
+            cg_graphs[k % nb].replay()
+        up_graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    atoms = float(sum(batches[k % nb].n_atoms for k in range(args.steps)))
+    loss = float(step.l2s[:batches[(args.steps - 1) % nb].n_mols].mean())
+    if world > 1:
+        t = torch.tensor([ms, atoms], dtype=torch.float64, device=dev)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, atoms = float(tmax[0]), float(t[1])
+    if rank == 0:
+        print(json.dumps({
+            "metric": "training step atoms/sec (fp32, 1024-mol batch per GPU)", "value": atoms / (ms * 1e-3),
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 (tf32x3 tensor-core products in the atomic networks)", "data": "synthetic",
+            "final_loss": loss, "gpu_launches": args.steps * FusedTrainStep.KERNELS,
+            "config": {"workload": "config3: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian, He init) + MSE "
+                                   "+ backward into weights and coordinates + NCCL all-reduce + Nadam",
+                       "molecules_per_step_per_gpu": args.mols, "path": "fused (C ABI only, no autograd)",
+                       "launch": "cuda_graph (forward+backward, coordinate gradient, update; all-reduce eager, "
+                                 "overlapping the coordinate gradient)"}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -468,6 +565,9 @@ def main():
                     help="aev: the benchmark metric (sort + featurize + featurize_grad); train: the full "
                          "data-parallel training step of benchmark configuration 3; forces: energies + forces of "
                          "config-1 batches through the C ABI only (both reported separately)")
+    ap.add_argument("--train-path", default="fused", choices=["fused", "autograd"],
+                    help="train workload: fused = C-ABI calls only (FusedTrainStep); autograd = torch autograd "
+                         "drives the same kernels (what TrainerMultiTower does)")
     ap.add_argument("--e2e-slots", type=int, default=4,
                     help="batches in flight (one stream each) in the end-to-end measurement")
     ap.add_argument("--case", default="config1", choices=["config1", "config2", "config4"],
@@ -483,7 +583,10 @@ def main():
         run_reference_arm(args)
         return
     if args.workload == "train":
-        run_train_workload(args)
+        if args.train_path == "fused":
+            run_fused_train_workload(args)
+        else:
+            run_train_workload(args)
         return
     if args.workload == "forces":
         run_forces_workload(args)

@@ -276,6 +276,23 @@ int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* args_host, const int
                             int split_precision, void* stream);
 
 /*
+ * Molecule energies and the squared-error loss -- replaces tf.gather + tf.segment_sum + the
+ * squared difference of khan/model/nn.py:171-172 and khan/training/trainer_multi_tower.py:350,390-392.
+ *   mol_energy[m] = sum over the atoms i of molecule m of atom_energy_sorted[gather_idxs[i]]
+ * (atom_energy_sorted is in the element-sorted order in which the networks produce it,
+ * gather_idxs as returned by ani_sort).  With `labels` (one target per molecule):
+ *   l2s[m] = (mol_energy[m] - labels[m])^2                                   (if l2s != NULL)
+ *   grad_atom_energy_sorted[gather_idxs[i]] = grad_scale * 2 (mol_energy[m] - labels[m])
+ * i.e. with grad_scale = 1 / n_mols the derivative of the mean squared error with respect to
+ * every atomic energy, in the order ani_mlp_backward_f32 reads it (if != NULL; entries of atoms
+ * outside every molecule are left untouched).  One warp per molecule, no atomics.
+ */
+int ani_molecule_energy_f32(const float* atom_energy_sorted, const int* gather_idxs, const int* mol_offsets,
+                            const int* mol_atom_counts, int n_mols, int n_atoms, const float* labels,
+                            float grad_scale, float* mol_energy, float* l2s, float* grad_atom_energy_sorted,
+                            void* stream);
+
+/*
  * One optimiser step over a flat float32 weight buffer, two launches: global-norm clipping,
  * Adam with Nesterov momentum, and the exponential moving average of the weights.  It takes the
  * place of tf.clip_by_global_norm + NadamOptimizer.apply_gradients +

@@ -18,7 +18,7 @@ CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
 HEADERS = ["ani_params.h", "ani_common.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_grad.cuh",
-           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh"]
+           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh", "ani_energy.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -71,6 +71,7 @@ SIGNATURES = {
     "ani_featurize_grad_inverse_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
     "ani_mlp_backward_f32": (_i, [ctypes.POINTER(MlpBackwardArgs), c_int_p, _i, _vp]),
     "ani_mlp_weight_grad_f32": (_i, [ctypes.POINTER(MlpWeightGradArgs), c_int_p, _i, _vp]),
+    "ani_molecule_energy_f32": (_i, [_vp] * 4 + [_i, _i, _vp, ctypes.c_float, _vp, _vp, _vp, _vp]),
     "ani_nadam_step_f32": (_i, [_vp] * 5 + [ctypes.c_longlong, _vp, _vp, _vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_f64": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),

@@ -19,6 +19,7 @@
 #include "ani_mlp_wgrad.cuh"
 #include "ani_charge.cuh"
 #include "ani_optim.cuh"
+#include "ani_energy.cuh"
 #include "ani_sort.cuh"
 
 namespace {
@@ -727,6 +728,24 @@ int ani_mlp_weight_grad_f32(const ani_mlp_weight_grad_args* a, const int* acs_ho
     p.range_start[kTypes] = ranges;
     cudaStream_t st = (cudaStream_t)stream;
     return split_precision ? mlp_wgrad_launch<true>(p, ranges, st) : mlp_wgrad_launch<false>(p, ranges, st);
+}
+
+int ani_molecule_energy_f32(const float* atom_energy_sorted, const int* gather_idxs, const int* mol_offsets,
+                            const int* mol_atom_counts, int n_mols, int n_atoms, const float* labels,
+                            float grad_scale, float* mol_energy, float* l2s, float* grad_atom_energy_sorted,
+                            void* stream)
+{
+    if (n_mols < 0 || n_atoms < 0) return ANI_ERR_BAD_SIZE;
+    if (n_mols == 0) return ANI_OK;
+    if (!mol_offsets || !mol_atom_counts || !mol_energy) return ANI_ERR_NULL_POINTER;
+    if (n_atoms > 0 && (!atom_energy_sorted || !gather_idxs)) return ANI_ERR_NULL_POINTER;
+    int grid = 0;
+    if (int rc = charge_grid(n_mols, &grid)) return rc;
+    molecule_energy_kernel<kNW><<<grid, kNW * kWarp, 0, (cudaStream_t)stream>>>(
+        atom_energy_sorted, gather_idxs, mol_offsets, mol_atom_counts, n_mols, n_atoms, labels, grad_scale,
+        mol_energy, l2s, grad_atom_energy_sorted);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
 }
 
 int ani_nadam_step_f32(float* params, const float* grads, float* m, float* v, float* ema,

@@ -1,6 +1,6 @@
 """Energies and forces of staged batches through the C ABI only (no autograd):
 
-    ani_sort -> featurize -> atomic networks (forward) -> molecule sums
+    ani_sort -> featurize -> atomic networks (forward) -> molecule sums (ani_molecule_energy)
              -> atomic networks (backward to the features, dE_mol/dE_atom = 1) -> featurize_grad
 
 which is what the reference evaluates for ``predict`` + ``coordinate_gradients``
@@ -46,10 +46,10 @@ class EnergyForces:
         ann = self.model.anns[t]
         return [w.detach() for w in ann.Ws], [b.detach() for b in ann.bs]
 
-    def run(self, sb: StagedBatch, mol_ids: torch.Tensor, stream: ctypes.c_void_p | None = None) -> None:
+    def run(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None) -> None:
         """One pass over the batch staged in ``sb``.  Afterwards ``self.mol_energy[:sb.n_mols]``
         holds the molecule energies and ``sb.grads[:, :sb.n_atoms]`` dE/dx, dE/dy, dE/dz (forces are
-        their negatives).  ``mol_ids``: int64 molecule index of every atom (device)."""
+        their negatives)."""
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this evaluator")
         if stream is None:
@@ -78,11 +78,11 @@ class EnergyForces:
             bwd.grad_features[t] = _ptr(sb.upstream, s * FEATURE_SIZE)   # the upstream of featurize_grad
         _lib.check(lib.ani_mlp_forward_f32(ctypes.byref(fwd), sb._acs_ptr, self.act_id, int(self.split), stream),
                    "ani_mlp_forward_f32")
-        # molecule energies: atom order = sorted order gathered, then one scatter-add per molecule
-        atom_e = self.energy_sorted[:n][sb.gather[:n].long()]
-        self.mol_energy[:sb.n_mols].zero_().index_add_(0, mol_ids[:n], atom_e)
+        _lib.check(lib.ani_molecule_energy_f32(_ptr(self.energy_sorted), _ptr(sb.gather), _ptr(sb.mol_offsets),
+                                               _ptr(sb.mol_counts), sb.n_mols, n, None, 0.0,
+                                               _ptr(self.mol_energy), None, None, stream), "ani_molecule_energy_f32")
         _lib.check(lib.ani_mlp_backward_f32(ctypes.byref(bwd), sb._acs_ptr, int(self.split), stream),
                    "ani_mlp_backward_f32")
         sb.run_featurize_grad(stream)
 
-    KERNELS_PER_PASS = 6   # sort, featurize, mlp forward, mlp backward, zero fill, featurize_grad (+ 4 small torch kernels)
+    KERNELS_PER_PASS = 7   # sort, featurize, mlp forward, molecule sums, mlp backward, zero fill, featurize_grad

@@ -169,12 +169,64 @@ def test_energy_forces_evaluator_matches_the_trainer():
     want_g = np.concatenate(list(tr.coordinate_gradients(ds, batch_size=64)), axis=0)      # (n_atoms, 3)
     sb = StagedBatch(b.n_atoms, b.n_mols)
     sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
-    mol_ids = torch.from_numpy(np.repeat(np.arange(b.n_mols), b.mol_atom_counts)).cuda()
     ev = EnergyForces(tr.model, b.n_atoms, b.n_mols)
     for _ in range(2):                      # twice: the buffers are reused
-        ev.run(sb, mol_ids)
+        ev.run(sb)
     torch.cuda.synchronize()
     got_e = ev.mol_energy[:b.n_mols].cpu().numpy()
     got_g = sb.grads[:, :b.n_atoms].cpu().numpy().T
     assert np.abs(got_e - want_e).max() < 1e-5 * np.abs(want_e).max()
     assert np.abs(got_g - want_g).max() < 1e-4 * np.abs(want_g).max()
+
+
+def test_fused_train_step_matches_the_autograd_step():
+    """FusedTrainStep (C ABI only) against the same step driven by torch autograd: same loss,
+    same weight gradients, same coordinate gradients, same weights after the update."""
+    import torch
+    from khan_b200 import ani_mod
+    from khan_b200.model import activations
+    from khan_b200.model.nn import MoleculeNN
+    from khan_b200.staged import HostBatch, StagedBatch
+    from khan_b200.training.fused_step import FusedTrainStep
+    from khan_b200.training.optim import FlatNadam
+    b = syn.config1(n_mols=60)
+    dev = torch.device("cuda", 0)
+    y = torch.from_numpy(np.random.default_rng(1).normal(size=b.n_mols).astype(np.float32)).to(dev)
+    results = []
+    for path in ("fused", "autograd"):
+        model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=11, init="he")
+        params = model.get_parameters()
+        opt = FlatNadam(params, lr=1e-3)
+        if path == "fused":
+            sb = StagedBatch(b.n_atoms, b.n_mols)
+            sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
+            step = FusedTrainStep(model, opt, b.n_atoms, b.n_mols)
+            step.forward_backward(sb, y)
+            step.coordinate_gradient(sb)
+            torch.cuda.synchronize()
+            loss = float(step.l2s[:b.n_mols].mean())
+            coord = sb.grads[:, :b.n_atoms].clone()
+        else:
+            xyz = torch.from_numpy(np.stack(b.coords(np.float32))).to(dev)
+            x, yy, z = (xyz[k].clone().requires_grad_(True) for k in range(3))
+            a = torch.from_numpy(b.atomic_numbers).to(dev)
+            mo, mac = torch.from_numpy(b.mol_offsets).to(dev), torch.from_numpy(b.mol_atom_counts).to(dev)
+            acs = np.bincount(b.atomic_numbers, minlength=4).astype(np.int32)
+            si, gi, _ = ani_mod.ani_sort(a)
+            feat = ani_mod.featurize_sorted_autograd(x, yy, z, a, mo, mac, si, acs)
+            ids = torch.from_numpy(np.repeat(np.arange(b.n_mols), b.mol_atom_counts)).to(dev)
+            pred = torch.zeros(b.n_mols, device=dev).index_add_(0, ids, model.atom_outputs(feat, acs, gi))
+            l = ((pred - y) ** 2).mean()
+            opt.zero_grad()
+            l.backward()
+            loss = float(l)
+            coord = torch.stack([x.grad, yy.grad, z.grad])
+        grads = opt.flat_grads.clone()
+        opt.step()
+        torch.cuda.synchronize()
+        results.append((loss, grads, coord, opt.flat_params.clone()))
+    (l0, g0, c0, w0), (l1, g1, c1, w1) = results
+    assert abs(l0 - l1) < 1e-5 * abs(l1)
+    assert (g0 - g1).abs().max().item() < 1e-4 * g1.abs().max().item()
+    assert (c0 - c1).abs().max().item() < 1e-4 * c1.abs().max().item()
+    assert (w0 - w1).abs().max().item() < 1e-5
