@@ -4,8 +4,8 @@
 //   A. scans the molecule (lane = candidate neighbour j, coordinates from global memory) and
 //      compacts the neighbours into per-element sub-lists in its slice of shared memory:
 //      (r, f_C) for r < R_Rc, and (unit vector, r, f_C) for r < A_Rc;
-//   R. accumulates the 64 radial features with lane = (half, radial shift), walking the
-//      radial sub-lists element by element;
+//   R. accumulates the 64 radial features with lane = (element, pair of radial shifts), every
+//      lane walking the radial sub-list of its element;
 //   B. evaluates, 32 neighbour pairs at a time (lane = pair), the 8 theta factors and the
 //      4 radial factors of each triplet into shared memory;
 //   C. contracts them with lane = (theta, shift): acc += A[theta][pair] * BF[shift][pair],
@@ -217,24 +217,25 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
             }
 
             ANI_PHASE(1);
-            // ---- R: radial features, lane = (half, shift) ----
+            // ---- R: radial features, lane = (element of the neighbour, pair of shifts): every lane
+            // walks the radial sub-list of its element and finishes two of the 64 features ----
 #if !(ANI_ABLATE & 1)
             {
-                const int half = lane >> 4;
-                const T shift = (T)c_tab.R_Rs[lane & 15];
-                T acc[kTypes];
-#pragma unroll
-                for (int g = 0; g < kTypes; g++) {
-                    acc[g] = (T)0;
-                    for (int p = half; p < cR[g]; p += 2) {
+                const int g = lane >> 3, sp = lane & 7;
+                const Pair<T> neg_shift{-(T)c_tab.R_Rs[2 * sp], -(T)c_tab.R_Rs[2 * sp + 1]};
+                const int n_g = pick4(cR, g);
+                const int n_max = max(max(cR[0], cR[1]), max(cR[2], cR[3]));
+                Pair<T> acc{(T)0, (T)0};
+                for (int p = 0; p < n_max; p++) {
+                    if (p < n_g) {
                         const Vec2<T> e = ws.rad[g * CAPR + p];
-                        const T d = e.x - shift;
-                        acc[g] += Num<T>::exp_neg((T)kR_eta, d * d) * e.y;
+                        const Pair<T> d = padd(Pair<T>{e.x, e.x}, neg_shift);
+                        const Pair<T> d2 = pmul(d, d);
+                        const Pair<T> v{Num<T>::exp_neg((T)kR_eta, d2.x), Num<T>::exp_neg((T)kR_eta, d2.y)};
+                        acc = pfma(v, Pair<T>{e.y, e.y}, acc);
                     }
-                    acc[g] += __shfl_xor_sync(kFull, acc[g], 16);
                 }
-                row[lane] = lane < 16 ? acc[0] : acc[1];
-                row[32 + lane] = lane < 16 ? acc[2] : acc[3];
+                *reinterpret_cast<Vec2<T>*>(row + g * kNumRs + 2 * sp) = Vec2<T>{acc.x, acc.y};
             }
 #endif
 
@@ -287,6 +288,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
                     const unsigned next_id = ws.pt.quad_bucket[(c0 >> 2) + 8];
 #pragma unroll
                     for (int q = 0; q < 8; q++) {
+                        if (c0 + 4 * q >= total) break;   // the rest of the chunk is past the list
                         T av[4], bv[4];
                         load4(a_row + 4 * q, av);
                         load4(b_row + 4 * q, bv);
