@@ -8,4 +8,16 @@ def __getattr__(name):
     if name in ("TrainerMultiTower", "TrainerMultiGPU"):
         from .training import trainer_multi_tower as t
         return getattr(t, name)
+    if name == "FlatNadam":
+        from .training.optim import FlatNadam
+        return FlatNadam
+    if name == "FusedTrainStep":
+        from .training.fused_step import FusedTrainStep
+        return FusedTrainStep
+    if name == "EnergyForces":
+        from .inference import EnergyForces
+        return EnergyForces
+    if name in ("BatchFeeder", "PackedDataset"):
+        from .data import feeder
+        return getattr(feeder, name)
     raise AttributeError(name)

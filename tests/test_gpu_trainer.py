@@ -230,3 +230,40 @@ def test_fused_train_step_matches_the_autograd_step():
     assert (g0 - g1).abs().max().item() < 1e-4 * g1.abs().max().item()
     assert (c0 - c1).abs().max().item() < 1e-4 * c1.abs().max().item()
     assert (w0 - w1).abs().max().item() < 1e-5
+
+
+def test_molecule_energy_kernel_on_a_ragged_table():
+    """ani_molecule_energy_f32 directly: sums through gather_idxs, squared errors, the MSE gradient
+    scattered back to the sorted order; empty molecules give 0; a bad gather index is reported."""
+    import ctypes
+    import torch
+    from khan_b200 import _lib, ani_mod
+    rng = np.random.default_rng(4)
+    counts = np.array([3, 0, 5, 1, 40, 2], np.int32)
+    offs = (np.cumsum(counts) - counts).astype(np.int32)
+    n = int(counts.sum())
+    e_sorted = rng.normal(size=n).astype(np.float32)
+    gather = rng.permutation(n).astype(np.int32)
+    labels = rng.normal(size=len(counts)).astype(np.float32)
+    dev = "cuda:0"
+    t = {k: torch.from_numpy(v).to(dev) for k, v in dict(e=e_sorted, g=gather, o=offs, c=counts, y=labels).items()}
+    mol = torch.full((len(counts),), 7.0, device=dev)
+    l2s = torch.zeros(len(counts), device=dev)
+    grad = torch.zeros(n, device=dev)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda x: ctypes.c_void_p(x.data_ptr())
+    rc = _lib.lib().ani_molecule_energy_f32(p(t["e"]), p(t["g"]), p(t["o"]), p(t["c"]), len(counts), n, p(t["y"]),
+                                            1.0 / len(counts), p(mol), p(l2s), p(grad), st)
+    assert rc == 0 and ani_mod.device_status() == 0
+    atom_e = e_sorted[gather]
+    want = np.array([atom_e[o:o + c].sum(dtype=np.float64) for o, c in zip(offs, counts)])
+    assert np.allclose(mol.cpu().numpy(), want, rtol=1e-5, atol=1e-6) and mol[1].item() == 0.0
+    assert np.allclose(l2s.cpu().numpy(), (want - labels) ** 2, rtol=1e-4, atol=1e-6)
+    want_g = np.zeros(n)
+    want_g[gather] = np.repeat(2 * (want - labels) / len(counts), counts)
+    assert np.allclose(grad.cpu().numpy(), want_g, rtol=1e-4, atol=1e-6)
+    bad = t["g"].clone()
+    bad[4] = n + 3
+    assert _lib.lib().ani_molecule_energy_f32(p(t["e"]), p(bad), p(t["o"]), p(t["c"]), len(counts), n, None, 0.0,
+                                              p(mol), None, None, st) == 0
+    assert ani_mod.device_status() == -6
