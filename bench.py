@@ -433,6 +433,7 @@ def run_train_workload(args):
     params = model.get_parameters()
     from khan_b200.training.optim import FlatNadam
     opt = FlatNadam(params, lr=1e-3, clip_norm=5.0)    # flat buffers: clip + Nadam + moving average in one call
+    model.accumulate_into_grad = True                  # weight gradients are added straight into those buffers
     nb = max(1, min(8, args.steps))
     staged = []
     for k, b in enumerate(syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)):

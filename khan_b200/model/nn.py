@@ -124,10 +124,10 @@ class _FusedMlp(torch.autograd.Function):
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().ani_mlp_forward_f32(ctypes.byref(args), acs_arr.ctypes.data_as(_lib.c_int_p),
-                                                      int(act_id), int(bool(split)), stream),
+                                                      int(act_id), int(split) & 1, stream),
                        "ani_mlp_forward_f32")
         ctx.save_for_backward(features, *acts, *dacts, *params)
-        ctx.acs, ctx.act_fn, ctx.split = acs_arr, act_fn, bool(split)
+        ctx.acs, ctx.act_fn, ctx.split, ctx.accumulate = acs_arr, act_fn, bool(int(split) & 1), bool(int(split) & 2)
         return energy
 
     @staticmethod
@@ -175,13 +175,15 @@ class _FusedMlp(torch.autograd.Function):
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().ani_mlp_backward_f32(ctypes.byref(args), acs.ctypes.data_as(_lib.c_int_p),
                                                        int(ctx.split), stream), "ani_mlp_backward_f32")
-        # weight and bias gradients: one more launch.  Where a parameter already has a gradient
-        # buffer (the flat optimiser gives every parameter one) the kernel adds into it directly
-        # and None is returned for it, which is what autograd's own accumulation would do with
-        # 32 separate additions; otherwise the gradients are slices of one zero-filled buffer.
+        # weight and bias gradients: one more launch.  With `accumulate_into_grad` set on the model
+        # (only valid when gradients are obtained with .backward(), as the trainer does) and a
+        # gradient buffer on every parameter (the flat optimiser provides them) the kernel adds
+        # into those buffers directly and None is returned, which is what autograd's own
+        # accumulation would do with 32 separate additions; otherwise the gradients are slices
+        # of one zero-filled buffer and are returned.
         sizes = [384 * 128, 128, 128 * 128, 128, 128 * 64, 64, 64, 4]   # the last slot holds b4 (1 value): keeps every slice 16-byte aligned
         per_elem = sum(sizes)
-        direct = all(p.grad is not None and p.grad.is_contiguous() and p.grad.dtype == torch.float32
+        direct = ctx.accumulate and all(p.grad is not None and p.grad.is_contiguous() and p.grad.dtype == torch.float32
                      and p.grad.data_ptr() % 16 == 0 for p in params)
         wbuf = None if direct else torch.zeros(4 * per_elem, **f32)
         wargs = _lib.MlpWeightGradArgs()
@@ -242,6 +244,7 @@ class MoleculeNN:
         self.precision = precision
         self.activation_fn = activation_fn
         self.split_precision = split_precision
+        self.accumulate_into_grad = False   # see _FusedMlp.backward; set by trainers that call .backward()
         self.anns = [AtomNN(layer_sizes, precision, activation_fn, atom_type=t, prefix=prefix,
                             device=device, generator=gen, init=init) for t in self.type_map]
 
@@ -271,8 +274,9 @@ class MoleculeNN:
             for a in self.anns:
                 for w, b in zip(a.Ws, a.bs):
                     params.extend([w, b])
+            flags = (1 if self.split_precision else 0) | (2 if self.accumulate_into_grad else 0)
             return _FusedMlp.apply(features, acs, activations.KERNEL_ID[self.activation_fn],
-                                   self.split_precision, self.activation_fn, *params)
+                                   flags, self.activation_fn, *params)
         starts = np.concatenate([[0], np.cumsum(acs)])
         parts = [ann.atom_energies(features[int(starts[t]):int(starts[t + 1])])
                  for t, ann in enumerate(self.anns)]

@@ -118,6 +118,7 @@ class TrainerMultiTower:
             self.optimizer = FlatNadam(self.parameters, lr=self.learning_rate, clip_norm=5.0,
                                        ema_decay=self.ema_decay)
             self.ema = [self.optimizer.ema_of(k) for k in range(len(self.parameters))]
+            self.model.accumulate_into_grad = True    # gradients only ever come from .backward() here
         else:
             self.optimizer = torch.optim.NAdam(self.parameters, lr=self.learning_rate, betas=(0.9, 0.999), eps=1e-8)
             self.ema = [p.detach().clone() for p in self.parameters]

@@ -128,6 +128,7 @@ def test_weight_gradients_accumulate_into_existing_buffers():
     acs = np.array([140, 0, 33, 600])
     n = int(acs.sum())
     model = nn.MoleculeNN(activation_fn=activations.celu, seed=8, init="he")
+    model.accumulate_into_grad = True
     gen = torch.Generator(device="cuda").manual_seed(9)
     feats = torch.rand((n, 384), device="cuda", generator=gen)
     w = torch.randn(n, device="cuda", generator=gen)
@@ -139,3 +140,8 @@ def test_weight_gradients_accumulate_into_existing_buffers():
     for p, f, ptr in zip(params, first, ptrs):
         assert p.grad.data_ptr() == ptr
         assert (p.grad - 2 * f).abs().max().item() <= 1e-5 * f.abs().max().item()
+    # without the flag torch.autograd.grad still gets its gradients returned
+    model.accumulate_into_grad = False
+    got = torch.autograd.grad((model.atom_energies_sorted(feats, acs) * w).sum(), params)
+    for g, f in zip(got, first):
+        assert (g - f).abs().max().item() <= 1e-5 * f.abs().max().item()

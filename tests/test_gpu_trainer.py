@@ -197,6 +197,7 @@ def test_fused_train_step_matches_the_autograd_step():
         model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=11, init="he")
         params = model.get_parameters()
         opt = FlatNadam(params, lr=1e-3)
+        model.accumulate_into_grad = path == "autograd"
         if path == "fused":
             sb = StagedBatch(b.n_atoms, b.n_mols)
             sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
