@@ -332,8 +332,9 @@ void FN(oracle_featurize_grad_inverse)(const REAL *X, const REAL *Y, const REAL 
  * Types follow the C++ expression: k_e is `const float` (parameters.h:10), so
  * k_e*q_i*q_j is evaluated in NumericType; (1 - f_C) is double, so the product, the
  * division and the addition to the NumericType accumulator run in double and are rounded
- * once per pair.  The reference has no golden numbers for this op (its tests check only
- * the gradient against finite differences, gpu_featurizer/test_kernel.py:412-447).
+ * once per pair.  PARITY UNPINNED for the energy values: the reference has no golden numbers
+ * for this op (its tests check only the gradient against finite differences,
+ * gpu_featurizer/test_kernel.py:412-447, which tests/test_oracle_charge.py repeats here).
  */
 void FN(oracle_charge)(const REAL *X, const REAL *Y, const REAL *Z, const REAL *Q,
                        const int *mol_offsets, const int *mol_counts, int n_mols, REAL *energies)
