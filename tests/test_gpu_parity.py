@@ -326,3 +326,28 @@ def test_inconsistent_offsets_are_reported_not_dereferenced(gpu):
     bad_mo = torch.tensor([0, 9], dtype=torch.int32, device=x.device)  # 9 + 3 > 11 atoms
     ani_mod.featurize(x, y, z, a, bad_mo, mac, si, ac)
     assert ani_mod.device_status() == -6
+
+
+def test_rigid_motion_invariance_at_full_size(gpu):
+    """Size-independent property at the full config-1 size: features do not change under a rigid
+    motion of every molecule, and the coordinate gradient rotates with the coordinates."""
+    b = syn.config1()
+    rng = np.random.default_rng(17)
+    q, _ = np.linalg.qr(rng.normal(size=(3, 3)))
+    if np.linalg.det(q) < 0:
+        q[:, 0] = -q[:, 0]
+    shift = np.array([0.7, -1.3, 2.1])
+    import copy
+    moved = copy.copy(b)
+    xyz = np.stack(b.coords(np.float64), axis=1) @ q.T + shift
+    moved.xs, moved.ys, moved.zs = xyz[:, 0].copy(), xyz[:, 1].copy(), xyz[:, 2].copy()
+    assert np.abs(np.stack(moved.coords(np.float64), axis=1) - xyz).max() == 0
+    f0 = gpu.gpu_featurize(b, np.float64)
+    f1 = gpu.gpu_featurize(moved, np.float64)
+    for t in range(4):
+        assert normwise(f1[t], f0[t]) < 1e-11
+    ac = np.bincount(b.atomic_numbers, minlength=4)
+    up = syn.upstream_grads(b, ac, dtype=np.float64)
+    g0 = np.stack(gpu.gpu_featurize_grad(b, np.float64, up), axis=1)
+    g1 = np.stack(gpu.gpu_featurize_grad(moved, np.float64, up), axis=1)
+    assert np.abs(g1 - g0 @ q.T).max() < 1e-10 * np.abs(g0).max()
