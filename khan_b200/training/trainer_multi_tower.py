@@ -325,14 +325,31 @@ class TrainerMultiTower:
                 e.mul_(decay).add_(p.detach(), alpha=1.0 - decay)
 
     # ------------------------------------------------------------------ user-facing helpers
+    def _device_predictions(self, dataset, batch_size):
+        """Energies (and squared errors, when the data set has targets) of every batch, left on
+        the devices: nothing here waits for the GPU, so the host runs ahead of it by as many
+        batches as the feeder allows, and the caller synchronises once."""
+        np_dt = np.float32 if self.precision == torch.float32 else np.float64
+        it = BatchFeeder(PackedDataset.from_raw(dataset, np_dt), batch_size, False, None,
+                         devices=self.towers, depth=2, hold=self.num_towers)
+        preds, l2s = [], []
+        try:
+            with torch.no_grad():
+                for k, fed in enumerate(it):
+                    out = self._tower_forward(self.towers[k % self.num_towers], fed, False)
+                    preds.append(out["pred"])
+                    if fed.ys is not None:
+                        l2s.append((out["pred"] - fed.ys) ** 2)
+        finally:
+            it.close()
+        return preds, l2s
+
     def predict(self, dataset, batch_size=2048):
         """Predicted energies in dataset order (``trainer_multi_tower.py:655-678``)."""
-        ordered = []
-        for ys, ids in self.feed_dataset(dataset, False, [self.tower_preds, self.tower_bids], batch_size):
-            order = np.argsort(np.array(ids))
-            for k in order:
-                ordered.extend(ys[k].tolist())
-        return ordered
+        preds, _ = self._device_predictions(dataset, batch_size)
+        if not preds:
+            return []
+        return torch.cat([p.to(self.towers[0]) for p in preds]).cpu().tolist()
 
     def featurize(self, dataset, batch_size=1024):
         """Per-molecule feature arrays, in dataset order (``trainer_multi_tower.py:617-653``)."""
@@ -348,15 +365,14 @@ class TrainerMultiTower:
         ops = [self.tower_coord_grads, self.tower_mos, self.tower_bids]
         for grads, mos, ids in self.feed_dataset(dataset, False, ops, batch_size):
             for k in np.argsort(np.array(ids)):
-                gx, gy, gz = grads[k]
-                cut = mos[k][1:]
-                for x, y, z in zip(np.split(gx, cut), np.split(gy, cut), np.split(gz, cut)):
-                    yield np.vstack([x, y, z]).transpose()
+                # one (n_atoms, 3) array per batch, cut once into per-molecule pieces
+                yield from np.split(np.stack(grads[k], axis=1), mos[k][1:])
 
     def eval_abs_rmse(self, dataset, batch_size=1024):
-        res = list(self.feed_dataset(dataset, False, [self.unordered_l2s], batch_size))
-        l2s = np.concatenate([np.concatenate(r[0]).reshape(-1) for r in res])
-        return float(np.sqrt(np.mean(l2s)) * HARTREE_TO_KCAL_PER_MOL)
+        """Absolute RMSE of the energies in kcal/mol (``trainer_multi_tower.py:560-578``)."""
+        _, l2s = self._device_predictions(dataset, batch_size)
+        total = torch.cat([v.to(self.towers[0]).double() for v in l2s])
+        return float(torch.sqrt(total.mean())) * HARTREE_TO_KCAL_PER_MOL
 
 
     def eval_rel_rmse(self, dataset, group_ys, batch_size=1024):
