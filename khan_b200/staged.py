@@ -36,9 +36,11 @@ class StagedBatch:
         self.n_atoms, self.n_mols = n_atoms, n_mols
         d, i32 = self.device, torch.int32
         self.xyz = torch.empty((3, n_atoms), dtype=dtype, device=d)
+        self.x, self.y, self.z = self.xyz[0], self.xyz[1], self.xyz[2]   # what the kernels read
         self.types = torch.empty(n_atoms, dtype=i32, device=d)
         self.mol_offsets = torch.empty(n_mols, dtype=i32, device=d)
         self.mol_counts = torch.empty(n_mols, dtype=i32, device=d)
+        self._own_inputs = (self.x, self.y, self.z, self.types, self.mol_offsets, self.mol_counts)
         self.scatter = torch.empty(n_atoms, dtype=i32, device=d)
         self.gather = torch.empty(n_atoms, dtype=i32, device=d)
         self.counts = torch.empty(4, dtype=i32, device=d)
@@ -57,8 +59,19 @@ class StagedBatch:
         if int(self.acs_host.sum()) != self.n_atoms:
             raise ValueError("atom counts do not add up to n_atoms")
 
+    def adopt(self, fed) -> None:
+        """Uses the device tensors of a fed batch (``khan_b200.data.feeder.FedBatch``) as the inputs of
+        the next passes, without copying them; the sort / feature / gradient buffers stay this
+        object's own.  The fed batch must stay alive until those passes have been enqueued."""
+        if fed.x.dtype != self.dtype:
+            raise ValueError("precision of the fed batch does not match")
+        self.set_shape(fed.n_atoms, fed.n_mols, fed.acs)
+        self.x, self.y, self.z = fed.x, fed.y, fed.z
+        self.types, self.mol_offsets, self.mol_counts = fed.types, fed.mol_offsets, fed.mol_counts
+
     def upload(self, host: "HostBatch", non_blocking: bool = True, with_upstream: bool = True) -> int:
         """Copies one pinned host batch in; returns the bytes moved."""
+        self.x, self.y, self.z, self.types, self.mol_offsets, self.mol_counts = self._own_inputs
         self.set_shape(host.n_atoms, host.n_mols, host.acs)
         n, m = self.n_atoms, self.n_mols
         for r in range(3):   # row by row: each copy is one contiguous range on both sides
@@ -94,8 +107,7 @@ class StagedBatch:
 
     def run_featurize(self, stream: ctypes.c_void_p) -> None:
         fn = getattr(_lib.lib(), "ani_featurize_" + self.suffix)
-        cap = self.n_atoms_cap
-        _lib.check(fn(_ptr(self.xyz), _ptr(self.xyz, cap), _ptr(self.xyz, 2 * cap), _ptr(self.types),
+        _lib.check(fn(_ptr(self.x), _ptr(self.y), _ptr(self.z), _ptr(self.types),
                       _ptr(self.mol_offsets), _ptr(self.mol_counts), self.n_mols, _ptr(self.scatter),
                       *self._element_ptrs(self.features), self._acs_ptr, stream),
                    "ani_featurize_" + self.suffix)
@@ -103,7 +115,7 @@ class StagedBatch:
     def run_featurize_grad(self, stream: ctypes.c_void_p) -> None:
         fn = getattr(_lib.lib(), "ani_featurize_grad_" + self.suffix)
         cap = self.n_atoms_cap
-        _lib.check(fn(_ptr(self.xyz), _ptr(self.xyz, cap), _ptr(self.xyz, 2 * cap), _ptr(self.types),
+        _lib.check(fn(_ptr(self.x), _ptr(self.y), _ptr(self.z), _ptr(self.types),
                       _ptr(self.mol_offsets), _ptr(self.mol_counts), self.n_mols, _ptr(self.scatter),
                       *self._element_ptrs(self.upstream), _ptr(self.grads), _ptr(self.grads, cap),
                       _ptr(self.grads, 2 * cap), self._acs_ptr, stream),

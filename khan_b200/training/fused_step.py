@@ -51,10 +51,11 @@ class FusedTrainStep:
                 if p.grad is None or p.grad.data_ptr() % 4:
                     raise ValueError("parameters must have gradient buffers (FlatNadam provides them)")
 
-    def forward_backward(self, sb: StagedBatch, labels: torch.Tensor, stream=None) -> None:
+    def forward_backward(self, sb: StagedBatch, labels: torch.Tensor, stream=None, feature_grad: bool = True) -> None:
         """Everything up to the weight gradients.  Afterwards ``self.l2s[:n_mols]`` holds the squared
         errors, the flat gradient buffer the weight gradients of this batch (it is zeroed here
-        first) and ``sb.upstream`` dLoss/dfeatures."""
+        first) and, unless ``feature_grad`` is False (energy-only training: the three products
+        towards the features are skipped), ``sb.upstream`` dLoss/dfeatures."""
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this step")
         if stream is None:
@@ -85,7 +86,7 @@ class FusedTrainStep:
             bwd.grad_energy[t] = wg.grad_energy[t] = _ptr(self.grad_energy_sorted, s)
             bwd.dz1[t], bwd.dz2[t], bwd.dz3[t] = (_ptr(z, s * z.shape[1]) for z in self.dzs)
             wg.dz1[t], wg.dz2[t], wg.dz3[t] = bwd.dz1[t], bwd.dz2[t], bwd.dz3[t]
-            bwd.grad_features[t] = _ptr(sb.upstream, s * FEATURE_SIZE)
+            bwd.grad_features[t] = _ptr(sb.upstream, s * FEATURE_SIZE) if feature_grad else None
             wg.dw1[t], wg.dw2[t], wg.dw3[t], wg.dw4[t] = _ptr(w1.grad), _ptr(w2.grad), _ptr(w3.grad), _ptr(w4.grad)
             wg.db1[t], wg.db2[t], wg.db3[t], wg.db4[t] = _ptr(b1.grad), _ptr(b2.grad), _ptr(b3.grad), _ptr(b4.grad)
         _lib.check(lib.ani_mlp_forward_f32(ctypes.byref(fwd), sb._acs_ptr, self.act_id, int(self.split), stream),

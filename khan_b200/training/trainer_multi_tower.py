@@ -140,6 +140,8 @@ class TrainerMultiTower:
         self.train_op_mse = _Op("train_op_mse")
         self.train_op_forces = _Op("train_op_forces")  # exp(force rmse)
         self.max_norm_ops = _Op("max_norm_ops")
+        self._device_l2s = _Op("_device_l2s")          # squared errors left on the device (no host wait)
+        self._fused = None                              # (capacity, StagedBatch, FusedTrainStep) of the fused path
 
     # ------------------------------------------------------------------ bookkeeping
     def initialize(self):
@@ -231,12 +233,68 @@ class TrainerMultiTower:
         need_grad = bool(training) or "tower_coord_grads" in names or "tower_force_rmses" in names
         need_coord = "tower_coord_grads" in names or "tower_force_rmses" in names or "train_op_forces" in names
         np_dt = np.float32 if self.precision == torch.float32 else np.float64
-        it = BatchFeeder(PackedDataset.from_raw(dataset, np_dt), batch_size, shuffle, fuzz,
-                         devices=self.towers, depth=2, hold=self.num_towers)
+        packed = PackedDataset.from_raw(dataset, np_dt)
+        it = BatchFeeder(packed, batch_size, shuffle, fuzz, devices=self.towers, depth=2, hold=self.num_towers)
+        fused_names = {"train_op", "train_op_rmse", "train_op_mse", "unordered_l2s", "tower_l2s", "tower_exp_loss",
+                       "tower_bids", "_device_l2s"}
+        fused = (self.num_towers == 1 and isinstance(self.optimizer, FlatNadam) and self.model.fused
+                 and len(training) == 1 and training[0] != "train_op_forces" and set(names) <= fused_names
+                 and packed.ys is not None and packed.num_mols() > 0)
         try:
-            yield from self._feed_rounds(it, names, training, need_grad, need_coord, before_hooks)
+            if fused:
+                yield from self._fused_rounds(it, names, training[0], packed.capacity(batch_size), before_hooks)
+            else:
+                yield from self._feed_rounds(it, names, training, need_grad, need_coord, before_hooks)
         finally:
             it.close()
+
+    def _fused_rounds(self, it, names, kind, capacity, before_hooks):
+        """Energy training on one device without autograd (``FusedTrainStep``): per batch sort,
+        featurize, networks forward, molecule energies + MSE gradient, networks backward, weight
+        gradients; the gradient of the requested loss is the MSE gradient times a scalar --
+        1 / (2 rmse) for the rmse loss, exp(rmse) / (2 rmse) for the reference's exp(rmse) loss
+        (``trainer_multi_tower.py:390-396``) -- computed on the device, so nothing waits for the GPU
+        unless a result is asked for."""
+        from ..staged import StagedBatch
+        from .fused_step import FusedTrainStep
+        cap_atoms, cap_mols = max(capacity[0], 1), max(capacity[1], 1)
+        if self._fused is None or self._fused[0][0] < cap_atoms or self._fused[0][1] < cap_mols:
+            dev = self.towers[0]
+            self._fused = ((cap_atoms, cap_mols), StagedBatch(cap_atoms, cap_mols, device=dev),
+                           FusedTrainStep(self.model, self.optimizer, cap_atoms, cap_mols, device=dev))
+        _, sb, step = self._fused
+        dev = self.towers[0]
+        for fed in it:
+            if before_hooks is not None:
+                self._run_hooks(before_hooks)
+            with torch.cuda.device(dev), torch.no_grad():
+                fed.wait()
+                sb.adopt(fed)
+                step.forward_backward(sb, fed.ys, feature_grad=False)
+                l2 = step.l2s[:fed.n_mols]
+                rmse = None
+                if kind != "train_op_mse" or "tower_exp_loss" in names:
+                    rmse = l2.mean().sqrt().clamp_min(1e-30)
+                if kind == "train_op":
+                    self.optimizer.flat_grads.mul_(torch.exp(rmse) / (2.0 * rmse))
+                elif kind == "train_op_rmse":
+                    self.optimizer.flat_grads.mul_(1.0 / (2.0 * rmse))
+                average_gradients(self.parameters, self.optimizer.flat_grads)
+                self.optimizer.step()
+                self.global_step += 1
+                row = []
+                for n in names:
+                    if n.startswith("train_op"):
+                        row.append(None)
+                    elif n in ("unordered_l2s", "tower_l2s"):
+                        row.append([l2.cpu().numpy()])
+                    elif n == "_device_l2s":
+                        row.append([l2.clone()])
+                    elif n == "tower_exp_loss":
+                        row.append([float(torch.exp(rmse.double()))])
+                    elif n == "tower_bids":
+                        row.append([np.array(fed.index)])
+            yield row
 
     def _feed_rounds(self, it, names, training, need_grad, need_coord, before_hooks):
         done = False
@@ -261,13 +319,19 @@ class TrainerMultiTower:
                     mol_yts, mol_grads = fed.ys, fed.grads
                     res = {"tower_bids": np.array(fed.index), "tower_mos": out["offsets"]}
                     pred = out["pred"]
-                    res["tower_preds"] = pred.detach().cpu().numpy()
+                    # only what was asked for is brought to the host: every copy is a wait for the GPU
+                    if "tower_preds" in names:
+                        res["tower_preds"] = pred.detach().cpu().numpy()
                     if mol_yts is not None:
                         l2 = (pred - mol_yts) ** 2
-                        res["tower_l2s"] = l2.detach().cpu().numpy()
-                        res["unordered_l2s"] = res["tower_l2s"]
+                        if "tower_l2s" in names or "unordered_l2s" in names:
+                            res["tower_l2s"] = l2.detach().cpu().numpy()
+                            res["unordered_l2s"] = res["tower_l2s"]
+                        if "_device_l2s" in names:
+                            res["_device_l2s"] = l2.detach().clone()
                         rmse = torch.sqrt(l2.mean())
-                        res["tower_exp_loss"] = float(torch.exp(rmse.detach().double()))
+                        if "tower_exp_loss" in names:
+                            res["tower_exp_loss"] = float(torch.exp(rmse.detach().double()))
                     if "tower_features" in names:
                         res["tower_features"] = out["feat_buf"].detach()[out["gi"].long()].cpu().numpy()
                     if need_coord:
@@ -392,7 +456,7 @@ class TrainerMultiTower:
         with the best test error in ``save_dir/best.npz``; after ``max_local_epoch_count`` epochs
         without improvement reload them, halve the learning rate and add 128 to the batch size.
         Returns the best test error (kcal/mol)."""
-        train_ops = [self.unordered_l2s, self.train_op]
+        train_ops = [self._device_l2s, self.train_op]
         best = self.eval_abs_rmse(rd_test)
         os.makedirs(save_dir, exist_ok=True)
         best_file = os.path.join(save_dir, "best.npz")
@@ -406,8 +470,8 @@ class TrainerMultiTower:
                 results = list(self.feed_dataset(rd_train, shuffle=True, target_ops=train_ops,
                                                  batch_size=batch_size, before_hooks=self.max_norm_ops,
                                                  fuzz=fuzz))
-                l2s = np.concatenate([np.concatenate(r[0]).reshape(-1) for r in results])
-                train_rmse = float(np.sqrt(np.mean(l2s))) * HARTREE_TO_KCAL_PER_MOL
+                l2s = torch.cat([v.reshape(-1).double() for r in results for v in r[0]])   # one wait per epoch
+                train_rmse = float(torch.sqrt(l2s.mean())) * HARTREE_TO_KCAL_PER_MOL
                 test_rmse = self.eval_abs_rmse(rd_test)
                 line = (f"{save_dir} tpe: {time.time() - start:.2f}s, g-epoch {self.global_epoch_count} "
                         f"l-epoch {self.local_epoch_count} lr {self.learning_rate:.0e} batch_size {batch_size} "

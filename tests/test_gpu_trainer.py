@@ -268,3 +268,29 @@ def test_molecule_energy_kernel_on_a_ragged_table():
     assert _lib.lib().ani_molecule_energy_f32(p(t["e"]), p(bad), p(t["o"]), p(t["c"]), len(counts), n, None, 0.0,
                                               p(mol), None, None, st) == 0
     assert ani_mod.device_status() == -6
+
+
+@pytest.mark.parametrize("op_name", ["train_op", "train_op_rmse", "train_op_mse"])
+def test_fused_training_path_of_the_trainer_matches_autograd(op_name, monkeypatch):
+    """feed_dataset with an energy-training op takes the autograd-free path on one float32 tower;
+    forcing the autograd path (by asking for a result the fused path does not produce) must give
+    the same weights after a few steps."""
+    import torch
+    from khan_b200 import RawDataset, TrainerMultiTower
+    b = syn.config1(n_mols=70)
+    mols = b.molecules()
+    ys = list(np.random.default_rng(2).normal(scale=0.1, size=len(mols)))
+    ds = RawDataset(mols, ys)
+    weights = []
+    for extra in (False, True):
+        tr = TrainerMultiTower(None, [torch.device("cuda", 0)], layer_sizes=(128, 128, 64, 1), seed=21)
+        ops = [getattr(tr, op_name)] + ([tr.tower_preds] if extra else [tr.unordered_l2s])
+        out = list(tr.feed_dataset(ds, False, ops, batch_size=32))
+        assert len(out) == 3 and all(r[0] is None for r in out)
+        if not extra:
+            assert tr._fused is not None and out[0][1][0].shape == (32,)
+        else:
+            assert tr._fused is None
+        assert tr.global_step == 3
+        weights.append(tr.optimizer.flat_params.clone())
+    assert (weights[0] - weights[1]).abs().max().item() < 2e-5
