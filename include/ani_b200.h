@@ -309,6 +309,16 @@ int ani_nadam_step_f32(float* params, const float* grads, float* m, float* v, fl
                        long long n, const float* hyper, void* state, void* stream);
 
 /*
+ * Max-norm constraint on weight rows, one launch: row r is params[row_offsets[r] ..
+ * row_offsets[r] + row_lengths[r]); a row whose Euclidean norm exceeds max_norm is scaled to
+ * norm max_norm.  Replaces the list of tf.assign(w, tf.clip_by_norm(w, 3.0, axes=1)) ops that
+ * the reference runs before every training batch (khan/training/trainer_multi_tower.py:432-436,
+ * `before_hooks=self.max_norm_ops` at :851).  row_offsets / row_lengths are device arrays.
+ */
+int ani_clip_rows_f32(float* params, const int* row_offsets, const int* row_lengths, int n_rows, float max_norm,
+                      void* stream);
+
+/*
  * AniCharge -- replaces the op of gpu_featurizer/ani_charges.cpp:45-56,58-113 (CPU, float and
  * double) and gpu_featurizer/ani_charges_gpu.cu:60-128 (GPU, float only).  Damped Coulomb
  * energy of every molecule,

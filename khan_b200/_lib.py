@@ -73,6 +73,7 @@ SIGNATURES = {
     "ani_mlp_weight_grad_f32": (_i, [ctypes.POINTER(MlpWeightGradArgs), c_int_p, _i, _vp]),
     "ani_molecule_energy_f32": (_i, [_vp] * 4 + [_i, _i, _vp, ctypes.c_float, _vp, _vp, _vp, _vp]),
     "ani_nadam_step_f32": (_i, [_vp] * 5 + [ctypes.c_longlong, _vp, _vp, _vp]),
+    "ani_clip_rows_f32": (_i, [_vp, _vp, _vp, _i, ctypes.c_float, _vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_f64": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_grad_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp, _vp]),

@@ -768,6 +768,20 @@ int ani_nadam_step_f32(float* params, const float* grads, float* m, float* v, fl
     return ANI_OK;
 }
 
+int ani_clip_rows_f32(float* params, const int* row_offsets, const int* row_lengths, int n_rows, float max_norm,
+                      void* stream)
+{
+    if (n_rows < 0 || !(max_norm > 0.0f)) return ANI_ERR_BAD_SIZE;
+    if (n_rows == 0) return ANI_OK;
+    if (!params || !row_offsets || !row_lengths) return ANI_ERR_NULL_POINTER;
+    const int per_block = kOptimThreads / kWarp;
+    const int grid = (n_rows + per_block - 1) / per_block;
+    clip_rows_kernel<<<grid, kOptimThreads, 0, (cudaStream_t)stream>>>(params, row_offsets, row_lengths, n_rows,
+                                                                       max_norm);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
 int ani_charge_f32(const float* xs, const float* ys, const float* zs, const float* qs,
                    const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
                    float* charge_energies, void* stream)

@@ -89,4 +89,29 @@ __global__ void __launch_bounds__(kOptimThreads)
     }
 }
 
+// Max-norm constraint on the rows of the weight matrices: every row whose Euclidean norm
+// exceeds max_norm is scaled back onto the sphere -- tf.clip_by_norm(w, 3.0, axes=1) over all
+// weight matrices (khan/training/trainer_multi_tower.py:432-436), one launch over a row table
+// instead of five small ops per matrix.  One warp per row.
+__global__ void __launch_bounds__(kOptimThreads)
+    clip_rows_kernel(float* __restrict__ w, const int* __restrict__ row_offsets, const int* __restrict__ row_lengths,
+                     int n_rows, float max_norm)
+{
+    const int lane = lane_id();
+    const int warps = gridDim.x * (kOptimThreads / kWarp);
+    for (int r = blockIdx.x * (kOptimThreads / kWarp) + warp_id(); r < n_rows; r += warps) {
+        float* row = w + row_offsets[r];
+        const int len = row_lengths[r];
+        float acc = 0.0f;
+        for (int i = lane; i < len; i += kWarp) acc += row[i] * row[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
+        const float norm = sqrtf(acc);
+        if (norm > max_norm) {
+            const float scale = max_norm / norm;
+            for (int i = lane; i < len; i += kWarp) row[i] *= scale;
+        }
+    }
+}
+
 }  // namespace ani

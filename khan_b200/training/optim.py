@@ -74,6 +74,27 @@ class FlatNadam:
                 self.ema.data_ptr(), self.n, self.hyper.data_ptr(), self.state.data_ptr(), stream),
                 "ani_nadam_step_f32")
 
+    def clip_rows(self, indices, max_norm: float = 3.0) -> None:
+        """Max-norm constraint on the rows of the matrices ``self.params[k]``, k in ``indices``
+        (``tf.clip_by_norm(w, max_norm, axes=1)``): one launch over a row table that is built on the
+        first call."""
+        key = tuple(indices)
+        if getattr(self, "_row_key", None) != key:
+            offs, lens = [], []
+            for k in key:
+                p, o = self.params[k], self.offsets[k]
+                rows, cols = (p.shape[0], p.numel() // p.shape[0]) if p.dim() >= 2 else (1, p.numel())
+                offs.extend(o + r * cols for r in range(rows))
+                lens.extend([cols] * rows)
+            self._row_offsets = torch.tensor(offs, dtype=torch.int32, device=self.device)
+            self._row_lengths = torch.tensor(lens, dtype=torch.int32, device=self.device)
+            self._row_key = key
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ani_clip_rows_f32(self.flat_params.data_ptr(), self._row_offsets.data_ptr(),
+                                                    self._row_lengths.data_ptr(), int(self._row_offsets.numel()),
+                                                    float(max_norm), stream), "ani_clip_rows_f32")
+
     def steps_done(self) -> int:
         """The device-side step counter (synchronises)."""
         return int(self.state[0].item())

@@ -361,7 +361,14 @@ class TrainerMultiTower:
         hooks = hooks if isinstance(hooks, (list, tuple)) else [hooks]
         for h in hooks:
             if isinstance(h, _Op) and h.name == "max_norm_ops":
-                with torch.no_grad():   # tf.clip_by_norm(w, 3.0, axes=1), trainer_multi_tower.py:432-436
+                # tf.clip_by_norm(w, 3.0, axes=1) over all weight matrices, trainer_multi_tower.py:432-436
+                if isinstance(self.optimizer, FlatNadam):
+                    if not hasattr(self, "_weight_indices"):
+                        weights = {id(w) for w in self._weight_matrices()}
+                        self._weight_indices = [k for k, p in enumerate(self.parameters) if id(p) in weights]
+                    self.optimizer.clip_rows(self._weight_indices, 3.0)
+                    continue
+                with torch.no_grad():
                     for w in self._weight_matrices():
                         norms = w.norm(dim=1, keepdim=True).clamp_min(1e-30)
                         w.mul_(torch.clamp(3.0 / norms, max=1.0))

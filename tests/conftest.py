@@ -38,3 +38,19 @@ def oracle_mod():
     if not oracle.available("port"):
         oracle.build()
     return oracle
+
+
+@pytest.fixture(autouse=True)
+def _no_stale_device_status(request):
+    """After every GPU test the device status word must be clear: a kernel that reported a bad
+    index, a bad element or a timeout is pinned on the test that ran it, not on a later one.
+    Tests that provoke a report on purpose read (and thereby clear) it themselves."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from khan_b200 import ani_mod
+    status = ani_mod.device_status()
+    assert status == 0, f"{request.node.name} left device status {status}"

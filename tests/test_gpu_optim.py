@@ -71,3 +71,25 @@ def test_step_inside_a_cuda_graph_sees_later_learning_rates():
     d2 = float((before - p.detach()).mean())
     assert 0.08 < d2 / d1 < 0.12       # ten times smaller step after the rate change
     assert opt.steps_done() == 3       # the warm-up and two replays; the capture itself runs nothing
+
+
+def test_clip_rows_is_clip_by_norm_over_axis_one():
+    """FlatNadam.clip_rows against tf.clip_by_norm(w, 3.0, axes=1) written out in torch
+    (khan/training/trainer_multi_tower.py:432-436); biases and vectors in the buffer are left alone."""
+    import torch
+    from khan_b200.training.optim import FlatNadam
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    shapes = [(384, 128), (128,), (128, 64), (64,), (64, 1), (1,)]
+    params = [(torch.randn(s, device="cuda", generator=gen) * (0.5 if k % 2 == 0 else 5.0)).requires_grad_(True)
+              for k, s in enumerate(shapes)]
+    want = [p.detach().clone() for p in params]
+    for k in (0, 2, 4):
+        norms = want[k].norm(dim=1, keepdim=True).clamp_min(1e-30)
+        want[k] = want[k] * torch.clamp(3.0 / norms, max=1.0)
+    opt = FlatNadam(params)
+    opt.clip_rows([0, 2, 4], 3.0)
+    opt.clip_rows([0, 2, 4], 3.0)      # idempotent, and the row table is reused
+    for p, w in zip(params, want):
+        assert (p.detach() - w).abs().max().item() <= 1e-6 * max(1.0, w.abs().max().item())
+    assert float(params[0].detach().norm(dim=1).max()) <= 3.0 + 1e-5
+    assert float(params[0].detach().norm(dim=1).max()) > 2.9          # the constraint was active
