@@ -430,14 +430,45 @@ class TrainerMultiTower:
                 for f in np.split(feats[k], mos[k][1:]):
                     yield f
 
-    def coordinate_gradients(self, dataset, batch_size=1024):
+    def coordinate_gradients(self, dataset, batch_size=1024, use_evaluator=True):
         """Per-molecule ``(n, 3)`` gradients of the predicted energy
-        (``trainer_multi_tower.py:580-614``)."""
+        (``trainer_multi_tower.py:580-614``).  On one float32 tower with the fused networks the
+        batches go through the allocation-free evaluator (``khan_b200.inference.EnergyForces``: C-ABI
+        calls only, no host wait per batch); ``use_evaluator=False`` forces the autograd path."""
+        if (use_evaluator and self.num_towers == 1 and self.precision == torch.float32 and self.model.fused
+                and self.towers[0].type == "cuda" and dataset.num_mols() > 0):
+            yield from self._evaluator_gradients(dataset, batch_size)
+            return
         ops = [self.tower_coord_grads, self.tower_mos, self.tower_bids]
         for grads, mos, ids in self.feed_dataset(dataset, False, ops, batch_size):
             for k in np.argsort(np.array(ids)):
                 # one (n_atoms, 3) array per batch, cut once into per-molecule pieces
                 yield from np.split(np.stack(grads[k], axis=1), mos[k][1:])
+
+    def _evaluator_gradients(self, dataset, batch_size):
+        from ..inference import EnergyForces
+        from ..staged import StagedBatch
+        packed = PackedDataset.from_raw(dataset, np.float32)
+        cap_atoms, cap_mols = (max(v, 1) for v in packed.capacity(batch_size))
+        dev = self.towers[0]
+        cached = getattr(self, "_infer", None)
+        if cached is None or cached[0][0] < cap_atoms or cached[0][1] < cap_mols:
+            self._infer = cached = ((cap_atoms, cap_mols), StagedBatch(cap_atoms, cap_mols, device=dev),
+                                    EnergyForces(self.model, cap_atoms, cap_mols, device=dev))
+        _, sb, ev = cached
+        it = BatchFeeder(packed, batch_size, False, None, devices=self.towers, depth=2, hold=1)
+        done = []
+        try:
+            with torch.cuda.device(dev), torch.no_grad():
+                for fed in it:
+                    fed.wait()
+                    sb.adopt(fed)
+                    ev.run(sb)
+                    done.append((sb.grads[:, :fed.n_atoms].t().contiguous(), fed.offsets_host))   # (n_atoms, 3), on the device
+        finally:
+            it.close()
+        for g, offsets in done:      # the first .cpu() waits for the GPU once
+            yield from np.split(g.cpu().numpy(), offsets[1:])
 
     def eval_abs_rmse(self, dataset, batch_size=1024):
         """Absolute RMSE of the energies in kcal/mol (``trainer_multi_tower.py:560-578``)."""

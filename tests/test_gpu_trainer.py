@@ -166,7 +166,9 @@ def test_energy_forces_evaluator_matches_the_trainer():
     ds = RawDataset(mols)
     tr = TrainerMultiTower(None, [torch.device("cuda", 0)], layer_sizes=(128, 128, 64, 1), seed=5)
     want_e = np.array(tr.predict(ds, batch_size=64))
-    want_g = np.concatenate(list(tr.coordinate_gradients(ds, batch_size=64)), axis=0)      # (n_atoms, 3)
+    want_g = np.concatenate(list(tr.coordinate_gradients(ds, batch_size=64, use_evaluator=False)), axis=0)   # autograd path, (n_atoms, 3)
+    fast_g = np.concatenate(list(tr.coordinate_gradients(ds, batch_size=16)), axis=0)                         # evaluator path, several batches
+    assert np.abs(fast_g - want_g).max() < 1e-4 * np.abs(want_g).max()
     sb = StagedBatch(b.n_atoms, b.n_mols)
     sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
     ev = EnergyForces(tr.model, b.n_atoms, b.n_mols)
