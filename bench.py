@@ -659,7 +659,7 @@ def main():
     # stream, join), plus one single-step graph per batch for the remainder K mod NB.
     n_streams = max(1, min(args.streams, nb))
     side = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
-    graphs = mega = None
+    graphs = mega = tail = None
     launch_mode = "eager"
     if not args.no_graph:
         try:
@@ -669,21 +669,28 @@ def main():
                 with torch.cuda.graph(g):
                     sb.run_step(stream_ptr())
                 graphs.append(g)
-            mega = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(mega):
-                cap = torch.cuda.current_stream()
-                for st in side:
-                    st.wait_stream(cap)
-                for b, sb in enumerate(staged):
-                    st = side[b % n_streams]
-                    with torch.cuda.stream(st):
-                        sb.run_step(ctypes.c_void_p(st.cuda_stream))
-                for st in side:
-                    cap.wait_stream(st)
+            def capture_overlapped(batches_to_run):
+                """One graph that runs the given staged batches on the side streams, round-robin."""
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    cap = torch.cuda.current_stream()
+                    for st in side:
+                        st.wait_stream(cap)
+                    for b, sb in enumerate(batches_to_run):
+                        st = side[b % n_streams]
+                        with torch.cuda.stream(st):
+                            sb.run_step(ctypes.c_void_p(st.cuda_stream))
+                    for st in side:
+                        cap.wait_stream(st)
+                return g
+
+            mega = capture_overlapped(staged)
+            # the K steps of the timed region are whole passes over the pool plus this remainder
+            tail = capture_overlapped(staged[:args.steps % nb]) if args.steps % nb else None
             launch_mode = "cuda_graph"
         except Exception as exc:
             print(f"[bench] CUDA graph capture failed ({exc!r}); launching eagerly", file=sys.stderr)
-            graphs = mega = None
+            graphs = mega = tail = None
             torch.cuda.synchronize()
 
     def run_steps(n_steps):
@@ -693,8 +700,12 @@ def main():
             while n_steps - done >= nb:
                 mega.replay()
                 done += nb
-            for k in range(n_steps - done):
-                graphs[k].replay()
+            rest = n_steps - done
+            if rest and tail is not None and rest == args.steps % nb:
+                tail.replay()
+            else:
+                for k in range(rest):
+                    graphs[k].replay()
         else:
             main = torch.cuda.current_stream()
             for st in side:
