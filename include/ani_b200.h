@@ -30,6 +30,8 @@
 #ifndef ANI_B200_H_
 #define ANI_B200_H_
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -207,10 +209,30 @@ typedef struct ani_mlp_args {
     float* dact1[4];      /* optional: d act / d x at the same places (the backward pass needs them) */
     float* dact2[4];
     float* dact3[4];
+    const void* packed[4];  /* optional: the same weights packed by ani_mlp_pack_weights_f32 */
 } ani_mlp_args;
 
 int ani_mlp_forward_f32(const ani_mlp_args* args_host, const int* acs_host, int activation,
                         int split_precision, void* stream);
+
+/*
+ * Optional pre-packing of the weights, no counterpart in the reference.  Writes, per element,
+ * ani_mlp_packed_bytes() bytes (1.19 MiB) that hold W1, W2, W3 cut into the 32-column chunks of
+ * both products that read them (forward: W^T; backward: W), split into tf32 high and low parts and
+ * laid out as the tensor cores read them.  A forward / backward call that is given `packed`
+ * fetches each chunk with one bulk asynchronous copy (TMA) instead of staging it with all threads;
+ * results are identical.  The packed copy must be refreshed after every change of the weights;
+ * elements whose packed[t] is NULL are skipped.  16-byte alignment required.
+ */
+typedef struct ani_mlp_pack_args {
+    const float* w1[4];   /* [384][128] */
+    const float* w2[4];   /* [128][128] */
+    const float* w3[4];   /* [128][64] */
+    void* packed[4];      /* ani_mlp_packed_bytes() each */
+} ani_mlp_pack_args;
+
+size_t ani_mlp_packed_bytes(void);
+int ani_mlp_pack_weights_f32(const ani_mlp_pack_args* args_host, void* stream);
 
 /*
  * Backward pass of the same four networks along the activations (float32), one launch:
@@ -237,6 +259,7 @@ typedef struct ani_mlp_backward_args {
     float* dz2[4];                /* [acs[t]][128] */
     float* dz3[4];                /* [acs[t]][64] */
     float* grad_features[4];      /* [acs[t]][384], may be NULL */
+    const void* packed[4];        /* optional: the same weights packed by ani_mlp_pack_weights_f32 */
 } ani_mlp_backward_args;
 
 int ani_mlp_backward_f32(const ani_mlp_backward_args* args_host, const int* acs_host,

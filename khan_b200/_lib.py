@@ -33,17 +33,22 @@ _vp = ctypes.c_void_p
 _i = ctypes.c_int
 
 class MlpArgs(ctypes.Structure):
-    """``ani_mlp_args`` of include/ani_b200.h: sixteen arrays of four device pointers."""
+    """``ani_mlp_args`` of include/ani_b200.h: seventeen arrays of four device pointers."""
     _fields_ = [(name, ctypes.c_void_p * 4) for name in (
         "features", "w1", "b1", "w2", "b2", "w3", "b3", "w4", "b4", "energy", "act1", "act2", "act3",
-        "dact1", "dact2", "dact3")]
+        "dact1", "dact2", "dact3", "packed")]
+
+
+class MlpPackArgs(ctypes.Structure):
+    """``ani_mlp_pack_args`` of include/ani_b200.h."""
+    _fields_ = [(name, ctypes.c_void_p * 4) for name in ("w1", "w2", "w3", "packed")]
 
 
 class MlpBackwardArgs(ctypes.Structure):
     """``ani_mlp_backward_args`` of include/ani_b200.h."""
     _fields_ = [(name, ctypes.c_void_p * 4) for name in (
         "grad_energy", "w1", "w2", "w3", "w4", "dact1", "dact2", "dact3", "dz1", "dz2", "dz3",
-        "grad_features")]
+        "grad_features", "packed")]
 
 
 class MlpWeightGradArgs(ctypes.Structure):
@@ -69,6 +74,8 @@ SIGNATURES = {
     "ani_featurize_grad_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
     "ani_featurize_grad_inverse_f32": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
     "ani_featurize_grad_inverse_f64": (_i, [_vp] * 6 + [_i] + [_vp] * 8 + [c_int_p, _vp]),
+    "ani_mlp_packed_bytes": (ctypes.c_size_t, []),
+    "ani_mlp_pack_weights_f32": (_i, [ctypes.POINTER(MlpPackArgs), _vp]),
     "ani_mlp_backward_f32": (_i, [ctypes.POINTER(MlpBackwardArgs), c_int_p, _i, _vp]),
     "ani_mlp_weight_grad_f32": (_i, [ctypes.POINTER(MlpWeightGradArgs), c_int_p, _i, _vp]),
     "ani_molecule_energy_f32": (_i, [_vp] * 4 + [_i, _i, _vp, ctypes.c_float, _vp, _vp, _vp, _vp]),

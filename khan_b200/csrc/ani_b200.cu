@@ -637,6 +637,8 @@ int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activati
         p.energy[t] = a->energy[t];
         p.act1[t] = a->act1[t]; p.act2[t] = a->act2[t]; p.act3[t] = a->act3[t];
         p.dact1[t] = a->dact1[t]; p.dact2[t] = a->dact2[t]; p.dact3[t] = a->dact3[t];
+        p.packed[t] = (const unsigned char*)a->packed[t];
+        if (reinterpret_cast<uintptr_t>(a->packed[t]) & 15) return ANI_ERR_MISALIGNED;
     }
     p.tile_start[kTypes] = tiles;
     cudaStream_t st = (cudaStream_t)stream;
@@ -647,6 +649,27 @@ int ani_mlp_forward_f32(const ani_mlp_args* a, const int* acs_host, int activati
         case kActNormal: return mlp_launch_act<kActNormal>(p, tiles, split, st);
         default: return mlp_launch_act<kActSoftplus>(p, tiles, split, st);
     }
+}
+
+size_t ani_mlp_packed_bytes(void) { return (size_t)kPackChunks * kPackedChunkBytes; }
+
+int ani_mlp_pack_weights_f32(const ani_mlp_pack_args* a, void* stream)
+{
+    if (!a) return ANI_ERR_NULL_POINTER;
+    MlpPackParams p;
+    bool any = false;
+    for (int t = 0; t < kTypes; t++) {
+        p.w1[t] = a->w1[t]; p.w2[t] = a->w2[t]; p.w3[t] = a->w3[t];
+        p.packed[t] = (unsigned char*)a->packed[t];
+        if (!a->packed[t]) continue;
+        if (!a->w1[t] || !a->w2[t] || !a->w3[t]) return ANI_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(a->packed[t]) & 15) return ANI_ERR_MISALIGNED;
+        any = true;
+    }
+    if (!any) return ANI_OK;
+    mlp_pack_kernel<<<dim3(kPackChunks, kTypes), kMlpThreads, 0, (cudaStream_t)stream>>>(p);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
 }
 
 int ani_mlp_backward_f32(const ani_mlp_backward_args* a, const int* acs_host, int split_precision,
@@ -674,6 +697,8 @@ int ani_mlp_backward_f32(const ani_mlp_backward_args* a, const int* acs_host, in
         p.dact1[t] = a->dact1[t]; p.dact2[t] = a->dact2[t]; p.dact3[t] = a->dact3[t];
         p.dz1[t] = a->dz1[t]; p.dz2[t] = a->dz2[t]; p.dz3[t] = a->dz3[t];
         p.grad_feat[t] = a->grad_features[t];
+        p.packed[t] = (const unsigned char*)a->packed[t];
+        if (reinterpret_cast<uintptr_t>(a->packed[t]) & 15) return ANI_ERR_MISALIGNED;
     }
     p.tile_start[kTypes] = tiles;
     cudaStream_t st = (cudaStream_t)stream;

@@ -56,6 +56,7 @@ struct MlpParams {
     float* dact1[kTypes];        // optional [count][128]: derivative of the activation at the same place
     float* dact2[kTypes];        // optional [count][128]
     float* dact3[kTypes];        // optional [count][64]
+    const unsigned char* packed[kTypes];   // optional: the weights pre-packed by mlp_pack_kernel
 };
 
 struct MlpShared {
@@ -99,6 +100,21 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
         if (done) return true;
     }
     return false;
+}
+// Adds `bytes` to the transaction count that the current phase of the barrier waits for.
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bulk asynchronous copy (TMA, untiled) global -> shared memory; completion is reported to the
+// barrier as `bytes` of its transaction count.  Addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_copy_to_shared(void* dst_smem, const void* src_global, unsigned bytes,
+                                                    unsigned long long* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_global), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
 {

@@ -36,6 +36,7 @@ struct MlpBackwardParams {
     float* dz2[kTypes];          // [count][128]
     float* dz3[kTypes];          // [count][64]
     float* grad_feat[kTypes];    // optional [count][384]
+    const unsigned char* packed[kTypes];   // optional: the weights pre-packed by mlp_pack_kernel
 };
 
 template <bool SPLIT>
@@ -115,7 +116,12 @@ __global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_backward_kernel(const M
         for (int s = 0; s < 2 && ok; s++) {
             // B[n = in][k = out] = W[n][k]: the weights as stored
             DirectGlobal<SPLIT> b_w{step_w[s], (size_t)step_k[s], 128, 128, 0};
-            pipe_produce<SPLIT, true>(sh, step_k[s] / kPipeK, ps, b_w, a_sh, b_w);
+            if (p.packed[e]) {
+                PackedB b_packed{p.packed[e] + (size_t)(s == 0 ? kPackBwdS0 : kPackBwdS1) * kPackedChunkBytes};
+                pipe_produce<SPLIT, true>(sh, step_k[s] / kPipeK, ps, b_w, a_sh, b_packed);
+            } else {
+                pipe_produce<SPLIT, true>(sh, step_k[s] / kPipeK, ps, b_w, a_sh, b_w);
+            }
             ok = pipe_drain(sh, ps);
             if (!ok) break;
             {
@@ -138,7 +144,12 @@ __global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_backward_kernel(const M
 #pragma unroll 1
             for (int n0 = 0; n0 < kMlpIn && ok; n0 += 128) {
                 DirectGlobal<SPLIT> b_w{p.w1[e] + (size_t)n0 * kMlpH1, (size_t)kMlpH1, 128, 128, 0};
-                pipe_produce<SPLIT, true>(sh, kMlpH1 / kPipeK, ps, b_w, a_sh, b_w);
+                if (p.packed[e]) {
+                    PackedB b_packed{p.packed[e] + (size_t)(kPackBwdF + 4 * (n0 / 128)) * kPackedChunkBytes};
+                    pipe_produce<SPLIT, true>(sh, kMlpH1 / kPipeK, ps, b_w, a_sh, b_packed);
+                } else {
+                    pipe_produce<SPLIT, true>(sh, kMlpH1 / kPipeK, ps, b_w, a_sh, b_w);
+                }
                 ok = pipe_drain(sh, ps);
                 if (!ok) break;
                 float v[32];

@@ -70,8 +70,16 @@ __global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_forward_kernel(const Ml
             DirectGlobal<SPLIT> a_feat{p.feat[e] + (size_t)row0 * kMlpIn, (size_t)kMlpIn, kMlpTile, n_rows, 0};
             // B[n = out][k = in] = W[k][n]: the weights are read as stored ([in][out]) and transposed
             Transposed<SPLIT> b_w{layer_w[layer], (size_t)N, 0, N, 0, K, make_float4(0.f, 0.f, 0.f, 0.f)};
-            if (layer == 0) pipe_produce<SPLIT, false>(sh, K / kPipeK, ps, a_feat, a_sh, b_w);
-            else pipe_produce<SPLIT, true>(sh, K / kPipeK, ps, a_feat, a_sh, b_w);
+            if (p.packed[e]) {      // pre-packed weights: one bulk copy per chunk instead of staging
+                const int first_chunk = layer == 0 ? kPackFwdL1 : (layer == 1 ? kPackFwdL2 : kPackFwdL3);
+                PackedB b_packed{p.packed[e] + (size_t)first_chunk * kPackedChunkBytes};
+                if (layer == 0) pipe_produce<SPLIT, false>(sh, K / kPipeK, ps, a_feat, a_sh, b_packed);
+                else pipe_produce<SPLIT, true>(sh, K / kPipeK, ps, a_feat, a_sh, b_packed);
+            } else if (layer == 0) {
+                pipe_produce<SPLIT, false>(sh, K / kPipeK, ps, a_feat, a_sh, b_w);
+            } else {
+                pipe_produce<SPLIT, true>(sh, K / kPipeK, ps, a_feat, a_sh, b_w);
+            }
             ANI_PHASE(0);
             ok = pipe_drain(sh, ps);
             ANI_PHASE(2);

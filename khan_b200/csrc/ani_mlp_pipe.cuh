@@ -83,6 +83,7 @@ struct PipeRegs {
 // Rows [0, rows) of a row-major global matrix (row stride ld); rows >= rows_valid read as zero;
 // chunk c covers columns k0 + 32 c .. + 31.
 template <bool SPLIT> struct DirectGlobal {
+    static constexpr bool kBulk = false;
     const float* base;
     size_t ld;
     int rows, rows_valid, k0;
@@ -139,6 +140,7 @@ __device__ __forceinline__ int transposed_quad(int rows)
 // rotate which of their four values they store -- times 4 different k.
 // colsum accumulates this thread's column sums (four columns) over everything it staged.
 template <bool SPLIT> struct Transposed {
+    static constexpr bool kBulk = false;
     const float* base;
     size_t ld;
     int col0, rows;
@@ -182,6 +184,23 @@ template <bool SPLIT> struct Transposed {
     }
 };
 
+// A B operand that was packed beforehand (mlp_pack_kernel): chunk c of the product is 32 KiB at
+// base + c * 32 KiB, already split into high and low parts and laid out exactly as a stage wants
+// it, so one thread moves it with ONE bulk asynchronous copy (TMA) that reports to the stage's
+// "full" barrier; the other 511 producers spend nothing on B.
+constexpr unsigned kPackedChunkBytes = 2 * kPipeOperandBytes;
+struct PackedB {
+    static constexpr bool kBulk = true;
+    const unsigned char* base;
+    __device__ __forceinline__ void load(int, PipeRegs&) const {}
+    __device__ __forceinline__ void store(const PipeRegs&, unsigned char*, unsigned char*) const {}
+};
+
+// Packed layout of one element's weights: chunk indices of every product.
+constexpr int kPackFwdL1 = 0, kPackFwdL2 = 12, kPackFwdL3 = 16;          // forward: W1 (12 chunks), W2 (4), W3 (4)
+constexpr int kPackBwdS0 = 20, kPackBwdS1 = 22, kPackBwdF = 26;          // backward: W3 (2), W2 (4), W1 blocks (3 x 4)
+constexpr int kPackChunks = 38;
+
 struct PipeState {
     unsigned chunks = 0;          // chunks issued so far in this kernel (stage = chunks & 1)
     unsigned parity0 = 0, parity1 = 0;
@@ -218,9 +237,17 @@ __device__ __forceinline__ void pipe_produce(MlpShared& sh, int nchunks, PipeSta
         const int s = (int)(ps.chunks & 1u);
         unsigned char* stage = sh.a_hi + s * kPipeStageBytes;
         pipe_wait_stage(sh, ps, s);
+        if (BSrc::kBulk) {
+            if (threadIdx.x == 0) {      // registered before this thread's own arrival below
+                mbar_expect_tx(&sh.full_bar[s], kPackedChunkBytes);
+                bulk_copy_to_shared(stage + 2 * kPipeOperandBytes, b_src.base + (size_t)c * kPackedChunkBytes,
+                                    kPackedChunkBytes, &sh.full_bar[s]);
+            }
+        } else {
+            b_src.store(rb, stage + 2 * kPipeOperandBytes, stage + 3 * kPipeOperandBytes);
+        }
         if (ASHARED) a_sh.store_chunk(c, stage, stage + kPipeOperandBytes);
         else a_src.store(ra, stage, stage + kPipeOperandBytes);
-        b_src.store(rb, stage + 2 * kPipeOperandBytes, stage + 3 * kPipeOperandBytes);
         if (c + 1 < nchunks) {           // the next chunk's loads fly while this one is consumed
             if (!ASHARED) a_src.load(c + 1, ra);
             b_src.load(c + 1, rb);
@@ -229,6 +256,44 @@ __device__ __forceinline__ void pipe_produce(MlpShared& sh, int nchunks, PipeSta
         mbar_arrive(&sh.full_bar[s]);
         if (s) ps.pending1 = true; else ps.pending0 = true;
         ps.chunks++;
+    }
+}
+
+// Packs the weights of the four elements into the stage layout (both products that read them:
+// forward B[n = out][k = in] = W[k][n], backward B[n = in][k = out] = W[n][k]), high and low tf32
+// parts.  grid = (kPackChunks, 4 elements); run once per weight update.
+struct MlpPackParams {
+    const float* w1[kTypes];   // [384][128]
+    const float* w2[kTypes];   // [128][128]
+    const float* w3[kTypes];   // [128][64]
+    unsigned char* packed[kTypes];
+};
+__global__ void __launch_bounds__(kMlpThreads) mlp_pack_kernel(const MlpPackParams p)
+{
+    const int e = blockIdx.y, chunk = blockIdx.x;
+    if (!p.packed[e]) return;
+    const float* w;
+    int ld, k0, n0, rows;
+    bool transposed;   // true: operand (n, k) = W[k0 + k][n0 + n];  false: W[n0 + n][k0 + k]
+    if (chunk < kPackFwdL2)      { w = p.w1[e]; ld = 128; transposed = true;  k0 = 32 * chunk;                n0 = 0; rows = 128; }
+    else if (chunk < kPackFwdL3) { w = p.w2[e]; ld = 128; transposed = true;  k0 = 32 * (chunk - kPackFwdL2); n0 = 0; rows = 128; }
+    else if (chunk < kPackBwdS0) { w = p.w3[e]; ld = 64;  transposed = true;  k0 = 32 * (chunk - kPackFwdL3); n0 = 0; rows = 64; }
+    else if (chunk < kPackBwdS1) { w = p.w3[e]; ld = 64;  transposed = false; k0 = 32 * (chunk - kPackBwdS0); n0 = 0; rows = 128; }
+    else if (chunk < kPackBwdF)  { w = p.w2[e]; ld = 128; transposed = false; k0 = 32 * (chunk - kPackBwdS1); n0 = 0; rows = 128; }
+    else {
+        const int c = chunk - kPackBwdF;
+        w = p.w1[e]; ld = 128; transposed = false; k0 = 32 * (c & 3); n0 = 128 * (c >> 2); rows = 128;
+    }
+    unsigned char* hi = p.packed[e] + (size_t)chunk * kPackedChunkBytes;
+    unsigned char* lo = hi + kPipeOperandBytes;
+    for (int idx = threadIdx.x; idx < kMlpTile * kPipeK; idx += kMlpThreads) {
+        const int n = idx / kPipeK, k = idx % kPipeK;
+        float v = 0.0f;
+        if (n < rows) v = transposed ? w[(size_t)(k0 + k) * ld + n0 + n] : w[(size_t)(n0 + n) * ld + k0 + k];
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        const int off = pipe_offset(n, k);
+        *reinterpret_cast<float*>(hi + off) = h;
+        *reinterpret_cast<float*>(lo + off) = v - h;
     }
 }
 

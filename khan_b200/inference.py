@@ -60,6 +60,7 @@ class EnergyForces:
         sb.run_sort(stream)
         sb.run_featurize(stream)
         fwd, bwd = _lib.MlpArgs(), _lib.MlpBackwardArgs()
+        packed = self.model.pack_weights(stream)
         for t in range(4):
             if acs[t] == 0:
                 continue
@@ -69,6 +70,8 @@ class EnergyForces:
             fwd.w1[t], fwd.w2[t], fwd.w3[t], fwd.w4[t] = _ptr(w1), _ptr(w2), _ptr(w3), _ptr(w4)
             fwd.b1[t], fwd.b2[t], fwd.b3[t], fwd.b4[t] = _ptr(b1), _ptr(b2), _ptr(b3), _ptr(b4)
             fwd.energy[t] = _ptr(self.energy_sorted, s)
+            if packed is not None:
+                fwd.packed[t] = bwd.packed[t] = _ptr(packed[t])
             fwd.act1[t], fwd.act2[t], fwd.act3[t] = (_ptr(a, s * a.shape[1]) for a in self.acts)
             fwd.dact1[t], fwd.dact2[t], fwd.dact3[t] = (_ptr(d, s * d.shape[1]) for d in self.dacts)
             bwd.grad_energy[t] = _ptr(self.ones, s)
@@ -85,4 +88,4 @@ class EnergyForces:
                    "ani_mlp_backward_f32")
         sb.run_featurize_grad(stream)
 
-    KERNELS_PER_PASS = 7   # sort, featurize, mlp forward, molecule sums, mlp backward, zero fill, featurize_grad
+    KERNELS_PER_PASS = 8   # weight packing, sort, featurize, mlp forward, molecule sums, mlp backward, zero fill, featurize_grad

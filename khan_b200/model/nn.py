@@ -92,7 +92,8 @@ class _FusedMlp(torch.autograd.Function):
     dense differentiable torch ops instead."""
 
     @staticmethod
-    def forward(ctx, features, acs, act_id, split, act_fn, *params):
+    def forward(ctx, features, acs, act_id, split, act_and_packed, *params):
+        act_fn, packed = act_and_packed
         # params: for each of the 4 elements W1,b1,W2,b2,W3,b3,W4,b4 (reference shapes, W = (in, out))
         n = features.shape[0]
         dev = features.device
@@ -120,6 +121,7 @@ class _FusedMlp(torch.autograd.Function):
             args.energy[t] = ptr(energy, s)
             args.act1[t], args.act2[t], args.act3[t] = (ptr(a, s * a.shape[1]) for a in acts)
             args.dact1[t], args.dact2[t], args.dact3[t] = (ptr(d, s * d.shape[1]) for d in dacts)
+            args.packed[t] = ptr(packed[t]) if packed is not None else None
         acs_arr = np.ascontiguousarray(np.asarray(acs, dtype=np.int32))
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         with torch.cuda.device(dev):
@@ -128,6 +130,7 @@ class _FusedMlp(torch.autograd.Function):
                        "ani_mlp_forward_f32")
         ctx.save_for_backward(features, *acts, *dacts, *params)
         ctx.acs, ctx.act_fn, ctx.split, ctx.accumulate = acs_arr, act_fn, bool(int(split) & 1), bool(int(split) & 2)
+        ctx.packed = packed      # the weights do not change between this pass and its backward pass
         return energy
 
     @staticmethod
@@ -171,6 +174,7 @@ class _FusedMlp(torch.autograd.Function):
             args.dact1[t], args.dact2[t], args.dact3[t] = ptr(d1, s * 128), ptr(d2, s * 128), ptr(d3, s * 64)
             args.dz1[t], args.dz2[t], args.dz3[t] = ptr(dz1, s * 128), ptr(dz2, s * 128), ptr(dz3, s * 64)
             args.grad_features[t] = ptr(grad_feat, s * 384) if grad_feat is not None else None
+            args.packed[t] = ptr(ctx.packed[t]) if ctx.packed is not None else None
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().ani_mlp_backward_f32(ctypes.byref(args), acs.ctypes.data_as(_lib.c_int_p),
@@ -260,6 +264,27 @@ class MoleculeNN:
             out.update(a.named_parameters())
         return out
 
+    def pack_weights(self, stream=None):
+        """Refreshes the pre-packed copy of W1, W2, W3 of the four networks (``ani_mlp_pack_weights_f32``:
+        one small launch) and returns it, ``[4, ani_mlp_packed_bytes()]`` bytes on the parameters' device.
+        The tensor-core kernels that are given it fetch their weight chunks with one bulk copy each;
+        it has to be refreshed whenever the weights changed, so the callers do it once per pass."""
+        dev = self.anns[0].Ws[0].device
+        if getattr(self, "_packed", None) is None or self._packed.device != dev:
+            self._packed = torch.empty((4, int(_lib.lib().ani_mlp_packed_bytes())), dtype=torch.uint8, device=dev)
+        args = _lib.MlpPackArgs()
+        for t, ann in enumerate(self.anns):
+            w1, w2, w3 = (w.detach() for w in ann.Ws[:3])
+            if not (w1.is_contiguous() and w2.is_contiguous() and w3.is_contiguous()):
+                return None
+            args.w1[t], args.w2[t], args.w3[t] = w1.data_ptr(), w2.data_ptr(), w3.data_ptr()
+            args.packed[t] = self._packed[t].data_ptr()
+        if stream is None:
+            stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().ani_mlp_pack_weights_f32(ctypes.byref(args), stream), "ani_mlp_pack_weights_f32")
+        return self._packed
+
     @property
     def fused(self) -> bool:
         return (self.precision == torch.float32 and self.layer_sizes == FUSED_LAYERS
@@ -275,8 +300,9 @@ class MoleculeNN:
                 for w, b in zip(a.Ws, a.bs):
                     params.extend([w, b])
             flags = (1 if self.split_precision else 0) | (2 if self.accumulate_into_grad else 0)
+            packed = self.pack_weights() if features.device == self.anns[0].Ws[0].device else None
             return _FusedMlp.apply(features, acs, activations.KERNEL_ID[self.activation_fn],
-                                   flags, self.activation_fn, *params)
+                                   flags, (self.activation_fn, packed), *params)
         starts = np.concatenate([[0], np.cumsum(acs)])
         parts = [ann.atom_energies(features[int(starts[t]):int(starts[t + 1])])
                  for t, ann in enumerate(self.anns)]

@@ -66,6 +66,7 @@ class FusedTrainStep:
         sb.run_sort(stream)
         sb.run_featurize(stream)
         fwd, bwd, wg = _lib.MlpArgs(), _lib.MlpBackwardArgs(), _lib.MlpWeightGradArgs()
+        packed = self.model.pack_weights(stream)
         for t in range(4):
             if acs[t] == 0:
                 continue
@@ -79,6 +80,8 @@ class FusedTrainStep:
             fwd.w4[t] = bwd.w4[t] = _ptr(w4.data)
             fwd.b1[t], fwd.b2[t], fwd.b3[t], fwd.b4[t] = _ptr(b1.data), _ptr(b2.data), _ptr(b3.data), _ptr(b4.data)
             fwd.energy[t] = _ptr(self.energy_sorted, s)
+            if packed is not None:
+                fwd.packed[t] = bwd.packed[t] = _ptr(packed[t])
             fwd.act1[t], fwd.act2[t], fwd.act3[t] = (_ptr(a, s * a.shape[1]) for a in self.acts)
             wg.act1[t], wg.act2[t], wg.act3[t] = fwd.act1[t], fwd.act2[t], fwd.act3[t]
             fwd.dact1[t], fwd.dact2[t], fwd.dact3[t] = (_ptr(d, s * d.shape[1]) for d in self.dacts)
@@ -114,4 +117,4 @@ class FusedTrainStep:
         self.coordinate_gradient(sb)
         self.optimizer.step()
 
-    KERNELS = 11   # sort, featurize, mlp fwd, molecule energy, mlp bwd, memset, wgrad, zero3, featurize_grad, sumsq, nadam
+    KERNELS = 12   # weight packing, sort, featurize, mlp fwd, molecule energy, mlp bwd, memset, wgrad, zero3, featurize_grad, sumsq, nadam

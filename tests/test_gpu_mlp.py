@@ -145,3 +145,31 @@ def test_weight_gradients_accumulate_into_existing_buffers():
     got = torch.autograd.grad((model.atom_energies_sorted(feats, acs) * w).sum(), params)
     for g, f in zip(got, first):
         assert (g - f).abs().max().item() <= 1e-5 * f.abs().max().item()
+
+
+def test_packed_and_unpacked_weight_paths_agree(monkeypatch):
+    """The kernels fetch pre-packed weight chunks with bulk copies by default; without a packed
+    copy they stage the weights themselves.  Same operands, same MMAs: identical energies, and
+    gradients equal up to the order of the floating-point reductions."""
+    import torch
+    from khan_b200.model import activations, nn
+    acs = np.array([300, 129, 0, 7])
+    n = int(acs.sum())
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    base = torch.rand((n, 384), device="cuda", generator=gen)
+    w = torch.randn(n, device="cuda", generator=gen)
+    results = []
+    for packed in (True, False):
+        model = nn.MoleculeNN(activation_fn=activations.gaussian, seed=13, init="he")
+        if not packed:
+            monkeypatch.setattr(nn.MoleculeNN, "pack_weights", lambda self, stream=None: None)
+        feats = base.clone().requires_grad_(True)
+        e = model.atom_energies_sorted(feats, acs)
+        (e * w).sum().backward()
+        results.append((e.detach().clone(), feats.grad.clone(),
+                        [p.grad.clone() for p in _interleaved(model) if p.grad is not None]))
+    (e0, f0, g0), (e1, f1, g1) = results
+    assert torch.equal(e0, e1)
+    assert torch.equal(f0, f1)
+    for a, b in zip(g0, g1):
+        assert (a - b).abs().max().item() <= 1e-5 * b.abs().max().item()
