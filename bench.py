@@ -351,8 +351,16 @@ def run_fused_train_workload(args):
         for k in range(max(3, args.warmup)):
             step.step(staged[k % nb], labels[k % nb])
     torch.cuda.synchronize()
+    class _Eager:      # --no-graph: the same calls issued directly (what ncu sees kernel by kernel)
+        def __init__(self, fn):
+            self.replay = fn
+
     fb_graphs, cg_graphs = [], []
     for sb, y in zip(staged, labels):
+        if args.no_graph:
+            fb_graphs.append(_Eager(lambda sb=sb, y=y: step.forward_backward(sb, y)))
+            cg_graphs.append(_Eager(lambda sb=sb: step.coordinate_gradient(sb)))
+            continue
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             step.forward_backward(sb, y)
@@ -361,9 +369,12 @@ def run_fused_train_workload(args):
         with torch.cuda.graph(g):
             step.coordinate_gradient(sb)
         cg_graphs.append(g)
-    up_graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(up_graph):
-        opt.step()
+    if args.no_graph:
+        up_graph = _Eager(opt.step)
+    else:
+        up_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(up_graph):
+            opt.step()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -402,8 +413,9 @@ def run_fused_train_workload(args):
             "config": {"workload": "config3: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian, He init) + MSE "
                                    "+ backward into weights and coordinates + NCCL all-reduce + Nadam",
                        "molecules_per_step_per_gpu": args.mols, "path": "fused (C ABI only, no autograd)",
-                       "launch": "cuda_graph (forward+backward, coordinate gradient, update; all-reduce eager, "
-                                 "overlapping the coordinate gradient)"}}), flush=True)
+                       "launch": ("eager" if args.no_graph else
+                                  "cuda_graph (forward+backward, coordinate gradient, update; all-reduce eager, "
+                                  "overlapping the coordinate gradient)")}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
