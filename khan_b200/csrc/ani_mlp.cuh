@@ -254,20 +254,4 @@ __device__ __forceinline__ void warp_tile_from_global(float* scratch, float* v, 
     __syncwarp();
 }
 
-// 32 consecutive floats of one row, as eight 16-byte accesses.
-__device__ __forceinline__ void store_row32(float* dst, const float* v)
-{
-#pragma unroll
-    for (int i = 0; i < 32; i += 4)
-        *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-}
-__device__ __forceinline__ void load_row32(const float* src, float* v)
-{
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-        const float4 q = *reinterpret_cast<const float4*>(src + i);
-        v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
-    }
-}
-
 }  // namespace ani
