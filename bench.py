@@ -321,7 +321,7 @@ def run_fused_train_workload(args):
     from khan_b200.model import activations
     from khan_b200.model.nn import MoleculeNN
     from khan_b200.staged import HostBatch, StagedBatch
-    from khan_b200.training.fused_step import FusedTrainStep
+    from khan_b200.training.fused_step import FusedTrainStep, StepPipeline
     from khan_b200.training.optim import FlatNadam
     from khan_b200.training.trainer_multi_tower import average_gradients
 
@@ -351,48 +351,68 @@ def run_fused_train_workload(args):
         for k in range(max(3, args.warmup)):
             step.step(staged[k % nb], labels[k % nb])
     torch.cuda.synchronize()
-    class _Eager:      # --no-graph: the same calls issued directly (what ncu sees kernel by kernel)
-        def __init__(self, fn):
-            self.replay = fn
-
-    fb_graphs, cg_graphs = [], []
-    for sb, y in zip(staged, labels):
-        if args.no_graph:
-            fb_graphs.append(_Eager(lambda sb=sb, y=y: step.forward_backward(sb, y)))
-            cg_graphs.append(_Eager(lambda sb=sb: step.coordinate_gradient(sb)))
-            continue
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            step.forward_backward(sb, y)
-        fb_graphs.append(g)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            step.coordinate_gradient(sb)
-        cg_graphs.append(g)
-    if args.no_graph:
-        up_graph = _Eager(opt.step)
-    else:
-        up_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(up_graph):
-            opt.step()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
+    pipelined = args.train_path == "fused" and nb >= 2
     main = torch.cuda.current_stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for k in range(args.steps):
-        fb_graphs[k % nb].replay()
-        if world > 1:      # coordinate gradients on the second stream, under the all-reduce
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                cg_graphs[k % nb].replay()
-            average_gradients(params, opt.flat_grads)
-            main.wait_stream(side)
+    if pipelined:
+        # next batch's sort + featurize and this batch's coordinate gradient beside the network kernels
+        pipe = StepPipeline(step, staged, labels, allreduce=world > 1, graphs=not args.no_graph)
+        pipe.prime()
+        for k in range(nb):
+            pipe.run(k)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for k in range(args.steps):
+            pipe.run(k)
+        e1.record()
+    else:
+        class _Eager:      # --no-graph: the same calls issued directly (what ncu sees kernel by kernel)
+            def __init__(self, fn):
+                self.replay = fn
+
+        fb_graphs, cg_graphs = [], []
+        for sb, y in zip(staged, labels):
+            if args.no_graph:
+                fb_graphs.append(_Eager(lambda sb=sb, y=y: step.forward_backward(sb, y)))
+                cg_graphs.append(_Eager(lambda sb=sb: step.coordinate_gradient(sb)))
+                continue
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step.forward_backward(sb, y)
+            fb_graphs.append(g)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step.coordinate_gradient(sb)
+            cg_graphs.append(g)
+        if args.no_graph:
+            up_graph = _Eager(opt.step)
         else:
-            cg_graphs[k % nb].replay()
-        up_graph.replay()
-    e1.record()
+            up_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(up_graph):
+                opt.step()
+        def serial_step(k):
+            fb_graphs[k % nb].replay()
+            if world > 1:      # coordinate gradients on the second stream, under the all-reduce
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    cg_graphs[k % nb].replay()
+                average_gradients(params, opt.flat_grads)
+                main.wait_stream(side)
+            else:
+                cg_graphs[k % nb].replay()
+            up_graph.replay()
+
+        for k in range(nb):
+            serial_step(k)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for k in range(args.steps):
+            serial_step(k)
+        e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     atoms = float(sum(batches[k % nb].n_atoms for k in range(args.steps)))
@@ -413,9 +433,13 @@ def run_fused_train_workload(args):
             "config": {"workload": "config3: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian, He init) + MSE "
                                    "+ backward into weights and coordinates + NCCL all-reduce + Nadam",
                        "molecules_per_step_per_gpu": args.mols, "path": "fused (C ABI only, no autograd)",
+                       "resident_batches": nb,
+                       "order": ("pipelined: sort + featurize of the next batch and the coordinate gradient of this "
+                                 "one run beside the network kernels on two side streams" if pipelined else
+                                 "serial: one kernel after another"),
                        "launch": ("eager" if args.no_graph else
-                                  "cuda_graph (forward+backward, coordinate gradient, update; all-reduce eager, "
-                                  "overlapping the coordinate gradient)")}}), flush=True)
+                                  "cuda_graph (all-reduce eager, between the weight gradients and the update, "
+                                  "under the coordinate gradient)")}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -578,9 +602,11 @@ def main():
                     help="aev: the benchmark metric (sort + featurize + featurize_grad); train: the full "
                          "data-parallel training step of benchmark configuration 3; forces: energies + forces of "
                          "config-1 batches through the C ABI only (both reported separately)")
-    ap.add_argument("--train-path", default="fused", choices=["fused", "autograd"],
-                    help="train workload: fused = C-ABI calls only (FusedTrainStep); autograd = torch autograd "
-                         "drives the same kernels (what TrainerMultiTower does)")
+    ap.add_argument("--train-path", default="fused", choices=["fused", "fused-serial", "autograd"],
+                    help="train workload: fused = C-ABI calls only (FusedTrainStep) with the next batch's featurize "
+                         "and the coordinate gradient beside the network kernels (StepPipeline); fused-serial = the "
+                         "same kernels one after another; autograd = torch autograd drives the same kernels (what "
+                         "TrainerMultiTower does)")
     ap.add_argument("--e2e-slots", type=int, default=4,
                     help="batches in flight (one stream each) in the end-to-end measurement")
     ap.add_argument("--case", default="config1", choices=["config1", "config2", "config4"],
@@ -596,7 +622,7 @@ def main():
         run_reference_arm(args)
         return
     if args.workload == "train":
-        if args.train_path == "fused":
+        if args.train_path in ("fused", "fused-serial"):
             run_fused_train_workload(args)
         else:
             run_train_workload(args)
@@ -758,6 +784,17 @@ def main():
         total_atoms = float(my_atoms)
     value = total_atoms / (elapsed_ms * 1e-3)
 
+    # ---- spread: passes over the resident pool timed one by one (not part of the headline) ----
+    pass_ms = []
+    if mega is not None:
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(min(32, max(2, args.steps // nb)) + 1)]
+        evs[0].record()
+        for ev in evs[1:]:
+            mega.replay()
+            ev.record()
+        torch.cuda.synchronize()
+        pass_ms = sorted(a.elapsed_time(b) / nb for a, b in zip(evs[:-1], evs[1:]))
+
     # ---- per-kernel durations (graphs of one kernel kind over all batches) ------------------
     def time_kernel(fn_name):
         g = torch.cuda.CUDAGraph()
@@ -886,6 +923,8 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "ms_per_step_by_pass": ({"median": pass_ms[len(pass_ms) // 2], "best": pass_ms[0], "worst": pass_ms[-1],
+                                 "passes": len(pass_ms), "steps_per_pass": nb} if pass_ms else None),
         "scaling": "weak", "vs_baseline": None, "dtype": "f64" if args.case == "config2" else "f32",
         "data": "synthetic",
         "config": {"workload": CASE_WORKLOAD[args.case],

@@ -51,22 +51,18 @@ class FusedTrainStep:
                 if p.grad is None or p.grad.data_ptr() % 4:
                     raise ValueError("parameters must have gradient buffers (FlatNadam provides them)")
 
-    def forward_backward(self, sb: StagedBatch, labels: torch.Tensor, stream=None, feature_grad: bool = True) -> None:
-        """Everything up to the weight gradients.  Afterwards ``self.l2s[:n_mols]`` holds the squared
-        errors, the flat gradient buffer the weight gradients of this batch (it is zeroed here
-        first) and, unless ``feature_grad`` is False (energy-only training: the three products
-        towards the features are skipped), ``sb.upstream`` dLoss/dfeatures."""
+    def _check(self, sb: StagedBatch) -> None:
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this step")
-        if stream is None:
-            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        lib = _lib.lib()
-        n, acs = sb.n_atoms, sb.acs_host
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _network_args(self, sb: StagedBatch, feature_grad: bool, packed=None):
+        """The three argument blocks of the atomic-network kernels for this batch."""
+        acs = sb.acs_host
         starts = np.concatenate([[0], np.cumsum(acs)])
-        sb.run_sort(stream)
-        sb.run_featurize(stream)
         fwd, bwd, wg = _lib.MlpArgs(), _lib.MlpBackwardArgs(), _lib.MlpWeightGradArgs()
-        packed = self.model.pack_weights(stream)
         for t in range(4):
             if acs[t] == 0:
                 continue
@@ -92,23 +88,55 @@ class FusedTrainStep:
             bwd.grad_features[t] = _ptr(sb.upstream, s * FEATURE_SIZE) if feature_grad else None
             wg.dw1[t], wg.dw2[t], wg.dw3[t], wg.dw4[t] = _ptr(w1.grad), _ptr(w2.grad), _ptr(w3.grad), _ptr(w4.grad)
             wg.db1[t], wg.db2[t], wg.db3[t], wg.db4[t] = _ptr(b1.grad), _ptr(b2.grad), _ptr(b3.grad), _ptr(b4.grad)
+        return fwd, bwd, wg
+
+    # The step in four phases, each on the CURRENT stream of the device.  ``featurize`` of a batch
+    # depends on nothing but its coordinates, so a caller may run it for the NEXT batch beside the
+    # network kernels of this one; ``coordinate_gradient`` and ``weight_gradients`` both depend on
+    # ``networks`` only and may run side by side (see StepPipeline).
+
+    def featurize(self, sb: StagedBatch) -> None:
+        """ani_sort + featurize: ``sb.features`` (element-sorted rows) and the sort indices."""
+        self._check(sb)
+        stream = self._stream()
+        sb.run_sort(stream)
+        sb.run_featurize(stream)
+
+    def networks(self, sb: StagedBatch, labels: torch.Tensor, feature_grad: bool = True) -> None:
+        """Weight packing, networks forward, molecule energies + MSE gradient, networks backward.
+        Afterwards ``self.l2s[:n_mols]`` holds the squared errors, the dz buffers the layer
+        gradients and, unless ``feature_grad`` is False (energy-only training: the three products
+        towards the features are skipped), ``sb.upstream`` dLoss/dfeatures."""
+        self._check(sb)
+        stream = self._stream()
+        lib = _lib.lib()
+        fwd, bwd, _ = self._network_args(sb, feature_grad, self.model.pack_weights(stream))
         _lib.check(lib.ani_mlp_forward_f32(ctypes.byref(fwd), sb._acs_ptr, self.act_id, int(self.split), stream),
                    "ani_mlp_forward_f32")
         _lib.check(lib.ani_molecule_energy_f32(_ptr(self.energy_sorted), _ptr(sb.gather), _ptr(sb.mol_offsets),
-                                               _ptr(sb.mol_counts), sb.n_mols, n, _ptr(labels),
+                                               _ptr(sb.mol_counts), sb.n_mols, sb.n_atoms, _ptr(labels),
                                                1.0 / max(sb.n_mols, 1), _ptr(self.mol_energy), _ptr(self.l2s),
                                                _ptr(self.grad_energy_sorted), stream), "ani_molecule_energy_f32")
         _lib.check(lib.ani_mlp_backward_f32(ctypes.byref(bwd), sb._acs_ptr, int(self.split), stream),
                    "ani_mlp_backward_f32")
+
+    def weight_gradients(self, sb: StagedBatch) -> None:
+        """Zeroes the flat gradient buffer and adds the weight gradients of this batch to it."""
+        stream = self._stream()
+        _, _, wg = self._network_args(sb, True)
         self.optimizer.flat_grads.zero_()
-        _lib.check(lib.ani_mlp_weight_grad_f32(ctypes.byref(wg), sb._acs_ptr, int(self.split), stream),
+        _lib.check(_lib.lib().ani_mlp_weight_grad_f32(ctypes.byref(wg), sb._acs_ptr, int(self.split), stream),
                    "ani_mlp_weight_grad_f32")
 
-    def coordinate_gradient(self, sb: StagedBatch, stream=None) -> None:
+    def forward_backward(self, sb: StagedBatch, labels: torch.Tensor, feature_grad: bool = True) -> None:
+        """Everything up to the weight gradients, in order on the current stream."""
+        self.featurize(sb)
+        self.networks(sb, labels, feature_grad)
+        self.weight_gradients(sb)
+
+    def coordinate_gradient(self, sb: StagedBatch) -> None:
         """dLoss/dx, dy, dz into ``sb.grads`` (featurize_grad with ``sb.upstream`` as its upstream)."""
-        if stream is None:
-            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        sb.run_featurize_grad(stream)
+        sb.run_featurize_grad(self._stream())
 
     def step(self, sb: StagedBatch, labels: torch.Tensor) -> None:
         """The whole step, eagerly, on the current stream (no overlap)."""
@@ -118,3 +146,108 @@ class FusedTrainStep:
         self.optimizer.step()
 
     KERNELS = 12   # weight packing, sort, featurize, mlp fwd, molecule energy, mlp bwd, memset, wgrad, zero3, featurize_grad, sumsq, nadam
+
+
+class StepPipeline:
+    """Training steps over a pool of resident batches with the independent kernels side by side:
+
+        feature stream    sort + featurize of batch b+1      (needs only its coordinates)
+        main stream       networks(b) -> weight gradients(b) -> [all-reduce] -> update
+        gradient stream                  coordinate gradient(b)          (needs networks(b) only)
+
+    The network kernels run one 128-atom tile per SM on about three quarters of the SMs and are
+    bound by their operand pipeline, the featurizer kernels by instruction issue, so they fill one
+    another's gaps.  The sequence of weights is the one of the serial step: featurize does not
+    read the weights, and each update still waits for everything of its own batch.
+
+    ``prime()`` featurizes batch 0; ``run(k)`` then performs step k on batch ``k % len(staged)``
+    and featurizes the batch after it.  With ``graphs`` the phases are captured once per batch
+    (one graph per step on a single GPU; with ``allreduce`` the collective stays outside the
+    graphs, between the weight gradients and the update, under the coordinate gradient).
+    """
+
+    def __init__(self, step: FusedTrainStep, staged, labels, allreduce: bool = False, graphs: bool = True):
+        if len(staged) < 2 or len(staged) != len(labels):
+            raise ValueError("StepPipeline needs at least two resident batches and one label vector per batch")
+        self.step, self.staged, self.labels = step, list(staged), list(labels)
+        self.allreduce = bool(allreduce)
+        self.nb = len(self.staged)
+        dev = step.device
+        self.feature_stream = torch.cuda.Stream(device=dev)
+        self.gradient_stream = torch.cuda.Stream(device=dev)
+        self._whole = self._head = self._wgrad = self._cgrad = self._update = None
+        if graphs:
+            self._capture()
+
+    # -- the pieces, each issued on the current stream with its side branch forked and joined --
+    def _head_piece(self, b: int) -> None:
+        cur = torch.cuda.current_stream(self.step.device)
+        self.feature_stream.wait_stream(cur)
+        with torch.cuda.stream(self.feature_stream):
+            self.step.featurize(self.staged[(b + 1) % self.nb])
+        self.step.networks(self.staged[b], self.labels[b])
+        cur.wait_stream(self.feature_stream)
+
+    def _tail_piece(self, b: int) -> None:
+        """Single GPU: weight gradients + update beside the coordinate gradient."""
+        cur = torch.cuda.current_stream(self.step.device)
+        self.gradient_stream.wait_stream(cur)
+        with torch.cuda.stream(self.gradient_stream):
+            self.step.coordinate_gradient(self.staged[b])
+        self.step.weight_gradients(self.staged[b])
+        self.step.optimizer.step()
+        cur.wait_stream(self.gradient_stream)
+
+    @staticmethod
+    def _graph_of(fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return g
+
+    def _capture(self) -> None:
+        step = self.step
+        with torch.cuda.device(step.device):
+            if not self.allreduce:
+                self._whole = [self._graph_of(lambda b=b: (self._head_piece(b), self._tail_piece(b)))
+                               for b in range(self.nb)]
+                return
+            self._head = [self._graph_of(lambda b=b: self._head_piece(b)) for b in range(self.nb)]
+            self._wgrad = [self._graph_of(lambda sb=sb: step.weight_gradients(sb)) for sb in self.staged]
+            self._cgrad = [self._graph_of(lambda sb=sb: step.coordinate_gradient(sb)) for sb in self.staged]
+            self._update = self._graph_of(step.optimizer.step)
+
+    def prime(self) -> None:
+        self.step.featurize(self.staged[0])
+
+    def run(self, k: int) -> None:
+        b = k % self.nb
+        step = self.step
+        if self._whole is not None:
+            self._whole[b].replay()
+            return
+        if not self.allreduce:
+            self._head_piece(b)
+            self._tail_piece(b)
+            return
+        cur = torch.cuda.current_stream(step.device)
+        if self._head is not None:
+            self._head[b].replay()
+        else:
+            self._head_piece(b)
+        self.gradient_stream.wait_stream(cur)
+        with torch.cuda.stream(self.gradient_stream):
+            if self._cgrad is not None:
+                self._cgrad[b].replay()
+            else:
+                step.coordinate_gradient(self.staged[b])
+        if self._wgrad is not None:
+            self._wgrad[b].replay()
+        else:
+            step.weight_gradients(self.staged[b])
+        average_gradients(step.model.get_parameters(), step.optimizer.flat_grads)
+        cur.wait_stream(self.gradient_stream)
+        if self._update is not None:
+            self._update.replay()
+        else:
+            step.optimizer.step()

@@ -235,6 +235,74 @@ def test_fused_train_step_matches_the_autograd_step():
     assert (w0 - w1).abs().max().item() < 1e-5
 
 
+@pytest.mark.parametrize("graphs", [True, False])
+def test_step_pipeline_gives_the_weights_of_the_serial_steps(graphs):
+    """StepPipeline (next batch's featurize and this batch's coordinate gradient on side streams,
+    optionally as CUDA graphs) against FusedTrainStep.step one kernel after another: the same
+    weights after seven steps over three batches, the same losses and coordinate gradients."""
+    import torch
+    from khan_b200.model import activations
+    from khan_b200.model.nn import MoleculeNN
+    from khan_b200.staged import HostBatch, StagedBatch
+    from khan_b200.training.fused_step import FusedTrainStep, StepPipeline
+    from khan_b200.training.optim import FlatNadam
+    dev = torch.device("cuda", 0)
+    pool = syn.batch_pool(3, n_mols=48, seed=21)
+    cap = max(b.n_atoms for b in pool)
+    ys = [torch.from_numpy(np.random.default_rng(30 + k).normal(size=b.n_mols).astype(np.float32)).to(dev)
+          for k, b in enumerate(pool)]
+    n_steps = 7
+    results = []
+    for pipelined in (False, True):
+        model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=13, init="he")
+        opt = FlatNadam(model.get_parameters(), lr=1e-3, clip_norm=5.0)
+        staged = []
+        for b in pool:
+            sb = StagedBatch(cap, 48)
+            sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
+            staged.append(sb)
+        step = FusedTrainStep(model, opt, cap, 48)
+        losses, coords = [], []
+        if pipelined:
+            side = torch.cuda.Stream()       # graphs are captured and replayed off the default stream
+            with torch.cuda.stream(side):
+                pipe = StepPipeline(step, staged, ys, graphs=graphs)
+                pipe.prime()
+                for k in range(n_steps):
+                    pipe.run(k)
+                    losses.append(step.l2s[:48].mean().clone())
+                    coords.append(staged[k % 3].grads[:, :pool[k % 3].n_atoms].clone())
+            torch.cuda.synchronize()
+        else:
+            for k in range(n_steps):
+                step.step(staged[k % 3], ys[k % 3])
+                losses.append(step.l2s[:48].mean().clone())
+                coords.append(staged[k % 3].grads[:, :pool[k % 3].n_atoms].clone())
+            torch.cuda.synchronize()
+        assert opt.steps_done() == n_steps
+        results.append((torch.stack(losses).cpu(), coords, opt.flat_params.clone()))
+    (l0, c0, w0), (l1, c1, w1) = results
+    assert (l0 - l1).abs().max().item() < 1e-4 * l0.abs().max().item()
+    for a, b in zip(c0, c1):
+        assert (a - b).abs().max().item() < 1e-3 * a.abs().max().item()
+    assert (w0 - w1).abs().max().item() < 1e-5
+
+
+def test_step_pipeline_needs_two_batches():
+    import torch
+    from khan_b200.model import activations
+    from khan_b200.model.nn import MoleculeNN
+    from khan_b200.staged import StagedBatch
+    from khan_b200.training.fused_step import FusedTrainStep, StepPipeline
+    from khan_b200.training.optim import FlatNadam
+    dev = torch.device("cuda", 0)
+    model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=13, init="he")
+    opt = FlatNadam(model.get_parameters(), lr=1e-3)
+    step = FusedTrainStep(model, opt, 64, 4)
+    with pytest.raises(ValueError):
+        StepPipeline(step, [StagedBatch(64, 4)], [torch.zeros(4, device=dev)])
+
+
 def test_molecule_energy_kernel_on_a_ragged_table():
     """ani_molecule_energy_f32 directly: sums through gather_idxs, squared errors, the MSE gradient
     scattered back to the sorted order; empty molecules give 0; a bad gather index is reported."""
