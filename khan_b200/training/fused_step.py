@@ -155,15 +155,17 @@ class StepPipeline:
         main stream       networks(b) -> weight gradients(b) -> [all-reduce] -> update
         gradient stream                  coordinate gradient(b)          (needs networks(b) only)
 
-    The network kernels run one 128-atom tile per SM on about three quarters of the SMs and are
-    bound by their operand pipeline, the featurizer kernels by instruction issue, so they fill one
-    another's gaps.  The sequence of weights is the one of the serial step: featurize does not
-    read the weights, and each update still waits for everything of its own batch.
+    The network kernels run one 128-atom tile per SM on about three quarters of the SMs, and a
+    featurizer CTA fits beside a network CTA, so the side streams use what the network kernels
+    leave free (measured on a 1024-molecule batch: networks + featurize 119 us side by side against
+    131 us in sequence) and the step needs no launch boundary between its phases.  The sequence of
+    weights is the one of the serial step: featurize does not read the weights, and each update
+    still waits for everything of its own batch.
 
     ``prime()`` featurizes batch 0; ``run(k)`` then performs step k on batch ``k % len(staged)``
     and featurizes the batch after it.  With ``graphs`` the phases are captured once per batch
     (one graph per step on a single GPU; with ``allreduce`` the collective stays outside the
-    graphs, between the weight gradients and the update, under the coordinate gradient).
+    graphs, between the graph that ends with the weight gradients and the graph of the update).
     """
 
     def __init__(self, step: FusedTrainStep, staged, labels, allreduce: bool = False, graphs: bool = True):
@@ -175,27 +177,26 @@ class StepPipeline:
         dev = step.device
         self.feature_stream = torch.cuda.Stream(device=dev)
         self.gradient_stream = torch.cuda.Stream(device=dev)
-        self._whole = self._head = self._wgrad = self._cgrad = self._update = None
+        self._whole = self._update = None
         if graphs:
             self._capture()
 
-    # -- the pieces, each issued on the current stream with its side branch forked and joined --
-    def _head_piece(self, b: int) -> None:
-        cur = torch.cuda.current_stream(self.step.device)
+    def _issue(self, b: int, update: bool) -> None:
+        """One step on the current stream with its two side branches forked and joined."""
+        step = self.step
+        cur = torch.cuda.current_stream(step.device)
         self.feature_stream.wait_stream(cur)
         with torch.cuda.stream(self.feature_stream):
-            self.step.featurize(self.staged[(b + 1) % self.nb])
-        self.step.networks(self.staged[b], self.labels[b])
+            step.featurize(self.staged[(b + 1) % self.nb])
+        step.networks(self.staged[b], self.labels[b])
+        # the featurizer joins here: letting it run on into the gradient kernels was measured slower
         cur.wait_stream(self.feature_stream)
-
-    def _tail_piece(self, b: int) -> None:
-        """Single GPU: weight gradients + update beside the coordinate gradient."""
-        cur = torch.cuda.current_stream(self.step.device)
         self.gradient_stream.wait_stream(cur)
         with torch.cuda.stream(self.gradient_stream):
-            self.step.coordinate_gradient(self.staged[b])
-        self.step.weight_gradients(self.staged[b])
-        self.step.optimizer.step()
+            step.coordinate_gradient(self.staged[b])
+        step.weight_gradients(self.staged[b])
+        if update:       # single GPU; with several ranks the all-reduce comes first
+            step.optimizer.step()
         cur.wait_stream(self.gradient_stream)
 
     @staticmethod
@@ -206,16 +207,11 @@ class StepPipeline:
         return g
 
     def _capture(self) -> None:
-        step = self.step
-        with torch.cuda.device(step.device):
-            if not self.allreduce:
-                self._whole = [self._graph_of(lambda b=b: (self._head_piece(b), self._tail_piece(b)))
-                               for b in range(self.nb)]
-                return
-            self._head = [self._graph_of(lambda b=b: self._head_piece(b)) for b in range(self.nb)]
-            self._wgrad = [self._graph_of(lambda sb=sb: step.weight_gradients(sb)) for sb in self.staged]
-            self._cgrad = [self._graph_of(lambda sb=sb: step.coordinate_gradient(sb)) for sb in self.staged]
-            self._update = self._graph_of(step.optimizer.step)
+        with torch.cuda.device(self.step.device):
+            self._whole = [self._graph_of(lambda b=b: self._issue(b, not self.allreduce))
+                           for b in range(self.nb)]
+            if self.allreduce:
+                self._update = self._graph_of(self.step.optimizer.step)
 
     def prime(self) -> None:
         self.step.featurize(self.staged[0])
@@ -225,28 +221,15 @@ class StepPipeline:
         step = self.step
         if self._whole is not None:
             self._whole[b].replay()
-            return
+        else:
+            self._issue(b, not self.allreduce)
         if not self.allreduce:
-            self._head_piece(b)
-            self._tail_piece(b)
             return
-        cur = torch.cuda.current_stream(step.device)
-        if self._head is not None:
-            self._head[b].replay()
-        else:
-            self._head_piece(b)
-        self.gradient_stream.wait_stream(cur)
-        with torch.cuda.stream(self.gradient_stream):
-            if self._cgrad is not None:
-                self._cgrad[b].replay()
-            else:
-                step.coordinate_gradient(self.staged[b])
-        if self._wgrad is not None:
-            self._wgrad[b].replay()
-        else:
-            step.weight_gradients(self.staged[b])
+        # Several ranks: the collective sits between the weight gradients and the update with nothing
+        # beside it.  (Measured on two GPUs: starting the coordinate gradient here instead, under the
+        # all-reduce, is slower -- presumably its persistent grid fills every SM and the collective's
+        # kernel waits behind it.)
         average_gradients(step.model.get_parameters(), step.optimizer.flat_grads)
-        cur.wait_stream(self.gradient_stream)
         if self._update is not None:
             self._update.replay()
         else:

@@ -235,11 +235,12 @@ def test_fused_train_step_matches_the_autograd_step():
     assert (w0 - w1).abs().max().item() < 1e-5
 
 
-@pytest.mark.parametrize("graphs", [True, False])
-def test_step_pipeline_gives_the_weights_of_the_serial_steps(graphs):
+@pytest.mark.parametrize("graphs,allreduce", [(True, False), (False, False), (True, True), (False, True)])
+def test_step_pipeline_gives_the_weights_of_the_serial_steps(graphs, allreduce):
     """StepPipeline (next batch's featurize and this batch's coordinate gradient on side streams,
     optionally as CUDA graphs) against FusedTrainStep.step one kernel after another: the same
-    weights after seven steps over three batches, the same losses and coordinate gradients."""
+    weights after seven steps over three batches, the same losses and coordinate gradients.
+    ``allreduce`` selects the multi-rank arrangement (the collective is a no-op in one process)."""
     import torch
     from khan_b200.model import activations
     from khan_b200.model.nn import MoleculeNN
@@ -266,7 +267,7 @@ def test_step_pipeline_gives_the_weights_of_the_serial_steps(graphs):
         if pipelined:
             side = torch.cuda.Stream()       # graphs are captured and replayed off the default stream
             with torch.cuda.stream(side):
-                pipe = StepPipeline(step, staged, ys, graphs=graphs)
+                pipe = StepPipeline(step, staged, ys, allreduce=allreduce, graphs=graphs)
                 pipe.prime()
                 for k in range(n_steps):
                     pipe.run(k)
