@@ -46,10 +46,12 @@ class EnergyForces:
         ann = self.model.anns[t]
         return [w.detach() for w in ann.Ws], [b.detach() for b in ann.bs]
 
-    def run(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None) -> None:
+    def run(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None, pack: bool = True) -> None:
         """One pass over the batch staged in ``sb``.  Afterwards ``self.mol_energy[:sb.n_mols]``
         holds the molecule energies and ``sb.grads[:, :sb.n_atoms]`` dE/dx, dE/dy, dE/dz (forces are
-        their negatives)."""
+        their negatives).  ``pack=False`` skips the refresh of the pre-packed weights: for a caller
+        that packed them (``model.pack_weights``) after the last change of the weights, e.g. once
+        before a series of passes that run side by side on several streams."""
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this evaluator")
         if stream is None:
@@ -60,7 +62,7 @@ class EnergyForces:
         sb.run_sort(stream)
         sb.run_featurize(stream)
         fwd, bwd = _lib.MlpArgs(), _lib.MlpBackwardArgs()
-        packed = self.model.pack_weights(stream)
+        packed = self.model.pack_weights(stream) if pack else self.model.packed_weights()
         for t in range(4):
             if acs[t] == 0:
                 continue
@@ -88,4 +90,4 @@ class EnergyForces:
                    "ani_mlp_backward_f32")
         sb.run_featurize_grad(stream)
 
-    KERNELS_PER_PASS = 8   # weight packing, sort, featurize, mlp forward, molecule sums, mlp backward, zero fill, featurize_grad
+    KERNELS_PER_PASS = 8   # weight packing (unless pack=False), sort, featurize, mlp forward, molecule sums, mlp backward, zero fill, featurize_grad

@@ -285,6 +285,10 @@ class MoleculeNN:
             _lib.check(_lib.lib().ani_mlp_pack_weights_f32(ctypes.byref(args), stream), "ani_mlp_pack_weights_f32")
         return self._packed
 
+    def packed_weights(self):
+        """The pre-packed copy as ``pack_weights`` last wrote it (None before the first call)."""
+        return getattr(self, "_packed", None)
+
     @property
     def fused(self) -> bool:
         return (self.precision == torch.float32 and self.layer_sizes == FUSED_LAYERS

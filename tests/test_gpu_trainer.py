@@ -179,6 +179,15 @@ def test_energy_forces_evaluator_matches_the_trainer():
     got_g = sb.grads[:, :b.n_atoms].cpu().numpy().T
     assert np.abs(got_e - want_e).max() < 1e-5 * np.abs(want_e).max()
     assert np.abs(got_g - want_g).max() < 1e-4 * np.abs(want_g).max()
+    # a second evaluator on another stream, reusing the weights packed above
+    other, st = EnergyForces(tr.model, b.n_atoms, b.n_mols), torch.cuda.Stream()
+    sb.grads.zero_()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        other.run(sb, pack=False)
+    torch.cuda.synchronize()
+    assert np.array_equal(other.mol_energy[:b.n_mols].cpu().numpy(), got_e)
+    assert np.abs(sb.grads[:, :b.n_atoms].cpu().numpy().T - want_g).max() < 1e-4 * np.abs(want_g).max()
 
 
 def test_fused_train_step_matches_the_autograd_step():
