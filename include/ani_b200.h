@@ -371,6 +371,53 @@ int ani_charge_grad_f64(const double* xs, const double* ys, const double* zs, co
                         const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
                         const double* grads, double* q_grads, void* stream);
 
+/*
+ * Host-side batch assembly (no CUDA call, usable without a GPU): writes the batch made of the
+ * molecules picks[0..n_picks) of a packed dataset, in that order, into one host arena -- what
+ * RawDataset.iterate of the reference builds with a Python loop over molecules and
+ * np.concatenate (khan/data/dataset.py:144-183) and what the reference's feed then copies
+ * (khan/training/trainer_multi_tower.py:749-828).
+ *
+ * Source (the packed dataset): mol_ptr[n_mols_total + 1] is the CSR of atom ranges; src_xyz is
+ * [3][src_stride] in float (src_is_f64 = 0) or double; src_types[...] element ids; src_ys
+ * (optional) one label per molecule and src_grads (optional) [3][src_stride], both in the
+ * DESTINATION precision.  noise (optional): [atoms of the batch][3] doubles added to the
+ * coordinates before the cast, the sum formed in double (the coordinate fuzz of
+ * RawDataset.iterate, drawn by the caller so that the random stream stays numpy's).
+ * Destination: dst_xyz / dst_grads [3][dst_stride] and dst_ys in float (dst_is_f64 = 0) or
+ * double, dst_types[cap_atoms], dst_mol_ids[cap_atoms] (index of the molecule within the batch),
+ * dst_mol_offsets / dst_mol_counts[cap_mols].  n_atoms_out receives the atoms of the batch and
+ * acs_out[4] the atoms per element.  ANI_ERR_BAD_SIZE if the batch does not fit cap_atoms /
+ * cap_mols (nothing is written then), ANI_ERR_BAD_INDEX for a pick outside the dataset.
+ */
+typedef struct ani_host_pack_args {
+    const long long* picks;
+    int n_picks;
+    long long n_mols_total;
+    const long long* mol_ptr;
+    const void* src_xyz;
+    long long src_stride;
+    int src_is_f64;
+    const int* src_types;
+    const void* src_ys;
+    const void* src_grads;
+    const double* noise;
+    void* dst_xyz;
+    void* dst_grads;
+    void* dst_ys;
+    long long dst_stride;
+    int dst_is_f64;
+    int* dst_types;
+    long long* dst_mol_ids;
+    int* dst_mol_offsets;
+    int* dst_mol_counts;
+    int cap_atoms;
+    int cap_mols;
+    int* n_atoms_out;
+    int* acs_out;
+} ani_host_pack_args;
+int ani_host_pack_batch(const ani_host_pack_args* args);
+
 #ifdef __cplusplus
 }
 #endif

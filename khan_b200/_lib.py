@@ -18,7 +18,7 @@ CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
 HEADERS = ["ani_params.h", "ani_common.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_grad.cuh",
-           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh", "ani_energy.cuh"]
+           "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh", "ani_energy.cuh", "ani_host_pack.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -42,6 +42,19 @@ class MlpArgs(ctypes.Structure):
 class MlpPackArgs(ctypes.Structure):
     """``ani_mlp_pack_args`` of include/ani_b200.h."""
     _fields_ = [(name, ctypes.c_void_p * 4) for name in ("w1", "w2", "w3", "packed")]
+
+
+class HostPackArgs(ctypes.Structure):
+    """``ani_host_pack_args`` of include/ani_b200.h."""
+    _fields_ = [("picks", ctypes.c_void_p), ("n_picks", ctypes.c_int), ("n_mols_total", ctypes.c_longlong),
+                ("mol_ptr", ctypes.c_void_p), ("src_xyz", ctypes.c_void_p), ("src_stride", ctypes.c_longlong),
+                ("src_is_f64", ctypes.c_int), ("src_types", ctypes.c_void_p), ("src_ys", ctypes.c_void_p),
+                ("src_grads", ctypes.c_void_p), ("noise", ctypes.c_void_p), ("dst_xyz", ctypes.c_void_p),
+                ("dst_grads", ctypes.c_void_p), ("dst_ys", ctypes.c_void_p), ("dst_stride", ctypes.c_longlong),
+                ("dst_is_f64", ctypes.c_int), ("dst_types", ctypes.c_void_p), ("dst_mol_ids", ctypes.c_void_p),
+                ("dst_mol_offsets", ctypes.c_void_p), ("dst_mol_counts", ctypes.c_void_p),
+                ("cap_atoms", ctypes.c_int), ("cap_mols", ctypes.c_int), ("n_atoms_out", ctypes.c_void_p),
+                ("acs_out", ctypes.c_void_p)]
 
 
 class MlpBackwardArgs(ctypes.Structure):
@@ -81,6 +94,7 @@ SIGNATURES = {
     "ani_molecule_energy_f32": (_i, [_vp] * 4 + [_i, _i, _vp, ctypes.c_float, _vp, _vp, _vp, _vp]),
     "ani_nadam_step_f32": (_i, [_vp] * 5 + [ctypes.c_longlong, _vp, _vp, _vp]),
     "ani_clip_rows_f32": (_i, [_vp, _vp, _vp, _i, ctypes.c_float, _vp]),
+    "ani_host_pack_batch": (_i, [_vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_f64": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_grad_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp, _vp]),

@@ -21,6 +21,7 @@
 #include "ani_optim.cuh"
 #include "ani_energy.cuh"
 #include "ani_sort.cuh"
+#include "ani_host_pack.h"
 
 namespace {
 
@@ -837,6 +838,12 @@ int ani_charge_grad_f64(const double* xs, const double* ys, const double* zs, co
 {
     return charge_grad_impl<double>(xs, ys, zs, qs, mol_offsets, mol_atom_counts, n_mols, n_atoms,
                                     grads, q_grads, stream);
+}
+
+int ani_host_pack_batch(const ani_host_pack_args* args)
+{
+    if (!args) return ANI_ERR_NULL_POINTER;
+    return ani::host_pack_batch(*args);
 }
 
 }  // extern "C"

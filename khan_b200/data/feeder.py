@@ -6,8 +6,8 @@ from a submitter thread (``khan/training/trainer_multi_tower.py:749-828``); that
 featurizer, bounds its throughput.  Here
 
 * :class:`PackedDataset` concatenates the molecules ONCE into CSR form (``ptr`` + flat element
-  ids + ``[3, N]`` coordinates), so a batch is a slice (in order) or one vectorised gather
-  (shuffled) -- no per-molecule Python work per batch;
+  ids + ``[3, N]`` coordinates), so a batch is one call of the library's host packer
+  (``ani_host_pack_batch``: a per-molecule copy loop in C++) -- no Python work per molecule;
 * :class:`BatchFeeder` runs a submitter thread that writes each batch into one pinned host
   arena and moves it to the device with ONE asynchronous copy on a copy stream, ``depth``
   batches ahead of the consumer, handing over with CUDA events.
@@ -18,11 +18,14 @@ The batch contents and their order are exactly those of ``RawDataset.iterate`` (
 """
 from __future__ import annotations
 
+import ctypes
 import queue
 import threading
 
 import numpy as np
 import torch
+
+from .. import _lib
 
 _ALIGN = 256
 
@@ -70,7 +73,46 @@ class PackedDataset:
         return int(top.sum()), k
 
     def gather(self, picks: np.ndarray, slot: "HostSlot", fuzz=None) -> None:
-        """Writes the batch made of molecules ``picks`` (in that order) into ``slot``."""
+        """Writes the batch made of molecules ``picks`` (in that order) into ``slot``: one call of
+        the library's host packer (``ani_host_pack_batch``), a per-molecule copy loop in C++."""
+        picks = np.ascontiguousarray(picks, dtype=np.int64)
+        m = len(picks)
+        if m > slot.cap_mols:
+            raise ValueError("batch larger than the slot")
+        total = int(self.ptr[-1])
+        if (self.types.shape[0] != total or self.xyz.shape != (3, total) or slot.np_dtype != self.dtype
+                or (self.grads is not None and self.grads.shape != (3, total))
+                or (self.ys is not None and self.ys.shape[0] != self.num_mols())):
+            raise ValueError("the arrays of the packed dataset do not match its molecule table")
+        noise = None
+        if fuzz is not None:   # same draw as RawDataset.iterate: uniform over an (n, 3) array
+            n = int(self.counts[picks].sum())
+            noise = np.random.uniform(-fuzz, fuzz, (n, 3))
+        a = _lib.HostPackArgs()
+        a.picks, a.n_picks, a.n_mols_total = picks.ctypes.data, m, self.num_mols()
+        a.mol_ptr = self.ptr.ctypes.data
+        a.src_xyz, a.src_stride = self.xyz.ctypes.data, self.xyz.shape[1]
+        a.src_is_f64 = int(self.xyz.dtype == np.float64)
+        a.src_types = self.types.ctypes.data
+        a.src_ys = None if self.ys is None else self.ys.ctypes.data
+        a.src_grads = None if self.grads is None else self.grads.ctypes.data
+        a.noise = None if noise is None else noise.ctypes.data
+        a.dst_xyz, a.dst_grads, a.dst_ys = slot.xyz.ctypes.data, slot.grads.ctypes.data, slot.ys.ctypes.data
+        a.dst_stride, a.dst_is_f64 = slot.cap_atoms, int(slot.np_dtype == np.float64)
+        a.dst_types, a.dst_mol_ids = slot.types.ctypes.data, slot.mol_ids.ctypes.data
+        a.dst_mol_offsets, a.dst_mol_counts = slot.mol_offsets.ctypes.data, slot.mol_counts.ctypes.data
+        a.cap_atoms, a.cap_mols = slot.cap_atoms, slot.cap_mols
+        n_atoms = ctypes.c_int(0)
+        a.n_atoms_out, a.acs_out = ctypes.addressof(n_atoms), slot.acs.ctypes.data
+        status = _lib.lib().ani_host_pack_batch(ctypes.byref(a))
+        if status == -2:
+            raise ValueError("batch larger than the slot")
+        _lib.check(status, "ani_host_pack_batch")
+        slot.n_atoms, slot.n_mols = int(n_atoms.value), m
+        slot.has_ys, slot.has_grads = self.ys is not None, self.grads is not None
+
+    def gather_numpy(self, picks: np.ndarray, slot: "HostSlot", fuzz=None) -> None:
+        """The same batch assembled with numpy indexing -- what ``gather`` is tested against."""
         counts = self.counts[picks]
         m = len(picks)
         n = int(counts.sum())

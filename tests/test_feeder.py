@@ -77,3 +77,47 @@ def test_submitter_errors_reach_the_consumer():
     packed.types = packed.types[:3]          # corrupt the packed data: gather will fail
     with pytest.raises((ValueError, IndexError)):
         list(feeder)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("source", [np.float32, np.float64])
+def test_native_packer_matches_numpy_indexing(dtype, source):
+    """ani_host_pack_batch against the numpy assembly of the same batch: every section of the
+    arena bit for bit -- shuffled picks with repeats, with and without fuzz, empty molecules."""
+    from khan_b200.data.feeder import HostSlot
+    rng = np.random.default_rng(5)
+    mols = [np.concatenate([rng.integers(0, 4, (n, 1)).astype(source), rng.normal(size=(n, 3)).astype(source)], axis=1)
+            for n in rng.integers(0, 30, 50)]
+    grads = [rng.normal(size=(len(m), 3)) for m in mols]
+    packed = PackedDataset(mols, rng.normal(size=len(mols)), grads, dtype)
+    assert packed.xyz.dtype == source
+    cap = packed.capacity(16)
+    a, b = HostSlot(cap[0], cap[1], dtype, pin=False), HostSlot(cap[0], cap[1], dtype, pin=False)
+    for picks, fuzz in ((np.arange(16), None), (np.arange(40, 50), None), (rng.permutation(50)[:16], None),
+                        (np.array([7, 7, 3, 49, 0]), 0.1), (np.zeros(0, np.int64), None), (rng.permutation(50)[:13], 0.05)):
+        np.random.seed(3)
+        packed.gather(picks, a, fuzz)
+        np.random.seed(3)
+        packed.gather_numpy(np.asarray(picks, np.int64), b, fuzz)
+        n, m = b.n_atoms, b.n_mols
+        assert (a.n_atoms, a.n_mols, a.has_ys, a.has_grads) == (n, m, True, True)
+        assert np.array_equal(a.acs, b.acs)
+        for name, used in (("xyz", n), ("grads", n)):
+            assert np.array_equal(getattr(a, name)[:, :used], getattr(b, name)[:, :used]), name
+        for name, used in (("types", n), ("mol_ids", n), ("mol_offsets", m), ("mol_counts", m), ("ys", m)):
+            assert np.array_equal(getattr(a, name)[:used], getattr(b, name)[:used]), name
+
+
+def test_native_packer_rejects_what_does_not_fit():
+    from khan_b200.data.feeder import HostSlot
+    ds = _dataset(9, with_grads=False)
+    packed = PackedDataset.from_raw(ds)
+    small = HostSlot(5, 9, np.float32, pin=False)
+    with pytest.raises(ValueError):
+        packed.gather(np.arange(9), small)
+    slot = HostSlot(*packed.capacity(9), np.float32, pin=False)
+    with pytest.raises(Exception) as info:
+        packed.gather(np.array([0, 99]), slot)
+    assert "ani_host_pack_batch" in str(info.value)
+    with pytest.raises(ValueError):
+        packed.gather(np.arange(3), HostSlot(*packed.capacity(9), np.float64, pin=False))
