@@ -46,12 +46,14 @@ class EnergyForces:
         ann = self.model.anns[t]
         return [w.detach() for w in ann.Ws], [b.detach() for b in ann.bs]
 
-    def run(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None, pack: bool = True) -> None:
+    def run(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None, pack: bool = True,
+            forces: bool = True) -> None:
         """One pass over the batch staged in ``sb``.  Afterwards ``self.mol_energy[:sb.n_mols]``
         holds the molecule energies and ``sb.grads[:, :sb.n_atoms]`` dE/dx, dE/dy, dE/dz (forces are
         their negatives).  ``pack=False`` skips the refresh of the pre-packed weights: for a caller
         that packed them (``model.pack_weights``) after the last change of the weights, e.g. once
-        before a series of passes that run side by side on several streams."""
+        before a series of passes that run side by side on several streams.  ``forces=False`` stops
+        after the molecule energies (``predict``)."""
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this evaluator")
         if stream is None:
@@ -86,6 +88,8 @@ class EnergyForces:
         _lib.check(lib.ani_molecule_energy_f32(_ptr(self.energy_sorted), _ptr(sb.gather), _ptr(sb.mol_offsets),
                                                _ptr(sb.mol_counts), sb.n_mols, n, None, 0.0,
                                                _ptr(self.mol_energy), None, None, stream), "ani_molecule_energy_f32")
+        if not forces:
+            return
         _lib.check(lib.ani_mlp_backward_f32(ctypes.byref(bwd), sb._acs_ptr, int(self.split), stream),
                    "ani_mlp_backward_f32")
         sb.run_featurize_grad(stream)

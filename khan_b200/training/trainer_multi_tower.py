@@ -401,6 +401,8 @@ class TrainerMultiTower:
         the devices: nothing here waits for the GPU, so the host runs ahead of it by as many
         batches as the feeder allows, and the caller synchronises once."""
         np_dt = np.float32 if self.precision == torch.float32 else np.float64
+        if self._evaluator_usable(dataset):
+            return self._evaluator_predictions(dataset, batch_size)
         it = BatchFeeder(PackedDataset.from_raw(dataset, np_dt), batch_size, False, None,
                          devices=self.towers, depth=2, hold=self.num_towers)
         preds, l2s = [], []
@@ -435,8 +437,7 @@ class TrainerMultiTower:
         (``trainer_multi_tower.py:580-614``).  On one float32 tower with the fused networks the
         batches go through the allocation-free evaluator (``khan_b200.inference.EnergyForces``: C-ABI
         calls only, no host wait per batch); ``use_evaluator=False`` forces the autograd path."""
-        if (use_evaluator and self.num_towers == 1 and self.precision == torch.float32 and self.model.fused
-                and self.towers[0].type == "cuda" and dataset.num_mols() > 0):
+        if use_evaluator and self._evaluator_usable(dataset):
             yield from self._evaluator_gradients(dataset, batch_size)
             return
         ops = [self.tower_coord_grads, self.tower_mos, self.tower_bids]
@@ -445,25 +446,54 @@ class TrainerMultiTower:
                 # one (n_atoms, 3) array per batch, cut once into per-molecule pieces
                 yield from np.split(np.stack(grads[k], axis=1), mos[k][1:])
 
-    def _evaluator_gradients(self, dataset, batch_size):
+    def _evaluator_usable(self, dataset) -> bool:
+        """One float32 CUDA tower with the fused networks: batches can go through the
+        allocation-free evaluator (``khan_b200.inference.EnergyForces``)."""
+        return (self.num_towers == 1 and self.precision == torch.float32 and self.model.fused
+                and self.towers[0].type == "cuda" and dataset.num_mols() > 0)
+
+    def _evaluator(self, packed, batch_size):
         from ..inference import EnergyForces
         from ..staged import StagedBatch
-        packed = PackedDataset.from_raw(dataset, np.float32)
         cap_atoms, cap_mols = (max(v, 1) for v in packed.capacity(batch_size))
         dev = self.towers[0]
         cached = getattr(self, "_infer", None)
         if cached is None or cached[0][0] < cap_atoms or cached[0][1] < cap_mols:
             self._infer = cached = ((cap_atoms, cap_mols), StagedBatch(cap_atoms, cap_mols, device=dev),
                                     EnergyForces(self.model, cap_atoms, cap_mols, device=dev))
-        _, sb, ev = cached
+        return cached[1], cached[2]
+
+    def _evaluator_predictions(self, dataset, batch_size):
+        """``_device_predictions`` through the evaluator: sort, featurize, networks forward and the
+        molecule sums as four C-ABI calls per batch, the weights packed once."""
+        packed = PackedDataset.from_raw(dataset, np.float32)
+        sb, ev = self._evaluator(packed, batch_size)
+        it = BatchFeeder(packed, batch_size, False, None, devices=self.towers, depth=2, hold=1)
+        preds, l2s = [], []
+        try:
+            with torch.cuda.device(self.towers[0]), torch.no_grad():
+                for k, fed in enumerate(it):
+                    fed.wait()
+                    sb.adopt(fed)
+                    ev.run(sb, pack=(k == 0), forces=False)
+                    preds.append(ev.mol_energy[:fed.n_mols].clone())
+                    if fed.ys is not None:
+                        l2s.append((preds[-1] - fed.ys) ** 2)
+        finally:
+            it.close()
+        return preds, l2s
+
+    def _evaluator_gradients(self, dataset, batch_size):
+        packed = PackedDataset.from_raw(dataset, np.float32)
+        sb, ev = self._evaluator(packed, batch_size)
         it = BatchFeeder(packed, batch_size, False, None, devices=self.towers, depth=2, hold=1)
         done = []
         try:
-            with torch.cuda.device(dev), torch.no_grad():
+            with torch.cuda.device(self.towers[0]), torch.no_grad():
                 for fed in it:
                     fed.wait()
                     sb.adopt(fed)
-                    ev.run(sb)
+                    ev.run(sb, pack=(len(done) == 0))
                     done.append((sb.grads[:, :fed.n_atoms].t().contiguous(), fed.offsets_host))   # (n_atoms, 3), on the device
         finally:
             it.close()
