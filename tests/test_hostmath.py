@@ -70,3 +70,14 @@ def test_ed_harder_rmse_known_answer():
     from khan_b200.utils import ed_harder_rmse
     want = (math.sqrt(4 / 3) + math.sqrt((9 + 9 + 0 + 16) / 4)) / 2
     assert abs(ed_harder_rmse([[2, 1, 3], [8, 9, 2, 3]], [3, 0, 2, 7, 8, 4, 1]) - want) < 1e-15
+
+
+def test_split_rows_equals_numpy_split():
+    from khan_b200.training.trainer_multi_tower import _split_rows
+    rng = np.random.default_rng(8)
+    counts = rng.integers(0, 9, 200)
+    offsets = (np.cumsum(counts) - counts).astype(np.int32)
+    rows = rng.normal(size=(int(counts.sum()), 3))
+    got, want = _split_rows(rows, offsets), np.split(rows, offsets[1:])
+    assert len(got) == len(want) == 200
+    assert all(np.array_equal(a, b) for a, b in zip(got, want))
