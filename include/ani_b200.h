@@ -9,8 +9,11 @@
  *
  * Conventions (all entry points):
  *  - every pointer is a DEVICE pointer unless the name ends in `_host`;
- *  - outputs are caller-allocated and fully written by the call: no pre-zeroing is needed
- *    (the reference zero-fills inside its functors, gpu_featurizer/functor_op_cpu.cpp:31-34);
+ *  - outputs are caller-allocated and, for every atom that a molecule range covers, fully
+ *    written by the call: no pre-zeroing is needed (the reference zero-fills inside its
+ *    functors, gpu_featurizer/functor_op_cpu.cpp:31-34).  Entries of atoms that belong to no
+ *    molecule range are left as they were (feature rows) or unspecified (gradients): zero the
+ *    arrays first if the molecule table does not cover the whole batch;
  *  - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = default stream)
  *    and the call returns without synchronising;
  *  - the return value is 0 (ANI_OK) or a negative ANI_ERR_* code; nothing calls exit()
@@ -136,6 +139,9 @@ int ani_featurize_f64(const double* xs, const double* ys, const double* zs,
  * AniCombinedGrad::Compute (gpu_featurizer/ani_op.cpp:129-196).  The reference has no GPU
  * kernel for this op (ani_op.cpp:339-340).  Vector-Jacobian product: given dL/dfeatures in
  * the four per-element buffers, writes dL/dx, dL/dy, dL/dz [n_atoms].
+ * Batches of small molecules (mean size <= 24 atoms) with 16-byte aligned grad_* buffers run one
+ * CTA per molecule, every output written once and bit-reproducible from run to run; other
+ * batches are accumulated with floating-point atomics (last bits may differ between runs).
  */
 int ani_featurize_grad_f32(const float* xs, const float* ys, const float* zs,
                            const int* atomic_numbers, const int* mol_offsets,

@@ -117,7 +117,11 @@ def featurize(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, scatter_
 
 def featurize_grad(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, scatter_idxs, acs,
                    h_grads, c_grads, n_grads, o_grads):
-    """FeaturizeGrad: returns ``x_grads, y_grads, z_grads`` (``[n_atoms]`` each)."""
+    """FeaturizeGrad: returns ``x_grads, y_grads, z_grads`` (``[n_atoms]`` each).
+
+    The arrays start as zeros, so an atom that no molecule range covers gets a zero gradient, as
+    in the reference (gpu_featurizer/functor_op_cpu.cpp:70-72); the C entry point itself writes
+    only the atoms of the molecules it is given."""
     xs, ys, zs, a, mo, mac, si = _common(xs, ys, zs, atomic_numbers, mol_offsets,
                                          mol_atom_counts, scatter_idxs)
     suf = _suffix(xs)
@@ -131,7 +135,7 @@ def featurize_grad(xs, ys, zs, atomic_numbers, mol_offsets, mol_atom_counts, sca
                              f"{int(acs_host[t]) * FEATURE_SIZE}")
         gs.append(g)
     with torch.cuda.device(xs.device):
-        outs = torch.empty((3, n_atoms), dtype=xs.dtype, device=xs.device)
+        outs = torch.zeros((3, n_atoms), dtype=xs.dtype, device=xs.device)
         fn = getattr(_lib.lib(), "ani_featurize_grad_" + suf)
         _lib.check(fn(_p(xs), _p(ys), _p(zs), _p(a), _p(mo), _p(mac), mo.numel(), _p(si),
                       *[_p(g) for g in gs], _p(outs[0]), _p(outs[1]), _p(outs[2]),

@@ -12,7 +12,9 @@
 #include "ani_common.cuh"
 
 #include "ani_featurize.cuh"
+#include "ani_featurize_mol.cuh"
 #include "ani_grad.cuh"
+#include "ani_grad_mol.cuh"
 #include "ani_grad_inverse.cuh"
 #include "ani_mlp_forward.cuh"
 #include "ani_mlp_backward.cuh"
@@ -138,10 +140,6 @@ int pick_slot_shift(long long n_atoms, int n_mols)
     int shift = 0;
     while ((1 << shift) < kNW) shift++;   // at least one slot per warp of a CTA
     while ((1 << shift) < mean && (1 << shift) < kSlotsPerMol) shift++;
-#ifdef ANI_TUNING
-    if (const char* e = getenv("ANI_SLOT_SHIFT")) shift = atoi(e);
-    if (const char* e = getenv("ANI_SLOT_MAJOR")) return shift | (atoi(e) ? kSlotMajorFlag : 0);
-#endif
     return shift | (mean <= kSlotsPerMol ? kSlotMajorFlag : 0);
 }
 
@@ -149,6 +147,24 @@ template <typename K> int set_smem(K kernel, size_t bytes)
 {
     ANI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     return ANI_OK;
+}
+
+// Batches whose MEAN molecule size is at most this take the one-CTA-per-molecule kernels (their
+// fast path covers molecules of up to kMolMaxAtoms atoms; a larger molecule in such a batch is
+// still handled, slowly).  Batches of larger molecules take the one-warp-per-atom kernels.
+constexpr int kMolMeanLimit = 24;
+#ifndef ANI_MOL_GRAD_WARPS
+#define ANI_MOL_GRAD_WARPS 4
+#endif
+constexpr int kMolGradWarps = ANI_MOL_GRAD_WARPS;   // warps of a CTA (= molecule) of the small-molecule gradient kernel
+bool small_molecules(long long n_atoms, int n_mols) { return n_mols > 0 && n_atoms <= (long long)n_mols * kMolMeanLimit; }
+
+// True when every non-null pointer of the list is 16-byte aligned.
+bool all_aligned16(std::initializer_list<const void*> ptrs)
+{
+    for (const void* q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) & 15) return false;
+    return true;
 }
 
 int check_acs(const int* acs_host, long long* n_atoms)
@@ -178,11 +194,22 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
     for (int t = 0; t < kTypes; t++)
         if (acs_host[t] > 0 && !outs[t]) return ANI_ERR_NULL_POINTER;
 
+    int dev = 0;
+    ANI_CUDA(cudaGetDevice(&dev));
+    // small molecules with outputs that take 16-byte stores: one warp (= one CTA) per round of four
+    // central atoms
+    if (small_molecules(n_atoms, n_mols) && all_aligned16({oh, oc, on, oo}) &&
+        (long long)n_mols * kMolRounds <= 0x7fffffffLL) {
+        featurize_mol_kernel<T><<<n_mols * kMolRounds, kWarp, 0, (cudaStream_t)stream>>>(
+            xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, oh, oc, on, oo, acs_host[0], acs_host[1],
+            acs_host[2], acs_host[3]);
+        ANI_CUDA(cudaGetLastError());
+        return ANI_OK;
+    }
+
     auto kernel = featurize_kernel<T, kNW, CAPT, CAPR>;
     const size_t smem = kNW * sizeof(FeaturizeWarpShared<T, CAPT, CAPR>);
     static thread_local int configured_dev = -1;
-    int dev = 0;
-    ANI_CUDA(cudaGetDevice(&dev));
     if (configured_dev != dev) {
         if (int rc = set_smem(kernel, smem)) return rc;
         configured_dev = dev;
@@ -194,10 +221,7 @@ int featurize_impl(const T* xs, const T* ys, const T* zs, const int* types, cons
     }
     const int slot_shift = pick_slot_shift(n_atoms, n_mols);
     const long long needed = (long long)n_mols * ((1 << (slot_shift & 31)) / kNW);
-    int grid = (int)(needed < cached_resident ? needed : cached_resident);
-#ifdef ANI_PHASE_TIMING
-    if (getenv("ANI_DEBUG_FULL_GRID")) grid = (int)needed;   // tuning builds: one item per warp
-#endif
+    const int grid = (int)(needed < cached_resident ? needed : cached_resident);
     kernel<<<grid, kNW * kWarp, smem, (cudaStream_t)stream>>>(
         xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, slot_shift, sis, oh, oc, on, oo, acs_host[0],
         acs_host[1], acs_host[2], acs_host[3]);
@@ -217,6 +241,28 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
     if (n_atoms == 0) return ANI_OK;
     if (!gx || !gy || !gz) return ANI_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
+    const T* gin[kTypes] = {gh, gc, gn, go};
+    // One CTA per molecule when the molecules are small and the upstream rows can be fetched with
+    // 16-byte copies: writes every output itself, so no zero fill.
+    if (n_mols > 0 && small_molecules(n_atoms, n_mols) && all_aligned16({gh, gc, gn, go})) {
+        if (!xs || !ys || !zs || !types || !mos || !macs || !sis) return ANI_ERR_NULL_POINTER;
+        for (int t = 0; t < kTypes; t++)
+            if (acs_host[t] > 0 && !gin[t]) return ANI_ERR_NULL_POINTER;
+        auto mol_kernel = featurize_grad_mol_kernel<T, kMolGradWarps>;
+        const size_t mol_smem = mol_grad_smem_bytes<T, kMolGradWarps>();
+        static thread_local int mol_configured_dev = -1;
+        int dev = 0;
+        ANI_CUDA(cudaGetDevice(&dev));
+        if (mol_configured_dev != dev) {
+            if (int rc = set_smem(mol_kernel, mol_smem)) return rc;
+            mol_configured_dev = dev;
+        }
+        mol_kernel<<<n_mols, kMolGradWarps * kWarp, mol_smem, st>>>(xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, gh,
+                                                          gc, gn, go, gx, gy, gz, acs_host[0], acs_host[1],
+                                                          acs_host[2], acs_host[3]);
+        ANI_CUDA(cudaGetLastError());
+        return ANI_OK;
+    }
     {
         const int threads = 256;
         long long blocks = (n_atoms + threads - 1) / threads;
@@ -226,7 +272,6 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
     }
     if (n_mols == 0) return ANI_OK;
     if (!xs || !ys || !zs || !types || !mos || !macs || !sis) return ANI_ERR_NULL_POINTER;
-    const T* gin[kTypes] = {gh, gc, gn, go};
     for (int t = 0; t < kTypes; t++)
         if (acs_host[t] > 0 && !gin[t]) return ANI_ERR_NULL_POINTER;
 
@@ -385,15 +430,6 @@ template <bool SPLIT> int mlp_wgrad_launch(const MlpWgradParams& p, int n_ranges
     return ANI_OK;
 }
 
-// True when every non-null pointer of the list is 16-byte aligned (the atomic-network kernels use
-// 16-byte accesses on all of their matrices).
-bool all_aligned16(std::initializer_list<const void*> ptrs)
-{
-    for (const void* q : ptrs)
-        if (reinterpret_cast<uintptr_t>(q) & 15) return false;
-    return true;
-}
-
 template <int ACT> int mlp_launch_act(const MlpParams& p, int n_tiles, bool split, cudaStream_t st)
 {
     return split ? mlp_launch<ACT, true>(p, n_tiles, st) : mlp_launch<ACT, false>(p, n_tiles, st);
@@ -439,18 +475,6 @@ const char* ani_status_string(int status)
 }
 
 const char* ani_last_cuda_error(void) { return cudaGetErrorString(t_last_error); }
-
-#ifdef ANI_PHASE_TIMING
-// Tuning builds only: copies out and clears the per-phase cycle counters (16 values).
-int ani_debug_phase_cycles(unsigned long long* out_host)
-{
-    ANI_CUDA(cudaDeviceSynchronize());
-    ANI_CUDA(cudaMemcpyFromSymbol(out_host, ani::g_phase_cycles, 16 * sizeof(unsigned long long)));
-    unsigned long long zero[16] = {0};
-    ANI_CUDA(cudaMemcpyToSymbol(ani::g_phase_cycles, zero, sizeof(zero)));
-    return ANI_OK;
-}
-#endif
 
 int ani_fma_probe(int precision_bits, int iterations, void* sink, long long* flops_host, void* stream)
 {

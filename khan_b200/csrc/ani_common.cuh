@@ -31,45 +31,6 @@ __device__ int g_status = 0;
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_status, 0, code); }
 
-// Optional per-phase cycle accounting (compiled in only with -DANI_PHASE_TIMING, for tuning):
-// every warp adds the cycles it spent between consecutive marks to g_phase_cycles[phase].
-#ifdef ANI_PHASE_TIMING
-__device__ unsigned long long g_phase_cycles[16];
-__device__ __forceinline__ long long now_cycles()
-{
-    long long t;
-    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
-    return t;
-}
-struct PhaseClock {
-    long long last;
-    unsigned long long acc[16];
-    __device__ __forceinline__ PhaseClock() : last(now_cycles())
-    {
-        for (int k = 0; k < 16; k++) acc[k] = 0;
-    }
-    __device__ __forceinline__ void mark(int k)
-    {
-        const long long now = now_cycles();
-        acc[k] += (unsigned long long)(now - last);
-        last = now;
-    }
-    __device__ __forceinline__ void flush()
-    {
-        if ((threadIdx.x & 31) == 0)
-            for (int k = 0; k < 16; k++)
-                if (acc[k]) atomicAdd(&g_phase_cycles[k], acc[k]);
-    }
-};
-#define ANI_PHASE_DECL PhaseClock phase_clock
-#define ANI_PHASE(k) phase_clock.mark(k)
-#define ANI_PHASE_FLUSH phase_clock.flush()
-#else
-#define ANI_PHASE_DECL
-#define ANI_PHASE(k)
-#define ANI_PHASE_FLUSH
-#endif
-
 __device__ __forceinline__ int lane_id() { return threadIdx.x & (kWarp - 1); }
 __device__ __forceinline__ int warp_id() { return threadIdx.x >> 5; }
 __device__ __forceinline__ unsigned lanemask_lt()

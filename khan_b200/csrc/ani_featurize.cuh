@@ -106,9 +106,6 @@ __device__ __noinline__ void featurize_atom_streaming(const T* __restrict__ xs,
     for (int b = 0; b < kPairBuckets; b++) row[kRadial + b * kTS + lane] = acc[b];
 }
 
-#ifndef ANI_ABLATE
-#define ANI_ABLATE 0   // tuning builds only: bit mask of phases to leave out (results are wrong)
-#endif
 #ifndef ANI_FWD_MIN_CTAS
 #define ANI_FWD_MIN_CTAS 8
 #endif
@@ -126,7 +123,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
 
-    ANI_PHASE_DECL;
     // The angular list is read at entry 0 by padding lanes and may be read before this warp
     // ever wrote it: give every entry a finite value once.
     for (int e = lane; e < kTypes * CAPT; e += kWarp) {
@@ -134,7 +130,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
         ws.ang_fc[e] = (T)0;
     }
     __syncwarp();
-    ANI_PHASE(14);
 
     __shared__ int cta_next_item;
     if (threadIdx.x == 0) cta_next_item = 0;
@@ -142,10 +137,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
     for (;;) {
         int m, slot;
         if (!next_work<NW>(&cta_next_item, n_mols, slot_shift & 31, (slot_shift & 32) != 0, &m, &slot)) break;
-        const int n_of_m = mol_counts[m];
-        if (n_of_m < 0) report(ANI_ERR_BAD_INDEX);   // forces the load to complete here in timing builds
-        ANI_PHASE(15);
-        if (slot >= n_of_m) continue;   // empty item: one cached load
+        if (slot >= mol_counts[m]) continue;   // empty item: one cached load
         MolRange mol;
         if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
         const int n = mol.n, base = mol.base;
@@ -165,7 +157,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
                 continue;
             }
             T* row = element_buffer<T>(ti, out_h, out_c, out_n, out_o) + (size_t)srow * kTotal;
-            ANI_PHASE(0);
 
             // ---- A: neighbour scan, lane = j ----
             int cA[kTypes] = {0, 0, 0, 0}, cR[kTypes] = {0, 0, 0, 0};
@@ -216,10 +207,8 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
                 continue;
             }
 
-            ANI_PHASE(1);
             // ---- R: radial features, lane = (element of the neighbour, pair of shifts): every lane
             // walks the radial sub-list of its element and finishes two of the 64 features ----
-#if !(ANI_ABLATE & 1)
             {
                 const int g = lane >> 3, sp = lane & 7;
                 const Pair<T> neg_shift{-(T)c_tab.R_Rs[2 * sp], -(T)c_tab.R_Rs[2 * sp + 1]};
@@ -237,18 +226,9 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
                 }
                 *reinterpret_cast<Vec2<T>*>(row + g * kNumRs + 2 * sp) = Vec2<T>{acc.x, acc.y};
             }
-#endif
 
-            ANI_PHASE(2);
             // ---- B + C: angular features ----
-#if ANI_ABLATE & 2
-            const int total = (cA[0] + cA[1] + cA[2] + cA[3]) * 0;
-            if (lane < 12) ws.pt.off[lane] = 0;
-            __syncwarp();
-#else
             const int total = build_pair_tables<CAPT>(ws.pt, cA);
-#endif
-            ANI_PHASE(3);
             if (total > kMaxPaddedPairs) {   // more pairs than the bucket table covers: slow path
                 featurize_atom_streaming<T>(xs, ys, zs, types, base, n, i, row);
                 __syncwarp();
@@ -262,7 +242,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
                 if (ws.pt.off[bk + 1] == ws.pt.off[bk]) row[kRadial + bk * kTS + lane] = (T)0;
             Pair<T> acc{(T)0, (T)0};
             for (int c0 = 0; c0 < total; c0 += kWarp) {
-#if !(ANI_ABLATE & 4)
                 {   // B: lane = pair
                     int bk, a, b;
                     const bool valid = decode_pair(ws.pt, c0 + lane, &bk, &a, &b);
@@ -277,10 +256,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
 #pragma unroll
                     for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = BF[q];
                 }
-#endif
                 __syncwarp();
-                ANI_PHASE(4);
-#if !(ANI_ABLATE & 8)
                 {   // C: lane = (theta, shift).  All 8 quads of the chunk, fully unrolled (slots past
                     // the end of the list hold zeros).  A block is written when the next quad belongs
                     // to another element pair; ids[8] is the first quad of the next chunk.
@@ -302,15 +278,10 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
                         }
                     }
                 }
-#endif
                 __syncwarp();
-                ANI_PHASE(5);
             }
-            ANI_PHASE(6);
         }
     }
-    ANI_PHASE(7);
-    ANI_PHASE_FLUSH;
 }
 
 }  // namespace ani

@@ -1,0 +1,396 @@
+// Forward kernel for batches of small molecules (at most 32 atoms each, the size range of the
+// data sets khan trains on: its loaders drop larger molecules, data_utils.py:54,281-283).
+//
+// The central atoms of a molecule, in element order, are cut into ROUNDS of four consecutive
+// atoms, and a CTA is ONE WARP doing one round: a molecule has 8 CTAs (8 rounds, 32 atoms), a
+// CTA whose round lies behind the end of the molecule leaves after one load.  No warp needs
+// anything from another, every round gives its registers and shared memory back as soon as it
+// is done, and the rounds of a large molecule spread over the SMs.  A warp keeps the whole
+// molecule in registers, lane = atom:
+//   0. every lane loads one atom; the atoms are ranked by element with four ballots and moved to
+//      their rank by shuffles, so that lane order = element order and every neighbour list that
+//      is compacted in lane order comes out sorted by element for free;
+//   A. per central atom of the round (coordinates by shuffle): one distance per lane; (r, f_C)
+//      of every atom of the molecule goes to a table (f_C = 0 beyond R_Rc), and the neighbours
+//      within A_Rc, compacted by a ballot, to the list (unit vector, r, f_C) of this central atom;
+//   R. the radial features of all central atoms of the round at once: lane = (central atom,
+//      pair of radial shifts) walks the table of its central atom.  The table is in element
+//      order for every central atom alike, so the loops over the four element runs are uniform
+//      and the 2 x 4 sums of a lane stay in registers; four 8-byte stores per lane;
+//   T. ONE table of all (central atom, element pair) groups of the round: start, size and list
+//      bases of each group, every group padded to a multiple of four slots;
+//   B. lane = slot, 32 slots at a time over the groups of ALL central atoms of the round (so the
+//      lanes stay filled although one atom has only some 50 neighbour pairs): 8 theta factors and
+//      4 radial factors of each triplet into shared memory.  A slot is decoded without a branch
+//      and without a division: pairs of different elements are numbered row-major, pairs of
+//      one element in circulant order (a, a + d), which is row-major in (d, a);
+//   C. lane = (theta, shift): acc += A[theta][slot] * BF[shift][slot], four slots per pair of
+//      16-byte loads; a 32-float block of a feature row is written when its group ends (the
+//      ends inside a chunk come from one ballot).
+// Nothing is accumulated with atomics and no row needs a zero fill by the caller; results do
+// not depend on the launch shape.
+//
+// A molecule with more than 32 atoms met by this kernel (the host picks it from the MEAN
+// molecule size) and a central atom with more than 24 neighbours within A_Rc go through the
+// streaming routine of ani_featurize.cuh.
+//
+// Computes what featurize_cpu of the reference computes (gpu_featurizer/kernel_cpu.cpp:406-537).
+#pragma once
+
+#include "ani_common.cuh"
+#include "ani_featurize.cuh"
+
+namespace ani {
+
+constexpr int kMolMaxAtoms = 32;       // molecules up to this size take the fast path
+constexpr int kMolCentrals = 4;        // central atoms per round
+constexpr int kMolCapA = 24;           // angular neighbours kept per central atom
+constexpr int kMolGroupStride = 16;    // group id = central slot * 16 + element-pair bucket
+constexpr int kMolNoGroup = 0xff;      // id of the quads behind the last group
+constexpr int kMolRounds = kMolMaxAtoms / kMolCentrals;   // rounds of the largest molecule of the fast path
+// padded slots of one central atom: at most CapA (CapA - 1) / 2 pairs + 3 per bucket, in quads
+constexpr int kMolQuadsPerCentral = (kMolCapA * (kMolCapA - 1) / 2 + 3 * kPairBuckets) / 4 + 1;
+constexpr int kMolQuadBytes = ((kMolCentrals * kMolQuadsPerCentral + 8 + 8 + 7) / 8) * 8;
+
+struct alignas(16) MolGroupInfo {
+    int off;         // first slot of the group (a multiple of 4)
+    int cnt;         // triplets in the group
+    int packed;      // list index of the first neighbour of element a | same for b << 8 | size of run b << 16 | a == b << 24
+    unsigned recip;  // ceil(2^16 / size of run b): q / nb == (q * recip) >> 16 for every slot number q in use
+};
+
+// Per warp: what the element sort leaves behind for the rest of the molecule's work.
+struct MolSortShared {
+    alignas(16) unsigned tmask[kTypes];   // lanes of each element after the sort
+    int srow[kMolMaxAtoms];               // scatter index of the atom in each lane
+    unsigned char src[kMolMaxAtoms];      // index inside the molecule of the atom in each lane
+};
+
+
+template <typename T> struct MolFwdWarpShared {
+    Vec4<T> ang_u[kMolCentrals * kMolCapA];   // (x_i - x_j) / r_ij and r_ij, element order, per central atom
+    T ang_fc[kMolCentrals * kMolCapA];        // f_C(r_ij, A_Rc)
+    Vec2<T> rad[kMolCentrals][kMolMaxAtoms];  // (r_ij, f_C(r_ij, R_Rc) or 0) of every atom j, per central atom
+    alignas(16) T A[kNumThetas][kPadStride];
+    alignas(16) T BF[kNumARs][kPadStride];
+    MolGroupInfo tab[kMolCentrals * kMolGroupStride];
+    T* row[kMolCentrals];                     // feature row of each central atom of the round
+    alignas(16) int cnt_a[kMolCentrals * kTypes];   // angular neighbours per element, per central atom
+    alignas(8) unsigned char quad_gid[kMolQuadBytes];
+    MolSortShared sort;
+};
+
+__device__ __forceinline__ unsigned low_lanes(int c) { return c >= 32 ? 0xffffffffu : ((1u << c) - 1u); }
+
+// One molecule's atom per lane, moved into element order; lanes >= n hold copies of dead lanes.
+// What is needed once per central atom only sits in the warp's shared memory instead.
+template <typename T> struct MolLanes {
+    T x, y, z;
+    int type;          // 0..3 (4 on dead lanes)
+};
+
+template <typename T>
+__device__ __forceinline__ void load_sorted_molecule(const T* __restrict__ xs, const T* __restrict__ ys,
+                                                     const T* __restrict__ zs, const int* __restrict__ types,
+                                                     const int* __restrict__ scatter, int base, int n,
+                                                     MolSortShared* sh, MolLanes<T>* out)
+{
+    unsigned char* inv = sh->src;
+    const int lane = lane_id();
+    const bool live = lane < n;
+    const int gj = base + (live ? lane : 0);
+    const T x0 = xs[gj], y0 = ys[gj], z0 = zs[gj];
+    const int s0 = scatter[gj];
+    const int t0 = live ? checked_type(types[gj]) : kTypes;
+    const unsigned m0 = __ballot_sync(kFull, t0 == 0), m1 = __ballot_sync(kFull, t0 == 1),
+                   m2 = __ballot_sync(kFull, t0 == 2), m3 = __ballot_sync(kFull, t0 == 3);
+    const int c0 = __popc(m0), c1 = __popc(m1), c2 = __popc(m2);
+    const unsigned mine = t0 == 0 ? m0 : (t0 == 1 ? m1 : (t0 == 2 ? m2 : (t0 == 3 ? m3 : ~(m0 | m1 | m2 | m3))));
+    const int start = t0 == 0 ? 0 : (t0 == 1 ? c0 : (t0 == 2 ? c0 + c1 : (t0 == 3 ? c0 + c1 + c2 : n)));
+    const int rank = start + __popc(mine & lanemask_lt());
+    __syncwarp();   // the previous molecule's readers are done
+    inv[rank] = (unsigned char)lane;
+    sh->srow[rank] = s0;
+    if (lane == 0) {
+        sh->tmask[0] = low_lanes(c0);
+        sh->tmask[1] = low_lanes(c0 + c1) & ~low_lanes(c0);
+        sh->tmask[2] = low_lanes(c0 + c1 + c2) & ~low_lanes(c0 + c1);
+        sh->tmask[3] = low_lanes(n) & ~low_lanes(c0 + c1 + c2);
+    }
+    __syncwarp();
+    const int src = inv[lane];
+    out->x = __shfl_sync(kFull, x0, src);
+    out->y = __shfl_sync(kFull, y0, src);
+    out->z = __shfl_sync(kFull, z0, src);
+    out->type = __shfl_sync(kFull, t0, src);
+}
+
+// Slot p of the round -> list indices (a, b) of its two neighbours.  Returns false for a
+// padding slot (a and b then point at entry 0 of the list, which always holds finite values).
+// Slot number q inside a group: different elements, q = ia * nb + ib; one element, q = (d - 1) * nb + a
+// with b = a + d mod nb (d <= nb / 2; the last row of an even nb holds only a < nb / 2).
+__device__ __forceinline__ bool decode_slot(const MolGroupInfo* tab, const unsigned char* quad_gid, int p,
+                                            int* a, int* b)
+{
+    const int gid = quad_gid[p >> 2];
+    const MolGroupInfo e = tab[gid == kMolNoGroup ? 0 : gid];
+    const int q = p - e.off;
+    const bool valid = gid != kMolNoGroup && q < e.cnt;
+    const int nb = (e.packed >> 16) & 0xff;
+    const bool same = (e.packed >> 24) != 0;
+    const int hi = (int)(((unsigned)q * e.recip) >> 16);   // q / nb
+    const int lo = q - hi * nb;                            // q % nb
+    int wrap = lo + hi + 1;
+    if (wrap >= nb) wrap -= nb;
+    const int ia = same ? lo : hi, ib = same ? wrap : lo;
+    *a = valid ? (e.packed & 0xff) + ia : 0;
+    *b = valid ? ((e.packed >> 8) & 0xff) + ib : 0;
+    return valid;
+}
+
+// The 8 theta factors and 4 radial factors of one triplet (see angular_factors in ani_params.h),
+// arranged for the device: every constant is an immediate operand of a scalar instruction and
+// only the squarings run as packed pairs.
+template <typename T> __device__ __forceinline__ void angular_factors_dev(T cosv, T rbar, T fcprod, T* A, T* BF)
+{
+    const T c = Num<T>::max_((T)-1, Num<T>::min_((T)1, cosv));
+    const T s = Num<T>::sqrt_(Num<T>::max_((T)0, (T)1 - c * c));
+    T b[kNumThetas];
+#pragma unroll
+    for (int t = 0; t < kNumThetas; t++) b[t] = c * theta_cos<T>(t) + (s * theta_sin<T>(t) + (T)1);
+#pragma unroll
+    for (int t = 0; t < kNumThetas; t += 2) {
+        const Pair<T> b1{b[t], b[t + 1]};
+        const Pair<T> b2 = pmul(b1, b1);
+        const Pair<T> b4 = pmul(b2, b2);
+        const Pair<T> b8 = pmul(b4, b4);
+        A[t] = b8.x;
+        A[t + 1] = b8.y;
+    }
+    const T f = (T)kA_pref * fcprod;
+    T d[kNumARs];
+#pragma unroll
+    for (int q = 0; q < kNumARs; q++) d[q] = rbar - angular_shift<T>(q);
+#pragma unroll
+    for (int q = 0; q < kNumARs; q += 2) {
+        const Pair<T> dd{d[q], d[q + 1]};
+        const Pair<T> d2 = pmul(dd, dd);
+        const Pair<T> bf = pmul(Pair<T>{Num<T>::exp_neg((T)kA_eta, d2.x), Num<T>::exp_neg((T)kA_eta, d2.y)}, Pair<T>{f, f});
+        BF[q] = bf.x;
+        BF[q + 1] = bf.y;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
+    featurize_mol_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
+                         const int* __restrict__ types, const int* __restrict__ mol_offsets,
+                         const int* __restrict__ mol_counts, int n_mols, int n_atoms,
+                         const int* __restrict__ scatter, T* out_h, T* out_c, T* out_n, T* out_o,
+                         int acs0, int acs1, int acs2, int acs3)
+{
+    __shared__ MolFwdWarpShared<T> ws;
+    using Granule = Vec4<float>;                      // 16 bytes of zeros, whatever T is
+    constexpr int kPerGranule = 16 / (int)sizeof(T);  // values in a granule
+    const int lane = lane_id();
+
+    // Round-major order of the grid: all first rounds (every molecule has one), then all second rounds, ...
+    // so the work that exists starts first and is spread evenly over the SMs, and the CTAs of rounds that
+    // most molecules do not have come last.
+    const int round = blockIdx.x / n_mols, m = blockIdx.x - round * n_mols;
+    MolRange mol;
+    if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) return;
+    const int n = mol.n, base = mol.base;
+
+    if (n > kMolMaxAtoms) {   // a large molecule in a batch of small ones: its CTAs take one atom at a time
+        for (int i = round; i < n; i += kMolRounds) {
+            const int gi = base + i;
+            const int ti = checked_type(types[gi]);
+            const int srow = scatter[gi];
+            const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
+            if (srow < 0 || srow >= cap) {
+                if (lane == 0) report(ANI_ERR_BAD_INDEX);
+                continue;
+            }
+            featurize_atom_streaming<T>(xs, ys, zs, types, base, n, i,
+                                        element_buffer<T>(ti, out_h, out_c, out_n, out_o) + (size_t)srow * kTotal);
+            __syncwarp();
+        }
+        return;
+    }
+    const int c_first = round * kMolCentrals;
+    if (c_first >= n) return;
+    const int G = min(kMolCentrals, n - c_first);
+
+    MolLanes<T> ml;
+    load_sorted_molecule<T>(xs, ys, zs, types, scatter, base, n, &ws.sort, &ml);
+
+    // Padding slots read entry 0 of the angular list, possibly before anything was written there.
+    if (lane == 0) {
+        ws.ang_u[0] = Vec4<T>{(T)1, (T)0, (T)0, (T)1};
+        ws.ang_fc[0] = (T)0;
+    }
+    if (lane < kMolCentrals * kTypes) ws.cnt_a[lane] = 0;
+    __syncwarp();
+
+    // ---- A: scan, one central atom after another ----
+    unsigned skip = 0;   // central atoms that are finished (streaming routine) or refused
+    for (int g = 0; g < G; g++) {
+        const int c = c_first + g;
+        const T xi = __shfl_sync(kFull, ml.x, c), yi = __shfl_sync(kFull, ml.y, c), zi = __shfl_sync(kFull, ml.z, c);
+        const int ti = __shfl_sync(kFull, ml.type, c);
+        const int srow = ws.sort.srow[c];
+        const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
+        if (srow < 0 || srow >= cap) {
+            if (lane == 0) report(ANI_ERR_BAD_INDEX);
+            skip |= 1u << g;
+            continue;
+        }
+        T* row = element_buffer<T>(ti, out_h, out_c, out_n, out_o) + (size_t)srow * kTotal;
+        if (lane == 0) ws.row[g] = row;
+
+        const T dx = xi - ml.x, dy = yi - ml.y, dz = zi - ml.z;
+        T r, inv;
+        length_and_inverse(dx * dx + dy * dy + dz * dz, &r, &inv);
+        const bool in_rad = lane < n && lane != c && r < (T)kR_Rc;
+        const bool in_ang = in_rad && r < (T)kA_Rc;
+        const unsigned mA = __ballot_sync(kFull, in_ang);
+        if (__popc(mA) > kMolCapA) {   // denser than the list: the streaming routine does the whole row
+            featurize_atom_streaming<T>(xs, ys, zs, types, base, n, ws.sort.src[c], row);
+            skip |= 1u << g;
+            __syncwarp();
+            continue;
+        }
+        // the angular blocks start as zeros (16-byte stores: 2.5 per lane); pass C writes the blocks of
+        // the element pairs that occur, after a __syncwarp, so the order of the two is fixed
+        {
+            Granule* zero = reinterpret_cast<Granule*>(row + kRadial);
+            constexpr int kGranules = kAngular / kPerGranule;
+#pragma unroll
+            for (int i = 0; i < (kGranules + kWarp - 1) / kWarp; i++)
+                if (i * kWarp + lane < kGranules) zero[i * kWarp + lane] = Granule{0.f, 0.f, 0.f, 0.f};
+        }
+        ws.rad[g][lane] = Vec2<T>{r, in_rad ? cutoff_value<T>(r, (T)kR_Rc) : (T)0};
+        if (in_ang) {
+            const int p = g * kMolCapA + __popc(mA & lanemask_lt());
+            ws.ang_u[p] = Vec4<T>{dx * inv, dy * inv, dz * inv, r};
+            ws.ang_fc[p] = cutoff_value<T>(r, (T)kA_Rc);
+        }
+        if (lane < kTypes) ws.cnt_a[g * kTypes + lane] = __popc(mA & ws.sort.tmask[lane]);
+    }
+    __syncwarp();
+
+    // ---- R: radial features of the whole round, lane = (central atom, pair of shifts) ----
+    {
+        const int g = lane >> 3, sp = lane & 7;
+        const Vec2<T>* list = ws.rad[g];
+        const T sh0 = (T)c_tab.R_Rs[2 * sp], sh1 = (T)c_tab.R_Rs[2 * sp + 1];
+        const uint4 tmq = *reinterpret_cast<const uint4*>(ws.sort.tmask);
+        const int run_end[kTypes] = {__popc(tmq.x), __popc(tmq.x | tmq.y), __popc(tmq.x | tmq.y | tmq.z), n};
+        Pair<T> acc[kTypes];
+        int p = 0;
+#pragma unroll
+        for (int t = 0; t < kTypes; t++) {
+            acc[t] = Pair<T>{(T)0, (T)0};
+            for (; p < run_end[t]; p++) {
+                const Vec2<T> e = list[p];
+                const Pair<T> d{e.x - sh0, e.x - sh1};
+                const Pair<T> d2 = pmul(d, d);
+                const Pair<T> v{Num<T>::exp_neg((T)kR_eta, d2.x), Num<T>::exp_neg((T)kR_eta, d2.y)};
+                acc[t] = pfma(v, Pair<T>{e.y, e.y}, acc[t]);
+            }
+        }
+        if (g < G && !((skip >> g) & 1u)) {
+            T* row = ws.row[g];
+#pragma unroll
+            for (int t = 0; t < kTypes; t++)
+                *reinterpret_cast<Vec2<T>*>(row + t * kNumRs + 2 * sp) = Vec2<T>{acc[t].x, acc[t].y};
+        }
+    }
+
+    // ---- T: one table for the groups (central atom, element pair) of the round.  Lane = (central
+    // atom, bucket) covers the first eight buckets in one pass; N-O and O-O pairs (buckets 8, 9)
+    // are rare and get a second, short pass only when they occur. ----
+    int total = 0;
+    for (int pass = 0; pass < 2; pass++) {
+        const int g = pass == 0 ? lane >> 3 : (lane >> 1) & 3;
+        const int bk = pass == 0 ? lane & 7 : 8 + (lane & 1);
+        const bool act = pass == 0 || lane < 8;
+        const int ta = (kBucketTa >> (2 * bk)) & 3, tb = (kBucketTb >> (2 * bk)) & 3;
+        const int4 ca = *reinterpret_cast<const int4*>(&ws.cnt_a[g * kTypes]);
+        const int cav[kTypes] = {ca.x, ca.y, ca.z, ca.w};
+        const int stv[kTypes] = {0, ca.x, ca.x + ca.y, ca.x + ca.y + ca.z};
+        const int na = pick4(cav, ta), nb = pick4(cav, tb);
+        const int cnt = act ? (ta == tb ? na * (na - 1) / 2 : na * nb) : 0;
+        if (pass == 1 && !__any_sync(kFull, cnt > 0)) break;
+        const int pad = (cnt + 3) & ~3;
+        int incl = pad;
+#pragma unroll
+        for (int o = 1; o < kWarp; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += y;
+        }
+        const int off = total + incl - pad;
+        if (cnt > 0) {
+            MolGroupInfo e;
+            e.off = off;
+            e.cnt = cnt;
+            e.packed = (g * kMolCapA + pick4(stv, ta)) | ((g * kMolCapA + pick4(stv, tb)) << 8) | (nb << 16) |
+                       ((ta == tb ? 1 : 0) << 24);
+            e.recip = (unsigned)(65536.0f * __frcp_rn((float)nb)) + 1u;   // in [2^16 / nb, 2^16 / nb + 1.01)
+            const int gid = g * kMolGroupStride + bk;
+            ws.tab[gid] = e;
+            for (int q = off >> 2; q < (off + pad) >> 2; q++) ws.quad_gid[q] = (unsigned char)gid;
+        }
+        total += __shfl_sync(kFull, incl, kWarp - 1);
+    }
+    // ids behind the last group, through the end of its chunk and the look-ahead of pass C
+    for (int q = (total >> 2) + lane; q < (((total + kWarp - 1) & ~(kWarp - 1)) >> 2) + 8; q += kWarp)
+        ws.quad_gid[q] = (unsigned char)kMolNoGroup;
+    __syncwarp();
+
+    // ---- B + C over the slots of the round ----
+    const T* a_row = &ws.A[lane >> 2][0];
+    const T* b_row = &ws.BF[lane & 3][0];
+    Pair<T> acc0{(T)0, (T)0}, acc1{(T)0, (T)0};
+    for (int c0 = 0; c0 < total; c0 += kWarp) {
+        {   // B: lane = slot
+            int a, b;
+            const bool valid = decode_slot(ws.tab, ws.quad_gid, c0 + lane, &a, &b);
+            const Vec4<T> ua = ws.ang_u[a], ub = ws.ang_u[b];
+            const T cosv = ua.x * ub.x + ua.y * ub.y + ua.z * ub.z;
+            const T rbar = (T)0.5 * (ua.w + ub.w);
+            const T fcprod = valid ? ws.ang_fc[a] * ws.ang_fc[b] : (T)0;
+            T A[kNumThetas], BF[kNumARs];
+            angular_factors_dev<T>(cosv, rbar, fcprod, A, BF);
+#pragma unroll
+            for (int t = 0; t < kNumThetas; t++) ws.A[t][lane] = A[t];
+#pragma unroll
+            for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = BF[q];
+        }
+        // quads of this chunk that end a group (lanes 0..7 look at one quad each)
+        const unsigned char* ids = &ws.quad_gid[c0 >> 2];
+        const unsigned my_id = ids[lane & 7];
+        const unsigned ends = __ballot_sync(kFull, lane < 8 && my_id != kMolNoGroup && my_id != ids[(lane & 7) + 1]);
+        __syncwarp();
+        // C: lane = (theta, shift).  Slots behind the last group hold BF = 0.
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            T av[4], bv[4];
+            load4(a_row + 4 * q, av);
+            load4(b_row + 4 * q, bv);
+            acc0 = pfma(Pair<T>{av[0], av[1]}, Pair<T>{bv[0], bv[1]}, acc0);
+            acc1 = pfma(Pair<T>{av[2], av[3]}, Pair<T>{bv[2], bv[3]}, acc1);
+            if ((ends >> q) & 1u) {
+                const unsigned id = ids[q];
+                T* row = ws.row[id >> 4];
+                row[kRadial + (id & 15u) * kTS + lane] = (acc0.x + acc0.y) + (acc1.x + acc1.y);
+                acc0 = Pair<T>{(T)0, (T)0};
+                acc1 = Pair<T>{(T)0, (T)0};
+            }
+        }
+        __syncwarp();
+    }
+}
+
+}  // namespace ani

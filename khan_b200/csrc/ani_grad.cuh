@@ -136,7 +136,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
     using WarpShared = GradWarpShared<T>;
     const int lane = lane_id(), warp = warp_id();
     WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
-    ANI_PHASE_DECL;
 
     __shared__ int cta_next_item;
     if (threadIdx.x == 0) cta_next_item = 0;
@@ -163,7 +162,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
                 if (lane == 0) report(ANI_ERR_BAD_INDEX);
                 continue;
             }
-            ANI_PHASE(8);
             const T* grow = (ti == 0 ? gh : (ti == 1 ? gc : (ti == 2 ? gn : go))) + (size_t)srow * kTotal;
             // upstream row -> shared memory (12 coalesced loads of 32 values)
             {
@@ -180,7 +178,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
             }
             __syncwarp();
             T fix = (T)0, fiy = (T)0, fiz = (T)0;  // this lane's share of the force on atom i
-            ANI_PHASE(9);
 
             // ---- A: neighbour scan + radial part, lane = j ----
             int n_ang = 0;
@@ -224,7 +221,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
                 n_ang += __popc(mA);
             }
             __syncwarp();
-            ANI_PHASE(10);
 
             if (n_ang > kGradMaxNeighbors) {
                 grad_atom_streaming<T>(xs, ys, zs, types, base, n, i, ws.g, gx, gy, gz);
@@ -279,7 +275,6 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
                     fay += __shfl_sync(kFull, gby, src);
                     faz += __shfl_sync(kFull, gbz, src);
                 }
-                ANI_PHASE(11);
                 // ---- C: sum the groups, push the neighbour forces out ----
                 for (int g = 1; g < groups; g++) {
                     const int src = lane + g * na < kWarp ? lane + g * na : lane;
@@ -306,11 +301,8 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
                 atomicAdd(&gz[gi], fiz);
             }
             __syncwarp();
-            ANI_PHASE(12);
         }
     }
-    ANI_PHASE(13);
-    ANI_PHASE_FLUSH;
 }
 
 // Zero fill of the three gradient arrays in one launch (the gradient kernel accumulates into

@@ -1,0 +1,424 @@
+// Coordinate-gradient kernel for batches of small molecules (at most 32 atoms each).
+//
+// One CTA per molecule, NW warps.  The central atoms of the molecule, in element order (see
+// load_sorted_molecule), are split evenly over the warps; a warp walks its share in ROUNDS of
+// three consecutive atoms and keeps the molecule in registers, lane = atom.  Per round:
+//   - the 384 upstream values of each of its central atoms are copied global -> shared memory
+//     with asynchronous 16-byte copies (cp.async), all requested at the start of the round, so
+//     the copies run under the arithmetic and cost three instructions per lane and row;
+//   - A. per central atom c: one distance per lane; a lane whose atom j is within R_Rc contracts
+//     the 16 upstream values of radial block type(j) with the radial derivatives and WRITES the
+//     force on j into the molecule's force table part[c][j]; neighbours within A_Rc are
+//     appended to the warp's neighbour list;
+//   - B. when the list is full (or the round is in), the neighbour pairs of ALL central atoms in
+//     the list are walked together in circulant order: the neighbours of a central atom with k
+//     neighbours occupy k consecutive lanes, lane a handles the pair (a, a + d mod k) for
+//     d = 1 .. k/2, keeps the force on a in registers and hands the force on b to its owner
+//     with one shuffle.  Spare lanes run further offsets d at the same time;
+//   - the lanes then add their neighbour's force to part[c][a].
+// After one __syncthreads the molecule's gradient is column sum minus row sum of the table
+// (every term depends on coordinate differences only, so the central atom gets minus what it
+// handed out): each output value is written once, nothing is accumulated with atomics, the
+// outputs need no zero fill and the result is bit-reproducible.
+//
+// A molecule with more than 32 atoms met by this kernel goes through the streaming routines
+// (zero fill by its own CTA, then global atomics, all inside the CTA).
+//
+// Computes what featurize_grad_cpu of the reference computes
+// (gpu_featurizer/kernel_cpu.cpp:217-366).
+#pragma once
+
+#include "ani_common.cuh"
+#include "ani_featurize_mol.cuh"
+#include "ani_grad.cuh"
+
+namespace ani {
+
+constexpr int kMolGradPitch = kMolMaxAtoms + 1;   // odd: rows and columns of the force table are both conflict-free
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
+{
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Central atoms per round = upstream rows a warp holds in shared memory.
+template <typename T> struct MolGradCfg {
+    static constexpr int kRowBufs = 3;
+};
+
+template <typename T> struct alignas(16) MolGradNeighbor {
+    Vec4<T> u;         // (x_c - x_j) / r, r
+    T inv_r, fc, dfc;  // 1 / r, f_C(r, A_Rc) and its derivative
+    int info;          // element | lane of j << 2 | first list entry of its central atom << 7 |
+                       // neighbours of that central atom << 12 | row buffer << 18 | lane of the central atom << 20
+};
+
+template <typename T> struct MolGradWarpShared {
+    alignas(16) T g[MolGradCfg<T>::kRowBufs][kGradRowWords];   // upstream rows, blocks of 32 at stride 36
+    MolGradNeighbor<T> nb[kWarp];
+    MolSortShared sort;
+};
+
+template <typename T, int NW> constexpr size_t mol_grad_smem_bytes()
+{
+    return NW * sizeof(MolGradWarpShared<T>) + 3 * kMolMaxAtoms * kMolGradPitch * sizeof(T);
+}
+
+// Bucket of the element pair (ta, tb), four bits per entry of the 4 x 4 table.
+constexpr unsigned long long kBucketLut =
+    0x0ull | (0x1ull << 4) | (0x2ull << 8) | (0x3ull << 12) | (0x1ull << 16) | (0x4ull << 20) | (0x5ull << 24) |
+    (0x6ull << 28) | (0x2ull << 32) | (0x5ull << 36) | (0x7ull << 40) | (0x8ull << 44) | (0x3ull << 48) |
+    (0x6ull << 52) | (0x8ull << 56) | (0x9ull << 60);
+__device__ __forceinline__ int bucket_of(int ta, int tb) { return (int)(kBucketLut >> (4 * (ta * kTypes + tb))) & 15; }
+
+// Radial part of the gradient of one central atom of a LARGE molecule, with global atomics
+// (the angular part is grad_atom_streaming of ani_grad.cuh).  g = upstream row in shared memory.
+template <typename T>
+__device__ __noinline__ void grad_atom_streaming_radial(const T* __restrict__ xs, const T* __restrict__ ys,
+                                                        const T* __restrict__ zs, const int* __restrict__ types,
+                                                        int base, int n, int i, const T* g, T* gx, T* gy, T* gz)
+{
+    const int lane = lane_id();
+    const T xi = xs[base + i], yi = ys[base + i], zi = zs[base + i];
+    T fix = (T)0, fiy = (T)0, fiz = (T)0;
+    for (int j0 = 0; j0 < n; j0 += kWarp) {
+        const int j = j0 + lane;
+        if (j < n && j != i) {
+            const T dx = xi - xs[base + j], dy = yi - ys[base + j], dz = zi - zs[base + j];
+            T r, inv;
+            length_and_inverse(dx * dx + dy * dy + dz * dz, &r, &inv);
+            if (r < (T)kR_Rc) {
+                T fc, dfc;
+                cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
+                const T d = radial_vjp<T, T>(r, fc, dfc, g + (types[base + j] & 3) * kNumRs);
+                const T fx = d * dx * inv, fy = d * dy * inv, fz = d * dz * inv;
+                fix += fx; fiy += fy; fiz += fz;
+                atomicAdd(&gx[base + j], -fx);
+                atomicAdd(&gy[base + j], -fy);
+                atomicAdd(&gz[base + j], -fz);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        fix += __shfl_xor_sync(kFull, fix, o);
+        fiy += __shfl_xor_sync(kFull, fiy, o);
+        fiz += __shfl_xor_sync(kFull, fiz, o);
+    }
+    if (lane == 0) {
+        atomicAdd(&gx[base + i], fix);
+        atomicAdd(&gy[base + i], fiy);
+        atomicAdd(&gz[base + i], fiz);
+    }
+}
+
+// radial_vjp and angular_vjp of ani_params.h, arranged for the device: the same arithmetic, but every
+// constant (shift, cos / sin of a theta shift) is an immediate operand of a scalar instruction, and
+// only products of two computed values run as packed pairs.  (A packed instruction takes its
+// operands from register pairs, so a pair of constants would cost two moves per use.)
+template <typename T> __device__ __forceinline__ T radial_vjp_dev(T rij, T fc, T dfc, const T* w)
+{
+    const T slope = (T)-2 * (T)kR_eta * fc;
+    const Pair<T> sl{slope, slope}, dd{dfc, dfc};
+    Pair<T> acc{(T)0, (T)0};
+#pragma unroll
+    for (int r = 0; r < kNumRs; r += 2) {
+        const Pair<T> d{rij - radial_shift<T>(r), rij - radial_shift<T>(r + 1)};
+        const Pair<T> d2 = pmul(d, d);
+        const Pair<T> e{Num<T>::exp_neg((T)kR_eta, d2.x), Num<T>::exp_neg((T)kR_eta, d2.y)};
+        acc = pfma(pmul(Pair<T>{w[r], w[r + 1]}, e), pfma(d, sl, dd), acc);
+    }
+    return acc.x + acc.y;
+}
+
+template <typename T>
+__device__ __forceinline__ void angular_vjp_dev(T cosv, T sin2, T rij, T rik, T fcj, T dfcj, T fck, T dfck,
+                                                const T* g, T* dc, T* drj, T* drk)
+{
+    const T c = Num<T>::max_((T)-1, Num<T>::min_((T)1, cosv));
+    const T s2 = Num<T>::min_((T)1, sin2);
+    const T s = Num<T>::sqrt_(s2);
+    const bool bent = s2 > (T)1e-12;  // sin(theta) > 1e-6
+    const T cot = bent ? c * Num<T>::rsqrt_(s2) : (T)0;
+    const T keep = bent ? (T)1 : (T)0;
+    const T rbar = (T)0.5 * (rij + rik);
+
+    Pair<T> e[kNumARs / 2], de[kNumARs / 2];   // exp(-eta d_q^2) and d_q exp(-eta d_q^2)
+#pragma unroll
+    for (int q = 0; q < kNumARs; q += 2) {
+        const Pair<T> d{rbar - angular_shift<T>(q), rbar - angular_shift<T>(q + 1)};
+        const Pair<T> d2 = pmul(d, d);
+        e[q / 2] = Pair<T>{Num<T>::exp_neg((T)kA_eta, d2.x), Num<T>::exp_neg((T)kA_eta, d2.y)};
+        de[q / 2] = pmul(d, e[q / 2]);
+    }
+    T u[kNumThetas], v[kNumThetas];   // u[t] = sum_q g[t][q] e[q], v[t] = sum_q g[t][q] de[q]
+#pragma unroll
+    for (int t = 0; t < kNumThetas; t++) {
+        const Pair<T> g01{g[t * kNumARs + 0], g[t * kNumARs + 1]}, g23{g[t * kNumARs + 2], g[t * kNumARs + 3]};
+        const Pair<T> pu = pfma(g23, e[1], pmul(g01, e[0]));
+        const Pair<T> pv = pfma(g23, de[1], pmul(g01, de[0]));
+        u[t] = pu.x + pu.y;
+        v[t] = pv.x + pv.y;
+    }
+    T b[kNumThetas];
+#pragma unroll
+    for (int t = 0; t < kNumThetas; t++) b[t] = c * theta_cos<T>(t) + (s * theta_sin<T>(t) + (T)1);
+    Pair<T> s0p{(T)0, (T)0}, s2p{(T)0, (T)0};
+    T sc = (T)0, ss = (T)0;
+#pragma unroll
+    for (int t = 0; t < kNumThetas; t += 2) {
+        const Pair<T> b1{b[t], b[t + 1]}, ut{u[t], u[t + 1]}, vt{v[t], v[t + 1]};
+        const Pair<T> b2 = pmul(b1, b1);
+        const Pair<T> b4 = pmul(b2, b2);
+        const Pair<T> b7 = pmul(pmul(b4, b2), b1);
+        const Pair<T> a = pmul(b7, b1);
+        s0p = pfma(a, ut, s0p);
+        s2p = pfma(a, vt, s2p);
+        const Pair<T> b7u = pmul(b7, ut);
+        sc += b7u.x * theta_cos<T>(t) + b7u.y * theta_cos<T>(t + 1);
+        ss += b7u.x * theta_sin<T>(t) + b7u.y * theta_sin<T>(t + 1);
+    }
+    const T s0 = s0p.x + s0p.y, s2sum = s2p.x + s2p.y;
+    const T f = (T)kA_pref * fcj * fck;
+    *dc = (T)8 * f * (keep * sc - cot * ss);                 // dA_t/dc = 8 b^7 (cos(theta_t) - sin(theta_t) c / s)
+    const T common = -(T)kA_eta * f * s2sum;                  // through rbar: d rbar / d r = 1/2, d e/d rbar = -2 eta d e
+    *drj = common + (T)kA_pref * dfcj * fck * s0;
+    *drk = common + (T)kA_pref * fcj * dfck * s0;
+}
+
+template <typename T, int NW>
+__global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? 20 / NW : 1)
+    featurize_grad_mol_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
+                              const int* __restrict__ types, const int* __restrict__ mol_offsets,
+                              const int* __restrict__ mol_counts, int n_mols, int n_atoms,
+                              const int* __restrict__ scatter, const T* __restrict__ gh,
+                              const T* __restrict__ gc, const T* __restrict__ gn, const T* __restrict__ go,
+                              T* gx, T* gy, T* gz, int acs0, int acs1, int acs2, int acs3)
+{
+    constexpr int GR = MolGradCfg<T>::kRowBufs;   // central atoms per round
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    using WarpShared = MolGradWarpShared<T>;
+    const int lane = lane_id(), warp = warp_id();
+    WarpShared& ws = reinterpret_cast<WarpShared*>(smem_raw)[warp];
+    T* part = reinterpret_cast<T*>(smem_raw + NW * sizeof(WarpShared));
+    auto part_at = [part](int plane, int c, int j) -> T& {
+        return part[(plane * kMolMaxAtoms + c) * kMolGradPitch + j];
+    };
+
+    for (int m = blockIdx.x; m < n_mols; m += gridDim.x) {
+        MolRange mol;
+        if (!load_molecule(mol_offsets, mol_counts, m, n_atoms, &mol)) continue;
+        const int n = mol.n, base = mol.base;
+
+        if (n > kMolMaxAtoms) {   // a large molecule in a batch of small ones
+            for (int j = threadIdx.x; j < n; j += NW * kWarp) {
+                gx[base + j] = (T)0;
+                gy[base + j] = (T)0;
+                gz[base + j] = (T)0;
+            }
+            __syncthreads();
+            for (int i = warp; i < n; i += NW) {
+                const int gi = base + i;
+                const int ti = checked_type(types[gi]);
+                const int srow = scatter[gi];
+                const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
+                if (srow < 0 || srow >= cap) {
+                    if (lane == 0) report(ANI_ERR_BAD_INDEX);
+                    continue;
+                }
+                const T* grow = (ti == 0 ? gh : (ti == 1 ? gc : (ti == 2 ? gn : go))) + (size_t)srow * kTotal;
+                T* g = ws.g[0];
+                g[lane] = grow[lane];
+                g[32 + lane] = grow[32 + lane];
+                for (int bk = 0; bk < kPairBuckets; bk++)
+                    g[kRadial + bk * kGradBucketStride + lane] = grow[kRadial + bk * kTS + lane];
+                __syncwarp();
+                grad_atom_streaming_radial<T>(xs, ys, zs, types, base, n, i, g, gx, gy, gz);
+                grad_atom_streaming<T>(xs, ys, zs, types, base, n, i, g, gx, gy, gz);
+                __syncwarp();
+            }
+            continue;
+        }
+
+        // every warp needs the sort for the last step, also one without a round of its own
+        MolLanes<T> ml;
+        load_sorted_molecule<T>(xs, ys, zs, types, scatter, base, n, &ws.sort, &ml);
+
+        // Every warp takes the same number of consecutive central atoms (so the CTA has no idle warps) and
+        // walks them in rounds of GR.  Which warp gets the first share rotates with the molecule: a warp's
+        // scheduler is fixed by its index, and the last share is the short one.
+        const int share = (n + NW - 1) / NW;
+        const int c_begin = ((warp + m) % NW) * share, c_end = min(n, c_begin + share);
+        for (int c_first = c_begin; c_first < c_end; c_first += GR) {
+            const int G = min(GR, c_end - c_first);
+            // ---- upstream rows of the round: one commit group per row slot ----
+#pragma unroll
+            for (int g = 0; g < GR; g++) {
+                const int c = min(c_first + g, n - 1);
+                const int ti = __shfl_sync(kFull, ml.type, c), sr = ws.sort.srow[c];
+                const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
+                if (g < G && sr >= 0 && sr < cap) {
+                    const T* grow = (ti == 0 ? gh : (ti == 1 ? gc : (ti == 2 ? gn : go))) + (size_t)sr * kTotal;
+                    T* dst = ws.g[g];
+                    constexpr int V = 16 / (int)sizeof(T);   // values per 16-byte copy
+#pragma unroll
+                    for (int s = 0; s < kTotal / V / kWarp; s++) {
+                        const int v = (lane + s * kWarp) * V;
+                        const int d = v < kRadial
+                                          ? v
+                                          : kRadial + ((v - kRadial) >> 5) * kGradBucketStride + ((v - kRadial) & 31);
+                        cp_async16(dst + d, grow + v);
+                    }
+                }
+                cp_async_commit();
+            }
+
+            int g = 0;
+            while (g < G) {
+                // ---- A: scan central atoms into the neighbour list until it is full ----
+                int used = 0, max_half = 0, taken = 0;
+                while (g < G) {
+                    const int c = c_first + g;
+                    const T xi = __shfl_sync(kFull, ml.x, c), yi = __shfl_sync(kFull, ml.y, c),
+                            zi = __shfl_sync(kFull, ml.z, c);
+                    const int ti = __shfl_sync(kFull, ml.type, c), sr = ws.sort.srow[c];
+                    const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
+                    const bool ok = sr >= 0 && sr < cap;
+                    const T dx = xi - ml.x, dy = yi - ml.y, dz = zi - ml.z;
+                    T r, inv;
+                    length_and_inverse(dx * dx + dy * dy + dz * dz, &r, &inv);
+                    const bool in_rad = ok && lane < n && lane != c && r < (T)kR_Rc;
+                    const bool in_ang = in_rad && r < (T)kA_Rc;
+                    const unsigned mA = __ballot_sync(kFull, in_ang);
+                    const int nA = __popc(mA);
+                    if (taken > 0 && used + nA > kWarp) break;   // this central atom opens the next pass
+
+                    // row slot g has landed when at most GR - 1 - g younger groups are pending
+                    if (g == 0) cp_async_wait<GR - 1>();
+                    else if (g == 1) cp_async_wait<(GR > 2 ? GR - 2 : 0)>();
+                    else if (g == 2) cp_async_wait<(GR > 3 ? GR - 3 : 0)>();
+                    else cp_async_wait<0>();
+                    __syncwarp();
+                    if (!ok && lane == 0) report(ANI_ERR_BAD_INDEX);
+                    const T* grow = ws.g[g];
+                    const T ux = dx * inv, uy = dy * inv, uz = dz * inv;
+                    T fx = (T)0, fy = (T)0, fz = (T)0;
+                    if (in_rad) {
+                        T fc, dfc;
+                        cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
+                        T w[kNumRs];
+#pragma unroll
+                        for (int q = 0; q < kNumRs; q += 4) load4(grow + ml.type * kNumRs + q, w + q);
+                        const T d = radial_vjp_dev<T>(r, fc, dfc, w);
+                        fx = d * ux; fy = d * uy; fz = d * uz;
+                    }
+                    if (lane < n) {   // force on atom j from the radial terms of central atom c (0 out of range)
+                        part_at(0, c, lane) = -fx;
+                        part_at(1, c, lane) = -fy;
+                        part_at(2, c, lane) = -fz;
+                    }
+                    if (in_ang) {
+                        MolGradNeighbor<T> e;
+                        e.u = Vec4<T>{ux, uy, uz, r};
+                        e.inv_r = inv;
+                        cutoff<T>(r, (T)kA_Rc, &e.fc, &e.dfc);
+                        e.info = ml.type | (lane << 2) | (used << 7) | (nA << 12) | (g << 18) | (c << 20);
+                        ws.nb[used + __popc(mA & lanemask_lt())] = e;
+                    }
+                    used += nA;
+                    taken++;
+                    max_half = max(max_half, nA >> 1);
+                    g++;
+                }
+                __syncwarp();
+
+                // ---- B: neighbour pairs of every central atom in the list, circulant order ----
+                if (max_half > 0) {
+                    // offsets d that run at once on spare lanes
+                    const int mult = used * 4 <= kWarp ? 4 : (used * 3 <= kWarp ? 3 : (used * 2 <= kWarp ? 2 : 1));
+                    const int copy = (lane >= used ? 1 : 0) + (lane >= 2 * used ? 1 : 0) + (lane >= 3 * used ? 1 : 0);
+                    const bool owner = copy < mult;
+                    const int l1 = owner ? lane - copy * used : 0;
+                    const MolGradNeighbor<T> ea = ws.nb[l1];
+                    const int ta = ea.info & 3, lb = (ea.info >> 7) & 31, na = (ea.info >> 12) & 63;
+                    const T* gblocks = ws.g[(ea.info >> 18) & 3] + kRadial;
+                    const int a = l1 - lb, hf = na >> 1;
+                    const bool even = (na & 1) == 0;
+                    T fax = (T)0, fay = (T)0, faz = (T)0;   // force on neighbour a, this copy's share
+                    const int iters = (max_half + mult - 1) / mult;
+                    for (int it = 0; it < iters; it++) {
+                        const int d = 1 + copy + it * mult;
+                        const bool in_range = owner && d <= hf;
+                        const bool valid = in_range && !(even && d == hf && a >= hf);
+                        int b = a + d;
+                        if (b >= na) b -= na;
+                        T gbx = (T)0, gby = (T)0, gbz = (T)0;
+                        if (valid) {
+                            const MolGradNeighbor<T> eb = ws.nb[lb + b];
+                            T c = ea.u.x * eb.u.x + ea.u.y * eb.u.y + ea.u.z * eb.u.z;
+                            c = Num<T>::max_((T)-1, Num<T>::min_((T)1, c));
+                            const T s2 = sin2_from_cross<T>(ea.u.x, ea.u.y, ea.u.z, eb.u.x, eb.u.y, eb.u.z);
+                            T gl[kTS];
+                            const T* gsrc = gblocks + bucket_of(ta, eb.info & 3) * kGradBucketStride;
+#pragma unroll
+                            for (int q = 0; q < kTS; q += 4) load4(gsrc + q, gl + q);
+                            T dc, dra, drb;
+                            angular_vjp_dev<T>(c, s2, ea.u.w, eb.u.w, ea.fc, ea.dfc, eb.fc, eb.dfc, gl, &dc, &dra, &drb);
+                            const T aa = -dc * ea.inv_r, ba = c * dc * ea.inv_r - dra;
+                            const T ab = -dc * eb.inv_r, bb = c * dc * eb.inv_r - drb;
+                            fax += aa * eb.u.x + ba * ea.u.x;
+                            fay += aa * eb.u.y + ba * ea.u.y;
+                            faz += aa * eb.u.z + ba * ea.u.z;
+                            gbx = ab * ea.u.x + bb * eb.u.x;
+                            gby = ab * ea.u.y + bb * eb.u.y;
+                            gbz = ab * ea.u.z + bb * eb.u.z;
+                        }
+                        // the force on b goes to the lane that owns b: lane a takes it from the lane
+                        // of (a - d) mod k in its own copy
+                        int sa = a - d;
+                        if (sa < 0) sa += na;
+                        const int from = in_range ? copy * used + lb + sa : lane;
+                        fax += __shfl_sync(kFull, gbx, from);
+                        fay += __shfl_sync(kFull, gby, from);
+                        faz += __shfl_sync(kFull, gbz, from);
+                    }
+                    for (int k2 = 1; k2 < mult; k2++) {   // sum the copies
+                        const int s = lane + k2 * used;
+                        const int from = s < kWarp ? s : lane;
+                        const T ox = __shfl_sync(kFull, fax, from), oy = __shfl_sync(kFull, fay, from),
+                                oz = __shfl_sync(kFull, faz, from);
+                        if (lane < used) { fax += ox; fay += oy; faz += oz; }
+                    }
+                    if (lane < used) {
+                        const int cen = (ea.info >> 20) & 31, at = (ea.info >> 2) & 31;
+                        part_at(0, cen, at) += fax;
+                        part_at(1, cen, at) += fay;
+                        part_at(2, cen, at) += faz;
+                    }
+                }
+                __syncwarp();
+            }
+            cp_async_wait<0>();   // row slots of a short round are empty groups; nothing may stay pending
+        }
+        __syncthreads();
+        // gradient of atom j = what the central atoms handed to j (column j) - what j handed out (row j)
+        for (int plane = warp; plane < 3; plane += NW) {
+            if (lane < n) {
+                T col = (T)0, rw = (T)0;
+                for (int c = 0; c < n; c++) col += part_at(plane, c, lane);
+                for (int j = 0; j < n; j++) rw += part_at(plane, lane, j);
+                T* dst = plane == 0 ? gx : (plane == 1 ? gy : gz);
+                dst[base + ws.sort.src[lane]] = col - rw;
+            }
+        }
+        __syncthreads();   // the table is reused by the next molecule of this CTA
+    }
+}
+
+}  // namespace ani

@@ -55,7 +55,6 @@ __global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_forward_kernel(const Ml
     } else {
         // ---- producers / epilogue warps ----
         PipeState ps;
-        ANI_PHASE_DECL;
         const float* layer_w[3] = {p.w1[e], p.w2[e], p.w3[e]};
         const float* layer_b[3] = {p.b1[e], p.b2[e], p.b3[e]};
         float* layer_out[3] = {p.act1[e], p.act2[e], p.act3[e]};
@@ -80,9 +79,7 @@ __global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_forward_kernel(const Ml
             } else {
                 pipe_produce<SPLIT, true>(sh, K / kPipeK, ps, a_feat, a_sh, b_w);
             }
-            ANI_PHASE(0);
             ok = pipe_drain(sh, ps);
-            ANI_PHASE(2);
             if (!ok) break;
             // ---- epilogue: bias, activation and its derivative; the row goes back to shared
             // memory as the next layer's A operand (the last hidden layer included: the output
@@ -104,12 +101,9 @@ __global__ void __launch_bounds__(kMlpAllThreads, 1) mlp_forward_kernel(const Ml
                 if (layer_out[layer]) warp_tile_to_global<false>(scratch, v, layer_out[layer] + g0, N, n_rows - tile_row0);
                 if (layer_dout[layer]) warp_tile_to_global<false>(scratch, d, layer_dout[layer] + g0, N, n_rows - tile_row0);
             }
-            ANI_PHASE(4);
             tc_fence_before();
             producer_sync();
-            ANI_PHASE(5);
         }
-        ANI_PHASE_FLUSH;
 
         if (ok) {
             // ---- output layer 64 -> 1: one thread per atom, its last hidden row from shared memory ----
