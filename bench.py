@@ -49,10 +49,13 @@ FEATURE_SIZE = 384
 FLOPS_FWD = (125, 156)
 FLOPS_GRAD = (201, 417)
 FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # SMs x lanes x FMA x max SM clock
-# DRAM bytes per atom seen by ncu (dram__bytes_read.sum + dram__bytes_write.sum) on an
-# 8192-molecule batch, whose 170 MB of features exceed the L2 (profiles/dram_traffic_8192_molecules.md);
-# traffic grows in proportion to the atoms, so a launch is scaled by its atom count.
+# DRAM bytes per atom that ncu saw (dram__bytes_read.sum + dram__bytes_write.sum) for the kernels
+# named in NCU_TRAFFIC_SOURCE, on an 8192-molecule batch whose 170 MB of features exceed the L2;
+# traffic grows in proportion to the atoms, so a launch is scaled by its atom count.  The numbers
+# belong to those kernels: when a kernel changes, the capture has to be repeated.
 NCU_DRAM_BYTES_PER_ATOM = {"featurize": 1035.2, "featurize_grad": 1571.7, "ani_sort": None}
+NCU_TRAFFIC_SOURCE = ("one ncu capture of featurize_kernel / featurize_grad_kernel (one warp per atom), "
+                      "8192-molecule batch, scaled by atoms")
 
 
 def measured_peaks():
@@ -63,11 +66,33 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
 
 
+_probe_lib = None
+
+
+def probe_lib():
+    """libbench_probe.so (built from bench_probe.cu by __graft_entry__.build())."""
+    global _probe_lib
+    if _probe_lib is None:
+        path = os.path.join(ROOT, "libbench_probe.so")
+        if not os.path.exists(path):
+            import __graft_entry__
+            __graft_entry__.build_bench_probe()
+        _probe_lib = ctypes.CDLL(path)
+        _probe_lib.bench_fma_probe.restype = ctypes.c_int
+        _probe_lib.bench_fma_probe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                               ctypes.POINTER(ctypes.c_longlong), ctypes.c_void_p]
+    return _probe_lib
+
+
+_fma_peak_cache = {}
+
+
 def measure_fma_peak(bits: int, device) -> float:
-    """TFLOP/s of the library's FMA-only probe kernel, best of 5 launches (CUDA events)."""
+    """TFLOP/s of the FMA-only probe kernel (bench_probe.cu), best of 5 launches (CUDA events)."""
     import torch
-    from khan_b200 import _lib
-    lib = _lib.lib()
+    if bits in _fma_peak_cache:
+        return _fma_peak_cache[bits]
+    lib = probe_lib()
     sink = torch.zeros(2, dtype=torch.float64, device=device)
     flops = ctypes.c_longlong(0)
     st = torch.cuda.current_stream()
@@ -76,12 +101,53 @@ def measure_fma_peak(bits: int, device) -> float:
     for rep in range(6):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        _lib.check(lib.ani_fma_probe(bits, iters, sink.data_ptr(), ctypes.byref(flops), st.cuda_stream), "ani_fma_probe")
+        rc = lib.bench_fma_probe(bits, iters, sink.data_ptr(), ctypes.byref(flops), st.cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"bench_fma_probe failed ({rc})")
         e1.record()
         torch.cuda.synchronize()
         if rep:
             best = max(best, flops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    _fma_peak_cache[bits] = best
     return best
+
+
+class Ctx:
+    """Rank, device and process group of this process (one rank per GPU under torchrun)."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1 and not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def barrier(self):
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.barrier()
+
+    def max_sum(self, ms: float, units: float):
+        """(max over ranks of a time, sum over ranks of a count)."""
+        import torch
+        import torch.distributed as dist
+        if self.world == 1:
+            return float(ms), float(units)
+        t = torch.tensor([ms, units], dtype=torch.float64, device=self.dev)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(tmax[0]), float(t[1])
+
+    def close(self):
+        import torch.distributed as dist
+        if self.world > 1 and dist.is_initialized():
+            dist.destroy_process_group()
 
 
 # ------------------------------------------------------------------------------------------
@@ -344,12 +410,14 @@ def run_forces_workload(args):
         dist.destroy_process_group()
 
 
-def run_fused_train_workload(args):
-    """The training step of `run_train_workload` on the C ABI only (khan_b200.training.fused_step):
-    no autograd, 11 launches, the gradient all-reduce issued right after the weight gradients so
-    that it overlaps the coordinate-gradient kernel, which runs on a second stream."""
+def measure_fused_train(ctx, mols: int, steps: int, warmup: int, train_path: str = "fused", graphs: bool = True,
+                        exposed: bool = True):
+    """The training step of benchmark configuration 3 on the C ABI only
+    (khan_b200.training.fused_step): no autograd, the gradient all-reduce (NCCL, one flat buffer)
+    issued right after the weight gradients.  Returns a dict; with several ranks and ``exposed`` the
+    same steps are timed once more without the all-reduce, and the difference per step is the part
+    of the collective that nothing hides."""
     import torch
-    import torch.distributed as dist
 
     from khan_b200.data import synthetic as syn
     from khan_b200.model import activations
@@ -359,56 +427,60 @@ def run_fused_train_workload(args):
     from khan_b200.training.optim import FlatNadam
     from khan_b200.training.trainer_multi_tower import average_gradients
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    rank, world, dev = ctx.rank, ctx.world, ctx.dev
     model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=1, init="he")
     params = model.get_parameters()
     opt = FlatNadam(params, lr=1e-3, clip_norm=5.0)
-    nb = max(1, min(8, args.steps))
-    batches = syn.batch_pool(nb, n_mols=args.mols, seed=1 + 100 * rank)
+    nb = max(1, min(8, steps))
+    batches = syn.batch_pool(nb, n_mols=mols, seed=1 + 100 * rank)
     cap = max(b.n_atoms for b in batches)
     staged, labels = [], []
     for k, b in enumerate(batches):
-        sb = StagedBatch(cap, args.mols, device=dev)
+        sb = StagedBatch(cap, mols, device=dev)
         sb.upload(HostBatch(b, None, pin=False), non_blocking=False, with_upstream=False)
         staged.append(sb)
         rng = np.random.default_rng(3000 + 100 * rank + k)
         labels.append(torch.from_numpy(rng.normal(size=b.n_mols).astype(np.float32)).to(dev))
-    step = FusedTrainStep(model, opt, cap, args.mols, device=dev)
+    step = FusedTrainStep(model, opt, cap, mols, device=dev)
     side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(side):
-        for k in range(max(3, args.warmup)):
+        for k in range(max(3, warmup)):
             step.step(staged[k % nb], labels[k % nb])
     torch.cuda.synchronize()
-    pipelined = args.train_path == "fused" and nb >= 2
+    pipelined = train_path == "fused" and nb >= 2
     main = torch.cuda.current_stream()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(run_one, prime=None):
+        if prime is not None:
+            prime()
+        for k in range(nb):
+            run_one(k)
+        ctx.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for k in range(steps):
+            run_one(k)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    ms_local = None
     if pipelined:
         # next batch's sort + featurize and this batch's coordinate gradient beside the network kernels
-        pipe = StepPipeline(step, staged, labels, allreduce=world > 1, graphs=not args.no_graph)
-        pipe.prime()
-        for k in range(nb):
-            pipe.run(k)
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0.record()
-        for k in range(args.steps):
-            pipe.run(k)
-        e1.record()
+        pipe = StepPipeline(step, staged, labels, allreduce=world > 1, graphs=graphs)
+        ms = timed(pipe.run, pipe.prime)
+        if world > 1 and exposed:
+            solo = StepPipeline(step, staged, labels, allreduce=False, graphs=graphs)
+            ms_local = timed(solo.run, solo.prime)
     else:
-        class _Eager:      # --no-graph: the same calls issued directly (what ncu sees kernel by kernel)
+        class _Eager:      # graphs off: the same calls issued directly (what ncu sees kernel by kernel)
             def __init__(self, fn):
                 self.replay = fn
 
         fb_graphs, cg_graphs = [], []
         for sb, y in zip(staged, labels):
-            if args.no_graph:
+            if not graphs:
                 fb_graphs.append(_Eager(lambda sb=sb, y=y: step.forward_backward(sb, y)))
                 cg_graphs.append(_Eager(lambda sb=sb: step.coordinate_gradient(sb)))
                 continue
@@ -420,15 +492,16 @@ def run_fused_train_workload(args):
             with torch.cuda.graph(g):
                 step.coordinate_gradient(sb)
             cg_graphs.append(g)
-        if args.no_graph:
+        if not graphs:
             up_graph = _Eager(opt.step)
         else:
             up_graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(up_graph):
                 opt.step()
-        def serial_step(k):
+
+        def serial_step(k, allreduce=True):
             fb_graphs[k % nb].replay()
-            if world > 1:      # coordinate gradients on the second stream, under the all-reduce
+            if world > 1 and allreduce:      # coordinate gradients on the second stream, under the all-reduce
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
                     cg_graphs[k % nb].replay()
@@ -438,44 +511,47 @@ def run_fused_train_workload(args):
                 cg_graphs[k % nb].replay()
             up_graph.replay()
 
-        for k in range(nb):
-            serial_step(k)
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0.record()
-        for k in range(args.steps):
-            serial_step(k)
-        e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    atoms = float(sum(batches[k % nb].n_atoms for k in range(args.steps)))
-    loss = float(step.l2s[:batches[(args.steps - 1) % nb].n_mols].mean())
-    if world > 1:
-        t = torch.tensor([ms, atoms], dtype=torch.float64, device=dev)
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        ms, atoms = float(tmax[0]), float(t[1])
-    if rank == 0:
+        ms = timed(serial_step)
+        if world > 1 and exposed:
+            ms_local = timed(lambda k: serial_step(k, allreduce=False))
+    atoms = float(sum(batches[k % nb].n_atoms for k in range(steps)))
+    loss = float(step.l2s[:batches[(steps - 1) % nb].n_mols].mean())
+    ms, atoms = ctx.max_sum(ms, atoms)
+    out = {"ms_per_step": ms / steps, "atoms_per_s": atoms / (ms * 1e-3), "steps": steps, "n_gpus": world,
+           "final_loss": loss, "gpu_launches_per_step": FusedTrainStep.KERNELS, "resident_batches": nb,
+           "pipelined": pipelined,
+           "collective": ("NCCL all-reduce (mean) of the flat gradient buffer, %d float32 values" % opt.flat_grads.numel()
+                          if world > 1 else "none (one rank)")}
+    if ms_local is not None:
+        ms_local, _ = ctx.max_sum(ms_local, 0.0)
+        out["ms_per_step_without_allreduce"] = ms_local / steps
+        out["exposed_allreduce_us"] = max(0.0, (ms - ms_local) / steps * 1e3)
+    return out
+
+
+def run_fused_train_workload(args):
+    """--workload train: prints the training-step line of benchmark configuration 3."""
+    ctx = Ctx()
+    r = measure_fused_train(ctx, args.mols, args.steps, args.warmup, args.train_path, graphs=not args.no_graph)
+    if ctx.rank == 0:
         print(json.dumps({
-            "metric": "training step atoms/sec (fp32, 1024-mol batch per GPU)", "value": atoms / (ms * 1e-3),
-            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": "training step atoms/sec (fp32, 1024-mol batch per GPU)", "value": r["atoms_per_s"],
+            "unit": UNIT, "n_gpus": ctx.world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32 (tf32x3 tensor-core products in the atomic networks)", "data": "synthetic",
-            "final_loss": loss, "gpu_launches": args.steps * FusedTrainStep.KERNELS,
+            "final_loss": r["final_loss"], "gpu_launches": args.steps * r["gpu_launches_per_step"],
+            "exposed_allreduce_us": r.get("exposed_allreduce_us"),
             "config": {"workload": "config3: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian, He init) + MSE "
                                    "+ backward into weights and coordinates + NCCL all-reduce + Nadam",
                        "molecules_per_step_per_gpu": args.mols, "path": "fused (C ABI only, no autograd)",
-                       "resident_batches": nb,
+                       "resident_batches": r["resident_batches"],
                        "order": ("pipelined: sort + featurize of the next batch and the coordinate gradient of this "
-                                 "one run beside the network kernels on two side streams" if pipelined else
+                                 "one run beside the network kernels on two side streams" if r["pipelined"] else
                                  "serial: one kernel after another"),
                        "launch": ("eager" if args.no_graph else
-                                  "cuda_graph (all-reduce eager, between the weight gradients and the update, "
-                                  "under the coordinate gradient)")}}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+                                  "cuda_graph (all-reduce eager, between the weight gradients and the update)")}}),
+              flush=True)
+    ctx.close()
 
 
 def run_train_workload(args):
@@ -618,6 +694,192 @@ CASE_WORKLOAD = {
 }
 
 
+CASE_FLOP_PEAK_NOTE = "min(FMA probe kernel measured in this run, 148 SM x 128 lanes x 2 x 1.965 GHz; half of that for float64)"
+
+
+def capture_overlapped(staged, side, fn_name="run_step"):
+    """One CUDA graph that runs ``fn_name`` of the given staged batches on the side streams, round-robin
+    (fork from the capture stream, one branch per stream, join)."""
+    import torch
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        cap = torch.cuda.current_stream()
+        for st in side:
+            st.wait_stream(cap)
+        for b, sb in enumerate(staged):
+            st = side[b % len(side)]
+            with torch.cuda.stream(st):
+                getattr(sb, fn_name)(ctypes.c_void_p(st.cuda_stream))
+        for st in side:
+            cap.wait_stream(st)
+    return g
+
+
+def time_kernel_alone(staged, fn_name, reps):
+    """Average duration (s) of one launch of a kernel kind: a graph of that kernel over all staged batches,
+    one after another on one stream, replayed ``reps`` times."""
+    import torch
+
+    def stream_ptr():
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    g = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(g):
+            for sb in staged:
+                getattr(sb, fn_name)(stream_ptr())
+        run = g.replay
+    except Exception:
+        torch.cuda.synchronize()
+
+        def run():
+            for sb in staged:
+                getattr(sb, fn_name)(stream_ptr())
+    run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / (reps * len(staged))
+
+
+def work_per_atom(batch, esize):
+    """Algorithmic bytes and flops per atom of each kernel for batches like ``batch``."""
+    from khan_b200.data import synthetic as syn
+    pairs, triplets = syn.count_work(batch)
+    p, t = pairs / batch.n_atoms, triplets / batch.n_atoms
+    coord = 3 * esize + 4
+    nbytes = {"ani_sort": 4 + 8, "featurize": coord + esize * FEATURE_SIZE,
+              "featurize_grad": coord + esize * FEATURE_SIZE + 3 * esize}
+    flops = {"ani_sort": 0.0, "featurize": FLOPS_FWD[0] * p + FLOPS_FWD[1] * t,
+             "featurize_grad": FLOPS_GRAD[0] * p + FLOPS_GRAD[1] * t}
+    return nbytes, flops, p, t
+
+
+def measure_case(ctx, case, n_batches=8, passes=7, n_streams=4):
+    """Another benchmark configuration, device-resident: config2 (the config-1 batches in float64) or
+    config4 (256 molecules of 64-256 atoms, float32).  One graph = one pass over the pool on a few
+    streams; the median of ``passes`` replays is reported, with each kernel timed alone."""
+    import torch
+    from khan_b200.data import synthetic as syn
+    from khan_b200.staged import HostBatch, StagedBatch
+    dev, rank = ctx.dev, ctx.rank
+    f64 = case == "config2"
+    tdtype, esize = (torch.float64, 8) if f64 else (torch.float32, 4)
+    if case == "config4":
+        mols = 256
+        batches = [syn.config4(seed=4 + 10 * k + 1000 * rank, n_mols=mols) for k in range(n_batches)]
+    else:
+        mols = N_MOLS
+        batches = syn.batch_pool(n_batches, n_mols=mols, seed=1 + 100 * rank)
+    cap = max(b.n_atoms for b in batches)
+    staged = []
+    for k, b in enumerate(batches):
+        ac = np.bincount(b.atomic_numbers, minlength=4)
+        sb = StagedBatch(cap, mols, dtype=tdtype, device=dev)
+        sb.upload(HostBatch(b, syn.upstream_grads(b, ac, seed=12 + k), dtype=tdtype, pin=False), non_blocking=False)
+        staged.append(sb)
+    torch.cuda.synchronize()
+    side = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
+    for sb in staged:
+        sb.run_step()
+    torch.cuda.synchronize()
+    g = capture_overlapped(staged, side)
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(passes):
+        ctx.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    atoms = float(sum(b.n_atoms for b in batches))
+    ms, atoms = ctx.max_sum(statistics.median(times), atoms)
+    kernel_s = {k: time_kernel_alone(staged, fn, 5) for k, fn in
+                (("ani_sort", "run_sort"), ("featurize", "run_featurize"), ("featurize_grad", "run_featurize_grad"))}
+    nbytes, flops, p, t = work_per_atom(batches[0], esize)
+    mean_atoms = sum(b.n_atoms for b in batches) / n_batches
+    dominant = max(kernel_s, key=kernel_s.get)
+    peak = min(measure_fma_peak(64 if f64 else 32, dev), FP32_PEAK_TFLOPS / (2 if f64 else 1))
+    per_gpu = atoms / (ms * 1e-3) / ctx.world
+    return {"workload": CASE_WORKLOAD[case], "atoms_per_s": atoms / (ms * 1e-3), "us_per_step": ms * 1e3 / n_batches,
+            "atoms_per_step": mean_atoms, "streams": n_streams, "resident_batches": n_batches,
+            "kernels_us": {k: v * 1e6 for k, v in kernel_s.items()}, "dominant_kernel": dominant,
+            "dominant_frac_of_arith_peak": flops[dominant] * mean_atoms / kernel_s[dominant] / 1e12 / peak,
+            "whole_step_frac_of_arith_peak": (flops["featurize"] + flops["featurize_grad"]) * per_gpu / 1e12 / peak,
+            "arith_peak_tflops": peak, "arith_peak": ("FP64" if f64 else "FP32") + ": " + CASE_FLOP_PEAK_NOTE,
+            "pairs_per_atom": p, "triplets_per_atom": t}
+
+
+def measure_sharded(ctx, steps=64):
+    """Benchmark configuration 1 as ONE 1024-molecule batch cut into contiguous molecule ranges over the
+    ranks (khan_b200.data.sharding): every rank sorts, featurizes and differentiates its own shard on its
+    GPU, no collective on the data path.  The time of a step is the max over ranks.  Rank 0 also runs the
+    whole batch alone and checks the reassembled feature rows (atom order) against it bit for bit."""
+    import torch
+    import torch.distributed as dist
+    from khan_b200.data import sharding, synthetic as syn
+    from khan_b200.staged import HostBatch, StagedBatch
+    dev, rank, world = ctx.dev, ctx.rank, ctx.world
+    batch = syn.config1(seed=1, n_mols=N_MOLS)
+    bounds = sharding.shard_bounds(batch.mol_atom_counts, world)
+    shard = sharding.shard_batch(batch, rank, world)
+
+    def stage(b):
+        ac = np.bincount(b.atomic_numbers, minlength=4)
+        sb = StagedBatch(max(1, b.n_atoms), max(1, b.n_mols), device=dev)
+        sb.upload(HostBatch(b, syn.upstream_grads(b, ac, seed=12), pin=False), non_blocking=False)
+        return sb
+
+    sb = stage(shard)
+    for _ in range(3):
+        sb.run_step()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(steps):
+            sb.run_step()
+    g.replay()
+    times = []
+    for _ in range(5):
+        ctx.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms, atoms = ctx.max_sum(statistics.median(times), float(shard.n_atoms) * steps)
+
+    # reassemble the shards' feature rows in atom order on rank 0
+    atoms_of = [int(batch.mol_atom_counts[a:b].sum()) for a, b in bounds]
+    pad = max(atoms_of)
+    mine = torch.zeros((pad, FEATURE_SIZE), dtype=torch.float32, device=dev)
+    mine[:shard.n_atoms] = sb.features[:shard.n_atoms][sb.gather[:shard.n_atoms].long()]
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    out = {"ms_per_step": ms / steps, "atoms_per_s": atoms / (ms * 1e-3), "n_gpus": world, "steps": steps,
+           "atoms_per_shard": atoms_of,
+           "note": "one 1024-molecule batch (13.7 k atoms) cut by molecule ranges; every step repeats the same shard, "
+                   "which stays in L2; no data-path collective"}
+    if rank == 0:
+        whole = stage(batch)
+        whole.run_step()
+        torch.cuda.synchronize()
+        ref = whole.features[:batch.n_atoms][whole.gather[:batch.n_atoms].long()]
+        got = torch.cat([p[:n] for p, n in zip(parts, atoms_of)])
+        out["features_equal_single_gpu_bit_for_bit"] = bool(torch.equal(got, ref))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -648,6 +910,10 @@ def main():
                          "(256 molecules of 64-256 atoms, float32) are extra measurements")
     ap.add_argument("--profile", action="store_true",
                     help="only W warm-up and K timed steps, launched eagerly on one stream (for ncu)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra keys of the line (config3 training step, sharded config 1, config2 / config4, "
+                         "energies + forces end to end)")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of exactly K steps each; the median is reported")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -672,14 +938,8 @@ def main():
     from khan_b200.data import synthetic as syn
     from khan_b200.staged import HostBatch, StagedBatch
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    ctx = Ctx()
+    rank, world, local_rank, dev = ctx.rank, ctx.world, ctx.local_rank, ctx.dev
     _lib.lib()  # fail loudly if the CUDA library is missing
 
     sampler = ClockSampler(local_rank)
@@ -707,6 +967,7 @@ def main():
         staged.append(sb)
     torch.cuda.synchronize()
     atoms_per_step = [sb.n_atoms for sb in staged]
+    launches_per_step = staged[0].kernels_per_step()
 
     def stream_ptr():
         return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -741,24 +1002,9 @@ def main():
                 with torch.cuda.graph(g):
                     sb.run_step(stream_ptr())
                 graphs.append(g)
-            def capture_overlapped(batches_to_run):
-                """One graph that runs the given staged batches on the side streams, round-robin."""
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    cap = torch.cuda.current_stream()
-                    for st in side:
-                        st.wait_stream(cap)
-                    for b, sb in enumerate(batches_to_run):
-                        st = side[b % n_streams]
-                        with torch.cuda.stream(st):
-                            sb.run_step(ctypes.c_void_p(st.cuda_stream))
-                    for st in side:
-                        cap.wait_stream(st)
-                return g
-
-            mega = capture_overlapped(staged)
+            mega = capture_overlapped(staged, side)
             # the K steps of the timed region are whole passes over the pool plus this remainder
-            tail = capture_overlapped(staged[:args.steps % nb]) if args.steps % nb else None
+            tail = capture_overlapped(staged[:args.steps % nb], side) if args.steps % nb else None
             launch_mode = "cuda_graph"
         except Exception as exc:
             print(f"[bench] CUDA graph capture failed ({exc!r}); launching eagerly", file=sys.stderr)
@@ -792,30 +1038,25 @@ def main():
         run_steps(nb)
         torch.cuda.synchronize()
 
-    # ---- timed region: exactly K steps -----------------------------------------------------
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_timed0 = time.perf_counter()
-    ev0.record()
-    run_steps(args.steps)
-    ev1.record()
-    torch.cuda.synchronize()
-    t_timed1 = time.perf_counter()
-    if world > 1:
-        dist.barrier()
-    elapsed_ms = ev0.elapsed_time(ev1)
+    # ---- timed regions: exactly K steps each, between a barrier + synchronize on both sides; the
+    # median region gives the headline and every region is listed (at the driver's K the region is
+    # a single graph replay of under a millisecond, so one region alone is at the mercy of jitter) ----
     my_atoms = sum(atoms_per_step[k % nb] for k in range(args.steps))
-    if world > 1:
-        t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-        a = torch.tensor([my_atoms], dtype=torch.float64, device=dev)
-        dist.all_reduce(a, op=dist.ReduceOp.SUM)
-        total_atoms = float(a.item())
-    else:
-        total_atoms = float(my_atoms)
+    region_ms = []
+    t_timed0 = time.perf_counter()
+    for _ in range(max(1, args.repeats)):
+        ctx.barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        run_steps(args.steps)
+        ev1.record()
+        torch.cuda.synchronize()
+        ctx.barrier()
+        ms, total_atoms = ctx.max_sum(ev0.elapsed_time(ev1), float(my_atoms))
+        region_ms.append(ms)
+    t_timed1 = time.perf_counter()
+    elapsed_ms = statistics.median(region_ms)
     value = total_atoms / (elapsed_ms * 1e-3)
 
     # ---- spread: passes over the resident pool timed one by one (not part of the headline) ----
@@ -830,32 +1071,10 @@ def main():
         pass_ms = sorted(a.elapsed_time(b) / nb for a, b in zip(evs[:-1], evs[1:]))
 
     # ---- per-kernel durations (graphs of one kernel kind over all batches) ------------------
-    def time_kernel(fn_name):
-        g = torch.cuda.CUDAGraph()
-        try:
-            with torch.cuda.graph(g):
-                for sb in staged:
-                    getattr(sb, fn_name)(stream_ptr())
-            run = g.replay
-        except Exception:
-            torch.cuda.synchronize()
-
-            def run():
-                for sb in staged:
-                    getattr(sb, fn_name)(stream_ptr())
-        reps = max(3, min(50, args.steps // nb))
-        run()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            run()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) * 1e-3 / (reps * nb)
-
-    kernel_s = {"ani_sort": time_kernel("run_sort"), "featurize": time_kernel("run_featurize"),
-                "featurize_grad": time_kernel("run_featurize_grad")}
+    reps = max(3, min(50, args.steps // nb))
+    kernel_s = {"ani_sort": time_kernel_alone(staged, "run_sort", reps),
+                "featurize": time_kernel_alone(staged, "run_featurize", reps),
+                "featurize_grad": time_kernel_alone(staged, "run_featurize_grad", reps)}
     t_load1 = time.perf_counter()
 
     # ---- end to end through the C ABI with host buffers ---------------------------------------
@@ -879,44 +1098,109 @@ def main():
                 atoms += slots[s].n_atoms
         return h2d, d2h, atoms
 
+    def copy_pass(n_steps):
+        """The transfers of e2e_pass with no kernel between them: what the host link alone allows."""
+        h2d = d2h = 0
+        for k in range(n_steps):
+            s = k % n_slots
+            with torch.cuda.stream(streams[s]):
+                h2d += slots[s].upload(host[k % n_host], non_blocking=True)
+                d2h += slots[s].download(out_feat[s], out_grad[s], non_blocking=True)
+        return h2d, d2h
+
+    main_stream = torch.cuda.current_stream()
+
+    def timed_host_passes(fn, n_passes=3):
+        """ms of each of n_passes calls of fn (max over ranks), with the streams fenced on both sides."""
+        out, last = [], None
+        for _ in range(n_passes):
+            ctx.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(main_stream)
+            for st in streams:
+                st.wait_event(e0)
+            last = fn()
+            for st in streams:
+                main_stream.wait_stream(st)
+            e1.record(main_stream)
+            torch.cuda.synchronize()
+            out.append(ctx.max_sum(e0.elapsed_time(e1), 0.0)[0])
+        return out, last
+
     e2e_pass(6)
     torch.cuda.synchronize()
-    main_stream = torch.cuda.current_stream()
-    # Three timed passes of e2e_steps steps each; the fastest is reported (all are listed).  The
-    # transfers share the host's PCIe root with whatever else runs on the machine, and a single
-    # pass was seen 30 % slower than its neighbours.
-    e2e_runs = []
-    for _ in range(3):
-        if world > 1:
-            dist.barrier()
+    # Three timed passes of e2e_steps steps each; the median is the reported value, the best is listed
+    # beside it.  The transfers share the host's PCIe root and memory with whatever else runs on the
+    # machine (all ranks of a multi-GPU run included).
+    e2e_runs, (h2d, d2h, e2e_atoms) = timed_host_passes(lambda: e2e_pass(e2e_steps))
+    e2e_ms = statistics.median(e2e_runs)
+    _, e2e_total = ctx.max_sum(0.0, float(e2e_atoms))
+    copy_runs, (c_h2d, c_d2h) = timed_host_passes(lambda: copy_pass(e2e_steps))
+    copy_ms = statistics.median(copy_runs)
+    e2e_extra = {"copy_only": {"atoms_per_s": e2e_total / (copy_ms * 1e-3),
+                               "gbs_per_rank": (c_h2d + c_d2h) / (copy_ms * 1e-3) / 1e9,
+                               "note": "the same host-to-device and device-to-host copies with no kernel launched: "
+                                       "the ceiling that the host link sets for this definition of end to end"}}
+    del slots, out_feat
+
+    # ---- energies + forces end to end: coordinates in, molecule energies and forces out -----------
+    e2e_forces = None
+    if not args.no_extras and args.case == "config1":
+        from khan_b200.inference import EnergyForces
+        from khan_b200.model import activations
+        from khan_b200.model.nn import MoleculeNN
+        model = MoleculeNN(activation_fn=activations.gaussian, device=dev, seed=1, init="he")
+        fslots = [StagedBatch(max_atoms, args.mols, device=dev) for _ in range(n_slots)]
+        evs = [EnergyForces(model, max_atoms, args.mols, device=dev) for _ in range(n_slots)]
+        out_e = [torch.empty(args.mols, dtype=torch.float32).pin_memory() for _ in range(n_slots)]
+        model.pack_weights(ctypes.c_void_p(main_stream.cuda_stream))
+
+        def forces_pass(n_steps):
+            h2d = d2h = atoms = 0
+            for k in range(n_steps):
+                i = k % n_slots
+                hb = host[k % n_host]
+                with torch.cuda.stream(streams[i]):
+                    h2d += fslots[i].upload(hb, non_blocking=True, with_upstream=False)
+                    evs[i].run(fslots[i], ctypes.c_void_p(streams[i].cuda_stream), pack=False)
+                    n, m = fslots[i].n_atoms, fslots[i].n_mols
+                    out_e[i][:m].copy_(evs[i].mol_energy[:m], non_blocking=True)
+                    for r in range(3):
+                        out_grad[i][r, :n].copy_(fslots[i].grads[r, :n], non_blocking=True)
+                    d2h += 4 * (m + 3 * n)
+                    atoms += n
+            return h2d, d2h, atoms
+
+        forces_pass(6)
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(main_stream)
-        for st in streams:
-            st.wait_event(e0)
-        h2d, d2h, e2e_atoms = e2e_pass(e2e_steps)
-        for st in streams:
-            main_stream.wait_stream(st)
-        e1.record(main_stream)
-        torch.cuda.synchronize()
-        run_ms = e0.elapsed_time(e1)
+        f_runs, (f_h2d, f_d2h, f_atoms) = timed_host_passes(lambda: forces_pass(e2e_steps))
+        f_ms = statistics.median(f_runs)
+        _, f_total = ctx.max_sum(0.0, float(f_atoms))
+        e2e_forces = {"value": f_total / (f_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": f_h2d / e2e_steps,
+                      "d2h_bytes_per_step": f_d2h / e2e_steps, "steps": e2e_steps, "pipeline_slots": n_slots,
+                      "passes_atoms_per_s": [f_total / (ms * 1e-3) for ms in f_runs], "reported": "median of 3 passes",
+                      "workload": "coordinates, element ids and molecule table in; molecule energies and dE/dx, dE/dy, "
+                                  "dE/dz out (sort + featurize + 4 atomic networks forward and backward + featurize_grad, "
+                                  "C-ABI calls only): the boundary predict / coordinate_gradients use"}
+        del fslots, evs
+
+    # ---- the other benchmark configurations, as extra keys of the same line -----------------------
+    extras = {}
+    if not args.no_extras and args.case == "config1" and args.mols == N_MOLS:
+        del staged, mega, tail, graphs
+        torch.cuda.empty_cache()
+        extras["config3"] = measure_fused_train(ctx, N_MOLS, steps=max(64, min(args.steps, 512)), warmup=args.warmup)
+        extras["config3"]["workload"] = ("config3: config-1 batch per GPU -> sort + featurize + 4 x MLP 384-128-128-64-1 "
+                                         "(gaussian, He init) + MSE + backward into weights and coordinates + NCCL "
+                                         "all-reduce of the weight gradients + Nadam")
         if world > 1:
-            t = torch.tensor([run_ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            run_ms = float(t.item())
-        e2e_runs.append(run_ms)
-    e2e_ms = min(e2e_runs)
-    if world > 1:
-        a = torch.tensor([e2e_atoms], dtype=torch.float64, device=dev)
-        dist.all_reduce(a, op=dist.ReduceOp.SUM)
-        e2e_total = float(a.item())
-    else:
-        e2e_total = float(e2e_atoms)
+            extras["config1_sharded"] = measure_sharded(ctx)
+        extras["cases"] = {c: measure_case(ctx, c) for c in ("config2", "config4")}
     sampler.stop()
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        ctx.close()
         return
 
     # ---- roofline of the dominant kernel --------------------------------------------------------
@@ -937,6 +1221,7 @@ def main():
                 "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"],
                 "traffic": (NCU_DRAM_BYTES_PER_ATOM[dominant] * mean_atoms
                             if args.case == "config1" and NCU_DRAM_BYTES_PER_ATOM.get(dominant) else None),
+                "traffic_source": NCU_TRAFFIC_SOURCE if args.case == "config1" else None,
                 "peak_source": peak_kind,
                 "algorithmic_bytes_per_launch": bytes_per_atom[dominant] * mean_atoms}
     formula_peak = FP32_PEAK_TFLOPS / (2 if args.case == "config2" else 1)
@@ -948,6 +1233,9 @@ def main():
                                     "1.965 GHz; half of that for float64)",
                      "peak_measured": fma_measured, "peak_formula": formula_peak,
                      "pairs_per_atom": p_per_atom, "triplets_per_atom": t_per_atom}
+    # the bound that binds is the one with the larger fraction: the arithmetic one for these kernels
+    roofline["binding_bound"] = ("fp32/fp64 arithmetic (roofline_fp32)" if roofline_fp32["frac"] >= roofline["frac"]
+                                 else "hbm")
     step_flops = (flops_per_atom["featurize"] + flops_per_atom["featurize_grad"])
     per_gpu = value / world
     whole_step = {"per_gpu_tflops": step_flops * per_gpu / 1e12,
@@ -957,6 +1245,8 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "timed_regions": {"ms_per_step": [ms / args.steps for ms in region_ms], "steps_each": args.steps,
+                          "reported": "median region"},
         "ms_per_step_by_pass": ({"median": pass_ms[len(pass_ms) // 2], "best": pass_ms[0], "worst": pass_ms[-1],
                                  "passes": len(pass_ms), "steps_per_pass": nb} if pass_ms else None),
         "scaling": "weak", "vs_baseline": None, "dtype": "f64" if args.case == "config2" else "f32",
@@ -969,13 +1259,18 @@ def main():
         "e2e": {"value": e2e_total / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": h2d / e2e_steps, "d2h_bytes_per_step": d2h / e2e_steps,
                 "steps": e2e_steps, "pipeline_slots": n_slots,
-                "passes_atoms_per_s": [e2e_total / (ms * 1e-3) for ms in e2e_runs], "reported": "fastest of 3 passes"},
-        "gpu_launches": args.steps * StagedBatch.KERNELS_PER_STEP,
+                "passes_atoms_per_s": [e2e_total / (ms * 1e-3) for ms in e2e_runs],
+                "best_atoms_per_s": e2e_total / (min(e2e_runs) * 1e-3), "reported": "median of 3 passes",
+                **e2e_extra},
+        "gpu_launches": args.steps * launches_per_step,
         "kernels": {k: {"avg_us": v * 1e6} for k, v in kernel_s.items()},
         "roofline": roofline, "roofline_fp32": roofline_fp32, "whole_step": whole_step,
         "clocks": sampler.summary(t_load0, t_load1),
         "clocks_timed_region": sampler.summary(t_timed0, t_timed1),
     }
+    if e2e_forces is not None:
+        line["e2e_forces"] = e2e_forces
+    line.update(extras)
     if world == 1 and not args.no_cpu_baseline and args.case == "config1":
         try:
             line["cpu_baseline"] = cpu_baseline(batches[0])
@@ -983,8 +1278,7 @@ def main():
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port",
                                     "sample": f"failed: {exc!r}"}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    ctx.close()
 
 
 if __name__ == "__main__":

@@ -59,13 +59,6 @@ const char* ani_status_string(int status);
 /* cudaGetErrorString of the last CUDA failure seen by this library on the calling thread. */
 const char* ani_last_cuda_error(void);
 
-/* Measurement aid, no counterpart in the reference: enqueues one kernel that does nothing
- * but `iterations` x 8 independent fused multiply-adds per thread on every SM (precision_bits
- * 32 or 64) and stores the number of floating-point operations it executes in *flops_host.
- * Timed by the caller, it gives the arithmetic peak that the featurizer kernels are compared
- * with.  `sink` is any 8 bytes of device memory (never written in practice). */
-int ani_fma_probe(int precision_bits, int iterations, void* sink, long long* flops_host, void* stream);
-
 /* Synchronises `stream`, then returns and clears the current device's status word:
  * ANI_OK or the first ANI_ERR_BAD_ELEMENT / ANI_ERR_BAD_INDEX seen by
  * a kernel since the last call.  No counterpart in the reference, which does not validate

@@ -17,7 +17,7 @@ LIB_PATH = os.environ.get("ANI_B200_LIB") or os.path.join(_HERE, "libani_b200.so
 CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
-HEADERS = ["ani_params.h", "ani_common.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_grad.cuh",
+HEADERS = ["ani_params.h", "ani_common.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_featurize_mol.cuh", "ani_grad.cuh", "ani_grad_mol.cuh",
            "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh", "ani_energy.cuh", "ani_host_pack.h"]
 
 NVCC_FLAGS = [
@@ -76,7 +76,6 @@ SIGNATURES = {
     "ani_feature_size": (_i, []),
     "ani_status_string": (ctypes.c_char_p, [_i]),
     "ani_last_cuda_error": (ctypes.c_char_p, []),
-    "ani_fma_probe": (_i, [_i, _i, _vp, ctypes.POINTER(ctypes.c_longlong), _vp]),
     "ani_device_status": (_i, [_vp]),
     "ani_sort": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
     "ani_sort_noalloc": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),

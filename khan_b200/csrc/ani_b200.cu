@@ -435,23 +435,6 @@ template <int ACT> int mlp_launch_act(const MlpParams& p, int n_tiles, bool spli
     return split ? mlp_launch<ACT, true>(p, n_tiles, st) : mlp_launch<ACT, false>(p, n_tiles, st);
 }
 
-// Arithmetic-peak probe: 8 independent fused multiply-add chains per thread, nothing else.
-template <typename T> __global__ void __launch_bounds__(256) fma_probe_kernel(int iterations, T seed, T* sink)
-{
-    T a[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) a[k] = seed + (T)(threadIdx.x + k);
-    const T m = (T)0.999, c = (T)1e-3;
-    for (int it = 0; it < iterations; it++) {
-#pragma unroll
-        for (int k = 0; k < 8; k++) a[k] = a[k] * m + c;
-    }
-    T sum = (T)0;
-#pragma unroll
-    for (int k = 0; k < 8; k++) sum += a[k];
-    if (sum == (T)-1) sink[0] = sum;   // never true; keeps the chains alive
-}
-
 }  // namespace
 
 extern "C" {
@@ -475,23 +458,6 @@ const char* ani_status_string(int status)
 }
 
 const char* ani_last_cuda_error(void) { return cudaGetErrorString(t_last_error); }
-
-int ani_fma_probe(int precision_bits, int iterations, void* sink, long long* flops_host, void* stream)
-{
-    if (!sink || !flops_host) return ANI_ERR_NULL_POINTER;
-    if (iterations < 0 || (precision_bits != 32 && precision_bits != 64)) return ANI_ERR_BAD_SIZE;
-    int dev = 0, sms = 0;
-    ANI_CUDA(cudaGetDevice(&dev));
-    ANI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const int blocks = sms * 8, threads = 256;
-    if (precision_bits == 32)
-        fma_probe_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(iterations, 1.0f, (float*)sink);
-    else
-        fma_probe_kernel<double><<<blocks, threads, 0, (cudaStream_t)stream>>>(iterations, 1.0, (double*)sink);
-    ANI_CUDA(cudaGetLastError());
-    *flops_host = 2LL * 8 * iterations * (long long)blocks * threads;
-    return ANI_OK;
-}
 
 int ani_device_status(void* stream)
 {

@@ -94,4 +94,4 @@ class EnergyForces:
                    "ani_mlp_backward_f32")
         sb.run_featurize_grad(stream)
 
-    KERNELS_PER_PASS = 8   # weight packing (unless pack=False), sort, featurize, mlp forward, molecule sums, mlp backward, zero fill, featurize_grad
+    KERNELS_PER_PASS = 7   # weight packing (unless pack=False), sort, featurize, mlp forward, molecule sums, mlp backward, featurize_grad

@@ -122,14 +122,20 @@ class StagedBatch:
                    "ani_featurize_grad_" + self.suffix)
 
     def run_step(self, stream: ctypes.c_void_p | None = None) -> None:
-        """One pass of the hot path: sort, forward, coordinate gradient (4 kernel launches)."""
+        """One pass of the hot path: sort, forward, coordinate gradient (``kernels_per_step()`` launches)."""
         if stream is None:
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         self.run_sort(stream)
         self.run_featurize(stream)
         self.run_featurize_grad(stream)
 
-    KERNELS_PER_STEP = 4  # sort, featurize, zero fill of the gradients, featurize_grad
+    KERNELS_PER_STEP = 3  # sort, featurize, featurize_grad (batches of small molecules)
+
+    def kernels_per_step(self) -> int:
+        """Kernel launches of ``run_step`` for the current batch: 3 for a batch of small molecules (mean
+        size <= 24 atoms, the rule of the library's dispatch), else 4 -- the gradient kernel for large
+        molecules accumulates with atomics and is preceded by a zero fill of its outputs."""
+        return 3 if self.n_mols > 0 and self.n_atoms <= 24 * self.n_mols else 4
 
 
 class HostBatch:

@@ -157,7 +157,7 @@ class FusedTrainStep:
         self.coordinate_gradient(sb)
         self.optimizer.step()
 
-    KERNELS = 12   # weight packing, sort, featurize, mlp fwd, molecule energy, mlp bwd, memset, wgrad, zero3, featurize_grad, sumsq, nadam
+    KERNELS = 11   # weight packing, sort, featurize, mlp fwd, molecule energy, mlp bwd, memset, wgrad, featurize_grad, sumsq, nadam
 
 
 class StepPipeline:
