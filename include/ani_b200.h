@@ -48,6 +48,7 @@ extern "C" {
 #define ANI_ERR_TOO_MANY_ATOMS (-7) /* size beyond what an entry point supports          */
 #define ANI_ERR_TIMEOUT (-8)        /* a bounded device-side wait ran out (status word)    */
 #define ANI_ERR_MISALIGNED (-9)     /* a pointer that must be 16-byte aligned is not       */
+#define ANI_ERR_CAPTURE (-10)       /* first-use set-up attempted while the stream is being captured */
 
 /* Number of features per atom (384).  Replaces the `feature_size` attr of the Featurize op
  * (gpu_featurizer/ani_op.cpp:104). */
@@ -73,6 +74,18 @@ int ani_device_status(void* stream);
  *   gather_idxs[i]  = position of atom i in the element-sorted concatenation;
  *   atom_counts[4]  = atoms per element (device memory, 4 ints).
  * The input is read on the device (the reference reads it on the host).
+ *
+ * Up to 65,536 atoms the call is one launch and uses no memory beyond its arguments.  Larger
+ * batches take three launches and a scratch buffer of (n_atoms / 1024 + 2) x 16 bytes that the
+ * library allocates and keeps, one per (device, stream):
+ *  - calls on different streams never share scratch, so they may overlap; calls on one stream
+ *    run in stream order and share theirs;
+ *  - the first large call on a stream (or the first one with more atoms than any before it)
+ *    calls cudaMalloc: make it outside any stream capture -- inside one it is refused with
+ *    ANI_ERR_CAPTURE and nothing is launched;
+ *  - a buffer that is outgrown is replaced but not freed (a captured graph may still hold its
+ *    address); all of them are released when the process ends.
+ * ani_sort_noalloc below never allocates.
  */
 int ani_sort(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gather_idxs,
              int* atom_counts, void* stream);
@@ -93,7 +106,8 @@ int ani_sort(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gat
  *    with ANI_ERR_TOO_MANY_ATOMS before anything is launched.  The array costs 64 KiB of
  *    device memory on every GPU that loads the library, for the life of the process.
  *  - The first call on each device looks up the array's device address (with that device
- *    current) and remembers it; make that first call before any stream capture.
+ *    current) and remembers it; make that first call before any stream capture (a first call
+ *    whose stream is being captured is refused with ANI_ERR_CAPTURE).
  *  - All calls on one device share the one array, and it keeps the previous call's contents.
  *    Every entry a call reads it has written first, so nothing needs clearing, but two calls
  *    that overlap on the GPU (different streams, or different host threads) race on it:

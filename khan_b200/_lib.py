@@ -153,6 +153,23 @@ def lib() -> ctypes.CDLL:
         return _lib
 
 
+def same_device(device, *tensors, where: str = "kernel launch") -> None:
+    """Raises unless every given tensor (None entries are skipped) lives on ``device``.  Every pointer
+    that goes into a launch must belong to the launching device: the kernels use plain loads and
+    stores, peer access between devices is never enabled, and a pointer into another GPU's memory
+    would fault on the device."""
+    import torch
+    dev = torch.device(device)
+    want = (dev.type, dev.index if dev.index is not None else (torch.cuda.current_device() if dev.type == "cuda" else None))
+    for t in tensors:
+        if t is None:
+            continue
+        have = (t.device.type, t.device.index)
+        if have != want:
+            raise ValueError(f"{where}: a tensor on {t.device} was passed to a launch on {dev}; "
+                             "all buffers and weights of a call must be on the launching GPU")
+
+
 class AniError(RuntimeError):
     """A C-ABI call returned a negative status."""
 

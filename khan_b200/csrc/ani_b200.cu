@@ -8,6 +8,7 @@
 
 #include <initializer_list>
 #include <mutex>
+#include <vector>
 
 #include "ani_common.cuh"
 
@@ -45,31 +46,55 @@ int cuda_fail(cudaError_t e)
 
 constexpr int kMaxDevices = 64;
 
-// Per-device scratch for the large-batch sort (per-tile element counts).  Grown on demand,
-// never shrunk, freed with the context.
+// Scratch of the large-batch sort (per-tile element counts), one buffer per (device, stream): two
+// calls that overlap on the GPU are on different streams and so never share a buffer.  A buffer
+// that has become too small is replaced but NEVER freed -- its address may be recorded in a CUDA
+// graph that is replayed later -- so the old ones stay allocated until the process ends (they are
+// a few KiB each and grow geometrically).
 struct SortScratch {
-    int* ptr = nullptr;
-    size_t bytes = 0;
+    int dev;
+    cudaStream_t stream;
+    int* ptr;
+    size_t bytes;
 };
 std::mutex g_scratch_mutex;
-SortScratch g_sort_scratch[kMaxDevices];
+std::vector<SortScratch> g_sort_scratch;
 
-int sort_scratch(size_t bytes, int** out)
+// True when work given to `stream` is being recorded into a graph instead of run.
+int stream_is_capturing(cudaStream_t stream, bool* capturing)
+{
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    ANI_CUDA(cudaStreamIsCapturing(stream, &status));
+    *capturing = status != cudaStreamCaptureStatusNone;
+    return ANI_OK;
+}
+
+int sort_scratch(size_t bytes, cudaStream_t stream, int** out)
 {
     int dev = 0;
     ANI_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) return ANI_ERR_BAD_SIZE;
     std::lock_guard<std::mutex> lock(g_scratch_mutex);
-    SortScratch& s = g_sort_scratch[dev];
-    if (s.bytes < bytes) {
-        if (s.ptr) ANI_CUDA(cudaFree(s.ptr));
-        s.ptr = nullptr;
-        s.bytes = 0;
-        size_t want = bytes < (1u << 16) ? (1u << 16) : bytes * 2;
-        ANI_CUDA(cudaMalloc(&s.ptr, want));
-        s.bytes = want;
+    SortScratch* slot = nullptr;
+    for (SortScratch& s : g_sort_scratch)
+        if (s.dev == dev && s.stream == stream) slot = &s;
+    if (slot && slot->bytes >= bytes) {
+        *out = slot->ptr;
+        return ANI_OK;
     }
-    *out = s.ptr;
+    // an allocation is not something a stream capture can record
+    bool capturing = false;
+    if (int rc = stream_is_capturing(stream, &capturing)) return rc;
+    if (capturing) return ANI_ERR_CAPTURE;
+    const size_t want = bytes < (1u << 16) ? (1u << 16) : bytes * 2;
+    int* ptr = nullptr;
+    ANI_CUDA(cudaMalloc(&ptr, want));
+    if (slot) {
+        slot->ptr = ptr;       // the previous buffer stays allocated (see above)
+        slot->bytes = want;
+    } else {
+        g_sort_scratch.push_back(SortScratch{dev, stream, ptr, want});
+    }
+    *out = ptr;
     return ANI_OK;
 }
 
@@ -86,13 +111,18 @@ static __device__ __align__(256) int g_sort_static_scratch[(kSortStaticMaxTiles 
 int* g_sort_static_ptr[kMaxDevices] = {};
 std::mutex g_sort_static_mutex;
 
-int sort_static_scratch(int** out)
+int sort_static_scratch(cudaStream_t stream, int** out)
 {
     int dev = 0;
     ANI_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return ANI_ERR_BAD_SIZE;
     std::lock_guard<std::mutex> lock(g_sort_static_mutex);
     if (!g_sort_static_ptr[dev]) {
+        // The look-up may load the module's data on this device: not something to do while the stream
+        // is being captured.  Make the first call on a device outside any capture.
+        bool capturing = false;
+        if (int rc = stream_is_capturing(stream, &capturing)) return rc;
+        if (capturing) return ANI_ERR_CAPTURE;
         int* ptr = nullptr;
         ANI_CUDA(cudaGetSymbolAddress((void**)&ptr, g_sort_static_scratch));  // current device = dev
         g_sort_static_ptr[dev] = ptr;
@@ -453,6 +483,9 @@ const char* ani_status_string(int status)
         case ANI_ERR_TOO_MANY_ATOMS: return "size beyond what this entry point supports";
         case ANI_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case ANI_ERR_MISALIGNED: return "a pointer that must be 16-byte aligned is not";
+        case ANI_ERR_CAPTURE:
+            return "first-use set-up (scratch allocation or address look-up) cannot run while the stream is being "
+                   "captured: make the same call once outside the capture";
         default: return "unknown status";
     }
 }
@@ -491,7 +524,7 @@ int ani_sort(const int* atomic_numbers, int n_atoms, int* scatter_idxs, int* gat
         return ANI_OK;
     }
     int* scratch = nullptr;
-    if (int rc = sort_scratch((size_t)(n_tiles + 1) * kTypes * sizeof(int), &scratch)) return rc;
+    if (int rc = sort_scratch((size_t)(n_tiles + 1) * kTypes * sizeof(int), st, &scratch)) return rc;
     sort_histogram_kernel<<<n_tiles, kSortThreads, 0, st>>>(atomic_numbers, n_atoms, scratch);
     ANI_CUDA(cudaGetLastError());
     sort_scan_kernel<<<1, kSortThreads, 0, st>>>(scratch, n_tiles);
@@ -516,7 +549,7 @@ int ani_sort_noalloc(const int* atomic_numbers, int n_atoms, int* scatter_idxs, 
     }
     if (!atomic_numbers || !scatter_idxs || !gather_idxs) return ANI_ERR_NULL_POINTER;
     int* scratch = nullptr;
-    if (int rc = sort_static_scratch(&scratch)) return rc;
+    if (int rc = sort_static_scratch(st, &scratch)) return rc;
     // Every scratch entry that is read is written first by the same call (the histogram kernel
     // fills entries [0, n_tiles), the scan kernel entry n_tiles), so nothing has to be cleared.
     const int n_tiles = (n_atoms + kSortTile - 1) / kSortTile;

@@ -42,7 +42,9 @@ class RawDataset:
             mol_Xs = np.concatenate(mols, axis=0)  # a copy: safe to modify
             mol_ids = np.repeat(np.arange(len(mols)), counts)
             if fuzz is not None:
-                mol_Xs[:, 1:4] += np.random.uniform(-fuzz, fuzz, mol_Xs[:, 1:4].shape)
+                # x of all atoms, then y, then z: the order in which the reference consumes numpy's
+                # stream (khan/data/dataset.py:166-169), so a seed gives the same perturbed batch
+                mol_Xs[:, 1:4] += np.random.uniform(-fuzz, fuzz, (3, mol_Xs.shape[0])).T
             mol_yts = [self.all_ys[p] for p in picks] if self.all_ys is not None else None
             mol_grads = (np.concatenate([self.all_grads[p] for p in picks], axis=0)
                          if self.all_grads is not None else None)

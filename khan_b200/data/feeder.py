@@ -53,12 +53,25 @@ class PackedDataset:
 
     @classmethod
     def from_raw(cls, raw, dtype=np.float32) -> "PackedDataset":
-        """Packs ``raw`` once per precision and keeps the result on the RawDataset object."""
+        """Packs ``raw`` once per precision and keeps the result on the RawDataset object.  The packed copy
+        is a SNAPSHOT: it is rebuilt when one of the three lists is replaced or changes its length, but an
+        edit of an array inside them (say, subtracting an offset from ``all_ys`` in place) is not seen --
+        call ``PackedDataset.invalidate(raw)`` after such an edit."""
         cache = raw.__dict__.setdefault("_packed", {})
         key = np.dtype(dtype).name
-        if key not in cache or cache[key][0] is not raw.all_Xs:
-            cache[key] = (raw.all_Xs, cls(raw.all_Xs, raw.all_ys, raw.all_grads, dtype))
+
+        def stamp():
+            return tuple((id(lst), None if lst is None else len(lst)) for lst in (raw.all_Xs, raw.all_ys, raw.all_grads))
+
+        if key not in cache or cache[key][0] != stamp():
+            cache[key] = (stamp(), cls(raw.all_Xs, raw.all_ys, raw.all_grads, dtype), raw.all_Xs, raw.all_ys,
+                          raw.all_grads)        # the lists are kept alive so that their ids stay theirs
         return cache[key][1]
+
+    @staticmethod
+    def invalidate(raw) -> None:
+        """Forgets the packed copies of ``raw`` (after its arrays were edited in place)."""
+        raw.__dict__.pop("_packed", None)
 
     def num_mols(self) -> int:
         return len(self.counts)
@@ -85,9 +98,9 @@ class PackedDataset:
                 or (self.ys is not None and self.ys.shape[0] != self.num_mols())):
             raise ValueError("the arrays of the packed dataset do not match its molecule table")
         noise = None
-        if fuzz is not None:   # same draw as RawDataset.iterate: uniform over an (n, 3) array
+        if fuzz is not None:   # same draws as RawDataset.iterate: x of all atoms, then y, then z
             n = int(self.counts[picks].sum())
-            noise = np.random.uniform(-fuzz, fuzz, (n, 3))
+            noise = np.ascontiguousarray(np.random.uniform(-fuzz, fuzz, (3, n)).T)
         a = _lib.HostPackArgs()
         a.picks, a.n_picks, a.n_mols_total = picks.ctypes.data, m, self.num_mols()
         a.mol_ptr = self.ptr.ctypes.data
@@ -127,8 +140,8 @@ class PackedDataset:
         slot.n_atoms, slot.n_mols = n, m
         if fuzz is None:
             slot.xyz[:, :n] = self.xyz[:, src]
-        else:   # same draw as RawDataset.iterate: uniform over an (n, 3) array
-            slot.xyz[:, :n] = self.xyz[:, src] + np.random.uniform(-fuzz, fuzz, (n, 3)).T
+        else:   # same draws as RawDataset.iterate: x of all atoms, then y, then z
+            slot.xyz[:, :n] = self.xyz[:, src] + np.random.uniform(-fuzz, fuzz, (3, n))
         slot.types[:n] = self.types[src]
         slot.mol_offsets[:m] = offsets
         slot.mol_counts[:m] = counts

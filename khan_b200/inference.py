@@ -31,6 +31,7 @@ class EnergyForces:
             raise ValueError("EnergyForces needs the fused float32 384-128-128-64-1 networks")
         self.model = model
         self.device = torch.device(device)
+        _lib.same_device(self.device, *model.get_parameters(), where="EnergyForces")
         self.act_id = activations.KERNEL_ID[model.activation_fn]
         self.split = bool(model.split_precision)
         f32 = dict(dtype=torch.float32, device=self.device)
@@ -56,6 +57,7 @@ class EnergyForces:
         after the molecule energies (``predict``)."""
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this evaluator")
+        _lib.same_device(self.device, sb.features, sb.x, where="EnergyForces.run")
         if stream is None:
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         lib = _lib.lib()

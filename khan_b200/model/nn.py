@@ -97,6 +97,7 @@ class _FusedMlp(torch.autograd.Function):
         # params: for each of the 4 elements W1,b1,W2,b2,W3,b3,W4,b4 (reference shapes, W = (in, out))
         n = features.shape[0]
         dev = features.device
+        _lib.same_device(dev, *params, packed, where="atomic networks (forward)")
         starts = np.concatenate([[0], np.cumsum(acs)])
         f32 = dict(dtype=torch.float32, device=dev)
         energy = torch.empty(n, **f32)
@@ -304,7 +305,8 @@ class MoleculeNN:
                 for w, b in zip(a.Ws, a.bs):
                     params.extend([w, b])
             flags = (1 if self.split_precision else 0) | (2 if self.accumulate_into_grad else 0)
-            packed = self.pack_weights() if features.device == self.anns[0].Ws[0].device else None
+            _lib.same_device(features.device, self.anns[0].Ws[0], where="MoleculeNN.atom_energies_sorted")
+            packed = self.pack_weights()
             return _FusedMlp.apply(features, acs, activations.KERNEL_ID[self.activation_fn],
                                    flags, (self.activation_fn, packed), *params)
         starts = np.concatenate([[0], np.cumsum(acs)])

@@ -35,6 +35,9 @@ class FusedTrainStep:
             raise ValueError("FusedTrainStep needs the fused float32 384-128-128-64-1 networks")
         self.model, self.optimizer = model, optimizer
         self.device = torch.device(device)
+        # every pointer of a launch must belong to the launching GPU (no peer access is ever enabled)
+        _lib.same_device(self.device, *model.get_parameters(), optimizer.flat_params, optimizer.flat_grads,
+                         where="FusedTrainStep")
         self.act_id = activations.KERNEL_ID[model.activation_fn]
         self.split = bool(model.split_precision)
         f32 = dict(dtype=torch.float32, device=self.device)
@@ -55,6 +58,7 @@ class FusedTrainStep:
     def _check(self, sb: StagedBatch) -> None:
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this step")
+        _lib.same_device(self.device, sb.features, sb.x, where="FusedTrainStep")
 
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)

@@ -99,6 +99,25 @@ class FlatNadam:
         """The device-side step counter (synchronises)."""
         return int(self.state[0].item())
 
+    def set_steps(self, n: int) -> None:
+        """Sets the device-side step counter, which drives the bias corrections of Nadam and the decay of
+        the moving average (the other words of the state are scratch of a step and are cleared)."""
+        self.state.zero_()
+        self.state[0:1].fill_(int(n))
+
+    def slots_of(self, index: int):
+        """First moment, second moment and moving average of parameter ``index``, shaped like it (views)."""
+        p, o = self.params[index], self.offsets[index]
+        return tuple(buf[o:o + p.numel()].view(p.shape) for buf in (self.m, self.v, self.ema))
+
+    def reset_state(self) -> None:
+        """Moments to zero, step counter to zero, moving average = the current weights: the state of a
+        freshly built optimiser around whatever the weights are now."""
+        self.m.zero_()
+        self.v.zero_()
+        self.ema.copy_(self.flat_params)
+        self.set_steps(0)
+
     def ema_of(self, index: int) -> torch.Tensor:
         """Moving average of parameter ``index``, shaped like it."""
         p, o = self.params[index], self.offsets[index]

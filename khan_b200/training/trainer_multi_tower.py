@@ -110,10 +110,20 @@ class TrainerMultiTower:
         assert len(towers) > 0
         self.sess = sess
         self.towers = [_device_of(t) for t in towers]
+        if len(self.towers) > 1:
+            # The reference builds one graph per tower inside one process (trainer_multi_tower.py:253-259,
+            # 290-419).  Here the parameters, the optimiser state and the pre-packed weights live on ONE
+            # device, and a kernel launched on another GPU with pointers to them would read memory that
+            # device cannot reach.  Several GPUs are one process each (torchrun), the weight gradients
+            # meeting in one NCCL all-reduce (average_gradients).
+            raise NotImplementedError(
+                "TrainerMultiTower takes one tower per process: start one process per GPU "
+                "(python -m torch.distributed.run --nproc-per-node N ...) and give each its own device; "
+                "the weight gradients are averaged over the ranks with one NCCL all-reduce")
         self.num_towers = len(self.towers)
         self.precision = precision
         self.feat_size = ani_mod.FEATURE_SIZE
-        # parameters live on the first tower; other towers get a broadcast copy per step
+        # the parameters live on the (only) tower
         self.model = MoleculeNN(layer_sizes=(self.feat_size,) + tuple(layer_sizes), precision=precision,
                                 activation_fn=activation_fn, prefix="near_", device=self.towers[0],
                                 seed=seed, init=init, split_precision=split_precision)
@@ -170,11 +180,49 @@ class TrainerMultiTower:
     def get_loss_op(self):
         return self.tower_exp_loss
 
+    # Names of the optimiser's variables in a reference checkpoint: TensorFlow names a slot after
+    # its variable ("near_W_H_384x128_l1:0" -> "near_W_H_384x128_l1/Nadam:0" and ".../Nadam_1:0" for
+    # the two moments, ".../ExponentialMovingAverage:0" for the shadow), and the Nadam optimiser keeps
+    # beta1_power / beta2_power (trainer_multi_tower.py:261-266, 451-470 saves every global variable).
+    _SLOTS = ("/Nadam:0", "/Nadam_1:0", "/ExponentialMovingAverage:0")
+
+    def _optimizer_slots(self):
+        """{checkpoint name: tensor} of the two Nadam moments and the moving average of every parameter."""
+        out = {}
+        names = list(self.model.named_parameters().keys())
+        by_id = {id(p): k for k, p in enumerate(self.parameters)}
+        for name, p in self.model.named_parameters().items():
+            k, base = by_id[id(p)], name[:-2]
+            if isinstance(self.optimizer, FlatNadam):
+                m, v, ema = self.optimizer.slots_of(k)
+            else:
+                st = self.optimizer.state.get(p, {})
+                m, v, ema = st.get("exp_avg"), st.get("exp_avg_sq"), self.ema[k]
+            for suffix, t in zip(self._SLOTS, (m, v, ema)):
+                if t is not None:
+                    out[base + suffix] = t
+        assert len(names) == len(self.parameters)
+        return out
+
+    def _optimizer_steps(self) -> int:
+        if isinstance(self.optimizer, FlatNadam):
+            return self.optimizer.steps_done()
+        steps = [int(st["step"]) for st in self.optimizer.state.values() if "step" in st]
+        return max(steps) if steps else 0
+
     def save_numpy(self, npz_file):
-        """Saves every variable under the reference's names (``near_W_H_384x128_l1:0`` ...)."""
+        """Saves every variable under the reference's names (``near_W_H_384x128_l1:0`` ...): the weights,
+        the two Nadam moments and the moving average of each, the step count behind the optimiser's bias
+        corrections, the learning rate and the epoch counters (the reference saves all of
+        ``tf.global_variables()``, ``trainer_multi_tower.py:451-470``)."""
         _, ext = os.path.splitext(npz_file)
         assert ext == ".npz"
         objs = {k: v.detach().cpu().numpy() for k, v in self.model.named_parameters().items()}
+        objs.update({k: v.detach().cpu().numpy() for k, v in self._optimizer_slots().items()})
+        steps = self._optimizer_steps()
+        objs["optimizer_step:0"] = np.asarray(steps, dtype=np.int32)
+        objs["beta1_power:0"] = np.asarray(0.9 ** (steps + 1), dtype=np.float32)
+        objs["beta2_power:0"] = np.asarray(0.999 ** (steps + 1), dtype=np.float32)
         objs["learning_rate:0"] = np.asarray(self.learning_rate)
         objs["global_step:0"] = np.asarray(self.global_step, dtype=np.int32)
         objs["global_epoch_count:0"] = np.asarray(self.global_epoch_count, dtype=np.int32)
@@ -182,25 +230,69 @@ class TrainerMultiTower:
         np.savez(npz_file, **objs)
 
     def load_numpy(self, npz_file, strict=False):
+        """Restores a checkpoint written by ``save_numpy`` or by the reference.  Weights, moments, moving
+        averages and the optimiser's step count are restored when present; a checkpoint that holds only
+        weights leaves the optimiser in the state of a new one around those weights (moments 0, step 0,
+        moving average = weights).  A name that matches nothing is reported (the reference raises on an
+        unknown name, ``trainer_multi_tower.py:493``; with ``strict`` so does this)."""
+        import warnings
         objs = np.load(npz_file, allow_pickle=False)
         named = self.model.named_parameters()
+        if not isinstance(self.optimizer, FlatNadam):       # torch creates its slots at the first step
+            for p in self.parameters:
+                if p not in self.optimizer.state:
+                    self.optimizer.state[p] = {"step": torch.as_tensor(0.0), "mu_product": torch.as_tensor(1.0),
+                                               "exp_avg": torch.zeros_like(p), "exp_avg_sq": torch.zeros_like(p)}
+        slots = self._optimizer_slots()
+        ignore = {"beta1_power:0", "beta2_power:0"}          # functions of the step count
+        have_slots, steps, unknown = 0, None, []
         for k in objs.keys():
             arr = objs[k]
-            if k in named:
-                p = named[k]
+            if k in named or k in slots:
+                p = named[k] if k in named else slots[k]
+                have_slots += k in slots
                 want = np.float32 if p.dtype == torch.float32 else np.float64
                 if arr.dtype != want and strict:
                     raise TypeError(f"Cannot deserialize {arr.dtype} into {want}. You may want to set strict=False.")
                 with torch.no_grad():
-                    p.copy_(torch.from_numpy(arr.astype(want)).to(p.device))
+                    p.copy_(torch.from_numpy(arr.astype(want)).to(p.device).view(p.shape))
             elif k == "learning_rate:0":
                 self.set_learning_rate(float(arr))
             elif k == "global_step:0":
                 self.global_step = int(arr)
+            elif k == "optimizer_step:0":
+                steps = int(arr)
             elif k == "global_epoch_count:0":
                 self.global_epoch_count = int(arr)
             elif k == "local_epoch_count:0":
                 self.local_epoch_count = int(arr)
+            elif k not in ignore:
+                unknown.append(k)
+        if unknown:
+            msg = f"load_numpy: {len(unknown)} names of {npz_file} match no variable of this trainer: {unknown[:6]}"
+            if strict:
+                raise KeyError(msg)
+            warnings.warn(msg)
+        if isinstance(self.optimizer, FlatNadam):
+            if have_slots == 0:
+                self.optimizer.reset_state()                 # weights only: a new optimiser around them
+            else:
+                # a reference checkpoint has no optimizer_step: its global_step counts the same updates
+                self.optimizer.set_steps(steps if steps is not None else self.global_step)
+            if self.model.fused:
+                self.model.pack_weights()
+        else:
+            n_steps = steps if steps is not None else self.global_step
+            mu_product = 1.0      # torch.optim.NAdam keeps the running product of its momentum schedule
+            for i in range(1, n_steps + 1):
+                mu_product *= 0.9 * (1.0 - 0.5 * 0.96 ** (i * 0.004))
+            for k, p in enumerate(self.parameters):
+                if have_slots == 0:
+                    self.optimizer.state.pop(p, None)
+                    self.ema[k].copy_(p.detach())
+                elif p in self.optimizer.state:
+                    self.optimizer.state[p]["step"] = torch.as_tensor(float(n_steps))
+                    self.optimizer.state[p]["mu_product"] = torch.as_tensor(mu_product)
 
     def set_learning_rate(self, lr: float):
         self.learning_rate = lr
@@ -582,5 +674,10 @@ class TrainerMultiGPU(TrainerMultiTower):
     n_gpus=...)``."""
 
     def __init__(self, sess=None, n_gpus=1, precision=torch.float32, layer_sizes=(128, 128, 64, 1), **kw):
-        super().__init__(sess, [torch.device("cuda", i) for i in range(n_gpus)], precision,
-                         layer_sizes=layer_sizes, **kw)
+        if n_gpus != 1:
+            raise NotImplementedError(
+                f"TrainerMultiGPU(n_gpus={n_gpus}): one process drives one GPU here; start {n_gpus} processes with "
+                "torchrun (one rank per GPU) and construct TrainerMultiGPU(n_gpus=1) in each -- its device is the "
+                "rank's current CUDA device and the weight gradients are averaged with one NCCL all-reduce")
+        super().__init__(sess, [torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)],
+                         precision, layer_sizes=layer_sizes, **kw)

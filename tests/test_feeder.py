@@ -121,3 +121,45 @@ def test_native_packer_rejects_what_does_not_fit():
     assert "ani_host_pack_batch" in str(info.value)
     with pytest.raises(ValueError):
         packed.gather(np.arange(3), HostSlot(*packed.capacity(9), np.float64, pin=False))
+
+
+def test_fuzz_consumes_numpys_stream_like_the_reference():
+    """The reference perturbs x of every atom of the batch, then y, then z, with three draws
+    (khan/data/dataset.py:166-169); the same seed must give the same batch here, from RawDataset.iterate
+    and from both assemblies of the packed data set."""
+    from khan_b200 import RawDataset
+    from khan_b200.data.feeder import HostSlot, PackedDataset
+    b = syn.gdb_like_batch(9, 3)
+    mols = b.molecules()
+    raw = RawDataset(mols)
+    flat = np.concatenate(mols, axis=0)
+    np.random.seed(5)
+    want = flat.copy()
+    for col in (1, 2, 3):                       # the reference's three draws, in its order
+        want[:, col] += np.random.uniform(-0.1, 0.1, want[:, col].shape)
+    np.random.seed(5)
+    got, _, _, _ = next(raw.iterate(len(mols), shuffle=False, fuzz=0.1))
+    np.testing.assert_array_equal(got, want)
+    packed = PackedDataset.from_raw(raw, np.float64)
+    cap_a, cap_m = packed.capacity(len(mols))
+    for assemble in (packed.gather, packed.gather_numpy):
+        slot = HostSlot(cap_a, cap_m, np.float64, pin=False)
+        np.random.seed(5)
+        assemble(np.arange(len(mols)), slot, fuzz=0.1)
+        np.testing.assert_array_equal(slot.xyz[:, :slot.n_atoms].T, want[:, 1:4])
+
+
+def test_packed_copy_follows_replaced_lists_and_invalidate():
+    from khan_b200 import RawDataset
+    from khan_b200.data.feeder import PackedDataset
+    mols = syn.gdb_like_batch(6, 4).molecules()
+    raw = RawDataset(mols, [0.0] * len(mols))
+    first = PackedDataset.from_raw(raw)
+    assert PackedDataset.from_raw(raw) is first
+    raw.all_ys = [1.0] * len(mols)              # a new list of targets: the packed copy is rebuilt
+    second = PackedDataset.from_raw(raw)
+    assert second is not first and float(second.ys[0]) == 1.0
+    raw.all_ys[0] = 7.0                         # an edit in place is not seen until invalidate()
+    assert PackedDataset.from_raw(raw) is second
+    PackedDataset.invalidate(raw)
+    assert float(PackedDataset.from_raw(raw).ys[0]) == 7.0

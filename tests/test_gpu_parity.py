@@ -66,6 +66,78 @@ def test_sort_single_element_and_sorted_inputs(gpu, oracle_mod):
         np.testing.assert_array_equal(gi, egi)
 
 
+def _host_sort(a):
+    order = np.argsort(a, kind="stable")
+    gather = np.empty(a.size, np.int64)
+    gather[order] = np.arange(a.size)
+    counts = np.bincount(a, minlength=4)
+    starts = np.concatenate([[0], np.cumsum(counts)])[:4]
+    return gather - starts[a], gather, counts
+
+
+def test_large_sorts_on_two_streams_do_not_share_scratch(gpu):
+    """Batches above 65,536 atoms use a scratch buffer that the library keeps per (device, stream): two
+    sorts in flight on two streams must both come out right."""
+    import ctypes
+    import torch
+    from khan_b200 import _lib
+    lib = _lib.lib()
+    rng = np.random.default_rng(31)
+    arrays = [rng.integers(0, 4, n).astype(np.int32) for n in (400_003, 333_337)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    dev_in = [gpu.to_dev(a) for a in arrays]
+    outs = [[torch.empty(a.size, dtype=torch.int32, device=gpu.DEV), torch.empty(a.size, dtype=torch.int32, device=gpu.DEV),
+             torch.empty(4, dtype=torch.int32, device=gpu.DEV)] for a in arrays]
+    torch.cuda.synchronize()
+    for _ in range(3):      # several rounds, so that the two streams really overlap
+        for a, d, o, st in zip(arrays, dev_in, outs, streams):
+            assert lib.ani_sort(d.data_ptr(), a.size, o[0].data_ptr(), o[1].data_ptr(), o[2].data_ptr(),
+                                ctypes.c_void_p(st.cuda_stream)) == 0
+    torch.cuda.synchronize()
+    for a, o in zip(arrays, outs):
+        scatter, gather, counts = _host_sort(a)
+        np.testing.assert_array_equal(o[0].cpu().numpy(), scatter)
+        np.testing.assert_array_equal(o[1].cpu().numpy(), gather)
+        np.testing.assert_array_equal(o[2].cpu().numpy(), counts)
+
+
+def test_large_sort_refuses_to_allocate_inside_a_stream_capture(gpu):
+    """The first large sort on a stream has to allocate its scratch, which a stream capture cannot
+    record: the call is refused (nothing launched) and works in the same capture once the scratch exists."""
+    import ctypes
+    import torch
+    from khan_b200 import _lib
+    lib = _lib.lib()
+    a = np.random.default_rng(32).integers(0, 4, 70_001).astype(np.int32)
+    d = gpu.to_dev(a)
+    o = [torch.empty(a.size, dtype=torch.int32, device=gpu.DEV), torch.empty(a.size, dtype=torch.int32, device=gpu.DEV),
+         torch.empty(4, dtype=torch.int32, device=gpu.DEV)]
+
+    def call(stream):
+        return lib.ani_sort(d.data_ptr(), a.size, o[0].data_ptr(), o[1].data_ptr(), o[2].data_ptr(),
+                            ctypes.c_void_p(stream.cuda_stream))
+
+    fresh = torch.cuda.Stream()      # a stream the library has never seen: no scratch yet
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(fresh):
+        g.capture_begin()
+        refused = call(fresh)
+        g.capture_end()
+    assert refused == -10 and "captur" in lib.ani_status_string(-10).decode()
+    assert call(fresh) == 0          # outside a capture: allocates
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(fresh):
+        g2.capture_begin()
+        recorded = call(fresh)
+        g2.capture_end()
+    assert recorded == 0
+    o[1].zero_()
+    g2.replay()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o[1].cpu().numpy(), _host_sort(a)[1])
+
+
 def test_sort_rejects_bad_element(gpu):
     from khan_b200 import ani_mod
     a = np.array([0, 1, 7, 2], np.int32)
@@ -99,7 +171,43 @@ def test_forward_config0_checksums(gpu, golden):
         np.testing.assert_allclose(s2, g["sumsq_" + tag], rtol=tol * 10)
 
 
+def _concat(*batches):
+    """Several batches as one (molecules of the first, then of the second, ...)."""
+    offs, base = [], 0
+    for b in batches:
+        offs.append(b.mol_offsets + base)
+        base += b.n_atoms
+    return syn.Batch(*(np.concatenate([getattr(b, f) for b in batches]) for f in ("xs", "ys", "zs", "atomic_numbers")),
+                     np.concatenate(offs).astype(np.int32),
+                     np.concatenate([b.mol_atom_counts for b in batches]).astype(np.int32))
+
+
+def _dense_blobs(n_mols, n, radius, seed):
+    """Molecules of n atoms inside a small sphere: more than 24 neighbours within A_Rc around most atoms."""
+    rng = np.random.default_rng(seed)
+    mols = []
+    for _ in range(n_mols):
+        pos = np.zeros((n, 3))
+        k = 0
+        while k < n:
+            c = rng.uniform(-radius, radius, 3)
+            if c @ c > radius * radius or (k and np.min(np.sum((pos[:k] - c) ** 2, axis=1)) < 0.36):
+                continue
+            pos[k] = c
+            k += 1
+        mols.append((rng.integers(0, 4, n).astype(np.int32), pos))
+    return syn._assemble(mols)
+
+
 CASES = {
+    # small molecules with a 40- and a 70-atom molecule among them: the batch takes the kernels for
+    # small molecules (mean size), the two large ones their in-kernel route
+    "large_among_small": lambda: _concat(syn.gdb_like_batch(60, 3), syn.config4(seed=5, n_mols=2, n_min=40, n_max=70),
+                                         syn.gdb_like_batch(30, 4)),
+    # 30 atoms within 2.2 A of a point: up to 29 neighbours within A_Rc (the angular lists hold 24)
+    "dense_small": lambda: _concat(_dense_blobs(3, 30, 2.2, 6), syn.gdb_like_batch(20, 8, heavy_min=1, heavy_max=2)),
+    "exactly_32_atoms": lambda: _concat(syn.config4(seed=6, n_mols=5, n_min=32, n_max=32),
+                                        syn.gdb_like_batch(40, 9, heavy_min=1, heavy_max=3)),
     "config0": lambda: syn.config0(),
     "config1": lambda: syn.config1(),
     "config4_part": lambda: syn.config4(n_mols=12),
@@ -183,6 +291,98 @@ def test_gradient_vs_oracle(gpu, oracle_mod, case, dt):
     for k in range(3):
         assert np.isfinite(out[k]).all()
         assert normwise(out[k], ref[k]) < FTOL[dt], (case, k)
+
+
+def test_float32_gradient_vs_the_float32_reference_where_it_is_finite(gpu, oracle_mod, ref_impl):
+    """The reference's own float32 gradient divides by sin(theta) and by 1 + cos(theta_t - theta) without a
+    guard (gpu_featurizer/kernel_cpu.cpp:335-353) and is non-finite for part of realistic inputs, so the
+    primary check above uses its float64 build.  Here: on the atoms where the float32 reference IS finite,
+    the GPU agrees with it too; how many atoms it loses is printed."""
+    b = syn.config1(n_mols=256)
+    si, gi, ac = oracle_mod.ani_sort(b.atomic_numbers)
+    up = syn.upstream_grads(b, ac, dtype=np.float32)
+    x, y, z = b.coords(np.float32)
+    ref32 = oracle_mod.featurize_grad(x, y, z, b.atomic_numbers, b.mol_offsets, b.mol_atom_counts, si, ac, *up,
+                                      impl=ref_impl, threads=8)
+    ref64 = oracle_mod.featurize_grad(*(v.astype(np.float64) for v in (x, y, z)), b.atomic_numbers, b.mol_offsets,
+                                      b.mol_atom_counts, si, ac, *[u.astype(np.float64) for u in up],
+                                      impl="port", threads=8)
+    out = gpu.gpu_featurize_grad(b, np.float32, up)
+    finite = np.isfinite(ref32[0]) & np.isfinite(ref32[1]) & np.isfinite(ref32[2])
+    # one non-finite term poisons the sums of its whole molecule in the reference: compare molecule-wise
+    mol_of = np.repeat(np.arange(b.n_mols), b.mol_atom_counts)
+    good_mol = np.ones(b.n_mols, bool)
+    good_mol[mol_of[~finite]] = False
+    keep = good_mol[mol_of]
+    print(f"float32 reference gradient: {int((~finite).sum())} of {b.n_atoms} atoms non-finite, "
+          f"{int((~good_mol).sum())} of {b.n_mols} molecules affected")
+    assert keep.sum() > b.n_atoms // 2
+    for k in range(3):
+        assert np.isfinite(out[k]).all()
+        scale = np.abs(ref64[k]).max()
+        # the float32 reference itself is only this close to its float64 build (cancellation in its
+        # expanded expressions): the GPU must be at least as close to it as that, and within 1e-5 of float64
+        ref_gap = np.abs(ref32[k][keep] - ref64[k][keep]).max() / scale
+        assert np.abs(out[k][keep] - ref32[k][keep]).max() / scale < max(1e-5, 2 * ref_gap)
+        assert np.abs(out[k] - ref64[k]).max() / scale < 1e-5
+
+
+def test_config4_at_full_size(gpu, oracle_mod, ref_impl):
+    """Benchmark configuration 4 as stated: 256 molecules of 64-256 atoms, float32.  Forward against the
+    reference build, gradient against the float64 oracle on the float32-rounded inputs."""
+    b = syn.config4()
+    assert b.n_mols == 256 and b.mol_atom_counts.min() >= 64 and b.mol_atom_counts.max() <= 256
+    si, gi, ac = oracle_mod.ani_sort(b.atomic_numbers)
+    x, y, z = b.coords(np.float32)
+    ref = oracle_mod.featurize(x, y, z, b.atomic_numbers, b.mol_offsets, b.mol_atom_counts, si, ac,
+                               impl=ref_impl, threads=8)
+    feats = gpu.gpu_featurize(b, np.float32)
+    for t in range(4):
+        assert normwise(feats[t], ref[t]) < 1e-5
+    up = syn.upstream_grads(b, ac, dtype=np.float32)
+    gref = oracle_mod.featurize_grad(*(v.astype(np.float64) for v in (x, y, z)), b.atomic_numbers, b.mol_offsets,
+                                     b.mol_atom_counts, si, ac, *[u.astype(np.float64) for u in up],
+                                     impl="port", threads=8)
+    out = gpu.gpu_featurize_grad(b, np.float32, up)
+    for k in range(3):
+        assert np.isfinite(out[k]).all()
+        assert normwise(out[k], gref[k]) < 1e-5
+
+
+def test_gradient_is_bit_reproducible(gpu):
+    """Batches of small molecules: every output is written once from a fixed summation order (no atomics),
+    so two runs agree bit for bit, in both precisions."""
+    b = syn.config1(n_mols=512)
+    ac = np.bincount(b.atomic_numbers, minlength=4)
+    for dt in (np.float32, np.float64):
+        up = syn.upstream_grads(b, ac, dtype=dt)
+        one = gpu.gpu_featurize_grad(b, dt, up)
+        two = gpu.gpu_featurize_grad(b, dt, up)
+        for a, c in zip(one, two):
+            np.testing.assert_array_equal(a, c)
+
+
+def test_gradient_takes_unaligned_upstream_buffers(gpu, oracle_mod):
+    """Upstream buffers that are not 16-byte aligned cannot be fetched with 16-byte copies: the call takes
+    the other kernel and gives the same result."""
+    import torch
+    from khan_b200 import ani_mod
+    b = syn.config1(n_mols=64)
+    x, y, z, a, mo, mac = gpu.batch_tensors(b, np.float32)
+    si, gi, ac = ani_mod.ani_sort(a)
+    acs = ac.cpu().numpy()
+    up = syn.upstream_grads(b, acs, dtype=np.float32)
+    aligned = ani_mod.featurize_grad(x, y, z, a, mo, mac, si, acs, *[gpu.to_dev(u) for u in up])
+    shifted = []
+    for u in up:   # a view that starts 4 bytes into an allocation
+        buf = torch.empty(u.size + 1, dtype=torch.float32, device=x.device)
+        buf[1:] = gpu.to_dev(u)
+        shifted.append(buf[1:])
+        assert buf[1:].data_ptr() % 16 == 4 or u.size == 0
+    other = ani_mod.featurize_grad(x, y, z, a, mo, mac, si, acs, *shifted)
+    ani_mod.check_device_status("featurize_grad")
+    for p, q in zip(aligned, other):
+        assert normwise(q.cpu().numpy(), p.cpu().numpy()) < 1e-5
 
 
 def test_gradient_sums_to_zero_per_molecule(gpu):

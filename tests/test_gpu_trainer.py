@@ -101,6 +101,25 @@ def test_training_lowers_the_loss_and_checkpoint_round_trips(small_dataset, tmp_
                               activation_fn=activations.gaussian, seed=9)
     other.load_numpy(path)
     np.testing.assert_allclose(other.predict(ds, 64), tr.predict(ds, 64), rtol=0, atol=1e-6)
+    # the optimiser state travels too, under the reference's slot names: the resumed trainer takes the
+    # SAME next steps as the one that kept running (moments, moving average and step count restored)
+    assert {"near_W_H_384x128_l1/Nadam:0", "near_W_H_384x128_l1/Nadam_1:0",
+            "near_W_H_384x128_l1/ExponentialMovingAverage:0", "beta1_power:0", "optimizer_step:0"} <= keys
+    assert other.optimizer.steps_done() == tr.optimizer.steps_done() == 60
+    assert torch.equal(other.optimizer.m, tr.optimizer.m) and torch.equal(other.optimizer.ema, tr.optimizer.ema)
+    for t in (tr, other):
+        list(t.feed_dataset(ds, shuffle=False, target_ops=[t.train_op_mse], batch_size=35))
+    assert (other.optimizer.flat_params - tr.optimizer.flat_params).abs().max().item() < 1e-6
+    # a checkpoint with weights only: the optimiser starts afresh around them, and says nothing is unknown
+    weights_only = {k: v for k, v in np.load(path).items() if k.endswith("_l1:0") or k.endswith("_l2:0")
+                    or k.endswith("_l3:0") or k.endswith("_l4:0")}
+    np.savez(str(tmp_path / "w.npz"), **weights_only)
+    other.load_numpy(str(tmp_path / "w.npz"))
+    assert other.optimizer.steps_done() == 0 and float(other.optimizer.m.abs().max()) == 0.0
+    assert torch.equal(other.optimizer.ema, other.optimizer.flat_params)
+    np.savez(str(tmp_path / "odd.npz"), **weights_only, some_other_variable=np.zeros(3))
+    with pytest.warns(UserWarning, match="match no variable"):
+        other.load_numpy(str(tmp_path / "odd.npz"))
 
 
 def test_feeder_uploads_match_the_host_batches():

@@ -27,7 +27,36 @@ def _sort_with(fn, a_dev, torch):
     return scatter.cpu().numpy(), gather.cpu().numpy(), counts.cpu().numpy()
 
 
+_first_call_done = False
+
+
+def test_noalloc_first_call_inside_a_stream_capture_is_refused():
+    """The first call on a device looks up the address of the library's array, which must not happen while
+    the stream is being captured: such a call is refused and launches nothing.  (Only meaningful when
+    this is the first ani_sort_noalloc call of the process, which it is when the file runs in order.)"""
+    global _first_call_done
+    import torch
+    from khan_b200 import _lib
+
+    lib = _lib.lib()
+    a = torch.from_numpy(np.random.default_rng(3).integers(0, 4, 5000).astype(np.int32)).to("cuda:0")
+    out = [torch.empty(5000, dtype=torch.int32, device="cuda:0"), torch.empty(5000, dtype=torch.int32, device="cuda:0"),
+           torch.empty(4, dtype=torch.int32, device="cuda:0")]
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        g.capture_begin()
+        status = lib.ani_sort_noalloc(a.data_ptr(), 5000, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                      ctypes.c_void_p(side.cuda_stream))
+        g.capture_end()
+    assert status == (0 if _first_call_done else -10)
+    _first_call_done = True
+
+
 def test_noalloc_sort_matches_sort_on_two_calls_in_a_row():
+    global _first_call_done
+    _first_call_done = True
     import torch
     from khan_b200 import _lib
 
