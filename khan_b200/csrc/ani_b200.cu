@@ -274,7 +274,8 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
     const T* gin[kTypes] = {gh, gc, gn, go};
     // One CTA per molecule when the molecules are small and the upstream rows can be fetched with
     // 16-byte copies: writes every output itself, so no zero fill.
-    if (n_mols > 0 && small_molecules(n_atoms, n_mols) && all_aligned16({gh, gc, gn, go})) {
+    if (n_mols > 0 && small_molecules(n_atoms, n_mols) && all_aligned16({gh, gc, gn, go}) &&
+        (long long)n_mols * kMolGradClasses <= 0x7fffffffLL) {
         if (!xs || !ys || !zs || !types || !mos || !macs || !sis) return ANI_ERR_NULL_POINTER;
         for (int t = 0; t < kTypes; t++)
             if (acs_host[t] > 0 && !gin[t]) return ANI_ERR_NULL_POINTER;
@@ -287,7 +288,7 @@ int featurize_grad_impl(const T* xs, const T* ys, const T* zs, const int* types,
             if (int rc = set_smem(mol_kernel, mol_smem)) return rc;
             mol_configured_dev = dev;
         }
-        mol_kernel<<<n_mols, kMolGradWarps * kWarp, mol_smem, st>>>(xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, gh,
+        mol_kernel<<<n_mols * kMolGradClasses, kMolGradWarps * kWarp, mol_smem, st>>>(xs, ys, zs, types, mos, macs, n_mols, (int)n_atoms, sis, gh,
                                                           gc, gn, go, gx, gy, gz, acs_host[0], acs_host[1],
                                                           acs_host[2], acs_host[3]);
         ANI_CUDA(cudaGetLastError());

@@ -47,10 +47,13 @@ constexpr int kMolCentrals = 4;        // central atoms per round
 constexpr int kMolCapA = 24;           // angular neighbours kept per central atom
 constexpr int kMolGroupStride = 16;    // group id = central slot * 16 + element-pair bucket
 constexpr int kMolNoGroup = 0xff;      // id of the quads behind the last group
+constexpr int kMolSlotsPerLane = 1;    // slots a lane evaluates per pass B (2 was measured: no gain)
+constexpr int kMolChunk = kMolSlotsPerLane * kWarp;   // slots per pass B / C
+constexpr int kMolChunkStride = kMolChunk + 4;        // + 4 words: keeps the 16-byte reads of pass C conflict-free
 constexpr int kMolRounds = kMolMaxAtoms / kMolCentrals;   // rounds of the largest molecule of the fast path
 // padded slots of one central atom: at most CapA (CapA - 1) / 2 pairs + 3 per bucket, in quads
 constexpr int kMolQuadsPerCentral = (kMolCapA * (kMolCapA - 1) / 2 + 3 * kPairBuckets) / 4 + 1;
-constexpr int kMolQuadBytes = ((kMolCentrals * kMolQuadsPerCentral + 8 + 8 + 7) / 8) * 8;
+constexpr int kMolQuadBytes = ((kMolCentrals * kMolQuadsPerCentral + 2 * (kMolChunk / 4) + 7) / 8) * 8;
 
 struct alignas(16) MolGroupInfo {
     int off;         // first slot of the group (a multiple of 4)
@@ -71,8 +74,8 @@ template <typename T> struct MolFwdWarpShared {
     Vec4<T> ang_u[kMolCentrals * kMolCapA];   // (x_i - x_j) / r_ij and r_ij, element order, per central atom
     T ang_fc[kMolCentrals * kMolCapA];        // f_C(r_ij, A_Rc)
     Vec2<T> rad[kMolCentrals][kMolMaxAtoms];  // (r_ij, f_C(r_ij, R_Rc) or 0) of every atom j, per central atom
-    alignas(16) T A[kNumThetas][kPadStride];
-    alignas(16) T BF[kNumARs][kPadStride];
+    alignas(16) T A[kNumThetas][kMolChunkStride];
+    alignas(16) T BF[kNumARs][kMolChunkStride];
     MolGroupInfo tab[kMolCentrals * kMolGroupStride];
     T* row[kMolCentrals];                     // feature row of each central atom of the round
     alignas(16) int cnt_a[kMolCentrals * kTypes];   // angular neighbours per element, per central atom
@@ -345,7 +348,7 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
         total += __shfl_sync(kFull, incl, kWarp - 1);
     }
     // ids behind the last group, through the end of its chunk and the look-ahead of pass C
-    for (int q = (total >> 2) + lane; q < (((total + kWarp - 1) & ~(kWarp - 1)) >> 2) + 8; q += kWarp)
+    for (int q = (total >> 2) + lane; q < (((total + kMolChunk - 1) & ~(kMolChunk - 1)) >> 2) + 1; q += kWarp)
         ws.quad_gid[q] = (unsigned char)kMolNoGroup;
     __syncwarp();
 
@@ -353,10 +356,12 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
     const T* a_row = &ws.A[lane >> 2][0];
     const T* b_row = &ws.BF[lane & 3][0];
     Pair<T> acc0{(T)0, (T)0}, acc1{(T)0, (T)0};
-    for (int c0 = 0; c0 < total; c0 += kWarp) {
-        {   // B: lane = slot
+    for (int c0 = 0; c0 < total; c0 += kMolChunk) {
+        // B: lane = slot, kMolSlotsPerLane slots per lane (independent of one another)
+#pragma unroll
+        for (int u = 0; u < kMolSlotsPerLane; u++) {
             int a, b;
-            const bool valid = decode_slot(ws.tab, ws.quad_gid, c0 + lane, &a, &b);
+            const bool valid = decode_slot(ws.tab, ws.quad_gid, c0 + u * kWarp + lane, &a, &b);
             const Vec4<T> ua = ws.ang_u[a], ub = ws.ang_u[b];
             const T cosv = ua.x * ub.x + ua.y * ub.y + ua.z * ub.z;
             const T rbar = (T)0.5 * (ua.w + ub.w);
@@ -364,18 +369,20 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
             T A[kNumThetas], BF[kNumARs];
             angular_factors_dev<T>(cosv, rbar, fcprod, A, BF);
 #pragma unroll
-            for (int t = 0; t < kNumThetas; t++) ws.A[t][lane] = A[t];
+            for (int t = 0; t < kNumThetas; t++) ws.A[t][u * kWarp + lane] = A[t];
 #pragma unroll
-            for (int q = 0; q < kNumARs; q++) ws.BF[q][lane] = BF[q];
+            for (int q = 0; q < kNumARs; q++) ws.BF[q][u * kWarp + lane] = BF[q];
         }
-        // quads of this chunk that end a group (lanes 0..7 look at one quad each)
+        // quads of this chunk that end a group (the first lanes look at one quad each)
         const unsigned char* ids = &ws.quad_gid[c0 >> 2];
-        const unsigned my_id = ids[lane & 7];
-        const unsigned ends = __ballot_sync(kFull, lane < 8 && my_id != kMolNoGroup && my_id != ids[(lane & 7) + 1]);
+        constexpr int kQuads = kMolChunk / 4;
+        const unsigned my_id = ids[lane & (kQuads - 1)];
+        const unsigned ends =
+            __ballot_sync(kFull, lane < kQuads && my_id != kMolNoGroup && my_id != ids[(lane & (kQuads - 1)) + 1]);
         __syncwarp();
         // C: lane = (theta, shift).  Slots behind the last group hold BF = 0.
 #pragma unroll
-        for (int q = 0; q < 8; q++) {
+        for (int q = 0; q < kQuads; q++) {
             T av[4], bv[4];
             load4(a_row + 4 * q, av);
             load4(b_row + 4 * q, bv);
