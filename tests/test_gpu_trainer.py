@@ -393,3 +393,22 @@ def test_fused_training_path_of_the_trainer_matches_autograd(op_name, monkeypatc
         assert tr.global_step == 3
         weights.append(tr.optimizer.flat_params.clone())
     assert (weights[0] - weights[1]).abs().max().item() < 2e-5
+
+
+def test_energy_server_answers_with_the_trainers_numbers():
+    """The server's evaluator is a trainer: its answer is predict + self energies and the coordinate gradient
+    in Hartree/Bohr, checked by finite differences of the served energy."""
+    import torch
+    from khan_b200 import TrainerMultiTower, energy_server as es
+    b = syn.kat_fixture()
+    mol = b.molecules()[0]
+    tr = TrainerMultiTower(None, ["cuda:0"], torch.float64, layer_sizes=(128, 128, 64, 1), seed=4)
+    ans = es.evaluate(tr, mol.tolist())
+    assert len(ans["gradient"]) == 3 * len(mol)
+    g = np.array(ans["gradient"]).reshape(-1, 3) / es.BOHR          # back to Hartree/Angstrom
+    for atom, axis in ((0, 0), (2, 1), (len(mol) - 1, 2)):
+        plus, minus = mol.copy(), mol.copy()
+        plus[atom, 1 + axis] += 1e-5
+        minus[atom, 1 + axis] -= 1e-5
+        fd = (es.evaluate(tr, plus.tolist())["energy"] - es.evaluate(tr, minus.tolist())["energy"]) / 2e-5
+        assert abs(fd - g[atom, axis]) < 1e-6 * max(1.0, abs(fd))
