@@ -554,6 +554,47 @@ def run_fused_train_workload(args):
     ctx.close()
 
 
+def run_frontend_workload(args):
+    """--workload frontend: the khan API itself on one GPU -- predict, coordinate_gradients and one training
+    epoch through feed_dataset -- over a data set of 32,768 GDB-like molecules held on the host."""
+    import torch
+    from khan_b200 import RawDataset, TrainerMultiTower
+    from khan_b200.data import synthetic as syn
+    ctx = Ctx()
+    mols = []
+    for s in range(16):
+        mols += syn.gdb_like_batch(2048, seed=100 + s).molecules()
+    ys = list(np.random.default_rng(0).normal(size=len(mols)))
+    ds = RawDataset(mols, ys)
+    n_atoms = sum(len(m) for m in mols)
+    tr = TrainerMultiTower(None, [ctx.dev], layer_sizes=(128, 128, 64, 1), seed=1)
+    calls = (("predict", lambda: tr.predict(ds, batch_size=2048)),
+             ("coordinate_gradients", lambda: sum(1 for _ in tr.coordinate_gradients(ds, batch_size=2048))),
+             ("train_epoch_exp_rmse_max_norm", lambda: sum(1 for _ in tr.feed_dataset(
+                 ds, True, [tr.train_op], 1024, before_hooks=tr.max_norm_ops))),
+             ("train_epoch_mse", lambda: sum(1 for _ in tr.feed_dataset(ds, True, [tr.train_op_mse], 1024))))
+    out = {}
+    for name, fn in calls:
+        fn()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        out[name] = {"atoms_per_s": n_atoms / best, "molecules_per_s": len(mols) / best, "seconds": best}
+    if ctx.rank == 0:
+        print(json.dumps({"metric": "khan front end atoms/sec (one GPU, wall clock, host data set)", "unit": UNIT,
+                          "n_gpus": 1, "data": "synthetic", "dtype": "f32",
+                          "config": {"workload": "32,768 GDB-like molecules (%d atoms) in a RawDataset; predict and "
+                                                 "coordinate_gradients at batch 2048, training epochs at batch 1024; "
+                                                 "fastest of 3 calls after one warm-up call" % n_atoms},
+                          "calls": out}), flush=True)
+    ctx.close()
+
+
 def run_train_workload(args):
     """One step = config-1 batch per GPU -> ani_sort -> featurize -> four atomic networks
     (384-128-128-64-1, gaussian, He-normal init seed 1) -> molecule energies -> MSE against
@@ -894,7 +935,7 @@ def main():
                     help="independent batches in flight: steps are issued round-robin over this many streams")
     ap.add_argument("--mols", type=int, default=N_MOLS,
                     help="molecules per batch (1024 is the benchmark workload; other sizes are for profiling)")
-    ap.add_argument("--workload", default="aev", choices=["aev", "train", "forces"],
+    ap.add_argument("--workload", default="aev", choices=["aev", "train", "forces", "frontend"],
                     help="aev: the benchmark metric (sort + featurize + featurize_grad); train: the full "
                          "data-parallel training step of benchmark configuration 3; forces: energies + forces of "
                          "config-1 batches through the C ABI only (both reported separately)")
@@ -929,6 +970,9 @@ def main():
         return
     if args.workload == "forces":
         run_forces_workload(args)
+        return
+    if args.workload == "frontend":
+        run_frontend_workload(args)
         return
 
     import torch

@@ -428,8 +428,57 @@ typedef struct ani_host_pack_args {
     int cap_mols;
     int* n_atoms_out;
     int* acs_out;
+    const int* src_mol_acs;   /* optional [n_mols_total][4]: atoms per element of every molecule of the dataset;
+                                 when given, the per-batch element counts are sums of these rows */
 } ani_host_pack_args;
 int ani_host_pack_batch(const ani_host_pack_args* args);
+
+/*
+ * One pass over a staged batch as ONE call: any run of the steps
+ *   pack weights -> ani_sort -> featurize -> networks forward -> molecule energies (+ MSE gradient)
+ *   -> networks backward -> zero + weight gradients -> featurize_grad
+ * chosen by `phases`, each step the entry point of that name above, enqueued in this order on
+ * `stream`.  It has no counterpart in the reference, where TensorFlow's executor walks the graph
+ * of trainer_multi_tower.py:290-427; it exists because the host-side cost of six to eight separate
+ * calls, each with its own argument block of per-element pointers, is what bounds predict /
+ * coordinate_gradients / feed_dataset from Python.  All row buffers hold the atoms in the
+ * element-sorted order of ani_sort (H rows, then C, N, O); the per-element pointers of the single
+ * calls are these bases plus the element's row offset, computed here from acs_host.
+ */
+#define ANI_PASS_PACK 1          /* ani_mlp_pack_weights_f32 (needs `packed`) */
+#define ANI_PASS_FEATURIZE 2     /* ani_sort + ani_featurize_f32 */
+#define ANI_PASS_FORWARD 4       /* ani_mlp_forward_f32 */
+#define ANI_PASS_ENERGY 8        /* ani_molecule_energy_f32 (with labels: l2s and grad_energy_sorted are written) */
+#define ANI_PASS_BACKWARD 16     /* ani_mlp_backward_f32 (feature_grads == NULL skips the products towards the features) */
+#define ANI_PASS_WEIGHT_GRAD 32  /* clear zero_ptr[0 .. zero_bytes), then ani_mlp_weight_grad_f32 */
+#define ANI_PASS_COORD_GRAD 64   /* ani_featurize_grad_f32 with feature_grads as its upstream */
+typedef struct ani_pass_args {
+    int phases;
+    int n_atoms, n_mols;
+    const int* acs_host;             /* HOST [4] */
+    int activation, split_precision;
+    const float *xs, *ys, *zs;       /* [n_atoms] */
+    const int *atomic_numbers, *mol_offsets, *mol_atom_counts;
+    int *scatter_idxs, *gather_idxs, *atom_counts;
+    float* features;                 /* [n_atoms][384] */
+    float* feature_grads;            /* [n_atoms][384] or NULL */
+    float *x_grads, *y_grads, *z_grads;
+    float* energy_sorted;            /* [n_atoms] */
+    float* grad_energy_sorted;       /* [n_atoms]: read by the backward steps, written by the energy step when labels != NULL */
+    float *act1, *act2, *act3;       /* [n_atoms][128], [128], [64] */
+    float *dact1, *dact2, *dact3;
+    float *dz1, *dz2, *dz3;
+    const float* labels;             /* [n_mols] or NULL */
+    float grad_scale;
+    float* mol_energy;               /* [n_mols] */
+    float* l2s;                      /* [n_mols] or NULL */
+    const float *w1[4], *b1[4], *w2[4], *b2[4], *w3[4], *b3[4], *w4[4], *b4[4];
+    float *dw1[4], *db1[4], *dw2[4], *db2[4], *dw3[4], *db3[4], *dw4[4], *db4[4];
+    void* packed[4];                 /* pre-packed weights per element, or NULL */
+    void* zero_ptr;                  /* cleared before the weight gradients are added (NULL: nothing) */
+    size_t zero_bytes;
+} ani_pass_args;
+int ani_network_pass_f32(const ani_pass_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -54,7 +54,28 @@ class HostPackArgs(ctypes.Structure):
                 ("dst_is_f64", ctypes.c_int), ("dst_types", ctypes.c_void_p), ("dst_mol_ids", ctypes.c_void_p),
                 ("dst_mol_offsets", ctypes.c_void_p), ("dst_mol_counts", ctypes.c_void_p),
                 ("cap_atoms", ctypes.c_int), ("cap_mols", ctypes.c_int), ("n_atoms_out", ctypes.c_void_p),
-                ("acs_out", ctypes.c_void_p)]
+                ("acs_out", ctypes.c_void_p), ("src_mol_acs", ctypes.c_void_p)]
+
+
+class PassArgs(ctypes.Structure):
+    """``ani_pass_args`` of include/ani_b200.h."""
+    _P4 = ctypes.c_void_p * 4
+    _fields_ = ([("phases", ctypes.c_int), ("n_atoms", ctypes.c_int), ("n_mols", ctypes.c_int),
+                 ("acs_host", ctypes.c_void_p), ("activation", ctypes.c_int), ("split_precision", ctypes.c_int)]
+                + [(n, ctypes.c_void_p) for n in (
+                    "xs", "ys", "zs", "atomic_numbers", "mol_offsets", "mol_atom_counts", "scatter_idxs", "gather_idxs",
+                    "atom_counts", "features", "feature_grads", "x_grads", "y_grads", "z_grads", "energy_sorted",
+                    "grad_energy_sorted", "act1", "act2", "act3", "dact1", "dact2", "dact3", "dz1", "dz2", "dz3",
+                    "labels")]
+                + [("grad_scale", ctypes.c_float), ("mol_energy", ctypes.c_void_p), ("l2s", ctypes.c_void_p)]
+                + [(n, ctypes.c_void_p * 4) for n in (
+                    "w1", "b1", "w2", "b2", "w3", "b3", "w4", "b4", "dw1", "db1", "dw2", "db2", "dw3", "db3", "dw4",
+                    "db4", "packed")]
+                + [("zero_ptr", ctypes.c_void_p), ("zero_bytes", ctypes.c_size_t)])
+
+
+PASS_PACK, PASS_FEATURIZE, PASS_FORWARD, PASS_ENERGY, PASS_BACKWARD, PASS_WEIGHT_GRAD, PASS_COORD_GRAD = (
+    1, 2, 4, 8, 16, 32, 64)
 
 
 class MlpBackwardArgs(ctypes.Structure):
@@ -94,6 +115,7 @@ SIGNATURES = {
     "ani_nadam_step_f32": (_i, [_vp] * 5 + [ctypes.c_longlong, _vp, _vp, _vp]),
     "ani_clip_rows_f32": (_i, [_vp, _vp, _vp, _i, ctypes.c_float, _vp]),
     "ani_host_pack_batch": (_i, [_vp]),
+    "ani_network_pass_f32": (_i, [ctypes.POINTER(PassArgs), _vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_f64": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_grad_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp, _vp]),

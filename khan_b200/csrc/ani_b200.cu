@@ -870,4 +870,96 @@ int ani_host_pack_batch(const ani_host_pack_args* args)
     return ani::host_pack_batch(*args);
 }
 
+int ani_network_pass_f32(const ani_pass_args* a, void* stream)
+{
+    if (!a) return ANI_ERR_NULL_POINTER;
+    long long n_atoms = 0;
+    if (int rc = check_acs(a->acs_host, &n_atoms)) return rc;
+    if (a->n_atoms < 0 || a->n_mols < 0 || n_atoms != a->n_atoms) return ANI_ERR_BAD_SIZE;
+    const int* acs = a->acs_host;
+    size_t start[kTypes];   // first row of each element
+    size_t at = 0;
+    for (int t = 0; t < kTypes; t++) {
+        start[t] = at;
+        at += (size_t)acs[t];
+    }
+    auto rows = [&](float* base, int t, int width) -> float* {
+        return base && acs[t] > 0 ? base + start[t] * (size_t)width : nullptr;
+    };
+    if (a->phases & ANI_PASS_PACK) {
+        ani_mlp_pack_args p;
+        for (int t = 0; t < kTypes; t++) {
+            p.w1[t] = a->w1[t]; p.w2[t] = a->w2[t]; p.w3[t] = a->w3[t];
+            p.packed[t] = a->packed[t];
+        }
+        if (int rc = ani_mlp_pack_weights_f32(&p, stream)) return rc;
+    }
+    if (a->phases & ANI_PASS_FEATURIZE) {
+        if (int rc = ani_sort(a->atomic_numbers, a->n_atoms, a->scatter_idxs, a->gather_idxs, a->atom_counts, stream))
+            return rc;
+        if (int rc = ani_featurize_f32(a->xs, a->ys, a->zs, a->atomic_numbers, a->mol_offsets, a->mol_atom_counts,
+                                       a->n_mols, a->scatter_idxs, rows(a->features, 0, kTotal),
+                                       rows(a->features, 1, kTotal), rows(a->features, 2, kTotal),
+                                       rows(a->features, 3, kTotal), acs, stream))
+            return rc;
+    }
+    if (a->phases & ANI_PASS_FORWARD) {
+        ani_mlp_args f;
+        for (int t = 0; t < kTypes; t++) {
+            f.features[t] = rows(a->features, t, kTotal);
+            f.w1[t] = a->w1[t]; f.b1[t] = a->b1[t]; f.w2[t] = a->w2[t]; f.b2[t] = a->b2[t];
+            f.w3[t] = a->w3[t]; f.b3[t] = a->b3[t]; f.w4[t] = a->w4[t]; f.b4[t] = a->b4[t];
+            f.energy[t] = rows(a->energy_sorted, t, 1);
+            f.act1[t] = rows(a->act1, t, kMlpH1); f.act2[t] = rows(a->act2, t, kMlpH2); f.act3[t] = rows(a->act3, t, kMlpH3);
+            f.dact1[t] = rows(a->dact1, t, kMlpH1); f.dact2[t] = rows(a->dact2, t, kMlpH2);
+            f.dact3[t] = rows(a->dact3, t, kMlpH3);
+            f.packed[t] = a->packed[t];
+        }
+        if (int rc = ani_mlp_forward_f32(&f, acs, a->activation, a->split_precision, stream)) return rc;
+    }
+    if (a->phases & ANI_PASS_ENERGY) {
+        if (int rc = ani_molecule_energy_f32(a->energy_sorted, a->gather_idxs, a->mol_offsets, a->mol_atom_counts,
+                                             a->n_mols, a->n_atoms, a->labels, a->grad_scale, a->mol_energy,
+                                             a->labels ? a->l2s : nullptr,
+                                             a->labels ? a->grad_energy_sorted : nullptr, stream))
+            return rc;
+    }
+    if (a->phases & ANI_PASS_BACKWARD) {
+        ani_mlp_backward_args b;
+        for (int t = 0; t < kTypes; t++) {
+            b.grad_energy[t] = rows(a->grad_energy_sorted, t, 1);
+            b.w1[t] = a->w1[t]; b.w2[t] = a->w2[t]; b.w3[t] = a->w3[t]; b.w4[t] = a->w4[t];
+            b.dact1[t] = rows(a->dact1, t, kMlpH1); b.dact2[t] = rows(a->dact2, t, kMlpH2);
+            b.dact3[t] = rows(a->dact3, t, kMlpH3);
+            b.dz1[t] = rows(a->dz1, t, kMlpH1); b.dz2[t] = rows(a->dz2, t, kMlpH2); b.dz3[t] = rows(a->dz3, t, kMlpH3);
+            b.grad_features[t] = rows(a->feature_grads, t, kTotal);
+            b.packed[t] = a->packed[t];
+        }
+        if (int rc = ani_mlp_backward_f32(&b, acs, a->split_precision, stream)) return rc;
+    }
+    if (a->phases & ANI_PASS_WEIGHT_GRAD) {
+        if (a->zero_ptr && a->zero_bytes)
+            ANI_CUDA(cudaMemsetAsync(a->zero_ptr, 0, a->zero_bytes, (cudaStream_t)stream));
+        ani_mlp_weight_grad_args w;
+        for (int t = 0; t < kTypes; t++) {
+            w.features[t] = rows(a->features, t, kTotal);
+            w.act1[t] = rows(a->act1, t, kMlpH1); w.act2[t] = rows(a->act2, t, kMlpH2); w.act3[t] = rows(a->act3, t, kMlpH3);
+            w.dz1[t] = rows(a->dz1, t, kMlpH1); w.dz2[t] = rows(a->dz2, t, kMlpH2); w.dz3[t] = rows(a->dz3, t, kMlpH3);
+            w.dw1[t] = a->dw1[t]; w.dw2[t] = a->dw2[t]; w.dw3[t] = a->dw3[t]; w.dw4[t] = a->dw4[t];
+            w.db1[t] = a->db1[t]; w.db2[t] = a->db2[t]; w.db3[t] = a->db3[t]; w.db4[t] = a->db4[t];
+            w.grad_energy[t] = rows(a->grad_energy_sorted, t, 1);
+        }
+        if (int rc = ani_mlp_weight_grad_f32(&w, acs, a->split_precision, stream)) return rc;
+    }
+    if (a->phases & ANI_PASS_COORD_GRAD) {
+        if (int rc = ani_featurize_grad_f32(a->xs, a->ys, a->zs, a->atomic_numbers, a->mol_offsets, a->mol_atom_counts,
+                                            a->n_mols, a->scatter_idxs, rows(a->feature_grads, 0, kTotal),
+                                            rows(a->feature_grads, 1, kTotal), rows(a->feature_grads, 2, kTotal),
+                                            rows(a->feature_grads, 3, kTotal), a->x_grads, a->y_grads, a->z_grads,
+                                            acs, stream))
+            return rc;
+    }
+    return ANI_OK;
+}
+
 }  // extern "C"

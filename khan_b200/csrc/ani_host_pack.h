@@ -6,6 +6,7 @@
 // fancy indexing took 0.43 ms of the feeder thread, this loop takes a few tens of microseconds.
 #pragma once
 
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 
@@ -26,6 +27,8 @@ inline void pack_coordinates(const ani_host_pack_args& a)
             if (a.noise) {      // noise is [n_total][3] doubles; the sum is formed in double, as numpy does
                 const double* nz = a.noise + 3 * d0 + c;
                 for (long long k = 0; k < cnt; k++) d[k] = (DST)((double)s[k] + nz[3 * k]);
+            } else if (sizeof(SRC) == sizeof(DST)) {
+                std::memcpy(d, s, (size_t)cnt * sizeof(DST));
             } else {
                 for (long long k = 0; k < cnt; k++) d[k] = (DST)s[k];
             }
@@ -57,6 +60,42 @@ inline int host_pack_batch(const ani_host_pack_args& a)
         a.dst_mol_counts[m] = (int)cnt;
         at += cnt;
     }
+    int acs[4] = {0, 0, 0, 0};
+    const size_t esize = a.dst_is_f64 ? 8 : 4;
+    // Consecutive picks (an unshuffled pass: predict, evaluation) are one contiguous range of every
+    // array of the data set: whole-range copies instead of one small copy per molecule and array.
+    bool consecutive = a.n_picks > 0 && !a.noise && a.src_is_f64 == a.dst_is_f64;
+    for (int m = 1; consecutive && m < a.n_picks; m++) consecutive = a.picks[m] == a.picks[0] + m;
+    if (consecutive) {
+        const long long s0 = a.mol_ptr[a.picks[0]];
+        for (int c = 0; c < 3; c++) {
+            std::memcpy(static_cast<char*>(a.dst_xyz) + (size_t)c * a.dst_stride * esize,
+                        static_cast<const char*>(a.src_xyz) + ((size_t)c * a.src_stride + s0) * esize, (size_t)n * esize);
+            if (a.src_grads)
+                std::memcpy(static_cast<char*>(a.dst_grads) + (size_t)c * a.dst_stride * esize,
+                            static_cast<const char*>(a.src_grads) + ((size_t)c * a.src_stride + s0) * esize,
+                            (size_t)n * esize);
+        }
+        std::memcpy(a.dst_types, a.src_types + s0, (size_t)n * sizeof(int));
+        if (a.src_ys)
+            std::memcpy(a.dst_ys, static_cast<const char*>(a.src_ys) + (size_t)a.picks[0] * esize, (size_t)a.n_picks * esize);
+        for (int m = 0; m < a.n_picks; m++) {
+            const long long d0 = a.dst_mol_offsets[m], cnt = a.dst_mol_counts[m];
+            std::fill(a.dst_mol_ids + d0, a.dst_mol_ids + d0 + cnt, (long long)m);
+            if (a.src_mol_acs) {
+                const int* row = a.src_mol_acs + 4 * a.picks[m];
+                for (int t = 0; t < 4; t++) acs[t] += row[t];
+            }
+        }
+        if (!a.src_mol_acs)
+            for (long long k = 0; k < n; k++) {
+                const int t = a.src_types[s0 + k];
+                if (t >= 0 && t < 4) acs[t]++;
+            }
+        for (int t = 0; t < 4; t++) a.acs_out[t] = acs[t];
+        *a.n_atoms_out = (int)n;
+        return ANI_OK;
+    }
     if (a.src_is_f64) {
         if (a.dst_is_f64) pack_coordinates<double, double>(a);
         else pack_coordinates<double, float>(a);
@@ -64,15 +103,18 @@ inline int host_pack_batch(const ani_host_pack_args& a)
         if (a.dst_is_f64) pack_coordinates<float, double>(a);
         else pack_coordinates<float, float>(a);
     }
-    int acs[4] = {0, 0, 0, 0};
-    const size_t esize = a.dst_is_f64 ? 8 : 4;
     for (int m = 0; m < a.n_picks; m++) {
         const long long s0 = a.mol_ptr[a.picks[m]], cnt = a.mol_ptr[a.picks[m] + 1] - s0, d0 = a.dst_mol_offsets[m];
         std::memcpy(a.dst_types + d0, a.src_types + s0, (size_t)cnt * sizeof(int));
-        for (long long k = 0; k < cnt; k++) {
-            a.dst_mol_ids[d0 + k] = m;
-            const int t = a.src_types[s0 + k];
-            if (t >= 0 && t < 4) acs[t]++;
+        std::fill(a.dst_mol_ids + d0, a.dst_mol_ids + d0 + cnt, (long long)m);
+        if (a.src_mol_acs) {
+            const int* row = a.src_mol_acs + 4 * a.picks[m];
+            for (int t = 0; t < 4; t++) acs[t] += row[t];
+        } else {
+            for (long long k = 0; k < cnt; k++) {
+                const int t = a.src_types[s0 + k];
+                if (t >= 0 && t < 4) acs[t]++;
+            }
         }
         if (a.src_grads)
             for (int c = 0; c < 3; c++)

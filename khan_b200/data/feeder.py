@@ -39,6 +39,7 @@ class PackedDataset:
         self.counts = np.fromiter((len(m) for m in all_Xs), dtype=np.int64, count=n_mols)
         self.ptr = np.zeros(n_mols + 1, np.int64)
         np.cumsum(self.counts, out=self.ptr[1:])
+        self._mol_acs = None
         cat = np.concatenate(all_Xs, axis=0) if n_mols else np.zeros((0, 4))
         self.types = np.ascontiguousarray(cat[:, 0].astype(np.int32))
         # coordinates stay in the precision they were given in; the cast to `dtype` happens per
@@ -101,22 +102,34 @@ class PackedDataset:
         if fuzz is not None:   # same draws as RawDataset.iterate: x of all atoms, then y, then z
             n = int(self.counts[picks].sum())
             noise = np.ascontiguousarray(np.random.uniform(-fuzz, fuzz, (3, n)).T)
-        a = _lib.HostPackArgs()
-        a.picks, a.n_picks, a.n_mols_total = picks.ctypes.data, m, self.num_mols()
-        a.mol_ptr = self.ptr.ctypes.data
-        a.src_xyz, a.src_stride = self.xyz.ctypes.data, self.xyz.shape[1]
-        a.src_is_f64 = int(self.xyz.dtype == np.float64)
-        a.src_types = self.types.ctypes.data
-        a.src_ys = None if self.ys is None else self.ys.ctypes.data
-        a.src_grads = None if self.grads is None else self.grads.ctypes.data
+        if self._mol_acs is None:      # atoms per element of every molecule, once per data set
+            ok = (self.types >= 0) & (self.types < 4)
+            mol_of = np.repeat(np.arange(self.num_mols()), self.counts)
+            acs = np.zeros((self.num_mols(), 4), np.int32)
+            np.add.at(acs, (mol_of[ok], self.types[ok]), 1)
+            self._mol_acs = acs
+        cached = slot.pack_args
+        if cached is None or cached[0] is not self:
+            # everything that depends only on (data set, slot) is written once; a batch changes four fields
+            a = _lib.HostPackArgs()
+            a.n_mols_total, a.mol_ptr = self.num_mols(), self.ptr.ctypes.data
+            a.src_xyz, a.src_stride = self.xyz.ctypes.data, self.xyz.shape[1]
+            a.src_is_f64 = int(self.xyz.dtype == np.float64)
+            a.src_types = self.types.ctypes.data
+            a.src_ys = None if self.ys is None else self.ys.ctypes.data
+            a.src_grads = None if self.grads is None else self.grads.ctypes.data
+            a.src_mol_acs = self._mol_acs.ctypes.data
+            a.dst_xyz, a.dst_grads, a.dst_ys = slot.xyz.ctypes.data, slot.grads.ctypes.data, slot.ys.ctypes.data
+            a.dst_stride, a.dst_is_f64 = slot.cap_atoms, int(slot.np_dtype == np.float64)
+            a.dst_types, a.dst_mol_ids = slot.types.ctypes.data, slot.mol_ids.ctypes.data
+            a.dst_mol_offsets, a.dst_mol_counts = slot.mol_offsets.ctypes.data, slot.mol_counts.ctypes.data
+            a.cap_atoms, a.cap_mols = slot.cap_atoms, slot.cap_mols
+            n_atoms = ctypes.c_int(0)
+            a.n_atoms_out, a.acs_out = ctypes.addressof(n_atoms), slot.acs.ctypes.data
+            cached = slot.pack_args = (self, a, n_atoms, (self.xyz, self.types, self.ys, self.grads, self.ptr))
+        _, a, n_atoms, _ = cached
+        a.picks, a.n_picks = picks.ctypes.data, m
         a.noise = None if noise is None else noise.ctypes.data
-        a.dst_xyz, a.dst_grads, a.dst_ys = slot.xyz.ctypes.data, slot.grads.ctypes.data, slot.ys.ctypes.data
-        a.dst_stride, a.dst_is_f64 = slot.cap_atoms, int(slot.np_dtype == np.float64)
-        a.dst_types, a.dst_mol_ids = slot.types.ctypes.data, slot.mol_ids.ctypes.data
-        a.dst_mol_offsets, a.dst_mol_counts = slot.mol_offsets.ctypes.data, slot.mol_counts.ctypes.data
-        a.cap_atoms, a.cap_mols = slot.cap_atoms, slot.cap_mols
-        n_atoms = ctypes.c_int(0)
-        a.n_atoms_out, a.acs_out = ctypes.addressof(n_atoms), slot.acs.ctypes.data
         status = _lib.lib().ani_host_pack_batch(ctypes.byref(a))
         if status == -2:
             raise ValueError("batch larger than the slot")
@@ -172,6 +185,7 @@ class HostSlot:
 
     def __init__(self, cap_atoms: int, cap_mols: int, dtype, pin: bool):
         self.cap_atoms, self.cap_mols = cap_atoms, cap_mols
+        self.pack_args = None       # argument block of the host packer for the data set last gathered into this slot
         self.np_dtype = np.dtype(dtype)
         self.table, self.nbytes = _layout(cap_atoms, cap_mols, self.np_dtype.itemsize)
         self.arena = torch.zeros(self.nbytes, dtype=torch.uint8)
@@ -195,37 +209,81 @@ class HostSlot:
         self.acs = np.zeros(4, np.int32)
 
 
+def arena_views(host: "HostSlot", arena: torch.Tensor) -> dict:
+    """Full-capacity typed views of the arrays laid out in ``arena`` (a device or host copy of the slot's
+    arena).  Built once per slot: a batch only slices them."""
+    tdt = torch.float32 if host.np_dtype == np.float32 else torch.float64
+
+    def view(name, dt, rows):
+        off, size = host.table[name]
+        t = arena[off:off + size].view(dt)
+        return t.view(rows, host.cap_atoms) if rows > 1 else t
+
+    return {"xyz": view("xyz", tdt, 3), "types": view("types", torch.int32, 1),
+            "mol_offsets": view("mol_offsets", torch.int32, 1), "mol_counts": view("mol_counts", torch.int32, 1),
+            "mol_ids": view("mol_ids", torch.int64, 1), "ys": view("ys", tdt, 1), "grads": view("grads", tdt, 3)}
+
+
 class FedBatch:
     """What the feeder hands to the consumer: tensors of one batch (device tensors when the
     feeder has a device, host tensors otherwise) plus the host-side sizes the C ABI needs."""
 
-    def __init__(self, index: int, device, host: HostSlot, arena: torch.Tensor, ready):
+    def __init__(self, index: int, device, host: HostSlot, arena: torch.Tensor, ready, views=None):
         self.index, self.device, self.ready = index, device, ready
         n, m = host.n_atoms, host.n_mols
         self.n_atoms, self.n_mols = n, m
         self.acs = host.acs.copy()
         self.offsets_host = host.mol_offsets[:m].copy()
         self.counts_host = host.mol_counts[:m].copy()
-        tdt = torch.float32 if host.np_dtype == np.float32 else torch.float64
-
-        def view(name, dt, rows, cols, used):
-            off, size = host.table[name]
-            t = arena[off:off + size].view(dt)
-            return t.view(rows, cols)[:, :used] if rows > 1 else t[:used]
-
-        xyz = view("xyz", tdt, 3, host.cap_atoms, n)
-        self.x, self.y, self.z = xyz[0], xyz[1], xyz[2]          # each one contiguous range
-        self.types = view("types", torch.int32, 1, 0, n)
-        self.mol_offsets = view("mol_offsets", torch.int32, 1, 0, m)
-        self.mol_counts = view("mol_counts", torch.int32, 1, 0, m)
-        self.mol_ids = view("mol_ids", torch.int64, 1, 0, n)
-        self.ys = view("ys", tdt, 1, 0, m) if host.has_ys else None
-        self.grads = view("grads", tdt, 3, host.cap_atoms, n) if host.has_grads else None
+        v = views if views is not None else arena_views(host, arena)
+        xyz = v["xyz"]
+        self.x, self.y, self.z = xyz[0, :n], xyz[1, :n], xyz[2, :n]          # each one contiguous range
+        self.types = v["types"][:n]
+        self.mol_offsets = v["mol_offsets"][:m]
+        self.mol_counts = v["mol_counts"][:m]
+        self.mol_ids = v["mol_ids"][:n]
+        self.ys = v["ys"][:m] if host.has_ys else None
+        self.grads = v["grads"][:, :n] if host.has_grads else None
 
     def wait(self) -> None:
         """Makes the current stream of the batch's device wait for the upload."""
         if self.ready is not None:
             torch.cuda.current_stream(self.device).wait_event(self.ready)
+
+
+# Slot rings (pinned host arenas + device arenas) of finished feeders, kept for the next feeder of the same
+# shape: allocating pinned memory costs milliseconds, more than a whole pass over a small data set.
+_ring_lock = threading.Lock()
+_ring_cache: dict = {}
+_RING_CACHE_MAX = 4
+
+
+def _ring_key(dev, cap_atoms, cap_mols, dtype, depth):
+    return (None if dev is None else (torch.device(dev).type, torch.device(dev).index), cap_atoms, cap_mols,
+            np.dtype(dtype).name, depth)
+
+
+def _take_ring(dev, cap_atoms, cap_mols, dtype, depth):
+    key = _ring_key(dev, cap_atoms, cap_mols, dtype, depth)
+    with _ring_lock:
+        ring = _ring_cache.pop(key, None)
+    if ring is not None:
+        return ring
+    ring = []
+    for _ in range(depth + 1):
+        host = HostSlot(cap_atoms, cap_mols, dtype, pin=dev is not None)
+        arena = torch.empty(host.nbytes, dtype=torch.uint8, device=dev) if dev is not None else host.arena
+        ring.append({"host": host, "arena": arena, "consumed": None, "uploaded": None,
+                     "views": arena_views(host, arena)})
+    return ring
+
+
+def _give_ring(dev, cap_atoms, cap_mols, dtype, depth, ring):
+    key = _ring_key(dev, cap_atoms, cap_mols, dtype, depth)
+    with _ring_lock:
+        if key not in _ring_cache and len(_ring_cache) >= _RING_CACHE_MAX:
+            _ring_cache.pop(next(iter(_ring_cache)))
+        _ring_cache[key] = ring
 
 
 class BatchFeeder:
@@ -247,14 +305,8 @@ class BatchFeeder:
         self.hold = max(1, hold if hold is not None else len(self.devices))
         cap_atoms, cap_mols = packed.capacity(batch_size)
         cap_atoms, cap_mols = max(cap_atoms, 1), max(cap_mols, 1)
-        self._slots = []
-        for dev in self.devices:
-            ring = []
-            for _ in range(self.depth + 1):
-                host = HostSlot(cap_atoms, cap_mols, packed.dtype, pin=dev is not None)
-                arena = torch.empty(host.nbytes, dtype=torch.uint8, device=dev) if dev is not None else host.arena
-                ring.append({"host": host, "arena": arena, "consumed": None})
-            self._slots.append(ring)
+        self._shape = (cap_atoms, cap_mols, packed.dtype)
+        self._slots = [_take_ring(dev, cap_atoms, cap_mols, packed.dtype, self.depth) for dev in self.devices]
         self._copy_streams = [torch.cuda.Stream(device=d) if d is not None else None for d in self.devices]
         self._ready = queue.Queue(maxsize=self.depth * len(self.devices))
         self._free = [queue.Queue() for _ in self.devices]
@@ -292,6 +344,9 @@ class BatchFeeder:
                 if slot["consumed"] is not None:
                     slot["consumed"].synchronize()     # the consumer's kernels on this slot are done
                     slot["consumed"] = None
+                if slot["uploaded"] is not None:
+                    slot["uploaded"].synchronize()     # the pinned arena may be rewritten only after its last copy
+                    slot["uploaded"] = None
                 picks = perm[b * self.batch_size: min((b + 1) * self.batch_size, p.num_mols())]
                 p.gather(picks, slot["host"], self.fuzz)
                 dev, ready = self.devices[tower], None
@@ -300,9 +355,8 @@ class BatchFeeder:
                         slot["arena"].copy_(slot["host"].arena, non_blocking=True)
                         ready = torch.cuda.Event()
                         ready.record()
-                fed = FedBatch(b, dev, slot["host"], slot["arena"], ready)
-                if dev is not None:
-                    ready.synchronize()   # the pinned arena may be rewritten only after the copy
+                fed = FedBatch(b, dev, slot["host"], slot["arena"], ready, slot["views"])
+                slot["uploaded"] = ready
                 self._put((tower, s, fed))
             self._put(None)
         except BaseException as exc:   # handed to the consumer, which re-raises it
@@ -352,6 +406,20 @@ class BatchFeeder:
                 return
 
     def close(self) -> None:
+        """Stops the submitter and hands the slot rings to the next feeder of the same shape.  Call it after
+        the work on the last batches has been enqueued (the iterator does so when it is exhausted)."""
         self._stop.set()
         if self._started and self._thread.is_alive() and threading.current_thread() is not self._thread:
             self._thread.join(timeout=5)
+        if self._slots is None or (self._started and self._thread.is_alive()):
+            return
+        for _, _, fed in list(self._held):      # what is still held counts as consumed from here on
+            self.release(fed)
+        while True:                             # batches the submitter had prepared but nobody took
+            try:
+                self._ready.get_nowait()
+            except queue.Empty:
+                break
+        for dev, ring in zip(self.devices, self._slots):
+            _give_ring(dev, *self._shape, self.depth, ring)
+        self._slots = None

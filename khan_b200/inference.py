@@ -47,53 +47,58 @@ class EnergyForces:
         ann = self.model.anns[t]
         return [w.detach() for w in ann.Ws], [b.detach() for b in ann.bs]
 
+    def _pass_args(self, sb: StagedBatch):
+        """The argument block of ``ani_network_pass_f32``: everything that does not change from batch to batch
+        is filled once (and again when the model's weights have moved), the batch's own fields per call."""
+        first = self.model.anns[0].Ws[0]
+        packed = self.model.packed_weights()
+        key = (first.data_ptr(), None if packed is None else packed.data_ptr())
+        if getattr(self, "_pa_key", None) != key:
+            a = _lib.PassArgs()
+            a.activation, a.split_precision = self.act_id, int(self.split)
+            a.energy_sorted, a.grad_energy_sorted = self.energy_sorted.data_ptr(), self.ones.data_ptr()
+            for name, bufs in (("act", self.acts), ("dact", self.dacts), ("dz", self.dzs)):
+                for k, t in enumerate(bufs):
+                    setattr(a, f"{name}{k + 1}", t.data_ptr())
+            a.mol_energy = self.mol_energy.data_ptr()
+            for t in range(4):
+                (w1, w2, w3, w4), (b1, b2, b3, b4) = self._weights(t)
+                for name, v in (("w1", w1), ("w2", w2), ("w3", w3), ("w4", w4), ("b1", b1), ("b2", b2), ("b3", b3),
+                                ("b4", b4)):
+                    getattr(a, name)[t] = v.data_ptr()
+                if packed is not None:
+                    a.packed[t] = packed[t].data_ptr()
+            self._pa, self._pa_key = a, key
+        a = self._pa
+        a.n_atoms, a.n_mols, a.acs_host = sb.n_atoms, sb.n_mols, sb.acs_host.ctypes.data
+        a.xs, a.ys, a.zs = sb.x.data_ptr(), sb.y.data_ptr(), sb.z.data_ptr()
+        a.atomic_numbers, a.mol_offsets, a.mol_atom_counts = (sb.types.data_ptr(), sb.mol_offsets.data_ptr(),
+                                                              sb.mol_counts.data_ptr())
+        a.scatter_idxs, a.gather_idxs, a.atom_counts = sb.scatter.data_ptr(), sb.gather.data_ptr(), sb.counts.data_ptr()
+        a.features, a.feature_grads = sb.features.data_ptr(), sb.upstream.data_ptr()
+        g, cap, esz = sb.grads.data_ptr(), sb.n_atoms_cap, sb.grads.element_size()
+        a.x_grads, a.y_grads, a.z_grads = g, g + cap * esz, g + 2 * cap * esz
+        return a
+
     def run(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None, pack: bool = True,
             forces: bool = True) -> None:
-        """One pass over the batch staged in ``sb``.  Afterwards ``self.mol_energy[:sb.n_mols]``
-        holds the molecule energies and ``sb.grads[:, :sb.n_atoms]`` dE/dx, dE/dy, dE/dz (forces are
-        their negatives).  ``pack=False`` skips the refresh of the pre-packed weights: for a caller
-        that packed them (``model.pack_weights``) after the last change of the weights, e.g. once
-        before a series of passes that run side by side on several streams.  ``forces=False`` stops
-        after the molecule energies (``predict``)."""
+        """One pass over the batch staged in ``sb`` -- one C-ABI call (``ani_network_pass_f32``).  Afterwards
+        ``self.mol_energy[:sb.n_mols]`` holds the molecule energies and ``sb.grads[:, :sb.n_atoms]`` dE/dx,
+        dE/dy, dE/dz (forces are their negatives).  ``pack=False`` skips the refresh of the pre-packed
+        weights: for a caller that packed them (``model.pack_weights``) after the last change of the
+        weights, e.g. once before a series of passes that run side by side on several streams.
+        ``forces=False`` stops after the molecule energies (``predict``)."""
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this evaluator")
         _lib.same_device(self.device, sb.features, sb.x, where="EnergyForces.run")
         if stream is None:
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        lib = _lib.lib()
-        n, acs = sb.n_atoms, sb.acs_host
-        starts = np.concatenate([[0], np.cumsum(acs)])
-        sb.run_sort(stream)
-        sb.run_featurize(stream)
-        fwd, bwd = _lib.MlpArgs(), _lib.MlpBackwardArgs()
-        packed = self.model.pack_weights(stream) if pack else self.model.packed_weights()
-        for t in range(4):
-            if acs[t] == 0:
-                continue
-            s = int(starts[t])
-            (w1, w2, w3, w4), (b1, b2, b3, b4) = self._weights(t)
-            fwd.features[t] = _ptr(sb.features, s * FEATURE_SIZE)
-            fwd.w1[t], fwd.w2[t], fwd.w3[t], fwd.w4[t] = _ptr(w1), _ptr(w2), _ptr(w3), _ptr(w4)
-            fwd.b1[t], fwd.b2[t], fwd.b3[t], fwd.b4[t] = _ptr(b1), _ptr(b2), _ptr(b3), _ptr(b4)
-            fwd.energy[t] = _ptr(self.energy_sorted, s)
-            if packed is not None:
-                fwd.packed[t] = bwd.packed[t] = _ptr(packed[t])
-            fwd.act1[t], fwd.act2[t], fwd.act3[t] = (_ptr(a, s * a.shape[1]) for a in self.acts)
-            fwd.dact1[t], fwd.dact2[t], fwd.dact3[t] = (_ptr(d, s * d.shape[1]) for d in self.dacts)
-            bwd.grad_energy[t] = _ptr(self.ones, s)
-            bwd.w1[t], bwd.w2[t], bwd.w3[t], bwd.w4[t] = _ptr(w1), _ptr(w2), _ptr(w3), _ptr(w4)
-            bwd.dact1[t], bwd.dact2[t], bwd.dact3[t] = (_ptr(d, s * d.shape[1]) for d in self.dacts)
-            bwd.dz1[t], bwd.dz2[t], bwd.dz3[t] = (_ptr(z, s * z.shape[1]) for z in self.dzs)
-            bwd.grad_features[t] = _ptr(sb.upstream, s * FEATURE_SIZE)   # the upstream of featurize_grad
-        _lib.check(lib.ani_mlp_forward_f32(ctypes.byref(fwd), sb._acs_ptr, self.act_id, int(self.split), stream),
-                   "ani_mlp_forward_f32")
-        _lib.check(lib.ani_molecule_energy_f32(_ptr(self.energy_sorted), _ptr(sb.gather), _ptr(sb.mol_offsets),
-                                               _ptr(sb.mol_counts), sb.n_mols, n, None, 0.0,
-                                               _ptr(self.mol_energy), None, None, stream), "ani_molecule_energy_f32")
-        if not forces:
-            return
-        _lib.check(lib.ani_mlp_backward_f32(ctypes.byref(bwd), sb._acs_ptr, int(self.split), stream),
-                   "ani_mlp_backward_f32")
-        sb.run_featurize_grad(stream)
+        if self.model.packed_weights() is None:
+            self.model.pack_weights(stream)          # allocates the packed copy (first use)
+            pack = False
+        a = self._pass_args(sb)
+        a.phases = ((_lib.PASS_PACK if pack else 0) | _lib.PASS_FEATURIZE | _lib.PASS_FORWARD | _lib.PASS_ENERGY
+                    | ((_lib.PASS_BACKWARD | _lib.PASS_COORD_GRAD) if forces else 0))
+        _lib.check(_lib.lib().ani_network_pass_f32(ctypes.byref(a), stream), "ani_network_pass_f32")
 
     KERNELS_PER_PASS = 7   # weight packing (unless pack=False), sort, featurize, mlp forward, molecule sums, mlp backward, featurize_grad

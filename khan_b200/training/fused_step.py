@@ -144,11 +144,53 @@ class FusedTrainStep:
         _lib.check(_lib.lib().ani_mlp_weight_grad_f32(ctypes.byref(wg), sb._acs_ptr, int(self.split), stream),
                    "ani_mlp_weight_grad_f32")
 
+    def _pass_args(self, sb: StagedBatch):
+        """Argument block of ``ani_network_pass_f32``; the fields that do not depend on the batch are filled
+        once (and again when the weights or their gradient buffers have moved)."""
+        first = self.model.anns[0].Ws[0]
+        packed = self.model.packed_weights()
+        key = (first.data_ptr(), first.grad.data_ptr(), None if packed is None else packed.data_ptr())
+        if getattr(self, "_pa_key", None) != key:
+            a = _lib.PassArgs()
+            a.activation, a.split_precision = self.act_id, int(self.split)
+            a.energy_sorted, a.grad_energy_sorted = self.energy_sorted.data_ptr(), self.grad_energy_sorted.data_ptr()
+            for name, bufs in (("act", self.acts), ("dact", self.dacts), ("dz", self.dzs)):
+                for k, t in enumerate(bufs):
+                    setattr(a, f"{name}{k + 1}", t.data_ptr())
+            a.mol_energy, a.l2s = self.mol_energy.data_ptr(), self.l2s.data_ptr()
+            for t, ann in enumerate(self.model.anns):
+                for k, (w, b) in enumerate(zip(ann.Ws, ann.bs)):
+                    getattr(a, f"w{k + 1}")[t], getattr(a, f"b{k + 1}")[t] = w.data_ptr(), b.data_ptr()
+                    getattr(a, f"dw{k + 1}")[t], getattr(a, f"db{k + 1}")[t] = w.grad.data_ptr(), b.grad.data_ptr()
+                if packed is not None:
+                    a.packed[t] = packed[t].data_ptr()
+            a.zero_ptr = self.optimizer.flat_grads.data_ptr()
+            a.zero_bytes = self.optimizer.flat_grads.numel() * 4
+            self._pa, self._pa_key = a, key
+        a = self._pa
+        a.n_atoms, a.n_mols, a.acs_host = sb.n_atoms, sb.n_mols, sb.acs_host.ctypes.data
+        a.xs, a.ys, a.zs = sb.x.data_ptr(), sb.y.data_ptr(), sb.z.data_ptr()
+        a.atomic_numbers, a.mol_offsets, a.mol_atom_counts = (sb.types.data_ptr(), sb.mol_offsets.data_ptr(),
+                                                              sb.mol_counts.data_ptr())
+        a.scatter_idxs, a.gather_idxs, a.atom_counts = sb.scatter.data_ptr(), sb.gather.data_ptr(), sb.counts.data_ptr()
+        a.features = sb.features.data_ptr()
+        return a
+
     def forward_backward(self, sb: StagedBatch, labels: torch.Tensor, feature_grad: bool = True) -> None:
-        """Everything up to the weight gradients, in order on the current stream."""
-        self.featurize(sb)
-        self.networks(sb, labels, feature_grad)
-        self.weight_gradients(sb)
+        """Everything up to the weight gradients, in order on the current stream: weight packing, sort,
+        featurize, networks forward, molecule energies + MSE gradient, networks backward, zero + weight
+        gradients -- one C-ABI call (``ani_network_pass_f32``)."""
+        self._check(sb)
+        stream = self._stream()
+        if self.model.packed_weights() is None:
+            self.model.pack_weights(stream)          # allocates the packed copy (first use)
+        a = self._pass_args(sb)
+        a.feature_grads = sb.upstream.data_ptr() if feature_grad else None
+        a.labels, a.grad_scale = labels.data_ptr(), 1.0 / max(sb.n_mols, 1)
+        a.phases = (_lib.PASS_PACK | _lib.PASS_FEATURIZE | _lib.PASS_FORWARD | _lib.PASS_ENERGY | _lib.PASS_BACKWARD
+                    | _lib.PASS_WEIGHT_GRAD)
+        _lib.check(_lib.lib().ani_network_pass_f32(ctypes.byref(a), stream), "ani_network_pass_f32")
+        self._args_key = None      # the per-phase argument blocks (networks / weight_gradients) are stale now
 
     def coordinate_gradient(self, sb: StagedBatch) -> None:
         """dLoss/dx, dy, dz into ``sb.grads`` (featurize_grad with ``sb.upstream`` as its upstream)."""
