@@ -1,8 +1,8 @@
 // Forward kernel for batches of small molecules (at most 32 atoms each, the size range of the
 // data sets khan trains on: its loaders drop larger molecules, data_utils.py:54,281-283).
 //
-// The central atoms of a molecule, in element order, are cut into ROUNDS of four consecutive
-// atoms, and a CTA is ONE WARP doing one round: a molecule has 8 CTAs (8 rounds, 32 atoms), a
+// The central atoms of a molecule, in element order, are dealt to ROUNDS of at most four atoms
+// (round r of R takes atoms r, r + R, ...), and a CTA is ONE WARP doing one round: a molecule has 8 CTAs (8 rounds, 32 atoms), a
 // CTA whose round lies behind the end of the molecule leaves after one load.  No warp needs
 // anything from another, every round gives its registers and shared memory back as soon as it
 // is done, and the rounds of a large molecule spread over the SMs.  A warp keeps the whole
@@ -221,9 +221,12 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
         }
         return;
     }
-    const int c_first = round * kMolCentrals;
-    if (c_first >= n) return;
-    const int G = min(kMolCentrals, n - c_first);
+    // Round r of a molecule with R rounds takes the central atoms r, r + R, r + 2 R, r + 3 R: every round
+    // gets the same mix of light and heavy atoms (atoms are in element order, and the cost of a central
+    // atom grows with the square of its neighbour count), so the rounds of a molecule cost about the same.
+    const int n_rounds = (n + kMolCentrals - 1) / kMolCentrals;
+    if (round >= n_rounds) return;
+    const int G = (n - round + n_rounds - 1) / n_rounds;
 
     MolLanes<T> ml;
     load_sorted_molecule<T>(xs, ys, zs, types, scatter, base, n, &ws.sort, &ml);
@@ -239,7 +242,7 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
     // ---- A: scan, one central atom after another ----
     unsigned skip = 0;   // central atoms that are finished (streaming routine) or refused
     for (int g = 0; g < G; g++) {
-        const int c = c_first + g;
+        const int c = round + g * n_rounds;
         const T xi = __shfl_sync(kFull, ml.x, c), yi = __shfl_sync(kFull, ml.y, c), zi = __shfl_sync(kFull, ml.z, c);
         const int ti = __shfl_sync(kFull, ml.type, c);
         const int srow = ws.sort.srow[c];

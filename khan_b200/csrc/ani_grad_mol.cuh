@@ -1,8 +1,8 @@
 // Coordinate-gradient kernel for batches of small molecules (at most 32 atoms each).
 //
 // One CTA per molecule, NW warps.  The central atoms of the molecule, in element order (see
-// load_sorted_molecule), are split evenly over the warps; a warp walks its share in ROUNDS of
-// three consecutive atoms and keeps the molecule in registers, lane = atom.  Per round:
+// load_sorted_molecule), are dealt to the warps in turn; a warp walks its share in ROUNDS of three
+// atoms and keeps the molecule in registers, lane = atom.  Per round:
 //   - the 384 upstream values of each of its central atoms are copied global -> shared memory
 //     with asynchronous 16-byte copies (cp.async), all requested at the start of the round, so
 //     the copies run under the arithmetic and cost three instructions per lane and row;
@@ -262,17 +262,19 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? 20 / NW : 1)
         MolLanes<T> ml;
         load_sorted_molecule<T>(xs, ys, zs, types, scatter, base, n, &ws.sort, &ml);
 
-        // Every warp takes the same number of consecutive central atoms (so the CTA has no idle warps) and
-        // walks them in rounds of GR.  Which warp gets the first share rotates with the molecule: a warp's
-        // scheduler is fixed by its index, and the last share is the short one.
-        const int share = (n + NW - 1) / NW;
-        const int c_begin = ((warp + m) % NW) * share, c_end = min(n, c_begin + share);
-        for (int c_first = c_begin; c_first < c_end; c_first += GR) {
-            const int G = min(GR, c_end - c_first);
+        // Warp w takes the central atoms w, w + NW, w + 2 NW, ... (element order) and walks them in rounds
+        // of GR: every warp gets the same number of atoms (no idle warps) AND the same mix of light and heavy
+        // ones -- the cost of a central atom grows with the square of its neighbour count, and consecutive
+        // atoms are of one element.  Which warp starts with atom 0 rotates with the molecule: a warp's
+        // scheduler is fixed by its index, and the last warps have one atom less.
+        const int w0 = (warp + m) % NW;
+        const int K = w0 < n ? (n - w0 + NW - 1) / NW : 0;   // central atoms of this warp
+        for (int k_first = 0; k_first < K; k_first += GR) {
+            const int G = min(GR, K - k_first);
             // ---- upstream rows of the round: one commit group per row slot ----
 #pragma unroll
             for (int g = 0; g < GR; g++) {
-                const int c = min(c_first + g, n - 1);
+                const int c = min(w0 + (k_first + g) * NW, n - 1);
                 const int ti = __shfl_sync(kFull, ml.type, c), sr = ws.sort.srow[c];
                 const int cap = ti == 0 ? acs0 : (ti == 1 ? acs1 : (ti == 2 ? acs2 : acs3));
                 if (g < G && sr >= 0 && sr < cap) {
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? 20 / NW : 1)
                 // ---- A: scan central atoms into the neighbour list until it is full ----
                 int used = 0, max_half = 0, taken = 0;
                 while (g < G) {
-                    const int c = c_first + g;
+                    const int c = w0 + (k_first + g) * NW;
                     const T xi = __shfl_sync(kFull, ml.x, c), yi = __shfl_sync(kFull, ml.y, c),
                             zi = __shfl_sync(kFull, ml.z, c);
                     const int ti = __shfl_sync(kFull, ml.type, c), sr = ws.sort.srow[c];
