@@ -129,6 +129,14 @@ __device__ __noinline__ void grad_atom_streaming_radial(const T* __restrict__ xs
 template <typename T> __device__ __forceinline__ T radial_vjp_dev(T rij, T fc, T dfc, const T* w)
 {
     const T slope = (T)-2 * (T)kR_eta * fc;
+    if constexpr (sizeof(T) == 8) {   // all 16 Gaussians from two exp() calls
+        double d[kNumRs], e[kNumRs];
+        gaussians_f64<RadialGrid>(rij, d, e);
+        double sum = 0.0;
+#pragma unroll
+        for (int r = 0; r < kNumRs; r++) sum += w[r] * e[r] * (d[r] * slope + dfc);
+        return sum;
+    }
     const Pair<T> sl{slope, slope}, dd{dfc, dfc};
     Pair<T> acc{(T)0, (T)0};
 #pragma unroll
@@ -154,6 +162,15 @@ __device__ __forceinline__ void angular_vjp_dev(T cosv, T sin2, T rij, T rik, T 
     const T rbar = (T)0.5 * (rij + rik);
 
     Pair<T> e[kNumARs / 2], de[kNumARs / 2];   // exp(-eta d_q^2) and d_q exp(-eta d_q^2)
+    if constexpr (sizeof(T) == 8) {
+        double dq[kNumARs], eq[kNumARs];
+        gaussians_f64<AngularGrid>(rbar, dq, eq);
+#pragma unroll
+        for (int q = 0; q < kNumARs; q += 2) {
+            e[q / 2] = Pair<T>{eq[q], eq[q + 1]};
+            de[q / 2] = Pair<T>{dq[q] * eq[q], dq[q + 1] * eq[q + 1]};
+        }
+    } else
 #pragma unroll
     for (int q = 0; q < kNumARs; q += 2) {
         const Pair<T> d{rbar - angular_shift<T>(q), rbar - angular_shift<T>(q + 1)};
@@ -197,7 +214,7 @@ __device__ __forceinline__ void angular_vjp_dev(T cosv, T sin2, T rij, T rik, T 
 }
 
 template <typename T, int NW>
-__global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? 20 / NW : 1)
+__global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? 20 / NW : 12 / NW)
     featurize_grad_mol_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
                               const int* __restrict__ types, const int* __restrict__ mol_offsets,
                               const int* __restrict__ mol_counts, int n_mols, int n_atoms,
