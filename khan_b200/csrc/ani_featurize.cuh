@@ -20,6 +20,7 @@
 #pragma once
 
 #include "ani_common.cuh"
+#include "ani_device_math.cuh"
 
 namespace ani {
 
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_FWD_MIN_CTAS *
                     const T rbar = (T)0.5 * (ua.w + ub.w);
                     const T fcprod = valid ? ws.ang_fc[a] * ws.ang_fc[b] : (T)0;
                     T A[kNumThetas], BF[kNumARs];
-                    angular_factors<T>(cosv, rbar, fcprod, A, BF);
+                    angular_factors_dev<T>(cosv, rbar, fcprod, A, BF);
 #pragma unroll
                     for (int t = 0; t < kNumThetas; t++) ws.A[t][lane] = A[t];
 #pragma unroll

@@ -38,6 +38,7 @@
 #pragma once
 
 #include "ani_common.cuh"
+#include "ani_device_math.cuh"
 #include "ani_featurize.cuh"
 
 namespace ani {
@@ -149,114 +150,6 @@ __device__ __forceinline__ bool decode_slot(const MolGroupInfo* tab, const unsig
     *a = valid ? (e.packed & 0xff) + ia : 0;
     *b = valid ? ((e.packed >> 8) & 0xff) + ib : 0;
     return valid;
-}
-
-// ---- float64 only: the Gaussians of all shifts from TWO calls of exp() ------------------------------
-// exp(-eta (r - s_k)^2) for equally spaced shifts s_k = s_0 + k D factorises into
-//   exp(-eta x^2) * exp(2 eta D x)^k * exp(-eta D^2 k^2),   x = r - s_0,
-// i.e. one exp for the first shift, one for the ratio, and a constant per shift.  The reference's
-// shifts are single-precision literals promoted to double (gpu_featurizer/parameters.h:79-114), so
-// they sit up to 1e-7 off the even grid; with e_k = (actual shift) - (grid point) the exact value is
-// the grid value times exp(eta e_k (x_k + d_k)), x_k / d_k the distance to the grid point / to the
-// actual shift, and that exponent is below 4e-6, so 1 + t + t^2 / 2 is exact to 1e-17.  In double a
-// library exp() costs some 35 instructions; this replaces 14 of the 16 radial and 2 of the 4 angular
-// ones of every pair.  (In float exp is one SFU instruction and nothing is gained.)
-struct RadialGrid {
-    static constexpr int kN = kNumRs;
-    static constexpr double kEta = 16.0, kS0 = 0.5, kDelta = 0.25625;
-    __device__ static double eps(int k)
-    {
-        constexpr double v[kN] = {0.00000000000000000e+00, 2.38418579323607105e-08, 4.76837158647214210e-08,
-                                  -4.76837157536991185e-08, -2.38418578213384080e-08, 1.11022302462515654e-16,
-                                  -9.53674315073982370e-08, 4.76837159757437234e-08, -4.76837156426768161e-08,
-                                  9.53674318404651444e-08, 2.22044604925031308e-16, -9.53674313963759346e-08,
-                                  4.76837160867660259e-08, -4.76837155316545136e-08, 9.53674319514874469e-08,
-                                  3.33066907387546962e-16};
-        return v[k];
-    }
-    __device__ static double grid_factor(int k)   // exp(-eta D^2 k^2)
-    {
-        constexpr double v[kN] = {1.0, 0.34971910635094079063, 0.014958134700577500195, 0.0000782481790297574252,
-                                  5.0062180207670567999e-8, 3.9172744395097853607e-12, 3.7488404577454681545e-17,
-                                  4.3878183249839540439e-23, 6.281148147606062409e-30, 1.0996846322891938883e-37,
-                                  2.3547022296838610375e-46, 6.1665542139028671753e-56, 1.9750942872771476687e-66,
-                                  7.7369863671725676252e-78, 3.7067607034345540139e-90, 2.1719808350408576127e-103};
-        return v[k];
-    }
-    __device__ static double shift(int k) { return radial_shift<double>(k); }
-};
-struct AngularGrid {
-    static constexpr int kN = kNumARs;
-    static constexpr double kEta = 6.0, kS0 = 0.5, kDelta = 0.65;
-    __device__ static double eps(int k)
-    {
-        constexpr double v[kN] = {0.00000000000000000e+00, -2.38418579323607105e-08, -4.76837158647214210e-08,
-                                  4.76837157536991185e-08};
-        return v[k];
-    }
-    __device__ static double grid_factor(int k)
-    {
-        constexpr double v[kN] = {1.0, 0.079261719264731553938, 0.000039468802825543528604, 1.2347282803234498325e-10};
-        return v[k];
-    }
-    __device__ static double shift(int k) { return angular_shift<double>(k); }
-};
-
-// d[k] = r - shift_k (the actual, promoted-float shift) and e[k] = exp(-eta d[k]^2), k = 0 .. Grid::kN - 1.
-template <typename Grid> __device__ __forceinline__ void gaussians_f64(double r, double* d, double* e)
-{
-    const double x0 = r - Grid::kS0;
-    const double first = exp(-Grid::kEta * x0 * x0);
-    const double ratio = exp(2.0 * Grid::kEta * Grid::kDelta * x0);
-    double power = 1.0;
-#pragma unroll
-    for (int k = 0; k < Grid::kN; k++) {
-        d[k] = r - Grid::shift(k);
-        const double xk = x0 - k * Grid::kDelta;
-        const double t = Grid::kEta * Grid::eps(k) * (xk + d[k]);
-        e[k] = (first * Grid::grid_factor(k)) * power * (1.0 + t * (1.0 + 0.5 * t));
-        power *= ratio;
-    }
-}
-
-// The 8 theta factors and 4 radial factors of one triplet (see angular_factors in ani_params.h),
-// arranged for the device: every constant is an immediate operand of a scalar instruction and
-// only the squarings run as packed pairs.
-template <typename T> __device__ __forceinline__ void angular_factors_dev(T cosv, T rbar, T fcprod, T* A, T* BF)
-{
-    const T c = Num<T>::max_((T)-1, Num<T>::min_((T)1, cosv));
-    const T s = Num<T>::sqrt_(Num<T>::max_((T)0, (T)1 - c * c));
-    T b[kNumThetas];
-#pragma unroll
-    for (int t = 0; t < kNumThetas; t++) b[t] = c * theta_cos<T>(t) + (s * theta_sin<T>(t) + (T)1);
-#pragma unroll
-    for (int t = 0; t < kNumThetas; t += 2) {
-        const Pair<T> b1{b[t], b[t + 1]};
-        const Pair<T> b2 = pmul(b1, b1);
-        const Pair<T> b4 = pmul(b2, b2);
-        const Pair<T> b8 = pmul(b4, b4);
-        A[t] = b8.x;
-        A[t + 1] = b8.y;
-    }
-    const T f = (T)kA_pref * fcprod;
-    if constexpr (sizeof(T) == 8) {
-        double d[kNumARs], e[kNumARs];
-        gaussians_f64<AngularGrid>(rbar, d, e);
-#pragma unroll
-        for (int q = 0; q < kNumARs; q++) BF[q] = e[q] * f;
-        return;
-    }
-    T d[kNumARs];
-#pragma unroll
-    for (int q = 0; q < kNumARs; q++) d[q] = rbar - angular_shift<T>(q);
-#pragma unroll
-    for (int q = 0; q < kNumARs; q += 2) {
-        const Pair<T> dd{d[q], d[q + 1]};
-        const Pair<T> d2 = pmul(dd, dd);
-        const Pair<T> bf = pmul(Pair<T>{Num<T>::exp_neg((T)kA_eta, d2.x), Num<T>::exp_neg((T)kA_eta, d2.y)}, Pair<T>{f, f});
-        BF[q] = bf.x;
-        BF[q + 1] = bf.y;
-    }
 }
 
 template <typename T>

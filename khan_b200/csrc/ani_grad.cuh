@@ -25,6 +25,7 @@
 #pragma once
 
 #include "ani_common.cuh"
+#include "ani_device_math.cuh"
 
 namespace ani {
 
@@ -79,7 +80,7 @@ __device__ __noinline__ void grad_atom_streaming(const T* __restrict__ xs, const
                     const int bk = pair_bucket(tj, types[base + k] & 3);
                     T dc, drj, drk;
                     const T s2 = sin2_from_cross<T>(ujx, ujy, ujz, ukx, uky, ukz);
-                    angular_vjp<T, T>(c, s2, rj, rk, fj, dfj, fk, dfk,
+                    angular_vjp_dev<T>(c, s2, rj, rk, fj, dfj, fk, dfk,
                                       g + kRadial + bk * kGradBucketStride, &dc, &drj, &drk);
                     const T aj = -dc / rj, bj = c * dc / rj - drj;
                     const T ak = -dc / rk, bkk = c * dc / rk - drk;
@@ -199,7 +200,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
                 if (in_rad) {
                     T fc, dfc;
                     cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
-                    const T d = radial_vjp<T, T>(r, fc, dfc, ws.g + tj * kNumRs);
+                    const T d = radial_vjp_dev<T>(r, fc, dfc, ws.g + tj * kNumRs);
                     const T fx = d * ux, fy = d * uy, fz = d * uz;
                     fix += fx; fiy += fy; fiz += fz;
                     atomicAdd(&gx[gj], -fx);
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(NW* kWarp, sizeof(T) == 4 ? ANI_GRAD_MIN_CTAS 
 #pragma unroll
                         for (int q = 0; q < kTS; q += 4) load4(gsrc + q, gl + q);
                         T dc, dra, drb;
-                        angular_vjp<T, T>(c, s2, ea.u.w, eb.u.w, ea.fc, ea.dfc, eb.fc, eb.dfc, gl, &dc,
+                        angular_vjp_dev<T>(c, s2, ea.u.w, eb.u.w, ea.fc, ea.dfc, eb.fc, eb.dfc, gl, &dc,
                                           &dra, &drb);
                         T ra_inv, rb_inv, unused;
                         length_and_inverse(ea.u.w * ea.u.w, &unused, &ra_inv);

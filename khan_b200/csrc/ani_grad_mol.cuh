@@ -100,7 +100,7 @@ __device__ __noinline__ void grad_atom_streaming_radial(const T* __restrict__ xs
             if (r < (T)kR_Rc) {
                 T fc, dfc;
                 cutoff<T>(r, (T)kR_Rc, &fc, &dfc);
-                const T d = radial_vjp<T, T>(r, fc, dfc, g + (types[base + j] & 3) * kNumRs);
+                const T d = radial_vjp_dev<T>(r, fc, dfc, g + (types[base + j] & 3) * kNumRs);
                 const T fx = d * dx * inv, fy = d * dy * inv, fz = d * dz * inv;
                 fix += fx; fiy += fy; fiz += fz;
                 atomicAdd(&gx[base + j], -fx);
@@ -120,97 +120,6 @@ __device__ __noinline__ void grad_atom_streaming_radial(const T* __restrict__ xs
         atomicAdd(&gy[base + i], fiy);
         atomicAdd(&gz[base + i], fiz);
     }
-}
-
-// radial_vjp and angular_vjp of ani_params.h, arranged for the device: the same arithmetic, but every
-// constant (shift, cos / sin of a theta shift) is an immediate operand of a scalar instruction, and
-// only products of two computed values run as packed pairs.  (A packed instruction takes its
-// operands from register pairs, so a pair of constants would cost two moves per use.)
-template <typename T> __device__ __forceinline__ T radial_vjp_dev(T rij, T fc, T dfc, const T* w)
-{
-    const T slope = (T)-2 * (T)kR_eta * fc;
-    if constexpr (sizeof(T) == 8) {   // all 16 Gaussians from two exp() calls
-        double d[kNumRs], e[kNumRs];
-        gaussians_f64<RadialGrid>(rij, d, e);
-        double sum = 0.0;
-#pragma unroll
-        for (int r = 0; r < kNumRs; r++) sum += w[r] * e[r] * (d[r] * slope + dfc);
-        return sum;
-    }
-    const Pair<T> sl{slope, slope}, dd{dfc, dfc};
-    Pair<T> acc{(T)0, (T)0};
-#pragma unroll
-    for (int r = 0; r < kNumRs; r += 2) {
-        const Pair<T> d{rij - radial_shift<T>(r), rij - radial_shift<T>(r + 1)};
-        const Pair<T> d2 = pmul(d, d);
-        const Pair<T> e{Num<T>::exp_neg((T)kR_eta, d2.x), Num<T>::exp_neg((T)kR_eta, d2.y)};
-        acc = pfma(pmul(Pair<T>{w[r], w[r + 1]}, e), pfma(d, sl, dd), acc);
-    }
-    return acc.x + acc.y;
-}
-
-template <typename T>
-__device__ __forceinline__ void angular_vjp_dev(T cosv, T sin2, T rij, T rik, T fcj, T dfcj, T fck, T dfck,
-                                                const T* g, T* dc, T* drj, T* drk)
-{
-    const T c = Num<T>::max_((T)-1, Num<T>::min_((T)1, cosv));
-    const T s2 = Num<T>::min_((T)1, sin2);
-    const T s = Num<T>::sqrt_(s2);
-    const bool bent = s2 > (T)1e-12;  // sin(theta) > 1e-6
-    const T cot = bent ? c * Num<T>::rsqrt_(s2) : (T)0;
-    const T keep = bent ? (T)1 : (T)0;
-    const T rbar = (T)0.5 * (rij + rik);
-
-    Pair<T> e[kNumARs / 2], de[kNumARs / 2];   // exp(-eta d_q^2) and d_q exp(-eta d_q^2)
-    if constexpr (sizeof(T) == 8) {
-        double dq[kNumARs], eq[kNumARs];
-        gaussians_f64<AngularGrid>(rbar, dq, eq);
-#pragma unroll
-        for (int q = 0; q < kNumARs; q += 2) {
-            e[q / 2] = Pair<T>{eq[q], eq[q + 1]};
-            de[q / 2] = Pair<T>{dq[q] * eq[q], dq[q + 1] * eq[q + 1]};
-        }
-    } else
-#pragma unroll
-    for (int q = 0; q < kNumARs; q += 2) {
-        const Pair<T> d{rbar - angular_shift<T>(q), rbar - angular_shift<T>(q + 1)};
-        const Pair<T> d2 = pmul(d, d);
-        e[q / 2] = Pair<T>{Num<T>::exp_neg((T)kA_eta, d2.x), Num<T>::exp_neg((T)kA_eta, d2.y)};
-        de[q / 2] = pmul(d, e[q / 2]);
-    }
-    T u[kNumThetas], v[kNumThetas];   // u[t] = sum_q g[t][q] e[q], v[t] = sum_q g[t][q] de[q]
-#pragma unroll
-    for (int t = 0; t < kNumThetas; t++) {
-        const Pair<T> g01{g[t * kNumARs + 0], g[t * kNumARs + 1]}, g23{g[t * kNumARs + 2], g[t * kNumARs + 3]};
-        const Pair<T> pu = pfma(g23, e[1], pmul(g01, e[0]));
-        const Pair<T> pv = pfma(g23, de[1], pmul(g01, de[0]));
-        u[t] = pu.x + pu.y;
-        v[t] = pv.x + pv.y;
-    }
-    T b[kNumThetas];
-#pragma unroll
-    for (int t = 0; t < kNumThetas; t++) b[t] = c * theta_cos<T>(t) + (s * theta_sin<T>(t) + (T)1);
-    Pair<T> s0p{(T)0, (T)0}, s2p{(T)0, (T)0};
-    T sc = (T)0, ss = (T)0;
-#pragma unroll
-    for (int t = 0; t < kNumThetas; t += 2) {
-        const Pair<T> b1{b[t], b[t + 1]}, ut{u[t], u[t + 1]}, vt{v[t], v[t + 1]};
-        const Pair<T> b2 = pmul(b1, b1);
-        const Pair<T> b4 = pmul(b2, b2);
-        const Pair<T> b7 = pmul(pmul(b4, b2), b1);
-        const Pair<T> a = pmul(b7, b1);
-        s0p = pfma(a, ut, s0p);
-        s2p = pfma(a, vt, s2p);
-        const Pair<T> b7u = pmul(b7, ut);
-        sc += b7u.x * theta_cos<T>(t) + b7u.y * theta_cos<T>(t + 1);
-        ss += b7u.x * theta_sin<T>(t) + b7u.y * theta_sin<T>(t + 1);
-    }
-    const T s0 = s0p.x + s0p.y, s2sum = s2p.x + s2p.y;
-    const T f = (T)kA_pref * fcj * fck;
-    *dc = (T)8 * f * (keep * sc - cot * ss);                 // dA_t/dc = 8 b^7 (cos(theta_t) - sin(theta_t) c / s)
-    const T common = -(T)kA_eta * f * s2sum;                  // through rbar: d rbar / d r = 1/2, d e/d rbar = -2 eta d e
-    *drj = common + (T)kA_pref * dfcj * fck * s0;
-    *drk = common + (T)kA_pref * fcj * dfck * s0;
 }
 
 template <typename T, int NW>
