@@ -53,9 +53,9 @@ FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # SMs x lanes x FMA x max SM 
 # named in NCU_TRAFFIC_SOURCE, on an 8192-molecule batch whose 170 MB of features exceed the L2;
 # traffic grows in proportion to the atoms, so a launch is scaled by its atom count.  The numbers
 # belong to those kernels: when a kernel changes, the capture has to be repeated.
-NCU_DRAM_BYTES_PER_ATOM = {"featurize": 1035.2, "featurize_grad": 1571.7, "ani_sort": None}
-NCU_TRAFFIC_SOURCE = ("one ncu capture of featurize_kernel / featurize_grad_kernel (one warp per atom), "
-                      "8192-molecule batch, scaled by atoms")
+NCU_DRAM_BYTES_PER_ATOM = {"featurize": 1063.3, "featurize_grad": 1563.9, "ani_sort": None}
+NCU_TRAFFIC_SOURCE = ("one ncu capture of featurize_mol_kernel / featurize_grad_mol_kernel (a molecule per warp / per "
+                      "CTA), 8192-molecule batch, scaled by atoms")
 
 
 def measured_peaks():
