@@ -112,6 +112,42 @@ def measure_fma_peak(bits: int, device) -> float:
     return best
 
 
+def _parse_cpulist(text):
+    cpus = set()
+    for part in text.strip().split(","):
+        if "-" in part:
+            lo, hi = part.split("-")
+            cpus.update(range(int(lo), int(hi) + 1))
+        elif part:
+            cpus.add(int(part))
+    return cpus
+
+
+def bind_near_gpu(local_rank, n_local):
+    """Restrict this process to host cores on the GPU's own NUMA node, before any pinned buffer is
+    allocated (pages are placed where they are first touched) and share those cores evenly with the
+    other ranks whose GPUs hang off the same node.  Reads sysfs only; returns a short record for the
+    result line, or None where the topology cannot be read (then nothing is changed)."""
+    import torch
+    try:
+        allowed = os.sched_getaffinity(0)
+        local = []
+        for i in range(n_local):
+            p = torch.cuda.get_device_properties(i)
+            bus = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+            with open("/sys/bus/pci/devices/%s/local_cpulist" % bus) as f:
+                local.append(frozenset(_parse_cpulist(f.read()) & allowed))
+        mine = local[local_rank]
+        sharers = [i for i in range(n_local) if local[i] == mine]
+        cpus = sorted(mine)[sharers.index(local_rank)::len(sharers)]
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return {"cores": len(cpus), "node_cores": len(mine), "ranks_on_node": len(sharers)}
+    except (OSError, AttributeError, ValueError, IndexError, RuntimeError):
+        return None
+
+
 class Ctx:
     """Rank, device and process group of this process (one rank per GPU under torchrun)."""
 
@@ -122,6 +158,7 @@ class Ctx:
         self.world = int(os.environ.get("WORLD_SIZE", "1"))
         self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+        self.host_binding = bind_near_gpu(self.local_rank, self.world) if self.world > 1 else None
         torch.cuda.set_device(self.local_rank)
         self.dev = torch.device("cuda", self.local_rank)
         if self.world > 1 and not dist.is_initialized():
@@ -1312,6 +1349,7 @@ def main():
         "gpu_launches": args.steps * launches_per_step,
         "kernels": {k: {"avg_us": v * 1e6} for k, v in kernel_s.items()},
         "roofline": roofline, "roofline_fp32": roofline_fp32, "whole_step": whole_step,
+        "host_binding": ctx.host_binding,
         "clocks": sampler.summary(t_load0, t_load1),
         "clocks_timed_region": sampler.summary(t_timed0, t_timed1),
     }

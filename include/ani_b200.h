@@ -480,6 +480,50 @@ typedef struct ani_pass_args {
 } ani_pass_args;
 int ani_network_pass_f32(const ani_pass_args* args, void* stream);
 
+/*
+ * The submitter thread of the batch feeder in native code (the reference: a Python thread that
+ * pushes feed_dicts into a TensorFlow FIFOQueue, khan/training/trainer_multi_tower.py:749-828,
+ * over batches assembled by khan/data/dataset.py:144-183).  A feeder owns a ring of slots; a slot
+ * is one pinned HOST arena laid out by the caller (the dst_* pointers of `pack` point into it),
+ * its DEVICE twin of the same size, and the source pointers of the packed data set (src_*,
+ * mol_ptr, n_mols_total, cap_* of `pack`; picks, noise and the *_out fields are set by the feeder).
+ * One pass:
+ *   ani_feeder_begin(f, order, n, batch_size)   batch b = molecules order[b*batch_size ...) of the
+ *                                               data set; starts the thread, which packs batch
+ *                                               after batch into free slots (ani_host_pack_batch)
+ *                                               and enqueues ONE host-to-device copy of the arena
+ *                                               per batch on the feeder's own copy stream
+ *   ani_feeder_next(f, &b)     blocks until the next batch is packed and its copy enqueued;
+ *                              returns 1 (a batch), 0 (pass over) or a negative ANI_ERR_* of the thread
+ *   ani_feeder_wait(f, slot, stream)      `stream` waits for that batch's copy
+ *   ani_feeder_release(f, slot, stream)   the slot may be refilled; the next copy into its device
+ *                                         arena is ordered behind the work enqueued on `stream` so far
+ *   ani_feeder_end(f)          stops the thread (idempotent; begin() calls it first)
+ * device < 0: host only -- no CUDA call is made, the consumer reads the host arenas (stream unused).
+ * A slot's arenas must outlive the feeder; ani_feeder_destroy waits for the copies still in flight.
+ * Calls on one feeder come from one consumer thread.
+ */
+typedef struct ani_feeder_slot {
+    ani_host_pack_args pack;
+    void* host_arena;   /* pinned when device >= 0 */
+    void* dev_arena;    /* NULL when device < 0 */
+    size_t nbytes;      /* bytes copied per batch (the whole arena) */
+} ani_feeder_slot;
+typedef struct ani_feeder_batch {
+    int slot;
+    long long batch_index;
+    int n_atoms, n_mols;
+    int acs[4];         /* atoms per element: what ani_sort returns as atom_counts */
+} ani_feeder_batch;
+typedef struct ani_feeder ani_feeder;
+int ani_feeder_create(int device, const ani_feeder_slot* slots, int n_slots, ani_feeder** out);
+int ani_feeder_begin(ani_feeder* f, const long long* order, long long n_order, int batch_size);
+int ani_feeder_next(ani_feeder* f, ani_feeder_batch* out);
+int ani_feeder_wait(ani_feeder* f, int slot, void* stream);
+int ani_feeder_release(ani_feeder* f, int slot, void* stream);
+int ani_feeder_end(ani_feeder* f);
+int ani_feeder_destroy(ani_feeder* f);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,12 +17,12 @@ LIB_PATH = os.environ.get("ANI_B200_LIB") or os.path.join(_HERE, "libani_b200.so
 CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
-HEADERS = ["ani_params.h", "ani_common.cuh", "ani_device_math.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_featurize_mol.cuh", "ani_grad.cuh", "ani_grad_mol.cuh",
+HEADERS = ["ani_params.h", "ani_common.cuh", "ani_device_math.cuh", "ani_feeder.h", "ani_sort.cuh", "ani_featurize.cuh", "ani_featurize_mol.cuh", "ani_grad.cuh", "ani_grad_mol.cuh",
            "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh", "ani_energy.cuh", "ani_host_pack.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread", "-shared",
 ]
 
 _lock = threading.Lock()
@@ -55,6 +55,18 @@ class HostPackArgs(ctypes.Structure):
                 ("dst_mol_offsets", ctypes.c_void_p), ("dst_mol_counts", ctypes.c_void_p),
                 ("cap_atoms", ctypes.c_int), ("cap_mols", ctypes.c_int), ("n_atoms_out", ctypes.c_void_p),
                 ("acs_out", ctypes.c_void_p), ("src_mol_acs", ctypes.c_void_p)]
+
+
+class FeederSlot(ctypes.Structure):
+    """``ani_feeder_slot`` of include/ani_b200.h."""
+    _fields_ = [("pack", HostPackArgs), ("host_arena", ctypes.c_void_p), ("dev_arena", ctypes.c_void_p),
+                ("nbytes", ctypes.c_size_t)]
+
+
+class FeederBatch(ctypes.Structure):
+    """``ani_feeder_batch`` of include/ani_b200.h."""
+    _fields_ = [("slot", ctypes.c_int), ("batch_index", ctypes.c_longlong), ("n_atoms", ctypes.c_int),
+                ("n_mols", ctypes.c_int), ("acs", ctypes.c_int * 4)]
 
 
 class PassArgs(ctypes.Structure):
@@ -116,6 +128,13 @@ SIGNATURES = {
     "ani_clip_rows_f32": (_i, [_vp, _vp, _vp, _i, ctypes.c_float, _vp]),
     "ani_host_pack_batch": (_i, [_vp]),
     "ani_network_pass_f32": (_i, [ctypes.POINTER(PassArgs), _vp]),
+    "ani_feeder_create": (_i, [_i, _vp, _i, ctypes.POINTER(_vp)]),
+    "ani_feeder_begin": (_i, [_vp, _vp, ctypes.c_longlong, _i]),
+    "ani_feeder_next": (_i, [_vp, ctypes.POINTER(FeederBatch)]),
+    "ani_feeder_wait": (_i, [_vp, _i, _vp]),
+    "ani_feeder_release": (_i, [_vp, _i, _vp]),
+    "ani_feeder_end": (_i, [_vp]),
+    "ani_feeder_destroy": (_i, [_vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_f64": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_grad_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp, _vp]),

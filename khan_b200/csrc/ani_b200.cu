@@ -7,6 +7,7 @@
 #include <stdlib.h>
 
 #include <initializer_list>
+#include <new>
 #include <mutex>
 #include <vector>
 
@@ -25,6 +26,7 @@
 #include "ani_energy.cuh"
 #include "ani_sort.cuh"
 #include "ani_host_pack.h"
+#include "ani_feeder.h"
 
 namespace {
 
@@ -868,6 +870,63 @@ int ani_host_pack_batch(const ani_host_pack_args* args)
 {
     if (!args) return ANI_ERR_NULL_POINTER;
     return ani::host_pack_batch(*args);
+}
+
+struct ani_feeder {
+    ani::Feeder impl;
+    ani_feeder(int device, const ani_feeder_slot* slots, int n) : impl(device, slots, n) {}
+};
+
+int ani_feeder_create(int device, const ani_feeder_slot* slots, int n_slots, ani_feeder** out)
+{
+    if (!slots || !out) return ANI_ERR_NULL_POINTER;
+    if (n_slots <= 0) return ANI_ERR_BAD_SIZE;
+    for (int s = 0; s < n_slots; s++)
+        if (!slots[s].host_arena || (device >= 0 && !slots[s].dev_arena)) return ANI_ERR_NULL_POINTER;
+    ani_feeder* f = new (std::nothrow) ani_feeder(device, slots, n_slots);
+    if (!f) return ANI_ERR_CUDA;
+    if (int rc = f->impl.init()) {
+        delete f;
+        return rc;
+    }
+    *out = f;
+    return ANI_OK;
+}
+
+int ani_feeder_begin(ani_feeder* f, const long long* order, long long n_order, int batch_size)
+{
+    return f ? f->impl.begin(order, n_order, batch_size) : ANI_ERR_NULL_POINTER;
+}
+
+int ani_feeder_next(ani_feeder* f, ani_feeder_batch* out)
+{
+    return f && out ? f->impl.next(out) : ANI_ERR_NULL_POINTER;
+}
+
+int ani_feeder_wait(ani_feeder* f, int slot, void* stream)
+{
+    return f ? f->impl.wait(slot, static_cast<cudaStream_t>(stream)) : ANI_ERR_NULL_POINTER;
+}
+
+int ani_feeder_release(ani_feeder* f, int slot, void* stream)
+{
+    return f ? f->impl.release(slot, static_cast<cudaStream_t>(stream)) : ANI_ERR_NULL_POINTER;
+}
+
+int ani_feeder_end(ani_feeder* f)
+{
+    if (!f) return ANI_ERR_NULL_POINTER;
+    f->impl.end();
+    return ANI_OK;
+}
+
+int ani_feeder_destroy(ani_feeder* f)
+{
+    if (!f) return ANI_OK;
+    f->impl.end();
+    const int rc = f->impl.drain();
+    delete f;
+    return rc;
 }
 
 int ani_network_pass_f32(const ani_pass_args* a, void* stream)

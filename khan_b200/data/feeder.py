@@ -86,6 +86,38 @@ class PackedDataset:
         top = np.sort(self.counts)[-k:] if k else np.zeros(0, np.int64)
         return int(top.sum()), k
 
+    def mol_acs(self) -> np.ndarray:
+        """Atoms per element of every molecule ``[n_mols, 4]``, counted once per data set."""
+        if self._mol_acs is None:
+            ok = (self.types >= 0) & (self.types < 4)
+            mol_of = np.repeat(np.arange(self.num_mols()), self.counts)
+            acs = np.zeros((self.num_mols(), 4), np.int32)
+            np.add.at(acs, (mol_of[ok], self.types[ok]), 1)
+            self._mol_acs = acs
+        return self._mol_acs
+
+    def check_shapes(self, slot: "HostSlot") -> None:
+        total = int(self.ptr[-1])
+        if (self.types.shape[0] != total or self.xyz.shape != (3, total) or slot.np_dtype != self.dtype
+                or (self.grads is not None and self.grads.shape != (3, total))
+                or (self.ys is not None and self.ys.shape[0] != self.num_mols())):
+            raise ValueError("the arrays of the packed dataset do not match its molecule table")
+
+    def fill_pack_args(self, a, slot: "HostSlot") -> None:
+        """The fields of an ``ani_host_pack_args`` that depend only on (data set, slot)."""
+        a.n_mols_total, a.mol_ptr = self.num_mols(), self.ptr.ctypes.data
+        a.src_xyz, a.src_stride = self.xyz.ctypes.data, self.xyz.shape[1]
+        a.src_is_f64 = int(self.xyz.dtype == np.float64)
+        a.src_types = self.types.ctypes.data
+        a.src_ys = None if self.ys is None else self.ys.ctypes.data
+        a.src_grads = None if self.grads is None else self.grads.ctypes.data
+        a.src_mol_acs = self.mol_acs().ctypes.data
+        a.dst_xyz, a.dst_grads, a.dst_ys = slot.xyz.ctypes.data, slot.grads.ctypes.data, slot.ys.ctypes.data
+        a.dst_stride, a.dst_is_f64 = slot.cap_atoms, int(slot.np_dtype == np.float64)
+        a.dst_types, a.dst_mol_ids = slot.types.ctypes.data, slot.mol_ids.ctypes.data
+        a.dst_mol_offsets, a.dst_mol_counts = slot.mol_offsets.ctypes.data, slot.mol_counts.ctypes.data
+        a.cap_atoms, a.cap_mols = slot.cap_atoms, slot.cap_mols
+
     def gather(self, picks: np.ndarray, slot: "HostSlot", fuzz=None) -> None:
         """Writes the batch made of molecules ``picks`` (in that order) into ``slot``: one call of
         the library's host packer (``ani_host_pack_batch``), a per-molecule copy loop in C++."""
@@ -93,37 +125,16 @@ class PackedDataset:
         m = len(picks)
         if m > slot.cap_mols:
             raise ValueError("batch larger than the slot")
-        total = int(self.ptr[-1])
-        if (self.types.shape[0] != total or self.xyz.shape != (3, total) or slot.np_dtype != self.dtype
-                or (self.grads is not None and self.grads.shape != (3, total))
-                or (self.ys is not None and self.ys.shape[0] != self.num_mols())):
-            raise ValueError("the arrays of the packed dataset do not match its molecule table")
+        self.check_shapes(slot)
         noise = None
         if fuzz is not None:   # same draws as RawDataset.iterate: x of all atoms, then y, then z
             n = int(self.counts[picks].sum())
             noise = np.ascontiguousarray(np.random.uniform(-fuzz, fuzz, (3, n)).T)
-        if self._mol_acs is None:      # atoms per element of every molecule, once per data set
-            ok = (self.types >= 0) & (self.types < 4)
-            mol_of = np.repeat(np.arange(self.num_mols()), self.counts)
-            acs = np.zeros((self.num_mols(), 4), np.int32)
-            np.add.at(acs, (mol_of[ok], self.types[ok]), 1)
-            self._mol_acs = acs
         cached = slot.pack_args
         if cached is None or cached[0] is not self:
             # everything that depends only on (data set, slot) is written once; a batch changes four fields
             a = _lib.HostPackArgs()
-            a.n_mols_total, a.mol_ptr = self.num_mols(), self.ptr.ctypes.data
-            a.src_xyz, a.src_stride = self.xyz.ctypes.data, self.xyz.shape[1]
-            a.src_is_f64 = int(self.xyz.dtype == np.float64)
-            a.src_types = self.types.ctypes.data
-            a.src_ys = None if self.ys is None else self.ys.ctypes.data
-            a.src_grads = None if self.grads is None else self.grads.ctypes.data
-            a.src_mol_acs = self._mol_acs.ctypes.data
-            a.dst_xyz, a.dst_grads, a.dst_ys = slot.xyz.ctypes.data, slot.grads.ctypes.data, slot.ys.ctypes.data
-            a.dst_stride, a.dst_is_f64 = slot.cap_atoms, int(slot.np_dtype == np.float64)
-            a.dst_types, a.dst_mol_ids = slot.types.ctypes.data, slot.mol_ids.ctypes.data
-            a.dst_mol_offsets, a.dst_mol_counts = slot.mol_offsets.ctypes.data, slot.mol_counts.ctypes.data
-            a.cap_atoms, a.cap_mols = slot.cap_atoms, slot.cap_mols
+            self.fill_pack_args(a, slot)
             n_atoms = ctypes.c_int(0)
             a.n_atoms_out, a.acs_out = ctypes.addressof(n_atoms), slot.acs.ctypes.data
             cached = slot.pack_args = (self, a, n_atoms, (self.xyz, self.types, self.ys, self.grads, self.ptr))
@@ -228,8 +239,9 @@ class FedBatch:
     """What the feeder hands to the consumer: tensors of one batch (device tensors when the
     feeder has a device, host tensors otherwise) plus the host-side sizes the C ABI needs."""
 
-    def __init__(self, index: int, device, host: HostSlot, arena: torch.Tensor, ready, views=None):
+    def __init__(self, index: int, device, host: HostSlot, arena: torch.Tensor, ready, views=None, waiter=None):
         self.index, self.device, self.ready = index, device, ready
+        self._waiter = waiter    # native submitter: makes a stream wait for the slot's upload
         n, m = host.n_atoms, host.n_mols
         self.n_atoms, self.n_mols = n, m
         self.acs = host.acs.copy()
@@ -247,7 +259,9 @@ class FedBatch:
 
     def wait(self) -> None:
         """Makes the current stream of the batch's device wait for the upload."""
-        if self.ready is not None:
+        if self._waiter is not None:
+            self._waiter()
+        elif self.ready is not None:
             torch.cuda.current_stream(self.device).wait_event(self.ready)
 
 
@@ -282,8 +296,61 @@ def _give_ring(dev, cap_atoms, cap_mols, dtype, depth, ring):
     key = _ring_key(dev, cap_atoms, cap_mols, dtype, depth)
     with _ring_lock:
         if key not in _ring_cache and len(_ring_cache) >= _RING_CACHE_MAX:
-            _ring_cache.pop(next(iter(_ring_cache)))
+            _drop_native(_ring_cache.pop(next(iter(_ring_cache))))   # its copies finish before its arenas go
+        elif key in _ring_cache and _ring_cache[key] is not ring:
+            _drop_native(_ring_cache[key])
         _ring_cache[key] = ring
+
+
+class _NativeHandle:
+    """Owns one ``ani_feeder`` of the library; destroyed (after its copies have finished) with the object."""
+
+    def __init__(self, device_index: int, slots_array, n: int):
+        self.ptr = ctypes.c_void_p()
+        _lib.check(_lib.lib().ani_feeder_create(device_index, ctypes.addressof(slots_array), n, ctypes.byref(self.ptr)),
+                   "ani_feeder_create")
+
+    def __del__(self):
+        if self.ptr:
+            _lib.lib().ani_feeder_destroy(self.ptr)
+            self.ptr = ctypes.c_void_p()
+
+
+def _drop_native(ring) -> None:
+    """Before a ring goes to the Python submitter: the native one is stopped and its copies have finished."""
+    nat = ring[0].pop("native", None)
+    if nat is not None:
+        nat["owner"].__del__()
+
+
+def _native_submitter(ring, packed: "PackedDataset", dev) -> dict:
+    """The native submitter bound to (ring, data set), made once and kept with the ring."""
+    nat = ring[0].get("native")
+    if nat is not None and nat["packed"] is packed:
+        return nat
+    _drop_native(ring)
+    for slot in ring:       # what a Python submitter left behind on these slots
+        for key in ("consumed", "uploaded"):
+            if slot[key] is not None:
+                slot[key].synchronize()
+                slot[key] = None
+    n = len(ring)
+    arr = (_lib.FeederSlot * n)()
+    for k, slot in enumerate(ring):
+        host = slot["host"]
+        packed.check_shapes(host)
+        packed.fill_pack_args(arr[k].pack, host)
+        arr[k].host_arena = host.arena.data_ptr()
+        arr[k].dev_arena = None if dev is None else slot["arena"].data_ptr()
+        arr[k].nbytes = host.nbytes
+        host.pack_args = None
+    index = -1 if dev is None else (torch.device(dev).index if torch.device(dev).index is not None
+                                    else torch.cuda.current_device())
+    owner = _NativeHandle(index, arr, n)
+    nat = {"owner": owner, "handle": owner.ptr, "packed": packed, "slots": arr, "batch": _lib.FeederBatch(),
+           "order": None, "keep": (packed.xyz, packed.types, packed.ys, packed.grads, packed.ptr, packed.mol_acs())}
+    ring[0]["native"] = nat
+    return nat
 
 
 class BatchFeeder:
@@ -319,6 +386,14 @@ class BatchFeeder:
         self._started = False
         self._finished = False
         self._held = []
+        # One device and no fuzz (whose draws come from numpy's global generator, batch by batch): the
+        # submitter is the library's native thread, and the interpreter lock stays with the consumer.
+        self._native = None
+        if fuzz is None and len(self.devices) == 1:
+            self._native = _native_submitter(self._slots[0], packed, self.devices[0])
+        else:
+            for ring in self._slots:
+                _drop_native(ring)
 
     # ---- submitter thread ---------------------------------------------------------------
     def _take_free(self, tower: int):
@@ -375,9 +450,53 @@ class BatchFeeder:
     def __iter__(self):
         return self
 
+    def _stream_ptr(self):
+        dev = self.devices[0]
+        return None if dev is None else ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def _next_native(self) -> FedBatch:
+        nat, p, L = self._native, self.packed, _lib.lib()
+        if not self._started:
+            self._started = True
+            perm = np.arange(p.num_mols(), dtype=np.int64)
+            if self.shuffle:
+                np.random.shuffle(perm)
+            nat["order"] = perm     # read by the native thread until the pass ends
+            _lib.check(L.ani_feeder_begin(nat["handle"], perm.ctypes.data, len(perm), self.batch_size),
+                       "ani_feeder_begin")
+        while len(self._held) >= self.hold:
+            self.release(self._held[0][2])
+        fb = nat["batch"]
+        rc = L.ani_feeder_next(nat["handle"], ctypes.byref(fb))
+        if rc <= 0:
+            self._finished = True
+            self.close()
+            if rc == -2:
+                raise ValueError("batch larger than the slot")
+            _lib.check(rc, "ani_feeder_next")
+            raise StopIteration
+        s = fb.slot
+        slot = self._slots[0][s]
+        host = slot["host"]
+        host.n_atoms, host.n_mols = fb.n_atoms, fb.n_mols
+        host.acs[:] = fb.acs
+        host.has_ys, host.has_grads = p.ys is not None, p.grads is not None
+        dev = self.devices[0]
+        waiter = None
+        if dev is not None:
+            handle = nat["handle"]
+
+            def waiter(s=s):
+                _lib.check(L.ani_feeder_wait(handle, s, self._stream_ptr()), "ani_feeder_wait")
+        fed = FedBatch(int(fb.batch_index), dev, host, slot["arena"], None, slot["views"], waiter)
+        self._held.append((0, s, fed))
+        return fed
+
     def __next__(self) -> FedBatch:
         if self._finished:
             raise StopIteration
+        if self._native is not None:
+            return self._next_native()
         if not self._started:
             self._started = True
             self._thread.start()
@@ -398,6 +517,10 @@ class BatchFeeder:
         for k, (tower, s, f) in enumerate(self._held):
             if f is fed:
                 del self._held[k]
+                if self._native is not None:
+                    _lib.check(_lib.lib().ani_feeder_release(self._native["handle"], s, self._stream_ptr()),
+                               "ani_feeder_release")
+                    return
                 if fed.device is not None:
                     evt = torch.cuda.Event()
                     evt.record(torch.cuda.current_stream(fed.device))
@@ -408,6 +531,16 @@ class BatchFeeder:
     def close(self) -> None:
         """Stops the submitter and hands the slot rings to the next feeder of the same shape.  Call it after
         the work on the last batches has been enqueued (the iterator does so when it is exhausted)."""
+        if self._native is not None:
+            if self._slots is None:
+                return
+            _lib.lib().ani_feeder_end(self._native["handle"])
+            for _, _, fed in list(self._held):
+                self.release(fed)
+            self._native["order"] = None
+            _give_ring(self.devices[0], *self._shape, self.depth, self._slots[0])
+            self._slots = None
+            return
         self._stop.set()
         if self._started and self._thread.is_alive() and threading.current_thread() is not self._thread:
             self._thread.join(timeout=5)

@@ -61,6 +61,44 @@ def test_round_robin_hold_and_slot_reuse():
     assert k == len(want) - 1
 
 
+def test_native_submitter_holds_reuses_and_survives_an_early_close():
+    """One device and no fuzz: the submitter is the library's thread (ani_feeder_*).  A held batch stays intact
+    while it runs ahead, a pass that is abandoned half way leaves the ring usable, and the next feeder on the
+    same data set and shape takes the ring AND the native submitter over."""
+    ds = _dataset(n_mols=64, with_grads=False)
+    want = list(ds.iterate(batch_size=4, shuffle=False))
+    packed = PackedDataset.from_raw(ds)
+    feeder = BatchFeeder(packed, 4, False, depth=1, hold=2)
+    assert feeder._native is not None
+    handle = feeder._native["handle"].value
+    previous = None
+    for k, fed in enumerate(feeder):
+        assert fed.index == k and np.array_equal(fed.x.numpy(), want[k][0][:, 1].astype(np.float32))
+        if previous is not None:
+            assert np.array_equal(previous.x.numpy(), want[k - 1][0][:, 1].astype(np.float32))
+        previous = fed
+        if k == 5:
+            break
+    feeder.close()                               # abandoned after six of sixteen batches
+    feeder.close()
+    for _ in range(3):                           # whole passes on the submitter that was kept with the ring
+        feeder = BatchFeeder(packed, 4, False, depth=1, hold=2)
+        assert feeder._native["handle"].value == handle
+        got = [fed.x.numpy().copy() for fed in feeder]
+        assert len(got) == len(want)
+        assert all(np.array_equal(g, w[0][:, 1].astype(np.float32)) for g, w in zip(got, want))
+    np.random.seed(11)
+    shuffled = list(ds.iterate(batch_size=4, shuffle=True))
+    np.random.seed(11)
+    got = [fed.x.numpy().copy() for fed in BatchFeeder(packed, 4, True, depth=1, hold=2)]
+    assert all(np.array_equal(g, w[0][:, 1].astype(np.float32)) for g, w in zip(got, shuffled))
+    # another data set of the same shape on the same ring: a new submitter, the old one is retired
+    other = PackedDataset(ds.all_Xs, ds.all_ys, None)
+    feeder = BatchFeeder(other, 4, False, depth=1, hold=2)
+    assert feeder._native["packed"] is other
+    assert len(list(feeder)) == len(want)
+
+
 def test_empty_dataset_and_packing_cache():
     ds = RawDataset([], [])
     assert list(BatchFeeder(PackedDataset.from_raw(ds), 8, False)) == []
@@ -74,7 +112,10 @@ def test_submitter_errors_reach_the_consumer():
     ds = _dataset(9, with_grads=False)
     packed = PackedDataset.from_raw(ds)
     feeder = BatchFeeder(packed, 4, False)
-    packed.types = packed.types[:3]          # corrupt the packed data: gather will fail
+    packed.ptr[-1] += 1000                   # corrupt the molecule table in place: the last batch cannot fit
+    with pytest.raises((ValueError, IndexError)):
+        list(feeder)
+    feeder = BatchFeeder(packed, 4, False, fuzz=0.1)   # the same through the Python submitter
     with pytest.raises((ValueError, IndexError)):
         list(feeder)
 
