@@ -793,6 +793,23 @@ def capture_overlapped(staged, side, fn_name="run_step"):
     return g
 
 
+def time_kernel_overlapped(staged, side, fn_name, reps):
+    """Average time (s) per launch of one kernel kind when its launches over all staged batches are spread over
+    the side streams exactly as the steps of the timed region are: the kernel's share of a step there, where
+    the tail of one launch runs beside the start of the next (time_kernel_alone has them one after another)."""
+    import torch
+    g = capture_overlapped(staged, side, fn_name)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / (reps * len(staged))
+
+
 def time_kernel_alone(staged, fn_name, reps):
     """Average duration (s) of one launch of a kernel kind: a graph of that kernel over all staged batches,
     one after another on one stream, replayed ``reps`` times."""
@@ -1156,6 +1173,11 @@ def main():
     kernel_s = {"ani_sort": time_kernel_alone(staged, "run_sort", reps),
                 "featurize": time_kernel_alone(staged, "run_featurize", reps),
                 "featurize_grad": time_kernel_alone(staged, "run_featurize_grad", reps)}
+    kernel_overlapped_s = None
+    if mega is not None:
+        kernel_overlapped_s = {k: time_kernel_overlapped(staged, side, fn, reps) for k, fn in
+                               (("ani_sort", "run_sort"), ("featurize", "run_featurize"),
+                                ("featurize_grad", "run_featurize_grad"))}
     t_load1 = time.perf_counter()
 
     # ---- end to end through the C ABI with host buffers ---------------------------------------
@@ -1179,16 +1201,19 @@ def main():
                 atoms += slots[s].n_atoms
         return h2d, d2h, atoms
 
-    def copy_pass(n_steps):
-        """The transfers of e2e_pass with no kernel between them: what the host link alone allows."""
+    def copy_pass(n_steps, up_too=True, down_too=True):
+        """The transfers of e2e_pass with no kernel between them (both directions, or one alone), one queue
+        per direction and nothing that orders one against the other: what the host link allows."""
         h2d = d2h = 0
-        up, down = streams[0], streams[-1]   # one queue per direction, nothing orders one against the other
+        up, down = streams[0], streams[-1]
         for k in range(n_steps):
             s = k % n_slots
-            with torch.cuda.stream(up):
-                h2d += slots[s].upload(host[k % n_host], non_blocking=True)
-            with torch.cuda.stream(down):
-                d2h += slots[s].download(out_feat[s], out_grad[s], non_blocking=True)
+            if up_too:
+                with torch.cuda.stream(up):
+                    h2d += slots[s].upload(host[k % n_host], non_blocking=True)
+            if down_too:
+                with torch.cuda.stream(down):
+                    d2h += slots[s].download(out_feat[s], out_grad[s], non_blocking=True)
         return h2d, d2h
 
     main_stream = torch.cuda.current_stream()
@@ -1221,11 +1246,17 @@ def main():
     _, e2e_total = ctx.max_sum(0.0, float(e2e_atoms))
     copy_runs, (c_h2d, c_d2h) = timed_host_passes(lambda: copy_pass(e2e_steps))
     copy_ms = statistics.median(copy_runs)
+    up_ms = statistics.median(timed_host_passes(lambda: copy_pass(e2e_steps, down_too=False))[0])
+    down_ms = statistics.median(timed_host_passes(lambda: copy_pass(e2e_steps, up_too=False))[0])
     e2e_extra = {"copy_only": {"atoms_per_s": e2e_total / (copy_ms * 1e-3),
                                "gbs_per_rank": (c_h2d + c_d2h) / (copy_ms * 1e-3) / 1e9,
+                               "h2d_alone_gbs_per_rank": c_h2d / (up_ms * 1e-3) / 1e9,
+                               "d2h_alone_gbs_per_rank": c_d2h / (down_ms * 1e-3) / 1e9,
+                               "ceiling_atoms_per_s": e2e_total / (max(up_ms, down_ms) * 1e-3),
                                "note": "the same host-to-device and device-to-host copies with no kernel launched, one "
-                                       "stream per direction and no ordering between the two: the ceiling that "
-                                       "the host link sets for this definition of end to end"}}
+                                       "stream per direction: both directions at once (atoms_per_s, gbs_per_rank), "
+                                       "each direction alone, and the ceiling if the slower direction hid the other "
+                                       "completely; times are the max over ranks"}}
     del slots, out_feat
 
     # ---- energies + forces end to end: coordinates in, molecule energies and forces out -----------
@@ -1317,6 +1348,11 @@ def main():
                                     "1.965 GHz; half of that for float64)",
                      "peak_measured": fma_measured, "peak_formula": formula_peak,
                      "pairs_per_atom": p_per_atom, "triplets_per_atom": t_per_atom}
+    if kernel_overlapped_s:
+        # the same kernel with its launches spread over the streams of the timed region (see time_kernel_overlapped)
+        t_ov = kernel_overlapped_s[dominant]
+        roofline_fp32["frac_on_the_step_streams"] = flops_per_atom[dominant] * mean_atoms / t_ov / 1e12 / arith_peak
+        roofline["frac_on_the_step_streams"] = bytes_per_atom[dominant] * mean_atoms / t_ov / 1e9 / roofline["peak"]
     # the bound that binds is the one with the larger fraction: the arithmetic one for these kernels
     roofline["binding_bound"] = ("fp32/fp64 arithmetic (roofline_fp32)" if roofline_fp32["frac"] >= roofline["frac"]
                                  else "hbm")
@@ -1347,7 +1383,9 @@ def main():
                 "best_atoms_per_s": e2e_total / (min(e2e_runs) * 1e-3), "reported": "median of 3 passes",
                 **e2e_extra},
         "gpu_launches": args.steps * launches_per_step,
-        "kernels": {k: {"avg_us": v * 1e6} for k, v in kernel_s.items()},
+        "kernels": {k: {"avg_us": v * 1e6,
+                        "avg_us_on_the_step_streams": (kernel_overlapped_s[k] * 1e6 if kernel_overlapped_s else None)}
+                    for k, v in kernel_s.items()},
         "roofline": roofline, "roofline_fp32": roofline_fp32, "whole_step": whole_step,
         "host_binding": ctx.host_binding,
         "clocks": sampler.summary(t_load0, t_load1),

@@ -17,7 +17,7 @@ LIB_PATH = os.environ.get("ANI_B200_LIB") or os.path.join(_HERE, "libani_b200.so
 CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
-HEADERS = ["ani_params.h", "ani_common.cuh", "ani_device_math.cuh", "ani_feeder.h", "ani_sort.cuh", "ani_featurize.cuh", "ani_featurize_mol.cuh", "ani_grad.cuh", "ani_grad_mol.cuh",
+HEADERS = ["ani_params.h", "ani_common.cuh", "ani_device_math.cuh", "ani_feeder.h", "ani_sort.cuh", "ani_featurize.cuh", "ani_featurize_mol.cuh", "ani_featurize_large.cuh", "ani_featurize_round_passes.inl", "ani_grad.cuh", "ani_grad_mol.cuh", "ani_grad_pair_pass.inl",
            "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh", "ani_energy.cuh", "ani_host_pack.h"]
 
 NVCC_FLAGS = [

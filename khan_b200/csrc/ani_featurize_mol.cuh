@@ -53,8 +53,10 @@ constexpr int kMolChunk = kMolSlotsPerLane * kWarp;   // slots per pass B / C
 constexpr int kMolChunkStride = kMolChunk + 4;        // + 4 words: keeps the 16-byte reads of pass C conflict-free
 constexpr int kMolRounds = kMolMaxAtoms / kMolCentrals;   // rounds of the largest molecule of the fast path
 // padded slots of one central atom: at most CapA (CapA - 1) / 2 pairs + 3 per bucket, in quads
-constexpr int kMolQuadsPerCentral = (kMolCapA * (kMolCapA - 1) / 2 + 3 * kPairBuckets) / 4 + 1;
-constexpr int kMolQuadBytes = ((kMolCentrals * kMolQuadsPerCentral + 2 * (kMolChunk / 4) + 7) / 8) * 8;
+constexpr int mol_quad_bytes(int cap_a)
+{
+    return ((kMolCentrals * ((cap_a * (cap_a - 1) / 2 + 3 * kPairBuckets) / 4 + 1) + 2 * (kMolChunk / 4) + 7) / 8) * 8;
+}
 
 struct alignas(16) MolGroupInfo {
     int off;         // first slot of the group (a multiple of 4)
@@ -71,16 +73,24 @@ struct MolSortShared {
 };
 
 
-template <typename T> struct MolFwdWarpShared {
-    Vec4<T> ang_u[kMolCentrals * kMolCapA];   // (x_i - x_j) / r_ij and r_ij, element order, per central atom
-    T ang_fc[kMolCentrals * kMolCapA];        // f_C(r_ij, A_Rc)
-    Vec2<T> rad[kMolCentrals][kMolMaxAtoms];  // (r_ij, f_C(r_ij, R_Rc) or 0) of every atom j, per central atom
+// What the angular passes (T, B, C) of a round work on: the angular neighbour lists of the round's
+// central atoms (element order inside each list), the group table, the factor chunks and the rows.
+// CAPA = angular neighbours kept per central atom (at most 32: list indices are packed into 8 bits).
+template <typename T, int CAPA, int CAPR> struct MolAngularShared {
+    static constexpr int kCapA = CAPA;
+    Vec4<T> ang_u[kMolCentrals * CAPA];   // (x_i - x_j) / r_ij and r_ij, element order, per central atom
+    T ang_fc[kMolCentrals * CAPA];        // f_C(r_ij, A_Rc)
+    Vec2<T> rad[kMolCentrals][CAPR];      // (r_ij, f_C(r_ij, R_Rc)) per central atom: the radial pass reads it, not T / B / C
     alignas(16) T A[kNumThetas][kMolChunkStride];
     alignas(16) T BF[kNumARs][kMolChunkStride];
     MolGroupInfo tab[kMolCentrals * kMolGroupStride];
     T* row[kMolCentrals];                     // feature row of each central atom of the round
     alignas(16) int cnt_a[kMolCentrals * kTypes];   // angular neighbours per element, per central atom
-    alignas(8) unsigned char quad_gid[kMolQuadBytes];
+    alignas(8) unsigned char quad_gid[mol_quad_bytes(CAPA)];
+};
+
+template <typename T> struct MolFwdWarpShared {
+    MolAngularShared<T, kMolCapA, kMolMaxAtoms> ang;   // its radial table: every atom j of the molecule, f_C = 0 out of range
     MolSortShared sort;
 };
 
@@ -201,10 +211,10 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
 
     // Padding slots read entry 0 of the angular list, possibly before anything was written there.
     if (lane == 0) {
-        ws.ang_u[0] = Vec4<T>{(T)1, (T)0, (T)0, (T)1};
-        ws.ang_fc[0] = (T)0;
+        ws.ang.ang_u[0] = Vec4<T>{(T)1, (T)0, (T)0, (T)1};
+        ws.ang.ang_fc[0] = (T)0;
     }
-    if (lane < kMolCentrals * kTypes) ws.cnt_a[lane] = 0;
+    if (lane < kMolCentrals * kTypes) ws.ang.cnt_a[lane] = 0;
     __syncwarp();
 
     // ---- A: scan, one central atom after another ----
@@ -221,7 +231,7 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
             continue;
         }
         T* row = element_buffer<T>(ti, out_h, out_c, out_n, out_o) + (size_t)srow * kTotal;
-        if (lane == 0) ws.row[g] = row;
+        if (lane == 0) ws.ang.row[g] = row;
 
         const T dx = xi - ml.x, dy = yi - ml.y, dz = zi - ml.z;
         T r, inv;
@@ -244,20 +254,20 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
             for (int i = 0; i < (kGranules + kWarp - 1) / kWarp; i++)
                 if (i * kWarp + lane < kGranules) zero[i * kWarp + lane] = Granule{0.f, 0.f, 0.f, 0.f};
         }
-        ws.rad[g][lane] = Vec2<T>{r, in_rad ? cutoff_value<T>(r, (T)kR_Rc) : (T)0};
+        ws.ang.rad[g][lane] = Vec2<T>{r, in_rad ? cutoff_value<T>(r, (T)kR_Rc) : (T)0};
         if (in_ang) {
             const int p = g * kMolCapA + __popc(mA & lanemask_lt());
-            ws.ang_u[p] = Vec4<T>{dx * inv, dy * inv, dz * inv, r};
-            ws.ang_fc[p] = cutoff_value<T>(r, (T)kA_Rc);
+            ws.ang.ang_u[p] = Vec4<T>{dx * inv, dy * inv, dz * inv, r};
+            ws.ang.ang_fc[p] = cutoff_value<T>(r, (T)kA_Rc);
         }
-        if (lane < kTypes) ws.cnt_a[g * kTypes + lane] = __popc(mA & ws.sort.tmask[lane]);
+        if (lane < kTypes) ws.ang.cnt_a[g * kTypes + lane] = __popc(mA & ws.sort.tmask[lane]);
     }
     __syncwarp();
 
     // ---- R: radial features of the whole round, lane = (central atom, pair of shifts) ----
     {
         const int g = lane >> 3, sp = lane & 7;
-        const Vec2<T>* list = ws.rad[g];
+        const Vec2<T>* list = ws.ang.rad[g];
         const T sh0 = (T)c_tab.R_Rs[2 * sp], sh1 = (T)c_tab.R_Rs[2 * sp + 1];
         const uint4 tmq = *reinterpret_cast<const uint4*>(ws.sort.tmask);
         const int run_end[kTypes] = {__popc(tmq.x), __popc(tmq.x | tmq.y), __popc(tmq.x | tmq.y | tmq.z), n};
@@ -275,100 +285,15 @@ __global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
             }
         }
         if (g < G && !((skip >> g) & 1u)) {
-            T* row = ws.row[g];
+            T* row = ws.ang.row[g];
 #pragma unroll
             for (int t = 0; t < kTypes; t++)
                 *reinterpret_cast<Vec2<T>*>(row + t * kNumRs + 2 * sp) = Vec2<T>{acc[t].x, acc[t].y};
         }
     }
 
-    // ---- T: one table for the groups (central atom, element pair) of the round.  Lane = (central
-    // atom, bucket) covers the first eight buckets in one pass; N-O and O-O pairs (buckets 8, 9)
-    // are rare and get a second, short pass only when they occur. ----
-    int total = 0;
-    for (int pass = 0; pass < 2; pass++) {
-        const int g = pass == 0 ? lane >> 3 : (lane >> 1) & 3;
-        const int bk = pass == 0 ? lane & 7 : 8 + (lane & 1);
-        const bool act = pass == 0 || lane < 8;
-        const int ta = (kBucketTa >> (2 * bk)) & 3, tb = (kBucketTb >> (2 * bk)) & 3;
-        const int4 ca = *reinterpret_cast<const int4*>(&ws.cnt_a[g * kTypes]);
-        const int cav[kTypes] = {ca.x, ca.y, ca.z, ca.w};
-        const int stv[kTypes] = {0, ca.x, ca.x + ca.y, ca.x + ca.y + ca.z};
-        const int na = pick4(cav, ta), nb = pick4(cav, tb);
-        const int cnt = act ? (ta == tb ? na * (na - 1) / 2 : na * nb) : 0;
-        if (pass == 1 && !__any_sync(kFull, cnt > 0)) break;
-        const int pad = (cnt + 3) & ~3;
-        int incl = pad;
-#pragma unroll
-        for (int o = 1; o < kWarp; o <<= 1) {
-            const int y = __shfl_up_sync(kFull, incl, o);
-            if (lane >= o) incl += y;
-        }
-        const int off = total + incl - pad;
-        if (cnt > 0) {
-            MolGroupInfo e;
-            e.off = off;
-            e.cnt = cnt;
-            e.packed = (g * kMolCapA + pick4(stv, ta)) | ((g * kMolCapA + pick4(stv, tb)) << 8) | (nb << 16) |
-                       ((ta == tb ? 1 : 0) << 24);
-            e.recip = (unsigned)(65536.0f * __frcp_rn((float)nb)) + 1u;   // in [2^16 / nb, 2^16 / nb + 1.01)
-            const int gid = g * kMolGroupStride + bk;
-            ws.tab[gid] = e;
-            for (int q = off >> 2; q < (off + pad) >> 2; q++) ws.quad_gid[q] = (unsigned char)gid;
-        }
-        total += __shfl_sync(kFull, incl, kWarp - 1);
-    }
-    // ids behind the last group, through the end of its chunk and the look-ahead of pass C
-    for (int q = (total >> 2) + lane; q < (((total + kMolChunk - 1) & ~(kMolChunk - 1)) >> 2) + 1; q += kWarp)
-        ws.quad_gid[q] = (unsigned char)kMolNoGroup;
-    __syncwarp();
-
-    // ---- B + C over the slots of the round ----
-    const T* a_row = &ws.A[lane >> 2][0];
-    const T* b_row = &ws.BF[lane & 3][0];
-    Pair<T> acc0{(T)0, (T)0}, acc1{(T)0, (T)0};
-    for (int c0 = 0; c0 < total; c0 += kMolChunk) {
-        // B: lane = slot, kMolSlotsPerLane slots per lane (independent of one another)
-#pragma unroll
-        for (int u = 0; u < kMolSlotsPerLane; u++) {
-            int a, b;
-            const bool valid = decode_slot(ws.tab, ws.quad_gid, c0 + u * kWarp + lane, &a, &b);
-            const Vec4<T> ua = ws.ang_u[a], ub = ws.ang_u[b];
-            const T cosv = ua.x * ub.x + ua.y * ub.y + ua.z * ub.z;
-            const T rbar = (T)0.5 * (ua.w + ub.w);
-            const T fcprod = valid ? ws.ang_fc[a] * ws.ang_fc[b] : (T)0;
-            T A[kNumThetas], BF[kNumARs];
-            angular_factors_dev<T>(cosv, rbar, fcprod, A, BF);
-#pragma unroll
-            for (int t = 0; t < kNumThetas; t++) ws.A[t][u * kWarp + lane] = A[t];
-#pragma unroll
-            for (int q = 0; q < kNumARs; q++) ws.BF[q][u * kWarp + lane] = BF[q];
-        }
-        // quads of this chunk that end a group (the first lanes look at one quad each)
-        const unsigned char* ids = &ws.quad_gid[c0 >> 2];
-        constexpr int kQuads = kMolChunk / 4;
-        const unsigned my_id = ids[lane & (kQuads - 1)];
-        const unsigned ends =
-            __ballot_sync(kFull, lane < kQuads && my_id != kMolNoGroup && my_id != ids[(lane & (kQuads - 1)) + 1]);
-        __syncwarp();
-        // C: lane = (theta, shift).  Slots behind the last group hold BF = 0.
-#pragma unroll
-        for (int q = 0; q < kQuads; q++) {
-            T av[4], bv[4];
-            load4(a_row + 4 * q, av);
-            load4(b_row + 4 * q, bv);
-            acc0 = pfma(Pair<T>{av[0], av[1]}, Pair<T>{bv[0], bv[1]}, acc0);
-            acc1 = pfma(Pair<T>{av[2], av[3]}, Pair<T>{bv[2], bv[3]}, acc1);
-            if ((ends >> q) & 1u) {
-                const unsigned id = ids[q];
-                T* row = ws.row[id >> 4];
-                row[kRadial + (id & 15u) * kTS + lane] = (acc0.x + acc0.y) + (acc1.x + acc1.y);
-                acc0 = Pair<T>{(T)0, (T)0};
-                acc1 = Pair<T>{(T)0, (T)0};
-            }
-        }
-        __syncwarp();
-    }
+    constexpr int kRoundCapA = kMolCapA;
+#include "ani_featurize_round_passes.inl"
 }
 
 }  // namespace ani

@@ -213,6 +213,12 @@ CASES = {
     "config4_part": lambda: syn.config4(n_mols=12),
     "tiny_mols": lambda: syn.gdb_like_batch(40, 7, heavy_min=1, heavy_max=1),
     "mid_33_to_70_atoms": lambda: syn.config4(seed=9, n_mols=6, n_min=33, n_max=70),
+    # batches that take the kernels for larger molecules, with neighbourhoods beyond their lists: 40 atoms
+    # within 2.3 A of a point (up to 39 neighbours within A_Rc, the angular lists hold 32) and 80 atoms
+    # within 2.25 A (79 neighbours within R_Rc, the radial lists hold 64)
+    "dense_large": lambda: _concat(_dense_blobs(2, 40, 2.3, 11), syn.config4(seed=7, n_mols=4, n_min=40, n_max=90)),
+    "very_dense_large": lambda: _concat(_dense_blobs(1, 80, 2.25, 12),
+                                        syn.config4(seed=8, n_mols=3, n_min=40, n_max=60)),
 }
 
 
