@@ -502,14 +502,34 @@ def measure_fused_train(ctx, mols: int, steps: int, warmup: int, train_path: str
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
 
-    ms_local = None
+    ms_local = ms_nccl = peer = peer_err = None
     if pipelined:
         # next batch's sort + featurize and this batch's coordinate gradient beside the network kernels
-        pipe = StepPipeline(step, staged, labels, allreduce=world > 1, graphs=graphs)
+        if world > 1 and opt.flat_grads.numel() % 4 == 0:
+            # the mean over the ranks as one kernel of the library over peer memory, inside the step's graph;
+            # checked once against the library all-reduce on a buffer of random numbers
+            import torch.distributed as dist
+            from khan_b200.training.peer_allreduce import try_peer_allreduce
+            peer = try_peer_allreduce(opt.flat_grads.numel(), dev)
+            if peer is not None:
+                gen = torch.Generator(device=dev)
+                gen.manual_seed(77 + rank)
+                probe = torch.randn(opt.flat_grads.numel(), device=dev, generator=gen)
+                want = probe.clone()
+                dist.all_reduce(want, op=dist.ReduceOp.SUM)
+                want /= world
+                ctx.barrier()
+                torch.cuda.synchronize()
+                peer_err = float((peer.mean_(probe) - want).abs().max())
+                torch.cuda.synchronize()
+        pipe = StepPipeline(step, staged, labels, allreduce=world > 1, graphs=graphs, peer=peer)
         ms = timed(pipe.run, pipe.prime)
         if world > 1 and exposed:
             solo = StepPipeline(step, staged, labels, allreduce=False, graphs=graphs)
             ms_local = timed(solo.run, solo.prime)
+            if peer is not None:       # the same steps with the library all-reduce between two graphs, for comparison
+                lib_pipe = StepPipeline(step, staged, labels, allreduce=True, graphs=graphs)
+                ms_nccl = timed(lib_pipe.run, lib_pipe.prime)
     else:
         class _Eager:      # graphs off: the same calls issued directly (what ncu sees kernel by kernel)
             def __init__(self, fn):
@@ -557,12 +577,26 @@ def measure_fused_train(ctx, mols: int, steps: int, warmup: int, train_path: str
     out = {"ms_per_step": ms / steps, "atoms_per_s": atoms / (ms * 1e-3), "steps": steps, "n_gpus": world,
            "final_loss": loss, "gpu_launches_per_step": FusedTrainStep.KERNELS, "resident_batches": nb,
            "pipelined": pipelined,
-           "collective": ("NCCL all-reduce (mean) of the flat gradient buffer, %d float32 values" % opt.flat_grads.numel()
-                          if world > 1 else "none (one rank)")}
+           "collective": ("none (one rank)" if world == 1 else
+                          ("mean of the flat gradient buffer (%d float32 values) by one kernel of the library over peer "
+                           "memory (CUDA IPC, plain NVLink loads), inside the step's CUDA graph"
+                           if peer is not None else
+                           "NCCL all-reduce (mean) of the flat gradient buffer, %d float32 values, between two graphs")
+                          % opt.flat_grads.numel())}
     if ms_local is not None:
         ms_local, _ = ctx.max_sum(ms_local, 0.0)
         out["ms_per_step_without_allreduce"] = ms_local / steps
         out["exposed_allreduce_us"] = max(0.0, (ms - ms_local) / steps * 1e3)
+    if ms_nccl is not None:
+        ms_nccl, _ = ctx.max_sum(ms_nccl, 0.0)
+        out["ms_per_step_with_nccl_allreduce"] = ms_nccl / steps
+    if peer is not None:
+        from khan_b200 import ani_mod
+        out["peer_mean_max_abs_err_vs_nccl"] = peer_err
+        out["device_status_after"] = int(ani_mod.device_status())   # -8 if a bounded wait for another rank ran out
+        ctx.barrier()
+        torch.cuda.synchronize()
+        peer.close()
     return out
 
 
@@ -578,15 +612,22 @@ def run_fused_train_workload(args):
             "dtype": "f32 (tf32x3 tensor-core products in the atomic networks)", "data": "synthetic",
             "final_loss": r["final_loss"], "gpu_launches": args.steps * r["gpu_launches_per_step"],
             "exposed_allreduce_us": r.get("exposed_allreduce_us"),
+            "collective": r.get("collective"),
+            "ms_per_step_without_allreduce": r.get("ms_per_step_without_allreduce"),
+            "ms_per_step_with_nccl_allreduce": r.get("ms_per_step_with_nccl_allreduce"),
+            "peer_mean_max_abs_err_vs_nccl": r.get("peer_mean_max_abs_err_vs_nccl"),
+            "device_status_after": r.get("device_status_after"),
             "config": {"workload": "config3: sort + featurize + 4 x MLP 384-128-128-64-1 (gaussian, He init) + MSE "
-                                   "+ backward into weights and coordinates + NCCL all-reduce + Nadam",
+                                   "+ backward into weights and coordinates + mean of the weight gradients over the ranks "
+                                   "+ Nadam",
                        "molecules_per_step_per_gpu": args.mols, "path": "fused (C ABI only, no autograd)",
                        "resident_batches": r["resident_batches"],
                        "order": ("pipelined: sort + featurize of the next batch and the coordinate gradient of this "
                                  "one run beside the network kernels on two side streams" if r["pipelined"] else
                                  "serial: one kernel after another"),
                        "launch": ("eager" if args.no_graph else
-                                  "cuda_graph (all-reduce eager, between the weight gradients and the update)")}}),
+                                  "one cuda_graph per step" if ctx.world == 1 or "peer memory" in (r.get("collective") or "")
+                                  else "cuda_graph (all-reduce eager, between the weight gradients and the update)")}}),
               flush=True)
     ctx.close()
 

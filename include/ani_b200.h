@@ -524,6 +524,31 @@ int ani_feeder_release(ani_feeder* f, int slot, void* stream);
 int ani_feeder_end(ani_feeder* f);
 int ani_feeder_destroy(ani_feeder* f);
 
+/*
+ * Mean of a float buffer over the GPUs of one node through peer memory, one kernel launch per rank
+ * and call: the average of the weight gradients over the towers (the reference: per-variable concat
+ * + reduce_mean on the CPU, khan/training/trainer_multi_tower.py:137-179).  One process per GPU;
+ * every rank creates a handle of the same capacity, the ranks exchange the 64-byte handles of their
+ * blocks (any host transport) and connect; from then on every rank calls ani_peer_mean_f32 the same
+ * number of times with buffers of the same length, and each call leaves the SAME mean, bit for bit,
+ * on every rank.  Launch only: it can be captured in a CUDA graph (the step number lives in device
+ * memory).  Calls on one handle must be ordered (one stream).  The wait for the other ranks is
+ * bounded (a fraction of a second by default): when it runs out, the call still ends, the result
+ * of that step is unspecified and ani_device_status reports ANI_ERR_TIMEOUT.
+ *   n: floats in the buffer, a multiple of 4, at most the capacity; buffer 16-byte aligned.
+ *   ani_peer_connect_raw / ani_peer_block: for ranks that live in one process (the peer's block by
+ *   address instead of by handle).  ani_peer_destroy synchronises the device first.
+ */
+typedef struct ani_peer ani_peer;
+int ani_peer_create(int rank, int world, long long n_floats, ani_peer** out);
+int ani_peer_handle(ani_peer* p, void* out64);
+int ani_peer_connect(ani_peer* p, int rank_q, const void* handle64);
+int ani_peer_connect_raw(ani_peer* p, int rank_q, void* block);
+void* ani_peer_block(ani_peer* p);
+int ani_peer_set_spin_limit(ani_peer* p, unsigned tries);
+int ani_peer_mean_f32(ani_peer* p, float* buffer, long long n, void* stream);
+int ani_peer_destroy(ani_peer* p);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,7 +17,7 @@ LIB_PATH = os.environ.get("ANI_B200_LIB") or os.path.join(_HERE, "libani_b200.so
 CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 SOURCES = ["ani_b200.cu"]
-HEADERS = ["ani_params.h", "ani_common.cuh", "ani_device_math.cuh", "ani_feeder.h", "ani_sort.cuh", "ani_featurize.cuh", "ani_featurize_mol.cuh", "ani_featurize_large.cuh", "ani_featurize_round_passes.inl", "ani_grad.cuh", "ani_grad_mol.cuh", "ani_grad_pair_pass.inl",
+HEADERS = ["ani_params.h", "ani_common.cuh", "ani_device_math.cuh", "ani_feeder.h", "ani_peer.cuh", "ani_sort.cuh", "ani_featurize.cuh", "ani_featurize_mol.cuh", "ani_featurize_large.cuh", "ani_featurize_round_passes.inl", "ani_grad.cuh", "ani_grad_mol.cuh", "ani_grad_pair_pass.inl",
            "ani_grad_inverse.cuh", "ani_mlp.cuh", "ani_mlp_pipe.cuh", "ani_mlp_forward.cuh", "ani_mlp_backward.cuh", "ani_mlp_wgrad.cuh", "ani_charge.cuh", "ani_optim.cuh", "ani_energy.cuh", "ani_host_pack.h"]
 
 NVCC_FLAGS = [
@@ -135,6 +135,14 @@ SIGNATURES = {
     "ani_feeder_release": (_i, [_vp, _i, _vp]),
     "ani_feeder_end": (_i, [_vp]),
     "ani_feeder_destroy": (_i, [_vp]),
+    "ani_peer_create": (_i, [_i, _i, ctypes.c_longlong, ctypes.POINTER(_vp)]),
+    "ani_peer_handle": (_i, [_vp, _vp]),
+    "ani_peer_connect": (_i, [_vp, _i, _vp]),
+    "ani_peer_connect_raw": (_i, [_vp, _i, _vp]),
+    "ani_peer_block": (_vp, [_vp]),
+    "ani_peer_set_spin_limit": (_i, [_vp, ctypes.c_uint]),
+    "ani_peer_mean_f32": (_i, [_vp, _vp, ctypes.c_longlong, _vp]),
+    "ani_peer_destroy": (_i, [_vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_f64": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),
     "ani_charge_grad_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp, _vp]),

@@ -5,6 +5,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <algorithm>
 #include <initializer_list>
@@ -29,6 +30,7 @@
 #include "ani_sort.cuh"
 #include "ani_host_pack.h"
 #include "ani_feeder.h"
+#include "ani_peer.cuh"
 
 namespace {
 
@@ -948,6 +950,124 @@ int ani_feeder_destroy(ani_feeder* f)
     const int rc = f->impl.drain();
     delete f;
     return rc;
+}
+
+struct ani_peer {
+    int device = 0, rank = 0, world = 1, grid = 1;
+    long long capacity = 0;              // floats per staging buffer
+    unsigned char* block = nullptr;      // local: [flags | staging 0 | staging 1]
+    ani::PeerState* state = nullptr;     // local
+    unsigned char* peer_block[ani::kPeerMaxRanks] = {};
+    bool mapped[ani::kPeerMaxRanks] = {};   // opened through CUDA IPC (to be closed)
+};
+
+int ani_peer_create(int rank, int world, long long n_floats, ani_peer** out)
+{
+    if (!out) return ANI_ERR_NULL_POINTER;
+    if (world < 1 || world > ani::kPeerMaxRanks || rank < 0 || rank >= world || n_floats <= 0) return ANI_ERR_BAD_SIZE;
+    ani_peer* p = new (std::nothrow) ani_peer();
+    if (!p) return ANI_ERR_CUDA;
+    p->rank = rank;
+    p->world = world;
+    p->capacity = (n_floats + 3) / 4 * 4;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDevice(&p->device);
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, p->device);
+    const size_t bytes = ani::kPeerFlagBytes + 2 * (size_t)p->capacity * sizeof(float);
+    if (e == cudaSuccess) e = cudaMalloc(&p->block, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p->block, 0, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&p->state, sizeof(ani::PeerState));
+    if (e == cudaSuccess) {
+        ani::PeerState init{0ull, 0ull, 0u, ani::kPeerSpinLimit};
+        e = cudaMemcpy(p->state, &init, sizeof(init), cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+        if (p->block) cudaFree(p->block);
+        if (p->state) cudaFree(p->state);
+        delete p;
+        return cuda_fail(e);
+    }
+    const long long groups = p->capacity / 4;
+    p->grid = (int)std::max<long long>(1, std::min<long long>((groups + ani::kPeerThreads - 1) / ani::kPeerThreads,
+                                                               prop.multiProcessorCount));
+    p->peer_block[rank] = p->block;
+    *out = p;
+    return ANI_OK;
+}
+
+int ani_peer_handle(ani_peer* p, void* out64)
+{
+    if (!p || !out64) return ANI_ERR_NULL_POINTER;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is exchanged as 64 bytes");
+    cudaIpcMemHandle_t h;
+    ANI_CUDA(cudaIpcGetMemHandle(&h, p->block));
+    memcpy(out64, &h, sizeof(h));
+    return ANI_OK;
+}
+
+int ani_peer_connect(ani_peer* p, int q, const void* handle64)
+{
+    if (!p || !handle64) return ANI_ERR_NULL_POINTER;
+    if (q < 0 || q >= p->world || q == p->rank || p->peer_block[q]) return ANI_ERR_BAD_INDEX;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    void* ptr = nullptr;
+    ANI_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    p->peer_block[q] = static_cast<unsigned char*>(ptr);
+    p->mapped[q] = true;
+    return ANI_OK;
+}
+
+int ani_peer_connect_raw(ani_peer* p, int q, void* block)
+{
+    if (!p || !block) return ANI_ERR_NULL_POINTER;
+    if (q < 0 || q >= p->world || q == p->rank || p->peer_block[q]) return ANI_ERR_BAD_INDEX;
+    p->peer_block[q] = static_cast<unsigned char*>(block);
+    return ANI_OK;
+}
+
+void* ani_peer_block(ani_peer* p) { return p ? p->block : nullptr; }
+
+int ani_peer_set_spin_limit(ani_peer* p, unsigned tries)
+{
+    if (!p) return ANI_ERR_NULL_POINTER;
+    ANI_CUDA(cudaMemcpy(&p->state->spin_limit, &tries, sizeof(tries), cudaMemcpyHostToDevice));
+    return ANI_OK;
+}
+
+int ani_peer_mean_f32(ani_peer* p, float* buffer, long long n, void* stream)
+{
+    if (!p || !buffer) return ANI_ERR_NULL_POINTER;
+    if (n < 0 || n > p->capacity || (n & 3)) return ANI_ERR_BAD_SIZE;
+    if (reinterpret_cast<uintptr_t>(buffer) & 15) return ANI_ERR_MISALIGNED;
+    ani::PeerParams a{};
+    a.buffer = buffer;
+    a.n4 = n / 4;
+    a.stage_floats = p->capacity;
+    a.rank = p->rank;
+    a.world = p->world;
+    for (int q = 0; q < p->world; q++) {
+        if (!p->peer_block[q]) return ANI_ERR_NULL_POINTER;   // a rank that was never connected
+        a.flags[q] = reinterpret_cast<unsigned*>(p->peer_block[q]);
+        a.stage[q] = reinterpret_cast<float*>(p->peer_block[q] + ani::kPeerFlagBytes);
+    }
+    a.state = p->state;
+    a.inv_world = 1.0f / (float)p->world;
+    ani::peer_mean_kernel<<<p->grid, ani::kPeerThreads, 0, (cudaStream_t)stream>>>(a);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
+int ani_peer_destroy(ani_peer* p)
+{
+    if (!p) return ANI_OK;
+    cudaDeviceSynchronize();
+    for (int q = 0; q < p->world; q++)
+        if (p->mapped[q]) cudaIpcCloseMemHandle(p->peer_block[q]);
+    cudaFree(p->block);
+    cudaFree(p->state);
+    delete p;
+    return ANI_OK;
 }
 
 int ani_network_pass_f32(const ani_pass_args* a, void* stream)

@@ -222,15 +222,20 @@ class StepPipeline:
 
     ``prime()`` featurizes batch 0; ``run(k)`` then performs step k on batch ``k % len(staged)``
     and featurizes the batch after it.  With ``graphs`` the phases are captured once per batch
-    (one graph per step on a single GPU; with ``allreduce`` the collective stays outside the
-    graphs, between the graph that ends with the weight gradients and the graph of the update).
+    (one graph per step on a single GPU, and with ``peer`` -- a ``PeerAllReduce`` -- on several: the mean
+    of the gradients over the ranks is then a kernel of the library inside the graph; with a library
+    all-reduce the collective stays outside the graphs, between the graph that ends with the weight
+    gradients and the graph of the update).
     """
 
-    def __init__(self, step: FusedTrainStep, staged, labels, allreduce: bool = False, graphs: bool = True):
+    def __init__(self, step: FusedTrainStep, staged, labels, allreduce: bool = False, graphs: bool = True,
+                 peer=None):
         if len(staged) < 2 or len(staged) != len(labels):
             raise ValueError("StepPipeline needs at least two resident batches and one label vector per batch")
         self.step, self.staged, self.labels = step, list(staged), list(labels)
         self.allreduce = bool(allreduce)
+        # a PeerAllReduce: the mean over the ranks is one kernel of the library and the step stays ONE graph
+        self.peer = peer if allreduce else None
         self.nb = len(self.staged)
         dev = step.device
         self.feature_stream = torch.cuda.Stream(device=dev)
@@ -253,7 +258,9 @@ class StepPipeline:
         with torch.cuda.stream(self.gradient_stream):
             step.coordinate_gradient(self.staged[b])
         step.weight_gradients(self.staged[b])
-        if update:       # single GPU; with several ranks the all-reduce comes first
+        if update:       # single GPU, or the mean over the ranks as a kernel of this library
+            if self.peer is not None:
+                self.peer.mean_(step.optimizer.flat_grads)
             step.optimizer.step()
         cur.wait_stream(self.gradient_stream)
 
@@ -266,9 +273,9 @@ class StepPipeline:
 
     def _capture(self) -> None:
         with torch.cuda.device(self.step.device):
-            self._whole = [self._graph_of(lambda b=b: self._issue(b, not self.allreduce))
-                           for b in range(self.nb)]
-            if self.allreduce:
+            whole = not self.allreduce or self.peer is not None
+            self._whole = [self._graph_of(lambda b=b: self._issue(b, whole)) for b in range(self.nb)]
+            if not whole:
                 self._update = self._graph_of(self.step.optimizer.step)
 
     def prime(self) -> None:
@@ -277,11 +284,12 @@ class StepPipeline:
     def run(self, k: int) -> None:
         b = k % self.nb
         step = self.step
+        whole = not self.allreduce or self.peer is not None
         if self._whole is not None:
             self._whole[b].replay()
         else:
-            self._issue(b, not self.allreduce)
-        if not self.allreduce:
+            self._issue(b, whole)
+        if whole:
             return
         # Several ranks: the collective sits between the weight gradients and the update with nothing
         # beside it.  (Measured on two GPUs: starting the coordinate gradient here instead, under the

@@ -44,14 +44,19 @@ def flatten_results(res, pos=0):
     return np.concatenate(flattened).reshape((-1,))
 
 
-def average_gradients(parameters, flat_grads=None):
+def average_gradients(parameters, flat_grads=None, peer=None):
     """Mean of the weight gradients over all ranks: ONE all-reduce of a flat bucket (296,452
     values for four 384-128-128-64-1 networks), the data-parallel replacement of the reference's
     per-variable concat + reduce_mean on the CPU (``trainer_multi_tower.py:137-179``).  A no-op
     without an initialised process group.  ``flat_grads``: the buffer all ``.grad`` tensors are
-    slices of (``FlatNadam.flat_grads``); it is reduced in place with no packing."""
+    slices of (``FlatNadam.flat_grads``); it is reduced in place with no packing.  ``peer``: a
+    ``PeerAllReduce`` -- the mean is then one kernel of this library over peer memory instead of the
+    library collective (and may be captured in a CUDA graph)."""
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return
+    if peer is not None and flat_grads is not None:
+        peer.mean_(flat_grads)
         return
     if flat_grads is not None:
         dist.all_reduce(flat_grads, op=dist.ReduceOp.SUM)
