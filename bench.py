@@ -575,7 +575,8 @@ def measure_fused_train(ctx, mols: int, steps: int, warmup: int, train_path: str
     loss = float(step.l2s[:batches[(steps - 1) % nb].n_mols].mean())
     ms, atoms = ctx.max_sum(ms, atoms)
     out = {"ms_per_step": ms / steps, "atoms_per_s": atoms / (ms * 1e-3), "steps": steps, "n_gpus": world,
-           "final_loss": loss, "gpu_launches_per_step": FusedTrainStep.KERNELS, "resident_batches": nb,
+           "final_loss": loss, "gpu_launches_per_step": FusedTrainStep.KERNELS + (1 if peer is not None else 0),
+           "resident_batches": nb,
            "pipelined": pipelined,
            "collective": ("none (one rank)" if world == 1 else
                           ("mean of the flat gradient buffer (%d float32 values) by one kernel of the library over peer "
