@@ -86,6 +86,18 @@ class PackedDataset:
         top = np.sort(self.counts)[-k:] if k else np.zeros(0, np.int64)
         return int(top.sum()), k
 
+    def batch_slices(self, batch_size: int):
+        """For an UNSHUFFLED pass: per batch, the row range of every molecule within the batch, as ready-made
+        ``slice`` objects (cutting a batch result into per-molecule arrays is a third faster with them than
+        with freshly built slices; made once per data set and batch size)."""
+        cache = self.__dict__.setdefault("_batch_slices", {})
+        if batch_size not in cache:
+            ptr = self.ptr.tolist()
+            n = self.num_mols()
+            cache[batch_size] = [[slice(ptr[m] - ptr[b0], ptr[m + 1] - ptr[b0]) for m in range(b0, min(b0 + batch_size, n))]
+                                 for b0 in range(0, n, batch_size)]
+        return cache[batch_size]
+
     def mol_acs(self) -> np.ndarray:
         """Atoms per element of every molecule ``[n_mols, 4]``, counted once per data set."""
         if self._mol_acs is None:

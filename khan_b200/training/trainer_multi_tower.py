@@ -599,12 +599,13 @@ class TrainerMultiTower:
         if ring is None or ring[0].shape[0] < cap:
             ring = self._grad_ring = [torch.empty((cap, 3), dtype=torch.float32).pin_memory() for _ in range(3)]
         it = BatchFeeder(packed, batch_size, False, None, devices=self.towers, depth=2, hold=1)
-        pending = []      # (host buffer, event, n_atoms, offsets) of batches whose copy is in flight
+        pending = []      # (host buffer, event, n_atoms, batch index) of batches whose copy is in flight
+        slices = packed.batch_slices(batch_size)
 
         def finished(entry):
-            buf, evt, n, offsets = entry
+            buf, evt, n, k = entry
             evt.synchronize()
-            return _split_rows(buf[:n].numpy().copy(), offsets)
+            return list(map(buf[:n].numpy().copy().__getitem__, slices[k]))
 
         try:
             with torch.cuda.device(self.towers[0]), torch.no_grad():
@@ -617,7 +618,7 @@ class TrainerMultiTower:
                     buf[:n].copy_(sb.grads[:, :n].t(), non_blocking=True)      # (n_atoms, 3), strided read on the device
                     evt = torch.cuda.Event()
                     evt.record()
-                    pending.append((buf, evt, n, fed.offsets_host))
+                    pending.append((buf, evt, n, fed.index))
                     if len(pending) == len(ring):       # the buffer of batch k + 1 must be free again
                         yield from finished(pending.pop(0))
         finally:
