@@ -546,6 +546,9 @@ int ani_peer_connect(ani_peer* p, int rank_q, const void* handle64);
 int ani_peer_connect_raw(ani_peer* p, int rank_q, void* block);
 void* ani_peer_block(ani_peer* p);
 int ani_peer_set_spin_limit(ani_peer* p, unsigned tries);
+int ani_peer_set_two_halves(ani_peer* p, int on);   /* on: every rank forms the mean of its slice and the slices are
+                                                       exchanged (default for more than four ranks); off: every rank
+                                                       sums everything.  The same setting on every rank. */
 int ani_peer_mean_f32(ani_peer* p, float* buffer, long long n, void* stream);
 int ani_peer_destroy(ani_peer* p);
 

@@ -141,6 +141,7 @@ SIGNATURES = {
     "ani_peer_connect_raw": (_i, [_vp, _i, _vp]),
     "ani_peer_block": (_vp, [_vp]),
     "ani_peer_set_spin_limit": (_i, [_vp, ctypes.c_uint]),
+    "ani_peer_set_two_halves": (_i, [_vp, _i]),
     "ani_peer_mean_f32": (_i, [_vp, _vp, ctypes.c_longlong, _vp]),
     "ani_peer_destroy": (_i, [_vp]),
     "ani_charge_f32": (_i, [_vp] * 6 + [_i, _i, _vp, _vp]),

@@ -954,6 +954,7 @@ int ani_feeder_destroy(ani_feeder* f)
 
 struct ani_peer {
     int device = 0, rank = 0, world = 1, grid = 1;
+    int two_halves = 0;                  // slice means + exchange (more than four ranks)
     long long capacity = 0;              // floats per staging buffer
     unsigned char* block = nullptr;      // local: [flags | staging 0 | staging 1]
     ani::PeerState* state = nullptr;     // local
@@ -973,12 +974,13 @@ int ani_peer_create(int rank, int world, long long n_floats, ani_peer** out)
     cudaDeviceProp prop;
     cudaError_t e = cudaGetDevice(&p->device);
     if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, p->device);
-    const size_t bytes = ani::kPeerFlagBytes + 2 * (size_t)p->capacity * sizeof(float);
+    // [flags | staging 0, 1 (every rank's contribution) | staging 2, 3 (this rank's slice means)]
+    const size_t bytes = ani::kPeerFlagBytes + 4 * (size_t)p->capacity * sizeof(float);
     if (e == cudaSuccess) e = cudaMalloc(&p->block, bytes);
     if (e == cudaSuccess) e = cudaMemset(p->block, 0, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&p->state, sizeof(ani::PeerState));
     if (e == cudaSuccess) {
-        ani::PeerState init{0ull, 0ull, 0u, ani::kPeerSpinLimit};
+        ani::PeerState init{0ull, 0ull, 0ull, 0u, ani::kPeerSpinLimit};
         e = cudaMemcpy(p->state, &init, sizeof(init), cudaMemcpyHostToDevice);
     }
     if (e != cudaSuccess) {
@@ -989,8 +991,9 @@ int ani_peer_create(int rank, int world, long long n_floats, ani_peer** out)
     }
     const long long groups = p->capacity / 4;
     p->grid = (int)std::max<long long>(1, std::min<long long>((groups + ani::kPeerThreads - 1) / ani::kPeerThreads,
-                                                               prop.multiProcessorCount));
+                                                               std::min(prop.multiProcessorCount, ani::kPeerMaxBlocks)));
     p->peer_block[rank] = p->block;
+    p->two_halves = world > 4 ? 1 : 0;
     *out = p;
     return ANI_OK;
 }
@@ -1028,6 +1031,13 @@ int ani_peer_connect_raw(ani_peer* p, int q, void* block)
 
 void* ani_peer_block(ani_peer* p) { return p ? p->block : nullptr; }
 
+int ani_peer_set_two_halves(ani_peer* p, int on)
+{
+    if (!p) return ANI_ERR_NULL_POINTER;
+    p->two_halves = on ? 1 : 0;
+    return ANI_OK;
+}
+
 int ani_peer_set_spin_limit(ani_peer* p, unsigned tries)
 {
     if (!p) return ANI_ERR_NULL_POINTER;
@@ -1053,6 +1063,7 @@ int ani_peer_mean_f32(ani_peer* p, float* buffer, long long n, void* stream)
     }
     a.state = p->state;
     a.inv_world = 1.0f / (float)p->world;
+    a.two_halves = p->two_halves;
     ani::peer_mean_kernel<<<p->grid, ani::kPeerThreads, 0, (cudaStream_t)stream>>>(a);
     ANI_CUDA(cudaGetLastError());
     return ANI_OK;

@@ -20,10 +20,12 @@ import torch
 from .. import _lib
 
 
-# Every rank reads the staging buffers of ALL ranks, so the bytes a rank pulls over NVLink grow with the
-# number of ranks.  Measured on the 296,464-value gradient buffer of the training step: faster than the NCCL
-# all-reduce on 2 and 4 GPUs (0.230 / 0.243 ms per step against 0.237 / 0.246), slower on 8 (0.274 against
-# 0.263: 8.3 MB per rank and step, and NCCL reduces inside the switch there).
+# Measured on the 296,464-value gradient buffer of the training step (ms per step, peer kernel / NCCL
+# all-reduce): 2 GPUs 0.230 / 0.237, 4 GPUs 0.243 / 0.246, 8 GPUs 0.274 / 0.263 -- with every rank summing
+# all staging buffers a rank pulls 8.3 MB per step over NVLink on 8 GPUs, and NCCL reduces inside the
+# switch there.  The two-halves form (slice means + exchange of the slices) moves a quarter of the bytes
+# but pays a second round of flags: on 4 GPUs 0.253 against 0.243.  So the callers get the peer kernel
+# for up to four ranks and the library all-reduce above.
 PEER_MAX_RANKS = 4
 
 
@@ -32,8 +34,15 @@ class PeerAllReduce:
     most ``n_floats`` values (a multiple of 4, 16-byte aligned).  Every rank must construct it and call
     ``mean_`` the same number of times, on one stream per rank."""
 
-    def __init__(self, n_floats: int, device, group=None):
+    def __init__(self, n_floats: int, device, group=None, two_halves=None):
+        """``two_halves``: True = every rank forms the mean of its slice and the slices are exchanged, False =
+        every rank sums everything, None = the library's choice (two halves above four ranks).  The
+        environment variable KHAN_B200_PEER_FORM ("two_halves" / "one") overrides it, for measurements."""
+        import os
         import torch.distributed as dist
+        form = os.environ.get("KHAN_B200_PEER_FORM")
+        if form in ("two_halves", "one"):
+            two_halves = form == "two_halves"
         self.device = torch.device(device)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.n_floats = int(n_floats)
@@ -42,6 +51,8 @@ class PeerAllReduce:
         with torch.cuda.device(self.device):
             status = L.ani_peer_create(self.rank, self.world, self.n_floats, ctypes.byref(self._ptr))
             mine = (ctypes.c_ubyte * 64)()
+            if status == 0 and two_halves is not None:
+                status = L.ani_peer_set_two_halves(self._ptr, int(bool(two_halves)))
             if status == 0:
                 status = L.ani_peer_handle(self._ptr, mine)
             handles = [None] * self.world
