@@ -15,8 +15,8 @@
 // staging[parity] is rewritten two steps later, and a rank cannot get there before every peer has
 // arrived at the step in between, i.e. has finished reading -- so one flag per (rank, peer) and two
 // staging buffers are all the synchronisation there is.  The step number lives in device memory and
-// is advanced by the kernel itself, so the launch can sit in a CUDA graph.  No NCCL call, no
-// multicast object; the grid is one block per SM at most, so that all blocks are resident while
+// is advanced by the kernel itself, so the launch can sit in a CUDA graph.  No NCCL call, plain
+// peer mappings only; the grid is one block per SM at most, so that all blocks are resident while
 // they wait.
 //
 // A second form (ani_peer_set_two_halves; the default above four ranks) moves fewer bytes: after the
