@@ -163,7 +163,7 @@ __device__ __forceinline__ bool decode_slot(const MolGroupInfo* tab, const unsig
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
+__global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 20)
     featurize_mol_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
                          const int* __restrict__ types, const int* __restrict__ mol_offsets,
                          const int* __restrict__ mol_counts, int n_mols, int n_atoms,
