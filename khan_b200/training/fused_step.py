@@ -115,6 +115,13 @@ class FusedTrainStep:
         sb.run_sort(stream)
         sb.run_featurize(stream)
 
+    def featurize_pass(self, sb: StagedBatch) -> None:
+        """The same as ``featurize`` through the one-call entry point (one argument block, one call)."""
+        self._check(sb)
+        a = self._pass_args(sb)
+        a.phases = _lib.PASS_FEATURIZE
+        _lib.check(_lib.lib().ani_network_pass_f32(ctypes.byref(a), self._stream()), "ani_network_pass_f32")
+
     def networks(self, sb: StagedBatch, labels: torch.Tensor, feature_grad: bool = True) -> None:
         """Weight packing, networks forward, molecule energies + MSE gradient, networks backward.
         Afterwards ``self.l2s[:n_mols]`` holds the squared errors, the dz buffers the layer
@@ -176,10 +183,13 @@ class FusedTrainStep:
         a.features = sb.features.data_ptr()
         return a
 
-    def forward_backward(self, sb: StagedBatch, labels: torch.Tensor, feature_grad: bool = True) -> None:
+    def forward_backward(self, sb: StagedBatch, labels: torch.Tensor, feature_grad: bool = True,
+                         featurized: bool = False) -> None:
         """Everything up to the weight gradients, in order on the current stream: weight packing, sort,
         featurize, networks forward, molecule energies + MSE gradient, networks backward, zero + weight
-        gradients -- one C-ABI call (``ani_network_pass_f32``)."""
+        gradients -- one C-ABI call (``ani_network_pass_f32``).  ``featurized``: sort + featurize of this
+        batch have been done already (``featurize``, say on another stream beside the previous batch's
+        networks) and are left out."""
         self._check(sb)
         stream = self._stream()
         if self.model.packed_weights() is None:
@@ -187,8 +197,8 @@ class FusedTrainStep:
         a = self._pass_args(sb)
         a.feature_grads = sb.upstream.data_ptr() if feature_grad else None
         a.labels, a.grad_scale = labels.data_ptr(), 1.0 / max(sb.n_mols, 1)
-        a.phases = (_lib.PASS_PACK | _lib.PASS_FEATURIZE | _lib.PASS_FORWARD | _lib.PASS_ENERGY | _lib.PASS_BACKWARD
-                    | _lib.PASS_WEIGHT_GRAD)
+        a.phases = (_lib.PASS_PACK | (0 if featurized else _lib.PASS_FEATURIZE) | _lib.PASS_FORWARD | _lib.PASS_ENERGY
+                    | _lib.PASS_BACKWARD | _lib.PASS_WEIGHT_GRAD)
         _lib.check(_lib.lib().ani_network_pass_f32(ctypes.byref(a), stream), "ani_network_pass_f32")
         self._args_key = None      # the per-phase argument blocks (networks / weight_gradients) are stale now
 

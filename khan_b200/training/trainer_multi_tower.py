@@ -339,12 +339,14 @@ class TrainerMultiTower:
         need_coord = "tower_coord_grads" in names or "tower_force_rmses" in names or "train_op_forces" in names
         np_dt = np.float32 if self.precision == torch.float32 else np.float64
         packed = PackedDataset.from_raw(dataset, np_dt)
-        it = BatchFeeder(packed, batch_size, shuffle, fuzz, devices=self.towers, depth=2, hold=self.num_towers)
         fused_names = {"train_op", "train_op_rmse", "train_op_mse", "unordered_l2s", "tower_l2s", "tower_exp_loss",
                        "tower_bids", "_device_l2s"}
         fused = (self.num_towers == 1 and isinstance(self.optimizer, FlatNadam) and self.model.fused
                  and len(training) == 1 and training[0] != "train_op_forces" and set(names) <= fused_names
                  and packed.ys is not None and packed.num_mols() > 0)
+        # the fused path works on two batches at a time (this one's networks, the next one's featurizer)
+        it = BatchFeeder(packed, batch_size, shuffle, fuzz, devices=self.towers, depth=3 if fused else 2,
+                         hold=2 if fused else self.num_towers)
         try:
             if fused:
                 yield from self._fused_rounds(it, names, training[0], packed.capacity(batch_size), before_hooks)
@@ -363,19 +365,43 @@ class TrainerMultiTower:
         from ..staged import StagedBatch
         from .fused_step import FusedTrainStep
         cap_atoms, cap_mols = max(capacity[0], 1), max(capacity[1], 1)
-        if self._fused is None or self._fused[0][0] < cap_atoms or self._fused[0][1] < cap_mols:
-            dev = self.towers[0]
-            self._fused = ((cap_atoms, cap_mols), StagedBatch(cap_atoms, cap_mols, device=dev),
-                           FusedTrainStep(self.model, self.optimizer, cap_atoms, cap_mols, device=dev))
-        _, sb, step = self._fused
         dev = self.towers[0]
-        for fed in it:
+        if self._fused is None or self._fused[0][0] < cap_atoms or self._fused[0][1] < cap_mols:
+            self._fused = ((cap_atoms, cap_mols),
+                           [StagedBatch(cap_atoms, cap_mols, device=dev), StagedBatch(cap_atoms, cap_mols, device=dev)],
+                           FusedTrainStep(self.model, self.optimizer, cap_atoms, cap_mols, device=dev),
+                           torch.cuda.Stream(device=dev))
+        _, sbs, step, side = self._fused
+        # Two batches in flight: sort + featurize of the NEXT batch run on a side stream beside the network
+        # kernels of this one (they need nothing but the coordinates; the network kernels leave a quarter of
+        # the SMs free), as in StepPipeline.  The sequence of weights is that of the serial order.
+        feeder = iter(it)
+
+        def start(fed, sb):
+            """Sort + featurize of a fed batch on the side stream, behind everything enqueued on the main one
+            (the previous use of ``sb`` among it)."""
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                fed.wait()
+                sb.adopt(fed)
+                step.featurize_pass(sb)
+
+        with torch.cuda.device(dev):
+            fed = next(feeder, None)
+            if fed is not None:
+                start(fed, sbs[0])
+        k = 0
+        while fed is not None:
             if before_hooks is not None:
                 self._run_hooks(before_hooks)
             with torch.cuda.device(dev), torch.no_grad():
-                fed.wait()
-                sb.adopt(fed)
-                step.forward_backward(sb, fed.ys, feature_grad=False)
+                sb = sbs[k & 1]
+                main = torch.cuda.current_stream(dev)
+                main.wait_stream(side)                      # this batch's features are there
+                nxt = next(feeder, None)
+                if nxt is not None:
+                    start(nxt, sbs[(k + 1) & 1])
+                step.forward_backward(sb, fed.ys, feature_grad=False, featurized=True)
                 l2 = step.l2s[:fed.n_mols]
                 rmse = None
                 if kind != "train_op_mse" or "tower_exp_loss" in names:
@@ -399,6 +425,7 @@ class TrainerMultiTower:
                         row.append([float(torch.exp(rmse.double()))])
                     elif n == "tower_bids":
                         row.append([np.array(fed.index)])
+                fed, k = nxt, k + 1
             yield row
 
     def _feed_rounds(self, it, names, training, need_grad, need_coord, before_hooks):
