@@ -355,6 +355,15 @@ int ani_clip_rows_f32(float* params, const int* row_offsets, const int* row_leng
                       void* stream);
 
 /*
+ * The gradient of the reference's training losses from the gradient of the mean squared error, one launch:
+ * grads[0 .. n) *= 1 / (2 rmse)  (kind 1: the rmse loss)  or  exp(rmse) / (2 rmse)  (kind 2: exp(rmse), the
+ * loss khan minimises, khan/training/trainer_multi_tower.py:390-396), rmse = sqrt(mean(l2s[0 .. n_mols))),
+ * formed on the device; rmse_out (one float, device; may be NULL) receives it.
+ */
+int ani_scale_by_loss_f32(float* grads, long long n, const float* l2s, int n_mols, int kind, float* rmse_out,
+                          void* stream);
+
+/*
  * AniCharge -- replaces the op of gpu_featurizer/ani_charges.cpp:45-56,58-113 (CPU, float and
  * double) and gpu_featurizer/ani_charges_gpu.cu:60-128 (GPU, float only).  Damped Coulomb
  * energy of every molecule,

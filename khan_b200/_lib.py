@@ -126,6 +126,7 @@ SIGNATURES = {
     "ani_molecule_energy_f32": (_i, [_vp] * 4 + [_i, _i, _vp, ctypes.c_float, _vp, _vp, _vp, _vp]),
     "ani_nadam_step_f32": (_i, [_vp] * 5 + [ctypes.c_longlong, _vp, _vp, _vp]),
     "ani_clip_rows_f32": (_i, [_vp, _vp, _vp, _i, ctypes.c_float, _vp]),
+    "ani_scale_by_loss_f32": (_i, [_vp, ctypes.c_longlong, _vp, _i, _i, _vp, _vp]),
     "ani_host_pack_batch": (_i, [_vp]),
     "ani_network_pass_f32": (_i, [ctypes.POINTER(PassArgs), _vp]),
     "ani_feeder_create": (_i, [_i, _vp, _i, ctypes.POINTER(_vp)]),

@@ -857,6 +857,17 @@ int ani_clip_rows_f32(float* params, const int* row_offsets, const int* row_leng
     return ANI_OK;
 }
 
+int ani_scale_by_loss_f32(float* grads, long long n, const float* l2s, int n_mols, int kind, float* rmse_out,
+                          void* stream)
+{
+    if (n < 0 || n_mols <= 0 || (kind != 1 && kind != 2)) return ANI_ERR_BAD_SIZE;
+    if (!l2s || (n > 0 && !grads)) return ANI_ERR_NULL_POINTER;
+    const long long blocks = std::max<long long>(1, std::min<long long>((n + kOptimThreads - 1) / kOptimThreads, 296));
+    loss_scale_kernel<<<(int)blocks, kOptimThreads, 0, (cudaStream_t)stream>>>(grads, n, l2s, n_mols, kind, rmse_out);
+    ANI_CUDA(cudaGetLastError());
+    return ANI_OK;
+}
+
 int ani_charge_f32(const float* xs, const float* ys, const float* zs, const float* qs,
                    const int* mol_offsets, const int* mol_atom_counts, int n_mols, int n_atoms,
                    float* charge_energies, void* stream)

@@ -114,4 +114,34 @@ __global__ void __launch_bounds__(kOptimThreads)
     }
 }
 
+// Gradient of the reference's training losses from the gradient of the mean squared error: with
+// mse = mean(l2s) and rmse = sqrt(mse), d rmse = d mse / (2 rmse) and d exp(rmse) = exp(rmse) d mse / (2 rmse)
+// (khan/training/trainer_multi_tower.py:390-396 minimises exp(rmse)).  Every block forms the mean of the
+// n_mols squared errors itself (the same order in every block, so the same factor) and scales its part of
+// the gradient buffer; block 0 also writes the rmse.  kind: 1 = rmse, 2 = exp(rmse).
+__global__ void __launch_bounds__(kOptimThreads)
+    loss_scale_kernel(float* __restrict__ grads, long long n, const float* __restrict__ l2s, int n_mols, int kind,
+                      float* __restrict__ rmse_out)
+{
+    __shared__ float warp_sums[kOptimThreads / kWarp];
+    __shared__ float factor_sh;
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < n_mols; i += kOptimThreads) acc += l2s[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
+    if (lane_id() == 0) warp_sums[warp_id()] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < kOptimThreads / kWarp; w++) total += warp_sums[w];
+        const float rmse = fmaxf(sqrtf(total / (float)max(n_mols, 1)), 1e-30f);
+        factor_sh = (kind == 2 ? expf(rmse) : 1.0f) / (2.0f * rmse);
+        if (blockIdx.x == 0 && rmse_out) *rmse_out = rmse;
+    }
+    __syncthreads();
+    const float f = factor_sh;
+    for (long long i = (long long)blockIdx.x * kOptimThreads + threadIdx.x; i < n; i += (long long)gridDim.x * kOptimThreads)
+        grads[i] *= f;
+}
+
 }  // namespace ani

@@ -15,13 +15,14 @@ reload the best weights, halve the learning rate and add 128 to the batch size.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 import time
 
 import numpy as np
 import torch
 
-from .. import ani_mod
+from .. import _lib, ani_mod
 from ..data.feeder import BatchFeeder, PackedDataset
 from ..model import activations
 from ..model.nn import MoleculeNN
@@ -372,6 +373,8 @@ class TrainerMultiTower:
                            FusedTrainStep(self.model, self.optimizer, cap_atoms, cap_mols, device=dev),
                            torch.cuda.Stream(device=dev))
         _, sbs, step, side = self._fused
+        if getattr(self, "_rmse_buf", None) is None:
+            self._rmse_buf = torch.zeros((), dtype=torch.float32, device=dev)
         # Two batches in flight: sort + featurize of the NEXT batch run on a side stream beside the network
         # kernels of this one (they need nothing but the coordinates; the network kernels leave a quarter of
         # the SMs free), as in StepPipeline.  The sequence of weights is that of the serial order.
@@ -404,12 +407,15 @@ class TrainerMultiTower:
                 step.forward_backward(sb, fed.ys, feature_grad=False, featurized=True)
                 l2 = step.l2s[:fed.n_mols]
                 rmse = None
-                if kind != "train_op_mse" or "tower_exp_loss" in names:
+                if kind in ("train_op", "train_op_rmse"):
+                    # one launch: rmse on the device, the weight gradients scaled by d loss / d mse
+                    rmse = self._rmse_buf
+                    g = self.optimizer.flat_grads
+                    _lib.check(_lib.lib().ani_scale_by_loss_f32(
+                        g.data_ptr(), g.numel(), l2.data_ptr(), fed.n_mols, 2 if kind == "train_op" else 1,
+                        rmse.data_ptr(), ctypes.c_void_p(main.cuda_stream)), "ani_scale_by_loss_f32")
+                elif "tower_exp_loss" in names:
                     rmse = l2.mean().sqrt().clamp_min(1e-30)
-                if kind == "train_op":
-                    self.optimizer.flat_grads.mul_(torch.exp(rmse) / (2.0 * rmse))
-                elif kind == "train_op_rmse":
-                    self.optimizer.flat_grads.mul_(1.0 / (2.0 * rmse))
                 average_gradients(self.parameters, self.optimizer.flat_grads)
                 self.optimizer.step()
                 self.global_step += 1
