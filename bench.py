@@ -648,7 +648,7 @@ def run_frontend_workload(args):
     n_atoms = sum(len(m) for m in mols)
     tr = TrainerMultiTower(None, [ctx.dev], layer_sizes=(128, 128, 64, 1), seed=1)
     calls = (("predict", lambda: tr.predict(ds, batch_size=2048)),
-             ("coordinate_gradients", lambda: sum(1 for _ in tr.coordinate_gradients(ds, batch_size=2048))),
+             ("coordinate_gradients", lambda: len(list(tr.coordinate_gradients(ds, batch_size=2048)))),
              ("train_epoch_exp_rmse_max_norm", lambda: sum(1 for _ in tr.feed_dataset(
                  ds, True, [tr.train_op], 1024, before_hooks=tr.max_norm_ops))),
              ("train_epoch_mse", lambda: sum(1 for _ in tr.feed_dataset(ds, True, [tr.train_op_mse], 1024))))

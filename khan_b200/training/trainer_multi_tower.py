@@ -16,6 +16,7 @@ reload the best weights, halve the learning rate and add 128 to the batch size.
 from __future__ import annotations
 
 import ctypes
+import itertools
 import os
 import time
 
@@ -575,14 +576,19 @@ class TrainerMultiTower:
         (``trainer_multi_tower.py:580-614``).  On one float32 tower with the fused networks the
         batches go through the allocation-free evaluator (``khan_b200.inference.EnergyForces``: C-ABI
         calls only, no host wait per batch); ``use_evaluator=False`` forces the autograd path."""
+        # an iterator, as in the reference; the per-batch lists are chained in C, so a molecule costs no
+        # Python frame of its own (two nested generators had cost more than cutting the arrays)
         if use_evaluator and self._evaluator_usable(dataset):
-            yield from self._evaluator_gradients(dataset, batch_size)
-            return
+            return itertools.chain.from_iterable(self._evaluator_gradients(dataset, batch_size))
+        return itertools.chain.from_iterable(self._autograd_gradients(dataset, batch_size))
+
+    def _autograd_gradients(self, dataset, batch_size):
+        """One list of per-molecule ``(n, 3)`` arrays per batch, through ``feed_dataset`` and autograd."""
         ops = [self.tower_coord_grads, self.tower_mos, self.tower_bids]
         for grads, mos, ids in self.feed_dataset(dataset, False, ops, batch_size):
             for k in np.argsort(np.array(ids)):
                 # one (n_atoms, 3) array per batch, cut once into per-molecule pieces
-                yield from _split_rows(np.stack(grads[k], axis=1), mos[k])
+                yield _split_rows(np.stack(grads[k], axis=1), mos[k])
 
     def _evaluator_usable(self, dataset) -> bool:
         """One float32 CUDA tower with the fused networks: batches can go through the
@@ -622,7 +628,7 @@ class TrainerMultiTower:
         return preds, l2s
 
     def _evaluator_gradients(self, dataset, batch_size):
-        """Gradients of all molecules through the evaluator.  The result of a batch is copied to a pinned
+        """Gradients of all molecules through the evaluator, one list per batch.  The result of a batch is copied to a pinned
         host buffer behind its kernels, and the host cuts the PREVIOUS batch into per-molecule arrays while
         the GPU works on this one (cutting 32,768 molecules takes as long as computing them)."""
         packed = PackedDataset.from_raw(dataset, np.float32)
@@ -653,11 +659,11 @@ class TrainerMultiTower:
                     evt.record()
                     pending.append((buf, evt, n, fed.index))
                     if len(pending) == len(ring):       # the buffer of batch k + 1 must be free again
-                        yield from finished(pending.pop(0))
+                        yield finished(pending.pop(0))
         finally:
             it.close()
         for entry in pending:
-            yield from finished(entry)
+            yield finished(entry)
 
     def eval_abs_rmse(self, dataset, batch_size=1024):
         """Absolute RMSE of the energies in kcal/mol (``trainer_multi_tower.py:560-578``)."""
