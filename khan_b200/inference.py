@@ -80,14 +80,28 @@ class EnergyForces:
         a.x_grads, a.y_grads, a.z_grads = g, g + cap * esz, g + 2 * cap * esz
         return a
 
+    def featurize(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None) -> None:
+        """Sort + featurize of the batch staged in ``sb`` only (one C-ABI call): they need nothing but the
+        coordinates, so a caller may run them for the NEXT batch on another stream beside the network kernels
+        of this one and then call ``run(..., featurized=True)``."""
+        if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
+            raise ValueError("batch does not fit this evaluator")
+        _lib.same_device(self.device, sb.features, sb.x, where="EnergyForces.featurize")
+        if stream is None:
+            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        a = self._pass_args(sb)
+        a.phases = _lib.PASS_FEATURIZE
+        _lib.check(_lib.lib().ani_network_pass_f32(ctypes.byref(a), stream), "ani_network_pass_f32")
+
     def run(self, sb: StagedBatch, stream: ctypes.c_void_p | None = None, pack: bool = True,
-            forces: bool = True) -> None:
+            forces: bool = True, featurized: bool = False) -> None:
         """One pass over the batch staged in ``sb`` -- one C-ABI call (``ani_network_pass_f32``).  Afterwards
         ``self.mol_energy[:sb.n_mols]`` holds the molecule energies and ``sb.grads[:, :sb.n_atoms]`` dE/dx,
         dE/dy, dE/dz (forces are their negatives).  ``pack=False`` skips the refresh of the pre-packed
         weights: for a caller that packed them (``model.pack_weights``) after the last change of the
         weights, e.g. once before a series of passes that run side by side on several streams.
-        ``forces=False`` stops after the molecule energies (``predict``)."""
+        ``forces=False`` stops after the molecule energies (``predict``); ``featurized=True`` leaves sort +
+        featurize out (``featurize`` has run for this batch)."""
         if sb.n_atoms > self.n_atoms_cap or sb.n_mols > self.n_mols_cap or sb.dtype != torch.float32:
             raise ValueError("batch does not fit this evaluator")
         _lib.same_device(self.device, sb.features, sb.x, where="EnergyForces.run")
@@ -97,8 +111,8 @@ class EnergyForces:
             self.model.pack_weights(stream)          # allocates the packed copy (first use)
             pack = False
         a = self._pass_args(sb)
-        a.phases = ((_lib.PASS_PACK if pack else 0) | _lib.PASS_FEATURIZE | _lib.PASS_FORWARD | _lib.PASS_ENERGY
-                    | ((_lib.PASS_BACKWARD | _lib.PASS_COORD_GRAD) if forces else 0))
+        a.phases = ((_lib.PASS_PACK if pack else 0) | (0 if featurized else _lib.PASS_FEATURIZE) | _lib.PASS_FORWARD
+                    | _lib.PASS_ENERGY | ((_lib.PASS_BACKWARD | _lib.PASS_COORD_GRAD) if forces else 0))
         _lib.check(_lib.lib().ani_network_pass_f32(ctypes.byref(a), stream), "ani_network_pass_f32")
 
     KERNELS_PER_PASS = 7   # weight packing (unless pack=False), sort, featurize, mlp forward, molecule sums, mlp backward, featurize_grad

@@ -612,17 +612,39 @@ class TrainerMultiTower:
         molecule sums as four C-ABI calls per batch, the weights packed once."""
         packed = PackedDataset.from_raw(dataset, np.float32)
         sb, ev = self._evaluator(packed, batch_size)
-        it = BatchFeeder(packed, batch_size, False, None, devices=self.towers, depth=2, hold=1)
+        dev = self.towers[0]
+        # two batches at a time: sort + featurize of the next one on a side stream beside the networks of this one
+        twin = getattr(self, "_infer_twin", None)
+        if twin is None or twin[0].n_atoms_cap < sb.n_atoms_cap or twin[0].n_mols_cap < sb.n_mols_cap:
+            from ..staged import StagedBatch
+            twin = self._infer_twin = (StagedBatch(sb.n_atoms_cap, sb.n_mols_cap, device=dev), torch.cuda.Stream(device=dev))
+        sbs, side = (sb, twin[0]), twin[1]
+        it = BatchFeeder(packed, batch_size, False, None, devices=self.towers, depth=3, hold=2)
         preds, l2s = [], []
+
+        def start(fed, target):
+            side.wait_stream(torch.cuda.current_stream(dev))      # the previous use of `target` is among it
+            with torch.cuda.stream(side):
+                fed.wait()
+                target.adopt(fed)
+                ev.featurize(target)
+
         try:
-            with torch.cuda.device(self.towers[0]), torch.no_grad():
-                for k, fed in enumerate(it):
-                    fed.wait()
-                    sb.adopt(fed)
-                    ev.run(sb, pack=(k == 0), forces=False)
+            with torch.cuda.device(dev), torch.no_grad():
+                feeder = iter(it)
+                fed, k = next(feeder, None), 0
+                if fed is not None:
+                    start(fed, sbs[0])
+                while fed is not None:
+                    torch.cuda.current_stream(dev).wait_stream(side)
+                    nxt = next(feeder, None)
+                    if nxt is not None:
+                        start(nxt, sbs[(k + 1) & 1])
+                    ev.run(sbs[k & 1], pack=(k == 0), forces=False, featurized=True)
                     preds.append(ev.mol_energy[:fed.n_mols].clone())
                     if fed.ys is not None:
                         l2s.append((preds[-1] - fed.ys) ** 2)
+                    fed, k = nxt, k + 1
         finally:
             it.close()
         return preds, l2s
