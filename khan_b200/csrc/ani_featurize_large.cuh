@@ -40,7 +40,7 @@ template <typename T> struct LargeFwdWarpShared {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 24 : 1)
+__global__ void __launch_bounds__(kWarp, sizeof(T) == 4 ? 32 : 1)
     featurize_large_kernel(const T* __restrict__ xs, const T* __restrict__ ys, const T* __restrict__ zs,
                            const int* __restrict__ types, const int* __restrict__ mol_offsets,
                            const int* __restrict__ mol_counts, int n_mols, int n_atoms, int rounds_in_grid,
