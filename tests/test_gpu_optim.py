@@ -93,3 +93,27 @@ def test_clip_rows_is_clip_by_norm_over_axis_one():
         assert (p.detach() - w).abs().max().item() <= 1e-6 * max(1.0, w.abs().max().item())
     assert float(params[0].detach().norm(dim=1).max()) <= 3.0 + 1e-5
     assert float(params[0].detach().norm(dim=1).max()) > 2.9          # the constraint was active
+
+
+@pytest.mark.parametrize("kind", [1, 2])
+def test_scale_by_loss_turns_the_mse_gradient_into_the_rmse_and_exp_rmse_gradients(kind):
+    """d rmse = d mse / (2 rmse), d exp(rmse) = exp(rmse) d mse / (2 rmse) with rmse = sqrt(mean(l2)):
+    the loss khan minimises (khan/training/trainer_multi_tower.py:390-396), against float64 numpy."""
+    import ctypes
+    import torch
+    from khan_b200 import _lib
+    rng = np.random.default_rng(kind)
+    for n, n_mols in ((296_464, 1024), (1000, 1), (37, 2049)):
+        g = rng.normal(size=n).astype(np.float32)
+        l2 = (rng.normal(size=n_mols) ** 2).astype(np.float32) * 0.01
+        rmse = np.sqrt(l2.astype(np.float64).mean())
+        factor = (np.exp(rmse) if kind == 2 else 1.0) / (2.0 * rmse)
+        dg, dl2 = torch.tensor(g, device="cuda"), torch.tensor(l2, device="cuda")
+        out_rmse = torch.zeros((), device="cuda")
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert _lib.lib().ani_scale_by_loss_f32(dg.data_ptr(), n, dl2.data_ptr(), n_mols, kind, out_rmse.data_ptr(),
+                                                stream) == 0
+        np.testing.assert_allclose(float(out_rmse), rmse, rtol=2e-6)
+        np.testing.assert_allclose(dg.cpu().numpy(), g.astype(np.float64) * factor, rtol=5e-6, atol=0)
+    assert _lib.lib().ani_scale_by_loss_f32(dg.data_ptr(), n, dl2.data_ptr(), n_mols, 3, None, stream) == -2
+    assert _lib.lib().ani_scale_by_loss_f32(dg.data_ptr(), n, dl2.data_ptr(), 0, 1, None, stream) == -2

@@ -207,6 +207,19 @@ def test_energy_forces_evaluator_matches_the_trainer():
     torch.cuda.synchronize()
     assert np.array_equal(other.mol_energy[:b.n_mols].cpu().numpy(), got_e)
     assert np.abs(sb.grads[:, :b.n_atoms].cpu().numpy().T - want_g).max() < 1e-4 * np.abs(want_g).max()
+    # the pass in two halves -- sort + featurize on one stream, the rest on another -- gives the same bits
+    keep_g = sb.grads[:, :b.n_atoms].clone()
+    sb.features.fill_(float("nan"))
+    sb.grads.zero_()
+    main = torch.cuda.current_stream()
+    st.wait_stream(main)
+    with torch.cuda.stream(st):
+        ev.featurize(sb)
+    main.wait_stream(st)
+    ev.run(sb, pack=False, featurized=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(ev.mol_energy[:b.n_mols].cpu().numpy(), got_e)
+    assert torch.equal(sb.grads[:, :b.n_atoms], keep_g)
 
 
 def test_fused_train_step_matches_the_autograd_step():
